@@ -1,0 +1,243 @@
+"""The cache manager: keys and values in fixed-size pages with a block table per request, one
+pool of pages per group of layers with the same needs, and slots for fixed-size per-request state.
+
+The reference keeps contiguous per-sequence buffers (crates/engine/src/flint.rs:436-478) and, for
+its sliding layers, a ring of 8192 rows (:26-28, :855-859); its only paging is virtual-memory
+growth in the other model's path (crates/cuda/kernels/vmm.cu:31-70).  Here:
+
+* a group is "full" (a request holds pages for every position) or "sliding" with a window W (a
+  request holds pages only for positions a later query can still see: after a step that leaves
+  the request at length n, blocks that lie wholly below n - W + 1 go back to the pool);
+* each group has its own pool and its own block table per request; a table lists the page of
+  every logical block (position // page_size), -1 where none is held;
+* pools are LIFO, so a page that was just given back is the next one handed out;
+* a request also holds one state slot for mixers with fixed-size state of their own.
+
+All of this is host bookkeeping; the device sees only the block tables the step function uploads.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+
+class OutOfPages(RuntimeError):
+    """A pool cannot supply the pages a step needs.  Nothing was allocated."""
+
+
+class OutOfSlots(RuntimeError):
+    """Every request slot is taken."""
+
+
+@dataclass(frozen=True)
+class GroupSpec:
+    kind: str                      # "full" | "sliding"
+    window: Optional[int] = None   # sliding: number of visible keys including the query's own position
+
+    def __post_init__(self):
+        if self.kind not in ("full", "sliding"):
+            raise ValueError(f"unknown cache group kind {self.kind!r}")
+        if self.kind == "sliding" and not (isinstance(self.window, int) and self.window > 0):
+            raise ValueError("a sliding group needs a positive window")
+
+
+class PagePool:
+    """Page ids 0..n-1 of one group; LIFO free list; every page is free or has exactly one owner."""
+
+    def __init__(self, num_pages: int):
+        self.num_pages = num_pages
+        self._free: List[int] = list(range(num_pages - 1, -1, -1))     # pop() hands out 0 first
+        self._owner: List[Optional[Hashable]] = [None] * num_pages
+
+    @property
+    def num_free(self) -> int:
+        return len(self._free)
+
+    def take(self, owner: Hashable) -> int:
+        if not self._free:
+            raise OutOfPages("no free page")
+        page = self._free.pop()
+        assert self._owner[page] is None, f"page {page} handed out twice"
+        self._owner[page] = owner
+        return page
+
+    def give_back(self, page: int, owner: Hashable) -> None:
+        if not 0 <= page < self.num_pages:
+            raise ValueError(f"page {page} outside the pool")
+        if self._owner[page] is None:
+            raise RuntimeError(f"page {page} freed twice")
+        if self._owner[page] != owner:
+            raise RuntimeError(f"page {page} belongs to {self._owner[page]!r}, not {owner!r}")
+        self._owner[page] = None
+        self._free.append(page)
+
+    def owner_of(self, page: int) -> Optional[Hashable]:
+        return self._owner[page]
+
+
+class SlotPool:
+    """Fixed-size per-request state lives in slot `s` of per-layer tensors [max_requests, ...]."""
+
+    def __init__(self, num_slots: int):
+        self.num_slots = num_slots
+        self._free = list(range(num_slots - 1, -1, -1))
+        self._used = set()
+
+    @property
+    def num_free(self) -> int:
+        return len(self._free)
+
+    def take(self) -> int:
+        if not self._free:
+            raise OutOfSlots(f"all {self.num_slots} request slots are in use")
+        s = self._free.pop()
+        self._used.add(s)
+        return s
+
+    def give_back(self, slot: int) -> None:
+        if slot not in self._used:
+            raise RuntimeError(f"slot {slot} freed twice")
+        self._used.remove(slot)
+        self._free.append(slot)
+
+
+@dataclass
+class _Request:
+    slot: int
+    length: int                         # tokens whose keys are in the cache
+    tables: List[List[int]]             # per group: page of each logical block, -1 where none
+    reserved: int = 0                   # tokens of the step in flight (pages held, not yet counted in length)
+
+
+class CacheManager:
+    def __init__(self, groups: Sequence[GroupSpec], page_size: int, num_pages: Sequence[int], max_requests: int):
+        if page_size <= 0:
+            raise ValueError("page_size must be positive")
+        if len(num_pages) != len(groups):
+            raise ValueError("one page count per group is needed")
+        self.groups = list(groups)
+        self.page_size = page_size
+        self.pools = [PagePool(n) for n in num_pages]
+        self.slots = SlotPool(max_requests)
+        self.requests: Dict[Hashable, _Request] = {}
+
+    # ------------------------------------------------------------------ requests
+    def add(self, rid: Hashable) -> int:
+        """Register a request; returns its state slot."""
+        if rid in self.requests:
+            raise KeyError(f"request {rid!r} is already live")
+        slot = self.slots.take()
+        self.requests[rid] = _Request(slot, 0, [[] for _ in self.groups])
+        return slot
+
+    def remove(self, rid: Hashable) -> None:
+        """The request ended (finished, aborted or preempted): every page and the slot go back."""
+        req = self.requests.pop(rid)
+        for g, table in enumerate(req.tables):
+            for page in reversed(table):
+                if page >= 0:
+                    self.pools[g].give_back(page, rid)
+        self.slots.give_back(req.slot)
+
+    def length(self, rid: Hashable) -> int:
+        return self.requests[rid].length
+
+    def slot(self, rid: Hashable) -> int:
+        return self.requests[rid].slot
+
+    def table(self, rid: Hashable, group: int) -> List[int]:
+        return self.requests[rid].tables[group]
+
+    # ------------------------------------------------------------------ pages for a step
+    def _first_needed_block(self, g: int, start: int) -> int:
+        """First logical block a step whose first new position is `start` reads in group g."""
+        spec = self.groups[g]
+        if spec.kind == "full":
+            return 0
+        return max(0, start - spec.window + 1) // self.page_size
+
+    def pages_needed(self, rid: Hashable, n_new: int) -> List[int]:
+        """Pages each group's pool must supply so that the request can run n_new more tokens."""
+        req = self.requests[rid]
+        start, end = req.length, req.length + n_new
+        out = []
+        for g in range(len(self.groups)):
+            table = req.tables[g]
+            first = self._first_needed_block(g, start)
+            last = (end - 1) // self.page_size if end > 0 else -1
+            need = 0
+            for b in range(first, last + 1):
+                if b >= len(table) or table[b] < 0:
+                    need += 1
+            out.append(need)
+        return out
+
+    def can_reserve(self, wants: Sequence[Tuple[Hashable, int]]) -> bool:
+        total = [0] * len(self.groups)
+        for rid, n in wants:
+            for g, c in enumerate(self.pages_needed(rid, n)):
+                total[g] += c
+        return all(total[g] <= self.pools[g].num_free for g in range(len(self.groups)))
+
+    def reserve(self, rid: Hashable, n_new: int) -> None:
+        """Hold pages for the next n_new positions of the request (all groups, or none: raises
+        OutOfPages without changing anything)."""
+        req = self.requests[rid]
+        if req.reserved:
+            raise RuntimeError(f"request {rid!r} already has a step in flight")
+        need = self.pages_needed(rid, n_new)
+        for g, c in enumerate(need):
+            if c > self.pools[g].num_free:
+                raise OutOfPages(f"group {g} ({self.groups[g].kind}) needs {c} pages for request {rid!r}, "
+                                 f"{self.pools[g].num_free} are free")
+        start, end = req.length, req.length + n_new
+        for g in range(len(self.groups)):
+            table = req.tables[g]
+            first = self._first_needed_block(g, start)
+            last = (end - 1) // self.page_size if end > 0 else -1
+            while len(table) <= last:
+                table.append(-1)
+            for b in range(first, last + 1):
+                if table[b] < 0:
+                    table[b] = self.pools[g].take(rid)
+        req.reserved = n_new
+
+    def commit(self, rid: Hashable) -> None:
+        """The step in flight is done: its tokens count, and pages a window has passed go back."""
+        req = self.requests[rid]
+        req.length += req.reserved
+        req.reserved = 0
+        for g, spec in enumerate(self.groups):
+            if spec.kind != "sliding":
+                continue
+            # the next query sits at position `length` and sees keys > length - window
+            dead = max(0, req.length - spec.window + 1) // self.page_size     # blocks [0, dead) lie wholly below
+            table = req.tables[g]
+            for b in range(min(dead, len(table))):
+                if table[b] >= 0:
+                    self.pools[g].give_back(table[b], rid)
+                    table[b] = -1
+
+    def cancel(self, rid: Hashable) -> None:
+        """The step in flight did not run: pages taken for it stay with the request (they are
+        reused by its next step or returned by remove)."""
+        self.requests[rid].reserved = 0
+
+    # ------------------------------------------------------------------ invariants (tests)
+    def check(self) -> None:
+        for g, pool in enumerate(self.pools):
+            held = {}
+            for rid, req in self.requests.items():
+                for b, page in enumerate(req.tables[g]):
+                    if page < 0:
+                        continue
+                    assert page not in held, f"group {g}: page {page} held by {held[page]} and {(rid, b)}"
+                    held[page] = (rid, b)
+                    assert pool.owner_of(page) == rid, f"group {g}: page {page} owner {pool.owner_of(page)!r} != {rid!r}"
+            free = list(pool._free)
+            assert len(set(free)) == len(free), f"group {g}: a page is twice in the free list"
+            assert not (set(free) & set(held)), f"group {g}: a page is both free and held"
+            assert len(free) + len(held) == pool.num_pages, f"group {g}: {pool.num_pages - len(free) - len(held)} pages lost"
+        slots = [r.slot for r in self.requests.values()]
+        assert len(set(slots)) == len(slots), "a state slot is held twice"
+        assert len(slots) + self.slots.num_free == self.slots.num_slots, "a state slot is lost"

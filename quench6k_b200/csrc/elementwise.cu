@@ -1,0 +1,85 @@
+// Embedding gather, RMSNorm over rows of the FP32 residual stream, and the MoE combine.
+// Reference formulas: crates/cuda/kernels/flint.cu:89-95 (embed), :97-122 (rmsnorm),
+// :1228-1239 (combine).  Unlike the reference no width is compiled in.
+#include "common.cuh"
+
+namespace {
+
+template <typename T>
+__global__ void embed_kernel(const int* tokens, const T* table, float* h, int D, int V) {
+    const int t = blockIdx.x;
+    int tok = tokens[t];
+    tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);      // ids are validated on the host; never read outside the table
+    const T* row = table + (size_t)tok * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) h[(size_t)t * D + i] = to_f32(row[i]);
+}
+
+// out[r] = T(x[row] * rsqrt(mean(x[row]^2) + eps) * w), row = rows ? rows[r] : r.  Sum of squares,
+// rsqrt and the products are FP32; the per-thread partial sums and the block sum run in a fixed order.
+template <typename T>
+__global__ void __launch_bounds__(256) rmsnorm_kernel(const float* x, const int* rows, const float* w, float eps,
+                                                      T* out, int D) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const float* xr = x + (size_t)(rows ? rows[r] : r) * D;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)D + eps);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) out[(size_t)r * D + i] = from_f32<T>(xr[i] * inv * w[i]);
+}
+
+// h[t, d] += sum_s w[t, s] * y[pair_row[t*S + s], d], slots in order (so the result does not
+// depend on where the permutation put the rows).
+__global__ void combine_kernel(const float* y, const int* pair_row, const float* sel_w, int S, int D, float* h) {
+    const int t = blockIdx.x;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float acc = 0.0f;
+        for (int s = 0; s < S; ++s) acc = fmaf(sel_w[t * S + s], y[(size_t)pair_row[t * S + s] * D + d], acc);
+        h[(size_t)t * D + d] += acc;
+    }
+}
+
+// act[r, i] = T(silu(g[r, i]) * u[r, i]) for gu = [rows, 2*I] (gate columns first).
+template <typename T>
+__global__ void swiglu_kernel(const float* gu, T* act, int I, size_t count) {
+    const size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (idx >= count) return;
+    const size_t r = idx / I;
+    const int i = (int)(idx % I);
+    const float g = gu[r * 2 * I + i], u = gu[r * 2 * I + I + i];
+    act[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
+}
+
+}  // namespace
+
+Q6K_API int q6k_embed(const int* tokens, const void* table, float* h, int T_, int D, int V, int dtype, cudaStream_t st) {
+    if (T_ == 0) return 0;
+    Q6K_REQUIRE(T_ > 0 && D > 0 && V > 0, "embed: bad sizes T=%d D=%d V=%d", T_, D, V);
+    Q6K_DISPATCH(dtype, embed_kernel<T><<<T_, 256, 0, st>>>(tokens, (const T*)table, h, D, V););
+    return q6k_check_launch("embed");
+}
+
+Q6K_API int q6k_rmsnorm(const float* x, const int* rows, const float* w, float eps, void* out, int R, int D, int dtype,
+                        cudaStream_t st) {
+    if (R == 0) return 0;
+    Q6K_REQUIRE(R > 0 && D > 0, "rmsnorm: bad sizes R=%d D=%d", R, D);
+    Q6K_DISPATCH(dtype, rmsnorm_kernel<T><<<R, 256, 0, st>>>(x, rows, w, eps, (T*)out, D););
+    return q6k_check_launch("rmsnorm");
+}
+
+Q6K_API int q6k_combine(const float* y, const int* pair_row, const float* sel_w, int T_, int S, int D, float* h,
+                        cudaStream_t st) {
+    if (T_ == 0) return 0;
+    Q6K_REQUIRE(T_ > 0 && S > 0 && D > 0, "combine: bad sizes T=%d S=%d D=%d", T_, S, D);
+    combine_kernel<<<T_, 256, 0, st>>>(y, pair_row, sel_w, S, D, h);
+    return q6k_check_launch("combine");
+}
+
+Q6K_API int q6k_swiglu(const float* gu, void* act, int rows, int I, int dtype, cudaStream_t st) {
+    if (rows == 0) return 0;
+    Q6K_REQUIRE(rows > 0 && I > 0, "swiglu: bad sizes rows=%d I=%d", rows, I);
+    const size_t count = (size_t)rows * I;
+    Q6K_DISPATCH(dtype, swiglu_kernel<T><<<(unsigned)((count + 255) / 256), 256, 0, st>>>(gu, (T*)act, I, count););
+    return q6k_check_launch("swiglu");
+}

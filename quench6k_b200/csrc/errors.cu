@@ -1,0 +1,21 @@
+// Error text of the exported launchers (one message per host thread).
+#include "common.cuh"
+
+static thread_local char g_msg[512] = "";
+
+int q6k_fail(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_msg, sizeof g_msg, fmt, ap);
+    va_end(ap);
+    return 1;
+}
+
+int q6k_check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) return 0;
+    return q6k_fail("%s: %s", what, cudaGetErrorString(e));
+}
+
+Q6K_API const char* q6k_last_error() { return g_msg; }
+Q6K_API int q6k_abi_version() { return 1; }

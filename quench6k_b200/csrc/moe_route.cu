@@ -1,0 +1,151 @@
+// Router scoring with top-k selection, and the token -> expert permutation.
+//
+// Scoring (FP32 throughout): sigmoid per expert, top-k by score, ties to the lower expert index,
+// weights divided by (their sum + 1e-20) (crates/cuda/kernels/flint.cu:829-868); or softmax over
+// all experts, top-k, divided by the chosen sum (crates/cuda/kernels/moe.cu:19-71).  NaN scores
+// count as 0 so that an expert index is never out of range.  Without renormalisation the chosen
+// scores are the weights.
+//
+// Permutation (reference: count/plan/scatter, flint.cu:1163-1209, which ranks with atomics): here
+// the row of a (token, slot) pair inside its expert's group is its rank among the pairs of that
+// expert in pair order, so the whole permutation is a pure function of the selection.
+#include "common.cuh"
+
+namespace {
+
+__global__ void route_kernel(const float* logits, int T_, int E, int k, int sigmoid, int renorm, int* sel_e, float* sel_w) {
+    extern __shared__ float sc[];             // [warps][E]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= T_) return;
+    float* v = sc + (size_t)warp * E;
+    const float* z = logits + (size_t)t * E;
+    float total = 1.0f;
+    if (sigmoid) {
+        for (int e = lane; e < E; e += 32) {
+            float s = 1.0f / (1.0f + expf(-z[e]));
+            v[e] = s >= 0.0f ? s : 0.0f;
+        }
+    } else {
+        float mx = -INFINITY;
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+        mx = warp_max(mx);
+        float sum = 0.0f;
+        for (int e = lane; e < E; e += 32) {
+            float s = expf(z[e] - mx);
+            s = s >= 0.0f ? s : 0.0f;
+            v[e] = s;
+            sum += s;
+        }
+        total = warp_sum(sum);
+    }
+    __syncwarp();
+    float chosen_sum = 0.0f;
+    for (int r = 0; r < k; ++r) {
+        float best = -1.0f;
+        int best_i = 0x7fffffff;
+        for (int e = lane; e < E; e += 32)
+            if (v[e] > best) best = v[e], best_i = e;       // ascending e: the lowest index of a tie wins
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (ob > best || (ob == best && oi < best_i)) best = ob, best_i = oi;
+        }
+        const float score = sigmoid ? best : best / total;
+        chosen_sum += score;
+        if (lane == 0) {
+            sel_e[(size_t)t * k + r] = best_i;
+            sel_w[(size_t)t * k + r] = score;
+            v[best_i] = -2.0f;
+        }
+        __syncwarp();
+    }
+    if (renorm && lane == 0) {
+        const float den = sigmoid ? chosen_sum + 1e-20f : chosen_sum;
+        for (int r = 0; r < k; ++r) sel_w[(size_t)t * k + r] /= den;
+    }
+}
+
+// One warp per expert: counts[e] and, for each pair p with sel_e[p] == e, rank[p] = number of
+// earlier pairs of the same expert.
+__global__ void count_rank_kernel(const int* sel_e, int pairs, int E, int* counts, int* rank) {
+    const int lane = threadIdx.x & 31;
+    const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (e >= E) return;
+    int base = 0;
+    for (int p0 = 0; p0 < pairs; p0 += 32) {
+        const int p = p0 + lane;
+        const bool hit = p < pairs && sel_e[p] == e;
+        const unsigned mask = __ballot_sync(0xffffffffu, hit);
+        if (hit) rank[p] = base + __popc(mask & ((1u << lane) - 1u));
+        base += __popc(mask);
+    }
+    if (lane == 0) counts[e] = base;
+}
+
+// offsets = exclusive scan of counts (E + 1 entries), in expert order.  One block.
+__global__ void offsets_kernel(const int* counts, int E, int* offsets) {
+    __shared__ int part[1024];
+    const int tid = threadIdx.x, n = blockDim.x;
+    const int per = (E + n - 1) / n;
+    int sum = 0;
+    for (int i = 0; i < per; ++i) {
+        const int e = tid * per + i;
+        if (e < E) sum += counts[e];
+    }
+    part[tid] = sum;
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0;
+        for (int i = 0; i < n; ++i) {
+            const int c = part[i];
+            part[i] = run;
+            run += c;
+        }
+        offsets[E] = run;
+    }
+    __syncthreads();
+    int run = part[tid];
+    for (int i = 0; i < per; ++i) {
+        const int e = tid * per + i;
+        if (e < E) {
+            offsets[e] = run;
+            run += counts[e];
+        }
+    }
+}
+
+// pair_row[p] = offsets[sel_e[p]] + rank[p]; row_token[pair_row[p]] = p / k.
+__global__ void scatter_kernel(const int* sel_e, const int* rank, const int* offsets, int pairs, int k, int* pair_row,
+                               int* row_token) {
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= pairs) return;
+    const int row = offsets[sel_e[p]] + rank[p];
+    pair_row[p] = row;
+    row_token[row] = p / k;
+}
+
+}  // namespace
+
+Q6K_API int q6k_route(const float* logits, int T_, int E, int k, int sigmoid, int renorm, int* sel_e, float* sel_w,
+                      cudaStream_t st) {
+    if (T_ == 0) return 0;
+    Q6K_REQUIRE(T_ > 0 && E > 0 && k > 0 && k <= E, "route: bad sizes T=%d E=%d k=%d", T_, E, k);
+    Q6K_REQUIRE(E <= 8192, "route: %d experts exceed the supported 8192", E);
+    const int warps = E <= 2048 ? 4 : 1;
+    const size_t smem = (size_t)warps * E * sizeof(float);
+    route_kernel<<<(T_ + warps - 1) / warps, warps * 32, smem, st>>>(logits, T_, E, k, sigmoid, renorm, sel_e, sel_w);
+    return q6k_check_launch("route");
+}
+
+// counts: [E], rank: [pairs], offsets: [E+1], pair_row: [pairs], row_token: [pairs]; all int32.
+Q6K_API int q6k_moe_permute(const int* sel_e, int pairs, int k, int E, int* counts, int* rank, int* offsets, int* pair_row,
+                            int* row_token, cudaStream_t st) {
+    if (pairs == 0) return 0;
+    Q6K_REQUIRE(pairs > 0 && k > 0 && E > 0, "moe_permute: bad sizes pairs=%d k=%d E=%d", pairs, k, E);
+    count_rank_kernel<<<(E + 7) / 8, 256, 0, st>>>(sel_e, pairs, E, counts, rank);
+    offsets_kernel<<<1, 256, 0, st>>>(counts, E, offsets);
+    scatter_kernel<<<(pairs + 255) / 256, 256, 0, st>>>(sel_e, rank, offsets, pairs, k, pair_row, row_token);
+    return q6k_check_launch("moe_permute");
+}

@@ -1,0 +1,76 @@
+// Per-head RMSNorm of q and k, rotary position encoding, q into the operand dtype and k, v into
+// the pages of the cache.  Reference: crates/cuda/kernels/flint.cu:125-173 (there for one
+// sequence, a contiguous cache, head size 128 and theta 10000 compiled in).
+//
+// Page layout of one layer's K (and V) plane: [num_pages, kv_heads, page_size, head_dim].
+// The row of position p of request r is page block_table[r][p / page_size], offset p % page_size.
+#include "common.cuh"
+
+namespace {
+
+// Grid (T, Hq + Hkv) when the cache is written, (T, Hq) when this layer only reads another
+// layer's cache.  One thread per head dimension (blockDim.x >= hd, a multiple of 32).
+template <typename T>
+__global__ void qk_prep_kernel(const float* qkv, int ld, int Hq, int Hkv, int hd, const float* q_norm, const float* k_norm,
+                               float eps, int rope, float log2_theta, const int* positions, const int* req_of_token,
+                               const int* block_table, int max_blocks, int page_size, T* q_out, T* k_pages, T* v_pages) {
+    extern __shared__ float xs[];            // hd floats
+    __shared__ float red[32];
+    const int t = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
+    const bool is_q = h < Hq;
+    const int pos = positions[t];
+    const bool live = d < hd;
+    const float* src = qkv + (size_t)t * ld + (is_q ? h * hd : (Hq + (h - Hq)) * hd);
+    float x = live ? src[d] : 0.0f;
+    const float* nw = is_q ? q_norm : k_norm;
+    if (nw) {
+        const float ss = block_sum(x * x, red);
+        if (live) x = x * rsqrtf(ss / (float)hd + eps) * nw[d];
+    }
+    if (rope) {
+        if (live) xs[d] = x;
+        __syncthreads();
+        if (live) {
+            const int half = hd / 2;
+            const int i = d < half ? d : d - half;
+            const float inv = exp2f(-(float)(2 * i) / (float)hd * log2_theta);
+            float sn, cs;
+            sincosf((float)pos * inv, &sn, &cs);
+            x = d < half ? xs[d] * cs - xs[d + half] * sn : xs[d] * cs + xs[d - half] * sn;
+        }
+    }
+    if (!live) return;
+    if (is_q) {
+        q_out[((size_t)t * Hq + h) * hd + d] = from_f32<T>(x);
+    } else {
+        const int kh = h - Hq;
+        const int page = block_table[(size_t)req_of_token[t] * max_blocks + pos / page_size];
+        if (page < 0) return;                 // no page behind this position: nothing is written
+        const size_t row = (((size_t)page * Hkv + kh) * page_size + pos % page_size) * hd + d;
+        k_pages[row] = from_f32<T>(x);
+        v_pages[row] = from_f32<T>(qkv[(size_t)t * ld + (size_t)(Hq + Hkv + kh) * hd + d]);
+    }
+}
+
+}  // namespace
+
+// qkv: FP32 [T, ld] with q heads, then k heads, then v heads in each row.  q_norm/k_norm: FP32 [hd]
+// or null (no QK-norm).  rope != 0 applies rotate-half RoPE with base theta at positions[t].
+// write_kv == 0: only q is produced (the layer reads a cache another layer wrote).
+Q6K_API int q6k_qk_prep(const float* qkv, int ld, int T_, int Hq, int Hkv, int hd, const float* q_norm, const float* k_norm,
+                        float eps, int rope, float theta, const int* positions, const int* req_of_token,
+                        const int* block_table, int max_blocks, int page_size, void* q_out, void* k_pages, void* v_pages,
+                        int write_kv, int dtype, cudaStream_t st) {
+    if (T_ == 0) return 0;
+    Q6K_REQUIRE(T_ > 0 && Hq > 0 && Hkv > 0 && hd > 0, "qk_prep: bad sizes T=%d Hq=%d Hkv=%d hd=%d", T_, Hq, Hkv, hd);
+    Q6K_REQUIRE(hd % 2 == 0 && hd <= 1024, "qk_prep: head_dim %d must be even and at most 1024", hd);
+    Q6K_REQUIRE(!rope || theta > 0.0f, "qk_prep: rope base %g must be positive", theta);
+    Q6K_REQUIRE(!write_kv || (page_size > 0 && max_blocks > 0), "qk_prep: bad page_size %d / max_blocks %d", page_size, max_blocks);
+    const int threads = (hd + 31) / 32 * 32;
+    dim3 grid(T_, write_kv ? Hq + Hkv : Hq);
+    const float l2t = rope ? log2f(theta) : 0.0f;
+    Q6K_DISPATCH(dtype, qk_prep_kernel<T><<<grid, threads, hd * sizeof(float), st>>>(
+                            qkv, ld, Hq, Hkv, hd, q_norm, k_norm, eps, rope, l2t, positions, req_of_token, block_table,
+                            max_blocks, page_size, (T*)q_out, (T*)k_pages, (T*)v_pages););
+    return q6k_check_launch("qk_prep");
+}

@@ -1,0 +1,166 @@
+// Sampling support on the device: per-row argmax (greedy) and an exact top-k candidate pool.
+//
+// The reference picks greedily with a device argmax, ties to the lower id
+// (crates/cuda/kernels/topk.cu:212-303), and samples from a pool of the top candidates that an
+// exact device top-k delivers to the host (crates/cli/src/flint.rs:339-353, topk.cu:28-146).
+// Both are kept: the pool comes back sorted by (logit descending, id ascending).
+#include "common.cuh"
+
+namespace {
+
+// Ascending-order-preserving key of a float; NaN sorts lowest.
+__device__ __forceinline__ unsigned key_of(float v) {
+    if (v != v) return 0u;
+    const unsigned u = __float_as_uint(v);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__global__ void __launch_bounds__(1024) argmax_kernel(const float* logits, int V, int* out) {
+    __shared__ unsigned bk[32];
+    __shared__ int bi[32];
+    const float* row = logits + (size_t)blockIdx.x * V;
+    unsigned best = 0u;
+    int best_i = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const unsigned k = key_of(row[i]);
+        if (k > best || (k == best && i < best_i)) best = k, best_i = i;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned ok = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ok > best || (ok == best && oi < best_i)) best = ok, best_i = oi;
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) bk[warp] = best, bi[warp] = best_i;
+    __syncthreads();
+    if (warp == 0) {
+        const int nw = blockDim.x >> 5;
+        best = lane < nw ? bk[lane] : 0u;
+        best_i = lane < nw ? bi[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned ok = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (ok > best || (ok == best && oi < best_i)) best = ok, best_i = oi;
+        }
+        if (lane == 0) out[blockIdx.x] = best_i;
+    }
+}
+
+constexpr int POOL_MAX = 256;
+
+// Exact top-K of one row per block (K <= 256): a 4-pass radix select finds the K-th largest key,
+// everything above it is taken, ties at it are taken in ascending id order, and the K candidates
+// are sorted by (key descending, id ascending) with a bitonic network.
+__global__ void __launch_bounds__(1024) topk_pool_kernel(const float* logits, int V, int K, int* out_ids, float* out_vals) {
+    __shared__ int hist[256];
+    __shared__ unsigned s_prefix;
+    __shared__ int s_need, s_count;
+    __shared__ unsigned ck[POOL_MAX];
+    __shared__ int ci[POOL_MAX];
+    __shared__ int seg_eq[1024];
+    const float* row = logits + (size_t)blockIdx.x * V;
+    const int tid = threadIdx.x, n = blockDim.x;
+    if (tid == 0) s_prefix = 0u, s_need = K;
+    __syncthreads();
+    // radix select, most significant byte first
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        const unsigned himask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        const unsigned prefix = s_prefix;
+        for (int i = tid; i < V; i += n) {
+            const unsigned k = key_of(row[i]);
+            if ((k & himask) == prefix) atomicAdd(&hist[(k >> shift) & 255], 1);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int need = s_need, b = 255;
+            for (; b > 0; --b) {
+                if (hist[b] >= need) break;
+                need -= hist[b];
+            }
+            s_need = need;                      // how many are wanted from bin b
+            s_prefix = prefix | ((unsigned)b << shift);
+        }
+        __syncthreads();
+    }
+    const unsigned kth = s_prefix;
+    const int need_eq = s_need;                 // ties at the K-th key that are taken
+    if (tid == 0) s_count = 0;
+    __syncthreads();
+    // strictly greater: any order (sorted below)
+    for (int i = tid; i < V; i += n) {
+        const unsigned k = key_of(row[i]);
+        if (k > kth) {
+            const int at = atomicAdd(&s_count, 1);
+            if (at < POOL_MAX) ck[at] = k, ci[at] = i;
+        }
+    }
+    // equal: the lowest ids.  Thread t owns the contiguous ids [t*seg, (t+1)*seg).
+    const int seg = (V + n - 1) / n;
+    const int b0 = tid * seg, b1 = min(V, b0 + seg);
+    int mine = 0;
+    for (int i = b0; i < b1; ++i) mine += key_of(row[i]) == kth;
+    seg_eq[tid] = mine;
+    __syncthreads();
+    const int gt = s_count;
+    if (tid == 0) {
+        int run = 0;
+        for (int i = 0; i < n; ++i) {
+            const int c = seg_eq[i];
+            seg_eq[i] = run;
+            run += c;
+        }
+    }
+    __syncthreads();
+    int r = seg_eq[tid];
+    for (int i = b0; i < b1 && r < need_eq; ++i)
+        if (key_of(row[i]) == kth) {
+            if (gt + r < POOL_MAX) ck[gt + r] = kth, ci[gt + r] = i;
+            ++r;
+        }
+    __syncthreads();
+    // pad to 256 and sort descending by (key, -id)
+    for (int i = tid; i < POOL_MAX; i += n)
+        if (i >= K) ck[i] = 0u, ci[i] = 0x7fffffff;
+    __syncthreads();
+    for (int size = 2; size <= POOL_MAX; size <<= 1)
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            if (tid < POOL_MAX / 2) {
+                const int lo = 2 * tid - (tid & (stride - 1));
+                const int hi = lo + stride;
+                const bool desc = (lo & size) == 0;
+                const bool lo_first = ck[lo] > ck[hi] || (ck[lo] == ck[hi] && ci[lo] < ci[hi]);
+                if (lo_first != desc) {
+                    const unsigned tk = ck[lo]; ck[lo] = ck[hi]; ck[hi] = tk;
+                    const int ti = ci[lo]; ci[lo] = ci[hi]; ci[hi] = ti;
+                }
+            }
+            __syncthreads();
+        }
+    for (int i = tid; i < K; i += n) {
+        out_ids[(size_t)blockIdx.x * K + i] = ci[i];
+        out_vals[(size_t)blockIdx.x * K + i] = row[ci[i]];
+    }
+}
+
+}  // namespace
+
+Q6K_API int q6k_argmax(const float* logits, int rows, int V, int* out, cudaStream_t st) {
+    if (rows == 0) return 0;
+    Q6K_REQUIRE(rows > 0 && V > 0, "argmax: bad sizes rows=%d V=%d", rows, V);
+    argmax_kernel<<<rows, 1024, 0, st>>>(logits, V, out);
+    return q6k_check_launch("argmax");
+}
+
+// ids: int32 [rows, K], vals: FP32 [rows, K], sorted by (logit descending, id ascending).
+Q6K_API int q6k_topk_pool(const float* logits, int rows, int V, int K, int* ids, float* vals, cudaStream_t st) {
+    if (rows == 0) return 0;
+    Q6K_REQUIRE(rows > 0 && V > 0, "topk_pool: bad sizes rows=%d V=%d", rows, V);
+    Q6K_REQUIRE(K >= 1 && K <= POOL_MAX && K <= V, "topk_pool: K=%d outside 1..min(%d, V=%d)", K, POOL_MAX, V);
+    topk_pool_kernel<<<rows, 1024, 0, st>>>(logits, V, K, ids, vals);
+    return q6k_check_launch("topk_pool");
+}

@@ -1,0 +1,42 @@
+"""What one step runs: for each request its next tokens and the places whose logits are wanted."""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Hashable, List, Optional, Sequence
+
+import torch
+
+
+@dataclass
+class StepEntry:
+    rid: Hashable
+    tokens: Sequence[int]                 # the request's next tokens (a prompt portion, or one decoded token)
+    want: Sequence[int] = ()              # indices into `tokens` whose logits are returned
+
+
+@dataclass
+class StepContext:
+    """The batch as the parts see it.  All tensors are int32 on the device.
+
+    Rows of the step are the entries' tokens back to back.  positions[t] is the row's position in
+    its request, req_of_token[t] the request's index within this step, q_start the prefix sums of
+    the entries' lengths, pos_start the first position of each entry, slot_ids each request's
+    state slot, block_tables[g] the page table [R, blocks] of cache group g, logit_rows the rows
+    whose logits are wanted."""
+    T: int
+    R: int
+    token_ids: torch.Tensor
+    positions: torch.Tensor
+    req_of_token: torch.Tensor
+    q_start: torch.Tensor
+    pos_start: torch.Tensor
+    slot_ids: torch.Tensor
+    block_tables: List[torch.Tensor]
+    logit_rows: torch.Tensor
+    n_logit_rows: int
+    # host copies, for parts that plan their launches
+    q_lens: List[int] = field(default_factory=list)
+    pos_starts: List[int] = field(default_factory=list)
+    slots: List[int] = field(default_factory=list)
+    max_context: int = 0                  # largest position + 1 in the step
+    max_q_len: int = 0

@@ -1,0 +1,219 @@
+"""The model on the device, its cache and the one step function.
+
+`step(entries)` takes any mix of (request, next tokens): portions of prompts beside single decoded
+tokens, cut anywhere.  It reserves pages, uploads the batch description in one copy, runs only the
+given tokens through the model from the cache that earlier steps left, commits the pages and
+returns the FP32 logits at the wanted places (reference: one sequence per call,
+crates/engine/src/flint.rs:699-771; batches of one-token segments, crates/engine/src/forward.rs:1166-1260).
+"""
+from __future__ import annotations
+
+import os
+from typing import Dict, Hashable, List, Optional, Sequence, Union
+
+import numpy as np
+import torch
+
+from ..cache import CacheManager, GroupSpec, OutOfPages
+from ..config.registry import load_config
+from ..models.decoder import DecoderModel
+from ..parts.base import LayerCache, Runtime
+from ..weights import load_folder, random_getter
+from .batch import StepContext, StepEntry
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
+
+
+def parse_dtype(d) -> torch.dtype:
+    if d not in _DTYPES:
+        raise ValueError(f"dtype {d!r} is neither bfloat16 nor float32")
+    return _DTYPES[d]
+
+
+class ModelRunner:
+    def __init__(self, model: DecoderModel, rt: Runtime, page_size: int, num_pages: Union[int, Sequence[int]],
+                 max_requests: int):
+        if rt.device.type != "cuda":
+            raise RuntimeError("the engine runs on a CUDA device only; there is no CPU path")
+        self.model, self.rt = model, rt
+        self.page_size = page_size
+        self.vocab_size = model.spec.vocab_size
+        # cache groups: executed positions whose mixers ask for the same kind of cache share one
+        reqs = model.cache_requests()
+        keys, self.group_of = [], []
+        for r in reqs:
+            if r is None:
+                self.group_of.append(None)
+                continue
+            if r.key() not in keys:
+                keys.append(r.key())
+            self.group_of.append(keys.index(r.key()))
+        self.group_specs = [GroupSpec(k[0], k[1]) for k in keys]
+        n_groups = len(keys)
+        pages = [num_pages] * n_groups if isinstance(num_pages, int) else list(num_pages)
+        if len(pages) != n_groups:
+            raise ValueError(f"{len(pages)} page counts for {n_groups} cache groups")
+        self.manager = CacheManager(self.group_specs, page_size, pages, max_requests)
+        self.caches: List[Optional[LayerCache]] = []
+        for p, r in enumerate(reqs):
+            src = model.kv_source[p]
+            if src is not None:
+                own = self.caches[src]
+                if own is None:
+                    raise ValueError(f"position {p} borrows the cache of position {src}, which has none")
+                self.caches.append(LayerCache(own.group, own.k, own.v, page_size, write=False))
+            elif r is None:
+                self.caches.append(None)
+            else:
+                g = self.group_of[p]
+                shape = (pages[g], r.kv_heads, page_size, r.head_dim)
+                self.caches.append(LayerCache(g, torch.zeros(shape, dtype=rt.dtype, device=rt.device),
+                                              torch.zeros(shape, dtype=rt.dtype, device=rt.device), page_size))
+        self.states = [None if s is None else torch.zeros((max_requests, *s), dtype=torch.float32, device=rt.device)
+                       for s in model.state_shapes()]
+        self._pinned: Optional[torch.Tensor] = None
+        self._pinned_free: Optional[torch.cuda.Event] = None      # set once the last upload has left the pinned block
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_folder(cls, folder: str, dtype="bfloat16", device="cuda:0", page_size: Optional[int] = None,
+                    num_pages: Union[int, Sequence[int]] = 256, max_requests: int = 64, tensor_cores: bool = True):
+        arch, cfg = load_config(folder)
+        model = DecoderModel(arch.build_spec(cfg))
+        rt = Runtime(torch.device(device), parse_dtype(dtype), tensor_cores)
+        model.bind(load_folder(folder, model.tensors()), rt)
+        ps = page_size or getattr(cfg, "kv_page_size", None) or 16
+        return cls(model, rt, ps, num_pages, max_requests)
+
+    @classmethod
+    def from_random(cls, cfg, seed: int, dtype="bfloat16", device="cuda:0", page_size: Optional[int] = None,
+                    num_pages: Union[int, Sequence[int]] = 256, max_requests: int = 64, tensor_cores: bool = True,
+                    arch=None):
+        """Random weights made on the device from the typed config and a seed (no files)."""
+        from ..config.registry import get_architecture
+        arch = arch or get_architecture(cfg.architectures[0])
+        spec = arch.build_spec(cfg)
+        model = DecoderModel(spec)
+        rt = Runtime(torch.device(device), parse_dtype(dtype), tensor_cores)
+        model.bind(random_getter(model.tensors(), seed, spec.init_std, device=rt.device), rt)
+        ps = page_size or getattr(cfg, "kv_page_size", None) or 16
+        return cls(model, rt, ps, num_pages, max_requests)
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, rid: Hashable) -> None:
+        slot = self.manager.add(rid)
+        for s in self.states:
+            if s is not None:
+                s[slot].zero_()
+
+    def end_request(self, rid: Hashable) -> None:
+        self.manager.remove(rid)
+
+    def has_request(self, rid: Hashable) -> bool:
+        return rid in self.manager.requests
+
+    # ------------------------------------------------------------------ the step
+    def _context(self, entries: Sequence[StepEntry]) -> StepContext:
+        mgr, ps = self.manager, self.page_size
+        R = len(entries)
+        q_lens = [len(e.tokens) for e in entries]
+        T = sum(q_lens)
+        pos_starts = [mgr.length(e.rid) for e in entries]
+        slots = [mgr.slot(e.rid) for e in entries]
+        widths = []
+        for g in range(len(self.group_specs)):
+            widths.append(max(1, max(len(mgr.table(e.rid, g)) for e in entries)))
+        n_want = sum(len(e.want) for e in entries)
+        total = 3 * T + (R + 1) + 2 * R + n_want + sum(R * w for w in widths)
+        if self._pinned_free is not None:
+            self._pinned_free.synchronize()
+        if self._pinned is None or self._pinned.numel() < total:
+            self._pinned = torch.empty(max(total, 4096), dtype=torch.int32, pin_memory=True)
+        host = self._pinned.numpy()
+        o = 0
+
+        def take(n):
+            nonlocal o
+            v = host[o:o + n]
+            o += n
+            return v
+
+        tok, pos, rot = take(T), take(T), take(T)
+        qs, psv, sl, lr = take(R + 1), take(R), take(R), take(n_want)
+        t = w = 0
+        qs[0] = 0
+        for r, e in enumerate(entries):
+            n = q_lens[r]
+            arr = np.asarray(e.tokens, dtype=np.int64)
+            if n and (arr.min() < 0 or arr.max() >= self.vocab_size):
+                raise ValueError(f"request {e.rid!r}: token id outside 0..{self.vocab_size - 1}")
+            tok[t:t + n] = arr
+            pos[t:t + n] = np.arange(pos_starts[r], pos_starts[r] + n)
+            rot[t:t + n] = r
+            for i in e.want:
+                if not 0 <= i < n:
+                    raise ValueError(f"request {e.rid!r}: wanted place {i} outside its {n} tokens")
+                lr[w] = t + i
+                w += 1
+            t += n
+            qs[r + 1] = t
+            psv[r] = pos_starts[r]
+            sl[r] = slots[r]
+        tabs = []
+        for g, wd in enumerate(widths):
+            tb = take(R * wd).reshape(R, wd)
+            tb[:] = -1
+            for r, e in enumerate(entries):
+                row = mgr.table(e.rid, g)
+                tb[r, :len(row)] = row
+            tabs.append((tb, wd))
+        dev = torch.empty(total, dtype=torch.int32, device=self.rt.device)
+        dev.copy_(self._pinned[:total], non_blocking=True)
+        if self._pinned_free is None:
+            self._pinned_free = torch.cuda.Event()
+        self._pinned_free.record()
+        o = 0
+
+        def view(n):
+            nonlocal o
+            v = dev[o:o + n]
+            o += n
+            return v
+
+        d_tok, d_pos, d_rot = view(T), view(T), view(T)
+        d_qs, d_ps, d_sl, d_lr = view(R + 1), view(R), view(R), view(n_want)
+        d_tabs = [view(R * wd).view(R, wd) for _, wd in tabs]
+        return StepContext(T=T, R=R, token_ids=d_tok, positions=d_pos, req_of_token=d_rot, q_start=d_qs, pos_start=d_ps,
+                           slot_ids=d_sl, block_tables=d_tabs, logit_rows=d_lr, n_logit_rows=n_want, q_lens=q_lens,
+                           pos_starts=pos_starts, slots=slots,
+                           max_context=max(p + n for p, n in zip(pos_starts, q_lens)), max_q_len=max(q_lens))
+
+    def can_run(self, entries: Sequence[StepEntry]) -> bool:
+        return self.manager.can_reserve([(e.rid, len(e.tokens)) for e in entries])
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run the entries' tokens as one batch; FP32 logits [wanted, vocab] in the order of the
+        entries and of their `want` (None if nothing is wanted).  Raises OutOfPages, leaving every
+        request as it was, if the pools cannot hold the step."""
+        entries = [e for e in entries if len(e.tokens)]
+        if not entries:
+            return None
+        rids = [e.rid for e in entries]
+        if len(set(rids)) != len(rids):
+            raise ValueError("a request appears twice in one step")
+        if not self.can_run(entries):
+            raise OutOfPages("the page pools cannot hold this step: " +
+                             ", ".join(f"{e.rid!r}+{len(e.tokens)}" for e in entries))
+        for e in entries:
+            self.manager.reserve(e.rid, len(e.tokens))
+        try:
+            ctx = self._context(entries)
+            logits = self.model.forward(ctx, self.caches, self.states)
+        except BaseException:
+            for e in entries:
+                self.manager.cancel(e.rid)
+            raise
+        for e in entries:
+            self.manager.commit(e.rid)
+        return logits

@@ -1,0 +1,244 @@
+"""Continuous batching above the step function.
+
+Each call to `schedule()` builds one step under a token budget:
+
+1. every running request whose prompt is in the cache decodes one token;
+2. what is left of the budget goes to prompt portions, first of running requests that are still
+   prefilling (in admission order), then of waiting requests, admitted first-come first-served
+   while a slot, budget and pages for the portion are there.  A portion may be cut anywhere; if the
+   pools cannot hold all of it, it shrinks to what they can hold, down to nothing (the request waits).
+
+When pages run out for the decode tokens, the most recently admitted running request is preempted:
+its pages and slot go back, and it returns to the front of the waiting queue to be recomputed from
+its prompt and the tokens it has produced.  A request running alone that cannot get a page ends
+with reason "length" (the cache is its context).  A prompt that could never fit is refused when
+it is added.
+
+The reference serves Flint one request at a time (crates/cli/src/serve.rs:981-1168) and, for its
+other model, admits a request only if its memory plan fits and fails requests when memory is held
+by running ones (crates/engine/src/session.rs:824-904); finish reasons are its Stop, Length and
+Cancelled (crates/engine/src/session.rs:162-169).  This scheduler is host logic only and runs
+against the cache manager without a GPU.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Callable, Deque, Dict, Hashable, List, Optional, Sequence
+
+from ..cache import CacheManager
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import SplitMix64
+from .batch import StepEntry
+
+FINISH_STOP, FINISH_LENGTH, FINISH_CANCELLED = "stop", "length", "cancelled"
+
+
+@dataclass
+class Request:
+    rid: Hashable
+    prompt: List[int]
+    params: SamplingParams
+    output: List[int] = field(default_factory=list)
+    finish_reason: Optional[str] = None
+    num_computed: int = 0                 # tokens of prompt + output whose keys are in the cache
+    preemptions: int = 0
+    rng: Optional[SplitMix64] = None
+
+    @property
+    def tokens(self) -> List[int]:
+        return self.prompt + self.output
+
+    @property
+    def finished(self) -> bool:
+        return self.finish_reason is not None
+
+
+@dataclass
+class ScheduledEntry:
+    request: Request
+    start: int                            # index into request.tokens of the first token run
+    count: int
+    samples: bool                         # the last token of this entry yields the request's next token
+
+
+@dataclass
+class ScheduledStep:
+    entries: List[ScheduledEntry]
+    preempted: List[Request] = field(default_factory=list)
+    finished: List[Request] = field(default_factory=list)      # ended while scheduling (cache exhausted)
+
+    def step_entries(self) -> List[StepEntry]:
+        out = []
+        for e in self.entries:
+            toks = e.request.tokens[e.start:e.start + e.count]
+            out.append(StepEntry(e.request.rid, toks, [e.count - 1] if e.samples else []))
+        return out
+
+    @property
+    def num_tokens(self) -> int:
+        return sum(e.count for e in self.entries)
+
+
+class Scheduler:
+    def __init__(self, manager: CacheManager, max_batch_tokens: int = 2048, max_running: Optional[int] = None,
+                 admit: Optional[Callable[[Hashable], None]] = None, release: Optional[Callable[[Hashable], None]] = None):
+        if max_batch_tokens < 1:
+            raise ValueError("max_batch_tokens must be at least 1")
+        self.manager = manager
+        self.max_batch_tokens = max_batch_tokens
+        self.max_running = max_running if max_running is not None else manager.slots.num_slots
+        self._admit = admit or manager.add
+        self._release = release or manager.remove
+        self.waiting: Deque[Request] = deque()
+        self.running: List[Request] = []          # admission order
+        self.by_id: Dict[Hashable, Request] = {}
+
+    # ------------------------------------------------------------------ queue
+    def capacity_tokens(self) -> int:
+        """Most tokens one request can ever hold: the smallest pool bounds it."""
+        return min(p.num_pages for p in self.manager.pools) * self.manager.page_size if self.manager.pools else 1 << 60
+
+    def add(self, req: Request) -> None:
+        if req.rid in self.by_id:
+            raise KeyError(f"request {req.rid!r} already exists")
+        if not req.prompt:
+            raise ValueError("a request needs at least one prompt token")
+        req.params.validate()
+        if len(req.prompt) + 1 > self.capacity_tokens():
+            raise ValueError(f"prompt of {len(req.prompt)} tokens exceeds the cache capacity of {self.capacity_tokens()} tokens")
+        self.by_id[req.rid] = req
+        self.waiting.append(req)
+
+    def abort(self, rid: Hashable) -> Optional[Request]:
+        req = self.by_id.get(rid)
+        if req is None or req.finished:
+            return None
+        self._finish(req, FINISH_CANCELLED)
+        return req
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def _finish(self, req: Request, reason: str) -> None:
+        req.finish_reason = reason
+        if req in self.running:
+            self.running.remove(req)
+            self._release(req.rid)
+        elif req in self.waiting:
+            self.waiting.remove(req)
+        self.by_id.pop(req.rid, None)
+
+    def _preempt(self, req: Request) -> None:
+        self.running.remove(req)
+        self._release(req.rid)
+        req.num_computed = 0
+        req.preemptions += 1
+        self.waiting.appendleft(req)
+
+    # ------------------------------------------------------------------ one step
+    def _fit(self, chosen: List, rid: Hashable, want: int) -> int:
+        """Largest n <= want such that the pools hold `chosen` plus n tokens of rid."""
+        if want <= 0:
+            return 0
+        if self.manager.can_reserve(chosen + [(rid, want)]):
+            return want
+        lo, hi = 0, want                   # can_reserve is monotone in n
+        while lo < hi:
+            mid = (lo + hi + 1) // 2
+            if self.manager.can_reserve(chosen + [(rid, mid)]):
+                lo = mid
+            else:
+                hi = mid - 1
+        return lo
+
+    def schedule(self) -> ScheduledStep:
+        step = ScheduledStep([])
+        budget = self.max_batch_tokens
+        # 1. decode tokens; preempt from the back until they fit
+        while True:
+            decoding = [r for r in self.running if r.num_computed == len(r.tokens) - 1 and r.output]
+            decoding = decoding[:budget]
+            wants = [(r.rid, 1) for r in decoding]
+            if self.manager.can_reserve(wants):
+                break
+            if len(self.running) == 1:
+                lone = self.running[0]
+                self._finish(lone, FINISH_LENGTH)
+                step.finished.append(lone)
+                continue
+            victim = self.running[-1]
+            self._preempt(victim)
+            step.preempted.append(victim)
+        chosen = list(wants)
+        for r in decoding:
+            step.entries.append(ScheduledEntry(r, r.num_computed, 1, True))
+        budget -= len(decoding)
+        in_step = {r.rid for r in decoding}
+        # 2. prompt portions of running requests still prefilling
+        for r in self.running:
+            if budget <= 0:
+                break
+            if r.rid in in_step:
+                continue
+            left = len(r.tokens) - r.num_computed
+            n = self._fit(chosen, r.rid, min(left, budget))
+            if n <= 0:
+                continue
+            step.entries.append(ScheduledEntry(r, r.num_computed, n, n == left))
+            chosen.append((r.rid, n))
+            in_step.add(r.rid)
+            budget -= n
+        # 3. admit waiting requests, first come first served
+        while self.waiting and budget > 0 and len(self.running) < self.max_running and self.manager.slots.num_free > 0:
+            r = self.waiting[0]
+            self._admit(r.rid)
+            left = len(r.tokens)
+            n = self._fit(chosen, r.rid, min(left, budget))
+            if n <= 0:
+                self._release(r.rid)
+                break                      # the head of the queue waits; nobody overtakes it
+            self.waiting.popleft()
+            self.running.append(r)
+            step.entries.append(ScheduledEntry(r, 0, n, n == left))
+            chosen.append((r.rid, n))
+            budget -= n
+        if not step.entries and not step.finished and self.running:
+            # every running request is mid-prefill and no page is free: make room from the back
+            if len(self.running) > 1:
+                victim = self.running[-1]
+                self._preempt(victim)
+                step.preempted.append(victim)
+                more = self.schedule()
+                more.preempted = step.preempted + more.preempted
+                return more
+            lone = self.running[0]
+            self._finish(lone, FINISH_LENGTH)
+            step.finished.append(lone)
+        return step
+
+    def update(self, step: ScheduledStep, sampled: Sequence[int]) -> List[Request]:
+        """Account for a finished step.  `sampled` holds one token for every entry with
+        samples=True, in order.  Returns the requests that ended."""
+        done: List[Request] = []
+        it = iter(sampled)
+        for e in step.entries:
+            r = e.request
+            if r.finished:                 # aborted while the step ran
+                if e.samples:
+                    next(it)
+                continue
+            r.num_computed += e.count
+            if not e.samples:
+                continue
+            tok = int(next(it))
+            r.output.append(tok)
+            if tok in r.params.stop_tokens:
+                self._finish(r, FINISH_STOP)
+            elif len(r.output) >= r.params.max_tokens:
+                self._finish(r, FINISH_LENGTH)
+            elif len(r.tokens) + 1 > self.capacity_tokens():
+                self._finish(r, FINISH_LENGTH)
+            if r.finished:
+                done.append(r)
+        return done

@@ -1,0 +1,42 @@
+"""Recursive Flint MoE: from its typed configuration to the architecture-neutral ModelSpec.
+
+Per layer (crates/engine/src/flint.rs:815-1075): RMSNorm, GQA self-attention (optional QK-norm,
+RoPE per the layer's flag, sinks, full or sliding window per the layer's flag), RMSNorm, then a
+dense SwiGLU MLP in the leading `first_k_dense_replace` layers and routed SwiGLU experts (with an
+optional ungated shared expert) in the rest; a final RMSNorm and the LM head.  Tensor names are
+the Hugging Face style ones listed in `tensor_names` below.
+"""
+from __future__ import annotations
+
+from ..config.flint import ARCHITECTURE, FlintConfig
+from ..config.registry import register_architecture
+from ..spec import LayerSpec, ModelSpec, PartSpec
+
+
+def build_spec(cfg: FlintConfig, norm_init: str = "ones") -> ModelSpec:
+    layers = []
+    for i in range(cfg.num_hidden_layers):
+        pos = (PartSpec("rope", {"head_dim": cfg.head_dim, "theta": cfg.rope_theta}) if cfg.layer_has_rope(i)
+               else PartSpec("none", {"head_dim": cfg.head_dim}))
+        mixer = PartSpec("attention", {
+            "num_heads": cfg.num_attention_heads, "num_kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+            "eps": cfg.rms_norm_eps, "pos": pos, "window": cfg.sliding_window if cfg.layer_is_sliding(i) else None,
+            "sinks": cfg.attn_sinks, "qk_norm": cfg.qk_norm, "norm_init": norm_init})
+        if cfg.layer_is_dense(i):
+            ffn = PartSpec("dense", {"intermediate_size": cfg.intermediate_size})
+        else:
+            ffn = PartSpec("moe", {
+                "num_experts": cfg.n_routed_experts, "top_k": cfg.num_experts_per_tok,
+                "intermediate_size": cfg.moe_intermediate_size, "scoring": cfg.scoring_func,
+                "renormalize": cfg.norm_topk_prob,
+                "shared_intermediate_size": cfg.shared_expert_intermediate_size if cfg.n_shared_experts > 0 else 0})
+        layers.append(LayerSpec(prefix=f"model.layers.{i}.", mixer=mixer, ffn=ffn,
+                                norm=PartSpec("rmsnorm", {"eps": cfg.rms_norm_eps, "init": norm_init})))
+    return ModelSpec(hidden_size=cfg.hidden_size, vocab_size=cfg.vocab_size, layers=layers,
+                     order=cfg.execution_order(), kv_source=cfg.kv_sources(),
+                     final_norm=PartSpec("rmsnorm", {"eps": cfg.rms_norm_eps, "init": norm_init}),
+                     head_name=None if cfg.tie_word_embeddings else "lm_head.weight",
+                     eos_token_ids=tuple(cfg.eos_token_id))
+
+
+register_architecture(ARCHITECTURE, FlintConfig, build_spec, aliases=("flint",))

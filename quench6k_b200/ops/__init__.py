@@ -1,0 +1,286 @@
+"""Python faces of the hand-written CUDA kernels.
+
+Each function checks devices, dtypes, shapes and contiguity, then calls the `extern "C"` launcher
+through ctypes on the current CUDA stream.  There is no CPU path and no library fallback: on a
+machine without the built extension or without a GPU these functions raise.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import Optional
+
+import torch
+
+from .build import BuildError, build, library
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 operands, not {dt}")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, shape=None):
+    if not t.is_cuda:
+        raise KernelError(f"{name} is on {t.device}; the kernels run on a CUDA device only")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} is not contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} has dtype {t.dtype}, expected {dtype}")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise KernelError(f"{name} has shape {tuple(t.shape)}, expected {tuple(shape)}")
+
+
+def _call(fn_name: str, *args):
+    lib = library()
+    fn = getattr(lib, fn_name)
+    fn.restype = ctypes.c_int
+    rc = fn(*args)
+    if rc != 0:
+        lib.q6k_last_error.restype = ctypes.c_char_p
+        raise KernelError(lib.q6k_last_error().decode())
+
+
+_i = ctypes.c_int
+_f = ctypes.c_float
+_ll = ctypes.c_longlong
+
+
+# --------------------------------------------------------------------------- elementwise
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """h[t] = float32(table[tokens[t]])."""
+    T = tokens.numel()
+    V, D = table.shape
+    _need(tokens, "tokens", torch.int32)
+    _need(table, "table")
+    if out is None:
+        out = torch.empty((T, D), dtype=torch.float32, device=table.device)
+    _need(out, "out", torch.float32, (T, D))
+    _call("q6k_embed", _ptr(tokens), _ptr(table), _ptr(out), _i(T), _i(D), _i(V), _i(dtype_code(table.dtype)), _stream())
+    return out
+
+
+def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r] = out_dtype(x[row] * rsqrt(mean(x[row]^2) + eps) * w); row = rows[r] if given."""
+    _need(x, "x", torch.float32)
+    D = x.shape[-1]
+    _need(w, "w", torch.float32, (D,))
+    R = x.shape[0] if rows is None else rows.numel()
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    if out is None:
+        out = torch.empty((R, D), dtype=out_dtype, device=x.device)
+    _need(out, "out", out_dtype, (R, D))
+    _call("q6k_rmsnorm", _ptr(x), _ptr(rows), _ptr(w), _f(eps), _ptr(out), _i(R), _i(D), _i(dtype_code(out_dtype)), _stream())
+    return out
+
+
+def combine(y: torch.Tensor, pair_row: torch.Tensor, sel_w: torch.Tensor, h: torch.Tensor) -> None:
+    """h[t] += sum_s sel_w[t, s] * y[pair_row[t, s]] in slot order."""
+    T, S = sel_w.shape
+    D = h.shape[1]
+    _need(y, "y", torch.float32)
+    _need(pair_row, "pair_row", torch.int32)
+    _need(sel_w, "sel_w", torch.float32)
+    _need(h, "h", torch.float32, (T, D))
+    if y.shape[1] != D or pair_row.numel() != T * S:
+        raise KernelError("combine: shapes disagree")
+    _call("q6k_combine", _ptr(y), _ptr(pair_row), _ptr(sel_w), _i(T), _i(S), _i(D), _ptr(h), _stream())
+
+
+def swiglu(gu: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """act = out_dtype(silu(gu[:, :I]) * gu[:, I:])."""
+    _need(gu, "gu", torch.float32)
+    rows, two_i = gu.shape
+    act = torch.empty((rows, two_i // 2), dtype=out_dtype, device=gu.device)
+    _call("q6k_swiglu", _ptr(gu), _ptr(act), _i(rows), _i(two_i // 2), _i(dtype_code(out_dtype)), _stream())
+    return act
+
+
+# --------------------------------------------------------------------------- matrix products (CUDA cores)
+EPI_STORE, EPI_ADD, EPI_SWIGLU = 0, 1, 2
+
+
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False,
+              w2: Optional[torch.Tensor] = None, a_rows: Optional[torch.Tensor] = None, groups=None,
+              rows: Optional[int] = None) -> torch.Tensor:
+    """out[r] (+)= a[row(r)] @ w_g^T with FP32 fused multiply-adds.
+
+    a: [*, K]; w: [N, K] or, grouped, [G, N, K]; w2 (same shape) switches to the SwiGLU epilogue,
+    whose output has a's dtype; otherwise the output is float32.  a_rows: int32 [M] gathers rows of
+    a.  groups: (group_offsets [G+1], tile_group, tile_row0, num_tiles) from `tile_list`.
+    """
+    _need(a, "a")
+    _need(w, "w", a.dtype)
+    K = a.shape[1]
+    grouped = w.dim() == 3
+    N = w.shape[-2]
+    if w.shape[-1] != K:
+        raise KernelError(f"gemm: a has K={K}, w has K={w.shape[-1]}")
+    if grouped and groups is None:
+        raise KernelError("gemm: a grouped weight needs group offsets and a tile list")
+    M = rows if rows is not None else (a_rows.numel() if a_rows is not None else a.shape[0])
+    epi = EPI_SWIGLU if w2 is not None else (EPI_ADD if accumulate else EPI_STORE)
+    out_dtype = a.dtype if w2 is not None else torch.float32
+    if out is None:
+        if accumulate:
+            raise KernelError("gemm: accumulate needs an output")
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    _need(out, "out", out_dtype)
+    if out.shape[0] < M or out.shape[1] != N:
+        raise KernelError(f"gemm: out has shape {tuple(out.shape)}, needs [{M}, {N}]")
+    if w2 is not None:
+        _need(w2, "w2", a.dtype, w.shape)
+    if a_rows is not None:
+        _need(a_rows, "a_rows", torch.int32)
+    stride = N * K if grouped else 0
+    if grouped:
+        offsets, tile_group, tile_row0, num_tiles = groups
+        max_tiles = tile_group.numel()
+    else:
+        offsets = tile_group = tile_row0 = num_tiles = None
+        max_tiles = 0
+    _call("q6k_gemm_simt", _ptr(a), _i(a.stride(0)), _ptr(a_rows), _ptr(w), _ptr(w2), _ll(stride), _ptr(out), _i(out.stride(0)),
+          _i(M), _i(N), _i(K), _ptr(tile_group), _ptr(tile_row0), _ptr(offsets), _ptr(num_tiles), _i(max_tiles), _i(epi),
+          _i(dtype_code(a.dtype)), _stream())
+    return out
+
+
+def simt_tile_rows() -> int:
+    lib = library()
+    lib.q6k_gemm_tile_rows.restype = ctypes.c_int
+    return lib.q6k_gemm_tile_rows()
+
+
+def tile_list(offsets: torch.Tensor, pairs: int, bm: int):
+    """(offsets, tile_group, tile_row0, num_tiles) for the groups' row tiles of bm rows."""
+    _need(offsets, "offsets", torch.int32)
+    G = offsets.numel() - 1
+    max_tiles = (pairs + bm - 1) // bm + G
+    tile_group = torch.empty(max_tiles, dtype=torch.int32, device=offsets.device)
+    tile_row0 = torch.empty(max_tiles, dtype=torch.int32, device=offsets.device)
+    num_tiles = torch.empty(1, dtype=torch.int32, device=offsets.device)
+    _call("q6k_tile_list", _ptr(offsets), _i(G), _i(bm), _ptr(tile_group), _ptr(tile_row0), _ptr(num_tiles), _i(max_tiles), _stream())
+    return offsets, tile_group, tile_row0, num_tiles
+
+
+# --------------------------------------------------------------------------- attention
+def qk_prep(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, q_norm, k_norm, eps: float, rope_theta: Optional[float],
+            positions: torch.Tensor, req_of_token: torch.Tensor, block_table: Optional[torch.Tensor], page_size: int,
+            k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], out_dtype: torch.dtype) -> torch.Tensor:
+    """QK-norm, RoPE, q -> out_dtype [T, Hq, hd]; k, v -> their pages (when k_pages is given)."""
+    _need(qkv, "qkv", torch.float32)
+    T = qkv.shape[0]
+    if qkv.shape[1] < (Hq + 2 * Hkv) * hd and k_pages is not None:
+        raise KernelError("qk_prep: qkv rows are too short")
+    _need(positions, "positions", torch.int32)
+    _need(req_of_token, "req_of_token", torch.int32)
+    write = k_pages is not None
+    if write:
+        _need(k_pages, "k_pages", out_dtype)
+        _need(v_pages, "v_pages", out_dtype, k_pages.shape)
+        _need(block_table, "block_table", torch.int32)
+        if tuple(k_pages.shape[1:]) != (Hkv, page_size, hd):
+            raise KernelError(f"qk_prep: pages have shape {tuple(k_pages.shape)}, expected [*, {Hkv}, {page_size}, {hd}]")
+    for nm, w in (("q_norm", q_norm), ("k_norm", k_norm)):
+        if w is not None:
+            _need(w, nm, torch.float32, (hd,))
+    q = torch.empty((T, Hq, hd), dtype=out_dtype, device=qkv.device)
+    max_blocks = block_table.shape[1] if block_table is not None else 1
+    _call("q6k_qk_prep", _ptr(qkv), _i(qkv.stride(0)), _i(T), _i(Hq), _i(Hkv), _i(hd), _ptr(q_norm), _ptr(k_norm), _f(eps),
+          _i(1 if rope_theta is not None else 0), _f(rope_theta or 0.0), _ptr(positions), _ptr(req_of_token), _ptr(block_table),
+          _i(max_blocks), _i(page_size), _ptr(q), _ptr(k_pages), _ptr(v_pages), _i(1 if write else 0),
+          _i(dtype_code(out_dtype)), _stream())
+    return q
+
+
+def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                      req_of_token: torch.Tensor, positions: torch.Tensor, window: Optional[int],
+                      sinks: Optional[torch.Tensor], scale: Optional[float] = None) -> torch.Tensor:
+    """Causal (optionally windowed, optionally with sinks) attention of every row over its request's pages."""
+    _need(q, "q")
+    T, Hq, hd = q.shape
+    _need(k_pages, "k_pages", q.dtype)
+    _need(v_pages, "v_pages", q.dtype, k_pages.shape)
+    _, Hkv, page_size, hd2 = k_pages.shape
+    if hd2 != hd:
+        raise KernelError(f"attention: q has head_dim {hd}, the pages {hd2}")
+    _need(block_table, "block_table", torch.int32)
+    _need(req_of_token, "req_of_token", torch.int32)
+    _need(positions, "positions", torch.int32)
+    if sinks is not None:
+        _need(sinks, "sinks", torch.float32, (Hq,))
+    out = torch.empty((T, Hq * hd), dtype=q.dtype, device=q.device)
+    _call("q6k_attention_generic", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), _i(block_table.shape[1]),
+          _i(page_size), _ptr(req_of_token), _ptr(positions), _i(window or 0), _ptr(sinks),
+          _f(scale if scale is not None else 1.0 / math.sqrt(hd)), _ptr(out), _i(T), _i(Hq), _i(Hkv), _i(hd),
+          _i(dtype_code(q.dtype)), _stream())
+    return out
+
+
+# --------------------------------------------------------------------------- routing
+def route(logits: torch.Tensor, k: int, scoring: str, renorm: bool):
+    """(sel_e int32 [T, k], sel_w float32 [T, k])."""
+    _need(logits, "logits", torch.float32)
+    T, E = logits.shape
+    if scoring not in ("softmax", "sigmoid"):
+        raise KernelError(f"route: unknown scoring {scoring!r}")
+    sel_e = torch.empty((T, k), dtype=torch.int32, device=logits.device)
+    sel_w = torch.empty((T, k), dtype=torch.float32, device=logits.device)
+    _call("q6k_route", _ptr(logits), _i(T), _i(E), _i(k), _i(1 if scoring == "sigmoid" else 0), _i(1 if renorm else 0),
+          _ptr(sel_e), _ptr(sel_w), _stream())
+    return sel_e, sel_w
+
+
+def moe_permute(sel_e: torch.Tensor, E: int):
+    """(offsets [E+1], pair_row [T, k], row_token [T*k]): rows sorted by expert, stable in pair order."""
+    _need(sel_e, "sel_e", torch.int32)
+    T, k = sel_e.shape
+    pairs = T * k
+    dev = sel_e.device
+    counts = torch.empty(E, dtype=torch.int32, device=dev)
+    rank = torch.empty(pairs, dtype=torch.int32, device=dev)
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    pair_row = torch.empty((T, k), dtype=torch.int32, device=dev)
+    row_token = torch.empty(pairs, dtype=torch.int32, device=dev)
+    _call("q6k_moe_permute", _ptr(sel_e), _i(pairs), _i(k), _i(E), _ptr(counts), _ptr(rank), _ptr(offsets), _ptr(pair_row),
+          _ptr(row_token), _stream())
+    return offsets, pair_row, row_token
+
+
+# --------------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    """int32 [rows]; ties go to the lower id."""
+    _need(logits, "logits", torch.float32)
+    rows, V = logits.shape
+    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _call("q6k_argmax", _ptr(logits), _i(rows), _i(V), _ptr(out), _stream())
+    return out
+
+
+def topk_pool(logits: torch.Tensor, k: int):
+    """(ids int32 [rows, k], vals float32 [rows, k]) sorted by (logit descending, id ascending); k <= 256."""
+    _need(logits, "logits", torch.float32)
+    rows, V = logits.shape
+    ids = torch.empty((rows, k), dtype=torch.int32, device=logits.device)
+    vals = torch.empty((rows, k), dtype=torch.float32, device=logits.device)
+    _call("q6k_topk_pool", _ptr(logits), _i(rows), _i(V), _i(k), _ptr(ids), _ptr(vals), _stream())
+    return ids, vals

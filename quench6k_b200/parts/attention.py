@@ -1,0 +1,95 @@
+"""Grouped-query self-attention over the paged cache, with optional per-head QK-norm, learned
+sinks and a sliding window (reference: crates/engine/src/flint.rs:815-913 for the order of
+operations, crates/cuda/kernels/flint.cu:125-173 and :211-561 for the arithmetic)."""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..spec import PartSpec, TensorSpec
+from . import linear
+from .base import (POSITION_ENCODINGS, CacheRequest, Mixer, make_part, register_mixer, to_f32, to_operand)
+
+
+@register_mixer("attention")
+class Attention(Mixer):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, eps: float,
+                 pos: PartSpec, window: Optional[int] = None, sinks: bool = False, qk_norm: bool = False,
+                 norm_init: str = "ones", sink_std: float = 1.0):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} KV heads")
+        if head_dim % 16 or head_dim > 256:
+            raise ValueError(f"head_dim {head_dim}: the attention kernels take multiples of 16 up to 256")
+        self.D, self.Hq, self.Hkv, self.hd = hidden_size, num_heads, num_kv_heads, head_dim
+        self.eps, self.window, self.has_sinks, self.qk_norm = float(eps), window, sinks, qk_norm
+        self.norm_init, self.sink_std = norm_init, sink_std
+        self.pos = make_part(POSITION_ENCODINGS, "position encoding", pos)
+        self.scale = 1.0 / math.sqrt(head_dim)
+
+    def tensors(self):
+        D, Hq, Hkv, hd = self.D, self.Hq, self.Hkv, self.hd
+        out = [TensorSpec("q_proj.weight", (Hq * hd, D)), TensorSpec("k_proj.weight", (Hkv * hd, D)),
+               TensorSpec("v_proj.weight", (Hkv * hd, D)), TensorSpec("o_proj.weight", (D, Hq * hd))]
+        if self.qk_norm:
+            init = ("ones",) if self.norm_init == "ones" else ("ones_plus", 0.1)
+            out += [TensorSpec("q_norm.weight", (hd,), "f32", init), TensorSpec("k_norm.weight", (hd,), "f32", init)]
+        if self.has_sinks:
+            out.append(TensorSpec("sinks", (Hq,), "f32", ("normal", self.sink_std)))
+        return out
+
+    def bind(self, get, rt):
+        self.rt = rt
+        # q, k and v rows stacked so one product yields [q | k | v] per token
+        self.w_qkv = torch.cat([to_operand(get("q_proj.weight"), rt), to_operand(get("k_proj.weight"), rt),
+                                to_operand(get("v_proj.weight"), rt)], dim=0).contiguous()
+        self.w_q = self.w_qkv[: self.Hq * self.hd]
+        self.w_o = to_operand(get("o_proj.weight"), rt)
+        self.q_norm = to_f32(get("q_norm.weight"), rt) if self.qk_norm else None
+        self.k_norm = to_f32(get("k_norm.weight"), rt) if self.qk_norm else None
+        self.sinks = to_f32(get("sinks"), rt) if self.has_sinks else None
+
+    def cache_request(self):
+        if self.window is not None:
+            return CacheRequest("sliding", int(self.window), self.Hkv, self.hd)
+        return CacheRequest("full", None, self.Hkv, self.hd)
+
+    def forward(self, xn, ctx, cache, state, out):
+        rt = self.rt
+        write = cache.write
+        qkv = linear.matmul(xn, self.w_qkv if write else self.w_q, rt)          # FP32 [T, (Hq + 2 Hkv) hd] or [T, Hq hd]
+        theta = self.pos.fused_rope_theta()
+        table = ctx.block_tables[cache.group]
+        if theta is None and not isinstance(self.pos, POSITION_ENCODINGS["none"]):
+            qkv = self._unfused_position(qkv, ctx, write)
+            q = ops.qk_prep(qkv, self.Hq, self.Hkv, self.hd, None, None, self.eps, None, ctx.positions, ctx.req_of_token,
+                            table if write else None, cache.page_size, cache.k if write else None,
+                            cache.v if write else None, rt.dtype)
+        else:
+            q = ops.qk_prep(qkv, self.Hq, self.Hkv, self.hd, self.q_norm, self.k_norm, self.eps, theta, ctx.positions,
+                            ctx.req_of_token, table if write else None, cache.page_size, cache.k if write else None,
+                            cache.v if write else None, rt.dtype)
+        a = ops.attention_generic(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, self.window, self.sinks,
+                                  self.scale)
+        linear.matmul(a, self.w_o, rt, out=out, accumulate=True)
+
+    def _unfused_position(self, qkv, ctx, write):
+        """QK-norm, then a position encoding that is not the fused rotary one, on FP32 q and k."""
+        T = qkv.shape[0]
+        nq, nk = self.Hq * self.hd, self.Hkv * self.hd
+        q = qkv[:, :nq].reshape(T * self.Hq, self.hd).contiguous()
+        if self.qk_norm:
+            q = ops.rmsnorm(q, self.q_norm, self.eps, torch.float32)
+        q = q.view(T, self.Hq, self.hd)
+        self.pos.apply(q, ctx.positions)
+        parts = [q.reshape(T, nq)]
+        if write:
+            k = qkv[:, nq:nq + nk].reshape(T * self.Hkv, self.hd).contiguous()
+            if self.qk_norm:
+                k = ops.rmsnorm(k, self.k_norm, self.eps, torch.float32)
+            k = k.view(T, self.Hkv, self.hd)
+            self.pos.apply(k, ctx.positions)
+            parts += [k.reshape(T, nk), qkv[:, nq + nk:]]
+        return torch.cat(parts, dim=1).contiguous()

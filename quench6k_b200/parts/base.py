@@ -1,0 +1,146 @@
+"""Interfaces of the parts a layer is put together from, and their registries.
+
+A part gets its sizes and constants as constructor parameters, declares the tensors it needs
+(names relative to its own prefix), binds them once, and runs on whatever rows the step hands it.
+No part knows which model it is in.
+
+To add a part, subclass the matching base, implement the methods below and register the class
+under a name with the matching `register_*`; a spec.PartSpec(kind=name, params=...) then selects it.
+
+  Norm            tensors(); bind(); forward(h_f32 [T, D], rows=None) -> [R, D] in the operand dtype
+  PositionEncoding  fused_rope_theta() -> float | None (None: not the fused rotary);
+                  apply(x_f32 [T, H, hd], positions_i32 [T]) -> None, in place (used when not fused)
+  Mixer           tensors(); bind(); cache_request() -> CacheRequest | None; state_shape() -> tuple | None;
+                  forward(xn [T, D], ctx: StepContext, cache: LayerCache | None, state: Tensor | None, out_f32 [T, D])
+                  adds its result into `out`
+  FeedForward     tensors(); bind(); forward(xn [T, D], ctx, out_f32 [T, D]) adds its result into `out`
+  Block           built from (norm1, mixer, norm2, ffn); forward(h, ctx, cache, state)
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, Dict, List, Optional, Tuple
+
+import torch
+
+from ..spec import PartSpec, TensorSpec
+
+
+@dataclass
+class Runtime:
+    """Where and in which precision the parts run."""
+    device: torch.device
+    dtype: torch.dtype                  # operand, activation and cache dtype: bfloat16, or float32 for the true 32-bit path
+    tensor_cores: bool = True           # bfloat16 only: use the tcgen05 kernels where a shape allows
+
+    @property
+    def is_fp32(self) -> bool:
+        return self.dtype == torch.float32
+
+
+@dataclass
+class CacheRequest:
+    """What a mixer needs from the cache manager.  Layers with equal requests share a group
+    (one block table per request and group)."""
+    kind: str                           # "full": every key; "sliding": the last `window` keys
+    window: Optional[int]
+    kv_heads: int
+    head_dim: int
+
+    def key(self) -> Tuple:
+        return (self.kind, self.window, self.kv_heads, self.head_dim)
+
+
+@dataclass
+class LayerCache:
+    """The pages of one executed layer position.  k, v: [num_pages, kv_heads, page_size, head_dim]."""
+    group: int
+    k: torch.Tensor
+    v: torch.Tensor
+    page_size: int
+    write: bool = True                  # False: this position reads the pages another position wrote
+
+
+class Part:
+    def tensors(self) -> List[TensorSpec]:
+        return []
+
+    def bind(self, get: Callable[[str], torch.Tensor], rt: Runtime) -> None:
+        """`get(name)` returns the stored tensor (on any device, stored dtype) by relative name."""
+        self.rt = rt
+
+
+class Norm(Part):
+    def forward(self, h: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def fused_rope_theta(self) -> Optional[float]:
+        return None
+
+    def apply(self, x: torch.Tensor, positions: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_request(self) -> Optional[CacheRequest]:
+        return None
+
+    def state_shape(self) -> Optional[Tuple[int, ...]]:
+        """Shape of this mixer's fixed-size per-request state (float32), or None."""
+        return None
+
+    def forward(self, xn, ctx, cache: Optional[LayerCache], state: Optional[torch.Tensor], out: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, xn, ctx, out: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
+class Block:
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, ffn: FeedForward):
+        self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
+
+    def forward(self, h, ctx, cache, state) -> None:
+        raise NotImplementedError
+
+
+NORMS: Dict[str, type] = {}
+POSITION_ENCODINGS: Dict[str, type] = {}
+MIXERS: Dict[str, type] = {}
+FEED_FORWARDS: Dict[str, type] = {}
+BLOCKS: Dict[str, type] = {}
+
+
+def _register(table: Dict[str, type], what: str):
+    def deco_for(name: str):
+        def deco(cls):
+            table[name] = cls
+            return cls
+        return deco
+    return deco_for
+
+
+register_norm = _register(NORMS, "norm")
+register_position_encoding = _register(POSITION_ENCODINGS, "position encoding")
+register_mixer = _register(MIXERS, "mixer")
+register_feed_forward = _register(FEED_FORWARDS, "feed-forward")
+register_block = _register(BLOCKS, "block")
+
+
+def make_part(table: Dict[str, type], what: str, spec: PartSpec, **extra):
+    if spec.kind not in table:
+        raise KeyError(f"unknown {what} {spec.kind!r}; registered: {', '.join(sorted(table))}")
+    return table[spec.kind](**extra, **spec.params)
+
+
+def to_operand(t: torch.Tensor, rt: Runtime) -> torch.Tensor:
+    """A stored matrix as the kernels consume it: on the device, in the runtime's operand dtype."""
+    return t.to(device=rt.device, dtype=rt.dtype).contiguous()
+
+
+def to_f32(t: torch.Tensor, rt: Runtime) -> torch.Tensor:
+    return t.to(device=rt.device, dtype=torch.float32).contiguous()

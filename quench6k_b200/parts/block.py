@@ -1,0 +1,14 @@
+"""Arrangement of the parts in a block.  "prenorm": h += mixer(norm1(h)); h += ffn(norm2(h)),
+the residual stream h staying FP32 (reference: crates/engine/src/flint.rs:815-1075, :617)."""
+from __future__ import annotations
+
+from .base import Block, register_block
+
+
+@register_block("prenorm")
+class PreNormBlock(Block):
+    def forward(self, h, ctx, cache, state):
+        xn = self.norm1.forward(h)
+        self.mixer.forward(xn, ctx, cache, state, h)
+        xn = self.norm2.forward(h)
+        self.ffn.forward(xn, ctx, h)

@@ -1,0 +1,80 @@
+"""Feed-forward parts: a dense SwiGLU MLP and a routed mixture of SwiGLU experts with an optional
+ungated shared expert.
+
+Reference: crates/engine/src/flint.rs:915-1075 (order of operations),
+crates/cuda/kernels/flint.cu:829-868 (sigmoid routing), crates/cuda/kernels/moe.cu:19-71 (softmax
+routing), flint.cu:1163-1239 (permutation, SwiGLU, combine in slot order).  The reference runs
+its dense MLP and its shared expert as extra expert slots with weight 1; here they are the dense
+part, added after the routed sum.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..spec import TensorSpec
+from . import linear
+from .base import FeedForward, register_feed_forward, to_operand
+
+
+@register_feed_forward("dense")
+class DenseSwiGLU(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int):
+        self.D, self.I = hidden_size, intermediate_size
+
+    def tensors(self):
+        return [TensorSpec("gate_proj.weight", (self.I, self.D)), TensorSpec("up_proj.weight", (self.I, self.D)),
+                TensorSpec("down_proj.weight", (self.D, self.I))]
+
+    def bind(self, get, rt):
+        self.rt = rt
+        self.w_gate, self.w_up = to_operand(get("gate_proj.weight"), rt), to_operand(get("up_proj.weight"), rt)
+        self.w_down = to_operand(get("down_proj.weight"), rt)
+
+    def forward(self, xn, ctx, out):
+        act = linear.swiglu_matmul(xn, self.w_gate, self.w_up, self.rt)
+        linear.matmul(act, self.w_down, self.rt, out=out, accumulate=True)
+
+
+@register_feed_forward("moe")
+class RoutedExperts(FeedForward):
+    def __init__(self, hidden_size: int, num_experts: int, top_k: int, intermediate_size: int, scoring: str = "softmax",
+                 renormalize: bool = True, shared_intermediate_size: int = 0):
+        if scoring not in ("softmax", "sigmoid"):
+            raise ValueError(f"unknown router scoring {scoring!r}")
+        if not 0 < top_k <= num_experts:
+            raise ValueError(f"top_k {top_k} outside 1..{num_experts}")
+        self.D, self.E, self.k, self.I = hidden_size, num_experts, top_k, intermediate_size
+        self.scoring, self.renorm = scoring, bool(renormalize)
+        self.shared = DenseSwiGLU(hidden_size, shared_intermediate_size) if shared_intermediate_size > 0 else None
+
+    def tensors(self):
+        E, I, D = self.E, self.I, self.D
+        out = [TensorSpec("gate.weight", (E, D)), TensorSpec("experts.gate_proj.weight", (E, I, D)),
+               TensorSpec("experts.up_proj.weight", (E, I, D)), TensorSpec("experts.down_proj.weight", (E, D, I))]
+        if self.shared is not None:
+            out += [TensorSpec("shared_experts." + t.name, t.shape, t.role, t.init) for t in self.shared.tensors()]
+        return out
+
+    def bind(self, get, rt):
+        self.rt = rt
+        self.w_router = to_operand(get("gate.weight"), rt)
+        self.w_gate = to_operand(get("experts.gate_proj.weight"), rt)
+        self.w_up = to_operand(get("experts.up_proj.weight"), rt)
+        self.w_down = to_operand(get("experts.down_proj.weight"), rt)
+        if self.shared is not None:
+            self.shared.bind(lambda n: get("shared_experts." + n), rt)
+
+    def forward(self, xn, ctx, out):
+        rt = self.rt
+        T = xn.shape[0]
+        pairs = T * self.k
+        logits = linear.matmul(xn, self.w_router, rt)                       # FP32 [T, E]
+        sel_e, sel_w = ops.route(logits, self.k, self.scoring, self.renorm)
+        offsets, pair_row, row_token = ops.moe_permute(sel_e, self.E)
+        groups = linear.group_tiles(offsets, pairs, rt)
+        act = linear.grouped_swiglu(xn, row_token, self.w_gate, self.w_up, groups, pairs, rt)    # [pairs, I]
+        y = linear.grouped_matmul(act, self.w_down, groups, pairs, rt)                            # FP32 [pairs, D]
+        ops.combine(y, pair_row, sel_w, out)
+        if self.shared is not None:
+            self.shared.forward(xn, ctx, out)

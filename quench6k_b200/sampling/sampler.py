@@ -1,0 +1,112 @@
+"""Greedy and sampled token choice.
+
+As in the reference (crates/cli/src/flint.rs:293-431), the device delivers, per logits row, either
+the argmax (greedy without penalties: ties to the lower id) or an exact pool of the top candidates
+(at most 256, or top_k if smaller; at least 64 when penalties may reorder them); the host applies
+presence and repetition penalties, sorts by (logit descending, id ascending), and for sampled
+requests computes p_i = exp((l_i - l_0) / temperature) in double precision, drops p_i < min_p,
+keeps the shortest prefix whose mass reaches top_p and inverts the CDF with u * total.
+
+u is the next value of a splitmix64 stream that starts at the request's seed
+(crates/cli/src/flint.rs:318-325), one value per sampled token of that request, so a request's
+tokens do not depend on what else was in its batches.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from .params import SamplingParams
+
+POOL = 256
+_M64 = (1 << 64) - 1
+
+
+class SplitMix64:
+    def __init__(self, seed: int):
+        self.state = seed & _M64
+
+    def uniform(self) -> float:
+        self.state = (self.state + 0x9E3779B97F4A7C15) & _M64
+        z = self.state
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _M64
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _M64
+        z ^= z >> 31
+        return (z >> 11) / float(1 << 53)
+
+
+def pool_size(p: SamplingParams, vocab: int) -> int:
+    if p.greedy and not p.penalized:
+        return 1
+    if p.top_k == 0:
+        n = POOL
+    else:
+        n = min(max(p.top_k, 64 if p.penalized else 1), POOL)
+    return min(n, vocab)
+
+
+def pick_from_pool(ids: Sequence[int], vals: Sequence[float], p: SamplingParams, generated: Sequence[int], rng: SplitMix64) -> int:
+    """One token from a candidate pool (any order) under the request's options."""
+    vals = np.asarray(vals, dtype=np.float32).copy()
+    ids = np.asarray(ids, dtype=np.int64)
+    if p.penalized and len(generated):
+        seen = np.isin(ids, np.asarray(list(set(generated)), dtype=np.int64))
+        v = vals[seen] - np.float32(p.presence_penalty)
+        v = np.where(v > 0, v / np.float32(p.repetition_penalty), v * np.float32(p.repetition_penalty)).astype(np.float32)
+        vals[seen] = v
+    order = np.lexsort((ids, -vals.astype(np.float64)))        # by logit descending, then id ascending
+    if p.greedy:
+        return int(ids[order[0]])
+    keep = len(order) if p.top_k == 0 else min(p.top_k, len(order))
+    order = order[:keep]
+    top = vals[order[0]]
+    scaled = ((vals[order] - top) / np.float32(p.temperature)).astype(np.float32)
+    probs = [math.exp(float(s)) for s in scaled]
+    if p.min_p > 0.0:
+        probs = [q if q >= p.min_p else 0.0 for q in probs]
+    total = sum(probs)
+    cut = len(probs)
+    if p.top_p < 1.0:
+        acc = 0.0
+        for i, q in enumerate(probs):
+            acc += q / total
+            if acc >= p.top_p:
+                cut = i + 1
+                break
+    total = sum(probs[:cut])
+    r = rng.uniform() * total
+    for i in range(cut):
+        r -= probs[i]
+        if r <= 0.0:
+            return int(ids[order[i]])
+    return int(ids[order[cut - 1]])
+
+
+class Sampler:
+    """Chooses the next token of each row of a logits block [rows, vocab] (device, FP32)."""
+
+    def sample(self, logits: torch.Tensor, params: List[SamplingParams], generated: List[Sequence[int]],
+               rngs: List[SplitMix64]) -> List[int]:
+        rows, vocab = logits.shape
+        sizes = [pool_size(p, vocab) for p in params]
+        out: List[int] = [0] * rows
+        if all(s == 1 for s in sizes):
+            picked = ops.argmax(logits).tolist()
+            return [int(t) for t in picked]
+        greedy_rows = [i for i, s in enumerate(sizes) if s == 1]
+        if greedy_rows:
+            picked = ops.argmax(logits).tolist()
+            for i in greedy_rows:
+                out[i] = int(picked[i])
+        k = max(sizes)
+        ids, vals = ops.topk_pool(logits, k)
+        ids, vals = ids.tolist(), vals.tolist()
+        for i, s in enumerate(sizes):
+            if s == 1:
+                continue
+            out[i] = pick_from_pool(ids[i][:s], vals[i][:s], params[i], generated[i], rngs[i])
+        return out

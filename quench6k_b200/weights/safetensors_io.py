@@ -1,0 +1,125 @@
+"""Reading and writing safetensors files without a library: 8-byte little-endian header length,
+a JSON header {name: {dtype, shape, data_offsets}}, then the raw little-endian data.
+
+Behaviour follows the reference's index (crates/engine/src/checkpoint.rs:108-246): every
+`*.safetensors` of a folder (or the shards that `model.safetensors.index.json` names) is indexed
+by tensor name, byte ranges are checked against the file, and a name that occurs twice is an error.
+"""
+from __future__ import annotations
+
+import json
+import mmap
+import os
+import struct
+from dataclasses import dataclass
+from typing import Dict, Iterable, List, Tuple
+
+import torch
+
+_DTYPES = {
+    "BF16": (torch.bfloat16, 2), "F16": (torch.float16, 2), "F32": (torch.float32, 4), "F64": (torch.float64, 8),
+    "I8": (torch.int8, 1), "U8": (torch.uint8, 1), "I16": (torch.int16, 2), "I32": (torch.int32, 4),
+    "I64": (torch.int64, 8), "BOOL": (torch.bool, 1),
+}
+_NAMES = {v[0]: k for k, v in _DTYPES.items()}
+
+
+class SafetensorsError(ValueError):
+    pass
+
+
+@dataclass
+class TensorEntry:
+    name: str
+    dtype: torch.dtype
+    shape: Tuple[int, ...]
+    path: str
+    begin: int        # absolute byte offsets in the file
+    end: int
+
+
+class SafetensorsFile:
+    def __init__(self, path: str):
+        self.path = path
+        size = os.path.getsize(path)
+        with open(path, "rb") as f:
+            head = f.read(8)
+            if len(head) < 8:
+                raise SafetensorsError(f"{path}: shorter than a safetensors header")
+            (n,) = struct.unpack("<Q", head)
+            if n > size - 8:
+                raise SafetensorsError(f"{path}: header length {n} exceeds the file ({size} bytes)")
+            try:
+                header = json.loads(f.read(n))
+            except json.JSONDecodeError as e:
+                raise SafetensorsError(f"{path}: header is not JSON ({e})") from None
+        base = 8 + n
+        self.entries: Dict[str, TensorEntry] = {}
+        for name, info in header.items():
+            if name == "__metadata__":
+                continue
+            if info["dtype"] not in _DTYPES:
+                raise SafetensorsError(f"{path}: tensor {name} has unsupported dtype {info['dtype']}")
+            dt, width = _DTYPES[info["dtype"]]
+            shape = tuple(int(x) for x in info["shape"])
+            b, e = info["data_offsets"]
+            count = 1
+            for s in shape:
+                count *= s
+            if e - b != count * width or b < 0 or base + e > size:
+                raise SafetensorsError(f"{path}: tensor {name} has byte range {b}..{e} for shape {shape} {info['dtype']} in a file of {size} bytes")
+            self.entries[name] = TensorEntry(name, dt, shape, path, base + b, base + e)
+        self._mm = None
+
+    def read(self, name: str) -> torch.Tensor:
+        """A CPU tensor with the stored dtype and shape (a copy; the map is not kept alive by it)."""
+        ent = self.entries[name]
+        if self._mm is None:
+            self._f = open(self.path, "rb")
+            self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ)
+        nbytes = ent.end - ent.begin
+        if nbytes == 0:
+            return torch.empty(ent.shape, dtype=ent.dtype)
+        buf = bytearray(self._mm[ent.begin:ent.end])
+        return torch.frombuffer(buf, dtype=ent.dtype).reshape(ent.shape)
+
+
+def index_folder(folder: str) -> Dict[str, Tuple[SafetensorsFile, TensorEntry]]:
+    """name -> (file, entry) over a model folder's safetensors files."""
+    idx_path = os.path.join(folder, "model.safetensors.index.json")
+    if os.path.exists(idx_path):
+        with open(idx_path) as f:
+            files = sorted(set(json.load(f)["weight_map"].values()))
+    else:
+        files = sorted(p for p in os.listdir(folder) if p.endswith(".safetensors"))
+    if not files:
+        raise SafetensorsError(f"{folder}: no .safetensors file")
+    out: Dict[str, Tuple[SafetensorsFile, TensorEntry]] = {}
+    for fn in files:
+        sf = SafetensorsFile(os.path.join(folder, fn))
+        for name, ent in sf.entries.items():
+            if name in out:
+                raise SafetensorsError(f"duplicate tensor {name} in {out[name][0].path} and {sf.path}")
+            out[name] = (sf, ent)
+    return out
+
+
+def write_safetensors(path: str, tensors: Iterable[Tuple[str, torch.Tensor]]) -> None:
+    """Write CPU tensors in the given order."""
+    items: List[Tuple[str, torch.Tensor]] = [(n, t.detach().cpu().contiguous()) for n, t in tensors]
+    header = {}
+    off = 0
+    for name, t in items:
+        if t.dtype not in _NAMES:
+            raise SafetensorsError(f"tensor {name}: dtype {t.dtype} cannot be stored")
+        nb = t.numel() * t.element_size()
+        header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + nb]}
+        off += nb
+    blob = json.dumps(header, separators=(",", ":")).encode()
+    blob += b" " * ((8 - len(blob) % 8) % 8)
+    with open(path, "wb") as f:
+        f.write(struct.pack("<Q", len(blob)))
+        f.write(blob)
+        for _, t in items:
+            if t.numel():
+                f.write(t.view(torch.uint8).numpy().tobytes() if t.dtype != torch.bool else t.numpy().tobytes())

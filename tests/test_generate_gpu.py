@@ -1,0 +1,95 @@
+"""Generation through the Python entry point and the command line, against the plain implementation."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import helpers
+import plain_flint as P
+
+pytestmark = pytest.mark.gpu
+
+
+def plain_greedy(cfg, weights, prompt, n):
+    toks = list(prompt)
+    margins = []
+    for _ in range(n):
+        logits = P.forward(cfg, weights, toks, dtype=torch.float64)[-1]
+        top = torch.topk(logits, 2).values
+        margins.append(float(top[0] - top[1]))
+        toks.append(int(torch.argmax(logits)))
+    return toks[len(prompt):], margins
+
+
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("A", "bfloat16"), ("C", "bfloat16")])
+def test_greedy_generation_matches_plain(tmp_path, name, dtype):
+    from quench6k_b200 import Engine, SamplingParams
+    cfg, weights = helpers.make_model_folder(str(tmp_path), name, seed=21)
+    prompts = [helpers.random_tokens(n, cfg["vocab_size"], 300 + n) for n in (7, 13, 5)]
+    eng = Engine.from_folder(str(tmp_path), dtype=dtype, num_pages=24, max_batch_tokens=6)     # prompts are cut into portions
+    outs = eng.generate(prompts, SamplingParams(max_tokens=8, temperature=0.0))
+    for p, o in zip(prompts, outs):
+        want, margins = plain_greedy(cfg, weights, p, 8)
+        assert o.finish_reason == "length" and len(o.tokens) == 8
+        for i, (g, w) in enumerate(zip(o.tokens, want)):
+            if g != w:
+                # a different token is only acceptable at a near-tie of the reference's two best logits
+                assert dtype == "bfloat16" and margins[i] < 2e-3, (i, g, w, margins[i])
+                break
+    eng.runner.manager.check()
+    assert not eng.runner.manager.requests
+
+
+def test_sampled_generation_is_reproducible_and_batch_independent(tmp_path):
+    from quench6k_b200 import Engine, SamplingParams
+    cfg, _ = helpers.make_model_folder(str(tmp_path), "B", seed=22)
+    prompts = [helpers.random_tokens(n, cfg["vocab_size"], 400 + n) for n in (5, 17, 29)]
+    params = [SamplingParams(max_tokens=10, temperature=0.8, top_k=0, top_p=1.0, seed=1000 + i) for i in range(3)]
+    eng = Engine.from_folder(str(tmp_path), dtype="float32", num_pages=32, max_batch_tokens=6)
+    together = eng.generate(prompts, params)
+    alone = [eng.generate([p], [sp])[0] for p, sp in zip(prompts, params)]
+    for a, b in zip(together, alone):
+        assert a.tokens == b.tokens
+    assert len({tuple(o.tokens) for o in together}) == 3
+    other = eng.generate(prompts[:1], [SamplingParams(max_tokens=10, temperature=0.8, top_k=0, top_p=1.0, seed=5)])[0]
+    assert other.tokens != together[0].tokens
+
+
+def test_preemption_gives_the_same_tokens(tmp_path):
+    from quench6k_b200 import Engine, SamplingParams
+    cfg, _ = helpers.make_model_folder(str(tmp_path), "A", seed=23)
+    prompts = [helpers.random_tokens(n, cfg["vocab_size"], 500 + n) for n in (9, 11, 6)]
+    sp = SamplingParams(max_tokens=14, temperature=0.0)
+    roomy = Engine.from_folder(str(tmp_path), dtype="float32", num_pages=64)
+    want = [o.tokens for o in roomy.generate(prompts, sp)]
+    tight = Engine.from_folder(str(tmp_path), dtype="float32", num_pages=12)      # 48 token places for 68 tokens
+    outs = tight.generate(prompts, sp)
+    assert tight.stats["preemptions"] > 0
+    assert [o.tokens for o in outs] == want
+    tight.runner.manager.check()
+
+
+def test_stop_token_ends_generation(tmp_path):
+    from quench6k_b200 import Engine, SamplingParams
+    cfg, _ = helpers.make_model_folder(str(tmp_path), "A", seed=24)
+    eng = Engine.from_folder(str(tmp_path), dtype="float32", num_pages=32)
+    prompt = helpers.random_tokens(10, cfg["vocab_size"], 1)
+    free = eng.generate([prompt], SamplingParams(max_tokens=12, temperature=0.0))[0].tokens
+    stop = free[4]
+    out = eng.generate([prompt], SamplingParams(max_tokens=12, temperature=0.0, stop_tokens=[stop]))[0]
+    assert out.finish_reason == "stop" and out.tokens == free[:free.index(stop) + 1]
+
+
+def test_command_line(tmp_path):
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg, weights = helpers.make_model_folder(str(tmp_path), "A", seed=25)
+    prompt = helpers.random_tokens(7, cfg["vocab_size"], 9)
+    r = subprocess.run([sys.executable, "-m", "quench6k_b200", "generate", "--model", str(tmp_path), "--prompt-ids",
+                        ",".join(map(str, prompt)), "--n", "8", "--dtype", "float32", "--context", "64"],
+                       cwd=root, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "prompt: 7 tokens" in r.stdout and "first-token top 5:" in r.stdout and "decode 7 tokens" in r.stdout
+    want, _ = plain_greedy(cfg, weights, prompt, 8)
+    assert f"ids: {want}" in r.stdout

@@ -1,0 +1,228 @@
+"""Each kernel alone against a plain PyTorch FP32 reference of the same operation, at sizes other
+than the engine's tiny configurations (odd widths, head sizes in steps of 16, ragged groups)."""
+import math
+
+import pytest
+import torch
+
+import plain_flint as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _t(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("V,D,T", [(50, 24, 7), (333, 100, 19)])
+def test_embed(dtype, V, D, T):
+    from quench6k_b200 import ops
+    table = _t(V, D, dtype=dtype)
+    tok = torch.randint(0, V, (T,), dtype=torch.int32, device=DEV)
+    out = ops.embed(tok, table)
+    assert torch.equal(out, table[tok.long()].float())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("R,D,eps", [(5, 72, 1e-6), (33, 2048, 1e-5), (3, 1000, 1e-3)])
+def test_rmsnorm(dtype, R, D, eps):
+    from quench6k_b200 import ops
+    x, w = _t(R, D, scale=3.0), _t(D, seed=1) + 1.0
+    out = ops.rmsnorm(x, w, eps, dtype)
+    ref = P.rmsnorm(x.double().cpu(), w.double().cpu(), eps)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert (out.double().cpu() - ref).abs().max() <= tol * ref.abs().max()
+    rows = torch.tensor([R - 1, 0, 2], dtype=torch.int32, device=DEV)
+    sel = ops.rmsnorm(x, w, eps, dtype, rows=rows)
+    assert torch.equal(sel, out[rows.long()])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K", [(1, 70, 33), (65, 129, 100), (200, 64, 257), (3, 1000, 72)])
+def test_gemm_simt(dtype, M, N, K):
+    from quench6k_b200 import ops
+    a, w = _t(M, K, dtype=dtype), _t(N, K, dtype=dtype, seed=1)
+    ref = a.double().cpu() @ w.double().cpu().T
+    out = ops.gemm_simt(a, w)
+    assert out.dtype == torch.float32
+    assert (out.double().cpu() - ref).abs().max() <= 2e-5 * math.sqrt(K) * ref.abs().max()
+    base = _t(M, N, seed=2)
+    acc = base.clone()
+    ops.gemm_simt(a, w, out=acc, accumulate=True)
+    assert (acc.double().cpu() - (base.double().cpu() + ref)).abs().max() <= 2e-5 * math.sqrt(K) * ref.abs().max()
+    # rows do not depend on the batch they are in
+    one = ops.gemm_simt(a[M // 2:M // 2 + 1].contiguous(), w)
+    assert torch.equal(one[0], out[M // 2])
+    w2 = _t(N, K, dtype=dtype, seed=3)
+    act = ops.gemm_simt(a, w, w2=w2)
+    g, u = ref, a.double().cpu() @ w2.double().cpu().T
+    want = P.silu(g) * u
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert act.dtype == dtype
+    assert (act.double().cpu() - want).abs().max() <= tol * math.sqrt(K) * want.abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_grouped_gemm_and_permutation(dtype):
+    from quench6k_b200 import ops
+    T, k, E, D, I = 37, 3, 10, 56, 24
+    g = torch.Generator().manual_seed(4)
+    sel = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32).to(DEV)
+    sel[:, 0] = torch.where(sel[:, 0] == 7, sel[:, 1], sel[:, 0])         # leave expert 7 nearly empty
+    offsets, pair_row, row_token = ops.moe_permute(sel, E)
+    flat = sel.flatten().cpu()
+    order = torch.sort(flat, stable=True).indices
+    assert offsets.cpu().tolist() == [int((flat < e).sum()) for e in range(E + 1)]
+    assert torch.equal(row_token.cpu().long(), order // k)
+    assert torch.equal(pair_row.flatten().cpu().long()[order], torch.arange(T * k))
+    groups = ops.tile_list(offsets, T * k, ops.simt_tile_rows())
+    x, wg, wu = _t(T, D, dtype=dtype), _t(E, I, D, dtype=dtype, seed=1), _t(E, I, D, dtype=dtype, seed=2)
+    wd = _t(E, D, I, dtype=dtype, seed=3)
+    act = ops.gemm_simt(x, wg, w2=wu, a_rows=row_token, groups=groups, rows=T * k)
+    y = ops.gemm_simt(act, wd, groups=groups, rows=T * k)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    for row in range(T * k):
+        e, t = int(flat[order[row]]), int(order[row]) // k
+        xa = x[t].double().cpu()
+        a_ref = P.silu(wg[e].double().cpu() @ xa) * (wu[e].double().cpu() @ xa)
+        assert (act[row].double().cpu() - a_ref).abs().max() <= tol * a_ref.abs().max() + 1e-9
+        y_ref = wd[e].double().cpu() @ act[row].double().cpu()
+        assert (y[row].double().cpu() - y_ref).abs().max() <= 1e-4 * y_ref.abs().max() + 1e-9
+    w = torch.rand(T, k, generator=g).to(DEV)
+    h = _t(T, D, seed=9)
+    want = h.double().cpu() + (w.double().cpu()[:, :, None] * y.double().cpu()[pair_row.cpu().long()]).sum(1)
+    ops.combine(y, pair_row, w, h)
+    assert (h.double().cpu() - want).abs().max() <= 1e-5 * want.abs().max()
+
+
+@pytest.mark.parametrize("scoring", ["softmax", "sigmoid"])
+@pytest.mark.parametrize("renorm", [True, False])
+@pytest.mark.parametrize("T,E,k", [(9, 6, 3), (40, 256, 8), (5, 100, 100), (3, 3000, 6)])
+def test_route(scoring, renorm, T, E, k):
+    from quench6k_b200 import ops
+    z = _t(T, E, scale=2.0)
+    z[:, 1] = z[:, 0]                                                    # ties
+    z = (z * 4).round() / 4
+    sel, w = ops.route(z, k, scoring, renorm)
+    rsel, rw = P.route(z.cpu().float(), scoring, k, renorm)
+    assert torch.equal(sel.cpu().long(), rsel)
+    assert (w.cpu() - rw).abs().max() <= 1e-5 * rw.abs().max()
+
+
+def _paged(k, v, page_size, num_pages, dtype, seed):
+    """Scatter whole-sequence k, v [T, Hkv, hd] into randomly chosen pages; returns pages and the table."""
+    T, Hkv, hd = k.shape
+    nb = (T + page_size - 1) // page_size
+    g = torch.Generator().manual_seed(seed)
+    table = torch.randperm(num_pages, generator=g)[:nb].to(torch.int32)
+    kp = torch.full((num_pages, Hkv, page_size, hd), float("nan"), dtype=dtype)
+    vp = torch.full((num_pages, Hkv, page_size, hd), float("nan"), dtype=dtype)
+    for t in range(T):
+        kp[table[t // page_size], :, t % page_size] = k[t].to(dtype)
+        vp[table[t // page_size], :, t % page_size] = v[t].to(dtype)
+    return kp.to(DEV), vp.to(DEV), table
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Hq,Hkv,hd,ps,window,sinks", [(4, 2, 16, 4, None, False), (6, 2, 48, 16, 21, True),
+                                                        (5, 5, 80, 8, None, True), (16, 2, 128, 16, 100, False),
+                                                        (3, 1, 256, 32, None, False)])
+def test_attention_generic(dtype, Hq, Hkv, hd, ps, window, sinks):
+    from quench6k_b200 import ops
+    T = 150
+    g = torch.Generator().manual_seed(Hq * 100 + hd)
+    q, k, v = (torch.randn(T, h, hd, generator=g) for h in (Hq, Hkv, Hkv))
+    # one far key must stand out among hundreds: scale one early key and the queries toward it
+    k[3] *= 4.0
+    q[-5:] += 2.0 * k[3].repeat_interleave(Hq // Hkv, 0) / k[3].norm()
+    sk = torch.randn(Hq, generator=g) if sinks else None
+    qd, kd, vd = (x.to(dtype) for x in (q, k, v))
+    ref = P.attention(qd.double(), kd.double(), vd.double(), window, sk.double() if sinks else None, dtype == torch.bfloat16)
+    kp, vp, table = _paged(kd, vd, ps, 64, dtype, seed=1)
+    # two "requests" share the launch: rows 0..T-1 of request 1 (table row 1); row 0 of the table is a decoy
+    bt = torch.stack([torch.flip(table, [0]), table]).to(DEV)
+    rot = torch.ones(T, dtype=torch.int32, device=DEV)
+    pos = torch.arange(T, dtype=torch.int32, device=DEV)
+    out = ops.attention_generic(qd.to(DEV), kp, vp, bt, rot, pos, window, sk.to(DEV) if sinks else None)
+    tol = 2e-5 if dtype == torch.float32 else 1.5e-2
+    err = (out.double().cpu().view(T, Hq, hd) - ref).abs().max() / ref.abs().max()
+    assert err <= tol, err
+    # a subset of rows (decode-like: only the last position) gives the same values
+    last = ops.attention_generic(qd[-1:].contiguous().to(DEV), kp, vp, bt, rot[-1:].contiguous(), pos[-1:].contiguous(), window,
+                                 sk.to(DEV) if sinks else None)
+    assert torch.equal(last[0], out[-1])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("Hq,Hkv,hd,ps,norm,theta", [(4, 2, 16, 4, False, 10000.0), (6, 3, 48, 8, True, 500000.0),
+                                                      (2, 1, 128, 16, True, None)])
+def test_qk_prep(dtype, Hq, Hkv, hd, ps, norm, theta):
+    from quench6k_b200 import ops
+    T, eps = 21, 1e-5
+    qkv = _t(T, (Hq + 2 * Hkv) * hd, seed=5)
+    qn, kn = (_t(hd, seed=6) + 1.0, _t(hd, seed=7) + 1.0) if norm else (None, None)
+    pos0 = 37
+    pos = torch.arange(pos0, pos0 + T, dtype=torch.int32, device=DEV)
+    rot = torch.zeros(T, dtype=torch.int32, device=DEV)
+    nb = (pos0 + T + ps - 1) // ps
+    table = torch.randperm(40)[:nb].to(torch.int32).view(1, nb).to(DEV)
+    kp = torch.zeros(40, Hkv, ps, hd, dtype=dtype, device=DEV)
+    vp = torch.zeros_like(kp)
+    q = ops.qk_prep(qkv, Hq, Hkv, hd, qn, kn, eps, theta, pos, rot, table, ps, kp, vp, dtype)
+    x = qkv.double().cpu()
+    rq = x[:, :Hq * hd].view(T, Hq, hd)
+    rk = x[:, Hq * hd:(Hq + Hkv) * hd].view(T, Hkv, hd)
+    rv = x[:, (Hq + Hkv) * hd:].view(T, Hkv, hd)
+    if norm:
+        rq, rk = P.rmsnorm(rq, qn.double().cpu(), eps), P.rmsnorm(rk, kn.double().cpu(), eps)
+    if theta is not None:
+        rq, rk = P.rope_neox(rq, pos.cpu(), theta), P.rope_neox(rk, pos.cpu(), theta)
+    tol = 2e-5 if dtype == torch.float32 else 1e-2
+    assert (q.double().cpu() - rq).abs().max() <= tol * rq.abs().max()
+    for t in range(T):
+        p = pos0 + t
+        page = int(table[0, p // ps])
+        assert (kp[page, :, p % ps].double().cpu() - rk[t]).abs().max() <= tol * rk.abs().max()
+        assert (vp[page, :, p % ps].double().cpu() - rv[t]).abs().max() <= tol * rv.abs().max()
+    # read-only layers produce the same q and leave the pages alone
+    k0 = kp.clone()
+    q2 = ops.qk_prep(qkv[:, :Hq * hd].contiguous(), Hq, Hkv, hd, qn, kn, eps, theta, pos, rot, None, ps, None, None, dtype)
+    assert torch.equal(q2, q) and torch.equal(kp, k0)
+
+
+@pytest.mark.parametrize("rows,V", [(1, 10), (5, 384), (3, 151936), (2, 70001)])
+def test_argmax_and_topk_pool(rows, V):
+    from quench6k_b200 import ops
+    x = _t(rows, V, scale=3.0, seed=V)
+    x = (x * 8).round() / 8                                              # many ties
+    am = ops.argmax(x).cpu().tolist()
+    for r in range(rows):
+        row = x[r].cpu()
+        assert am[r] == int((row == row.max()).nonzero()[0])
+    for k in (1, 5, 64, 256):
+        if k > V:
+            continue
+        ids, vals = ops.topk_pool(x, k)
+        for r in range(rows):
+            row = x[r].cpu().tolist()
+            want = sorted(range(V), key=lambda i: (-row[i], i))[:k]
+            assert ids[r].cpu().tolist() == want
+            assert vals[r].cpu().tolist() == [row[i] for i in want]
+
+
+def test_kernels_refuse_what_they_cannot_do():
+    from quench6k_b200 import ops
+    q = torch.zeros(1, 2, 24, device=DEV)
+    pages = torch.zeros(2, 1, 4, 24, device=DEV)
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(ops.KernelError, match="multiple of 16"):
+        ops.attention_generic(q, pages, pages, z.view(1, 1), z, z, None, None)
+    with pytest.raises(ops.KernelError, match="outside"):
+        ops.topk_pool(torch.zeros(1, 1000, device=DEV), 300)
+    with pytest.raises(ops.KernelError, match="CUDA device"):
+        ops.argmax(torch.zeros(2, 5))
+    with pytest.raises(ops.KernelError, match="dtype"):
+        ops.embed(torch.zeros(2, dtype=torch.int64, device=DEV), torch.zeros(4, 4, device=DEV))

@@ -1,0 +1,200 @@
+"""Each part of a layer alone, built through its registry with sizes of its own, against the plain
+implementation's function for that part; and a toy mixer with state of its own, defined here,
+registered, built and stepped without touching the framework's files."""
+import math
+
+import pytest
+import torch
+
+import helpers
+import plain_flint as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _bind(part, rt, seed=0, std=0.5):
+    from quench6k_b200.weights import make_tensor
+    store = {t.name: make_tensor(t, seed, std) for t in part.tensors()}
+    part.bind(lambda n: store[n], rt)
+    return store
+
+
+def _rt(dtype):
+    from quench6k_b200.parts import Runtime
+    return Runtime(torch.device(DEV), dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_part(dtype):
+    from quench6k_b200.parts import NORMS, make_part
+    from quench6k_b200.spec import PartSpec
+    n = make_part(NORMS, "norm", PartSpec("rmsnorm", {"eps": 1e-4, "init": "random"}), size=88)
+    store = _bind(n, _rt(dtype))
+    h = torch.randn(9, 88, device=DEV) * 2
+    out = n.forward(h)
+    ref = P.rmsnorm(h.double().cpu(), store["weight"].double(), 1e-4)
+    assert out.dtype == dtype
+    assert (out.double().cpu() - ref).abs().max() <= (1e-5 if dtype == torch.float32 else 1e-2) * ref.abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shared", [0, 40])
+def test_feed_forward_parts(dtype, shared):
+    from quench6k_b200.parts import FEED_FORWARDS, make_part
+    from quench6k_b200.spec import PartSpec
+    D, T = 56, 23
+    em = dtype == torch.bfloat16
+    tol = 1e-4 if dtype == torch.float32 else 3e-2
+    x = (torch.randn(T, D) * 0.7).to(dtype)
+    dense = make_part(FEED_FORWARDS, "feed-forward", PartSpec("dense", {"intermediate_size": 72}), hidden_size=D)
+    st = _bind(dense, _rt(dtype), std=0.2)
+    out = torch.zeros(T, D, device=DEV)
+    dense.forward(x.to(DEV), None, out)
+    ref = P.swiglu_mlp(x.double(), st["gate_proj.weight"].double(), st["up_proj.weight"].double(), st["down_proj.weight"].double(), em)
+    assert (out.double().cpu() - ref).abs().max() <= tol * ref.abs().max()
+    moe = make_part(FEED_FORWARDS, "feed-forward", PartSpec("moe", {"num_experts": 12, "top_k": 5, "intermediate_size": 24,
+                    "scoring": "sigmoid", "renormalize": True, "shared_intermediate_size": shared}), hidden_size=D)
+    st = _bind(moe, _rt(dtype), seed=2, std=0.2)
+    out = torch.full((T, D), 0.25, device=DEV)                      # the part adds into the stream
+    moe.forward(x.to(DEV), None, out)
+    ref = P.moe(x.double(), st["gate.weight"].double(), st["experts.gate_proj.weight"].double(),
+                st["experts.up_proj.weight"].double(), st["experts.down_proj.weight"].double(), "sigmoid", 5, True, em)
+    if shared:
+        ref = ref + P.swiglu_mlp(x.double(), st["shared_experts.gate_proj.weight"].double(),
+                                 st["shared_experts.up_proj.weight"].double(), st["shared_experts.down_proj.weight"].double(), em)
+    assert ((out.double().cpu() - 0.25) - ref).abs().max() <= tol * ref.abs().max()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window,sinks,qk_norm,rope", [(None, False, False, True), (7, True, True, True), (None, True, True, False)])
+def test_attention_part_over_pages(dtype, window, sinks, qk_norm, rope):
+    """Two requests in one step, one of them continuing from a cache an earlier step left."""
+    from quench6k_b200.parts import MIXERS, LayerCache, make_part
+    from quench6k_b200.spec import PartSpec
+    D, Hq, Hkv, hd, ps = 40, 6, 2, 32, 4
+    em = dtype == torch.bfloat16
+    pos = PartSpec("rope", {"head_dim": hd, "theta": 3000.0}) if rope else PartSpec("none", {"head_dim": hd})
+    att = make_part(MIXERS, "mixer", PartSpec("attention", {"num_heads": Hq, "num_kv_heads": Hkv, "head_dim": hd, "eps": 1e-5,
+                    "pos": pos, "window": window, "sinks": sinks, "qk_norm": qk_norm, "norm_init": "random"}), hidden_size=D)
+    st = _bind(att, _rt(dtype), seed=4, std=0.3)
+    req = att.cache_request()
+    assert (req.kind, req.window, req.kv_heads, req.head_dim) == ("sliding" if window else "full", window, Hkv, hd)
+    lens = [19, 11]
+    xs = [(torch.randn(n, D) * 0.8).to(dtype) for n in lens]
+    cache = LayerCache(0, torch.zeros(16, Hkv, ps, hd, dtype=dtype, device=DEV), torch.zeros(16, Hkv, ps, hd, dtype=dtype, device=DEV), ps)
+    tables = [[[9, 2, 14, 5, 0], [7, 3, 11]]]
+    # step 1: the first 13 tokens of request 0; step 2: its last 6 beside all of request 1
+    out1 = torch.zeros(13, D, device=DEV)
+    att.forward(xs[0][:13].to(DEV), helpers.make_context([13], [0], [[tables[0][0]]]), cache, None, out1)
+    out2 = torch.zeros(6 + 11, D, device=DEV)
+    att.forward(torch.cat([xs[0][13:], xs[1]]).to(DEV), helpers.make_context([6, 11], [13, 0], tables), cache, None, out2)
+    got = [torch.cat([out1, out2[:6]]).double().cpu(), out2[6:].double().cpu()]
+    for r, n in enumerate(lens):
+        x = xs[r].double()
+        q = (x @ st["q_proj.weight"].double().T).view(n, Hq, hd)
+        k = (x @ st["k_proj.weight"].double().T).view(n, Hkv, hd)
+        v = (x @ st["v_proj.weight"].double().T).view(n, Hkv, hd)
+        if qk_norm:
+            q, k = P.rmsnorm(q, st["q_norm.weight"].double(), 1e-5), P.rmsnorm(k, st["k_norm.weight"].double(), 1e-5)
+        if rope:
+            q, k = P.rope_neox(q, torch.arange(n), 3000.0), P.rope_neox(k, torch.arange(n), 3000.0)
+        q, k, v = P._r(q, em), P._r(k, em), P._r(v, em)
+        a = P._r(P.attention(q, k, v, window, st["sinks"].double() if sinks else None, em), em).reshape(n, Hq * hd)
+        ref = a @ st["o_proj.weight"].double().T
+        err = (got[r] - ref).abs().max() / ref.abs().max()
+        assert err <= (1e-4 if dtype == torch.float32 else 3e-2), (r, err)
+
+
+def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
+    """A mixer that keeps a running mean of its inputs per request (fixed-size state, no keys),
+    and an architecture that alternates it with attention, are defined here and run through the
+    unchanged framework: registry, weights, cache manager (state slots), step function."""
+    from dataclasses import dataclass
+    from quench6k_b200.config import register_architecture
+    from quench6k_b200.engine import ModelRunner, StepEntry
+    from quench6k_b200.parts import Mixer, register_mixer
+    from quench6k_b200.spec import LayerSpec, ModelSpec, PartSpec, TensorSpec
+
+    @register_mixer("toy_running_mean")
+    class RunningMean(Mixer):
+        """y_t = w * mean(x_0..x_t); the state is (sum [D], count [1]) per request."""
+        def __init__(self, hidden_size):
+            self.D = hidden_size
+
+        def tensors(self):
+            return [TensorSpec("w", (self.D,), "f32", ("ones_plus", 0.5))]
+
+        def bind(self, get, rt):
+            self.rt = rt
+            self.w = get("w").to(rt.device, torch.float32)
+
+        def state_shape(self):
+            return (self.D + 1,)
+
+        def forward(self, xn, ctx, cache, state, out):
+            assert cache is None
+            x = xn.float()
+            at = 0
+            for r, n in enumerate(ctx.q_lens):
+                s = state[ctx.slots[r]]
+                cs = torch.cumsum(x[at:at + n], 0) + s[:self.D]
+                cnt = s[self.D] + torch.arange(1, n + 1, device=x.device, dtype=torch.float32)
+                out[at:at + n] += self.w * cs / cnt[:, None]
+                s[:self.D] = cs[-1]
+                s[self.D] = cnt[-1]
+                at += n
+
+    @dataclass
+    class ToyConfig:
+        hidden_size: int
+        vocab_size: int
+        architectures: list
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d["hidden_size"], d["vocab_size"], d["architectures"])
+
+        def to_dict(self):
+            return dict(self.__dict__)
+
+        def save(self, folder):
+            import json, os
+            with open(os.path.join(folder, "config.json"), "w") as f:
+                json.dump(self.to_dict(), f)
+
+    def build(cfg):
+        norm = PartSpec("rmsnorm", {"eps": 1e-5, "init": "random"})
+        ffn = PartSpec("dense", {"intermediate_size": 24})
+        attn = PartSpec("attention", {"num_heads": 2, "num_kv_heads": 1, "head_dim": 16, "eps": 1e-5,
+                                      "pos": PartSpec("rope", {"head_dim": 16, "theta": 1000.0})})
+        layers = [LayerSpec("model.layers.0.", PartSpec("toy_running_mean", {}), ffn, norm),
+                  LayerSpec("model.layers.1.", attn, ffn, norm)]
+        return ModelSpec(cfg.hidden_size, cfg.vocab_size, layers, order=[0, 1, 0], kv_source=[None, None, None], final_norm=norm)
+
+    register_architecture("ToyRunningMeanLM", ToyConfig, build)
+    cfg = ToyConfig(32, 50, ["ToyRunningMeanLM"])
+    runner = ModelRunner.from_random(cfg, seed=1, dtype="float32", page_size=4, num_pages=12, max_requests=3)
+    assert [s is not None for s in runner.states] == [True, False, True]          # layer 0 runs twice: two states
+    assert [c is not None for c in runner.caches] == [False, True, False]
+    toks = {"a": helpers.random_tokens(21, 50, 1), "b": helpers.random_tokens(17, 50, 2)}
+    # whole
+    whole = {}
+    for rid, t in toks.items():
+        runner.add_request(rid)
+        whole[rid] = runner.step([StepEntry(rid, t, list(range(len(t))))]).cpu()
+        runner.end_request(rid)
+    # cut and mixed; slots are reused, so stale state would show
+    runner.add_request("a"), runner.add_request("b")
+    got = {"a": [], "b": []}
+    o = runner.step([StepEntry("a", toks["a"][:9], list(range(9)))])
+    got["a"].append(o.cpu())
+    o = runner.step([StepEntry("a", toks["a"][9:10], [0]), StepEntry("b", toks["b"][:12], list(range(12)))]).cpu()
+    got["a"].append(o[:1]), got["b"].append(o[1:])
+    o = runner.step([StepEntry("b", toks["b"][12:], list(range(5))), StepEntry("a", toks["a"][10:], list(range(11)))]).cpu()
+    got["b"].append(o[:5]), got["a"].append(o[5:])
+    for rid in toks:
+        g = torch.cat(got[rid])
+        assert (g - whole[rid]).abs().max() <= 1e-5 * whole[rid].abs().max()
+    runner.end_request("a"), runner.end_request("b")
+    runner.manager.check()

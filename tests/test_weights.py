@@ -1,0 +1,90 @@
+import os
+
+import pytest
+import torch
+
+import helpers
+import tiny_configs
+from quench6k_b200.config import FlintConfig
+from quench6k_b200.models.decoder import DecoderModel
+from quench6k_b200.models.flint import build_spec
+from quench6k_b200.spec import TensorSpec
+from quench6k_b200.weights import (SafetensorsError, WeightError, index_folder, load_folder, make_tensor,
+                                   standard_normal, write_safetensors)
+
+
+def _decl(name="A"):
+    return DecoderModel(build_spec(FlintConfig.from_dict(tiny_configs.get(name)))).tensors()
+
+
+def test_random_folder_loads_back(tmp_path):
+    cfg_d, weights = helpers.make_model_folder(str(tmp_path), "B", seed=3)
+    decl = _decl("B")
+    get = load_folder(str(tmp_path), decl)
+    for spec in decl:
+        t = get(spec.name)
+        assert tuple(t.shape) == tuple(spec.shape)
+        assert t.dtype == (torch.float32 if spec.role == "f32" else torch.bfloat16)
+    assert os.path.exists(tmp_path / "config.json") and os.path.exists(tmp_path / "model.safetensors")
+
+
+def test_seed_and_name_decide_the_values():
+    s = TensorSpec("x.weight", (7, 5))
+    a, b = make_tensor(s, 1, 0.02), make_tensor(s, 1, 0.02)
+    assert torch.equal(a, b)
+    assert not torch.equal(a, make_tensor(s, 2, 0.02))
+    assert not torch.equal(a, make_tensor(TensorSpec("y.weight", (7, 5)), 1, 0.02))
+    z = standard_normal(5, "n", 0, 200000, "cpu")
+    assert abs(z.mean().item()) < 0.01 and abs(z.std().item() - 1.0) < 0.01
+    # pieces of a tensor equal the whole
+    assert torch.equal(standard_normal(5, "n", 1000, 50, "cpu"), z[1000:1050])
+    ones = make_tensor(TensorSpec("n.weight", (9,), "f32", ("ones",)), 0, 0.02)
+    assert ones.dtype == torch.float32 and torch.all(ones == 1)
+
+
+def test_one_error_lists_missing_unexpected_and_wrong(tmp_path):
+    cfg_d, weights = helpers.make_model_folder(str(tmp_path), "A", seed=0)
+    bad = dict(weights)
+    del bad["model.norm.weight"]
+    del bad["model.layers.1.self_attn.o_proj.weight"]
+    bad["model.layers.0.extra.bias"] = torch.zeros(3)
+    bad["lm_head.weight"] = torch.zeros(10, 64, dtype=torch.bfloat16)
+    bad["model.layers.0.mlp.gate.weight"] = torch.zeros(8, 64, dtype=torch.int32)
+    write_safetensors(str(tmp_path / "model.safetensors"), bad.items())
+    with pytest.raises(WeightError) as e:
+        load_folder(str(tmp_path), _decl("A"))
+    msg = str(e.value)
+    assert "model.norm.weight" in msg and "model.layers.1.self_attn.o_proj.weight" in msg
+    assert "model.layers.0.extra.bias" in msg
+    assert "lm_head.weight: shape [10, 64], expected [256, 64]" in msg
+    assert "model.layers.0.mlp.gate.weight: dtype" in msg
+    assert e.value.missing == ["model.layers.1.self_attn.o_proj.weight", "model.norm.weight"]
+    assert e.value.unexpected == ["model.layers.0.extra.bias"]
+    assert len(e.value.wrong) == 2
+
+
+def test_stored_dtypes_are_kept(tmp_path):
+    write_safetensors(str(tmp_path / "model.safetensors"), [
+        ("a", torch.randn(3, 4).to(torch.bfloat16)), ("b", torch.randn(5)), ("c", torch.arange(6, dtype=torch.int64)),
+        ("d", torch.randn(2, 2).to(torch.float16))])
+    decl = [TensorSpec("a", (3, 4)), TensorSpec("b", (5,), "f32"), TensorSpec("c", (6,), "i32"), TensorSpec("d", (2, 2))]
+    get = load_folder(str(tmp_path), decl)
+    assert get("a").dtype == torch.bfloat16 and get("b").dtype == torch.float32
+    assert get("c").dtype == torch.int32 and get("c").tolist() == list(range(6))
+    assert get("d").dtype == torch.bfloat16
+
+
+def test_broken_files(tmp_path):
+    with pytest.raises(SafetensorsError, match="no .safetensors"):
+        index_folder(str(tmp_path))
+    p = tmp_path / "model.safetensors"
+    p.write_bytes(b"\x10\x00\x00")
+    with pytest.raises(SafetensorsError, match="shorter"):
+        index_folder(str(tmp_path))
+    p.write_bytes((1 << 40).to_bytes(8, "little") + b"{}")
+    with pytest.raises(SafetensorsError, match="header length"):
+        index_folder(str(tmp_path))
+    write_safetensors(str(p), [("a", torch.zeros(4))])
+    write_safetensors(str(tmp_path / "other.safetensors"), [("a", torch.zeros(4))])
+    with pytest.raises(SafetensorsError, match="duplicate tensor a"):
+        index_folder(str(tmp_path))

@@ -8,9 +8,11 @@
 
 namespace {
 
-// Ascending-order-preserving key of a float; NaN sorts lowest.
+// Ascending-order-preserving key of a float; NaN sorts lowest; -0 and +0 are the same key, as
+// they compare equal.
 __device__ __forceinline__ unsigned key_of(float v) {
     if (v != v) return 0u;
+    if (v == 0.0f) v = 0.0f;
     const unsigned u = __float_as_uint(v);
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }

@@ -85,6 +85,9 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: Optiona
     return out
 
 
+_last_route_margin = None      # set by route(): per token, (k-th logit - (k+1)-th logit) / rms of the token's router logits
+
+
 def route(logits: torch.Tensor, scoring: str, top_k: int, renorm: bool):
     """Router scores, the top-k experts (ties -> lower expert index) and their weights.
     sigmoid: score = 1/(1+exp(-z)), weights = score / (sum of chosen + 1e-20)
@@ -96,8 +99,16 @@ def route(logits: torch.Tensor, scoring: str, top_k: int, renorm: bool):
         score = torch.softmax(logits, dim=-1)
     else:
         raise ValueError(scoring)
-    order = torch.sort(score, dim=-1, descending=True, stable=True).indices[:, :top_k]
+    ranked = torch.sort(score, dim=-1, descending=True, stable=True)
+    order = ranked.indices[:, :top_k]
     w = torch.gather(score, 1, order)
+    global _last_route_margin
+    if score.shape[-1] > top_k:
+        # both scorings are monotone in the logit, so the choice is the order of the logits
+        z = torch.sort(logits, dim=-1, descending=True).values
+        _last_route_margin = (z[:, top_k - 1] - z[:, top_k]) / logits.pow(2).mean(dim=-1).sqrt()
+    else:
+        _last_route_margin = torch.full((score.shape[0],), float("inf"), dtype=score.dtype)
     if renorm:
         s = w.sum(dim=-1, keepdim=True)
         w = w / (s + 1e-20) if scoring == "sigmoid" else w / s
@@ -133,8 +144,11 @@ def moe(x: torch.Tensor, router_w: torch.Tensor, wg: torch.Tensor, wu: torch.Ten
 
 # --------------------------------------------------------------------------- whole model
 def forward(cfg: Dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtype=torch.float64,
-            emulate_bf16: bool = False) -> torch.Tensor:
-    """Logits [T, V] of one whole sequence; the layer loop of crates/engine/src/flint.rs:775-1117
+            emulate_bf16: bool = False, return_margins: bool = False):
+    """Logits [T, V] of one whole sequence (with return_margins also, per position, the smallest
+    gap over the MoE layers between the last chosen and the first rejected router logit, relative to
+    the rms of the token's router logits:
+    where it is tiny, rounding may legitimately choose another expert); the layer loop of crates/engine/src/flint.rs:775-1117
     (embed, per layer: norm, q/k/v, qk-norm, RoPE, attention, o-proj + residual, norm, router +
     experts (+ shared expert) or dense MLP + residual; final norm and LM head)."""
     W = {k: v.to(dtype) for k, v in weights.items()}
@@ -150,6 +164,7 @@ def forward(cfg: Dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtyp
     pos = torch.arange(T)
     h = embed(torch.tensor(tokens), W["model.embed_tokens.weight"])
     kept = {}
+    margins = torch.full((T,), float("inf"), dtype=dtype)
     for p, i in enumerate(order):
         pre = f"model.layers.{i}."
         xn = _r(rmsnorm(h, W[pre + "input_layernorm.weight"], eps), em)
@@ -184,6 +199,7 @@ def forward(cfg: Dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtyp
                     W[pre + "mlp.experts.up_proj.weight"], W[pre + "mlp.experts.down_proj.weight"],
                     cfg.get("scoring_func", "softmax"), cfg["num_experts_per_tok"],
                     cfg.get("norm_topk_prob", True), em)
+            margins = torch.minimum(margins, _last_route_margin)
             if cfg.get("n_shared_experts", 0) > 0:
                 f = f + swiglu_mlp(xn, W[pre + "mlp.shared_experts.gate_proj.weight"],
                                    W[pre + "mlp.shared_experts.up_proj.weight"],
@@ -191,7 +207,8 @@ def forward(cfg: Dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtyp
         h = h + f
     xn = _r(rmsnorm(h, W["model.norm.weight"], eps), em)
     head = W["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings") else W["lm_head.weight"]
-    return xn @ head.T
+    logits = xn @ head.T
+    return (logits, margins) if return_margins else logits
 
 
 # --------------------------------------------------------------------------- sampling

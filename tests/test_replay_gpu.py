@@ -13,7 +13,8 @@ import helpers
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [71, 130, 45, 96, 64, 33], "B": [85, 140, 37, 101, 66, 50], "C": [90, 57, 129, 48, 75, 40]}
+LENGTHS = {"A": [71, 130, 45, 96, 64, 33, 120, 58, 77], "B": [85, 140, 37, 101, 66, 50, 90, 125, 44],
+           "C": [90, 57, 129, 48, 75, 40, 110, 66, 83]}
 
 
 @pytest.fixture(scope="module", params=["A", "B", "C"])
@@ -33,8 +34,10 @@ def _check(model, dtype, steps, max_tokens, what):
     got = helpers.collect(model["requests"], steps, outputs)
     ref = model["ref"][dtype == "bfloat16"]
     worst = 0.0
+    reach = max(8, model["cfg"].get("sliding_window") or 0)
     for rid in model["requests"]:
-        worst = max(worst, helpers.assert_close(got[rid], ref[rid], dtype, f"{model['name']} {dtype} {what} {rid}"))
+        worst = max(worst, helpers.assert_close(got[rid], ref[rid], dtype, f"{model['name']} {dtype} {what} {rid}", reach))
+    print(f"{model['name']} {dtype} {what}: worst error {worst:.3e}")
     return got, worst
 
 
@@ -101,7 +104,7 @@ def test_first_tokens_and_long_decoding(model):
                           "end": ["x"] if i == len(toks) - 1 else []})
         outputs, _ = helpers.run_replay(folder, dtype, steps, len(toks))
         got = helpers.collect({"x": toks}, steps, outputs)["x"]
-        helpers.assert_close(got, ref, dtype, f"{model['name']} {dtype} long decoding")
+        helpers.assert_close(got, ref, dtype, f"{model['name']} {dtype} long decoding", max(8, cfg.get("sliding_window") or 0))
 
 
 def test_trace_run_program(model, tmp_path):

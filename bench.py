@@ -1,0 +1,292 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200, with roofline fractions.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+The default run has the layer sizes of the half-depth Flint configuration (24 layers, hidden 2048,
+32 query / 4 KV heads of 128, 256 experts of width 512, top-8, vocabulary 151,936) with random
+weights, a batch of 8 requests that each hold 32,768 cached tokens, bfloat16.  One JSON line:
+`value` is decoded tokens a second timed on the device (CUDA events around K decode steps of
+ModelRunner.step plus the device argmax); `e2e` is the same through Engine.step() with host token
+ids in (pinned host memory -> device) and sampled ids out (device -> host) every step; `prefill`
+is one 2,048-token prompt in one step; `points` are decode at batch 1 and 64; `roofline` is the
+decode step's bytes (every weight it uses once, and the cache of the live requests) over its time
+over the peak copy bandwidth.  Peaks come from MEASURED_PEAKS.json beside this file when the
+measuring harness wrote it, else from the fallback figures below.
+
+The caches are filled with random values instead of by a prefill (the weights are random too), so
+every request stands at the context length at once; what the decode step reads and computes is the
+same.  Inputs are larger than L2: one decode step streams gigabytes of weights and cache.
+"""
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+CONFIG2 = {
+    "architectures": ["FlintForCausalLM"], "hidden_size": 2048, "num_hidden_layers": 24, "num_attention_heads": 32,
+    "num_key_value_heads": 4, "head_dim": 128, "vocab_size": 151936, "n_routed_experts": 256, "num_experts_per_tok": 8,
+    "moe_intermediate_size": 512, "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "kv_page_size": 16,
+}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            out = dict(FALLBACK_PEAKS)
+            out.update({k: float(v) for k, v in d.items() if k in out and isinstance(v, (int, float))})
+            out["source"] = "measured"
+            return out
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while a timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.lines, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])), mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def expected_experts(E, k, B):
+    return E * (1.0 - (1.0 - k / E) ** B)
+
+
+def decode_bytes(cfg, layers, B, ctx):
+    """Bytes one decode step has to read: every weight it uses once, and the cache of the live requests."""
+    D, Hq, Hkv, hd = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    E, k, I, V = cfg["n_routed_experts"], cfg["num_experts_per_tok"], cfg["moe_intermediate_size"], cfg["vocab_size"]
+    attn = ((Hq + 2 * Hkv) * hd * D + D * Hq * hd) * 2
+    router = E * D * 2
+    experts = expected_experts(E, k, B) * 3 * I * D * 2
+    weights = layers * (attn + router + experts) + V * D * 2
+    kv = B * ctx * layers * 2 * Hkv * hd * 2
+    return weights + kv, weights, kv
+
+
+def prefill_flops(cfg, layers, T):
+    D, Hq, Hkv, hd = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    E, k, I, V = cfg["n_routed_experts"], cfg["num_experts_per_tok"], cfg["moe_intermediate_size"], cfg["vocab_size"]
+    per_token = (Hq + 2 * Hkv) * hd * D + D * Hq * hd + E * D + k * 3 * I * D
+    matmul = 2.0 * T * layers * per_token + 2.0 * V * D
+    attention = layers * 4.0 * Hq * hd * T * (T / 2.0)
+    return matmul + attention
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=16)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (both numbers are reported)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--context", type=int, default=32768)
+    ap.add_argument("--prefill-tokens", type=int, default=2048)
+    ap.add_argument("--points", default="1,64", help="further decode batch sizes, comma separated ('' for none)")
+    ap.add_argument("--dtype", default="bfloat16")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable": "lkarlslund/quench6k is a Rust workspace (Cargo.toml, no setup.py or "
+                          "pyproject.toml): pip cannot install it offline, cargo/rustc are absent, and its kernels are sm_120a-only"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+    from quench6k_b200 import Engine, SamplingParams, ops
+    from quench6k_b200.config import FlintConfig
+    from quench6k_b200.engine import StepEntry
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device"
+    torch.cuda.set_device(0)
+    pk = peaks()
+    cfg_d = dict(CONFIG2)
+    full_layers = cfg_d["num_hidden_layers"]
+    layers = args.layers or full_layers
+    cfg_d["num_hidden_layers"] = layers
+    cfg = FlintConfig.from_dict(cfg_d)
+    page = cfg.kv_page_size
+    point_batches = [int(x) for x in args.points.split(",") if x.strip()]
+    max_b = max([args.batch] + point_batches)
+    ctx = args.context
+    pages_per_req = (ctx + 64 + page - 1) // page + 1
+    num_pages = max(max_b * pages_per_req, (args.prefill_tokens + page - 1) // page + 1)
+    t0 = time.time()
+    eng = Engine.from_random(cfg, seed=0, dtype=args.dtype, page_size=page, num_pages=num_pages, max_requests=max_b,
+                             max_batch_tokens=max(args.prefill_tokens, max_b))
+    runner = eng.runner
+    for c in runner.caches:                      # stand-in for the keys and values a prefill would have left
+        c.k.normal_(0.0, 0.5)
+        c.v.normal_(0.0, 0.5)
+    torch.cuda.synchronize()
+    print(f"[bench] model and cache ready in {time.time() - t0:.1f}s ({torch.cuda.memory_allocated() / 2**30:.1f} GiB on the device)",
+          file=sys.stderr, flush=True)
+    gen = torch.Generator().manual_seed(1)
+    V = cfg.vocab_size
+
+    def rand_ids(n):
+        return torch.randint(0, V, (n,), generator=gen).tolist()
+
+    def timed_decode(B, steps, warmup):
+        """Device-timed decode steps of B requests standing at `ctx` cached tokens."""
+        rids = [f"d{B}_{i}" for i in range(B)]
+        for r in rids:
+            runner.add_request(r)
+        for at in range(0, ctx, page):           # page by page, round robin: the requests' pages interleave in the pool
+            for r in rids:
+                runner.assume_cached(r, min(page, ctx - at))
+        toks = [rand_ids(steps + warmup) for _ in rids]
+
+        def one(i):
+            logits = runner.step([StepEntry(r, [toks[j][i]], [0]) for j, r in enumerate(rids)])
+            return ops.argmax(logits)
+
+        for i in range(warmup):
+            one(i)
+        torch.cuda.synchronize()
+        l0 = ops.launch_count
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(warmup, warmup + steps):
+            one(i)
+        b.record()
+        torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / steps
+        launches = ops.launch_count - l0
+        for r in rids:
+            runner.end_request(r)
+        return ms, launches
+
+    clocks = ClockSampler()
+    clocks.start()
+    ms, launches = timed_decode(args.batch, args.steps, args.warmup)
+    clock_info = clocks.stop()
+    value = args.batch * 1000.0 / ms
+    total_b, w_b, kv_b = decode_bytes(cfg_d, layers, args.batch, ctx)
+    achieved = total_b / (ms * 1e-3) / 1e9
+
+    points = {}
+    for B in point_batches:
+        pms, _ = timed_decode(B, max(4, args.steps // 2), 3)
+        points[f"decode_b{B}"] = round(B * 1000.0 / pms, 1)
+
+    # prefill: one prompt of T tokens in one step, the logits of its last token wanted
+    T = args.prefill_tokens
+    pre_ms = []
+    for it in range(3):
+        runner.add_request("p")
+        ids = rand_ids(T)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        runner.step([StepEntry("p", ids, [T - 1])])
+        b.record()
+        torch.cuda.synchronize()
+        pre_ms.append(a.elapsed_time(b))
+        runner.end_request("p")
+    pms = min(pre_ms[1:])
+    pf = prefill_flops(cfg_d, layers, T)
+    prefill = {"value": round(T * 1000.0 / pms, 1), "tokens": T, "ms": round(pms, 3),
+               "frac": round(pf / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # end to end: Engine.step() with host ids in and sampled ids out each step
+    sp = SamplingParams(max_tokens=args.steps + args.warmup + 8, temperature=0.0)
+    for i in range(args.batch):
+        eng.adopt_request(rand_ids(ctx), rand_ids(1)[0], sp)
+    for _ in range(args.warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    for _ in range(args.steps):
+        eng.step()
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t1
+    for r in list(eng.scheduler.running):
+        eng.abort(r.rid)
+    R = args.batch
+    h2d = 4 * (3 * R + (R + 1) + 2 * R + R + R * ((ctx + 64 + page - 1) // page))       # the step's int32 block, tables included
+    e2e = {"value": round(args.batch * args.steps / e2e_s, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d,
+           "d2h_bytes_per_step": 4 * R}
+
+    out = {
+        "metric": f"decode tok/s at batch {args.batch} (context {ctx}); prefill tok/s at {T} tokens; % of roofline",
+        "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16" if args.dtype in ("bfloat16", "bf16") else "fp32",
+        "data": "synthetic: seeded random weights N(0,0.02), uniform-random token ids, caches filled with random values",
+        "config": {"model": "Recursive Flint MoE, half-depth shape", "layers": layers, "layers_full": full_layers,
+                   "hidden": cfg.hidden_size, "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                   "head_dim": cfg.head_dim, "experts": cfg.n_routed_experts, "top_k": cfg.num_experts_per_tok,
+                   "expert_width": cfg.moe_intermediate_size, "vocab": cfg.vocab_size, "rope_theta": cfg.rope_theta,
+                   "page_size": page, "global_batch": args.batch, "seq_len": ctx, "prefill_tokens": T,
+                   "parallelism": "single-gpu", "l2": "inputs larger than L2 (weights and cache stream from HBM every step)",
+                   "kv_fill": "random values, no prefill", "peaks": pk["source"]},
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes": int(total_b), "weight_bytes": int(w_b), "kv_bytes": int(kv_b)},
+        "points": points, "e2e": e2e, "gpu_launches": launches, "clocks": clock_info, "impl": "ours",
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -71,6 +71,26 @@ class Engine:
         self.scheduler.add(req)
         return rid
 
+    def adopt_request(self, prompt: Sequence[int], first_token: int, params: Optional[SamplingParams] = None,
+                      rid: Optional[Hashable] = None) -> Hashable:
+        """Add a request whose prompt is taken to be in the cache already, with its first generated
+        token given: it decodes from its next step on.  Pages for the prompt are taken here; their
+        contents are the caller's business (benchmarks fill the pools with random values)."""
+        params = params or SamplingParams()
+        params.validate()
+        if rid is None:
+            rid = next(self._ids)
+        seed = params.seed if params.seed is not None else random.getrandbits(64)
+        req = Request(rid, [int(t) for t in prompt], params, output=[int(first_token)], rng=SplitMix64(seed))
+        self.runner.add_request(rid)
+        step = 1 << 16
+        for at in range(0, len(req.prompt), step):
+            self.runner.assume_cached(rid, min(step, len(req.prompt) - at))
+        req.num_computed = len(req.prompt)
+        self.scheduler.by_id[rid] = req
+        self.scheduler.running.append(req)
+        return rid
+
     def abort(self, rid: Hashable) -> None:
         self.scheduler.abort(rid)
 

@@ -110,6 +110,13 @@ class ModelRunner:
     def end_request(self, rid: Hashable) -> None:
         self.manager.remove(rid)
 
+    def assume_cached(self, rid: Hashable, n_tokens: int) -> None:
+        """Take pages for the request's next n_tokens positions and count them as computed without
+        running the model: the caller has put (or will put) keys and values into those pages.
+        Benchmarks use it to stand at a given context length without a prefill."""
+        self.manager.reserve(rid, n_tokens)
+        self.manager.commit(rid)
+
     def has_request(self, rid: Hashable) -> bool:
         return rid in self.manager.requests
 

@@ -48,7 +48,14 @@ def _need(t: torch.Tensor, name: str, dtype=None, shape=None):
         raise KernelError(f"{name} has shape {tuple(t.shape)}, expected {tuple(shape)}")
 
 
+# kernels launched per exported function (for launch accounting in benchmarks)
+_LAUNCHES = {"q6k_moe_permute": 3}
+launch_count = 0
+
+
 def _call(fn_name: str, *args):
+    global launch_count
+    launch_count += _LAUNCHES.get(fn_name, 1)
     lib = library()
     fn = getattr(lib, fn_name)
     fn.restype = ctypes.c_int

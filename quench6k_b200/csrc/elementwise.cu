@@ -51,7 +51,22 @@ __global__ void swiglu_kernel(const float* gu, T* act, int I, size_t count) {
     act[idx] = from_f32<T>(g / (1.0f + expf(-g)) * u);
 }
 
+// out[r, :] = x[idx[r], :] for rows of `bytes` bytes (a multiple of 16), 16 bytes per thread step.
+__global__ void gather_rows_kernel(const uint4* x, const int* idx, uint4* out, int vec_per_row) {
+    const size_t src = (size_t)idx[blockIdx.x] * vec_per_row, dst = (size_t)blockIdx.x * vec_per_row;
+    for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) out[dst + i] = x[src + i];
+}
+
 }  // namespace
+
+// Rows of any element type: row_bytes must be a multiple of 16 and both buffers 16-byte aligned.
+Q6K_API int q6k_gather_rows(const void* x, const int* idx, void* out, int rows, int row_bytes, cudaStream_t st) {
+    if (rows == 0) return 0;
+    Q6K_REQUIRE(rows > 0 && row_bytes > 0 && row_bytes % 16 == 0, "gather_rows: rows of %d bytes are not a multiple of 16", row_bytes);
+    Q6K_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0, "gather_rows: buffers must be 16-byte aligned");
+    gather_rows_kernel<<<rows, 128, 0, st>>>((const uint4*)x, idx, (uint4*)out, row_bytes / 16);
+    return q6k_check_launch("gather_rows");
+}
 
 Q6K_API int q6k_embed(const int* tokens, const void* table, float* h, int T_, int D, int V, int dtype, cudaStream_t st) {
     if (T_ == 0) return 0;

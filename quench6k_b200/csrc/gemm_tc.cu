@@ -1,0 +1,448 @@
+// bfloat16 matrix products on the 5th-generation tensor cores (tcgen05.mma, accumulators in tensor
+// memory), operands brought into shared memory by TMA.  sm_100a only.
+//
+//   out[r, n] (+)= sum_k A[r, k] * W_g[n, k]       A: [rows, K], W: [groups, N, K], K contiguous
+//
+// The reference runs every projection and every expert through one grouped kernel with mma.sync
+// tiles of 64 rows (crates/cuda/kernels/moe.cu:142-255) and single-token products through
+// CUDA-core GEMVs (crates/cuda/kernels/flint.cu:589-824).  Here one kernel serves both regimes by
+// swapping the operands: a tile of 128 WEIGHT rows is the M side of the MMA and the tokens are the
+// N side (16 to 256 of them), so a decode step of a few tokens still fills the tensor core's M
+// and simply streams the weights through a deep TMA pipeline, while a prefill tile reuses each
+// weight tile over up to 256 tokens.
+//
+// One CTA computes one [128 weights x BT tokens] tile (optionally one slice of K):
+//   warp 0     producer: waits for a free stage, arms its mbarrier with the byte count, issues the
+//              TMA loads of the weight tile(s) [128 x 64] and the token tile [BT x 64] (128-byte swizzle)
+//   warp 1     allocates tensor memory; one thread issues 4 tcgen05.mma (K = 16 each) per stage and
+//              commits the stage's "empty" barrier; after the last stage commits "accumulator full"
+//   warps 2-5  epilogue: tcgen05.ld of their 32 accumulator lanes (one lane = one weight row, one
+//              column = one token) and the store: plain, added into the FP32 stream, SwiGLU of two
+//              accumulators, or a split-K partial
+// Every wait on an mbarrier is bounded; a wait that runs out records a code in a status word that
+// q6k_tc_status() returns, the roles fall through to the common exit, and tensor memory is freed.
+#include <cuda.h>
+
+#include <map>
+#include <mutex>
+#include <tuple>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int BK = 64;                 // bf16 per k-block: one 128-byte swizzle row
+constexpr int WM = 128;                // weight rows per tile (UMMA M)
+constexpr int MAX_STAGES = 8;
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;     // about two seconds
+
+enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3 };
+
+__device__ int g_tc_status = 0;
+
+struct Params {
+    void* out;
+    float* partial;                    // split-K partials [splits, rows_total, N]
+    const int* tile_group;             // grouped: per row tile its group and first row
+    const int* tile_row0;
+    const int* group_offsets;
+    const int* num_tiles;
+    int rows_total, N, K, ldo;
+    int epilogue, stages, kb_per_split;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// Bounded wait for the phase of the given parity to complete.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    long long t0 = 0;
+    for (uint32_t spin = 0;; ++spin) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if ((spin & 255u) == 255u) {
+            const long long now = clock64();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > WAIT_LIMIT_CYCLES) return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) with the
+// 128-byte swizzle, 8-row groups 1024 bytes apart; version 1 (sm_100).
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+
+// Instruction descriptor: D FP32, A and B bfloat16, both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t umma_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(WM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}" ::"r"(tmem_d),
+        "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+__host__ __device__ constexpr int tmem_cols(int want) { return want <= 32 ? 32 : want <= 64 ? 64 : want <= 128 ? 128 : want <= 256 ? 256 : 512; }
+
+template <int BT, bool DUAL>
+__global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_w2,
+                                                       const __grid_constant__ CUtensorMap tm_a, const Params p) {
+    // which tile
+    int g = 0, row0 = blockIdx.y * BT, row_end = p.rows_total;
+    if (p.tile_group) {
+        if ((int)blockIdx.y >= *p.num_tiles) return;
+        g = p.tile_group[blockIdx.y];
+        row0 = p.tile_row0[blockIdx.y];
+        row_end = p.group_offsets[g + 1];
+    }
+    if (row0 >= row_end) return;
+    const int n0 = blockIdx.x * WM;
+    const int kb_total = (p.K + BK - 1) / BK;
+    const int kb0 = blockIdx.z * p.kb_per_split;
+    const int nkb = min(p.kb_per_split, kb_total - kb0);
+    if (nkb <= 0) return;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr uint32_t W_BYTES = WM * BK * 2, A_BYTES = BT * BK * 2;
+    constexpr uint32_t STAGE_BYTES = W_BYTES * (DUAL ? 2 : 1) + A_BYTES;
+    __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 1];
+    __shared__ uint32_t tmem_base_slot;
+    const int stages = p.stages;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[MAX_STAGES]), accum_bar = smem_u32(&bars[2 * MAX_STAGES]);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int COLS = tmem_cols(DUAL ? 2 * BT : BT);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(accum_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_a) : "memory");
+        if (DUAL) asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_w2) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const int wy = g * p.N + n0;
+            for (int i = 0; i < nkb; ++i) {
+                const int s = i % stages;
+                const uint32_t ph = (i / stages) & 1;
+                if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) {
+                    atomicExch(&g_tc_status, 1);
+                    break;
+                }
+                const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                const uint32_t fb = full0 + 8 * s;
+                mbar_expect_tx(fb, STAGE_BYTES);
+                const int kx = (kb0 + i) * BK;
+                tma_load_2d(st, &tm_w, kx, wy, fb);
+                if (DUAL) tma_load_2d(st + W_BYTES, &tm_w2, kx, wy, fb);
+                tma_load_2d(st + W_BYTES * (DUAL ? 2 : 1), &tm_a, kx, row0, fb);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc(BT);
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; ++i) {
+                const int s = i % stages;
+                const uint32_t ph = (i / stages) & 1;
+                if (!mbar_wait(full0 + 8 * s, ph)) {
+                    atomicExch(&g_tc_status, 2);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                const uint64_t dw = umma_desc_sw128(st), dw2 = umma_desc_sw128(st + W_BYTES);
+                const uint64_t da = umma_desc_sw128(st + W_BYTES * (DUAL ? 2 : 1));
+#pragma unroll
+                for (int k = 0; k < BK / 16; ++k) {
+                    const uint32_t acc = (i | k) != 0;
+                    umma_bf16(tmem_base, dw + 2 * k, da + 2 * k, idesc, acc);          // + 32 bytes of K per step
+                    if (DUAL) umma_bf16(tmem_base + BT, dw2 + 2 * k, da + 2 * k, idesc, acc);
+                }
+                umma_commit(empty0 + 8 * s);
+            }
+            umma_commit(accum_bar);          // arrives when every MMA issued so far has finished
+        }
+    } else {
+        // epilogue: this warp owns accumulator lanes 32*(warp%4) .. +31
+        const int quarter = warp & 3;
+        const int n_local = quarter * 32 + lane;
+        const int n = n0 + n_local;
+        const bool ok = mbar_wait(accum_bar, 0);
+        if (!ok && lane == 0) atomicExch(&g_tc_status, 3);
+        tc_fence_after();
+        if (ok) {
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+            const int valid = min(BT, row_end - row0);
+#pragma unroll 1
+            for (int c0 = 0; c0 < valid; c0 += 16) {
+                float v[16], u[16];
+                tmem_ld16(lane_addr + c0, v);
+                if (DUAL) tmem_ld16(lane_addr + BT + c0, u);
+                if (n < p.N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int t = c0 + j;
+                        if (t >= valid) break;
+                        const size_t row = (size_t)(row0 + t);
+                        if (p.epilogue == EPI_STORE) {
+                            ((float*)p.out)[row * p.ldo + n] = v[j];
+                        } else if (p.epilogue == EPI_ADD) {
+                            ((float*)p.out)[row * p.ldo + n] += v[j];
+                        } else if (p.epilogue == EPI_SWIGLU) {
+                            const float gte = v[j];
+                            ((__nv_bfloat16*)p.out)[row * p.ldo + n] = __float2bfloat16_rn(gte / (1.0f + expf(-gte)) * u[DUAL ? j : 0]);
+                        } else {
+                            p.partial[((size_t)blockIdx.z * p.rows_total + row) * p.N + n] = v[j];
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(COLS) : "memory");
+    }
+}
+
+// out[r, n] (=|+=) sum_s partial[s, r, n], s ascending.
+__global__ void splitk_reduce_kernel(const float* partial, int splits, size_t count, float* out, int N, int ldo, int add) {
+    const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
+    if (i >= count) return;
+    float acc = 0.0f;
+    for (int s = 0; s < splits; ++s) acc += partial[(size_t)s * count + i];
+    const size_t o = (i / N) * ldo + i % N;
+    out[o] = add ? out[o] + acc : acc;
+}
+
+// ---------------------------------------------------------------------------------------- host
+typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiled encode_fn() {
+    static EncodeTiled fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiled)p;
+    });
+    return fn;
+}
+
+// A [rows, K] bfloat16 matrix with a row pitch in elements, cut into boxes of [box_rows, 64].
+int make_map(CUtensorMap* map, const void* base, long long rows, int K, long long pitch, int box_rows, bool weights) {
+    EncodeTiled fn = encode_fn();
+    if (!fn) return q6k_fail("gemm_tc: the driver does not offer cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)pitch * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          weights ? CU_TENSOR_MAP_L2_PROMOTION_L2_256B : CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return q6k_fail("gemm_tc: cuTensorMapEncodeTiled failed with code %d (rows %lld, K %d, pitch %lld)", (int)r, rows, K, pitch);
+    return 0;
+}
+
+// Weight maps do not change between calls: keep them by (address, rows, K).
+std::mutex g_map_mutex;
+std::map<std::tuple<const void*, long long, int>, CUtensorMap> g_weight_maps;
+
+int weight_map(CUtensorMap* out, const void* base, long long rows, int K) {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    auto key = std::make_tuple(base, rows, K);
+    auto it = g_weight_maps.find(key);
+    if (it == g_weight_maps.end()) {
+        CUtensorMap m;
+        if (int rc = make_map(&m, base, rows, K, K, WM, true)) return rc;
+        it = g_weight_maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return 0;
+}
+
+template <int BT, bool DUAL>
+int launch(const CUtensorMap& tw, const CUtensorMap& tw2, const CUtensorMap& ta, Params p, dim3 grid, cudaStream_t st) {
+    constexpr int stage = WM * BK * 2 * (DUAL ? 2 : 1) + BT * BK * 2;
+    // two CTAs per SM when three stages fit in half of the shared memory, else one CTA with a deeper ring
+    int stages = (110 * 1024) / stage;
+    if (stages < 3) stages = (216 * 1024) / stage;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    p.stages = stages;
+    const size_t smem = (size_t)stages * stage + 1024;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_tc_kernel<BT, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024) != cudaSuccess)
+            return q6k_check_launch("gemm_tc: shared memory attribute");
+        configured = true;
+    }
+    gemm_tc_kernel<BT, DUAL><<<grid, 192, smem, st>>>(tw, tw2, ta, p);
+    return q6k_check_launch("gemm_tc");
+}
+
+}  // namespace
+
+Q6K_API int q6k_tc_status() {
+    int v = -1;
+    if (cudaMemcpyFromSymbol(&v, g_tc_status, sizeof v) != cudaSuccess) return -1;
+    return v;
+}
+
+Q6K_API int q6k_tc_token_tile(int rows, int dual) {
+    const int cap = dual ? 128 : 256;
+    for (int bt = 16; bt < cap; bt *= 2)
+        if (rows <= bt) return bt;
+    return cap;
+}
+
+// Bytes of split-K workspace the dense call below may use for (rows, N, K); 0 if it will not split.
+static int splits_for(int rows, int N, int K, int bt) {
+    const int n_tiles = (N + WM - 1) / WM, row_tiles = (rows + bt - 1) / bt, kb = (K + BK - 1) / BK;
+    const int ctas = n_tiles * row_tiles;
+    if (ctas >= 120 || kb < 4) return 1;
+    int s = (240 + ctas - 1) / ctas;
+    if (s > kb / 2) s = kb / 2;
+    return s < 1 ? 1 : s;
+}
+
+Q6K_API long long q6k_gemm_tc_workspace(int rows, int N, int K) {
+    const int bt = q6k_tc_token_tile(rows, 0);
+    const int s = splits_for(rows, N, K, bt);
+    return s > 1 ? (long long)s * rows * N * 4 : 0;
+}
+
+// A: bfloat16 [rows_total, K] with row pitch lda (elements).  W (and W2 for the SwiGLU epilogue):
+// bfloat16 [groups, N, K] contiguous.  epilogue: 0 store FP32, 1 add into FP32, 2 SwiGLU -> bfloat16.
+// Grouped when tile_group != null: bt is the token tile the tile list was made for.  Dense calls
+// may split K over CTAs when the output has too few tiles to fill the GPU; they then need
+// `workspace` of q6k_gemm_tc_workspace bytes.
+Q6K_API int q6k_gemm_tc(const void* A, long long lda, int rows_total, const void* W, const void* W2, int groups, int N, int K,
+                        void* out, int ldo, int epilogue, const int* tile_group, const int* tile_row0,
+                        const int* group_offsets, const int* num_tiles, int max_tiles, int bt, float* workspace,
+                        long long workspace_bytes, cudaStream_t st) {
+    if (rows_total == 0 || N == 0) return 0;
+    Q6K_REQUIRE(rows_total > 0 && N > 0 && K > 0 && groups > 0, "gemm_tc: bad sizes rows=%d N=%d K=%d groups=%d", rows_total, N, K, groups);
+    Q6K_REQUIRE(K % 8 == 0 && lda % 8 == 0, "gemm_tc: K=%d and the row pitch %lld must be multiples of 8 (TMA rows start on 16 bytes)", K, lda);
+    Q6K_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0 && (!W2 || ((uintptr_t)W2 & 15) == 0),
+                "gemm_tc: operands must be 16-byte aligned");
+    Q6K_REQUIRE(epilogue >= 0 && epilogue <= 2, "gemm_tc: unknown epilogue %d", epilogue);
+    const bool dual = epilogue == EPI_SWIGLU;
+    Q6K_REQUIRE(!dual || W2, "gemm_tc: the SwiGLU epilogue needs two weight matrices");
+    const bool grouped = tile_group != nullptr;
+    if (!grouped) bt = q6k_tc_token_tile(rows_total, dual);
+    Q6K_REQUIRE(bt == 16 || bt == 32 || bt == 64 || bt == 128 || (bt == 256 && !dual), "gemm_tc: token tile %d is not supported", bt);
+    Q6K_REQUIRE((long long)groups * N < (1LL << 31), "gemm_tc: weight rows exceed the TMA coordinate range");
+
+    CUtensorMap tw, tw2, ta;
+    if (int rc = weight_map(&tw, W, (long long)groups * N, K)) return rc;
+    tw2 = tw;
+    if (dual)
+        if (int rc = weight_map(&tw2, W2, (long long)groups * N, K)) return rc;
+    if (int rc = make_map(&ta, A, rows_total, K, lda, bt, false)) return rc;
+
+    Params p{};
+    p.out = out;
+    p.tile_group = tile_group, p.tile_row0 = tile_row0, p.group_offsets = group_offsets, p.num_tiles = num_tiles;
+    p.rows_total = rows_total, p.N = N, p.K = K, p.ldo = ldo, p.epilogue = epilogue;
+    const int kb = (K + BK - 1) / BK;
+    int splits = 1;
+    if (!grouped && !dual) {
+        splits = splits_for(rows_total, N, K, bt);
+        if (splits > 1 && (!workspace || workspace_bytes < (long long)splits * rows_total * N * 4)) splits = 1;
+    }
+    p.kb_per_split = (kb + splits - 1) / splits;
+    splits = (kb + p.kb_per_split - 1) / p.kb_per_split;
+    if (splits > 1) {
+        p.partial = workspace;
+        p.epilogue = EPI_PARTIAL;
+    }
+    const int ytiles = grouped ? max_tiles : (rows_total + bt - 1) / bt;
+    Q6K_REQUIRE(ytiles <= 65535 && splits <= 65535, "gemm_tc: %d row tiles exceed the grid limit", ytiles);
+    dim3 grid((N + WM - 1) / WM, ytiles, splits);
+    int rc;
+#define GO(BT_)                                                                    \
+    case BT_:                                                                      \
+        rc = dual ? launch<(BT_ > 128 ? 128 : BT_), true>(tw, tw2, ta, p, grid, st) \
+                  : launch<BT_, false>(tw, tw2, ta, p, grid, st);                  \
+        break;
+    switch (bt) {
+        GO(16) GO(32) GO(64) GO(128) GO(256)
+        default: return q6k_fail("gemm_tc: token tile %d", bt);
+    }
+#undef GO
+    if (rc) return rc;
+    if (splits > 1) {
+        const size_t count = (size_t)rows_total * N;
+        splitk_reduce_kernel<<<(unsigned)((count + 255) / 256), 256, 0, st>>>(workspace, splits, count, (float*)out, N, ldo,
+                                                                             epilogue == EPI_ADD);
+        return q6k_check_launch("gemm_tc split-K reduce");
+    }
+    return 0;
+}

@@ -49,7 +49,7 @@ def _need(t: torch.Tensor, name: str, dtype=None, shape=None):
 
 
 # kernels launched per exported function (for launch accounting in benchmarks)
-_LAUNCHES = {"q6k_moe_permute": 3}
+_LAUNCHES = {"q6k_moe_permute": 3, "q6k_gemm_tc": 1}
 launch_count = 0
 
 
@@ -187,6 +187,96 @@ def tile_list(offsets: torch.Tensor, pairs: int, bm: int):
     num_tiles = torch.empty(1, dtype=torch.int32, device=offsets.device)
     _call("q6k_tile_list", _ptr(offsets), _i(G), _i(bm), _ptr(tile_group), _ptr(tile_row0), _ptr(num_tiles), _i(max_tiles), _stream())
     return offsets, tile_group, tile_row0, num_tiles
+
+
+# --------------------------------------------------------------------------- matrix products (tcgen05 tensor cores)
+def gather_rows(x: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    """out[r] = x[idx[r]] (rows of a multiple of 16 bytes)."""
+    _need(x, "x")
+    _need(idx, "idx", torch.int32)
+    out = torch.empty((idx.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+    _call("q6k_gather_rows", _ptr(x), _ptr(idx), _ptr(out), _i(idx.numel()), _i(x.shape[1] * x.element_size()), _stream())
+    return out
+
+
+def tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the tensor-core kernel takes these operands: bfloat16, K a multiple of 8, rows
+    starting on 16 bytes."""
+    return (a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0
+            and a.stride(1) == 1 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and w.is_contiguous())
+
+
+def tc_token_tile(rows: int, dual: bool) -> int:
+    lib = library()
+    lib.q6k_tc_token_tile.restype = ctypes.c_int
+    return lib.q6k_tc_token_tile(_i(rows), _i(1 if dual else 0))
+
+
+def tc_status() -> int:
+    """0, or the code of a bounded wait that ran out inside a tensor-core kernel (synchronises)."""
+    lib = library()
+    lib.q6k_tc_status.restype = ctypes.c_int
+    return lib.q6k_tc_status()
+
+
+_workspaces = {}
+
+
+def _workspace(nbytes: int, device) -> torch.Tensor:
+    key = (str(device), torch.cuda.current_stream().cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() * 4 < nbytes:
+        ws = torch.empty(max(nbytes // 4, 1 << 20), dtype=torch.float32, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False,
+            w2: Optional[torch.Tensor] = None, groups=None, bt: int = 0, rows: Optional[int] = None) -> torch.Tensor:
+    """The same contract as gemm_simt without the row gather, on tcgen05 tensor cores: bfloat16
+    operands, FP32 accumulation in tensor memory.  Grouped calls pass the tile list made for
+    token tile `bt` (tile_list(offsets, pairs, bt))."""
+    if not tc_supported(a, w):
+        raise KernelError("gemm_tc: operands must be bfloat16 with K a multiple of 8 and 16-byte aligned rows")
+    K = a.shape[1]
+    grouped = w.dim() == 3
+    G = w.shape[0] if grouped else 1
+    N = w.shape[-2]
+    if w.shape[-1] != K:
+        raise KernelError(f"gemm_tc: a has K={K}, w has K={w.shape[-1]}")
+    if grouped and groups is None:
+        raise KernelError("gemm_tc: a grouped weight needs group offsets and a tile list")
+    M = rows if rows is not None else a.shape[0]
+    epi = EPI_SWIGLU if w2 is not None else (EPI_ADD if accumulate else EPI_STORE)
+    out_dtype = torch.bfloat16 if w2 is not None else torch.float32
+    if out is None:
+        if accumulate:
+            raise KernelError("gemm_tc: accumulate needs an output")
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    _need(out, "out", out_dtype)
+    if out.shape[0] < M or out.shape[1] != N:
+        raise KernelError(f"gemm_tc: out has shape {tuple(out.shape)}, needs [{M}, {N}]")
+    if w2 is not None:
+        _need(w2, "w2", torch.bfloat16, w.shape)
+    lib = library()
+    ws = None
+    ws_bytes = 0
+    if grouped:
+        offsets, tile_group, tile_row0, num_tiles = groups
+        max_tiles = tile_group.numel()
+    else:
+        offsets = tile_group = tile_row0 = num_tiles = None
+        max_tiles = 0
+        if w2 is None:
+            lib.q6k_gemm_tc_workspace.restype = ctypes.c_longlong
+            ws_bytes = lib.q6k_gemm_tc_workspace(_i(M), _i(N), _i(K))
+            if ws_bytes:
+                ws = _workspace(ws_bytes, a.device)
+                ws_bytes = ws.numel() * 4
+    _call("q6k_gemm_tc", _ptr(a), _ll(a.stride(0)), _i(M), _ptr(w), _ptr(w2), _i(G), _i(N), _i(K), _ptr(out), _i(out.stride(0)),
+          _i(epi), _ptr(tile_group), _ptr(tile_row0), _ptr(offsets), _ptr(num_tiles), _i(max_tiles), _i(bt), _ptr(ws),
+          _ll(ws_bytes), _stream())
+    return out
 
 
 # --------------------------------------------------------------------------- attention

@@ -72,9 +72,9 @@ class RoutedExperts(FeedForward):
         logits = linear.matmul(xn, self.w_router, rt)                       # FP32 [T, E]
         sel_e, sel_w = ops.route(logits, self.k, self.scoring, self.renorm)
         offsets, pair_row, row_token = ops.moe_permute(sel_e, self.E)
-        groups = linear.group_tiles(offsets, pairs, rt)
-        act = linear.grouped_swiglu(xn, row_token, self.w_gate, self.w_up, groups, pairs, rt)    # [pairs, I]
-        y = linear.grouped_matmul(act, self.w_down, groups, pairs, rt)                            # FP32 [pairs, D]
+        plan = linear.group_plan(xn, self.w_gate, offsets, row_token, pairs, rt)
+        act = linear.grouped_swiglu(xn, plan, self.w_gate, self.w_up, rt)                         # [pairs, I]
+        y = linear.grouped_matmul(act, plan, self.w_down, rt)                                     # FP32 [pairs, D]
         ops.combine(y, pair_row, sel_w, out)
         if self.shared is not None:
             self.shared.forward(xn, ctx, out)

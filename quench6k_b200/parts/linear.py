@@ -1,8 +1,8 @@
 """Chooses the matrix-product kernel for an operand dtype and shape.
 
 float32 operands always take the CUDA-core FP32 kernel (no reduced-precision matrix mode exists on
-that path).  bfloat16 operands take the tensor-core kernels where the shape allows and the
-CUDA-core kernel otherwise.
+that path).  bfloat16 operands take the tcgen05 tensor-core kernel where the shape allows (K a
+multiple of 8, rows starting on 16 bytes) and the CUDA-core kernel otherwise.
 """
 from __future__ import annotations
 
@@ -13,25 +13,55 @@ import torch
 from .. import ops
 
 
+def _tc(a: torch.Tensor, w: torch.Tensor, rt) -> bool:
+    return rt.tensor_cores and not rt.is_fp32 and ops.tc_supported(a, w)
+
+
 def matmul(a: torch.Tensor, w: torch.Tensor, rt, out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
     """FP32 out[r] (+)= a[r] @ w^T;  a: [M, K], w: [N, K]."""
+    if _tc(a, w, rt):
+        return ops.gemm_tc(a, w, out=out, accumulate=accumulate)
     return ops.gemm_simt(a, w, out=out, accumulate=accumulate)
 
 
 def swiglu_matmul(a: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, rt) -> torch.Tensor:
     """act[r] = silu(a[r] @ w_gate^T) * (a[r] @ w_up^T) in a's dtype."""
+    if _tc(a, w_gate, rt):
+        return ops.gemm_tc(a, w_gate, w2=w_up)
     return ops.gemm_simt(a, w_gate, w2=w_up)
 
 
-def grouped_swiglu(a: torch.Tensor, row_token: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, groups, pairs: int, rt):
+class GroupPlan:
+    """Row tiles of the experts' groups for one permutation, for whichever kernel runs them."""
+
+    def __init__(self, offsets: torch.Tensor, row_token: torch.Tensor, pairs: int, num_groups: int, rt, tc: bool):
+        self.pairs, self.row_token, self.tc = pairs, row_token, tc
+        if tc:
+            avg = max(1, pairs // max(1, num_groups))
+            want = avg + avg // 2
+            self.bt_dual = ops.tc_token_tile(want, True)
+            self.bt = self.bt_dual
+            self.tiles = ops.tile_list(offsets, pairs, self.bt)
+        else:
+            self.tiles = ops.tile_list(offsets, pairs, ops.simt_tile_rows())
+
+
+def group_plan(a: torch.Tensor, w: torch.Tensor, offsets, row_token, pairs: int, rt) -> GroupPlan:
+    return GroupPlan(offsets, row_token, pairs, w.shape[0], rt, _tc(a, w, rt))
+
+
+def grouped_swiglu(a: torch.Tensor, plan: GroupPlan, w_gate: torch.Tensor, w_up: torch.Tensor, rt) -> torch.Tensor:
     """act[row] = SwiGLU of a[row_token[row]] with the weights of the row's group; [pairs, I]."""
-    return ops.gemm_simt(a, w_gate, w2=w_up, a_rows=row_token, groups=groups, rows=pairs)
+    if plan.tc:
+        xs = ops.gather_rows(a, plan.row_token)
+        return ops.gemm_tc(xs, w_gate, w2=w_up, groups=plan.tiles, bt=plan.bt, rows=plan.pairs)
+    return ops.gemm_simt(a, w_gate, w2=w_up, a_rows=plan.row_token, groups=plan.tiles, rows=plan.pairs)
 
 
-def grouped_matmul(a: torch.Tensor, w: torch.Tensor, groups, pairs: int, rt) -> torch.Tensor:
+def grouped_matmul(a: torch.Tensor, plan: GroupPlan, w: torch.Tensor, rt) -> torch.Tensor:
     """FP32 y[row] = a[row] @ w_g^T with the weights of the row's group; [pairs, N]."""
-    return ops.gemm_simt(a, w, groups=groups, rows=pairs)
-
-
-def group_tiles(offsets: torch.Tensor, pairs: int, rt):
-    return ops.tile_list(offsets, pairs, ops.simt_tile_rows())
+    if plan.tc and ops.tc_supported(a, w):
+        return ops.gemm_tc(a, w, groups=plan.tiles, bt=plan.bt, rows=plan.pairs)
+    if plan.tc:
+        return ops.gemm_simt(a, w, groups=ops.tile_list(plan.tiles[0], plan.pairs, ops.simt_tile_rows()), rows=plan.pairs)
+    return ops.gemm_simt(a, w, groups=plan.tiles, rows=plan.pairs)

@@ -226,3 +226,64 @@ def test_kernels_refuse_what_they_cannot_do():
         ops.argmax(torch.zeros(2, 5))
     with pytest.raises(ops.KernelError, match="dtype"):
         ops.embed(torch.zeros(2, dtype=torch.int64, device=DEV), torch.zeros(4, 4, device=DEV))
+
+
+# --------------------------------------------------------------------------- tcgen05 tensor-core products
+@pytest.mark.parametrize("M,N,K", [(1, 256, 64), (8, 5120, 2048), (16, 100, 72), (17, 384, 200), (70, 130, 1024),
+                                   (200, 512, 136), (300, 1000, 4096), (2048, 640, 512), (5, 2048, 4096)])
+def test_gemm_tc_dense(M, N, K):
+    from quench6k_b200 import ops
+    a, w = _t(M, K, dtype=torch.bfloat16), _t(N, K, dtype=torch.bfloat16, seed=1)
+    ref = a.double().cpu() @ w.double().cpu().T
+    out = ops.gemm_tc(a, w)
+    assert ops.tc_status() == 0
+    tol = 1e-5 * math.sqrt(K) * ref.abs().max()
+    assert (out.double().cpu() - ref).abs().max() <= tol
+    base = _t(M, N, seed=2)
+    acc = base.clone()
+    ops.gemm_tc(a, w, out=acc, accumulate=True)
+    assert (acc.double().cpu() - (base.double().cpu() + ref)).abs().max() <= tol
+    w2 = _t(N, K, dtype=torch.bfloat16, seed=3)
+    act = ops.gemm_tc(a, w, w2=w2)
+    want = P.silu(ref) * (a.double().cpu() @ w2.double().cpu().T)
+    assert act.dtype == torch.bfloat16
+    assert (act.double().cpu() - want).abs().max() <= 1e-2 * want.abs().max()
+    assert ops.tc_status() == 0
+    # a row's result does not depend on the rows beside it as long as the shape class is the same
+    if M > 1:
+        again = ops.gemm_tc(torch.cat([a[1:], a[:1]]).contiguous(), w)
+        assert torch.equal(again[-1], out[0])
+
+
+def test_gemm_tc_refuses_unaligned():
+    from quench6k_b200 import ops
+    a, w = _t(4, 20, dtype=torch.bfloat16), _t(8, 20, dtype=torch.bfloat16)
+    assert not ops.tc_supported(a, w)
+    with pytest.raises(ops.KernelError, match="multiple of 8"):
+        ops.gemm_tc(a, w)
+
+
+@pytest.mark.parametrize("T,k,E,D,I", [(37, 3, 10, 64, 40), (8, 8, 256, 256, 128), (300, 4, 16, 136, 72), (2048, 8, 64, 128, 64)])
+def test_gemm_tc_grouped(T, k, E, D, I):
+    from quench6k_b200 import ops
+    g = torch.Generator().manual_seed(T)
+    sel = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32).to(DEV)
+    offsets, pair_row, row_token = ops.moe_permute(sel, E)
+    pairs = T * k
+    x = _t(T, D, dtype=torch.bfloat16)
+    wg, wu = _t(E, I, D, dtype=torch.bfloat16, seed=1, scale=0.3), _t(E, I, D, dtype=torch.bfloat16, seed=2, scale=0.3)
+    wd = _t(E, D, I, dtype=torch.bfloat16, seed=3, scale=0.3)
+    avg = max(1, pairs // E)
+    bt = ops.tc_token_tile(avg + avg // 2, True)
+    tiles = ops.tile_list(offsets, pairs, bt)
+    xs = ops.gather_rows(x, row_token)
+    assert torch.equal(xs, x[row_token.long()])
+    act = ops.gemm_tc(xs, wg, w2=wu, groups=tiles, bt=bt, rows=pairs)
+    y = ops.gemm_tc(act, wd, groups=tiles, bt=bt, rows=pairs)
+    assert ops.tc_status() == 0
+    # reference: the CUDA-core kernel (itself checked against float64 above)
+    simt_tiles = ops.tile_list(offsets, pairs, ops.simt_tile_rows())
+    act_ref = ops.gemm_simt(x, wg, w2=wu, a_rows=row_token, groups=simt_tiles, rows=pairs)
+    y_ref = ops.gemm_simt(act, wd, groups=simt_tiles, rows=pairs)
+    assert (act.float() - act_ref.float()).abs().max() <= 1e-2 * act_ref.float().abs().max()
+    assert (y - y_ref).abs().max() <= 1e-4 * y_ref.abs().max()

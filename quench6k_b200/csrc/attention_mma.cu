@@ -1,0 +1,384 @@
+// bfloat16 attention over the paged cache on tensor cores, for decode rows and prompt portions in
+// one launch, with the key range split over CTAs and merged afterwards.
+//
+// Arithmetic as the reference's attn_kernel / attn_merge_kernel (crates/cuda/kernels/flint.cu:211-561):
+// scores in base 2 (scale * log2 e folded in), causal and window mask per row, online softmax per
+// key tile, probabilities rounded to bfloat16 before they are summed, sinks in the merge's
+// denominator only.  Differences: keys and values come from pages through the block table; a
+// launch covers rows of many requests through a tile list; head size and group size are
+// parameters (head size 64 or 128 here; other sizes run on the generic kernel).
+//
+// A tile is up to ROWS = 16 (narrow) or 64 (wide) query rows of one request and one KV head:
+// row = token_in_tile * G + head_in_group.  Key tiles hold 64 keys, aligned to multiples of 64 of
+// the key index.  Narrow tiles (decode): the 4 warps share the 16 rows and split each key tile
+// (16 keys each), then merge their partial softmax states through shared memory.  Wide tiles
+// (prompt portions): each warp owns 16 rows and walks all 64 keys of a tile.
+// K and V rows are copied with 16-byte cp.async into a 2-stage ring; chunks are XOR-swizzled by
+// the row so that ldmatrix reads are free of bank conflicts.
+#include "common.cuh"
+
+namespace {
+
+constexpr int KT = 64;                       // keys per tile
+constexpr float LOG2E = 1.4426950408889634f;
+
+struct AttnParams {
+    const __nv_bfloat16* q;                  // [T, Hq, HD]
+    const __nv_bfloat16* k_pages;            // [pages, Hkv, page_size, HD]
+    const __nv_bfloat16* v_pages;
+    const int* block_table;                  // [R, max_blocks]
+    const int* req_of_token;
+    const int* positions;
+    const int* tile_tok0;                    // first row of each tile
+    const int* tile_ntok;                    // tokens of each tile (consecutive positions of one request)
+    const float* sinks;                      // [Hq] or null
+    __nv_bfloat16* out;                      // [T, Hq*HD]
+    float* part_o;                           // [T*Hq, max_splits, HD]
+    float* part_ml;                          // [T*Hq, max_splits, 2]
+    int max_blocks, page_size, window, Hq, Hkv, G, max_splits, min_tiles;
+    float scale_log2;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;            // 0 source bytes: the 16 destination bytes become zeros
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t* r, uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t* r, uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Effective number of key splits of a tile: a function of its key range and the launch only,
+// computed alike by the attention and the merge kernel.
+__device__ __forceinline__ void split_plan(int first_tile, int end_tile, int max_splits, int min_tiles, int& per, int& se) {
+    const int n = end_tile - first_tile;
+    int want = n / min_tiles;
+    want = want < 1 ? 1 : (want > max_splits ? max_splits : want);
+    per = (n + want - 1) / want;
+    se = (n + per - 1) / per;
+}
+
+// Byte offset of 16-byte chunk c of row r in a swizzled [rows][HD] bf16 tile.
+template <int HD> __device__ __forceinline__ uint32_t sw(int r, int c) { return (uint32_t)(r * HD * 2 + ((c ^ (r & 7)) << 4)); }
+
+template <int HD, bool WIDE>
+__global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) {
+    constexpr int ROWS = WIDE ? 64 : 16;
+    constexpr int CH = HD / 8;               // 16-byte chunks per row
+    constexpr int KW = WIDE ? KT : 16;       // keys of a tile this warp handles
+    constexpr int NB = KW / 8;               // score n-blocks per warp
+    constexpr int DB = HD / 8;               // output n-blocks
+    constexpr uint32_t TILE_BYTES = KT * HD * 2;
+    extern __shared__ __align__(128) uint8_t smem[];
+    // [Q: ROWS x HD][K stage 0][K stage 1][V stage 0][V stage 1]
+    const uint32_t q_s = smem_u32(smem), k_s = q_s + ROWS * HD * 2, v_s = k_s + 2 * TILE_BYTES;
+
+    const int tile = blockIdx.z, kh = blockIdx.y, split = blockIdx.x;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g8 = lane >> 2, t4 = lane & 3;
+    const int G = p.G;
+    const int tok0 = p.tile_tok0[tile], ntok = p.tile_ntok[tile];
+    const int pos_first = p.positions[tok0], pos_last = pos_first + ntok - 1;
+    const int* bt = p.block_table + (size_t)p.req_of_token[tok0] * p.max_blocks;
+    const int k_lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    const int first_tile = k_lo / KT, end_tile = pos_last / KT + 1;
+    int per, se;
+    split_plan(first_tile, end_tile, p.max_splits, p.min_tiles, per, se);
+    if (split >= se) return;
+    const int t_begin = first_tile + split * per, t_end = min(end_tile, t_begin + per);
+
+    // ---- Q tile into shared memory (zero rows past the tile's tokens)
+    for (int idx = tid; idx < ROWS * CH; idx += 128) {
+        const int r = idx / CH, c = idx % CH, tt = r / G, hg = r % G;
+        const bool valid = tt < ntok;
+        const __nv_bfloat16* src = p.q + ((size_t)(tok0 + (valid ? tt : 0)) * p.Hq + kh * G + hg) * HD + c * 8;
+        cp_async16(q_s + sw<HD>(r, c), src, valid);
+    }
+    auto load_kv = [&](int stage, int kt) {
+        for (int idx = tid; idx < KT * CH; idx += 128) {
+            const int r = idx / CH, c = idx % CH, j = kt * KT + r;
+            const bool in = j >= k_lo && j <= pos_last;
+            int page = in ? bt[j / p.page_size] : -1;
+            const bool valid = page >= 0;
+            const size_t off = valid ? (((size_t)page * p.Hkv + kh) * p.page_size + j % p.page_size) * HD + c * 8 : 0;
+            cp_async16(k_s + stage * TILE_BYTES + sw<HD>(r, c), p.k_pages + off, valid);
+            cp_async16(v_s + stage * TILE_BYTES + sw<HD>(r, c), p.v_pages + off, valid);
+        }
+    };
+    load_kv(0, t_begin);
+    cp_async_commit();
+
+    // this thread's two rows (g8 and g8 + 8 of the warp's 16) and their key limits
+    const int rbase = WIDE ? warp * 16 : 0, koff = WIDE ? 0 : warp * 16;
+    int lim_hi[2], lim_lo[2];
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+        const int r = rbase + g8 + hr * 8, tt = r / G;
+        const int pos = pos_first + tt;
+        lim_hi[hr] = tt < ntok ? pos : -1;
+        lim_lo[hr] = p.window > 0 ? pos - p.window + 1 : 0;
+    }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+    float o[DB][4];
+#pragma unroll
+    for (int n = 0; n < DB; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
+
+    cp_async_wait<0>();
+    __syncthreads();
+    uint32_t qa[HD / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) ldmatrix_x4(qa[ks], q_s + sw<HD>(rbase + (lane & 15), ks * 2 + (lane >> 4)));
+
+    for (int kt = t_begin; kt < t_end; ++kt) {
+        const int stage = (kt - t_begin) & 1;
+        if (kt + 1 < t_end) load_kv(stage ^ 1, kt + 1);
+        cp_async_commit();
+        const uint32_t kb = k_s + stage * TILE_BYTES, vb = v_s + stage * TILE_BYTES;
+        const int j0 = kt * KT + koff;
+        // ---- S = Q K^T for this warp's keys
+        float s[NB][4];
+#pragma unroll
+        for (int n = 0; n < NB; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+            for (int nj = 0; nj < NB / 2; ++nj) {
+                uint32_t b[4];
+                const int key = koff + nj * 16 + ((lane >> 4) << 3) + (lane & 7);
+                ldmatrix_x4(b, kb + sw<HD>(key, ks * 2 + ((lane >> 3) & 1)));
+                mma_bf16(s[2 * nj], qa[ks], b[0], b[1]);
+                mma_bf16(s[2 * nj + 1], qa[ks], b[2], b[3]);
+            }
+        }
+        // ---- mask, online softmax
+        float mx[2] = {m[0], m[1]};
+#pragma unroll
+        for (int n = 0; n < NB; ++n)
+#pragma unroll
+            for (int x = 0; x < 4; ++x) {
+                const int hr = x >> 1, j = j0 + n * 8 + 2 * t4 + (x & 1);
+                const bool ok = j <= lim_hi[hr] && j >= lim_lo[hr];
+                s[n][x] = ok ? s[n][x] * p.scale_log2 : -INFINITY;
+                mx[hr] = fmaxf(mx[hr], s[n][x]);
+            }
+        float corr[2];
+#pragma unroll
+        for (int hr = 0; hr < 2; ++hr) {
+            mx[hr] = fmaxf(mx[hr], __shfl_xor_sync(0xffffffffu, mx[hr], 1));
+            mx[hr] = fmaxf(mx[hr], __shfl_xor_sync(0xffffffffu, mx[hr], 2));
+            corr[hr] = mx[hr] == -INFINITY ? 1.0f : exp2f(m[hr] - mx[hr]);
+            m[hr] = mx[hr];
+            l[hr] *= corr[hr];
+        }
+#pragma unroll
+        for (int n = 0; n < DB; ++n) o[n][0] *= corr[0], o[n][1] *= corr[0], o[n][2] *= corr[1], o[n][3] *= corr[1];
+        uint32_t pa[KW / 16][4];
+#pragma unroll
+        for (int n = 0; n < NB; ++n) {
+            float pr[4];
+#pragma unroll
+            for (int x = 0; x < 4; ++x) pr[x] = m[x >> 1] == -INFINITY ? 0.0f : exp2f(s[n][x] - m[x >> 1]);
+            // rounded to bfloat16 before summing, so that l matches the P that multiplies V
+            const __nv_bfloat162 lo2 = __floats2bfloat162_rn(pr[0], pr[1]), hi2 = __floats2bfloat162_rn(pr[2], pr[3]);
+            const float2 flo = __bfloat1622float2(lo2), fhi = __bfloat1622float2(hi2);
+            l[0] += flo.x + flo.y;
+            l[1] += fhi.x + fhi.y;
+            pa[n / 2][(n % 2) * 2 + 0] = *reinterpret_cast<const uint32_t*>(&lo2);
+            pa[n / 2][(n % 2) * 2 + 1] = *reinterpret_cast<const uint32_t*>(&hi2);
+        }
+        // ---- O += P V
+#pragma unroll
+        for (int ks = 0; ks < KW / 16; ++ks) {
+#pragma unroll
+            for (int dj = 0; dj < DB / 2; ++dj) {
+                uint32_t b[4];
+                const int key = koff + ks * 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
+                ldmatrix_x4_trans(b, vb + sw<HD>(key, dj * 2 + (lane >> 4)));
+                mma_bf16(o[2 * dj], pa[ks], b[0], b[1]);
+                mma_bf16(o[2 * dj + 1], pa[ks], b[2], b[3]);
+            }
+        }
+        cp_async_wait<0>();
+        __syncthreads();
+    }
+    // row sums live per thread: add the quad's
+#pragma unroll
+    for (int hr = 0; hr < 2; ++hr) {
+        l[hr] += __shfl_xor_sync(0xffffffffu, l[hr], 1);
+        l[hr] += __shfl_xor_sync(0xffffffffu, l[hr], 2);
+    }
+
+    // ---- results: (m, l, o) per row; narrow tiles first merge the 4 warps' key subsets
+    float* red = reinterpret_cast<float*>(smem);             // reuse the tile ring (all loads have landed, all reads are done)
+    if (!WIDE) {
+        // red: [4 warps][16 rows][HD + 2]
+        constexpr int LD = HD + 2;
+#pragma unroll
+        for (int hr = 0; hr < 2; ++hr) {
+            float* dst = red + ((size_t)warp * 16 + g8 + hr * 8) * LD;
+            if (t4 == 0) dst[HD] = m[hr], dst[HD + 1] = l[hr];
+#pragma unroll
+            for (int n = 0; n < DB; ++n) {
+                dst[n * 8 + 2 * t4] = o[n][hr * 2];
+                dst[n * 8 + 2 * t4 + 1] = o[n][hr * 2 + 1];
+            }
+        }
+        __syncthreads();
+        // 128 threads: row = tid / 8, 8 threads share a row's HD values
+        const int r = tid >> 3, sub = tid & 7, tt = r / G, hg = r % G;
+        if (tt >= ntok) return;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, red[((size_t)w * 16 + r) * LD + HD]);
+        float wgt[4], L = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = red[((size_t)w * 16 + r) * LD + HD];
+            wgt[w] = mw == -INFINITY ? 0.0f : exp2f(mw - M);
+            L += wgt[w] * red[((size_t)w * 16 + r) * LD + HD + 1];
+        }
+        const size_t row = (size_t)(tok0 + tt) * p.Hq + kh * G + hg;
+        float osc = 1.0f, den = L;
+        if (se == 1 && p.sinks) {
+            const float sk = p.sinks[kh * G + hg] * LOG2E, Mx = fmaxf(M, sk);
+            osc = exp2f(M - Mx);
+            den = L * osc + exp2f(sk - Mx);
+        }
+        for (int d = sub; d < HD; d += 8) {
+            float acc = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) acc += wgt[w] * red[((size_t)w * 16 + r) * LD + d];
+            if (se == 1) p.out[row * HD + d] = __float2bfloat16_rn(acc * osc / den);
+            else p.part_o[(row * p.max_splits + split) * HD + d] = acc;
+        }
+        if (se > 1 && sub == 0) {
+            p.part_ml[(row * p.max_splits + split) * 2] = M;
+            p.part_ml[(row * p.max_splits + split) * 2 + 1] = L;
+        }
+    } else {
+#pragma unroll
+        for (int hr = 0; hr < 2; ++hr) {
+            const int r = rbase + g8 + hr * 8, tt = r / G, hg = r % G;
+            if (tt >= ntok) continue;
+            const size_t row = (size_t)(tok0 + tt) * p.Hq + kh * G + hg;
+            if (se == 1) {
+                float osc = 1.0f, den = l[hr];
+                if (p.sinks) {
+                    const float sk = p.sinks[kh * G + hg] * LOG2E, Mx = fmaxf(m[hr], sk);
+                    osc = exp2f(m[hr] - Mx);
+                    den = l[hr] * osc + exp2f(sk - Mx);
+                }
+                const float inv = osc / den;
+#pragma unroll
+                for (int n = 0; n < DB; ++n)
+                    *reinterpret_cast<uint32_t*>(p.out + row * HD + n * 8 + 2 * t4) = pack_bf16(o[n][hr * 2] * inv, o[n][hr * 2 + 1] * inv);
+            } else {
+                float* po = p.part_o + (row * p.max_splits + split) * HD;
+#pragma unroll
+                for (int n = 0; n < DB; ++n) *reinterpret_cast<float2*>(po + n * 8 + 2 * t4) = make_float2(o[n][hr * 2], o[n][hr * 2 + 1]);
+                if (t4 == 0) {
+                    p.part_ml[(row * p.max_splits + split) * 2] = m[hr];
+                    p.part_ml[(row * p.max_splits + split) * 2 + 1] = l[hr];
+                }
+            }
+        }
+    }
+}
+
+// out[row] = sum_s 2^(m_s - M) o_s / (sum_s 2^(m_s - M) l_s + 2^(sink - M)); one block per (tile, KV head).
+template <int HD>
+__global__ void __launch_bounds__(128) attention_merge_kernel(const AttnParams p) {
+    const int tile = blockIdx.x, kh = blockIdx.y, G = p.G;
+    const int tok0 = p.tile_tok0[tile], ntok = p.tile_ntok[tile];
+    const int pos_first = p.positions[tok0], pos_last = pos_first + ntok - 1;
+    const int k_lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    int per, se;
+    split_plan(k_lo / KT, pos_last / KT + 1, p.max_splits, p.min_tiles, per, se);
+    if (se == 1) return;                      // the attention kernel wrote the output itself
+    for (int idx = threadIdx.x; idx < ntok * G * HD; idx += blockDim.x) {
+        const int r = idx / HD, d = idx % HD, tt = r / G, hg = r % G;
+        const size_t row = (size_t)(tok0 + tt) * p.Hq + kh * G + hg;
+        const float* ml = p.part_ml + row * p.max_splits * 2;
+        const float* po = p.part_o + row * p.max_splits * HD;
+        const float sk = p.sinks ? p.sinks[kh * G + hg] * LOG2E : -INFINITY;
+        float M = sk;
+        for (int s = 0; s < se; ++s) M = fmaxf(M, ml[s * 2]);
+        float den = p.sinks ? exp2f(sk - M) : 0.0f, num = 0.0f;
+        for (int s = 0; s < se; ++s) {
+            const float ms = ml[s * 2];
+            const float w = ms == -INFINITY ? 0.0f : exp2f(ms - M);
+            den = fmaf(w, ms == -INFINITY ? 0.0f : ml[s * 2 + 1], den);
+            num = fmaf(w, po[(size_t)s * HD + d], num);
+        }
+        p.out[row * HD + d] = __float2bfloat16_rn(num / den);
+    }
+}
+
+template <int HD, bool WIDE>
+int launch(const AttnParams& p, int n_tiles, cudaStream_t st) {
+    constexpr int ROWS = WIDE ? 64 : 16;
+    const size_t ring = ROWS * HD * 2 + 4 * KT * HD * 2;
+    const size_t red = WIDE ? 0 : 4 * 16 * (HD + 2) * sizeof(float);
+    const size_t smem = ring > red ? ring : red;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attention_mma_kernel<HD, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return q6k_check_launch("attention_mma: shared memory attribute");
+        configured = true;
+    }
+    attention_mma_kernel<HD, WIDE><<<dim3(p.max_splits, p.Hkv, n_tiles), 128, smem, st>>>(p);
+    if (int rc = q6k_check_launch("attention_mma")) return rc;
+    if (p.max_splits > 1) {
+        attention_merge_kernel<HD><<<dim3(n_tiles, p.Hkv), 128, 0, st>>>(p);
+        return q6k_check_launch("attention_merge");
+    }
+    return 0;
+}
+
+}  // namespace
+
+// Rows per tile for a group size: 16 (narrow) or 64 (wide) query rows hold rows/G tokens.
+Q6K_API int q6k_attention_mma_supported(int hd, int G, int wide) { return (hd == 64 || hd == 128) && G >= 1 && G <= (wide ? 64 : 16); }
+
+// q: bfloat16 [T, Hq, hd]; pages: bfloat16 [*, Hkv, page_size, hd]; tiles: tile_tok0/tile_ntok [n_tiles], the
+// tokens of a tile being consecutive positions of one request, at most (wide ? 64 : 16) / G of them.
+// part_o: FP32 [T*Hq*max_splits*hd], part_ml: FP32 [T*Hq*max_splits*2] (unused when max_splits == 1).
+Q6K_API int q6k_attention_mma(const void* q, const void* k_pages, const void* v_pages, const int* block_table, int max_blocks,
+                              int page_size, const int* req_of_token, const int* positions, const int* tile_tok0,
+                              const int* tile_ntok, int n_tiles, int wide, int window, const float* sinks, float scale, void* out,
+                              float* part_o, float* part_ml, int max_splits, int min_tiles, int Hq, int Hkv, int hd,
+                              cudaStream_t st) {
+    if (n_tiles == 0) return 0;
+    Q6K_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention_mma: bad head counts Hq=%d Hkv=%d", Hq, Hkv);
+    const int G = Hq / Hkv;
+    Q6K_REQUIRE(q6k_attention_mma_supported(hd, G, wide), "attention_mma: head_dim %d / group size %d is not covered by the tensor-core kernel", hd, G);
+    Q6K_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0 && max_splits >= 1 && max_splits <= 65535 && min_tiles >= 1,
+                "attention_mma: bad page_size %d / max_blocks %d / window %d / splits %d", page_size, max_blocks, window, max_splits);
+    Q6K_REQUIRE(max_splits == 1 || (part_o && part_ml), "attention_mma: splitting the keys needs the partial buffers");
+    Q6K_REQUIRE(Hkv <= 65535 && n_tiles <= 65535, "attention_mma: grid limit exceeded (Hkv=%d, tiles=%d)", Hkv, n_tiles);
+    AttnParams p{};
+    p.q = (const __nv_bfloat16*)q, p.k_pages = (const __nv_bfloat16*)k_pages, p.v_pages = (const __nv_bfloat16*)v_pages;
+    p.block_table = block_table, p.req_of_token = req_of_token, p.positions = positions;
+    p.tile_tok0 = tile_tok0, p.tile_ntok = tile_ntok, p.sinks = sinks, p.out = (__nv_bfloat16*)out;
+    p.part_o = part_o, p.part_ml = part_ml;
+    p.max_blocks = max_blocks, p.page_size = page_size, p.window = window, p.Hq = Hq, p.Hkv = Hkv, p.G = G;
+    p.max_splits = max_splits, p.min_tiles = min_tiles, p.scale_log2 = scale * LOG2E;
+    if (hd == 128) return wide ? launch<128, true>(p, n_tiles, st) : launch<128, false>(p, n_tiles, st);
+    return wide ? launch<64, true>(p, n_tiles, st) : launch<64, false>(p, n_tiles, st);
+}

@@ -40,3 +40,19 @@ class StepContext:
     slots: List[int] = field(default_factory=list)
     max_context: int = 0                  # largest position + 1 in the step
     max_q_len: int = 0
+    plans: dict = field(default_factory=dict)     # per-step launch plans that parts share across layers (keyed by the part)
+
+    def query_tiles(self, tokens_per_tile: int):
+        """Tiles of at most `tokens_per_tile` consecutive tokens of one request, as device arrays
+        (first row, token count) and their number; made once per step and size."""
+        key = ("query_tiles", tokens_per_tile)
+        if key not in self.plans:
+            first, count, at = [], [], 0
+            for n in self.q_lens:
+                for i in range(0, n, tokens_per_tile):
+                    first.append(at + i)
+                    count.append(min(tokens_per_tile, n - i))
+                at += n
+            both = torch.tensor([first, count], dtype=torch.int32).to(self.token_ids.device, non_blocking=True)
+            self.plans[key] = (both[0], both[1], len(first))
+        return self.plans[key]

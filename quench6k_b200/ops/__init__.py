@@ -49,7 +49,7 @@ def _need(t: torch.Tensor, name: str, dtype=None, shape=None):
 
 
 # kernels launched per exported function (for launch accounting in benchmarks)
-_LAUNCHES = {"q6k_moe_permute": 3, "q6k_gemm_tc": 1}
+_LAUNCHES = {"q6k_moe_permute": 3, "q6k_gemm_tc": 1, "q6k_attention_mma": 2}
 launch_count = 0
 
 
@@ -330,6 +330,45 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
           _i(page_size), _ptr(req_of_token), _ptr(positions), _i(window or 0), _ptr(sinks),
           _f(scale if scale is not None else 1.0 / math.sqrt(hd)), _ptr(out), _i(T), _i(Hq), _i(Hkv), _i(hd),
           _i(dtype_code(q.dtype)), _stream())
+    return out
+
+
+def attention_mma_supported(hd: int, G: int, wide: bool) -> bool:
+    lib = library()
+    lib.q6k_attention_mma_supported.restype = ctypes.c_int
+    return bool(lib.q6k_attention_mma_supported(_i(hd), _i(G), _i(1 if wide else 0)))
+
+
+def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                  req_of_token: torch.Tensor, positions: torch.Tensor, tile_tok0: torch.Tensor, tile_ntok: torch.Tensor,
+                  wide: bool, window: Optional[int], sinks: Optional[torch.Tensor], max_splits: int = 1, min_tiles: int = 2,
+                  scale: Optional[float] = None) -> torch.Tensor:
+    """bfloat16 tensor-core attention over the pages.  Tiles: tile_tok0[i] is the first row and
+    tile_ntok[i] the number of tokens (consecutive positions of one request, at most
+    (64 if wide else 16) // G) of tile i.  max_splits: upper bound of key splits per tile."""
+    _need(q, "q", torch.bfloat16)
+    T, Hq, hd = q.shape
+    _need(k_pages, "k_pages", torch.bfloat16)
+    _need(v_pages, "v_pages", torch.bfloat16, k_pages.shape)
+    _, Hkv, page_size, hd2 = k_pages.shape
+    if hd2 != hd:
+        raise KernelError(f"attention: q has head_dim {hd}, the pages {hd2}")
+    for nm, t in (("block_table", block_table), ("req_of_token", req_of_token), ("positions", positions),
+                  ("tile_tok0", tile_tok0), ("tile_ntok", tile_ntok)):
+        _need(t, nm, torch.int32)
+    if sinks is not None:
+        _need(sinks, "sinks", torch.float32, (Hq,))
+    n_tiles = tile_tok0.numel()
+    out = torch.empty((T, Hq * hd), dtype=torch.bfloat16, device=q.device)
+    part_o = part_ml = None
+    if max_splits > 1:
+        ws = _workspace(T * Hq * max_splits * (hd + 2) * 4, q.device)
+        part_o = ws[: T * Hq * max_splits * hd]
+        part_ml = ws[T * Hq * max_splits * hd: T * Hq * max_splits * (hd + 2)]
+    _call("q6k_attention_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), _i(block_table.shape[1]), _i(page_size),
+          _ptr(req_of_token), _ptr(positions), _ptr(tile_tok0), _ptr(tile_ntok), _i(n_tiles), _i(1 if wide else 0), _i(window or 0),
+          _ptr(sinks), _f(scale if scale is not None else 1.0 / math.sqrt(hd)), _ptr(out), _ptr(part_o), _ptr(part_ml),
+          _i(max_splits), _i(min_tiles), _i(Hq), _i(Hkv), _i(hd), _stream())
     return out
 
 

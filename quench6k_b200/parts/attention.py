@@ -71,9 +71,24 @@ class Attention(Mixer):
             q = ops.qk_prep(qkv, self.Hq, self.Hkv, self.hd, self.q_norm, self.k_norm, self.eps, theta, ctx.positions,
                             ctx.req_of_token, table if write else None, cache.page_size, cache.k if write else None,
                             cache.v if write else None, rt.dtype)
-        a = ops.attention_generic(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, self.window, self.sinks,
-                                  self.scale)
+        a = self._attend(q, cache, table, ctx)
         linear.matmul(a, self.w_o, rt, out=out, accumulate=True)
+
+    def _attend(self, q, cache, table, ctx):
+        """Tensor-core kernel for bfloat16 where it covers the head and group size, else the generic one."""
+        rt, G = self.rt, self.Hq // self.Hkv
+        if rt.is_fp32 or not rt.tensor_cores:
+            return ops.attention_generic(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, self.window, self.sinks, self.scale)
+        wide = ctx.max_q_len > max(1, 16 // G) or not ops.attention_mma_supported(self.hd, G, False)
+        if not ops.attention_mma_supported(self.hd, G, wide):
+            return ops.attention_generic(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, self.window, self.sinks, self.scale)
+        tok0, ntok, n_tiles = ctx.query_tiles((64 if wide else 16) // G)
+        # split the keys over CTAs until the GPU is full: about three CTAs per SM
+        span = ctx.max_context if self.window is None else min(ctx.max_context, self.window + ctx.max_q_len)
+        key_tiles = (span + 63) // 64 + 1
+        max_splits = max(1, min(64, -(-444 // (n_tiles * self.Hkv)), key_tiles // 2))
+        return ops.attention_mma(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, tok0, ntok, wide, self.window,
+                                 self.sinks, max_splits=max_splits, min_tiles=2, scale=self.scale)
 
     def _unfused_position(self, qkv, ctx, write):
         """QK-norm, then a position encoding that is not the fused rotary one, on FP32 q and k."""

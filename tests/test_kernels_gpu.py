@@ -5,6 +5,7 @@ import math
 import pytest
 import torch
 
+import helpers
 import plain_flint as P
 
 pytestmark = pytest.mark.gpu
@@ -287,3 +288,59 @@ def test_gemm_tc_grouped(T, k, E, D, I):
     y_ref = ops.gemm_simt(act, wd, groups=simt_tiles, rows=pairs)
     assert (act.float() - act_ref.float()).abs().max() <= 1e-2 * act_ref.float().abs().max()
     assert (y - y_ref).abs().max() <= 1e-4 * y_ref.abs().max()
+
+
+# --------------------------------------------------------------------------- tensor-core attention
+@pytest.mark.parametrize("Hq,Hkv,hd,ps,window,sinks", [(32, 4, 128, 16, None, False), (8, 2, 64, 8, None, True),
+                                                        (6, 2, 128, 16, 100, True), (16, 1, 64, 32, 37, False),
+                                                        (5, 5, 128, 4, None, False)])
+@pytest.mark.parametrize("mode", ["decode", "portions"])
+def test_attention_mma(Hq, Hkv, hd, ps, window, sinks, mode):
+    """Several requests of different lengths in one launch; decode rows (narrow tiles, keys split
+    over CTAs and merged) or prompt portions (wide tiles); against float64 with one far key made
+    to stand out."""
+    from quench6k_b200 import ops
+    G = Hq // Hkv
+    g = torch.Generator().manual_seed(Hq * 1000 + hd + (window or 0))
+    lens = [700, 150, 333, 64, 65]
+    num_pages = sum(-(-n // ps) for n in lens) + 5
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    kp = torch.full((num_pages, Hkv, ps, hd), float("nan"), dtype=torch.bfloat16)
+    vp = torch.full((num_pages, Hkv, ps, hd), float("nan"), dtype=torch.bfloat16)
+    tables, refs, qs = [], [], []
+    for n in lens:
+        q, k, v = (torch.randn(n, h, hd, generator=g) for h in (Hq, Hkv, Hkv))
+        k[3] *= 3.0
+        q[-20:] += 1.5 * k[3].repeat_interleave(G, 0) / k[3].norm()
+        qd, kd, vd = (x.to(torch.bfloat16) for x in (q, k, v))
+        sk = torch.randn(Hq, generator=g) if sinks else None
+        if sinks and tables:
+            sk = refs[0][1]                                # one sink vector per layer
+        refs.append((P.attention(qd.double(), kd.double(), vd.double(), window, sk.double() if sinks else None, True), sk))
+        table = [perm.pop() for _ in range(-(-n // ps))]
+        for t in range(n):
+            kp[table[t // ps], :, t % ps] = kd[t]
+            vp[table[t // ps], :, t % ps] = vd[t]
+        tables.append(table)
+        qs.append(qd)
+    width = max(len(t) for t in tables)
+    bt = torch.tensor([t + [-1] * (width - len(t)) for t in tables], dtype=torch.int32, device=DEV)
+    sk = refs[0][1].to(DEV) if sinks else None
+    if mode == "decode":
+        q_lens = [min(2, max(1, 16 // G))] * len(lens) if G <= 8 else [1] * len(lens)
+        q_lens[1] = 1
+    else:
+        q_lens = [130, 150, 33, 3, 65]
+    starts = [n - ql for n, ql in zip(lens, q_lens)]
+    ctx = helpers.make_context(q_lens, starts, [tables])
+    q = torch.cat([qs[r][starts[r]:] for r in range(len(lens))]).contiguous().to(DEV)
+    wide = mode == "portions"
+    tok0, ntok, n_tiles = ctx.query_tiles((64 if wide else 16) // G)
+    want = torch.cat([refs[r][0][starts[r]:] for r in range(len(lens))]).reshape(-1, Hq * hd)
+    for max_splits in (1, 4, 64):
+        out = ops.attention_mma(q, kp.to(DEV), vp.to(DEV), bt, ctx.req_of_token, ctx.positions, tok0, ntok, wide, window, sk,
+                                max_splits=max_splits, min_tiles=1)
+        err = (out.double().cpu() - want).abs().max() / want.abs().max()
+        assert err <= 1.5e-2, (max_splits, err)
+    gen = ops.attention_generic(q, kp.to(DEV), vp.to(DEV), bt, ctx.req_of_token, ctx.positions, window, sk)
+    assert (out.float() - gen.float()).abs().max() <= 2e-2 * gen.float().abs().max()

@@ -301,33 +301,34 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
     }
 }
 
-// out[row] = sum_s 2^(m_s - M) o_s / (sum_s 2^(m_s - M) l_s + 2^(sink - M)); one block per (tile, KV head).
+// out[row] = sum_s 2^(m_s - M) o_s / (sum_s 2^(m_s - M) l_s + 2^(sink - M)); one block per (tile, KV head, row of
+// the tile), one thread per head dimension; the splits' values are fetched with independent loads.
 template <int HD>
-__global__ void __launch_bounds__(128) attention_merge_kernel(const AttnParams p) {
-    const int tile = blockIdx.x, kh = blockIdx.y, G = p.G;
+__global__ void __launch_bounds__(HD) attention_merge_kernel(const AttnParams p) {
+    const int tile = blockIdx.x, kh = blockIdx.y, r = blockIdx.z, G = p.G, d = threadIdx.x;
     const int tok0 = p.tile_tok0[tile], ntok = p.tile_ntok[tile];
+    const int tt = r / G, hg = r % G;
+    if (tt >= ntok) return;
     const int pos_first = p.positions[tok0], pos_last = pos_first + ntok - 1;
     const int k_lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
     int per, se;
     split_plan(k_lo / KT, pos_last / KT + 1, p.max_splits, p.min_tiles, per, se);
     if (se == 1) return;                      // the attention kernel wrote the output itself
-    for (int idx = threadIdx.x; idx < ntok * G * HD; idx += blockDim.x) {
-        const int r = idx / HD, d = idx % HD, tt = r / G, hg = r % G;
-        const size_t row = (size_t)(tok0 + tt) * p.Hq + kh * G + hg;
-        const float* ml = p.part_ml + row * p.max_splits * 2;
-        const float* po = p.part_o + row * p.max_splits * HD;
-        const float sk = p.sinks ? p.sinks[kh * G + hg] * LOG2E : -INFINITY;
-        float M = sk;
-        for (int s = 0; s < se; ++s) M = fmaxf(M, ml[s * 2]);
-        float den = p.sinks ? exp2f(sk - M) : 0.0f, num = 0.0f;
-        for (int s = 0; s < se; ++s) {
-            const float ms = ml[s * 2];
-            const float w = ms == -INFINITY ? 0.0f : exp2f(ms - M);
-            den = fmaf(w, ms == -INFINITY ? 0.0f : ml[s * 2 + 1], den);
-            num = fmaf(w, po[(size_t)s * HD + d], num);
-        }
-        p.out[row * HD + d] = __float2bfloat16_rn(num / den);
+    const size_t row = (size_t)(tok0 + tt) * p.Hq + kh * G + hg;
+    const float* ml = p.part_ml + row * p.max_splits * 2;
+    const float* po = p.part_o + row * p.max_splits * HD;
+    const float sk = p.sinks ? p.sinks[kh * G + hg] * LOG2E : -INFINITY;
+    float M = sk;
+    for (int s = 0; s < se; ++s) M = fmaxf(M, ml[s * 2]);
+    float den = p.sinks ? exp2f(sk - M) : 0.0f, num = 0.0f;
+#pragma unroll 8
+    for (int s = 0; s < se; ++s) {
+        const float ms = ml[s * 2];
+        const float w = ms == -INFINITY ? 0.0f : exp2f(ms - M);
+        den = fmaf(w, ms == -INFINITY ? 0.0f : ml[s * 2 + 1], den);
+        num = fmaf(w, po[(size_t)s * HD + d], num);
     }
+    p.out[row * HD + d] = __float2bfloat16_rn(num / den);
 }
 
 template <int HD, bool WIDE>
@@ -345,7 +346,7 @@ int launch(const AttnParams& p, int n_tiles, cudaStream_t st) {
     attention_mma_kernel<HD, WIDE><<<dim3(p.max_splits, p.Hkv, n_tiles), 128, smem, st>>>(p);
     if (int rc = q6k_check_launch("attention_mma")) return rc;
     if (p.max_splits > 1) {
-        attention_merge_kernel<HD><<<dim3(n_tiles, p.Hkv), 128, 0, st>>>(p);
+        attention_merge_kernel<HD><<<dim3(n_tiles, p.Hkv, ROWS), HD, 0, st>>>(p);
         return q6k_check_launch("attention_merge");
     }
     return 0;

@@ -32,12 +32,11 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(const float* x, const int*
 // h[t, d] += sum_s w[t, s] * y[pair_row[t*S + s], d], slots in order (so the result does not
 // depend on where the permutation put the rows).
 __global__ void combine_kernel(const float* y, const int* pair_row, const float* sel_w, int S, int D, float* h) {
-    const int t = blockIdx.x;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float acc = 0.0f;
-        for (int s = 0; s < S; ++s) acc = fmaf(sel_w[t * S + s], y[(size_t)pair_row[t * S + s] * D + d], acc);
-        h[(size_t)t * D + d] += acc;
-    }
+    const int t = blockIdx.x, d = blockIdx.y * blockDim.x + threadIdx.x;
+    if (d >= D) return;
+    float acc = 0.0f;
+    for (int s = 0; s < S; ++s) acc = fmaf(sel_w[t * S + s], y[(size_t)pair_row[t * S + s] * D + d], acc);
+    h[(size_t)t * D + d] += acc;
 }
 
 // act[r, i] = T(silu(g[r, i]) * u[r, i]) for gu = [rows, 2*I] (gate columns first).
@@ -87,7 +86,7 @@ Q6K_API int q6k_combine(const float* y, const int* pair_row, const float* sel_w,
                         cudaStream_t st) {
     if (T_ == 0) return 0;
     Q6K_REQUIRE(T_ > 0 && S > 0 && D > 0, "combine: bad sizes T=%d S=%d D=%d", T_, S, D);
-    combine_kernel<<<T_, 256, 0, st>>>(y, pair_row, sel_w, S, D, h);
+    combine_kernel<<<dim3(T_, (D + 255) / 256), 256, 0, st>>>(y, pair_row, sel_w, S, D, h);
     return q6k_check_launch("combine");
 }
 

@@ -17,16 +17,8 @@ __device__ __forceinline__ unsigned key_of(float v) {
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
-__global__ void __launch_bounds__(1024) argmax_kernel(const float* logits, int V, int* out) {
-    __shared__ unsigned bk[32];
-    __shared__ int bi[32];
-    const float* row = logits + (size_t)blockIdx.x * V;
-    unsigned best = 0u;
-    int best_i = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const unsigned k = key_of(row[i]);
-        if (k > best || (k == best && i < best_i)) best = k, best_i = i;
-    }
+// Best (key, index) of a block's candidates; ties go to the lower index.  Result in thread 0.
+__device__ __forceinline__ void block_best(unsigned& best, int& best_i, unsigned* bk, int* bi) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const unsigned ok = __shfl_xor_sync(0xffffffffu, best, o);
@@ -46,8 +38,43 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const float* logits, int V
             const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
             if (ok > best || (ok == best && oi < best_i)) best = ok, best_i = oi;
         }
-        if (lane == 0) out[blockIdx.x] = best_i;
     }
+}
+
+constexpr int ARGMAX_SLICE = 8192;
+
+// Stage 1: block (slice, row) finds the best of its slice of the row.
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const float* logits, int V, int slices, unsigned* pk, int* pi) {
+    __shared__ unsigned bk[32];
+    __shared__ int bi[32];
+    const float* row = logits + (size_t)blockIdx.y * V;
+    const int lo = blockIdx.x * ARGMAX_SLICE, hi = min(V, lo + ARGMAX_SLICE);
+    unsigned best = 0u;
+    int best_i = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const unsigned k = key_of(row[i]);
+        if (k > best || (k == best && i < best_i)) best = k, best_i = i;
+    }
+    block_best(best, best_i, bk, bi);
+    if (threadIdx.x == 0) pk[blockIdx.y * slices + blockIdx.x] = best, pi[blockIdx.y * slices + blockIdx.x] = best_i;
+}
+
+// Stage 2: one warp per row picks among the slices' winners.
+__global__ void argmax_final_kernel(const unsigned* pk, const int* pi, int slices, int* out) {
+    unsigned best = 0u;
+    int best_i = 0x7fffffff;
+    for (int s = threadIdx.x; s < slices; s += 32) {
+        const unsigned k = pk[blockIdx.x * slices + s];
+        const int i = pi[blockIdx.x * slices + s];
+        if (k > best || (k == best && i < best_i)) best = k, best_i = i;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned ok = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ok > best || (ok == best && oi < best_i)) best = ok, best_i = oi;
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = best_i;
 }
 
 constexpr int POOL_MAX = 256;
@@ -151,10 +178,17 @@ __global__ void __launch_bounds__(1024) topk_pool_kernel(const float* logits, in
 
 }  // namespace
 
-Q6K_API int q6k_argmax(const float* logits, int rows, int V, int* out, cudaStream_t st) {
+Q6K_API int q6k_argmax_scratch_ints(int rows, int V) { return 2 * rows * ((V + ARGMAX_SLICE - 1) / ARGMAX_SLICE); }
+
+// scratch: q6k_argmax_scratch_ints(rows, V) 32-bit words.
+Q6K_API int q6k_argmax(const float* logits, int rows, int V, int* out, void* scratch, cudaStream_t st) {
     if (rows == 0) return 0;
-    Q6K_REQUIRE(rows > 0 && V > 0, "argmax: bad sizes rows=%d V=%d", rows, V);
-    argmax_kernel<<<rows, 1024, 0, st>>>(logits, V, out);
+    Q6K_REQUIRE(rows > 0 && V > 0 && rows <= 65535, "argmax: bad sizes rows=%d V=%d", rows, V);
+    const int slices = (V + ARGMAX_SLICE - 1) / ARGMAX_SLICE;
+    unsigned* pk = (unsigned*)scratch;
+    int* pi = (int*)scratch + (size_t)rows * slices;
+    argmax_partial_kernel<<<dim3(slices, rows), 256, 0, st>>>(logits, V, slices, pk, pi);
+    argmax_final_kernel<<<rows, 32, 0, st>>>(pk, pi, slices, out);
     return q6k_check_launch("argmax");
 }
 

@@ -14,6 +14,7 @@ from typing import Dict, Hashable, List, Optional, Sequence, Union
 import numpy as np
 import torch
 
+from .. import ops
 from ..cache import CacheManager, GroupSpec, OutOfPages
 from ..config.registry import load_config
 from ..models.decoder import DecoderModel
@@ -33,7 +34,7 @@ def parse_dtype(d) -> torch.dtype:
 
 class ModelRunner:
     def __init__(self, model: DecoderModel, rt: Runtime, page_size: int, num_pages: Union[int, Sequence[int]],
-                 max_requests: int):
+                 max_requests: int, cuda_graphs: bool = True):
         if rt.device.type != "cuda":
             raise RuntimeError("the engine runs on a CUDA device only; there is no CPU path")
         self.model, self.rt = model, rt
@@ -72,24 +73,31 @@ class ModelRunner:
                                               torch.zeros(shape, dtype=rt.dtype, device=rt.device), page_size))
         self.states = [None if s is None else torch.zeros((max_requests, *s), dtype=torch.float32, device=rt.device)
                        for s in model.state_shapes()]
+        # decode-only steps (one token per request, its logits wanted) replay a CUDA graph per
+        # (number of requests, block-table widths); the reference captures one per sequence and
+        # token count (crates/engine/src/flint.rs:735-771)
+        self.cuda_graphs = cuda_graphs and model.graph_safe()
+        self._graphs: Dict = {}
+        self.graph_replays = 0
         self._pinned: Optional[torch.Tensor] = None
         self._pinned_free: Optional[torch.cuda.Event] = None      # set once the last upload has left the pinned block
 
     # ------------------------------------------------------------------ construction
     @classmethod
     def from_folder(cls, folder: str, dtype="bfloat16", device="cuda:0", page_size: Optional[int] = None,
-                    num_pages: Union[int, Sequence[int]] = 256, max_requests: int = 64, tensor_cores: bool = True):
+                    num_pages: Union[int, Sequence[int]] = 256, max_requests: int = 64, tensor_cores: bool = True,
+                    cuda_graphs: bool = True):
         arch, cfg = load_config(folder)
         model = DecoderModel(arch.build_spec(cfg))
         rt = Runtime(torch.device(device), parse_dtype(dtype), tensor_cores)
         model.bind(load_folder(folder, model.tensors()), rt)
         ps = page_size or getattr(cfg, "kv_page_size", None) or 16
-        return cls(model, rt, ps, num_pages, max_requests)
+        return cls(model, rt, ps, num_pages, max_requests, cuda_graphs)
 
     @classmethod
     def from_random(cls, cfg, seed: int, dtype="bfloat16", device="cuda:0", page_size: Optional[int] = None,
                     num_pages: Union[int, Sequence[int]] = 256, max_requests: int = 64, tensor_cores: bool = True,
-                    arch=None):
+                    arch=None, cuda_graphs: bool = True):
         """Random weights made on the device from the typed config and a seed (no files)."""
         from ..config.registry import get_architecture
         arch = arch or get_architecture(cfg.architectures[0])
@@ -98,7 +106,7 @@ class ModelRunner:
         rt = Runtime(torch.device(device), parse_dtype(dtype), tensor_cores)
         model.bind(random_getter(model.tensors(), seed, spec.init_std, device=rt.device), rt)
         ps = page_size or getattr(cfg, "kv_page_size", None) or 16
-        return cls(model, rt, ps, num_pages, max_requests)
+        return cls(model, rt, ps, num_pages, max_requests, cuda_graphs)
 
     # ------------------------------------------------------------------ requests
     def add_request(self, rid: Hashable) -> None:
@@ -121,16 +129,18 @@ class ModelRunner:
         return rid in self.manager.requests
 
     # ------------------------------------------------------------------ the step
-    def _context(self, entries: Sequence[StepEntry]) -> StepContext:
+    def _context(self, entries: Sequence[StepEntry], widths: Optional[List[int]] = None,
+                 static: Optional[torch.Tensor] = None) -> StepContext:
+        """The step's description: built on the host in one pinned block, uploaded in one copy
+        (into `static` when given: a device block a CUDA graph reads)."""
         mgr, ps = self.manager, self.page_size
         R = len(entries)
         q_lens = [len(e.tokens) for e in entries]
         T = sum(q_lens)
         pos_starts = [mgr.length(e.rid) for e in entries]
         slots = [mgr.slot(e.rid) for e in entries]
-        widths = []
-        for g in range(len(self.group_specs)):
-            widths.append(max(1, max(len(mgr.table(e.rid, g)) for e in entries)))
+        if widths is None:
+            widths = self._widths(entries)
         n_want = sum(len(e.want) for e in entries)
         total = 3 * T + (R + 1) + 2 * R + n_want + sum(R * w for w in widths)
         if self._pinned_free is not None:
@@ -175,7 +185,9 @@ class ModelRunner:
                 row = mgr.table(e.rid, g)
                 tb[r, :len(row)] = row
             tabs.append((tb, wd))
-        dev = torch.empty(total, dtype=torch.int32, device=self.rt.device)
+        dev = static if static is not None else torch.empty(total, dtype=torch.int32, device=self.rt.device)
+        if dev.numel() != total:
+            raise RuntimeError("the static step block does not match this step's layout")
         dev.copy_(self._pinned[:total], non_blocking=True)
         if self._pinned_free is None:
             self._pinned_free = torch.cuda.Event()
@@ -196,6 +208,42 @@ class ModelRunner:
                            pos_starts=pos_starts, slots=slots,
                            max_context=max(p + n for p, n in zip(pos_starts, q_lens)), max_q_len=max(q_lens))
 
+    def _widths(self, entries: Sequence[StepEntry]) -> List[int]:
+        mgr = self.manager
+        return [max(1, max(len(mgr.table(e.rid, g)) for e in entries)) for g in range(len(self.group_specs))]
+
+    def _forward(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Eager for general steps; decode-only steps go through a CUDA graph per step shape."""
+        decode = self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
+        if not decode:
+            return self.model.forward(self._context(entries), self.caches, self.states)
+        widths = [(w + 63) // 64 * 64 for w in self._widths(entries)]
+        key = (len(entries), tuple(widths))
+        slot = self._graphs.get(key)
+        if slot is None:
+            # first step of this shape: run it eagerly from a static block, then record the same
+            # launches into a graph (recording executes nothing)
+            R = len(entries)
+            total = 3 * R + (R + 1) + 2 * R + R + sum(R * w for w in widths)
+            static = torch.empty(total, dtype=torch.int32, device=self.rt.device)
+            ctx = self._context(entries, widths, static)
+            ctx.max_context = max(widths) * self.page_size          # launch plans must hold for every replay
+            logits = self.model.forward(ctx, self.caches, self.states)
+            result = logits.clone()
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count
+            with torch.cuda.graph(graph):
+                out = self.model.forward(ctx, self.caches, self.states)
+            self._graphs[key] = (graph, ctx, static, out, ops.launch_count - before)
+            return result
+        graph, ctx, static, out, launches = slot
+        self._context(entries, widths, static)
+        graph.replay()
+        self.graph_replays += 1
+        ops.launch_count += launches
+        return out
+
     def can_run(self, entries: Sequence[StepEntry]) -> bool:
         return self.manager.can_reserve([(e.rid, len(e.tokens)) for e in entries])
 
@@ -215,8 +263,7 @@ class ModelRunner:
         for e in entries:
             self.manager.reserve(e.rid, len(e.tokens))
         try:
-            ctx = self._context(entries)
-            logits = self.model.forward(ctx, self.caches, self.states)
+            logits = self._forward(entries)
         except BaseException:
             for e in entries:
                 self.manager.cancel(e.rid)

@@ -64,6 +64,12 @@ class DecoderModel:
         """Per executed position: the shape of its mixer's fixed-size per-request state, or None."""
         return [self.blocks[i].mixer.state_shape() for i in self.order]
 
+    def graph_safe(self) -> bool:
+        parts = [self.final_norm]
+        for b in self.blocks:
+            parts += [b.norm1, b.mixer, b.norm2, b.ffn]
+        return all(getattr(x, "graph_safe", False) for x in parts)
+
     # ------------------------------------------------------------------ weights
     def bind(self, get: Callable[[str], torch.Tensor], rt: Runtime) -> None:
         s = self.spec

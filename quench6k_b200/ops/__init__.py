@@ -49,7 +49,7 @@ def _need(t: torch.Tensor, name: str, dtype=None, shape=None):
 
 
 # kernels launched per exported function (for launch accounting in benchmarks)
-_LAUNCHES = {"q6k_moe_permute": 3, "q6k_gemm_tc": 1, "q6k_attention_mma": 2}
+_LAUNCHES = {"q6k_moe_permute": 3, "q6k_gemm_tc": 1, "q6k_attention_mma": 2, "q6k_argmax": 2}
 launch_count = 0
 
 
@@ -181,7 +181,7 @@ def tile_list(offsets: torch.Tensor, pairs: int, bm: int):
     """(offsets, tile_group, tile_row0, num_tiles) for the groups' row tiles of bm rows."""
     _need(offsets, "offsets", torch.int32)
     G = offsets.numel() - 1
-    max_tiles = (pairs + bm - 1) // bm + G
+    max_tiles = pairs // bm + min(pairs, G)          # full tiles plus at most one ragged tile per non-empty group
     tile_group = torch.empty(max_tiles, dtype=torch.int32, device=offsets.device)
     tile_row0 = torch.empty(max_tiles, dtype=torch.int32, device=offsets.device)
     num_tiles = torch.empty(1, dtype=torch.int32, device=offsets.device)
@@ -223,7 +223,7 @@ _workspaces = {}
 
 
 def _workspace(nbytes: int, device) -> torch.Tensor:
-    key = (str(device), torch.cuda.current_stream().cuda_stream)
+    key = str(device)                     # one scratch buffer per device: the engine runs on one stream
     ws = _workspaces.get(key)
     if ws is None or ws.numel() * 4 < nbytes:
         ws = torch.empty(max(nbytes // 4, 1 << 20), dtype=torch.float32, device=device)
@@ -408,7 +408,10 @@ def argmax(logits: torch.Tensor) -> torch.Tensor:
     _need(logits, "logits", torch.float32)
     rows, V = logits.shape
     out = torch.empty(rows, dtype=torch.int32, device=logits.device)
-    _call("q6k_argmax", _ptr(logits), _i(rows), _i(V), _ptr(out), _stream())
+    lib = library()
+    lib.q6k_argmax_scratch_ints.restype = ctypes.c_int
+    scratch = torch.empty(lib.q6k_argmax_scratch_ints(_i(rows), _i(V)), dtype=torch.int32, device=logits.device)
+    _call("q6k_argmax", _ptr(logits), _i(rows), _i(V), _ptr(out), _ptr(scratch), _stream())
     return out
 
 

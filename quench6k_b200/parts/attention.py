@@ -16,6 +16,8 @@ from .base import (POSITION_ENCODINGS, CacheRequest, Mixer, make_part, register_
 
 @register_mixer("attention")
 class Attention(Mixer):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int, eps: float,
                  pos: PartSpec, window: Optional[int] = None, sinks: bool = False, qk_norm: bool = False,
                  norm_init: str = "ones", sink_std: float = 1.0):

@@ -62,6 +62,12 @@ class LayerCache:
 
 
 class Part:
+    # True if forward() launches the same kernels with the same arguments whenever the step has
+    # the same number of rows and the same block-table widths (everything else read on the device):
+    # such steps may be replayed from a CUDA graph.  Parts that look at the step's host fields
+    # (q_lens, pos_starts, slots) must leave this False.
+    graph_safe = False
+
     def tensors(self) -> List[TensorSpec]:
         return []
 

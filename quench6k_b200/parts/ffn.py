@@ -19,6 +19,8 @@ from .base import FeedForward, register_feed_forward, to_operand
 
 @register_feed_forward("dense")
 class DenseSwiGLU(FeedForward):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.D, self.I = hidden_size, intermediate_size
 
@@ -38,6 +40,8 @@ class DenseSwiGLU(FeedForward):
 
 @register_feed_forward("moe")
 class RoutedExperts(FeedForward):
+    graph_safe = True
+
     def __init__(self, hidden_size: int, num_experts: int, top_k: int, intermediate_size: int, scoring: str = "softmax",
                  renormalize: bool = True, shared_intermediate_size: int = 0):
         if scoring not in ("softmax", "sigmoid"):

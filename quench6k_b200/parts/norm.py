@@ -9,6 +9,8 @@ from .base import Norm, register_norm, to_f32
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
+    graph_safe = True
+
     def __init__(self, size: int, eps: float, init: str = "ones"):
         self.size, self.eps, self.init = size, float(eps), init
 

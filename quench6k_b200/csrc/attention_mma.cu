@@ -13,9 +13,18 @@
 // the key index.  Narrow tiles (decode): the 4 warps share the 16 rows and split each key tile
 // (16 keys each), then merge their partial softmax states through shared memory.  Wide tiles
 // (prompt portions): each warp owns 16 rows and walks all 64 keys of a tile.
-// K and V rows are copied with 16-byte cp.async into a 2-stage ring; chunks are XOR-swizzled by
-// the row so that ldmatrix reads are free of bank conflicts.
+// K and V tiles travel through a ring of shared-memory stages.  With pages of 8 rows or a multiple
+// (the usual case) a producer warp brings each page's [rows x 64] boxes in by TMA (one tensor map
+// over a layer's K or V pool, 128-byte swizzle, zero fill for keys that have no page) and signals
+// the four consumer warps through mbarriers (full: transaction bytes; empty: one arrival per
+// warp); every wait is bounded and records a code in a status word when it runs out.  With other
+// page sizes the consumer warps copy the rows themselves with 16-byte cp.async into two stages.
+// Either way the 16-byte chunks are XOR-swizzled by the row, so ldmatrix reads are conflict-free.
+#include <map>
+#include <tuple>
+
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace {
 
@@ -37,9 +46,10 @@ struct AttnParams {
     float* part_ml;                          // [T*Hq, max_splits, 2]
     int max_blocks, page_size, window, Hq, Hkv, G, max_splits, min_tiles;
     float scale_log2;
+    int pool_rows;                           // rows of the [pages * Hkv * page_size, HD] view of a pool (TMA path)
 };
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ int g_attn_status = 0;
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
     const int n = valid ? 16 : 0;            // 0 source bytes: the 16 destination bytes become zeros
@@ -75,20 +85,28 @@ __device__ __forceinline__ void split_plan(int first_tile, int end_tile, int max
     se = (n + per - 1) / per;
 }
 
-// Byte offset of 16-byte chunk c of row r in a swizzled [rows][HD] bf16 tile.
+// Byte offset of 16-byte chunk c of row r in a swizzled [rows][HD] bf16 tile (the Q tile).
 template <int HD> __device__ __forceinline__ uint32_t sw(int r, int c) { return (uint32_t)(r * HD * 2 + ((c ^ (r & 7)) << 4)); }
+// Byte offset of chunk c of key r in a K or V tile: [HD/64 column halves][64 keys][128 bytes], the
+// layout TMA's 128-byte swizzle produces for boxes that start on multiples of 8 keys.
+__device__ __forceinline__ uint32_t swk(int r, int c) { return (uint32_t)((c >> 3) * (KT * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)); }
 
-template <int HD, bool WIDE>
-__global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) {
+template <int HD, bool WIDE, bool TMA>
+__global__ void __launch_bounds__(TMA ? 160 : 128) attention_mma_kernel(const __grid_constant__ CUtensorMap tm_k,
+                                                                        const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
     constexpr int ROWS = WIDE ? 64 : 16;
     constexpr int CH = HD / 8;               // 16-byte chunks per row
     constexpr int KW = WIDE ? KT : 16;       // keys of a tile this warp handles
     constexpr int NB = KW / 8;               // score n-blocks per warp
     constexpr int DB = HD / 8;               // output n-blocks
     constexpr uint32_t TILE_BYTES = KT * HD * 2;
-    extern __shared__ __align__(128) uint8_t smem[];
-    // [Q: ROWS x HD][K stage 0][K stage 1][V stage 0][V stage 1]
-    const uint32_t q_s = smem_u32(smem), k_s = q_s + ROWS * HD * 2, v_s = k_s + 2 * TILE_BYTES;
+    constexpr int STAGES = TMA ? (HD == 128 ? 3 : 4) : 2;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // [K stage 0 .. S-1][V stage 0 .. S-1][Q: ROWS x HD]; stages start on 1024 bytes (swizzle pattern)
+    const uint32_t k_s = smem_u32(smem), v_s = k_s + STAGES * TILE_BYTES, q_s = v_s + STAGES * TILE_BYTES;
+    __shared__ __align__(8) uint64_t bars[8];
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[4]);
 
     const int tile = blockIdx.z, kh = blockIdx.y, split = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g8 = lane >> 2, t4 = lane & 3;
@@ -103,26 +121,71 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
     if (split >= se) return;
     const int t_begin = first_tile + split * per, t_end = min(end_tile, t_begin + per);
 
-    // ---- Q tile into shared memory (zero rows past the tile's tokens)
-    for (int idx = tid; idx < ROWS * CH; idx += 128) {
-        const int r = idx / CH, c = idx % CH, tt = r / G, hg = r % G;
-        const bool valid = tt < ntok;
-        const __nv_bfloat16* src = p.q + ((size_t)(tok0 + (valid ? tt : 0)) * p.Hq + kh * G + hg) * HD + c * 8;
-        cp_async16(q_s + sw<HD>(r, c), src, valid);
+    if (TMA && tid == 0) {
+        for (int s2 = 0; s2 < STAGES; ++s2) {
+            mbar_init(full0 + 8 * s2, 1);
+            mbar_init(empty0 + 8 * s2, 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_v) : "memory");
     }
-    auto load_kv = [&](int stage, int kt) {
+    // ---- Q tile into shared memory (zero rows past the tile's tokens)
+    if (warp < 4) {
+        for (int idx = tid; idx < ROWS * CH; idx += 128) {
+            const int r = idx / CH, c = idx % CH, tt = r / G, hg = r % G;
+            const bool valid = tt < ntok;
+            const __nv_bfloat16* src = p.q + ((size_t)(tok0 + (valid ? tt : 0)) * p.Hq + kh * G + hg) * HD + c * 8;
+            cp_async16(q_s + sw<HD>(r, c), src, valid);
+        }
+    }
+    auto load_kv = [&](int stage, int kt) {      // the cp.async path: every consumer thread copies its chunks
         for (int idx = tid; idx < KT * CH; idx += 128) {
             const int r = idx / CH, c = idx % CH, j = kt * KT + r;
             const bool in = j >= k_lo && j <= pos_last;
             int page = in ? bt[j / p.page_size] : -1;
             const bool valid = page >= 0;
             const size_t off = valid ? (((size_t)page * p.Hkv + kh) * p.page_size + j % p.page_size) * HD + c * 8 : 0;
-            cp_async16(k_s + stage * TILE_BYTES + sw<HD>(r, c), p.k_pages + off, valid);
-            cp_async16(v_s + stage * TILE_BYTES + sw<HD>(r, c), p.v_pages + off, valid);
+            cp_async16(k_s + stage * TILE_BYTES + swk(r, c), p.k_pages + off, valid);
+            cp_async16(v_s + stage * TILE_BYTES + swk(r, c), p.v_pages + off, valid);
         }
     };
-    load_kv(0, t_begin);
+    if (!TMA) load_kv(0, t_begin);
     cp_async_commit();
+    cp_async_wait<0>();
+    __syncthreads();
+
+    if (TMA && warp == 4) {
+        // ---- producer: one thread brings every tile of this CTA's key range into the ring
+        if (lane == 0) {
+            const int ps = p.page_size, box = ps < KT ? ps : KT;        // keys per TMA box
+            for (int i = 0; i < t_end - t_begin; ++i) {
+                const int s2 = i % STAGES;
+                if (!mbar_wait(empty0 + 8 * s2, ((i / STAGES) & 1) ^ 1)) {
+                    atomicExch(&g_attn_status, 1);
+                    break;
+                }
+                const uint32_t fb = full0 + 8 * s2;
+                mbar_expect_tx(fb, 2 * TILE_BYTES);
+                const int j0 = (t_begin + i) * KT;
+                for (int b = 0; b < KT / box; ++b) {
+                    const int j = j0 + b * box;
+                    int y = p.pool_rows;                                 // out of range: the box is filled with zeros
+                    if (j + box > k_lo && j <= pos_last) {
+                        const int page = bt[j / ps];
+                        if (page >= 0) y = (page * p.Hkv + kh) * ps + j % ps;
+                    }
+#pragma unroll
+                    for (int h = 0; h < HD / 64; ++h) {
+                        const uint32_t off = s2 * TILE_BYTES + h * (KT * 128) + b * box * 128;
+                        tma_load_2d(k_s + off, &tm_k, h * 64, y, fb);
+                        tma_load_2d(v_s + off, &tm_v, h * 64, y, fb);
+                    }
+                }
+            }
+        }
+        return;
+    }
 
     // this thread's two rows (g8 and g8 + 8 of the warp's 16) and their key limits
     const int rbase = WIDE ? warp * 16 : 0, koff = WIDE ? 0 : warp * 16;
@@ -139,16 +202,29 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
 #pragma unroll
     for (int n = 0; n < DB; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
 
-    cp_async_wait<0>();
-    __syncthreads();
     uint32_t qa[HD / 16][4];
 #pragma unroll
     for (int ks = 0; ks < HD / 16; ++ks) ldmatrix_x4(qa[ks], q_s + sw<HD>(rbase + (lane & 15), ks * 2 + (lane >> 4)));
 
     for (int kt = t_begin; kt < t_end; ++kt) {
-        const int stage = (kt - t_begin) & 1;
-        if (kt + 1 < t_end) load_kv(stage ^ 1, kt + 1);
-        cp_async_commit();
+        const int it = kt - t_begin, stage = it % STAGES;
+        if (TMA) {
+            if (!mbar_wait(full0 + 8 * stage, (it / STAGES) & 1)) {
+                if (lane == 0) atomicExch(&g_attn_status, 2);
+                break;
+            }
+            if (kt == end_tile - 1 && (pos_last + 1) % KT != 0) {
+                // the last page came in whole: rows past the last key hold whatever the page held
+                // before (masked scores ignore K, but 0 * V must not meet a stale NaN): clear them
+                const int r0 = pos_last + 1 - kt * KT;
+                for (int idx = r0 * CH + tid; idx < KT * CH; idx += 128)
+                    *reinterpret_cast<uint4*>(smem + (v_s - k_s) + stage * TILE_BYTES + swk(idx / CH, idx % CH)) = make_uint4(0, 0, 0, 0);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+            }
+        } else {
+            if (kt + 1 < t_end) load_kv(stage ^ 1, kt + 1);
+            cp_async_commit();
+        }
         const uint32_t kb = k_s + stage * TILE_BYTES, vb = v_s + stage * TILE_BYTES;
         const int j0 = kt * KT + koff;
         // ---- S = Q K^T for this warp's keys
@@ -161,7 +237,7 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
             for (int nj = 0; nj < NB / 2; ++nj) {
                 uint32_t b[4];
                 const int key = koff + nj * 16 + ((lane >> 4) << 3) + (lane & 7);
-                ldmatrix_x4(b, kb + sw<HD>(key, ks * 2 + ((lane >> 3) & 1)));
+                ldmatrix_x4(b, kb + swk(key, ks * 2 + ((lane >> 3) & 1)));
                 mma_bf16(s[2 * nj], qa[ks], b[0], b[1]);
                 mma_bf16(s[2 * nj + 1], qa[ks], b[2], b[3]);
             }
@@ -209,13 +285,18 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
             for (int dj = 0; dj < DB / 2; ++dj) {
                 uint32_t b[4];
                 const int key = koff + ks * 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
-                ldmatrix_x4_trans(b, vb + sw<HD>(key, dj * 2 + (lane >> 4)));
+                ldmatrix_x4_trans(b, vb + swk(key, dj * 2 + (lane >> 4)));
                 mma_bf16(o[2 * dj], pa[ks], b[0], b[1]);
                 mma_bf16(o[2 * dj + 1], pa[ks], b[2], b[3]);
             }
         }
-        cp_async_wait<0>();
-        __syncthreads();
+        if (TMA) {
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty0 + 8 * stage);
+        } else {
+            cp_async_wait<0>();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
     }
     // row sums live per thread: add the quad's
 #pragma unroll
@@ -227,6 +308,7 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
     // ---- results: (m, l, o) per row; narrow tiles first merge the 4 warps' key subsets
     float* red = reinterpret_cast<float*>(smem);             // reuse the tile ring (all loads have landed, all reads are done)
     if (!WIDE) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");         // every consumer warp is past its last tile
         // red: [4 warps][16 rows][HD + 2]
         constexpr int LD = HD + 2;
 #pragma unroll
@@ -239,7 +321,7 @@ __global__ void __launch_bounds__(128) attention_mma_kernel(const AttnParams p) 
                 dst[n * 8 + 2 * t4 + 1] = o[n][hr * 2 + 1];
             }
         }
-        __syncthreads();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
         // 128 threads: row = tid / 8, 8 threads share a row's HD values
         const int r = tid >> 3, sub = tid & 7, tt = r / G, hg = r % G;
         if (tt >= ntok) return;
@@ -331,25 +413,49 @@ __global__ void __launch_bounds__(HD) attention_merge_kernel(const AttnParams p)
     p.out[row * HD + d] = __float2bfloat16_rn(num / den);
 }
 
-template <int HD, bool WIDE>
-int launch(const AttnParams& p, int n_tiles, cudaStream_t st) {
+// Tensor maps over the K and V pools of a layer do not change: keep them by (address, rows, box).
+std::mutex g_pool_mutex;
+std::map<std::tuple<const void*, long long, int, int>, CUtensorMap> g_pool_maps;
+
+int pool_map(CUtensorMap* out, const void* base, long long rows, int hd, int box_rows) {
+    std::lock_guard<std::mutex> lock(g_pool_mutex);
+    auto key = std::make_tuple(base, rows, hd, box_rows);
+    auto it = g_pool_maps.find(key);
+    if (it == g_pool_maps.end()) {
+        CUtensorMap m;
+        if (int rc = make_bf16_map(&m, base, rows, hd, hd, box_rows, true, "attention_mma")) return rc;
+        it = g_pool_maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return 0;
+}
+
+template <int HD, bool WIDE, bool TMA>
+int launch(const AttnParams& p, const CUtensorMap& tk, const CUtensorMap& tv, int n_tiles, cudaStream_t st) {
     constexpr int ROWS = WIDE ? 64 : 16;
-    const size_t ring = ROWS * HD * 2 + 4 * KT * HD * 2;
+    constexpr int STAGES = TMA ? (HD == 128 ? 3 : 4) : 2;
+    const size_t ring = 2 * STAGES * KT * HD * 2 + ROWS * HD * 2;
     const size_t red = WIDE ? 0 : 4 * 16 * (HD + 2) * sizeof(float);
-    const size_t smem = ring > red ? ring : red;
+    const size_t smem = (ring > red ? ring : red) + 1024;
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(attention_mma_kernel<HD, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(attention_mma_kernel<HD, WIDE, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return q6k_check_launch("attention_mma: shared memory attribute");
         configured = true;
     }
-    attention_mma_kernel<HD, WIDE><<<dim3(p.max_splits, p.Hkv, n_tiles), 128, smem, st>>>(p);
+    attention_mma_kernel<HD, WIDE, TMA><<<dim3(p.max_splits, p.Hkv, n_tiles), TMA ? 160 : 128, smem, st>>>(tk, tv, p);
     if (int rc = q6k_check_launch("attention_mma")) return rc;
     if (p.max_splits > 1) {
         attention_merge_kernel<HD><<<dim3(n_tiles, p.Hkv, ROWS), HD, 0, st>>>(p);
         return q6k_check_launch("attention_merge");
     }
     return 0;
+}
+
+template <int HD>
+int launch_hd(const AttnParams& p, const CUtensorMap& tk, const CUtensorMap& tv, bool wide, bool tma, int n_tiles, cudaStream_t st) {
+    if (tma) return wide ? launch<HD, true, true>(p, tk, tv, n_tiles, st) : launch<HD, false, true>(p, tk, tv, n_tiles, st);
+    return wide ? launch<HD, true, false>(p, tk, tv, n_tiles, st) : launch<HD, false, false>(p, tk, tv, n_tiles, st);
 }
 
 }  // namespace
@@ -360,8 +466,15 @@ Q6K_API int q6k_attention_mma_supported(int hd, int G, int wide) { return (hd ==
 // q: bfloat16 [T, Hq, hd]; pages: bfloat16 [*, Hkv, page_size, hd]; tiles: tile_tok0/tile_ntok [n_tiles], the
 // tokens of a tile being consecutive positions of one request, at most (wide ? 64 : 16) / G of them.
 // part_o: FP32 [T*Hq*max_splits*hd], part_ml: FP32 [T*Hq*max_splits*2] (unused when max_splits == 1).
-Q6K_API int q6k_attention_mma(const void* q, const void* k_pages, const void* v_pages, const int* block_table, int max_blocks,
-                              int page_size, const int* req_of_token, const int* positions, const int* tile_tok0,
+Q6K_API int q6k_attention_status() {
+    int v = -1;
+    if (cudaMemcpyFromSymbol(&v, g_attn_status, sizeof v) != cudaSuccess) return -1;
+    return v;
+}
+
+// num_pages: pages in each pool (the TMA path addresses a pool as one [num_pages * Hkv * page_size, hd] matrix).
+Q6K_API int q6k_attention_mma(const void* q, const void* k_pages, const void* v_pages, long long num_pages, const int* block_table,
+                              int max_blocks, int page_size, const int* req_of_token, const int* positions, const int* tile_tok0,
                               const int* tile_ntok, int n_tiles, int wide, int window, const float* sinks, float scale, void* out,
                               float* part_o, float* part_ml, int max_splits, int min_tiles, int Hq, int Hkv, int hd,
                               cudaStream_t st) {
@@ -380,6 +493,16 @@ Q6K_API int q6k_attention_mma(const void* q, const void* k_pages, const void* v_
     p.part_o = part_o, p.part_ml = part_ml;
     p.max_blocks = max_blocks, p.page_size = page_size, p.window = window, p.Hq = Hq, p.Hkv = Hkv, p.G = G;
     p.max_splits = max_splits, p.min_tiles = min_tiles, p.scale_log2 = scale * LOG2E;
-    if (hd == 128) return wide ? launch<128, true>(p, n_tiles, st) : launch<128, false>(p, n_tiles, st);
-    return wide ? launch<64, true>(p, n_tiles, st) : launch<64, false>(p, n_tiles, st);
+    // pages of 8, 16, 32, 64 keys (or whole multiples of 64) are boxes TMA can place on the swizzle pattern
+    const long long pool_rows = num_pages * Hkv * page_size;
+    const bool tma = page_size % 8 == 0 && (KT % page_size == 0 || page_size % KT == 0) && pool_rows < (1LL << 31) &&
+                     ((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0;
+    CUtensorMap tk{}, tv{};
+    if (tma) {
+        const int box = page_size < KT ? page_size : KT;
+        p.pool_rows = (int)pool_rows;
+        if (int rc = pool_map(&tk, k_pages, pool_rows, hd, box)) return rc;
+        if (int rc = pool_map(&tv, v_pages, pool_rows, hd, box)) return rc;
+    }
+    return hd == 128 ? launch_hd<128>(p, tk, tv, wide, tma, n_tiles, st) : launch_hd<64>(p, tk, tv, wide, tma, n_tiles, st);
 }

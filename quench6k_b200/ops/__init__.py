@@ -216,7 +216,8 @@ def tc_status() -> int:
     """0, or the code of a bounded wait that ran out inside a tensor-core kernel (synchronises)."""
     lib = library()
     lib.q6k_tc_status.restype = ctypes.c_int
-    return lib.q6k_tc_status()
+    lib.q6k_attention_status.restype = ctypes.c_int
+    return lib.q6k_tc_status() or lib.q6k_attention_status()
 
 
 _workspaces = {}
@@ -365,7 +366,8 @@ def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
         ws = _workspace(T * Hq * max_splits * (hd + 2) * 4, q.device)
         part_o = ws[: T * Hq * max_splits * hd]
         part_ml = ws[T * Hq * max_splits * hd: T * Hq * max_splits * (hd + 2)]
-    _call("q6k_attention_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), _i(block_table.shape[1]), _i(page_size),
+    _call("q6k_attention_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ll(k_pages.shape[0]), _ptr(block_table),
+          _i(block_table.shape[1]), _i(page_size),
           _ptr(req_of_token), _ptr(positions), _ptr(tile_tok0), _ptr(tile_ntok), _i(n_tiles), _i(1 if wide else 0), _i(window or 0),
           _ptr(sinks), _f(scale if scale is not None else 1.0 / math.sqrt(hd)), _ptr(out), _ptr(part_o), _ptr(part_ml),
           _i(max_splits), _i(min_tiles), _i(Hq), _i(Hkv), _i(hd), _stream())

@@ -20,6 +20,8 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
+import numpy as np
+
 
 class OutOfPages(RuntimeError):
     """A pool cannot supply the pages a step needs.  Nothing was allocated."""
@@ -101,11 +103,40 @@ class SlotPool:
         self._free.append(slot)
 
 
+class BlockTable:
+    """Pages of one request in one group by logical block: a growable int32 array.  Blocks
+    [0, first_held) were given back (-1); blocks [first_held, len) hold a page each."""
+
+    __slots__ = ("buf", "n", "first_held")
+
+    def __init__(self):
+        self.buf = np.full(16, -1, dtype=np.int32)
+        self.n = 0
+        self.first_held = 0
+
+    def __len__(self) -> int:
+        return self.n
+
+    def append(self, page: int) -> None:
+        if self.n == len(self.buf):
+            grown = np.full(2 * len(self.buf), -1, dtype=np.int32)
+            grown[:self.n] = self.buf[:self.n]
+            self.buf = grown
+        self.buf[self.n] = page
+        self.n += 1
+
+    def array(self) -> np.ndarray:
+        return self.buf[:self.n]
+
+    def tolist(self) -> List[int]:
+        return self.buf[:self.n].tolist()
+
+
 @dataclass
 class _Request:
     slot: int
     length: int                         # tokens whose keys are in the cache
-    tables: List[List[int]]             # per group: page of each logical block, -1 where none
+    tables: List[BlockTable]            # per group
     reserved: int = 0                   # tokens of the step in flight (pages held, not yet counted in length)
 
 
@@ -127,16 +158,15 @@ class CacheManager:
         if rid in self.requests:
             raise KeyError(f"request {rid!r} is already live")
         slot = self.slots.take()
-        self.requests[rid] = _Request(slot, 0, [[] for _ in self.groups])
+        self.requests[rid] = _Request(slot, 0, [BlockTable() for _ in self.groups])
         return slot
 
     def remove(self, rid: Hashable) -> None:
         """The request ended (finished, aborted or preempted): every page and the slot go back."""
         req = self.requests.pop(rid)
         for g, table in enumerate(req.tables):
-            for page in reversed(table):
-                if page >= 0:
-                    self.pools[g].give_back(page, rid)
+            for page in reversed(table.tolist()[table.first_held:]):
+                self.pools[g].give_back(page, rid)
         self.slots.give_back(req.slot)
 
     def length(self, rid: Hashable) -> int:
@@ -146,7 +176,15 @@ class CacheManager:
         return self.requests[rid].slot
 
     def table(self, rid: Hashable, group: int) -> List[int]:
-        return self.requests[rid].tables[group]
+        """Pages by logical block as a list (-1 where none is held)."""
+        return self.requests[rid].tables[group].tolist()
+
+    def table_array(self, rid: Hashable, group: int) -> np.ndarray:
+        """The same as an int32 array view (valid until the request's next reserve)."""
+        return self.requests[rid].tables[group].array()
+
+    def table_len(self, rid: Hashable, group: int) -> int:
+        return len(self.requests[rid].tables[group])
 
     # ------------------------------------------------------------------ pages for a step
     def _first_needed_block(self, g: int, start: int) -> int:
@@ -157,19 +195,18 @@ class CacheManager:
         return max(0, start - spec.window + 1) // self.page_size
 
     def pages_needed(self, rid: Hashable, n_new: int) -> List[int]:
-        """Pages each group's pool must supply so that the request can run n_new more tokens."""
+        """Pages each group's pool must supply so that the request can run n_new more tokens.
+        A table holds a page for every block from the first one the next step reads up to its
+        end (full groups never give pages back early; a sliding group gives back exactly the
+        blocks below the next step's first block), so the need is the blocks past the table's end."""
         req = self.requests[rid]
-        start, end = req.length, req.length + n_new
+        end = req.length + n_new
+        last = (end - 1) // self.page_size if end > 0 else -1
         out = []
         for g in range(len(self.groups)):
             table = req.tables[g]
-            first = self._first_needed_block(g, start)
-            last = (end - 1) // self.page_size if end > 0 else -1
-            need = 0
-            for b in range(first, last + 1):
-                if b >= len(table) or table[b] < 0:
-                    need += 1
-            out.append(need)
+            assert self._first_needed_block(g, req.length) >= table.first_held, "a block the next step reads was given back"
+            out.append(max(0, last + 1 - len(table)))
         return out
 
     def can_reserve(self, wants: Sequence[Tuple[Hashable, int]]) -> bool:
@@ -190,16 +227,12 @@ class CacheManager:
             if c > self.pools[g].num_free:
                 raise OutOfPages(f"group {g} ({self.groups[g].kind}) needs {c} pages for request {rid!r}, "
                                  f"{self.pools[g].num_free} are free")
-        start, end = req.length, req.length + n_new
+        end = req.length + n_new
+        last = (end - 1) // self.page_size if end > 0 else -1
         for g in range(len(self.groups)):
             table = req.tables[g]
-            first = self._first_needed_block(g, start)
-            last = (end - 1) // self.page_size if end > 0 else -1
             while len(table) <= last:
-                table.append(-1)
-            for b in range(first, last + 1):
-                if table[b] < 0:
-                    table[b] = self.pools[g].take(rid)
+                table.append(self.pools[g].take(rid))
         req.reserved = n_new
 
     def commit(self, rid: Hashable) -> None:
@@ -213,10 +246,10 @@ class CacheManager:
             # the next query sits at position `length` and sees keys > length - window
             dead = max(0, req.length - spec.window + 1) // self.page_size     # blocks [0, dead) lie wholly below
             table = req.tables[g]
-            for b in range(min(dead, len(table))):
-                if table[b] >= 0:
-                    self.pools[g].give_back(table[b], rid)
-                    table[b] = -1
+            for b in range(table.first_held, min(dead, len(table))):
+                self.pools[g].give_back(int(table.buf[b]), rid)
+                table.buf[b] = -1
+            table.first_held = max(table.first_held, min(dead, len(table)))
 
     def cancel(self, rid: Hashable) -> None:
         """The step in flight did not run: pages taken for it stay with the request (they are
@@ -228,7 +261,9 @@ class CacheManager:
         for g, pool in enumerate(self.pools):
             held = {}
             for rid, req in self.requests.items():
-                for b, page in enumerate(req.tables[g]):
+                tab = req.tables[g]
+                for b, page in enumerate(tab.tolist()):
+                    assert (page < 0) == (b < tab.first_held), f"group {g}: request {rid!r} block {b} page {page} first_held {tab.first_held}"
                     if page < 0:
                         continue
                     assert page not in held, f"group {g}: page {page} held by {held[page]} and {(rid, b)}"

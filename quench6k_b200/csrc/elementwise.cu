@@ -16,14 +16,25 @@ __global__ void embed_kernel(const int* tokens, const T* table, float* h, int D,
 
 // out[r] = T(x[row] * rsqrt(mean(x[row]^2) + eps) * w), row = rows ? rows[r] : r.  Sum of squares,
 // rsqrt and the products are FP32; the per-thread partial sums and the block sum run in a fixed order.
+// With `add`, x[row] += add[r] first and the sum is written back (the residual add of the block,
+// folded in as the reference does, crates/cuda/kernels/flint.cu:97-122).
 template <typename T>
-__global__ void __launch_bounds__(256) rmsnorm_kernel(const float* x, const int* rows, const float* w, float eps,
+__global__ void __launch_bounds__(256) rmsnorm_kernel(float* x, const float* add, const int* rows, const float* w, float eps,
                                                       T* out, int D) {
     __shared__ float red[32];
     const int r = blockIdx.x;
-    const float* xr = x + (size_t)(rows ? rows[r] : r) * D;
+    float* xr = x + (size_t)(rows ? rows[r] : r) * D;
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
+    if (add) {
+        const float* ar = add + (size_t)r * D;
+        for (int i = threadIdx.x; i < D; i += blockDim.x) {
+            const float v = xr[i] + ar[i];
+            xr[i] = v;                         // each thread re-reads only what it wrote itself
+            ss = fmaf(v, v, ss);
+        }
+    } else {
+        for (int i = threadIdx.x; i < D; i += blockDim.x) ss = fmaf(xr[i], xr[i], ss);
+    }
     ss = block_sum(ss, red);
     const float inv = rsqrtf(ss / (float)D + eps);
     for (int i = threadIdx.x; i < D; i += blockDim.x) out[(size_t)r * D + i] = from_f32<T>(xr[i] * inv * w[i]);
@@ -74,11 +85,13 @@ Q6K_API int q6k_embed(const int* tokens, const void* table, float* h, int T_, in
     return q6k_check_launch("embed");
 }
 
-Q6K_API int q6k_rmsnorm(const float* x, const int* rows, const float* w, float eps, void* out, int R, int D, int dtype,
+// add: FP32 [R, D] or null; when given, x[row] += add[r] is stored before normalising (rows must then be null).
+Q6K_API int q6k_rmsnorm(float* x, const float* add, const int* rows, const float* w, float eps, void* out, int R, int D, int dtype,
                         cudaStream_t st) {
     if (R == 0) return 0;
     Q6K_REQUIRE(R > 0 && D > 0, "rmsnorm: bad sizes R=%d D=%d", R, D);
-    Q6K_DISPATCH(dtype, rmsnorm_kernel<T><<<R, 256, 0, st>>>(x, rows, w, eps, (T*)out, D););
+    Q6K_REQUIRE(!(add && rows), "rmsnorm: the fused add takes no row selection");
+    Q6K_DISPATCH(dtype, rmsnorm_kernel<T><<<R, 256, 0, st>>>(x, add, rows, w, eps, (T*)out, D););
     return q6k_check_launch("rmsnorm");
 }
 

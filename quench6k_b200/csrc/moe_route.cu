@@ -67,32 +67,40 @@ __global__ void route_kernel(const float* logits, int T_, int E, int k, int sigm
     }
 }
 
-// One warp per expert: counts[e] and, for each pair p with sel_e[p] == e, rank[p] = number of
-// earlier pairs of the same expert.
-__global__ void count_rank_kernel(const int* sel_e, int pairs, int E, int* counts, int* rank) {
+constexpr int PERM_CHUNK = 1024;           // pairs per chunk of the permutation kernels
+
+// One warp per (expert, chunk of pairs): how many pairs of the chunk chose the expert.
+__global__ void count_kernel(const int* sel_e, int pairs, int E, int* counts) {
     const int lane = threadIdx.x & 31;
-    const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), c = blockIdx.y;
     if (e >= E) return;
-    int base = 0;
-    for (int p0 = 0; p0 < pairs; p0 += 32) {
+    const int lo = c * PERM_CHUNK, hi = min(pairs, lo + PERM_CHUNK);
+    int n = 0;
+    for (int p0 = lo; p0 < hi; p0 += 32) {
         const int p = p0 + lane;
-        const bool hit = p < pairs && sel_e[p] == e;
-        const unsigned mask = __ballot_sync(0xffffffffu, hit);
-        if (hit) rank[p] = base + __popc(mask & ((1u << lane) - 1u));
-        base += __popc(mask);
+        n += __popc(__ballot_sync(0xffffffffu, p < hi && sel_e[p] == e));
     }
-    if (lane == 0) counts[e] = base;
+    if (lane == 0) counts[c * E + e] = n;
 }
 
-// offsets = exclusive scan of counts (E + 1 entries), in expert order.  One block.
-__global__ void offsets_kernel(const int* counts, int E, int* offsets) {
+// counts[c, e] -> the chunk's first row within its expert (in place), and offsets = exclusive
+// scan over the experts of their totals (E + 1 entries).  One block.
+__global__ void offsets_kernel(int* counts, int chunks, int E, int* offsets) {
     __shared__ int part[1024];
     const int tid = threadIdx.x, n = blockDim.x;
     const int per = (E + n - 1) / n;
     int sum = 0;
     for (int i = 0; i < per; ++i) {
         const int e = tid * per + i;
-        if (e < E) sum += counts[e];
+        if (e >= E) break;
+        int run = 0;
+        for (int c = 0; c < chunks; ++c) {
+            const int v = counts[c * E + e];
+            counts[c * E + e] = run;
+            run += v;
+        }
+        offsets[e] = run;                      // the expert's total, replaced by its offset below
+        sum += run;
     }
     part[tid] = sum;
     __syncthreads();
@@ -109,21 +117,33 @@ __global__ void offsets_kernel(const int* counts, int E, int* offsets) {
     int run = part[tid];
     for (int i = 0; i < per; ++i) {
         const int e = tid * per + i;
-        if (e < E) {
-            offsets[e] = run;
-            run += counts[e];
-        }
+        if (e >= E) break;
+        const int total = offsets[e];
+        offsets[e] = run;
+        run += total;
     }
 }
 
-// pair_row[p] = offsets[sel_e[p]] + rank[p]; row_token[pair_row[p]] = p / k.
-__global__ void scatter_kernel(const int* sel_e, const int* rank, const int* offsets, int pairs, int k, int* pair_row,
-                               int* row_token) {
-    const int p = blockIdx.x * blockDim.x + threadIdx.x;
-    if (p >= pairs) return;
-    const int row = offsets[sel_e[p]] + rank[p];
-    pair_row[p] = row;
-    row_token[row] = p / k;
+// One warp per (expert, chunk): the row of each of its pairs is the expert's offset plus the
+// number of earlier pairs of the same expert; row_token[row] = pair / k.
+__global__ void rank_kernel(const int* sel_e, const int* chunk_base, const int* offsets, int pairs, int k, int E, int* pair_row,
+                            int* row_token) {
+    const int lane = threadIdx.x & 31;
+    const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), c = blockIdx.y;
+    if (e >= E) return;
+    const int lo = c * PERM_CHUNK, hi = min(pairs, lo + PERM_CHUNK);
+    int base = offsets[e] + chunk_base[c * E + e];
+    for (int p0 = lo; p0 < hi; p0 += 32) {
+        const int p = p0 + lane;
+        const bool hit = p < hi && sel_e[p] == e;
+        const unsigned mask = __ballot_sync(0xffffffffu, hit);
+        if (hit) {
+            const int row = base + __popc(mask & ((1u << lane) - 1u));
+            pair_row[p] = row;
+            row_token[row] = p / k;
+        }
+        base += __popc(mask);
+    }
 }
 
 }  // namespace
@@ -139,13 +159,18 @@ Q6K_API int q6k_route(const float* logits, int T_, int E, int k, int sigmoid, in
     return q6k_check_launch("route");
 }
 
-// counts: [E], rank: [pairs], offsets: [E+1], pair_row: [pairs], row_token: [pairs]; all int32.
-Q6K_API int q6k_moe_permute(const int* sel_e, int pairs, int k, int E, int* counts, int* rank, int* offsets, int* pair_row,
-                            int* row_token, cudaStream_t st) {
+Q6K_API int q6k_moe_permute_scratch_ints(int pairs, int E) { return ((pairs + PERM_CHUNK - 1) / PERM_CHUNK) * E; }
+
+// scratch: q6k_moe_permute_scratch_ints(pairs, E) ints; offsets: [E+1], pair_row: [pairs], row_token: [pairs]; all int32.
+Q6K_API int q6k_moe_permute(const int* sel_e, int pairs, int k, int E, int* scratch, int* offsets, int* pair_row, int* row_token,
+                            cudaStream_t st) {
     if (pairs == 0) return 0;
     Q6K_REQUIRE(pairs > 0 && k > 0 && E > 0, "moe_permute: bad sizes pairs=%d k=%d E=%d", pairs, k, E);
-    count_rank_kernel<<<(E + 7) / 8, 256, 0, st>>>(sel_e, pairs, E, counts, rank);
-    offsets_kernel<<<1, 256, 0, st>>>(counts, E, offsets);
-    scatter_kernel<<<(pairs + 255) / 256, 256, 0, st>>>(sel_e, rank, offsets, pairs, k, pair_row, row_token);
+    const int chunks = (pairs + PERM_CHUNK - 1) / PERM_CHUNK;
+    Q6K_REQUIRE(chunks <= 65535, "moe_permute: %d pairs exceed the grid limit", pairs);
+    const dim3 grid((E + 7) / 8, chunks);
+    count_kernel<<<grid, 256, 0, st>>>(sel_e, pairs, E, scratch);
+    offsets_kernel<<<1, 256, 0, st>>>(scratch, chunks, E, offsets);
+    rank_kernel<<<grid, 256, 0, st>>>(sel_e, scratch, offsets, pairs, k, E, pair_row, row_token);
     return q6k_check_launch("moe_permute");
 }

@@ -52,6 +52,63 @@ __global__ void qk_prep_kernel(const float* qkv, int ld, int Hq, int Hkv, int hd
     }
 }
 
+// The same for head sizes that are multiples of 64: one warp per (token, head), each lane holding
+// head_dim/32 elements d = lane + 32 i, so both elements of every rotation pair (d, d + head_dim/2)
+// sit in one lane and nothing goes through shared memory.  Block = 8 warps = 8 heads of one token.
+template <typename T, int EPL>
+__global__ void __launch_bounds__(256) qk_prep_warp_kernel(const float* qkv, int ld, int Hq, int Hkv, const float* q_norm,
+                                                           const float* k_norm, float eps, int rope, float log2_theta,
+                                                           const int* positions, const int* req_of_token, const int* block_table,
+                                                           int max_blocks, int page_size, T* q_out, T* k_pages, T* v_pages,
+                                                           int heads) {
+    constexpr int hd = EPL * 32, half = hd / 2;
+    const int t = blockIdx.x, h = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (h >= heads) return;
+    const bool is_q = h < Hq;
+    const int pos = positions[t];
+    const float* src = qkv + (size_t)t * ld + (size_t)h * hd;           // q heads then k heads are contiguous in a row
+    float x[EPL], ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+        x[i] = src[lane + 32 * i];
+        ss = fmaf(x[i], x[i], ss);
+    }
+    const float* nw = is_q ? q_norm : k_norm;
+    if (nw) {
+        const float inv = rsqrtf(warp_sum(ss) / (float)hd + eps);
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) x[i] = x[i] * inv * nw[lane + 32 * i];
+    }
+    if (rope) {
+#pragma unroll
+        for (int i = 0; i < EPL / 2; ++i) {
+            const int d = lane + 32 * i;                                 // d < half; partner d + half is element i + EPL/2
+            const float inv = exp2f(-(float)(2 * d) / (float)hd * log2_theta);
+            float sn, cs;
+            sincosf((float)pos * inv, &sn, &cs);
+            const float lo = x[i], hi = x[i + EPL / 2];
+            x[i] = lo * cs - hi * sn;
+            x[i + EPL / 2] = hi * cs + lo * sn;
+        }
+    }
+    if (is_q) {
+        T* dst = q_out + ((size_t)t * Hq + h) * hd;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) dst[lane + 32 * i] = from_f32<T>(x[i]);
+    } else {
+        const int kh = h - Hq;
+        const int page = block_table[(size_t)req_of_token[t] * max_blocks + pos / page_size];
+        if (page < 0) return;
+        const size_t row = (((size_t)page * Hkv + kh) * page_size + pos % page_size) * hd;
+        const float* vsrc = qkv + (size_t)t * ld + (size_t)(Hq + Hkv + kh) * hd;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            k_pages[row + lane + 32 * i] = from_f32<T>(x[i]);
+            v_pages[row + lane + 32 * i] = from_f32<T>(vsrc[lane + 32 * i]);
+        }
+    }
+}
+
 }  // namespace
 
 // qkv: FP32 [T, ld] with q heads, then k heads, then v heads in each row.  q_norm/k_norm: FP32 [hd]
@@ -66,9 +123,24 @@ Q6K_API int q6k_qk_prep(const float* qkv, int ld, int T_, int Hq, int Hkv, int h
     Q6K_REQUIRE(hd % 2 == 0 && hd <= 1024, "qk_prep: head_dim %d must be even and at most 1024", hd);
     Q6K_REQUIRE(!rope || theta > 0.0f, "qk_prep: rope base %g must be positive", theta);
     Q6K_REQUIRE(!write_kv || (page_size > 0 && max_blocks > 0), "qk_prep: bad page_size %d / max_blocks %d", page_size, max_blocks);
-    const int threads = (hd + 31) / 32 * 32;
-    dim3 grid(T_, write_kv ? Hq + Hkv : Hq);
     const float l2t = rope ? log2f(theta) : 0.0f;
+    const int heads = write_kv ? Hq + Hkv : Hq;
+    if (hd == 64 || hd == 128 || hd == 256) {
+        dim3 wgrid(T_, (heads + 7) / 8);
+        Q6K_REQUIRE(wgrid.y <= 65535, "qk_prep: %d heads exceed the grid limit", heads);
+#define WARP_LAUNCH(EPL)                                                                                                    \
+    qk_prep_warp_kernel<T, EPL><<<wgrid, 256, 0, st>>>(qkv, ld, Hq, Hkv, q_norm, k_norm, eps, rope, l2t, positions, req_of_token, \
+                                                       block_table, max_blocks, page_size, (T*)q_out, (T*)k_pages, (T*)v_pages, heads)
+        Q6K_DISPATCH(dtype, {
+            if (hd == 64) WARP_LAUNCH(2);
+            else if (hd == 128) WARP_LAUNCH(4);
+            else WARP_LAUNCH(8);
+        });
+#undef WARP_LAUNCH
+        return q6k_check_launch("qk_prep");
+    }
+    const int threads = (hd + 31) / 32 * 32;
+    dim3 grid(T_, heads);
     Q6K_DISPATCH(dtype, qk_prep_kernel<T><<<grid, threads, hd * sizeof(float), st>>>(
                             qkv, ld, Hq, Hkv, hd, q_norm, k_norm, eps, rope, l2t, positions, req_of_token, block_table,
                             max_blocks, page_size, (T*)q_out, (T*)k_pages, (T*)v_pages););

@@ -182,7 +182,7 @@ class ModelRunner:
             tb = take(R * wd).reshape(R, wd)
             tb[:] = -1
             for r, e in enumerate(entries):
-                row = mgr.table(e.rid, g)
+                row = mgr.table_array(e.rid, g)
                 tb[r, :len(row)] = row
             tabs.append((tb, wd))
         dev = static if static is not None else torch.empty(total, dtype=torch.int32, device=self.rt.device)
@@ -210,7 +210,7 @@ class ModelRunner:
 
     def _widths(self, entries: Sequence[StepEntry]) -> List[int]:
         mgr = self.manager
-        return [max(1, max(len(mgr.table(e.rid, g)) for e in entries)) for g in range(len(self.group_specs))]
+        return [max(1, max(mgr.table_len(e.rid, g) for e in entries)) for g in range(len(self.group_specs))]
 
     def _forward(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Eager for general steps; decode-only steps go through a CUDA graph per step shape."""

@@ -50,6 +50,19 @@ class Request:
         return self.prompt + self.output
 
     @property
+    def num_tokens(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+    def token_slice(self, start: int, count: int) -> List[int]:
+        """tokens[start:start+count] without building the whole list."""
+        n = len(self.prompt)
+        if start >= n:
+            return self.output[start - n:start - n + count]
+        if start + count <= n:
+            return self.prompt[start:start + count]
+        return self.prompt[start:] + self.output[:start + count - n]
+
+    @property
     def finished(self) -> bool:
         return self.finish_reason is not None
 
@@ -71,7 +84,7 @@ class ScheduledStep:
     def step_entries(self) -> List[StepEntry]:
         out = []
         for e in self.entries:
-            toks = e.request.tokens[e.start:e.start + e.count]
+            toks = e.request.token_slice(e.start, e.count)
             out.append(StepEntry(e.request.rid, toks, [e.count - 1] if e.samples else []))
         return out
 
@@ -157,7 +170,7 @@ class Scheduler:
         budget = self.max_batch_tokens
         # 1. decode tokens; preempt from the back until they fit
         while True:
-            decoding = [r for r in self.running if r.num_computed == len(r.tokens) - 1 and r.output]
+            decoding = [r for r in self.running if r.num_computed == r.num_tokens - 1 and r.output]
             decoding = decoding[:budget]
             wants = [(r.rid, 1) for r in decoding]
             if self.manager.can_reserve(wants):
@@ -181,7 +194,7 @@ class Scheduler:
                 break
             if r.rid in in_step:
                 continue
-            left = len(r.tokens) - r.num_computed
+            left = r.num_tokens - r.num_computed
             n = self._fit(chosen, r.rid, min(left, budget))
             if n <= 0:
                 continue
@@ -193,7 +206,7 @@ class Scheduler:
         while self.waiting and budget > 0 and len(self.running) < self.max_running and self.manager.slots.num_free > 0:
             r = self.waiting[0]
             self._admit(r.rid)
-            left = len(r.tokens)
+            left = r.num_tokens
             n = self._fit(chosen, r.rid, min(left, budget))
             if n <= 0:
                 self._release(r.rid)
@@ -237,7 +250,7 @@ class Scheduler:
                 self._finish(r, FINISH_STOP)
             elif len(r.output) >= r.params.max_tokens:
                 self._finish(r, FINISH_LENGTH)
-            elif len(r.tokens) + 1 > self.capacity_tokens():
+            elif r.num_tokens + 1 > self.capacity_tokens():
                 self._finish(r, FINISH_LENGTH)
             if r.finished:
                 done.append(r)

@@ -85,8 +85,9 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor]
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
-            out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """out[r] = out_dtype(x[row] * rsqrt(mean(x[row]^2) + eps) * w); row = rows[r] if given."""
+            out: Optional[torch.Tensor] = None, add: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r] = out_dtype(x[row] * rsqrt(mean(x[row]^2) + eps) * w); row = rows[r] if given.
+    With `add` (float32, x's shape), x += add is stored first: the block's residual add, fused."""
     _need(x, "x", torch.float32)
     D = x.shape[-1]
     _need(w, "w", torch.float32, (D,))
@@ -96,7 +97,9 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype
     if out is None:
         out = torch.empty((R, D), dtype=out_dtype, device=x.device)
     _need(out, "out", out_dtype, (R, D))
-    _call("q6k_rmsnorm", _ptr(x), _ptr(rows), _ptr(w), _f(eps), _ptr(out), _i(R), _i(D), _i(dtype_code(out_dtype)), _stream())
+    if add is not None:
+        _need(add, "add", torch.float32, x.shape)
+    _call("q6k_rmsnorm", _ptr(x), _ptr(add), _ptr(rows), _ptr(w), _f(eps), _ptr(out), _i(R), _i(D), _i(dtype_code(out_dtype)), _stream())
     return out
 
 
@@ -394,12 +397,13 @@ def moe_permute(sel_e: torch.Tensor, E: int):
     T, k = sel_e.shape
     pairs = T * k
     dev = sel_e.device
-    counts = torch.empty(E, dtype=torch.int32, device=dev)
-    rank = torch.empty(pairs, dtype=torch.int32, device=dev)
+    lib = library()
+    lib.q6k_moe_permute_scratch_ints.restype = ctypes.c_int
+    scratch = torch.empty(lib.q6k_moe_permute_scratch_ints(_i(pairs), _i(E)), dtype=torch.int32, device=dev)
     offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
     pair_row = torch.empty((T, k), dtype=torch.int32, device=dev)
     row_token = torch.empty(pairs, dtype=torch.int32, device=dev)
-    _call("q6k_moe_permute", _ptr(sel_e), _i(pairs), _i(k), _i(E), _ptr(counts), _ptr(rank), _ptr(offsets), _ptr(pair_row),
+    _call("q6k_moe_permute", _ptr(sel_e), _i(pairs), _i(k), _i(E), _ptr(scratch), _ptr(offsets), _ptr(pair_row),
           _ptr(row_token), _stream())
     return offsets, pair_row, row_token
 

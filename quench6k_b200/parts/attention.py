@@ -74,7 +74,7 @@ class Attention(Mixer):
                             ctx.req_of_token, table if write else None, cache.page_size, cache.k if write else None,
                             cache.v if write else None, rt.dtype)
         a = self._attend(q, cache, table, ctx)
-        linear.matmul(a, self.w_o, rt, out=out, accumulate=True)
+        return linear.matmul(a, self.w_o, rt)              # the block adds it into the stream inside its next norm
 
     def _attend(self, q, cache, table, ctx):
         """Tensor-core kernel for bfloat16 where it covers the head and group size, else the generic one."""

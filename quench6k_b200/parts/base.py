@@ -7,12 +7,14 @@ No part knows which model it is in.
 To add a part, subclass the matching base, implement the methods below and register the class
 under a name with the matching `register_*`; a spec.PartSpec(kind=name, params=...) then selects it.
 
-  Norm            tensors(); bind(); forward(h_f32 [T, D], rows=None) -> [R, D] in the operand dtype
+  Norm            tensors(); bind(); forward(h_f32 [T, D], rows=None, add=None) -> [R, D] in the operand dtype;
+                  with `add` (float32 [T, D]) it first stores h += add (the block's residual add, fused)
   PositionEncoding  fused_rope_theta() -> float | None (None: not the fused rotary);
                   apply(x_f32 [T, H, hd], positions_i32 [T]) -> None, in place (used when not fused)
   Mixer           tensors(); bind(); cache_request() -> CacheRequest | None; state_shape() -> tuple | None;
                   forward(xn [T, D], ctx: StepContext, cache: LayerCache | None, state: Tensor | None, out_f32 [T, D])
-                  adds its result into `out`
+                  adds its result into `out` and returns None, or leaves `out` alone and returns the
+                  float32 [T, D] result for the block to add
   FeedForward     tensors(); bind(); forward(xn [T, D], ctx, out_f32 [T, D]) adds its result into `out`
   Block           built from (norm1, mixer, norm2, ffn); forward(h, ctx, cache, state)
 """
@@ -77,7 +79,7 @@ class Part:
 
 
 class Norm(Part):
-    def forward(self, h: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, h: torch.Tensor, rows: Optional[torch.Tensor] = None, add: Optional[torch.Tensor] = None) -> torch.Tensor:
         raise NotImplementedError
 
 
@@ -97,7 +99,7 @@ class Mixer(Part):
         """Shape of this mixer's fixed-size per-request state (float32), or None."""
         return None
 
-    def forward(self, xn, ctx, cache: Optional[LayerCache], state: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    def forward(self, xn, ctx, cache: Optional[LayerCache], state: Optional[torch.Tensor], out: torch.Tensor) -> Optional[torch.Tensor]:
         raise NotImplementedError
 
 

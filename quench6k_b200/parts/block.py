@@ -9,6 +9,6 @@ from .base import Block, register_block
 class PreNormBlock(Block):
     def forward(self, h, ctx, cache, state):
         xn = self.norm1.forward(h)
-        self.mixer.forward(xn, ctx, cache, state, h)
-        xn = self.norm2.forward(h)
+        delta = self.mixer.forward(xn, ctx, cache, state, h)
+        xn = self.norm2.forward(h, add=delta)           # h += delta inside the norm when the mixer returned its result
         self.ffn.forward(xn, ctx, h)

@@ -22,5 +22,5 @@ class RMSNorm(Norm):
         self.rt = rt
         self.weight = to_f32(get("weight"), rt)
 
-    def forward(self, h, rows=None):
-        return ops.rmsnorm(h, self.weight, self.eps, self.rt.dtype, rows=rows)
+    def forward(self, h, rows=None, add=None):
+        return ops.rmsnorm(h, self.weight, self.eps, self.rt.dtype, rows=rows, add=add)

@@ -39,6 +39,11 @@ def test_rmsnorm(dtype, R, D, eps):
     rows = torch.tensor([R - 1, 0, 2], dtype=torch.int32, device=DEV)
     sel = ops.rmsnorm(x, w, eps, dtype, rows=rows)
     assert torch.equal(sel, out[rows.long()])
+    add = _t(R, D, seed=3)
+    x2 = x.clone()
+    fused = ops.rmsnorm(x2, w, eps, dtype, add=add)
+    assert torch.equal(x2, x + add)
+    assert torch.equal(fused, ops.rmsnorm(x + add, w, eps, dtype))
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -159,7 +164,8 @@ def test_attention_generic(dtype, Hq, Hkv, hd, ps, window, sinks):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("Hq,Hkv,hd,ps,norm,theta", [(4, 2, 16, 4, False, 10000.0), (6, 3, 48, 8, True, 500000.0),
-                                                      (2, 1, 128, 16, True, None)])
+                                                      (2, 1, 128, 16, True, None), (32, 4, 128, 16, True, 1e6),
+                                                      (5, 5, 64, 8, False, 10000.0), (3, 1, 256, 16, True, 777.0)])
 def test_qk_prep(dtype, Hq, Hkv, hd, ps, norm, theta):
     from quench6k_b200 import ops
     T, eps = 21, 1e-5

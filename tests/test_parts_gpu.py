@@ -85,10 +85,13 @@ def test_attention_part_over_pages(dtype, window, sinks, qk_norm, rope):
     cache = LayerCache(0, torch.zeros(16, Hkv, ps, hd, dtype=dtype, device=DEV), torch.zeros(16, Hkv, ps, hd, dtype=dtype, device=DEV), ps)
     tables = [[[9, 2, 14, 5, 0], [7, 3, 11]]]
     # step 1: the first 13 tokens of request 0; step 2: its last 6 beside all of request 1
-    out1 = torch.zeros(13, D, device=DEV)
-    att.forward(xs[0][:13].to(DEV), helpers.make_context([13], [0], [[tables[0][0]]]), cache, None, out1)
-    out2 = torch.zeros(6 + 11, D, device=DEV)
-    att.forward(torch.cat([xs[0][13:], xs[1]]).to(DEV), helpers.make_context([6, 11], [13, 0], tables), cache, None, out2)
+    def run(x, ctx):
+        out = torch.zeros(x.shape[0], D, device=DEV)
+        delta = att.forward(x.to(DEV), ctx, cache, None, out)       # a mixer adds into `out` or returns its result
+        return out if delta is None else delta
+
+    out1 = run(xs[0][:13], helpers.make_context([13], [0], [[tables[0][0]]]))
+    out2 = run(torch.cat([xs[0][13:], xs[1]]), helpers.make_context([6, 11], [13, 0], tables))
     got = [torch.cat([out1, out2[:6]]).double().cpu(), out2[6:].double().cpu()]
     for r, n in enumerate(lens):
         x = xs[r].double()

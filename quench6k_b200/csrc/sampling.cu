@@ -5,6 +5,7 @@
 // exact device top-k delivers to the host (crates/cli/src/flint.rs:339-353, topk.cu:28-146).
 // Both are kept: the pool comes back sorted by (logit descending, id ascending).
 #include "common.cuh"
+#include "no_alloc.h"
 
 namespace {
 
@@ -199,4 +200,42 @@ Q6K_API int q6k_topk_pool(const float* logits, int rows, int V, int K, int* ids,
     Q6K_REQUIRE(K >= 1 && K <= POOL_MAX && K <= V, "topk_pool: K=%d outside 1..min(%d, V=%d)", K, POOL_MAX, V);
     topk_pool_kernel<<<rows, 1024, 0, st>>>(logits, V, K, ids, vals);
     return q6k_check_launch("topk_pool");
+}
+
+// ---------------------------------------------------------------------------------------------
+// The variant that allocates nothing (see no_alloc.h).  The scratch of the two-pass argmax sits in
+// the library's device image; host code may not use the array's name as a device pointer, so the
+// address is fetched once per device and handed to the kernels.
+namespace {
+
+constexpr int NOALLOC_SLICES = (Q6K_NOALLOC_MAX_VOCAB + ARGMAX_SLICE - 1) / ARGMAX_SLICE;
+static __device__ __align__(256) unsigned g_noalloc_scratch[2 * Q6K_NOALLOC_MAX_ROWS * NOALLOC_SLICES];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+void* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};       // device address of the array, per device, once looked up
+
+}  // namespace
+
+Q6K_API int q6k_argmax_noalloc(const float* logits, int rows, int vocab, int* out, cudaStream_t st) {
+    if (rows == 0) return 0;
+    Q6K_REQUIRE(rows > 0 && vocab > 0, "argmax_noalloc: bad sizes rows=%d vocab=%d", rows, vocab);
+    Q6K_REQUIRE(rows <= Q6K_NOALLOC_MAX_ROWS, "argmax_noalloc: %d rows exceed the built-in scratch for %d rows", rows, Q6K_NOALLOC_MAX_ROWS);
+    Q6K_REQUIRE(vocab <= Q6K_NOALLOC_MAX_VOCAB, "argmax_noalloc: vocabulary %d exceeds the built-in scratch for %d", vocab,
+                Q6K_NOALLOC_MAX_VOCAB);
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES)
+        return q6k_fail("argmax_noalloc: cannot tell the current device (or its index %d is beyond %d)", dev, NOALLOC_MAX_DEVICES - 1);
+    if (!g_noalloc_ptr[dev]) {
+        // first call on this device: the symbol's address in this device's copy of the image
+        void* ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess || !ptr) return q6k_fail("argmax_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+        g_noalloc_ptr[dev] = ptr;
+    }
+    const int slices = (vocab + ARGMAX_SLICE - 1) / ARGMAX_SLICE;
+    unsigned* pk = (unsigned*)g_noalloc_ptr[dev];
+    int* pi = (int*)g_noalloc_ptr[dev] + (size_t)rows * slices;
+    argmax_partial_kernel<<<dim3(slices, rows), 256, 0, st>>>(logits, vocab, slices, pk, pi);
+    argmax_final_kernel<<<rows, 32, 0, st>>>(pk, pi, slices, out);
+    return q6k_check_launch("argmax_noalloc");
 }

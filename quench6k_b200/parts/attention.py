@@ -85,12 +85,24 @@ class Attention(Mixer):
         if not ops.attention_mma_supported(self.hd, G, wide):
             return ops.attention_generic(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, self.window, self.sinks, self.scale)
         tok0, ntok, n_tiles = ctx.query_tiles((64 if wide else 16) // G)
-        # split the keys over CTAs until the GPU is full: about three CTAs per SM
+        # split the keys over CTAs until the GPU is full, and no further: one wave of resident CTAs
+        # (a second, partly filled wave would cost as much as a full one)
         span = ctx.max_context if self.window is None else min(ctx.max_context, self.window + ctx.max_q_len)
         key_tiles = (span + 63) // 64 + 1
-        max_splits = max(1, min(64, -(-444 // (n_tiles * self.Hkv)), key_tiles // 2))
+        max_splits = max(1, min(64, self._resident_ctas(wide) // (n_tiles * self.Hkv), key_tiles // 2))
         return ops.attention_mma(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, tok0, ntok, wide, self.window,
                                  self.sinks, max_splits=max_splits, min_tiles=2, scale=self.scale)
+
+    def _resident_ctas(self, wide: bool) -> int:
+        """CTAs of the tensor-core attention kernel that fit on the GPU at once (shared memory bound)."""
+        key = ("resident", wide)
+        if key not in self.__dict__:
+            props = torch.cuda.get_device_properties(self.rt.device)
+            stages = 3 if self.hd == 128 else 4
+            smem = 2 * stages * 64 * self.hd * 2 + (64 if wide else 16) * self.hd * 2 + 2048
+            per_sm = max(1, min(2 if self.hd == 128 else 3, (props.shared_memory_per_multiprocessor - 1024) // smem))
+            self.__dict__[key] = per_sm * props.multi_processor_count
+        return self.__dict__[key]
 
     def _unfused_position(self, qkv, ctx, write):
         """QK-norm, then a position encoding that is not the fused rotary one, on FP32 q and k."""

@@ -41,13 +41,55 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(float* x, const float* add
 }
 
 // h[t, d] += sum_s w[t, s] * y[pair_row[t*S + s], d], slots in order (so the result does not
-// depend on where the permutation put the rows).
+// depend on where the permutation put the rows).  pair_row == null: rows are in pair order.
 __global__ void combine_kernel(const float* y, const int* pair_row, const float* sel_w, int S, int D, float* h) {
     const int t = blockIdx.x, d = blockIdx.y * blockDim.x + threadIdx.x;
     if (d >= D) return;
     float acc = 0.0f;
-    for (int s = 0; s < S; ++s) acc = fmaf(sel_w[t * S + s], y[(size_t)pair_row[t * S + s] * D + d], acc);
+    for (int s = 0; s < S; ++s) acc = fmaf(sel_w[t * S + s], y[(size_t)(pair_row ? pair_row[t * S + s] : t * S + s) * D + d], acc);
     h[(size_t)t * D + d] += acc;
+}
+
+// The same with the row held in registers (D <= 256 * 4 * V4, D a multiple of 4): one pass over
+// the row, 16-byte loads.  `add_splits` > 1: add is [add_splits, R, D] and its slices are summed in
+// order first (the split-K partials of the product that feeds the residual add).
+template <typename T, int V4>
+__global__ void __launch_bounds__(256) rmsnorm_reg_kernel(float* x, const float* add, int add_splits, size_t add_stride, const int* rows,
+                                                          const float* w, float eps, T* out, int D) {
+    __shared__ float red[32];
+    const int r = blockIdx.x, nv = D >> 2;
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)(rows ? rows[r] : r) * D);
+    float4 v[V4];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < V4; ++i) {
+        const int c = threadIdx.x + 256 * i;
+        if (c < nv) {
+            v[i] = xr[c];
+            if (add) {
+                float4 a = reinterpret_cast<const float4*>(add + (size_t)r * D)[c];
+                for (int s = 1; s < add_splits; ++s) {
+                    const float4 b = reinterpret_cast<const float4*>(add + s * add_stride + (size_t)r * D)[c];
+                    a.x += b.x, a.y += b.y, a.z += b.z, a.w += b.w;
+                }
+                v[i].x += a.x, v[i].y += a.y, v[i].z += a.z, v[i].w += a.w;
+                xr[c] = v[i];
+            }
+            ss = fmaf(v[i].x, v[i].x, ss), ss = fmaf(v[i].y, v[i].y, ss), ss = fmaf(v[i].z, v[i].z, ss), ss = fmaf(v[i].w, v[i].w, ss);
+        }
+    }
+    ss = block_sum(ss, red);
+    const float inv = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+    for (int i = 0; i < V4; ++i) {
+        const int c = threadIdx.x + 256 * i;
+        if (c < nv) {
+            const float4 g = reinterpret_cast<const float4*>(w)[c];
+            T* o = out + (size_t)r * D + 4 * c;
+            o[0] = from_f32<T>(v[i].x * inv * g.x), o[1] = from_f32<T>(v[i].y * inv * g.y);
+            o[2] = from_f32<T>(v[i].z * inv * g.z), o[3] = from_f32<T>(v[i].w * inv * g.w);
+        }
+    }
 }
 
 // act[r, i] = T(silu(g[r, i]) * u[r, i]) for gu = [rows, 2*I] (gate columns first).
@@ -86,11 +128,25 @@ Q6K_API int q6k_embed(const int* tokens, const void* table, float* h, int T_, in
 }
 
 // add: FP32 [R, D] or null; when given, x[row] += add[r] is stored before normalising (rows must then be null).
-Q6K_API int q6k_rmsnorm(float* x, const float* add, const int* rows, const float* w, float eps, void* out, int R, int D, int dtype,
-                        cudaStream_t st) {
+// add_splits > 1: add is [add_splits, R, D] (slices add_stride floats apart), summed in order.
+Q6K_API int q6k_rmsnorm(float* x, const float* add, int add_splits, long long add_stride, const int* rows, const float* w, float eps,
+                        void* out, int R, int D, int dtype, cudaStream_t st) {
     if (R == 0) return 0;
     Q6K_REQUIRE(R > 0 && D > 0, "rmsnorm: bad sizes R=%d D=%d", R, D);
     Q6K_REQUIRE(!(add && rows), "rmsnorm: the fused add takes no row selection");
+    Q6K_REQUIRE(add_splits >= 1, "rmsnorm: bad split count %d", add_splits);
+    const bool vec = D % 4 == 0 && D <= 256 * 4 * 4 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && (!add || ((uintptr_t)add & 15) == 0) &&
+                     (add_stride % 4 == 0);
+    if (vec) {
+        const int v4 = (D / 4 + 255) / 256;
+        Q6K_DISPATCH(dtype, {
+            if (v4 <= 1) rmsnorm_reg_kernel<T, 1><<<R, 256, 0, st>>>(x, add, add_splits, (size_t)add_stride, rows, w, eps, (T*)out, D);
+            else if (v4 <= 2) rmsnorm_reg_kernel<T, 2><<<R, 256, 0, st>>>(x, add, add_splits, (size_t)add_stride, rows, w, eps, (T*)out, D);
+            else rmsnorm_reg_kernel<T, 4><<<R, 256, 0, st>>>(x, add, add_splits, (size_t)add_stride, rows, w, eps, (T*)out, D);
+        });
+        return q6k_check_launch("rmsnorm");
+    }
+    Q6K_REQUIRE(add_splits == 1, "rmsnorm: summing split partials needs a width that is a multiple of 4 and at most 4096 (got %d)", D);
     Q6K_DISPATCH(dtype, rmsnorm_kernel<T><<<R, 256, 0, st>>>(x, add, rows, w, eps, (T*)out, D););
     return q6k_check_launch("rmsnorm");
 }

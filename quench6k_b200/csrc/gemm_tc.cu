@@ -47,6 +47,7 @@ struct Params {
     const int* num_tiles;
     int rows_total, N, K, ldo;
     int epilogue, stages, kb_per_split;
+    int pair_div;                      // > 0: one tile per (token, slot) pair, see q6k_gemm_tc_pairs
 };
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) with the
@@ -93,12 +94,21 @@ template <int BT, bool DUAL>
 __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_w2,
                                                        const __grid_constant__ CUtensorMap tm_a, const Params p) {
     // which tile
-    int g = 0, row0 = blockIdx.y * BT, row_end = p.rows_total;
-    if (p.tile_group) {
+    int g = 0, row0 = blockIdx.y * BT, row_end = p.rows_total, out0 = row0;
+    if (p.pair_div > 0) {
+        // tile y is pair y: its expert's weights, the single input row y / pair_div, the output row y
+        g = p.tile_group[blockIdx.y];
+        row0 = blockIdx.y / p.pair_div;
+        row_end = row0 + 1;
+        out0 = blockIdx.y;
+    } else if (p.tile_group) {
         if ((int)blockIdx.y >= *p.num_tiles) return;
         g = p.tile_group[blockIdx.y];
         row0 = p.tile_row0[blockIdx.y];
         row_end = p.group_offsets[g + 1];
+        out0 = row0;
+    } else {
+        out0 = row0;
     }
     if (row0 >= row_end) return;
     const int n0 = blockIdx.x * WM;
@@ -205,7 +215,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
                     for (int j = 0; j < 16; ++j) {
                         const int t = c0 + j;
                         if (t >= valid) break;
-                        const size_t row = (size_t)(row0 + t);
+                        const size_t row = (size_t)(out0 + t);
                         if (p.epilogue == EPI_STORE) {
                             ((float*)p.out)[row * p.ldo + n] = v[j];
                         } else if (p.epilogue == EPI_ADD) {
@@ -302,8 +312,13 @@ static int splits_for(int rows, int N, int K, int bt) {
     if (ctas >= 120 || kb < 4) return 1;
     int s = (240 + ctas - 1) / ctas;
     if (s > kb / 2) s = kb / 2;
-    return s < 1 ? 1 : s;
+    if (s < 1) s = 1;
+    const int per = (kb + s - 1) / s;          // k-blocks per slice; the slices that are not empty:
+    return (kb + per - 1) / per;
 }
+
+// Number of K slices the dense call below uses for (rows, N, K).
+Q6K_API int q6k_gemm_tc_splits(int rows, int N, int K) { return splits_for(rows, N, K, q6k_tc_token_tile(rows, 0)); }
 
 Q6K_API long long q6k_gemm_tc_workspace(int rows, int N, int K) {
     const int bt = q6k_tc_token_tile(rows, 0);
@@ -315,11 +330,13 @@ Q6K_API long long q6k_gemm_tc_workspace(int rows, int N, int K) {
 // bfloat16 [groups, N, K] contiguous.  epilogue: 0 store FP32, 1 add into FP32, 2 SwiGLU -> bfloat16.
 // Grouped when tile_group != null: bt is the token tile the tile list was made for.  Dense calls
 // may split K over CTAs when the output has too few tiles to fill the GPU; they then need
-// `workspace` of q6k_gemm_tc_workspace bytes.
+// `workspace` of q6k_gemm_tc_workspace bytes.  keep_partials != 0: when K is split, the partial
+// products stay in the workspace as FP32 [q6k_gemm_tc_splits, rows, N] for the caller's next
+// kernel to sum (in slice order) and `out` is not written.
 Q6K_API int q6k_gemm_tc(const void* A, long long lda, int rows_total, const void* W, const void* W2, int groups, int N, int K,
                         void* out, int ldo, int epilogue, const int* tile_group, const int* tile_row0,
                         const int* group_offsets, const int* num_tiles, int max_tiles, int bt, float* workspace,
-                        long long workspace_bytes, cudaStream_t st) {
+                        long long workspace_bytes, int keep_partials, cudaStream_t st) {
     if (rows_total == 0 || N == 0) return 0;
     Q6K_REQUIRE(rows_total > 0 && N > 0 && K > 0 && groups > 0, "gemm_tc: bad sizes rows=%d N=%d K=%d groups=%d", rows_total, N, K, groups);
     Q6K_REQUIRE(K % 8 == 0 && lda % 8 == 0, "gemm_tc: K=%d and the row pitch %lld must be multiples of 8 (TMA rows start on 16 bytes)", K, lda);
@@ -371,11 +388,40 @@ Q6K_API int q6k_gemm_tc(const void* A, long long lda, int rows_total, const void
     }
 #undef GO
     if (rc) return rc;
-    if (splits > 1) {
+    if (splits > 1 && !keep_partials) {
         const size_t count = (size_t)rows_total * N;
         splitk_reduce_kernel<<<(unsigned)((count + 255) / 256), 256, 0, st>>>(workspace, splits, count, (float*)out, N, ldo,
                                                                              epilogue == EPI_ADD);
         return q6k_check_launch("gemm_tc split-K reduce");
     }
     return 0;
+}
+
+// Few tokens (decode): one tile per (token, slot) pair instead of a permutation.  pair_expert:
+// int32 [pairs] (the router's selection, flattened); pair y multiplies input row y / pair_div of A
+// (pair_div = slots per token for the gate/up product, 1 for the down product, whose input rows
+// are already per pair) with the weights of expert pair_expert[y] and writes output row y.
+// epilogue: 0 store FP32, 2 SwiGLU -> bfloat16.
+Q6K_API int q6k_gemm_tc_pairs(const void* A, long long lda, int a_rows, const void* W, const void* W2, int groups, int N, int K,
+                              void* out, int ldo, int epilogue, const int* pair_expert, int pairs, int pair_div, cudaStream_t st) {
+    if (pairs == 0 || N == 0) return 0;
+    Q6K_REQUIRE(a_rows > 0 && N > 0 && K > 0 && groups > 0 && pairs > 0 && pair_div > 0, "gemm_tc_pairs: bad sizes rows=%d N=%d K=%d pairs=%d", a_rows, N, K, pairs);
+    Q6K_REQUIRE(K % 8 == 0 && lda % 8 == 0, "gemm_tc_pairs: K=%d and the row pitch %lld must be multiples of 8", K, lda);
+    Q6K_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0 && (!W2 || ((uintptr_t)W2 & 15) == 0), "gemm_tc_pairs: operands must be 16-byte aligned");
+    Q6K_REQUIRE(epilogue == EPI_STORE || epilogue == EPI_SWIGLU, "gemm_tc_pairs: unknown epilogue %d", epilogue);
+    const bool dual = epilogue == EPI_SWIGLU;
+    Q6K_REQUIRE(!dual || W2, "gemm_tc_pairs: the SwiGLU epilogue needs two weight matrices");
+    Q6K_REQUIRE(pairs <= 65535 && (long long)groups * N < (1LL << 31), "gemm_tc_pairs: too many pairs or weight rows");
+    CUtensorMap tw, tw2, ta;
+    if (int rc = weight_map(&tw, W, (long long)groups * N, K)) return rc;
+    tw2 = tw;
+    if (dual)
+        if (int rc = weight_map(&tw2, W2, (long long)groups * N, K)) return rc;
+    if (int rc = make_map(&ta, A, a_rows, K, lda, 16, false)) return rc;
+    Params p{};
+    p.out = out, p.tile_group = pair_expert, p.rows_total = a_rows, p.N = N, p.K = K, p.ldo = ldo, p.epilogue = epilogue;
+    p.kb_per_split = (K + BK - 1) / BK;
+    p.pair_div = pair_div;
+    dim3 grid((N + WM - 1) / WM, pairs, 1);
+    return dual ? launch<16, true>(tw, tw2, ta, p, grid, st) : launch<16, false>(tw, tw2, ta, p, grid, st);
 }

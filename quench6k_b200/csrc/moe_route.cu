@@ -67,6 +67,128 @@ __global__ void route_kernel(const float* logits, int T_, int E, int k, int sigm
     }
 }
 
+// Top-k of one token's scores held in shared memory v[0..E) by one warp: ties to the lower index.
+// Writes the chosen experts and weights (renormalised if asked).  `total` divides softmax scores.
+__device__ __forceinline__ void warp_topk(float* v, int E, int k, int sigmoid, int renorm, float total, int* sel_e, float* sel_w) {
+    const int lane = threadIdx.x & 31;
+    float chosen_sum = 0.0f, mine = 0.0f;
+    for (int r = 0; r < k; ++r) {
+        float best = -1.0f;
+        int best_i = 0x7fffffff;
+        for (int e = lane; e < E; e += 32)
+            if (v[e] > best) best = v[e], best_i = e;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (ob > best || (ob == best && oi < best_i)) best = ob, best_i = oi;
+        }
+        const float score = sigmoid ? best : best / total;
+        chosen_sum += score;
+        if (lane == 0) {
+            sel_e[r] = best_i;
+            v[best_i] = -2.0f;
+        }
+        if (lane == (r & 31)) mine = score;          // lane r keeps the r-th score (k <= 32 here; larger k: below)
+        if (r >= 32 && lane == 0) sel_w[r] = score;
+        __syncwarp();
+    }
+    const float den = !renorm ? 1.0f : (sigmoid ? chosen_sum + 1e-20f : chosen_sum);
+    if (lane < k && lane < 32) sel_w[lane] = mine / den;
+    if (k > 32 && renorm && lane == 0)
+        for (int r = 32; r < k; ++r) sel_w[r] /= den;
+}
+
+// Router of a decode step in one launch (reference: router_kernel, crates/cuda/kernels/flint.cu:1002-1055,
+// which also routes in its last block): a block per expert computes the logits of every token
+// (T <= 16) against bfloat16 activations with FP32 accumulation; the block that finishes last
+// (atomic ticket, no waiting) scores and picks the top-k of every token.
+constexpr int SMALL_T = 16;
+__global__ void __launch_bounds__(512) router_small_kernel(const __nv_bfloat16* xn, const __nv_bfloat16* w, int T_, int E, int D, int k,
+                                                           int sigmoid, int renorm, float* logits, int* sel_e, float* sel_w,
+                                                           unsigned* ticket) {
+    extern __shared__ float sc[];             // the last block: [16 warps][E] scores
+    __shared__ float red[16][SMALL_T];
+    __shared__ int is_last;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int e = blockIdx.x;                 // one block per expert: every thread takes 16-byte pieces of the row
+    {
+        float acc[SMALL_T];
+#pragma unroll
+        for (int t = 0; t < SMALL_T; ++t) acc[t] = 0.0f;
+        const __nv_bfloat16* wr = w + (size_t)e * D;
+        for (int d0 = threadIdx.x * 8; d0 < D; d0 += 512 * 8) {
+            const uint4 wv = *reinterpret_cast<const uint4*>(wr + d0);
+            const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+            float wf[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(w2[i]);
+                wf[2 * i] = f.x, wf[2 * i + 1] = f.y;
+            }
+#pragma unroll
+            for (int t = 0; t < SMALL_T; ++t) {
+                if (t < T_) {
+                    const uint4 xv = *reinterpret_cast<const uint4*>(xn + (size_t)t * D + d0);
+                    const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float2 f = __bfloat1622float2(x2[i]);
+                        acc[t] = fmaf(f.x, wf[2 * i], acc[t]);
+                        acc[t] = fmaf(f.y, wf[2 * i + 1], acc[t]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < SMALL_T; ++t) {
+            if (t < T_) {
+                const float z = warp_sum(acc[t]);
+                if (lane == 0) red[warp][t] = z;
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x < T_) {
+            float z = 0.0f;
+#pragma unroll
+            for (int wi = 0; wi < 16; ++wi) z += red[wi][threadIdx.x];       // warps in order: a fixed sum
+            logits[(size_t)threadIdx.x * E + e] = z;
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    for (int t = warp; t < T_; t += 16) {        // a warp per token
+        float* v = sc + (size_t)warp * E;
+        const float* z = logits + (size_t)t * E;
+        float total = 1.0f;
+        if (sigmoid) {
+            for (int x = lane; x < E; x += 32) {
+                const float s = 1.0f / (1.0f + expf(-__ldcg(z + x)));
+                v[x] = s >= 0.0f ? s : 0.0f;
+            }
+        } else {
+            float mx = -INFINITY;
+            for (int x = lane; x < E; x += 32) mx = fmaxf(mx, __ldcg(z + x));
+            mx = warp_max(mx);
+            float sum = 0.0f;
+            for (int x = lane; x < E; x += 32) {
+                float s = expf(__ldcg(z + x) - mx);
+                s = s >= 0.0f ? s : 0.0f;
+                v[x] = s;
+                sum += s;
+            }
+            total = warp_sum(sum);
+        }
+        __syncwarp();
+        warp_topk(v, E, k, sigmoid, renorm, total, sel_e + (size_t)t * k, sel_w + (size_t)t * k);
+    }
+    if (threadIdx.x == 0) *ticket = 0;          // ready for the next launch
+}
+
 constexpr int PERM_CHUNK = 1024;           // pairs per chunk of the permutation kernels
 
 // One warp per (expert, chunk of pairs): how many pairs of the chunk chose the expert.
@@ -157,6 +279,19 @@ Q6K_API int q6k_route(const float* logits, int T_, int E, int k, int sigmoid, in
     const size_t smem = (size_t)warps * E * sizeof(float);
     route_kernel<<<(T_ + warps - 1) / warps, warps * 32, smem, st>>>(logits, T_, E, k, sigmoid, renorm, sel_e, sel_w);
     return q6k_check_launch("route");
+}
+
+// xn: bfloat16 [T, D], T <= 16, D a multiple of 8; w: bfloat16 [E, D]; logits: FP32 [T, E] scratch;
+// ticket: one zeroed 32-bit word that the kernel leaves zeroed.
+Q6K_API int q6k_router_small(const void* xn, const void* w, int T_, int E, int D, int k, int sigmoid, int renorm, float* logits,
+                             int* sel_e, float* sel_w, unsigned* ticket, cudaStream_t st) {
+    if (T_ == 0) return 0;
+    Q6K_REQUIRE(T_ > 0 && T_ <= SMALL_T, "router_small: %d tokens exceed %d", T_, SMALL_T);
+    Q6K_REQUIRE(E > 0 && k > 0 && k <= E && E <= 704, "router_small: bad sizes E=%d k=%d (at most 704 experts)", E, k);
+    Q6K_REQUIRE(D > 0 && D % 8 == 0 && ((uintptr_t)xn & 15) == 0 && ((uintptr_t)w & 15) == 0, "router_small: D=%d must be a multiple of 8 and the operands 16-byte aligned", D);
+    router_small_kernel<<<E, 512, 16 * E * sizeof(float), st>>>((const __nv_bfloat16*)xn, (const __nv_bfloat16*)w, T_, E, D, k,
+                                                                       sigmoid, renorm, logits, sel_e, sel_w, ticket);
+    return q6k_check_launch("router_small");
 }
 
 Q6K_API int q6k_moe_permute_scratch_ints(int pairs, int E) { return ((pairs + PERM_CHUNK - 1) / PERM_CHUNK) * E; }

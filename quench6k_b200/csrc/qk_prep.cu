@@ -11,7 +11,7 @@ namespace {
 // Grid (T, Hq + Hkv) when the cache is written, (T, Hq) when this layer only reads another
 // layer's cache.  One thread per head dimension (blockDim.x >= hd, a multiple of 32).
 template <typename T>
-__global__ void qk_prep_kernel(const float* qkv, int ld, int Hq, int Hkv, int hd, const float* q_norm, const float* k_norm,
+__global__ void qk_prep_kernel(const float* qkv, int ld, int splits, size_t split_stride, int Hq, int Hkv, int hd, const float* q_norm, const float* k_norm,
                                float eps, int rope, float log2_theta, const int* positions, const int* req_of_token,
                                const int* block_table, int max_blocks, int page_size, T* q_out, T* k_pages, T* v_pages) {
     extern __shared__ float xs[];            // hd floats
@@ -21,7 +21,9 @@ __global__ void qk_prep_kernel(const float* qkv, int ld, int Hq, int Hkv, int hd
     const int pos = positions[t];
     const bool live = d < hd;
     const float* src = qkv + (size_t)t * ld + (is_q ? h * hd : (Hq + (h - Hq)) * hd);
-    float x = live ? src[d] : 0.0f;
+    float x = 0.0f;
+    if (live)
+        for (int s = 0; s < splits; ++s) x += src[s * split_stride + d];        // split-K partials, in order
     const float* nw = is_q ? q_norm : k_norm;
     if (nw) {
         const float ss = block_sum(x * x, red);
@@ -48,7 +50,9 @@ __global__ void qk_prep_kernel(const float* qkv, int ld, int Hq, int Hkv, int hd
         if (page < 0) return;                 // no page behind this position: nothing is written
         const size_t row = (((size_t)page * Hkv + kh) * page_size + pos % page_size) * hd + d;
         k_pages[row] = from_f32<T>(x);
-        v_pages[row] = from_f32<T>(qkv[(size_t)t * ld + (size_t)(Hq + Hkv + kh) * hd + d]);
+        float v = 0.0f;
+        for (int s = 0; s < splits; ++s) v += qkv[s * split_stride + (size_t)t * ld + (size_t)(Hq + Hkv + kh) * hd + d];
+        v_pages[row] = from_f32<T>(v);
     }
 }
 
@@ -56,7 +60,7 @@ __global__ void qk_prep_kernel(const float* qkv, int ld, int Hq, int Hkv, int hd
 // head_dim/32 elements d = lane + 32 i, so both elements of every rotation pair (d, d + head_dim/2)
 // sit in one lane and nothing goes through shared memory.  Block = 8 warps = 8 heads of one token.
 template <typename T, int EPL>
-__global__ void __launch_bounds__(256) qk_prep_warp_kernel(const float* qkv, int ld, int Hq, int Hkv, const float* q_norm,
+__global__ void __launch_bounds__(256) qk_prep_warp_kernel(const float* qkv, int ld, int splits, size_t split_stride, int Hq, int Hkv, const float* q_norm,
                                                            const float* k_norm, float eps, int rope, float log2_theta,
                                                            const int* positions, const int* req_of_token, const int* block_table,
                                                            int max_blocks, int page_size, T* q_out, T* k_pages, T* v_pages,
@@ -71,6 +75,7 @@ __global__ void __launch_bounds__(256) qk_prep_warp_kernel(const float* qkv, int
 #pragma unroll
     for (int i = 0; i < EPL; ++i) {
         x[i] = src[lane + 32 * i];
+        for (int s = 1; s < splits; ++s) x[i] += src[s * split_stride + lane + 32 * i];     // split-K partials, in order
         ss = fmaf(x[i], x[i], ss);
     }
     const float* nw = is_q ? q_norm : k_norm;
@@ -103,8 +108,10 @@ __global__ void __launch_bounds__(256) qk_prep_warp_kernel(const float* qkv, int
         const float* vsrc = qkv + (size_t)t * ld + (size_t)(Hq + Hkv + kh) * hd;
 #pragma unroll
         for (int i = 0; i < EPL; ++i) {
+            float v = vsrc[lane + 32 * i];
+            for (int s = 1; s < splits; ++s) v += vsrc[s * split_stride + lane + 32 * i];
             k_pages[row + lane + 32 * i] = from_f32<T>(x[i]);
-            v_pages[row + lane + 32 * i] = from_f32<T>(vsrc[lane + 32 * i]);
+            v_pages[row + lane + 32 * i] = from_f32<T>(v);
         }
     }
 }
@@ -114,12 +121,14 @@ __global__ void __launch_bounds__(256) qk_prep_warp_kernel(const float* qkv, int
 // qkv: FP32 [T, ld] with q heads, then k heads, then v heads in each row.  q_norm/k_norm: FP32 [hd]
 // or null (no QK-norm).  rope != 0 applies rotate-half RoPE with base theta at positions[t].
 // write_kv == 0: only q is produced (the layer reads a cache another layer wrote).
-Q6K_API int q6k_qk_prep(const float* qkv, int ld, int T_, int Hq, int Hkv, int hd, const float* q_norm, const float* k_norm,
+// splits > 1: qkv is [splits, T, ld] (slices split_stride floats apart) and the slices are summed in order first.
+Q6K_API int q6k_qk_prep(const float* qkv, int ld, int splits, long long split_stride, int T_, int Hq, int Hkv, int hd, const float* q_norm, const float* k_norm,
                         float eps, int rope, float theta, const int* positions, const int* req_of_token,
                         const int* block_table, int max_blocks, int page_size, void* q_out, void* k_pages, void* v_pages,
                         int write_kv, int dtype, cudaStream_t st) {
     if (T_ == 0) return 0;
     Q6K_REQUIRE(T_ > 0 && Hq > 0 && Hkv > 0 && hd > 0, "qk_prep: bad sizes T=%d Hq=%d Hkv=%d hd=%d", T_, Hq, Hkv, hd);
+    Q6K_REQUIRE(splits >= 1, "qk_prep: bad split count %d", splits);
     Q6K_REQUIRE(hd % 2 == 0 && hd <= 1024, "qk_prep: head_dim %d must be even and at most 1024", hd);
     Q6K_REQUIRE(!rope || theta > 0.0f, "qk_prep: rope base %g must be positive", theta);
     Q6K_REQUIRE(!write_kv || (page_size > 0 && max_blocks > 0), "qk_prep: bad page_size %d / max_blocks %d", page_size, max_blocks);
@@ -129,7 +138,7 @@ Q6K_API int q6k_qk_prep(const float* qkv, int ld, int T_, int Hq, int Hkv, int h
         dim3 wgrid(T_, (heads + 7) / 8);
         Q6K_REQUIRE(wgrid.y <= 65535, "qk_prep: %d heads exceed the grid limit", heads);
 #define WARP_LAUNCH(EPL)                                                                                                    \
-    qk_prep_warp_kernel<T, EPL><<<wgrid, 256, 0, st>>>(qkv, ld, Hq, Hkv, q_norm, k_norm, eps, rope, l2t, positions, req_of_token, \
+    qk_prep_warp_kernel<T, EPL><<<wgrid, 256, 0, st>>>(qkv, ld, splits, (size_t)split_stride, Hq, Hkv, q_norm, k_norm, eps, rope, l2t, positions, req_of_token, \
                                                        block_table, max_blocks, page_size, (T*)q_out, (T*)k_pages, (T*)v_pages, heads)
         Q6K_DISPATCH(dtype, {
             if (hd == 64) WARP_LAUNCH(2);
@@ -142,7 +151,7 @@ Q6K_API int q6k_qk_prep(const float* qkv, int ld, int T_, int Hq, int Hkv, int h
     const int threads = (hd + 31) / 32 * 32;
     dim3 grid(T_, heads);
     Q6K_DISPATCH(dtype, qk_prep_kernel<T><<<grid, threads, hd * sizeof(float), st>>>(
-                            qkv, ld, Hq, Hkv, hd, q_norm, k_norm, eps, rope, l2t, positions, req_of_token, block_table,
+                            qkv, ld, splits, (size_t)split_stride, Hq, Hkv, hd, q_norm, k_norm, eps, rope, l2t, positions, req_of_token, block_table,
                             max_blocks, page_size, (T*)q_out, (T*)k_pages, (T*)v_pages););
     return q6k_check_launch("qk_prep");
 }

@@ -52,9 +52,22 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* logits
     const int lo = blockIdx.x * ARGMAX_SLICE, hi = min(V, lo + ARGMAX_SLICE);
     unsigned best = 0u;
     int best_i = 0x7fffffff;
-    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-        const unsigned k = key_of(row[i]);
-        if (k > best || (k == best && i < best_i)) best = k, best_i = i;
+    // eight loads in flight per thread before the compares
+    for (int i0 = lo + threadIdx.x; i0 < hi; i0 += 8 * blockDim.x) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * blockDim.x;
+            v[u] = i < hi ? row[i] : 0.0f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = i0 + u * blockDim.x;
+            if (i < hi) {
+                const unsigned k = key_of(v[u]);
+                if (k > best || (k == best && i < best_i)) best = k, best_i = i;
+            }
+        }
     }
     block_best(best, best_i, bk, bi);
     if (threadIdx.x == 0) pk[blockIdx.y * slices + blockIdx.x] = best, pi[blockIdx.y * slices + blockIdx.x] = best_i;

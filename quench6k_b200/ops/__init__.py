@@ -97,9 +97,17 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype
     if out is None:
         out = torch.empty((R, D), dtype=out_dtype, device=x.device)
     _need(out, "out", out_dtype, (R, D))
+    splits, stride = 1, 0
     if add is not None:
-        _need(add, "add", torch.float32, x.shape)
-    _call("q6k_rmsnorm", _ptr(x), _ptr(add), _ptr(rows), _ptr(w), _f(eps), _ptr(out), _i(R), _i(D), _i(dtype_code(out_dtype)), _stream())
+        _need(add, "add", torch.float32)
+        if add.dim() == 3:                       # [splits, R, D]: partial sums, added in order
+            splits, stride = add.shape[0], add.shape[1] * add.shape[2]
+            if tuple(add.shape[1:]) != tuple(x.shape):
+                raise KernelError("rmsnorm: the partial sums do not match x")
+        elif tuple(add.shape) != tuple(x.shape):
+            raise KernelError("rmsnorm: add does not match x")
+    _call("q6k_rmsnorm", _ptr(x), _ptr(add), _i(splits), _ll(stride), _ptr(rows), _ptr(w), _f(eps), _ptr(out), _i(R), _i(D),
+          _i(dtype_code(out_dtype)), _stream())
     return out
 
 
@@ -108,10 +116,11 @@ def combine(y: torch.Tensor, pair_row: torch.Tensor, sel_w: torch.Tensor, h: tor
     T, S = sel_w.shape
     D = h.shape[1]
     _need(y, "y", torch.float32)
-    _need(pair_row, "pair_row", torch.int32)
     _need(sel_w, "sel_w", torch.float32)
     _need(h, "h", torch.float32, (T, D))
-    if y.shape[1] != D or pair_row.numel() != T * S:
+    if pair_row is not None:
+        _need(pair_row, "pair_row", torch.int32)
+    if y.shape[1] != D or (pair_row is not None and pair_row.numel() != T * S) or y.shape[0] < T * S:
         raise KernelError("combine: shapes disagree")
     _call("q6k_combine", _ptr(y), _ptr(pair_row), _ptr(sel_w), _i(T), _i(S), _i(D), _ptr(h), _stream())
 
@@ -236,10 +245,14 @@ def _workspace(nbytes: int, device) -> torch.Tensor:
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, accumulate: bool = False,
-            w2: Optional[torch.Tensor] = None, groups=None, bt: int = 0, rows: Optional[int] = None) -> torch.Tensor:
+            w2: Optional[torch.Tensor] = None, groups=None, bt: int = 0, rows: Optional[int] = None,
+            keep_partials: bool = False) -> torch.Tensor:
     """The same contract as gemm_simt without the row gather, on tcgen05 tensor cores: bfloat16
     operands, FP32 accumulation in tensor memory.  Grouped calls pass the tile list made for
-    token tile `bt` (tile_list(offsets, pairs, bt))."""
+    token tile `bt` (tile_list(offsets, pairs, bt)).  keep_partials (dense, plain store): when the
+    kernel slices K over CTAs the result is the FP32 partial products [slices, M, N], a view of the
+    device's scratch buffer that stays valid until the next kernel that uses scratch; the consumer
+    sums the slices in order."""
     if not tc_supported(a, w):
         raise KernelError("gemm_tc: operands must be bfloat16 with K a multiple of 8 and 16-byte aligned rows")
     K = a.shape[1]
@@ -253,16 +266,23 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
     M = rows if rows is not None else a.shape[0]
     epi = EPI_SWIGLU if w2 is not None else (EPI_ADD if accumulate else EPI_STORE)
     out_dtype = torch.bfloat16 if w2 is not None else torch.float32
+    lib = library()
+    splits = 1
+    if keep_partials:
+        if grouped or w2 is not None or accumulate or out is not None:
+            raise KernelError("gemm_tc: partial products are kept only for a dense product that is stored")
+        lib.q6k_gemm_tc_splits.restype = ctypes.c_int
+        splits = lib.q6k_gemm_tc_splits(_i(M), _i(N), _i(K))
+        keep_partials = splits > 1
     if out is None:
         if accumulate:
             raise KernelError("gemm_tc: accumulate needs an output")
-        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        out = torch.empty((M, N) if not keep_partials else (1, N), dtype=out_dtype, device=a.device)
     _need(out, "out", out_dtype)
-    if out.shape[0] < M or out.shape[1] != N:
+    if (out.shape[0] < M and not keep_partials) or out.shape[1] != N:
         raise KernelError(f"gemm_tc: out has shape {tuple(out.shape)}, needs [{M}, {N}]")
     if w2 is not None:
         _need(w2, "w2", torch.bfloat16, w.shape)
-    lib = library()
     ws = None
     ws_bytes = 0
     if grouped:
@@ -279,7 +299,9 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
                 ws_bytes = ws.numel() * 4
     _call("q6k_gemm_tc", _ptr(a), _ll(a.stride(0)), _i(M), _ptr(w), _ptr(w2), _i(G), _i(N), _i(K), _ptr(out), _i(out.stride(0)),
           _i(epi), _ptr(tile_group), _ptr(tile_row0), _ptr(offsets), _ptr(num_tiles), _i(max_tiles), _i(bt), _ptr(ws),
-          _ll(ws_bytes), _stream())
+          _ll(ws_bytes), _i(1 if keep_partials else 0), _stream())
+    if keep_partials:
+        return ws[: splits * M * N].view(splits, M, N)
     return out
 
 
@@ -287,8 +309,13 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
 def qk_prep(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, q_norm, k_norm, eps: float, rope_theta: Optional[float],
             positions: torch.Tensor, req_of_token: torch.Tensor, block_table: Optional[torch.Tensor], page_size: int,
             k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], out_dtype: torch.dtype) -> torch.Tensor:
-    """QK-norm, RoPE, q -> out_dtype [T, Hq, hd]; k, v -> their pages (when k_pages is given)."""
+    """QK-norm, RoPE, q -> out_dtype [T, Hq, hd]; k, v -> their pages (when k_pages is given).
+    qkv may be [slices, T, width]: split-K partial products, summed in order first."""
     _need(qkv, "qkv", torch.float32)
+    splits, split_stride = 1, 0
+    if qkv.dim() == 3:
+        splits, split_stride = qkv.shape[0], qkv.shape[1] * qkv.shape[2]
+        qkv = qkv[0]
     T = qkv.shape[0]
     if qkv.shape[1] < (Hq + 2 * Hkv) * hd and k_pages is not None:
         raise KernelError("qk_prep: qkv rows are too short")
@@ -306,7 +333,7 @@ def qk_prep(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, q_norm, k_norm, eps: 
             _need(w, nm, torch.float32, (hd,))
     q = torch.empty((T, Hq, hd), dtype=out_dtype, device=qkv.device)
     max_blocks = block_table.shape[1] if block_table is not None else 1
-    _call("q6k_qk_prep", _ptr(qkv), _i(qkv.stride(0)), _i(T), _i(Hq), _i(Hkv), _i(hd), _ptr(q_norm), _ptr(k_norm), _f(eps),
+    _call("q6k_qk_prep", _ptr(qkv), _i(qkv.stride(0)), _i(splits), _ll(split_stride), _i(T), _i(Hq), _i(Hkv), _i(hd), _ptr(q_norm), _ptr(k_norm), _f(eps),
           _i(1 if rope_theta is not None else 0), _f(rope_theta or 0.0), _ptr(positions), _ptr(req_of_token), _ptr(block_table),
           _i(max_blocks), _i(page_size), _ptr(q), _ptr(k_pages), _ptr(v_pages), _i(1 if write else 0),
           _i(dtype_code(out_dtype)), _stream())
@@ -389,6 +416,49 @@ def route(logits: torch.Tensor, k: int, scoring: str, renorm: bool):
     _call("q6k_route", _ptr(logits), _i(T), _i(E), _i(k), _i(1 if scoring == "sigmoid" else 0), _i(1 if renorm else 0),
           _ptr(sel_e), _ptr(sel_w), _stream())
     return sel_e, sel_w
+
+
+SMALL_T = 16
+_tickets = {}
+
+
+def router_small(xn: torch.Tensor, w: torch.Tensor, k: int, scoring: str, renorm: bool):
+    """Router logits, scores and top-k of at most 16 tokens in one launch: (sel_e [T, k], sel_w [T, k])."""
+    _need(xn, "xn", torch.bfloat16)
+    _need(w, "w", torch.bfloat16)
+    T, D = xn.shape
+    E = w.shape[0]
+    if w.shape[1] != D:
+        raise KernelError("router_small: widths disagree")
+    dev = xn.device
+    ticket = _tickets.get(str(dev))
+    if ticket is None:
+        ticket = _tickets[str(dev)] = torch.zeros(1, dtype=torch.int32, device=dev)
+    logits = torch.empty((T, E), dtype=torch.float32, device=dev)
+    sel_e = torch.empty((T, k), dtype=torch.int32, device=dev)
+    sel_w = torch.empty((T, k), dtype=torch.float32, device=dev)
+    _call("q6k_router_small", _ptr(xn), _ptr(w), _i(T), _i(E), _i(D), _i(k), _i(1 if scoring == "sigmoid" else 0),
+          _i(1 if renorm else 0), _ptr(logits), _ptr(sel_e), _ptr(sel_w), _ptr(ticket), _stream())
+    return sel_e, sel_w
+
+
+def gemm_tc_pairs(a: torch.Tensor, w: torch.Tensor, pair_expert: torch.Tensor, pair_div: int, w2: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Expert products of a decode step without a permutation: pair y (= token * slots + slot)
+    multiplies row y // pair_div of `a` with expert pair_expert[y]; output row y.  With w2 the
+    SwiGLU epilogue (bfloat16 output), else FP32."""
+    if not tc_supported(a, w) or w.dim() != 3:
+        raise KernelError("gemm_tc_pairs: operands must be bfloat16, K a multiple of 8, weights [experts, N, K]")
+    _need(pair_expert, "pair_expert", torch.int32)
+    pairs = pair_expert.numel()
+    G, N, K = w.shape
+    if a.shape[1] != K:
+        raise KernelError(f"gemm_tc_pairs: a has K={a.shape[1]}, w has K={K}")
+    if w2 is not None:
+        _need(w2, "w2", torch.bfloat16, w.shape)
+    out = torch.empty((pairs, N), dtype=torch.bfloat16 if w2 is not None else torch.float32, device=a.device)
+    _call("q6k_gemm_tc_pairs", _ptr(a), _ll(a.stride(0)), _i(a.shape[0]), _ptr(w), _ptr(w2), _i(G), _i(N), _i(K), _ptr(out),
+          _i(out.stride(0)), _i(EPI_SWIGLU if w2 is not None else EPI_STORE), _ptr(pair_expert), _i(pairs), _i(pair_div), _stream())
+    return out
 
 
 def moe_permute(sel_e: torch.Tensor, E: int):

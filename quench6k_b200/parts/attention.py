@@ -61,10 +61,12 @@ class Attention(Mixer):
     def forward(self, xn, ctx, cache, state, out):
         rt = self.rt
         write = cache.write
-        qkv = linear.matmul(xn, self.w_qkv if write else self.w_q, rt)          # FP32 [T, (Hq + 2 Hkv) hd] or [T, Hq hd]
         theta = self.pos.fused_rope_theta()
+        fused_pos = theta is not None or isinstance(self.pos, POSITION_ENCODINGS["none"])
+        # FP32 [T, (Hq + 2 Hkv) hd] or [T, Hq hd]; for few rows possibly as split-K partials, which qk_prep sums
+        qkv = linear.matmul(xn, self.w_qkv if write else self.w_q, rt, partials_ok=fused_pos)
         table = ctx.block_tables[cache.group]
-        if theta is None and not isinstance(self.pos, POSITION_ENCODINGS["none"]):
+        if not fused_pos:
             qkv = self._unfused_position(qkv, ctx, write)
             q = ops.qk_prep(qkv, self.Hq, self.Hkv, self.hd, None, None, self.eps, None, ctx.positions, ctx.req_of_token,
                             table if write else None, cache.page_size, cache.k if write else None,
@@ -74,7 +76,8 @@ class Attention(Mixer):
                             ctx.req_of_token, table if write else None, cache.page_size, cache.k if write else None,
                             cache.v if write else None, rt.dtype)
         a = self._attend(q, cache, table, ctx)
-        return linear.matmul(a, self.w_o, rt)              # the block adds it into the stream inside its next norm
+        # the block adds it into the stream inside its next norm (which also sums split-K partials)
+        return linear.matmul(a, self.w_o, rt, partials_ok=True)
 
     def _attend(self, q, cache, table, ctx):
         """Tensor-core kernel for bfloat16 where it covers the head and group size, else the generic one."""

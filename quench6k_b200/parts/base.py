@@ -8,13 +8,14 @@ To add a part, subclass the matching base, implement the methods below and regis
 under a name with the matching `register_*`; a spec.PartSpec(kind=name, params=...) then selects it.
 
   Norm            tensors(); bind(); forward(h_f32 [T, D], rows=None, add=None) -> [R, D] in the operand dtype;
-                  with `add` (float32 [T, D]) it first stores h += add (the block's residual add, fused)
+                  with `add` (float32 [T, D], or [slices, T, D] partial sums to be added in order) it
+                  first stores h += add (the block's residual add, fused)
   PositionEncoding  fused_rope_theta() -> float | None (None: not the fused rotary);
                   apply(x_f32 [T, H, hd], positions_i32 [T]) -> None, in place (used when not fused)
   Mixer           tensors(); bind(); cache_request() -> CacheRequest | None; state_shape() -> tuple | None;
                   forward(xn [T, D], ctx: StepContext, cache: LayerCache | None, state: Tensor | None, out_f32 [T, D])
                   adds its result into `out` and returns None, or leaves `out` alone and returns the
-                  float32 [T, D] result for the block to add
+                  float32 [T, D] result (or [slices, T, D] partial sums) for the block's next norm to add
   FeedForward     tensors(); bind(); forward(xn [T, D], ctx, out_f32 [T, D]) adds its result into `out`
   Block           built from (norm1, mixer, norm2, ffn); forward(h, ctx, cache, state)
 """

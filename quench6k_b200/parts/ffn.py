@@ -73,6 +73,17 @@ class RoutedExperts(FeedForward):
         rt = self.rt
         T = xn.shape[0]
         pairs = T * self.k
+        if (T <= ops.SMALL_T and rt.tensor_cores and not rt.is_fp32 and self.E <= 704 and ops.tc_supported(xn, self.w_gate)
+                and self.I % 8 == 0):
+            # a decode step: router and top-k in one launch, then one weight tile stream per
+            # (token, slot) pair straight from the selection, no permutation and no gather
+            sel_e, sel_w = ops.router_small(xn, self.w_router, self.k, self.scoring, self.renorm)
+            act = ops.gemm_tc_pairs(xn, self.w_gate, sel_e, self.k, w2=self.w_up)         # [pairs, I]
+            y = ops.gemm_tc_pairs(act, self.w_down, sel_e, 1)                              # FP32 [pairs, D]
+            ops.combine(y, None, sel_w, out)
+            if self.shared is not None:
+                self.shared.forward(xn, ctx, out)
+            return
         logits = linear.matmul(xn, self.w_router, rt)                       # FP32 [T, E]
         sel_e, sel_w = ops.route(logits, self.k, self.scoring, self.renorm)
         offsets, pair_row, row_token = ops.moe_permute(sel_e, self.E)

@@ -17,9 +17,14 @@ def _tc(a: torch.Tensor, w: torch.Tensor, rt) -> bool:
     return rt.tensor_cores and not rt.is_fp32 and ops.tc_supported(a, w)
 
 
-def matmul(a: torch.Tensor, w: torch.Tensor, rt, out: Optional[torch.Tensor] = None, accumulate: bool = False) -> torch.Tensor:
-    """FP32 out[r] (+)= a[r] @ w^T;  a: [M, K], w: [N, K]."""
+def matmul(a: torch.Tensor, w: torch.Tensor, rt, out: Optional[torch.Tensor] = None, accumulate: bool = False,
+           partials_ok: bool = False) -> torch.Tensor:
+    """FP32 out[r] (+)= a[r] @ w^T;  a: [M, K], w: [N, K].  partials_ok: the caller's next kernel
+    can sum split-K partial products itself, so the result may come as [slices, M, N] (a view of
+    the device's scratch buffer: consume it before the next kernel that uses scratch)."""
     if _tc(a, w, rt):
+        if partials_ok and out is None and not accumulate and w.shape[0] % 4 == 0:
+            return ops.gemm_tc(a, w, keep_partials=True)
         return ops.gemm_tc(a, w, out=out, accumulate=accumulate)
     return ops.gemm_simt(a, w, out=out, accumulate=accumulate)
 

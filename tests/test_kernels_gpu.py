@@ -350,3 +350,35 @@ def test_attention_mma(Hq, Hkv, hd, ps, window, sinks, mode):
         assert err <= 1.5e-2, (max_splits, err)
     gen = ops.attention_generic(q, kp.to(DEV), vp.to(DEV), bt, ctx.req_of_token, ctx.positions, window, sk)
     assert (out.float() - gen.float()).abs().max() <= 2e-2 * gen.float().abs().max()
+
+
+@pytest.mark.parametrize("scoring,renorm", [("softmax", True), ("sigmoid", False)])
+@pytest.mark.parametrize("T,E,k,D,I", [(1, 256, 8, 2048, 512), (8, 64, 6, 256, 128), (16, 10, 3, 72, 40)])
+def test_decode_moe_path(scoring, renorm, T, E, k, D, I):
+    """router_small + per-pair expert tiles against the general path (router GEMM, route, permutation, grouped tiles)."""
+    from quench6k_b200 import ops
+    x = _t(T, D, dtype=torch.bfloat16)
+    wr = _t(E, D, dtype=torch.bfloat16, seed=1, scale=0.02)      # small: a saturated sigmoid would tie in FP32
+    wg, wu = _t(E, I, D, dtype=torch.bfloat16, seed=2, scale=0.2), _t(E, I, D, dtype=torch.bfloat16, seed=3, scale=0.2)
+    wd = _t(E, D, I, dtype=torch.bfloat16, seed=4, scale=0.2)
+    sel_e, sel_w = ops.router_small(x, wr, k, scoring, renorm)
+    logits = x.double().cpu() @ wr.double().cpu().T
+    ref_e, ref_w = P.route(logits, scoring, k, renorm)
+    assert torch.equal(sel_e.cpu().long(), ref_e)
+    assert (sel_w.double().cpu() - ref_w).abs().max() <= 1e-4 * ref_w.abs().max()
+    again_e, again_w = ops.router_small(x, wr, k, scoring, renorm)          # the ticket was left ready
+    assert torch.equal(again_e, sel_e) and torch.equal(again_w, sel_w)
+    act = ops.gemm_tc_pairs(x, wg, sel_e, k, w2=wu)
+    y = ops.gemm_tc_pairs(act, wd, sel_e, 1)
+    assert ops.tc_status() == 0
+    for p in range(T * k):
+        e, t = int(sel_e.flatten()[p]), p // k
+        xa = x[t].double().cpu()
+        a_ref = P.silu(wg[e].double().cpu() @ xa) * (wu[e].double().cpu() @ xa)
+        assert (act[p].double().cpu() - a_ref).abs().max() <= 1e-2 * a_ref.abs().max() + 1e-9
+        y_ref = wd[e].double().cpu() @ act[p].double().cpu()
+        assert (y[p].double().cpu() - y_ref).abs().max() <= 1e-4 * y_ref.abs().max() + 1e-9
+    h = _t(T, D, seed=9)
+    want = h.double().cpu() + (sel_w.double().cpu()[:, :, None] * y.double().cpu().view(T, k, D)).sum(1)
+    ops.combine(y, None, sel_w, h)
+    assert (h.double().cpu() - want).abs().max() <= 1e-5 * want.abs().max()

@@ -88,7 +88,9 @@ def test_attention_part_over_pages(dtype, window, sinks, qk_norm, rope):
     def run(x, ctx):
         out = torch.zeros(x.shape[0], D, device=DEV)
         delta = att.forward(x.to(DEV), ctx, cache, None, out)       # a mixer adds into `out` or returns its result
-        return out if delta is None else delta
+        if delta is None:
+            return out
+        return delta.sum(0) if delta.dim() == 3 else delta          # split-K partial sums
 
     out1 = run(xs[0][:13], helpers.make_context([13], [0], [[tables[0][0]]]))
     out2 = run(torch.cat([xs[0][13:], xs[1]]), helpers.make_context([6, 11], [13, 0], tables))

@@ -93,3 +93,32 @@ def test_command_line(tmp_path):
     assert "prompt: 7 tokens" in r.stdout and "first-token top 5:" in r.stdout and "decode 7 tokens" in r.stdout
     want, _ = plain_greedy(cfg, weights, prompt, 8)
     assert f"ids: {want}" in r.stdout
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_graph_replay_equals_eager_steps(tmp_path, dtype):
+    """Decode-only steps replay a CUDA graph; the logits must equal those of the same steps run
+    eagerly (the reference checks graph decoding against eager decoding the same way,
+    crates/cli/src/flint.rs:116-131)."""
+    from quench6k_b200.engine import ModelRunner, StepEntry
+    cfg, _ = helpers.make_model_folder(str(tmp_path), "B", seed=31)
+    prompts = {f"r{i}": helpers.random_tokens(n, cfg["vocab_size"], 600 + n) for i, n in enumerate((9, 21, 14))}
+    tails = {rid: helpers.random_tokens(12, cfg["vocab_size"], 700 + i) for i, rid in enumerate(prompts)}
+    outs = {}
+    for graphs in (False, True):
+        runner = ModelRunner.from_folder(str(tmp_path), dtype=dtype, num_pages=32, cuda_graphs=graphs)
+        assert runner.cuda_graphs == graphs
+        for rid, p in prompts.items():
+            runner.add_request(rid)
+        runner.step([StepEntry(rid, p, []) for rid, p in prompts.items()])
+        got = []
+        for i in range(12):
+            live = list(prompts)[: 3 if i < 8 else 2]                       # the batch shrinks: another graph
+            got.append(runner.step([StepEntry(rid, [tails[rid][i]], [0]) for rid in live]).clone().cpu())
+        outs[graphs] = got
+        assert (runner.graph_replays > 0) == graphs
+    for a, b in zip(outs[False], outs[True]):
+        if dtype == "float32":
+            assert torch.equal(a, b)
+        else:
+            assert (a - b).abs().max() <= 1e-2 * a.abs().max()

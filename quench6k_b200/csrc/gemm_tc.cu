@@ -11,14 +11,16 @@
 // and simply streams the weights through a deep TMA pipeline, while a prefill tile reuses each
 // weight tile over up to 256 tokens.
 //
-// One CTA computes one [128 weights x BT tokens] tile (optionally one slice of K):
+// A persistent CTA per SM walks tiles of [128 weights x BT tokens] (optionally one slice of K each):
 //   warp 0     producer: waits for a free stage, arms its mbarrier with the byte count, issues the
 //              TMA loads of the weight tile(s) [128 x 64] and the token tile [BT x 64] (128-byte swizzle)
-//   warp 1     allocates tensor memory; one thread issues 4 tcgen05.mma (K = 16 each) per stage and
-//              commits the stage's "empty" barrier; after the last stage commits "accumulator full"
+//   warp 1     allocates tensor memory (two accumulator buffers); one thread issues 4 tcgen05.mma
+//              (K = 16 each) per stage and commits the stage's "empty" barrier; after a tile's last
+//              stage it commits "accumulator full" and turns to the other buffer
 //   warps 2-5  epilogue: tcgen05.ld of their 32 accumulator lanes (one lane = one weight row, one
 //              column = one token) and the store: plain, added into the FP32 stream, SwiGLU of two
-//              accumulators, or a split-K partial
+//              accumulators, or a split-K partial; they hand a buffer back ("accumulator empty") as soon
+//              as its values are in registers, so the next tile's MMAs overlap the stores
 // Every wait on an mbarrier is bounded; a wait that runs out records a code in a status word that
 // q6k_tc_status() returns, the roles fall through to the common exit, and tensor memory is freed.
 #include <map>
@@ -32,7 +34,7 @@ namespace {
 
 constexpr int BK = 64;                 // bf16 per k-block: one 128-byte swizzle row
 constexpr int WM = 128;                // weight rows per tile (UMMA M)
-constexpr int MAX_STAGES = 8;
+constexpr int MAX_STAGES = 12;
 
 enum { EPI_STORE = 0, EPI_ADD = 1, EPI_SWIGLU = 2, EPI_PARTIAL = 3 };
 
@@ -45,9 +47,11 @@ struct Params {
     const int* tile_row0;
     const int* group_offsets;
     const int* num_tiles;
+    const int* pair_order;             // pair mode: tile y works on pair pair_order[y] (null: pair y)
     int rows_total, N, K, ldo;
     int epilogue, stages, kb_per_split;
     int pair_div;                      // > 0: one tile per (token, slot) pair, see q6k_gemm_tc_pairs
+    int n_y, n_z;                      // row tiles (or pairs; an upper bound when num_tiles is given) and K slices
 };
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) with the
@@ -90,50 +94,76 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
 
 __host__ __device__ constexpr int tmem_cols(int want) { return want <= 32 ? 32 : want <= 64 ? 64 : want <= 128 ? 128 : want <= 256 ? 256 : 512; }
 
+// One tile of the persistent schedule: which weights, which token rows, which slice of K.
+struct Tile {
+    int g, n0, row0, row_end, out0, kb0, nkb, z;
+};
+
+// Tile t of the launch: n-tiles fastest (neighbouring CTAs share the token tile), then row tiles
+// (or pairs, or the grouped tile list), then K slices.  Every role of a CTA decodes the same
+// sequence t = blockIdx.x, blockIdx.x + gridDim.x, ...
+template <int BT>
+__device__ __forceinline__ bool decode_tile(const Params& p, int t, int n_x, int n_y, Tile& o) {
+    const int x = t % n_x, y = (t / n_x) % n_y;
+    o.z = t / (n_x * n_y);
+    o.n0 = x * WM;
+    o.g = 0;
+    if (p.pair_div > 0) {
+        // tile y is pair y: its expert's weights, the single input row y / pair_div, the output row y
+        const int pair = p.pair_order ? p.pair_order[y] : y;
+        o.g = p.tile_group[pair];
+        o.row0 = pair / p.pair_div;
+        o.row_end = o.row0 + 1;
+        o.out0 = pair;
+    } else if (p.tile_group) {
+        o.g = p.tile_group[y];
+        o.row0 = p.tile_row0[y];
+        o.row_end = p.group_offsets[o.g + 1];
+        o.out0 = o.row0;
+    } else {
+        o.row0 = y * BT;
+        o.row_end = p.rows_total;
+        o.out0 = o.row0;
+    }
+    const int kb_total = (p.K + BK - 1) / BK;
+    o.kb0 = o.z * p.kb_per_split;
+    o.nkb = min(p.kb_per_split, kb_total - o.kb0);
+    return o.row0 < o.row_end && o.nkb > 0;
+}
+
+// Persistent: one CTA per SM walks the tiles.  The producer runs ahead through the shared-memory
+// ring across tile boundaries; the MMA thread alternates between two accumulators in tensor
+// memory, so the epilogue warps drain one tile while the next one is being multiplied.
 template <int BT, bool DUAL>
 __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_w2,
                                                        const __grid_constant__ CUtensorMap tm_a, const Params p) {
-    // which tile
-    int g = 0, row0 = blockIdx.y * BT, row_end = p.rows_total, out0 = row0;
-    if (p.pair_div > 0) {
-        // tile y is pair y: its expert's weights, the single input row y / pair_div, the output row y
-        g = p.tile_group[blockIdx.y];
-        row0 = blockIdx.y / p.pair_div;
-        row_end = row0 + 1;
-        out0 = blockIdx.y;
-    } else if (p.tile_group) {
-        if ((int)blockIdx.y >= *p.num_tiles) return;
-        g = p.tile_group[blockIdx.y];
-        row0 = p.tile_row0[blockIdx.y];
-        row_end = p.group_offsets[g + 1];
-        out0 = row0;
-    } else {
-        out0 = row0;
-    }
-    if (row0 >= row_end) return;
-    const int n0 = blockIdx.x * WM;
-    const int kb_total = (p.K + BK - 1) / BK;
-    const int kb0 = blockIdx.z * p.kb_per_split;
-    const int nkb = min(p.kb_per_split, kb_total - kb0);
-    if (nkb <= 0) return;
+    const int n_x = (p.N + WM - 1) / WM;
+    const int n_y = p.pair_div > 0 ? p.n_y : (p.tile_group ? *p.num_tiles : p.n_y);
+    const int total = n_x * n_y * p.n_z;
+    if ((int)blockIdx.x >= total) return;
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     constexpr uint32_t W_BYTES = WM * BK * 2, A_BYTES = BT * BK * 2;
     constexpr uint32_t STAGE_BYTES = W_BYTES * (DUAL ? 2 : 1) + A_BYTES;
-    __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 1];
+    constexpr int ACC_COLS = DUAL ? 2 * BT : BT;           // columns of one accumulator buffer
+    constexpr int COLS = tmem_cols(2 * ACC_COLS);
+    __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 4];
     __shared__ uint32_t tmem_base_slot;
     const int stages = p.stages;
-    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[MAX_STAGES]), accum_bar = smem_u32(&bars[2 * MAX_STAGES]);
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[MAX_STAGES]);
+    const uint32_t acc_full0 = smem_u32(&bars[2 * MAX_STAGES]), acc_empty0 = smem_u32(&bars[2 * MAX_STAGES + 2]);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr int COLS = tmem_cols(DUAL ? 2 * BT : BT);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < stages; ++s) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
         }
-        mbar_init(accum_bar, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full0 + 8 * b, 1);
+            mbar_init(acc_empty0 + 8 * b, 4);              // one arrival per epilogue warp
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_w) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_a) : "memory");
@@ -151,71 +181,102 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
 
     if (warp == 0) {
         if (lane == 0) {
-            const int wy = g * p.N + n0;
-            for (int i = 0; i < nkb; ++i) {
-                const int s = i % stages;
-                const uint32_t ph = (i / stages) & 1;
-                if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) {
-                    atomicExch(&g_tc_status, 1);
-                    break;
+            int it = 0;                                    // k-blocks issued so far, over all tiles
+            bool ok = true;
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                Tile tl;
+                if (!decode_tile<BT>(p, t, n_x, n_y, tl)) continue;
+                const int wy = tl.g * p.N + tl.n0;
+                for (int i = 0; i < tl.nkb; ++i, ++it) {
+                    const int s = it % stages;
+                    if (!mbar_wait(empty0 + 8 * s, ((it / stages) & 1) ^ 1)) {
+                        atomicExch(&g_tc_status, 1);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                    const uint32_t fb = full0 + 8 * s;
+                    mbar_expect_tx(fb, STAGE_BYTES);
+                    const int kx = (tl.kb0 + i) * BK;
+                    tma_load_2d(st, &tm_w, kx, wy, fb);
+                    if (DUAL) tma_load_2d(st + W_BYTES, &tm_w2, kx, wy, fb);
+                    tma_load_2d(st + W_BYTES * (DUAL ? 2 : 1), &tm_a, kx, tl.row0, fb);
                 }
-                const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
-                const uint32_t fb = full0 + 8 * s;
-                mbar_expect_tx(fb, STAGE_BYTES);
-                const int kx = (kb0 + i) * BK;
-                tma_load_2d(st, &tm_w, kx, wy, fb);
-                if (DUAL) tma_load_2d(st + W_BYTES, &tm_w2, kx, wy, fb);
-                tma_load_2d(st + W_BYTES * (DUAL ? 2 : 1), &tm_a, kx, row0, fb);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc(BT);
+            int it = 0, nt = 0;                            // k-blocks and tiles consumed so far
             bool ok = true;
-            for (int i = 0; i < nkb && ok; ++i) {
-                const int s = i % stages;
-                const uint32_t ph = (i / stages) & 1;
-                if (!mbar_wait(full0 + 8 * s, ph)) {
-                    atomicExch(&g_tc_status, 2);
-                    ok = false;
+            for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
+                Tile tl;
+                if (!decode_tile<BT>(p, t, n_x, n_y, tl)) continue;
+                const int buf = nt & 1;
+                if (!mbar_wait(acc_empty0 + 8 * buf, ((nt >> 1) & 1) ^ 1)) {      // the epilogue has drained this buffer
+                    atomicExch(&g_tc_status, 4);
                     break;
                 }
                 tc_fence_after();
-                const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
-                const uint64_t dw = umma_desc_sw128(st), dw2 = umma_desc_sw128(st + W_BYTES);
-                const uint64_t da = umma_desc_sw128(st + W_BYTES * (DUAL ? 2 : 1));
+                const uint32_t acc_addr = tmem_base + buf * ACC_COLS;
+                for (int i = 0; i < tl.nkb; ++i, ++it) {
+                    const int s = it % stages;
+                    if (!mbar_wait(full0 + 8 * s, (it / stages) & 1)) {
+                        atomicExch(&g_tc_status, 2);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                    const uint64_t dw = umma_desc_sw128(st), dw2 = umma_desc_sw128(st + W_BYTES);
+                    const uint64_t da = umma_desc_sw128(st + W_BYTES * (DUAL ? 2 : 1));
 #pragma unroll
-                for (int k = 0; k < BK / 16; ++k) {
-                    const uint32_t acc = (i | k) != 0;
-                    umma_bf16(tmem_base, dw + 2 * k, da + 2 * k, idesc, acc);          // + 32 bytes of K per step
-                    if (DUAL) umma_bf16(tmem_base + BT, dw2 + 2 * k, da + 2 * k, idesc, acc);
+                    for (int k = 0; k < BK / 16; ++k) {
+                        const uint32_t acc = (i | k) != 0;
+                        umma_bf16(acc_addr, dw + 2 * k, da + 2 * k, idesc, acc);          // + 32 bytes of K per step
+                        if (DUAL) umma_bf16(acc_addr + BT, dw2 + 2 * k, da + 2 * k, idesc, acc);
+                    }
+                    umma_commit(empty0 + 8 * s);
                 }
-                umma_commit(empty0 + 8 * s);
+                if (!ok) break;
+                umma_commit(acc_full0 + 8 * buf);          // arrives when every MMA issued so far has finished
+                ++nt;
             }
-            umma_commit(accum_bar);          // arrives when every MMA issued so far has finished
         }
     } else {
         // epilogue: this warp owns accumulator lanes 32*(warp%4) .. +31
         const int quarter = warp & 3;
         const int n_local = quarter * 32 + lane;
-        const int n = n0 + n_local;
-        const bool ok = mbar_wait(accum_bar, 0);
-        if (!ok && lane == 0) atomicExch(&g_tc_status, 3);
-        tc_fence_after();
-        if (ok) {
-            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-            const int valid = min(BT, row_end - row0);
+        int nt = 0;
+        for (int t = blockIdx.x; t < total; t += gridDim.x) {
+            Tile tl;
+            if (!decode_tile<BT>(p, t, n_x, n_y, tl)) continue;
+            const int buf = nt & 1;
+            if (!mbar_wait(acc_full0 + 8 * buf, (nt >> 1) & 1)) {
+                if (lane == 0) atomicExch(&g_tc_status, 3);
+                break;
+            }
+            tc_fence_after();
+            const int n = tl.n0 + n_local;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * ACC_COLS;
+            const int valid = min(BT, tl.row_end - tl.row0);
 #pragma unroll 1
             for (int c0 = 0; c0 < valid; c0 += 16) {
                 float v[16], u[16];
                 tmem_ld16(lane_addr + c0, v);
                 if (DUAL) tmem_ld16(lane_addr + BT + c0, u);
+                if (c0 + 16 >= valid) {
+                    // everything this warp needs of the buffer is in registers: hand it back
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
+                }
                 if (n < p.N) {
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
-                        const int t = c0 + j;
-                        if (t >= valid) break;
-                        const size_t row = (size_t)(out0 + t);
+                        const int tt = c0 + j;
+                        if (tt >= valid) break;
+                        const size_t row = (size_t)(tl.out0 + tt);
                         if (p.epilogue == EPI_STORE) {
                             ((float*)p.out)[row * p.ldo + n] = v[j];
                         } else if (p.epilogue == EPI_ADD) {
@@ -224,11 +285,12 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
                             const float gte = v[j];
                             ((__nv_bfloat16*)p.out)[row * p.ldo + n] = __float2bfloat16_rn(gte / (1.0f + expf(-gte)) * u[DUAL ? j : 0]);
                         } else {
-                            p.partial[((size_t)blockIdx.z * p.rows_total + row) * p.N + n] = v[j];
+                            p.partial[((size_t)tl.z * p.rows_total + row) * p.N + n] = v[j];
                         }
                     }
                 }
             }
+            ++nt;
         }
     }
     tc_fence_before();
@@ -271,14 +333,27 @@ int weight_map(CUtensorMap* out, const void* base, long long rows, int K) {
     return 0;
 }
 
+int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
+// n_y: row tiles, pairs, or the tile list's capacity; n_z: K slices.
 template <int BT, bool DUAL>
-int launch(const CUtensorMap& tw, const CUtensorMap& tw2, const CUtensorMap& ta, Params p, dim3 grid, cudaStream_t st) {
+int launch(const CUtensorMap& tw, const CUtensorMap& tw2, const CUtensorMap& ta, Params p, int n_y, int n_z, cudaStream_t st) {
     constexpr int stage = WM * BK * 2 * (DUAL ? 2 : 1) + BT * BK * 2;
-    // two CTAs per SM when three stages fit in half of the shared memory, else one CTA with a deeper ring
-    int stages = (110 * 1024) / stage;
-    if (stages < 3) stages = (216 * 1024) / stage;
+    // narrow token tiles (weight streaming): two CTAs per SM, each with half of the shared memory;
+    // wide ones: one CTA per SM whose ring takes all of it
+    int per_sm = BT <= 64 ? (220 * 1024) / (stage * 3) : 1;
+    per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
+    int stages = ((220 / per_sm) * 1024) / stage;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     p.stages = stages;
+    p.n_y = n_y, p.n_z = n_z;
     const size_t smem = (size_t)stages * stage + 1024;
     static bool configured = false;
     if (!configured) {
@@ -286,6 +361,9 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tw2, const CUtensorMap& ta,
             return q6k_check_launch("gemm_tc: shared memory attribute");
         configured = true;
     }
+    const long long total = (long long)((p.N + WM - 1) / WM) * n_y * n_z;
+    const int slots = sm_count() * per_sm;
+    const int grid = (int)(total < slots ? total : slots);
     gemm_tc_kernel<BT, DUAL><<<grid, 192, smem, st>>>(tw, tw2, ta, p);
     return q6k_check_launch("gemm_tc");
 }
@@ -309,20 +387,34 @@ Q6K_API int q6k_tc_token_tile(int rows, int dual) {
 static int splits_for(int rows, int N, int K, int bt) {
     const int n_tiles = (N + WM - 1) / WM, row_tiles = (rows + bt - 1) / bt, kb = (K + BK - 1) / BK;
     const int ctas = n_tiles * row_tiles;
-    if (ctas >= 120 || kb < 4) return 1;
-    int s = (240 + ctas - 1) / ctas;
+    if (ctas * 2 > sm_count() || kb < 4) return 1;
+    int s = sm_count() / ctas;                 // fill one wave of the persistent CTAs
     if (s > kb / 2) s = kb / 2;
     if (s < 1) s = 1;
     const int per = (kb + s - 1) / s;          // k-blocks per slice; the slices that are not empty:
     return (kb + per - 1) / per;
 }
 
+// Token tile and K slices of a dense product: the widest token tile that holds the rows, narrowed
+// while many rows meet so few weight tiles that half of the SMs would idle (the router at prefill);
+// K is sliced only when even that leaves most SMs without a tile (a few rows: decode).
+static void dense_plan(int rows, int N, int K, bool dual, int* bt, int* splits) {
+    int b = q6k_tc_token_tile(rows, dual);
+    const int n_tiles = (N + WM - 1) / WM;
+    while (b > 32 && rows > b && n_tiles * ((rows + b - 1) / b) * 2 < sm_count()) b /= 2;
+    *bt = b;
+    *splits = dual ? 1 : splits_for(rows, N, K, b);
+}
+
 // Number of K slices the dense call below uses for (rows, N, K).
-Q6K_API int q6k_gemm_tc_splits(int rows, int N, int K) { return splits_for(rows, N, K, q6k_tc_token_tile(rows, 0)); }
+Q6K_API int q6k_gemm_tc_splits(int rows, int N, int K) {
+    int bt, s;
+    dense_plan(rows, N, K, false, &bt, &s);
+    return s;
+}
 
 Q6K_API long long q6k_gemm_tc_workspace(int rows, int N, int K) {
-    const int bt = q6k_tc_token_tile(rows, 0);
-    const int s = splits_for(rows, N, K, bt);
+    const int s = q6k_gemm_tc_splits(rows, N, K);
     return s > 1 ? (long long)s * rows * N * 4 : 0;
 }
 
@@ -346,7 +438,8 @@ Q6K_API int q6k_gemm_tc(const void* A, long long lda, int rows_total, const void
     const bool dual = epilogue == EPI_SWIGLU;
     Q6K_REQUIRE(!dual || W2, "gemm_tc: the SwiGLU epilogue needs two weight matrices");
     const bool grouped = tile_group != nullptr;
-    if (!grouped) bt = q6k_tc_token_tile(rows_total, dual);
+    int planned_splits = 1;
+    if (!grouped) dense_plan(rows_total, N, K, dual, &bt, &planned_splits);
     Q6K_REQUIRE(bt == 16 || bt == 32 || bt == 64 || bt == 128 || (bt == 256 && !dual), "gemm_tc: token tile %d is not supported", bt);
     Q6K_REQUIRE((long long)groups * N < (1LL << 31), "gemm_tc: weight rows exceed the TMA coordinate range");
 
@@ -364,7 +457,7 @@ Q6K_API int q6k_gemm_tc(const void* A, long long lda, int rows_total, const void
     const int kb = (K + BK - 1) / BK;
     int splits = 1;
     if (!grouped && !dual) {
-        splits = splits_for(rows_total, N, K, bt);
+        splits = planned_splits;
         if (splits > 1 && (!workspace || workspace_bytes < (long long)splits * rows_total * N * 4)) splits = 1;
     }
     p.kb_per_split = (kb + splits - 1) / splits;
@@ -374,13 +467,11 @@ Q6K_API int q6k_gemm_tc(const void* A, long long lda, int rows_total, const void
         p.epilogue = EPI_PARTIAL;
     }
     const int ytiles = grouped ? max_tiles : (rows_total + bt - 1) / bt;
-    Q6K_REQUIRE(ytiles <= 65535 && splits <= 65535, "gemm_tc: %d row tiles exceed the grid limit", ytiles);
-    dim3 grid((N + WM - 1) / WM, ytiles, splits);
     int rc;
-#define GO(BT_)                                                                    \
-    case BT_:                                                                      \
-        rc = dual ? launch<(BT_ > 128 ? 128 : BT_), true>(tw, tw2, ta, p, grid, st) \
-                  : launch<BT_, false>(tw, tw2, ta, p, grid, st);                  \
+#define GO(BT_)                                                                               \
+    case BT_:                                                                                 \
+        rc = dual ? launch<(BT_ > 128 ? 128 : BT_), true>(tw, tw2, ta, p, ytiles, splits, st) \
+                  : launch<BT_, false>(tw, tw2, ta, p, ytiles, splits, st);                   \
         break;
     switch (bt) {
         GO(16) GO(32) GO(64) GO(128) GO(256)
@@ -401,9 +492,12 @@ Q6K_API int q6k_gemm_tc(const void* A, long long lda, int rows_total, const void
 // int32 [pairs] (the router's selection, flattened); pair y multiplies input row y / pair_div of A
 // (pair_div = slots per token for the gate/up product, 1 for the down product, whose input rows
 // are already per pair) with the weights of expert pair_expert[y] and writes output row y.
+// pair_order (int32 [pairs] or null): the order in which the pairs are worked on; sorted by expert
+// it lets the tiles of one expert run side by side and find its weights in L2.
 // epilogue: 0 store FP32, 2 SwiGLU -> bfloat16.
 Q6K_API int q6k_gemm_tc_pairs(const void* A, long long lda, int a_rows, const void* W, const void* W2, int groups, int N, int K,
-                              void* out, int ldo, int epilogue, const int* pair_expert, int pairs, int pair_div, cudaStream_t st) {
+                              void* out, int ldo, int epilogue, const int* pair_expert, const int* pair_order, int pairs, int pair_div,
+                              cudaStream_t st) {
     if (pairs == 0 || N == 0) return 0;
     Q6K_REQUIRE(a_rows > 0 && N > 0 && K > 0 && groups > 0 && pairs > 0 && pair_div > 0, "gemm_tc_pairs: bad sizes rows=%d N=%d K=%d pairs=%d", a_rows, N, K, pairs);
     Q6K_REQUIRE(K % 8 == 0 && lda % 8 == 0, "gemm_tc_pairs: K=%d and the row pitch %lld must be multiples of 8", K, lda);
@@ -411,7 +505,7 @@ Q6K_API int q6k_gemm_tc_pairs(const void* A, long long lda, int a_rows, const vo
     Q6K_REQUIRE(epilogue == EPI_STORE || epilogue == EPI_SWIGLU, "gemm_tc_pairs: unknown epilogue %d", epilogue);
     const bool dual = epilogue == EPI_SWIGLU;
     Q6K_REQUIRE(!dual || W2, "gemm_tc_pairs: the SwiGLU epilogue needs two weight matrices");
-    Q6K_REQUIRE(pairs <= 65535 && (long long)groups * N < (1LL << 31), "gemm_tc_pairs: too many pairs or weight rows");
+    Q6K_REQUIRE((long long)groups * N < (1LL << 31), "gemm_tc_pairs: too many weight rows");
     CUtensorMap tw, tw2, ta;
     if (int rc = weight_map(&tw, W, (long long)groups * N, K)) return rc;
     tw2 = tw;
@@ -422,6 +516,6 @@ Q6K_API int q6k_gemm_tc_pairs(const void* A, long long lda, int a_rows, const vo
     p.out = out, p.tile_group = pair_expert, p.rows_total = a_rows, p.N = N, p.K = K, p.ldo = ldo, p.epilogue = epilogue;
     p.kb_per_split = (K + BK - 1) / BK;
     p.pair_div = pair_div;
-    dim3 grid((N + WM - 1) / WM, pairs, 1);
-    return dual ? launch<16, true>(tw, tw2, ta, p, grid, st) : launch<16, false>(tw, tw2, ta, p, grid, st);
+    p.pair_order = pair_order;
+    return dual ? launch<16, true>(tw, tw2, ta, p, pairs, 1, st) : launch<16, false>(tw, tw2, ta, p, pairs, 1, st);
 }

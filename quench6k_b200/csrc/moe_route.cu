@@ -106,7 +106,7 @@ __device__ __forceinline__ void warp_topk(float* v, int E, int k, int sigmoid, i
 constexpr int SMALL_T = 16;
 __global__ void __launch_bounds__(512) router_small_kernel(const __nv_bfloat16* xn, const __nv_bfloat16* w, int T_, int E, int D, int k,
                                                            int sigmoid, int renorm, float* logits, int* sel_e, float* sel_w,
-                                                           unsigned* ticket) {
+                                                           int* order, unsigned* ticket) {
     extern __shared__ float sc[];             // the last block: [16 warps][E] scores
     __shared__ float red[16][SMALL_T];
     __shared__ int is_last;
@@ -185,6 +185,18 @@ __global__ void __launch_bounds__(512) router_small_kernel(const __nv_bfloat16* 
         }
         __syncwarp();
         warp_topk(v, E, k, sigmoid, renorm, total, sel_e + (size_t)t * k, sel_w + (size_t)t * k);
+    }
+    // pairs sorted by expert (stable): tiles of one expert run side by side and share its weights in L2
+    __syncthreads();
+    const int pairs = T_ * k;
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = sel_e[p];
+        int rank = 0;
+        for (int q = 0; q < pairs; ++q) {
+            const int eq = sel_e[q];
+            rank += (eq < e) || (eq == e && q < p);
+        }
+        order[rank] = p;
     }
     if (threadIdx.x == 0) *ticket = 0;          // ready for the next launch
 }
@@ -283,14 +295,15 @@ Q6K_API int q6k_route(const float* logits, int T_, int E, int k, int sigmoid, in
 
 // xn: bfloat16 [T, D], T <= 16, D a multiple of 8; w: bfloat16 [E, D]; logits: FP32 [T, E] scratch;
 // ticket: one zeroed 32-bit word that the kernel leaves zeroed.
+// order: int32 [T*k], the pairs (token * k + slot) sorted by expert, ties in pair order.
 Q6K_API int q6k_router_small(const void* xn, const void* w, int T_, int E, int D, int k, int sigmoid, int renorm, float* logits,
-                             int* sel_e, float* sel_w, unsigned* ticket, cudaStream_t st) {
+                             int* sel_e, float* sel_w, int* order, unsigned* ticket, cudaStream_t st) {
     if (T_ == 0) return 0;
     Q6K_REQUIRE(T_ > 0 && T_ <= SMALL_T, "router_small: %d tokens exceed %d", T_, SMALL_T);
     Q6K_REQUIRE(E > 0 && k > 0 && k <= E && E <= 704, "router_small: bad sizes E=%d k=%d (at most 704 experts)", E, k);
     Q6K_REQUIRE(D > 0 && D % 8 == 0 && ((uintptr_t)xn & 15) == 0 && ((uintptr_t)w & 15) == 0, "router_small: D=%d must be a multiple of 8 and the operands 16-byte aligned", D);
     router_small_kernel<<<E, 512, 16 * E * sizeof(float), st>>>((const __nv_bfloat16*)xn, (const __nv_bfloat16*)w, T_, E, D, k,
-                                                                       sigmoid, renorm, logits, sel_e, sel_w, ticket);
+                                                                       sigmoid, renorm, logits, sel_e, sel_w, order, ticket);
     return q6k_check_launch("router_small");
 }
 

@@ -423,7 +423,8 @@ _tickets = {}
 
 
 def router_small(xn: torch.Tensor, w: torch.Tensor, k: int, scoring: str, renorm: bool):
-    """Router logits, scores and top-k of at most 16 tokens in one launch: (sel_e [T, k], sel_w [T, k])."""
+    """Router logits, scores and top-k of at most 16 tokens in one launch:
+    (sel_e [T, k], sel_w [T, k], order [T*k]: the pairs sorted by expert)."""
     _need(xn, "xn", torch.bfloat16)
     _need(w, "w", torch.bfloat16)
     T, D = xn.shape
@@ -437,12 +438,14 @@ def router_small(xn: torch.Tensor, w: torch.Tensor, k: int, scoring: str, renorm
     logits = torch.empty((T, E), dtype=torch.float32, device=dev)
     sel_e = torch.empty((T, k), dtype=torch.int32, device=dev)
     sel_w = torch.empty((T, k), dtype=torch.float32, device=dev)
+    order = torch.empty(T * k, dtype=torch.int32, device=dev)
     _call("q6k_router_small", _ptr(xn), _ptr(w), _i(T), _i(E), _i(D), _i(k), _i(1 if scoring == "sigmoid" else 0),
-          _i(1 if renorm else 0), _ptr(logits), _ptr(sel_e), _ptr(sel_w), _ptr(ticket), _stream())
-    return sel_e, sel_w
+          _i(1 if renorm else 0), _ptr(logits), _ptr(sel_e), _ptr(sel_w), _ptr(order), _ptr(ticket), _stream())
+    return sel_e, sel_w, order
 
 
-def gemm_tc_pairs(a: torch.Tensor, w: torch.Tensor, pair_expert: torch.Tensor, pair_div: int, w2: Optional[torch.Tensor] = None) -> torch.Tensor:
+def gemm_tc_pairs(a: torch.Tensor, w: torch.Tensor, pair_expert: torch.Tensor, pair_div: int, w2: Optional[torch.Tensor] = None,
+                  order: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Expert products of a decode step without a permutation: pair y (= token * slots + slot)
     multiplies row y // pair_div of `a` with expert pair_expert[y]; output row y.  With w2 the
     SwiGLU epilogue (bfloat16 output), else FP32."""
@@ -450,6 +453,8 @@ def gemm_tc_pairs(a: torch.Tensor, w: torch.Tensor, pair_expert: torch.Tensor, p
         raise KernelError("gemm_tc_pairs: operands must be bfloat16, K a multiple of 8, weights [experts, N, K]")
     _need(pair_expert, "pair_expert", torch.int32)
     pairs = pair_expert.numel()
+    if order is not None:
+        _need(order, "order", torch.int32, (pairs,))
     G, N, K = w.shape
     if a.shape[1] != K:
         raise KernelError(f"gemm_tc_pairs: a has K={a.shape[1]}, w has K={K}")
@@ -457,7 +462,8 @@ def gemm_tc_pairs(a: torch.Tensor, w: torch.Tensor, pair_expert: torch.Tensor, p
         _need(w2, "w2", torch.bfloat16, w.shape)
     out = torch.empty((pairs, N), dtype=torch.bfloat16 if w2 is not None else torch.float32, device=a.device)
     _call("q6k_gemm_tc_pairs", _ptr(a), _ll(a.stride(0)), _i(a.shape[0]), _ptr(w), _ptr(w2), _i(G), _i(N), _i(K), _ptr(out),
-          _i(out.stride(0)), _i(EPI_SWIGLU if w2 is not None else EPI_STORE), _ptr(pair_expert), _i(pairs), _i(pair_div), _stream())
+          _i(out.stride(0)), _i(EPI_SWIGLU if w2 is not None else EPI_STORE), _ptr(pair_expert), _ptr(order), _i(pairs), _i(pair_div),
+          _stream())
     return out
 
 

@@ -77,9 +77,9 @@ class RoutedExperts(FeedForward):
                 and self.I % 8 == 0):
             # a decode step: router and top-k in one launch, then one weight tile stream per
             # (token, slot) pair straight from the selection, no permutation and no gather
-            sel_e, sel_w = ops.router_small(xn, self.w_router, self.k, self.scoring, self.renorm)
-            act = ops.gemm_tc_pairs(xn, self.w_gate, sel_e, self.k, w2=self.w_up)         # [pairs, I]
-            y = ops.gemm_tc_pairs(act, self.w_down, sel_e, 1)                              # FP32 [pairs, D]
+            sel_e, sel_w, order = ops.router_small(xn, self.w_router, self.k, self.scoring, self.renorm)
+            act = ops.gemm_tc_pairs(xn, self.w_gate, sel_e, self.k, w2=self.w_up, order=order)      # [pairs, I]
+            y = ops.gemm_tc_pairs(act, self.w_down, sel_e, 1, order=order)                           # FP32 [pairs, D]
             ops.combine(y, None, sel_w, out)
             if self.shared is not None:
                 self.shared.forward(xn, ctx, out)

@@ -361,15 +361,18 @@ def test_decode_moe_path(scoring, renorm, T, E, k, D, I):
     wr = _t(E, D, dtype=torch.bfloat16, seed=1, scale=0.02)      # small: a saturated sigmoid would tie in FP32
     wg, wu = _t(E, I, D, dtype=torch.bfloat16, seed=2, scale=0.2), _t(E, I, D, dtype=torch.bfloat16, seed=3, scale=0.2)
     wd = _t(E, D, I, dtype=torch.bfloat16, seed=4, scale=0.2)
-    sel_e, sel_w = ops.router_small(x, wr, k, scoring, renorm)
+    sel_e, sel_w, order = ops.router_small(x, wr, k, scoring, renorm)
+    flat = sel_e.flatten().cpu()
+    assert torch.equal(order.cpu().long(), torch.sort(flat, stable=True).indices)
     logits = x.double().cpu() @ wr.double().cpu().T
     ref_e, ref_w = P.route(logits, scoring, k, renorm)
     assert torch.equal(sel_e.cpu().long(), ref_e)
     assert (sel_w.double().cpu() - ref_w).abs().max() <= 1e-4 * ref_w.abs().max()
-    again_e, again_w = ops.router_small(x, wr, k, scoring, renorm)          # the ticket was left ready
+    again_e, again_w, _ = ops.router_small(x, wr, k, scoring, renorm)       # the ticket was left ready
     assert torch.equal(again_e, sel_e) and torch.equal(again_w, sel_w)
-    act = ops.gemm_tc_pairs(x, wg, sel_e, k, w2=wu)
-    y = ops.gemm_tc_pairs(act, wd, sel_e, 1)
+    act = ops.gemm_tc_pairs(x, wg, sel_e, k, w2=wu, order=order)
+    y = ops.gemm_tc_pairs(act, wd, sel_e, 1, order=order)
+    assert torch.equal(act, ops.gemm_tc_pairs(x, wg, sel_e, k, w2=wu))      # the order of work does not change a value
     assert ops.tc_status() == 0
     for p in range(T * k):
         e, t = int(sel_e.flatten()[p]), p // k

@@ -8,11 +8,11 @@
 // launch covers rows of many requests through a tile list; head size and group size are
 // parameters (head size 64 or 128 here; other sizes run on the generic kernel).
 //
-// A tile is up to ROWS = 16 (narrow) or 64 (wide) query rows of one request and one KV head:
+// A tile is up to ROWS = 16 (narrow) or 128 (wide) query rows of one request and one KV head:
 // row = token_in_tile * G + head_in_group.  Key tiles hold 64 keys, aligned to multiples of 64 of
 // the key index.  Narrow tiles (decode): the 4 warps share the 16 rows and split each key tile
 // (16 keys each), then merge their partial softmax states through shared memory.  Wide tiles
-// (prompt portions): each warp owns 16 rows and walks all 64 keys of a tile.
+// (prompt portions): 8 warps, each owning 16 rows and walking all 64 keys of a tile.
 // K and V tiles travel through a ring of shared-memory stages.  With pages of 8 rows or a multiple
 // (the usual case) a producer warp brings each page's [rows x 64] boxes in by TMA (one tensor map
 // over a layer's K or V pool, 128-byte swizzle, zero fill for keys that have no page) and signals
@@ -92,9 +92,11 @@ template <int HD> __device__ __forceinline__ uint32_t sw(int r, int c) { return 
 __device__ __forceinline__ uint32_t swk(int r, int c) { return (uint32_t)((c >> 3) * (KT * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)); }
 
 template <int HD, bool WIDE, bool TMA>
-__global__ void __launch_bounds__(TMA ? 160 : 128) attention_mma_kernel(const __grid_constant__ CUtensorMap tm_k,
+__global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0)) attention_mma_kernel(const __grid_constant__ CUtensorMap tm_k,
                                                                         const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
-    constexpr int ROWS = WIDE ? 64 : 16;
+    constexpr int CW = WIDE ? 8 : 4;         // consumer warps
+    constexpr int CT = CW * 32;              // consumer threads
+    constexpr int ROWS = WIDE ? 128 : 16;
     constexpr int CH = HD / 8;               // 16-byte chunks per row
     constexpr int KW = WIDE ? KT : 16;       // keys of a tile this warp handles
     constexpr int NB = KW / 8;               // score n-blocks per warp
@@ -124,15 +126,15 @@ __global__ void __launch_bounds__(TMA ? 160 : 128) attention_mma_kernel(const __
     if (TMA && tid == 0) {
         for (int s2 = 0; s2 < STAGES; ++s2) {
             mbar_init(full0 + 8 * s2, 1);
-            mbar_init(empty0 + 8 * s2, 4);
+            mbar_init(empty0 + 8 * s2, CW);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_v) : "memory");
     }
     // ---- Q tile into shared memory (zero rows past the tile's tokens)
-    if (warp < 4) {
-        for (int idx = tid; idx < ROWS * CH; idx += 128) {
+    if (warp < CW) {
+        for (int idx = tid; idx < ROWS * CH; idx += CT) {
             const int r = idx / CH, c = idx % CH, tt = r / G, hg = r % G;
             const bool valid = tt < ntok;
             const __nv_bfloat16* src = p.q + ((size_t)(tok0 + (valid ? tt : 0)) * p.Hq + kh * G + hg) * HD + c * 8;
@@ -140,7 +142,7 @@ __global__ void __launch_bounds__(TMA ? 160 : 128) attention_mma_kernel(const __
         }
     }
     auto load_kv = [&](int stage, int kt) {      // the cp.async path: every consumer thread copies its chunks
-        for (int idx = tid; idx < KT * CH; idx += 128) {
+        for (int idx = tid; idx < KT * CH; idx += CT) {
             const int r = idx / CH, c = idx % CH, j = kt * KT + r;
             const bool in = j >= k_lo && j <= pos_last;
             int page = in ? bt[j / p.page_size] : -1;
@@ -155,7 +157,7 @@ __global__ void __launch_bounds__(TMA ? 160 : 128) attention_mma_kernel(const __
     cp_async_wait<0>();
     __syncthreads();
 
-    if (TMA && warp == 4) {
+    if (TMA && warp == CW) {
         // ---- producer: one thread brings every tile of this CTA's key range into the ring
         if (lane == 0) {
             const int ps = p.page_size, box = ps < KT ? ps : KT;        // keys per TMA box
@@ -217,9 +219,9 @@ __global__ void __launch_bounds__(TMA ? 160 : 128) attention_mma_kernel(const __
                 // the last page came in whole: rows past the last key hold whatever the page held
                 // before (masked scores ignore K, but 0 * V must not meet a stale NaN): clear them
                 const int r0 = pos_last + 1 - kt * KT;
-                for (int idx = r0 * CH + tid; idx < KT * CH; idx += 128)
+                for (int idx = r0 * CH + tid; idx < KT * CH; idx += CT)
                     *reinterpret_cast<uint4*>(smem + (v_s - k_s) + stage * TILE_BYTES + swk(idx / CH, idx % CH)) = make_uint4(0, 0, 0, 0);
-                asm volatile("bar.sync 1, 128;" ::: "memory");
+                asm volatile("bar.sync 1, %0;" ::"n"(CT) : "memory");
             }
         } else {
             if (kt + 1 < t_end) load_kv(stage ^ 1, kt + 1);
@@ -295,7 +297,7 @@ __global__ void __launch_bounds__(TMA ? 160 : 128) attention_mma_kernel(const __
             if (lane == 0) mbar_arrive(empty0 + 8 * stage);
         } else {
             cp_async_wait<0>();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(CT) : "memory");
         }
     }
     // row sums live per thread: add the quad's
@@ -432,7 +434,7 @@ int pool_map(CUtensorMap* out, const void* base, long long rows, int hd, int box
 
 template <int HD, bool WIDE, bool TMA>
 int launch(const AttnParams& p, const CUtensorMap& tk, const CUtensorMap& tv, int n_tiles, cudaStream_t st) {
-    constexpr int ROWS = WIDE ? 64 : 16;
+    constexpr int ROWS = WIDE ? 128 : 16;
     constexpr int STAGES = TMA ? (HD == 128 ? 3 : 4) : 2;
     const size_t ring = 2 * STAGES * KT * HD * 2 + ROWS * HD * 2;
     const size_t red = WIDE ? 0 : 4 * 16 * (HD + 2) * sizeof(float);
@@ -443,7 +445,7 @@ int launch(const AttnParams& p, const CUtensorMap& tk, const CUtensorMap& tv, in
             return q6k_check_launch("attention_mma: shared memory attribute");
         configured = true;
     }
-    attention_mma_kernel<HD, WIDE, TMA><<<dim3(p.max_splits, p.Hkv, n_tiles), TMA ? 160 : 128, smem, st>>>(tk, tv, p);
+    attention_mma_kernel<HD, WIDE, TMA><<<dim3(p.max_splits, p.Hkv, n_tiles), (WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0), smem, st>>>(tk, tv, p);
     if (int rc = q6k_check_launch("attention_mma")) return rc;
     if (p.max_splits > 1) {
         attention_merge_kernel<HD><<<dim3(n_tiles, p.Hkv, ROWS), HD, 0, st>>>(p);
@@ -460,11 +462,11 @@ int launch_hd(const AttnParams& p, const CUtensorMap& tk, const CUtensorMap& tv,
 
 }  // namespace
 
-// Rows per tile for a group size: 16 (narrow) or 64 (wide) query rows hold rows/G tokens.
-Q6K_API int q6k_attention_mma_supported(int hd, int G, int wide) { return (hd == 64 || hd == 128) && G >= 1 && G <= (wide ? 64 : 16); }
+// Rows per tile for a group size: 16 (narrow) or 128 (wide) query rows hold rows/G tokens.
+Q6K_API int q6k_attention_mma_supported(int hd, int G, int wide) { return (hd == 64 || hd == 128) && G >= 1 && G <= (wide ? 128 : 16); }
 
 // q: bfloat16 [T, Hq, hd]; pages: bfloat16 [*, Hkv, page_size, hd]; tiles: tile_tok0/tile_ntok [n_tiles], the
-// tokens of a tile being consecutive positions of one request, at most (wide ? 64 : 16) / G of them.
+// tokens of a tile being consecutive positions of one request, at most (wide ? 128 : 16) / G of them.
 // part_o: FP32 [T*Hq*max_splits*hd], part_ml: FP32 [T*Hq*max_splits*2] (unused when max_splits == 1).
 Q6K_API int q6k_attention_status() {
     int v = -1;

@@ -376,7 +376,7 @@ def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                   scale: Optional[float] = None) -> torch.Tensor:
     """bfloat16 tensor-core attention over the pages.  Tiles: tile_tok0[i] is the first row and
     tile_ntok[i] the number of tokens (consecutive positions of one request, at most
-    (64 if wide else 16) // G) of tile i.  max_splits: upper bound of key splits per tile."""
+    (128 if wide else 16) // G) of tile i.  max_splits: upper bound of key splits per tile."""
     _need(q, "q", torch.bfloat16)
     T, Hq, hd = q.shape
     _need(k_pages, "k_pages", torch.bfloat16)

@@ -87,7 +87,7 @@ class Attention(Mixer):
         wide = ctx.max_q_len > max(1, 16 // G) or not ops.attention_mma_supported(self.hd, G, False)
         if not ops.attention_mma_supported(self.hd, G, wide):
             return ops.attention_generic(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, self.window, self.sinks, self.scale)
-        tok0, ntok, n_tiles = ctx.query_tiles((64 if wide else 16) // G)
+        tok0, ntok, n_tiles = ctx.query_tiles((128 if wide else 16) // G)
         # split the keys over CTAs until the GPU is full, and no further: one wave of resident CTAs
         # (a second, partly filled wave would cost as much as a full one)
         span = ctx.max_context if self.window is None else min(ctx.max_context, self.window + ctx.max_q_len)
@@ -102,7 +102,7 @@ class Attention(Mixer):
         if key not in self.__dict__:
             props = torch.cuda.get_device_properties(self.rt.device)
             stages = 3 if self.hd == 128 else 4
-            smem = 2 * stages * 64 * self.hd * 2 + (64 if wide else 16) * self.hd * 2 + 2048
+            smem = 2 * stages * 64 * self.hd * 2 + (128 if wide else 16) * self.hd * 2 + 2048
             per_sm = max(1, min(2 if self.hd == 128 else 3, (props.shared_memory_per_multiprocessor - 1024) // smem))
             self.__dict__[key] = per_sm * props.multi_processor_count
         return self.__dict__[key]

@@ -341,7 +341,7 @@ def test_attention_mma(Hq, Hkv, hd, ps, window, sinks, mode):
     ctx = helpers.make_context(q_lens, starts, [tables])
     q = torch.cat([qs[r][starts[r]:] for r in range(len(lens))]).contiguous().to(DEV)
     wide = mode == "portions"
-    tok0, ntok, n_tiles = ctx.query_tiles((64 if wide else 16) // G)
+    tok0, ntok, n_tiles = ctx.query_tiles((128 if wide else 16) // G)
     want = torch.cat([refs[r][0][starts[r]:] for r in range(len(lens))]).reshape(-1, Hq * hd)
     for max_splits in (1, 4, 64):
         out = ops.attention_mma(q, kp.to(DEV), vp.to(DEV), bt, ctx.req_of_token, ctx.positions, tok0, ntok, wide, window, sk,

@@ -73,11 +73,12 @@ class ModelRunner:
                                               torch.zeros(shape, dtype=rt.dtype, device=rt.device), page_size))
         self.states = [None if s is None else torch.zeros((max_requests, *s), dtype=torch.float32, device=rt.device)
                        for s in model.state_shapes()]
-        # decode-only steps (one token per request, its logits wanted) replay a CUDA graph per
-        # (number of requests, block-table widths); the reference captures one per sequence and
-        # token count (crates/engine/src/flint.rs:735-771)
+        # steps whose shape repeats (above all decode steps) replay a CUDA graph per shape; the
+        # reference captures one per sequence and token count (crates/engine/src/flint.rs:735-771)
         self.cuda_graphs = cuda_graphs and model.graph_safe()
         self._graphs: Dict = {}
+        self._shapes_seen: Dict = {}
+        self.max_graphs = 64
         self.graph_replays = 0
         self._pinned: Optional[torch.Tensor] = None
         self._pinned_free: Optional[torch.cuda.Event] = None      # set once the last upload has left the pinned block
@@ -213,23 +214,34 @@ class ModelRunner:
         return [max(1, max(mgr.table_len(e.rid, g) for e in entries)) for g in range(len(self.group_specs))]
 
     def _forward(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
-        """Eager for general steps; decode-only steps go through a CUDA graph per step shape."""
-        decode = self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries)
-        if not decode:
+        """Eager for steps of a new shape; a step whose shape (tokens and wanted places per entry,
+        block-table widths) has been seen before replays a CUDA graph recorded for that shape.
+        Decode steps are recorded at once; other shapes when they come a second time (a prompt
+        cut into equal portions repeats its shape, a one-off mix does not)."""
+        if not self.cuda_graphs:
             return self.model.forward(self._context(entries), self.caches, self.states)
         widths = [(w + 63) // 64 * 64 for w in self._widths(entries)]
-        key = (len(entries), tuple(widths))
+        shape = tuple((len(e.tokens), tuple(e.want)) for e in entries)
+        key = (shape, tuple(widths))
         slot = self._graphs.get(key)
         if slot is None:
-            # first step of this shape: run it eagerly from a static block, then record the same
-            # launches into a graph (recording executes nothing)
-            R = len(entries)
-            total = 3 * R + (R + 1) + 2 * R + R + sum(R * w for w in widths)
+            decode = all(len(e.tokens) == 1 for e in entries)
+            seen = self._shapes_seen.get(key, 0) + 1
+            self._shapes_seen[key] = seen
+            if not decode and (seen < 2 or len(self._graphs) >= self.max_graphs):
+                if len(self._shapes_seen) > 4096:
+                    self._shapes_seen.clear()
+                return self.model.forward(self._context(entries), self.caches, self.states)
+            # run the step eagerly from a static block, then record the same launches into a graph
+            # (recording executes nothing)
+            R, T = len(entries), sum(len(e.tokens) for e in entries)
+            n_want = sum(len(e.want) for e in entries)
+            total = 3 * T + (R + 1) + 2 * R + n_want + sum(R * w for w in widths)
             static = torch.empty(total, dtype=torch.int32, device=self.rt.device)
             ctx = self._context(entries, widths, static)
             ctx.max_context = max(widths) * self.page_size          # launch plans must hold for every replay
             logits = self.model.forward(ctx, self.caches, self.states)
-            result = logits.clone()
+            result = logits.clone() if logits is not None else None
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count

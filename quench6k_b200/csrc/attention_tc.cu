@@ -1,0 +1,447 @@
+// bfloat16 attention for prompt portions on the 5th-generation tensor cores: both products of
+// every key tile (S = Q K^T and O += P V) are tcgen05.mma with their accumulators in tensor
+// memory; K and V pages come in by TMA.  sm_100a only; head size 128.
+//
+// Arithmetic as the reference's attn_kernel (crates/cuda/kernels/flint.cu:211-529): scores in base 2
+// with scale * log2 e folded in, causal and window mask per row, online softmax per key tile,
+// probabilities rounded to bfloat16 before they are summed, the sink added to the denominator at
+// the end (:505-526).  The reference computes it with mma.sync tiles of 64 or 128 rows; here:
+//
+// A CTA takes one tile of up to 128 query rows (row = token_in_tile * G + head_in_group, one
+// request, one KV head) and walks key tiles of 128 keys.
+//   warp 0      producer: TMA boxes [page rows x 64] of the K and V pages of a key tile into a
+//               two-stage ring ([2 column halves][128 keys][128 bytes], 128-byte swizzle; keys
+//               without a page are zero-filled through an out-of-range coordinate)
+//   warp 1      one thread issues the MMAs: S_i = Q K_i^T (8 x K=16, both operands K-major) into one
+//               of two S buffers in tensor memory, one tile ahead of the softmax; then, when P_i is
+//               in shared memory, O += P_i V_i (8 x K=16, V as an MN-major operand)
+//   warps 2-5   softmax: one thread per query row reads its row of S from tensor memory
+//               (tcgen05.ld, no shuffles), keeps the running max and sum, rescales O in tensor
+//               memory when the max moved (tcgen05.ld / tcgen05.st), writes P as bfloat16 into shared
+//               memory in the K-major swizzled layout the MMA reads, and finally normalises O
+// Tensor memory: S0 at columns 0..127, S1 at 128..255, O at 256..383.
+// Every wait on an mbarrier is bounded and records a code in a status word when it runs out.
+#include <map>
+#include <tuple>
+
+#include "common.cuh"
+#include "tma.cuh"
+
+namespace {
+
+constexpr int HD = 128;                      // head size
+constexpr int BM = 128;                      // query rows per tile
+constexpr int BN = 128;                      // keys per key tile
+constexpr float LOG2E = 1.4426950408889634f;
+constexpr uint32_t HALF_BYTES = 128 * 128;   // one 64-column half of a [128 x 128] bf16 tile
+constexpr uint32_t TILE_BYTES = 2 * HALF_BYTES;
+
+struct TcAttnParams {
+    const __nv_bfloat16* q;                  // [T, Hq, HD]
+    const int* block_table;                  // [R, max_blocks]
+    const int* req_of_token;
+    const int* positions;
+    const int* tile_tok0;
+    const int* tile_ntok;
+    const float* sinks;                      // [Hq] or null
+    __nv_bfloat16* out;                      // [T, Hq*HD]
+    int max_blocks, page_size, window, Hq, Hkv, G, pool_rows;
+    float scale_log2;
+};
+
+__device__ int g_attn_tc_status = 0;
+
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+
+// K-major operand, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// MN-major operand (V: for one key the head dimensions are contiguous), 128-byte swizzle: 64
+// elements of N per 128-byte row, the next 64 elements of N HALF_BYTES further (leading offset),
+// 8-key groups 1024 bytes apart (stride offset).
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(HALF_BYTES >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// D FP32, A and B bfloat16, M = 128, N = 128; b_mn: B is MN-major.
+__host__ __device__ constexpr uint32_t idesc_128x128(bool b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn ? 1u : 0u) << 16) | ((uint32_t)(128 >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}" ::"r"(tmem_d),
+        "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, "
+        "%20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, "
+        "%20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+        "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+        "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+        "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+        "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+        "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+        "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// Byte offset of 16-byte chunk c (0..15) of row r in a [2 halves][128 rows][128 bytes] swizzled tile.
+__device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)((c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)); }
+
+__global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                                                           const TcAttnParams p) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    // [Q][P][K0][V0][K1][V1], each a [2][128][128 B] tile of 32 KB
+    const uint32_t q_s = smem_u32(smem), p_s = q_s + TILE_BYTES, kv_s = p_s + TILE_BYTES;
+    __shared__ __align__(8) uint64_t bars[10];
+    __shared__ uint32_t tmem_slot;
+    const uint32_t kv_full0 = smem_u32(&bars[0]), kv_empty0 = smem_u32(&bars[2]), s_full0 = smem_u32(&bars[4]);
+    const uint32_t p_full = smem_u32(&bars[6]), pv_done = smem_u32(&bars[7]), q_full = smem_u32(&bars[8]);
+
+    const int tile = blockIdx.x, kh = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = p.G;
+    const int tok0 = p.tile_tok0[tile], ntok = p.tile_ntok[tile];
+    const int pos_first = p.positions[tok0], pos_last = pos_first + ntok - 1;
+    const int* bt = p.block_table + (size_t)p.req_of_token[tok0] * p.max_blocks;
+    const int k_lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    const int first_tile = k_lo / BN, n_tiles = pos_last / BN + 1 - first_tile;
+
+    if (tid == 0) {
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(kv_full0 + 8 * s, 1);
+            mbar_init(kv_empty0 + 8 * s, 1);
+            mbar_init(s_full0 + 8 * s, 1);
+        }
+        mbar_init(p_full, 128);
+        mbar_init(pv_done, 1);
+        mbar_init(q_full, 128);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_v) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = tmem_slot;
+    const uint32_t tmem_o = tmem + 256;
+
+    if (warp == 0) {
+        // ---- producer
+        if (lane == 0) {
+            const int ps = p.page_size, box = ps < BN ? ps : BN;
+            for (int i = 0; i < n_tiles; ++i) {
+                const int s = i & 1;
+                if (!mbar_wait(kv_empty0 + 8 * s, ((i >> 1) & 1) ^ 1)) {
+                    atomicExch(&g_attn_tc_status, 1);
+                    break;
+                }
+                const uint32_t fb = kv_full0 + 8 * s;
+                mbar_expect_tx(fb, 2 * TILE_BYTES);
+                const int j0 = (first_tile + i) * BN;
+                const uint32_t k_dst = kv_s + s * 2 * TILE_BYTES, v_dst = k_dst + TILE_BYTES;
+                for (int b = 0; b < BN / box; ++b) {
+                    const int j = j0 + b * box;
+                    int y = p.pool_rows;                                 // out of range: zeros
+                    if (j + box > k_lo && j <= pos_last) {
+                        const int page = bt[j / ps];
+                        if (page >= 0) y = (page * p.Hkv + kh) * ps + j % ps;
+                    }
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t off = h * HALF_BYTES + b * box * 128;
+                        tma_load_2d(k_dst + off, &tm_k, h * 64, y, fb);
+                        tma_load_2d(v_dst + off, &tm_v, h * 64, y, fb);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = idesc_128x128(false), idesc_o = idesc_128x128(true);
+            bool ok = mbar_wait(q_full, 0);
+            if (!ok) atomicExch(&g_attn_tc_status, 2);
+            auto issue_s = [&](int i) -> bool {
+                const int s = i & 1;
+                if (!mbar_wait(kv_full0 + 8 * s, (i >> 1) & 1)) {
+                    atomicExch(&g_attn_tc_status, 3);
+                    return false;
+                }
+                tc_fence_after();
+                const uint32_t k_src = kv_s + s * 2 * TILE_BYTES;
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+                    umma(tmem + s * BN, desc_k_major(q_s + off), desc_k_major(k_src + off), idesc_s, k != 0);
+                }
+                umma_commit(s_full0 + 8 * s);
+                return true;
+            };
+            if (ok) ok = issue_s(0);
+            for (int i = 0; i < n_tiles && ok; ++i) {
+                if (i + 1 < n_tiles) ok = issue_s(i + 1);           // one tile ahead of the softmax
+                if (!ok) break;
+                if (!mbar_wait(p_full, i & 1)) {
+                    atomicExch(&g_attn_tc_status, 4);
+                    break;
+                }
+                tc_fence_after();
+                const int s = i & 1;
+                const uint32_t v_src = kv_s + s * 2 * TILE_BYTES + TILE_BYTES;
+#pragma unroll
+                for (int k = 0; k < BN / 16; ++k) {
+                    // A: P, K-major over the keys; B: V, MN-major, 16 keys = 2048 bytes per step
+                    const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
+                    umma(tmem_o, desc_k_major(p_s + a_off), desc_mn_major(v_src + k * 2048), idesc_o, (i | k) != 0);
+                }
+                umma_commit(kv_empty0 + 8 * s);
+                umma_commit(pv_done);
+            }
+        }
+    } else {
+        // ---- softmax, correction, epilogue: thread = query row
+        const int quarter = warp & 3, row = quarter * 32 + lane, st = tid - 64;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        // Q tile (zero rows past the tile's tokens), by cp.async into the swizzled layout
+        for (int idx = st; idx < BM * 16; idx += 128) {
+            const int r = idx >> 4, c = idx & 15, tt = r / G, hg = r % G;
+            const bool valid = tt < ntok;
+            const __nv_bfloat16* src = p.q + ((size_t)(tok0 + (valid ? tt : 0)) * p.Hq + kh * G + hg) * HD + c * 8;
+            cp_async16(q_s + swz(r, c), src, valid);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_arrive(q_full);
+
+        const int tt = row / G, hg = row % G;
+        const bool row_valid = tt < ntok;
+        const int pos = pos_first + tt;
+        const int lim_hi = row_valid ? pos : -1, lim_lo = p.window > 0 ? pos - p.window + 1 : 0;
+        float m = -INFINITY, l = 0.0f;
+        bool ok = true;
+        for (int i = 0; i < n_tiles; ++i) {
+            const int sb = i & 1, j0 = (first_tile + i) * BN;
+            if (!mbar_wait(s_full0 + 8 * sb, (i >> 1) & 1)) {
+                if (lane == 0) atomicExch(&g_attn_tc_status, 5);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t s_addr = tmem + lane_base + sb * BN;
+            // pass 1: the row's maximum over this tile
+            float mx = m;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                float v[32];
+                tmem_ld32(s_addr + c * 32, v);
+#pragma unroll
+                for (int x = 0; x < 32; ++x) {
+                    const int j = j0 + c * 32 + x;
+                    if (j <= lim_hi && j >= lim_lo) mx = fmaxf(mx, v[x] * p.scale_log2);
+                }
+            }
+            const float corr = mx == -INFINITY ? 1.0f : exp2f(m - mx);
+            // P and O of the previous tile must be consumed before either is touched
+            if (i > 0 && !mbar_wait(pv_done, (i - 1) & 1)) {
+                if (lane == 0) atomicExch(&g_attn_tc_status, 6);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            if (i > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+#pragma unroll 1
+                for (int c = 0; c < HD / 32; ++c) {
+                    float o[32];
+                    tmem_ld32(tmem_o + lane_base + c * 32, o);
+#pragma unroll
+                    for (int x = 0; x < 32; ++x) o[x] *= corr;
+                    tmem_st32(tmem_o + lane_base + c * 32, o);
+                }
+                tmem_st_wait();
+            }
+            // pass 2: probabilities, rounded to bfloat16 before they are summed, into shared memory
+            float sum = 0.0f;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                float v[32];
+                tmem_ld32(s_addr + c * 32, v);
+                uint32_t packed[16];
+#pragma unroll
+                for (int x = 0; x < 32; x += 2) {
+                    const int j = j0 + c * 32 + x;
+                    const bool ok0 = j <= lim_hi && j >= lim_lo, ok1 = j + 1 <= lim_hi && j + 1 >= lim_lo;
+                    const float p0 = ok0 ? exp2f(v[x] * p.scale_log2 - mx) : 0.0f;
+                    const float p1 = ok1 ? exp2f(v[x + 1] * p.scale_log2 - mx) : 0.0f;
+                    const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+                    const float2 pf = __bfloat1622float2(pb);
+                    sum += pf.x + pf.y;
+                    packed[x >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
+                }
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4)           // 32 keys = 4 chunks of 16 bytes
+                    *reinterpret_cast<uint4*>(smem + (p_s - q_s) + swz(row, c * 4 + q4)) =
+                        make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+            }
+            l = l * corr + sum;
+            m = mx;
+            if (i == n_tiles - 1 && (pos_last + 1) % BN != 0) {
+                // the last page came in whole: clear the V rows past the last key (0 * stale NaN)
+                if (!mbar_wait(kv_full0 + 8 * (i & 1), (i >> 1) & 1)) {
+                    if (lane == 0) atomicExch(&g_attn_tc_status, 7);
+                    ok = false;
+                    break;
+                }
+                const uint32_t v_off = (kv_s - q_s) + (i & 1) * 2 * TILE_BYTES + TILE_BYTES;
+                const int r0 = pos_last + 1 - j0;
+                for (int idx = r0 * 16 + st; idx < BN * 16; idx += 128)
+                    *reinterpret_cast<uint4*>(smem + v_off + swz(idx >> 4, idx & 15)) = make_uint4(0, 0, 0, 0);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            mbar_arrive(p_full);
+        }
+        if (ok && n_tiles > 0) {
+            if (!mbar_wait(pv_done, (n_tiles - 1) & 1)) {
+                if (lane == 0) atomicExch(&g_attn_tc_status, 8);
+                ok = false;
+            }
+            tc_fence_after();
+        }
+        if (ok) {
+            // every lane takes part in the aligned tensor-memory loads; only rows of real tokens store
+            float osc = 1.0f, den = l;
+            if (p.sinks && row_valid) {
+                const float sk = p.sinks[kh * G + hg] * LOG2E, Mx = fmaxf(m, sk);
+                osc = exp2f(m - Mx);
+                den = l * osc + exp2f(sk - Mx);
+            }
+            const float inv = row_valid ? osc / den : 0.0f;
+            __nv_bfloat16* dst = p.out + ((size_t)(tok0 + (row_valid ? tt : 0)) * p.Hq + kh * G + hg) * HD;
+#pragma unroll 1
+            for (int c = 0; c < HD / 32; ++c) {
+                float o[32];
+                tmem_ld32(tmem_o + lane_base + c * 32, o);
+                uint32_t packed[16];
+#pragma unroll
+                for (int x = 0; x < 32; x += 2) {
+                    const __nv_bfloat162 pb = __floats2bfloat162_rn(o[x] * inv, o[x + 1] * inv);
+                    packed[x >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
+                }
+                if (row_valid) {
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4)
+                        *reinterpret_cast<uint4*>(dst + c * 32 + q4 * 8) = make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+    }
+}
+
+std::mutex g_tc_pool_mutex;
+std::map<std::tuple<const void*, long long, int>, CUtensorMap> g_tc_pool_maps;
+
+int tc_pool_map(CUtensorMap* out, const void* base, long long rows, int box_rows) {
+    std::lock_guard<std::mutex> lock(g_tc_pool_mutex);
+    auto key = std::make_tuple(base, rows, box_rows);
+    auto it = g_tc_pool_maps.find(key);
+    if (it == g_tc_pool_maps.end()) {
+        CUtensorMap m;
+        if (int rc = make_bf16_map(&m, base, rows, HD, HD, box_rows, true, "attention_tc")) return rc;
+        it = g_tc_pool_maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return 0;
+}
+
+}  // namespace
+
+Q6K_API int q6k_attention_tc_status() {
+    int v = -1;
+    if (cudaMemcpyFromSymbol(&v, g_attn_tc_status, sizeof v) != cudaSuccess) return -1;
+    return v;
+}
+
+// Whether the kernel covers these sizes: head size 128, up to 128 rows per tile (G <= 128), pages
+// of 8, 16, 32, 64 or 128 keys.
+Q6K_API int q6k_attention_tc_supported(int hd, int G, int page_size) {
+    return hd == HD && G >= 1 && G <= BM && page_size >= 8 && page_size <= BN && BN % page_size == 0;
+}
+
+// q: bfloat16 [T, Hq, 128]; pages: bfloat16 [num_pages, Hkv, page_size, 128]; tiles of at most 128 / G
+// tokens (consecutive positions of one request); out: bfloat16 [T, Hq*128].  Every tile reads its whole
+// key range (no key splits): the kernel for prompt portions.
+Q6K_API int q6k_attention_tc(const void* q, const void* k_pages, const void* v_pages, long long num_pages, const int* block_table,
+                             int max_blocks, int page_size, const int* req_of_token, const int* positions, const int* tile_tok0,
+                             const int* tile_ntok, int n_tiles, int window, const float* sinks, float scale, void* out, int Hq, int Hkv,
+                             int hd, cudaStream_t st) {
+    if (n_tiles == 0) return 0;
+    Q6K_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention_tc: bad head counts Hq=%d Hkv=%d", Hq, Hkv);
+    const int G = Hq / Hkv;
+    Q6K_REQUIRE(q6k_attention_tc_supported(hd, G, page_size), "attention_tc: head_dim %d / group size %d / page size %d is not covered", hd, G, page_size);
+    Q6K_REQUIRE(max_blocks > 0 && window >= 0 && Hkv <= 65535, "attention_tc: bad max_blocks %d / window %d / Hkv %d", max_blocks, window, Hkv);
+    const long long pool_rows = num_pages * Hkv * page_size;
+    Q6K_REQUIRE(pool_rows < (1LL << 31) && ((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0 && ((uintptr_t)q & 15) == 0 &&
+                    ((uintptr_t)out & 15) == 0,
+                "attention_tc: pools too large for TMA coordinates or operands not 16-byte aligned");
+    TcAttnParams p{};
+    p.q = (const __nv_bfloat16*)q, p.block_table = block_table, p.req_of_token = req_of_token, p.positions = positions;
+    p.tile_tok0 = tile_tok0, p.tile_ntok = tile_ntok, p.sinks = sinks, p.out = (__nv_bfloat16*)out;
+    p.max_blocks = max_blocks, p.page_size = page_size, p.window = window, p.Hq = Hq, p.Hkv = Hkv, p.G = G;
+    p.pool_rows = (int)pool_rows, p.scale_log2 = scale * LOG2E;
+    CUtensorMap tk, tv;
+    if (int rc = tc_pool_map(&tk, k_pages, pool_rows, page_size)) return rc;
+    if (int rc = tc_pool_map(&tv, v_pages, pool_rows, page_size)) return rc;
+    const size_t smem = 6 * TILE_BYTES + 1024;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+            return q6k_check_launch("attention_tc: shared memory attribute");
+        configured = true;
+    }
+    attention_tc_kernel<<<dim3(n_tiles, Hkv), 192, smem, st>>>(tk, tv, p);
+    return q6k_check_launch("attention_tc");
+}

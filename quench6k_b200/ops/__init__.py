@@ -229,7 +229,8 @@ def tc_status() -> int:
     lib = library()
     lib.q6k_tc_status.restype = ctypes.c_int
     lib.q6k_attention_status.restype = ctypes.c_int
-    return lib.q6k_tc_status() or lib.q6k_attention_status()
+    lib.q6k_attention_tc_status.restype = ctypes.c_int
+    return lib.q6k_tc_status() or lib.q6k_attention_status() or lib.q6k_attention_tc_status()
 
 
 _workspaces = {}
@@ -361,6 +362,38 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
           _i(page_size), _ptr(req_of_token), _ptr(positions), _i(window or 0), _ptr(sinks),
           _f(scale if scale is not None else 1.0 / math.sqrt(hd)), _ptr(out), _i(T), _i(Hq), _i(Hkv), _i(hd),
           _i(dtype_code(q.dtype)), _stream())
+    return out
+
+
+def attention_tc_supported(hd: int, G: int, page_size: int) -> bool:
+    lib = library()
+    lib.q6k_attention_tc_supported.restype = ctypes.c_int
+    return bool(lib.q6k_attention_tc_supported(_i(hd), _i(G), _i(page_size)))
+
+
+def attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                 req_of_token: torch.Tensor, positions: torch.Tensor, tile_tok0: torch.Tensor, tile_ntok: torch.Tensor,
+                 window: Optional[int], sinks: Optional[torch.Tensor], scale: Optional[float] = None) -> torch.Tensor:
+    """bfloat16 attention for prompt portions with both products on tcgen05 tensor cores
+    (accumulators in tensor memory, K/V pages by TMA).  Head size 128; tiles of at most 128 // G
+    tokens (consecutive positions of one request); each tile reads its whole key range."""
+    _need(q, "q", torch.bfloat16)
+    T, Hq, hd = q.shape
+    _need(k_pages, "k_pages", torch.bfloat16)
+    _need(v_pages, "v_pages", torch.bfloat16, k_pages.shape)
+    _, Hkv, page_size, hd2 = k_pages.shape
+    if hd2 != hd:
+        raise KernelError(f"attention: q has head_dim {hd}, the pages {hd2}")
+    for nm, t in (("block_table", block_table), ("req_of_token", req_of_token), ("positions", positions),
+                  ("tile_tok0", tile_tok0), ("tile_ntok", tile_ntok)):
+        _need(t, nm, torch.int32)
+    if sinks is not None:
+        _need(sinks, "sinks", torch.float32, (Hq,))
+    out = torch.empty((T, Hq * hd), dtype=torch.bfloat16, device=q.device)
+    _call("q6k_attention_tc", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ll(k_pages.shape[0]), _ptr(block_table),
+          _i(block_table.shape[1]), _i(page_size), _ptr(req_of_token), _ptr(positions), _ptr(tile_tok0), _ptr(tile_ntok),
+          _i(tile_tok0.numel()), _i(window or 0), _ptr(sinks), _f(scale if scale is not None else 1.0 / math.sqrt(hd)), _ptr(out),
+          _i(Hq), _i(Hkv), _i(hd), _stream())
     return out
 
 

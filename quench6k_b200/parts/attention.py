@@ -88,6 +88,10 @@ class Attention(Mixer):
         if not ops.attention_mma_supported(self.hd, G, wide):
             return ops.attention_generic(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, self.window, self.sinks, self.scale)
         tok0, ntok, n_tiles = ctx.query_tiles((128 if wide else 16) // G)
+        if wide and ops.attention_tc_supported(self.hd, G, cache.page_size) and n_tiles * self.Hkv >= self._sm_count():
+            # prompt portions with enough tiles to fill the GPU: both products on tcgen05, no key splits
+            return ops.attention_tc(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, tok0, ntok, self.window,
+                                    self.sinks, scale=self.scale)
         # split the keys over CTAs until the GPU is full, and no further: one wave of resident CTAs
         # (a second, partly filled wave would cost as much as a full one)
         span = ctx.max_context if self.window is None else min(ctx.max_context, self.window + ctx.max_q_len)
@@ -95,6 +99,11 @@ class Attention(Mixer):
         max_splits = max(1, min(64, self._resident_ctas(wide) // (n_tiles * self.Hkv), key_tiles // 2))
         return ops.attention_mma(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, tok0, ntok, wide, self.window,
                                  self.sinks, max_splits=max_splits, min_tiles=2, scale=self.scale)
+
+    def _sm_count(self) -> int:
+        if "_sms" not in self.__dict__:
+            self._sms = torch.cuda.get_device_properties(self.rt.device).multi_processor_count
+        return self._sms
 
     def _resident_ctas(self, wide: bool) -> int:
         """CTAs of the tensor-core attention kernel that fit on the GPU at once (shared memory bound)."""

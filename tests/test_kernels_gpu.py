@@ -385,3 +385,45 @@ def test_decode_moe_path(scoring, renorm, T, E, k, D, I):
     want = h.double().cpu() + (sel_w.double().cpu()[:, :, None] * y.double().cpu().view(T, k, D)).sum(1)
     ops.combine(y, None, sel_w, h)
     assert (h.double().cpu() - want).abs().max() <= 1e-5 * want.abs().max()
+
+
+@pytest.mark.parametrize("Hq,Hkv,ps,window,sinks", [(32, 4, 16, None, False), (8, 1, 8, None, True), (6, 2, 32, 100, True),
+                                                     (16, 16, 64, 37, False), (5, 1, 128, None, False)])
+def test_attention_tc(Hq, Hkv, ps, window, sinks):
+    """Prompt portions of several requests (some continuing from a cache) through the tcgen05
+    attention kernel, against float64 with one far key made to stand out."""
+    from quench6k_b200 import ops
+    hd, G = 128, Hq // Hkv
+    g = torch.Generator().manual_seed(Hq * 1000 + ps + (window or 0))
+    lens = [700, 150, 333, 64, 129]
+    num_pages = sum(-(-n // ps) for n in lens) + 5
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    kp = torch.full((num_pages, Hkv, ps, hd), float("nan"), dtype=torch.bfloat16)
+    vp = torch.full((num_pages, Hkv, ps, hd), float("nan"), dtype=torch.bfloat16)
+    tables, refs, qs = [], [], []
+    sk = torch.randn(Hq, generator=g) if sinks else None
+    for n in lens:
+        q, k, v = (torch.randn(n, h, hd, generator=g) for h in (Hq, Hkv, Hkv))
+        k[3] *= 3.0
+        q[-20:] += 1.5 * k[3].repeat_interleave(G, 0) / k[3].norm()
+        qd, kd, vd = (x.to(torch.bfloat16) for x in (q, k, v))
+        refs.append(P.attention(qd.double(), kd.double(), vd.double(), window, sk.double() if sinks else None, True))
+        table = [perm.pop() for _ in range(-(-n // ps))]
+        for t in range(n):
+            kp[table[t // ps], :, t % ps] = kd[t]
+            vp[table[t // ps], :, t % ps] = vd[t]
+        tables.append(table)
+        qs.append(qd)
+    width = max(len(t) for t in tables)
+    bt = torch.tensor([t + [-1] * (width - len(t)) for t in tables], dtype=torch.int32, device=DEV)
+    q_lens = [700, 150, 33, 3, 129]
+    starts = [n - ql for n, ql in zip(lens, q_lens)]
+    ctx = helpers.make_context(q_lens, starts, [tables])
+    q = torch.cat([qs[r][starts[r]:] for r in range(len(lens))]).contiguous().to(DEV)
+    tok0, ntok, n_tiles = ctx.query_tiles(128 // G)
+    want = torch.cat([refs[r][starts[r]:] for r in range(len(lens))]).reshape(-1, Hq * hd)
+    out = ops.attention_tc(q, kp.to(DEV), vp.to(DEV), bt, ctx.req_of_token, ctx.positions, tok0, ntok, window,
+                           sk.to(DEV) if sinks else None)
+    assert ops.tc_status() == 0
+    err = (out.double().cpu() - want).abs().max() / want.abs().max()
+    assert err <= 1.5e-2, err

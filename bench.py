@@ -138,6 +138,7 @@ def main():
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--points", default="1,64", help="further decode batch sizes, comma separated ('' for none)")
     ap.add_argument("--dtype", default="bfloat16")
+    ap.add_argument("--page-size", type=int, default=None, help="KV page size (default: the configuration's 16)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -162,6 +163,8 @@ def main():
     full_layers = cfg_d["num_hidden_layers"]
     layers = args.layers or full_layers
     cfg_d["num_hidden_layers"] = layers
+    if args.page_size:
+        cfg_d["kv_page_size"] = args.page_size
     cfg = FlintConfig.from_dict(cfg_d)
     page = cfg.kv_page_size
     point_batches = [int(x) for x in args.points.split(",") if x.strip()]

@@ -9,15 +9,16 @@
 //
 // A CTA takes one tile of up to 128 query rows (row = token_in_tile * G + head_in_group, one
 // request, one KV head) and walks key tiles of 128 keys.
-//   warp 0      producer: TMA boxes [page rows x 64] of the K and V pages of a key tile into a
-//               two-stage ring ([2 column halves][128 keys][128 bytes], 128-byte swizzle; keys
-//               without a page are zero-filled through an out-of-range coordinate)
+//   warp 0      producers: one lane brings the K tiles, another the V tiles, as TMA boxes
+//               [page rows x 64] into rings of three and two tiles ([2 column halves][128 keys]
+//               [128 bytes], 128-byte swizzle; keys without a page are zero-filled through an
+//               out-of-range coordinate); a K tile is free again as soon as its scores exist
 //   warp 1      one thread issues the MMAs: S_i = Q K_i^T (8 x K=16, both operands K-major) into one
 //               of two S buffers in tensor memory, one tile ahead of the softmax; then, when P_i is
 //               in shared memory, O += P_i V_i (8 x K=16, V as an MN-major operand)
 //   warps 2-5   softmax: one thread per query row reads its row of S from tensor memory
 //               (tcgen05.ld, no shuffles), keeps the running max and sum, rescales O in tensor
-//               memory when the max moved (tcgen05.ld / tcgen05.st), writes P as bfloat16 into shared
+//               memory when the max has grown by more than 2^8 (tcgen05.ld / tcgen05.st), writes P as bfloat16 into shared
 //               memory in the K-major swizzled layout the MMA reads, and finally normalises O
 // Tensor memory: S0 at columns 0..127, S1 at 128..255, O at 256..383.
 // Every wait on an mbarrier is bounded and records a code in a status word when it runs out.
@@ -35,6 +36,7 @@ constexpr int BN = 128;                      // keys per key tile
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr uint32_t HALF_BYTES = 128 * 128;   // one 64-column half of a [128 x 128] bf16 tile
 constexpr uint32_t TILE_BYTES = 2 * HALF_BYTES;
+constexpr int KS = 3, VS = 2;                // stages of the K and of the V ring
 
 struct TcAttnParams {
     const __nv_bfloat16* q;                  // [T, Hq, HD]
@@ -100,6 +102,20 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
 #pragma unroll
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
+// The same without the wait: several loads may be in flight; tmem_ld_wait() before any value is used.
+__device__ __forceinline__ void tmem_ld32_issue(uint32_t taddr, float* v) {
+    uint32_t* r = reinterpret_cast<uint32_t*>(v);
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, "
+        "%20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+          "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+          "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+          "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, "
@@ -116,6 +132,13 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// 2^x by the special-function unit: 2^-inf = 0, no range fix-ups (arguments here are <= 8).
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 // Byte offset of 16-byte chunk c (0..15) of row r in a [2 halves][128 rows][128 bytes] swizzled tile.
 __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)((c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)); }
 
@@ -123,14 +146,15 @@ __global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant
                                                            const TcAttnParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    // [Q][P][K0][V0][K1][V1], each a [2][128][128 B] tile of 32 KB
-    const uint32_t q_s = smem_u32(smem), p_s = q_s + TILE_BYTES, kv_s = p_s + TILE_BYTES;
-    __shared__ __align__(8) uint64_t bars[10];
+    // [Q][P][K0][K1][K2][V0][V1], each a [2][128][128 B] tile of 32 KB: K is free again as soon as
+    // its scores are computed and runs three tiles deep, V waits for the softmax and runs two deep
+    const uint32_t q_s = smem_u32(smem), p_s = q_s + TILE_BYTES, k_s = p_s + TILE_BYTES, v_s = k_s + KS * TILE_BYTES;
+    __shared__ __align__(8) uint64_t bars[16];
     __shared__ uint32_t tmem_slot;
-    const uint32_t kv_full0 = smem_u32(&bars[0]), kv_empty0 = smem_u32(&bars[2]), s_full0 = smem_u32(&bars[4]);
-    const uint32_t p_full = smem_u32(&bars[6]), pv_done = smem_u32(&bars[7]), q_full = smem_u32(&bars[8]);
+    const uint32_t k_full0 = smem_u32(&bars[0]), k_empty0 = smem_u32(&bars[3]), v_full0 = smem_u32(&bars[6]), v_empty0 = smem_u32(&bars[8]);
+    const uint32_t s_full0 = smem_u32(&bars[10]), p_full = smem_u32(&bars[12]), pv_done = smem_u32(&bars[13]), q_full = smem_u32(&bars[14]);
 
-    const int tile = blockIdx.x, kh = blockIdx.y;
+    const int tile = gridDim.x - 1 - blockIdx.x, kh = blockIdx.y;      // later tiles see more keys: start them first
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = p.G;
     const int tok0 = p.tile_tok0[tile], ntok = p.tile_ntok[tile];
@@ -140,9 +164,13 @@ __global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant
     const int first_tile = k_lo / BN, n_tiles = pos_last / BN + 1 - first_tile;
 
     if (tid == 0) {
-        for (int s = 0; s < 2; ++s) {
-            mbar_init(kv_full0 + 8 * s, 1);
-            mbar_init(kv_empty0 + 8 * s, 1);
+        for (int s = 0; s < KS; ++s) {
+            mbar_init(k_full0 + 8 * s, 1);
+            mbar_init(k_empty0 + 8 * s, 1);
+        }
+        for (int s = 0; s < VS; ++s) {
+            mbar_init(v_full0 + 8 * s, 1);
+            mbar_init(v_empty0 + 8 * s, 1);
             mbar_init(s_full0 + 8 * s, 1);
         }
         mbar_init(p_full, 128);
@@ -163,19 +191,22 @@ __global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant
     const uint32_t tmem_o = tmem + 256;
 
     if (warp == 0) {
-        // ---- producer
-        if (lane == 0) {
-            const int ps = p.page_size, box = ps < BN ? ps : BN;
+        // ---- producers: lane 0 brings the K tiles, lane 1 the V tiles (each at its ring's pace)
+        if (lane < 2) {
+            const bool is_k = lane == 0;
+            const int ps = p.page_size, box = ps < BN ? ps : BN, ring = is_k ? KS : VS;
+            const uint32_t full0 = is_k ? k_full0 : v_full0, empty0 = is_k ? k_empty0 : v_empty0, base = is_k ? k_s : v_s;
+            const CUtensorMap* map = is_k ? &tm_k : &tm_v;
             for (int i = 0; i < n_tiles; ++i) {
-                const int s = i & 1;
-                if (!mbar_wait(kv_empty0 + 8 * s, ((i >> 1) & 1) ^ 1)) {
+                const int s = i % ring;
+                if (!mbar_wait(empty0 + 8 * s, ((i / ring) & 1) ^ 1)) {
                     atomicExch(&g_attn_tc_status, 1);
                     break;
                 }
-                const uint32_t fb = kv_full0 + 8 * s;
-                mbar_expect_tx(fb, 2 * TILE_BYTES);
+                const uint32_t fb = full0 + 8 * s;
+                mbar_expect_tx(fb, TILE_BYTES);
                 const int j0 = (first_tile + i) * BN;
-                const uint32_t k_dst = kv_s + s * 2 * TILE_BYTES, v_dst = k_dst + TILE_BYTES;
+                const uint32_t dst = base + s * TILE_BYTES;
                 for (int b = 0; b < BN / box; ++b) {
                     const int j = j0 + b * box;
                     int y = p.pool_rows;                                 // out of range: zeros
@@ -184,11 +215,7 @@ __global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant
                         if (page >= 0) y = (page * p.Hkv + kh) * ps + j % ps;
                     }
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const uint32_t off = h * HALF_BYTES + b * box * 128;
-                        tma_load_2d(k_dst + off, &tm_k, h * 64, y, fb);
-                        tma_load_2d(v_dst + off, &tm_v, h * 64, y, fb);
-                    }
+                    for (int h = 0; h < 2; ++h) tma_load_2d(dst + h * HALF_BYTES + b * box * 128, map, h * 64, y, fb);
                 }
             }
         }
@@ -199,39 +226,40 @@ __global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant
             bool ok = mbar_wait(q_full, 0);
             if (!ok) atomicExch(&g_attn_tc_status, 2);
             auto issue_s = [&](int i) -> bool {
-                const int s = i & 1;
-                if (!mbar_wait(kv_full0 + 8 * s, (i >> 1) & 1)) {
+                const int ks = i % KS, sb = i & 1;
+                if (!mbar_wait(k_full0 + 8 * ks, (i / KS) & 1)) {
                     atomicExch(&g_attn_tc_status, 3);
                     return false;
                 }
                 tc_fence_after();
-                const uint32_t k_src = kv_s + s * 2 * TILE_BYTES;
+                const uint32_t k_src = k_s + ks * TILE_BYTES;
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
                     const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-                    umma(tmem + s * BN, desc_k_major(q_s + off), desc_k_major(k_src + off), idesc_s, k != 0);
+                    umma(tmem + sb * BN, desc_k_major(q_s + off), desc_k_major(k_src + off), idesc_s, k != 0);
                 }
-                umma_commit(s_full0 + 8 * s);
+                umma_commit(k_empty0 + 8 * ks);                     // the K tile is free once its scores exist
+                umma_commit(s_full0 + 8 * sb);
                 return true;
             };
             if (ok) ok = issue_s(0);
             for (int i = 0; i < n_tiles && ok; ++i) {
                 if (i + 1 < n_tiles) ok = issue_s(i + 1);           // one tile ahead of the softmax
                 if (!ok) break;
-                if (!mbar_wait(p_full, i & 1)) {
+                const int vs = i % VS;
+                if (!mbar_wait(p_full, i & 1) || !mbar_wait(v_full0 + 8 * vs, (i / VS) & 1)) {
                     atomicExch(&g_attn_tc_status, 4);
                     break;
                 }
                 tc_fence_after();
-                const int s = i & 1;
-                const uint32_t v_src = kv_s + s * 2 * TILE_BYTES + TILE_BYTES;
+                const uint32_t v_src = v_s + vs * TILE_BYTES;
 #pragma unroll
                 for (int k = 0; k < BN / 16; ++k) {
                     // A: P, K-major over the keys; B: V, MN-major, 16 keys = 2048 bytes per step
                     const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
                     umma(tmem_o, desc_k_major(p_s + a_off), desc_mn_major(v_src + k * 2048), idesc_o, (i | k) != 0);
                 }
-                umma_commit(kv_empty0 + 8 * s);
+                umma_commit(v_empty0 + 8 * vs);
                 umma_commit(pv_done);
             }
         }
@@ -266,19 +294,35 @@ __global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant
             }
             tc_fence_after();
             const uint32_t s_addr = tmem + lane_base + sb * BN;
-            // pass 1: the row's maximum over this tile
-            float mx = m;
+            // tiles that every row of the CTA sees whole (below the diagonal, inside the window) need no mask
+            const bool whole = j0 + BN - 1 <= pos_first && (p.window == 0 || j0 >= pos_last - p.window + 1);
+            // pass 1: the row's maximum over this tile, 32 scores at a time (loops kept rolled: the
+            // code of a tile has to stay in the instruction cache)
+            float mx = -INFINITY;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 float v[32];
                 tmem_ld32(s_addr + c * 32, v);
+                if (whole) {
 #pragma unroll
-                for (int x = 0; x < 32; ++x) {
-                    const int j = j0 + c * 32 + x;
-                    if (j <= lim_hi && j >= lim_lo) mx = fmaxf(mx, v[x] * p.scale_log2);
+                    for (int x = 0; x < 32; ++x) mx = fmaxf(mx, v[x]);
+                } else {
+#pragma unroll
+                    for (int x = 0; x < 32; ++x) {
+                        const int j = j0 + c * 32 + x;
+                        if (j <= lim_hi && j >= lim_lo) mx = fmaxf(mx, v[x]);
+                    }
                 }
             }
-            const float corr = mx == -INFINITY ? 1.0f : exp2f(m - mx);
+            mx *= p.scale_log2;                          // the scale is positive: max commutes with it
+            // The reference point of the exponentials follows the running maximum lazily: it moves
+            // only when the maximum has grown by more than 2^8, so O in tensor memory is rescaled
+            // rarely; probabilities then reach at most 256, which bfloat16 and the FP32 sums hold.
+            float ref = m, corr = 1.0f;
+            if (mx > m + 8.0f || m == -INFINITY) {
+                ref = fmaxf(m, mx);
+                corr = (m == -INFINITY) ? 1.0f : exp2f(m - ref);
+            }
             // P and O of the previous tile must be consumed before either is touched
             if (i > 0 && !mbar_wait(pv_done, (i - 1) & 1)) {
                 if (lane == 0) atomicExch(&g_attn_tc_status, 6);
@@ -297,23 +341,31 @@ __global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant
                 }
                 tmem_st_wait();
             }
-            // pass 2: probabilities, rounded to bfloat16 before they are summed, into shared memory
+            // pass 2: probabilities p = 2^(s * scale - ref), rounded to bfloat16 before they are summed,
+            // into shared memory; a masked score counts as -inf and gives 0; so does a row without any
+            // key yet (ref = -inf)
+            const float neg_ref = ref == -INFINITY ? 0.0f : -ref;
             float sum = 0.0f;
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 float v[32];
                 tmem_ld32(s_addr + c * 32, v);
+                if (!whole) {
+#pragma unroll
+                    for (int x = 0; x < 32; ++x) {
+                        const int j = j0 + c * 32 + x;
+                        v[x] = (j <= lim_hi && j >= lim_lo) ? v[x] : -INFINITY;
+                    }
+                }
                 uint32_t packed[16];
 #pragma unroll
                 for (int x = 0; x < 32; x += 2) {
-                    const int j = j0 + c * 32 + x;
-                    const bool ok0 = j <= lim_hi && j >= lim_lo, ok1 = j + 1 <= lim_hi && j + 1 >= lim_lo;
-                    const float p0 = ok0 ? exp2f(v[x] * p.scale_log2 - mx) : 0.0f;
-                    const float p1 = ok1 ? exp2f(v[x + 1] * p.scale_log2 - mx) : 0.0f;
+                    const float p0 = ex2_approx(fmaf(v[x], p.scale_log2, neg_ref));
+                    const float p1 = ex2_approx(fmaf(v[x + 1], p.scale_log2, neg_ref));
                     const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-                    const float2 pf = __bfloat1622float2(pb);
-                    sum += pf.x + pf.y;
-                    packed[x >> 1] = *reinterpret_cast<const uint32_t*>(&pb);
+                    const uint32_t bits = *reinterpret_cast<const uint32_t*>(&pb);
+                    sum += __uint_as_float(bits << 16) + __uint_as_float(bits & 0xffff0000u);
+                    packed[x >> 1] = bits;
                 }
 #pragma unroll
                 for (int q4 = 0; q4 < 4; ++q4)           // 32 keys = 4 chunks of 16 bytes
@@ -321,15 +373,15 @@ __global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant
                         make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
             }
             l = l * corr + sum;
-            m = mx;
+            m = ref;
             if (i == n_tiles - 1 && (pos_last + 1) % BN != 0) {
                 // the last page came in whole: clear the V rows past the last key (0 * stale NaN)
-                if (!mbar_wait(kv_full0 + 8 * (i & 1), (i >> 1) & 1)) {
+                if (!mbar_wait(v_full0 + 8 * (i % VS), (i / VS) & 1)) {
                     if (lane == 0) atomicExch(&g_attn_tc_status, 7);
                     ok = false;
                     break;
                 }
-                const uint32_t v_off = (kv_s - q_s) + (i & 1) * 2 * TILE_BYTES + TILE_BYTES;
+                const uint32_t v_off = (v_s - q_s) + (i % VS) * TILE_BYTES;
                 const int r0 = pos_last + 1 - j0;
                 for (int idx = r0 * 16 + st; idx < BN * 16; idx += 128)
                     *reinterpret_cast<uint4*>(smem + v_off + swz(idx >> 4, idx & 15)) = make_uint4(0, 0, 0, 0);
@@ -435,7 +487,7 @@ Q6K_API int q6k_attention_tc(const void* q, const void* k_pages, const void* v_p
     CUtensorMap tk, tv;
     if (int rc = tc_pool_map(&tk, k_pages, pool_rows, page_size)) return rc;
     if (int rc = tc_pool_map(&tv, v_pages, pool_rows, page_size)) return rc;
-    const size_t smem = 6 * TILE_BYTES + 1024;
+    const size_t smem = (2 + KS + VS) * TILE_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
         if (cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)

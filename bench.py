@@ -193,9 +193,10 @@ def main():
         rids = [f"d{B}_{i}" for i in range(B)]
         for r in rids:
             runner.add_request(r)
-        for at in range(0, ctx, page):           # page by page, round robin: the requests' pages interleave in the pool
+        chunk = args.prefill_tokens              # pages are taken as a chunked prefill would take them:
+        for at in range(0, ctx, chunk):          # one portion of each request in turn
             for r in rids:
-                runner.assume_cached(r, min(page, ctx - at))
+                runner.assume_cached(r, min(chunk, ctx - at))
         toks = [rand_ids(steps + warmup) for _ in rids]
 
         def one(i):
@@ -281,7 +282,7 @@ def main():
                    "expert_width": cfg.moe_intermediate_size, "vocab": cfg.vocab_size, "rope_theta": cfg.rope_theta,
                    "page_size": page, "global_batch": args.batch, "seq_len": ctx, "prefill_tokens": T,
                    "parallelism": "single-gpu", "l2": "inputs larger than L2 (weights and cache stream from HBM every step)",
-                   "kv_fill": "random values, no prefill", "peaks": pk["source"]},
+                   "kv_fill": "random values; pages taken in portions of prefill_tokens per request in turn", "peaks": pk["source"]},
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "bytes": int(total_b), "weight_bytes": int(w_b), "kv_bytes": int(kv_b)},

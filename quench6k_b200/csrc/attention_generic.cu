@@ -20,7 +20,7 @@ constexpr int MAX_HD = 256, DPL = MAX_HD / 32;   // head dims per lane
 template <typename T>
 __global__ void __launch_bounds__(128) attention_generic_kernel(const T* q, const T* k_pages, const T* v_pages,
                                                                 const int* block_table, int max_blocks, int page_size,
-                                                                const int* req_of_token, const int* positions, int window,
+                                                                int num_pages, const int* req_of_token, const int* positions, int window,
                                                                 const float* sinks, float scale, T* out, int Hq, int Hkv,
                                                                 int hd) {
     extern __shared__ float qs[];             // [warps][hd]
@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(128) attention_generic_kernel(const T* q, cons
     const int* bt = block_table + (size_t)req_of_token[t] * max_blocks;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
     float* qw = qs + warp * hd;
-    const size_t page_stride = (size_t)Hkv * page_size * hd;
+    const size_t head_base = (size_t)kh * num_pages;          // pools are [Hkv, num_pages, page_size, hd]
 
     for (int g = warp; g < G; g += nwarps) {
         const int h = kh * G + g;
@@ -46,7 +46,7 @@ __global__ void __launch_bounds__(128) attention_generic_kernel(const T* q, cons
             size_t row = 0;
             if (ok) {
                 const int page = bt[j / page_size];
-                row = (size_t)page * page_stride + ((size_t)kh * page_size + j % page_size) * hd;
+                row = ((head_base + page) * page_size + j % page_size) * hd;
                 const T* kr = k_pages + row;
                 float acc = 0.0f;
                 for (int d = 0; d < hd; ++d) acc = fmaf(qw[d], to_f32(kr[d]), acc);
@@ -93,9 +93,9 @@ __global__ void __launch_bounds__(128) attention_generic_kernel(const T* q, cons
 
 }  // namespace
 
-// q: [T, Hq, hd]; pages: [num_pages, Hkv, page_size, hd]; block_table: [R, max_blocks];
+// q: [T, Hq, hd]; pages: [Hkv, num_pages, page_size, hd]; block_table: [R, max_blocks];
 // window 0: every earlier key is visible; sinks: FP32 [Hq] or null; out: [T, Hq*hd].
-Q6K_API int q6k_attention_generic(const void* q, const void* k_pages, const void* v_pages, const int* block_table,
+Q6K_API int q6k_attention_generic(const void* q, const void* k_pages, const void* v_pages, int num_pages, const int* block_table,
                                   int max_blocks, int page_size, const int* req_of_token, const int* positions, int window,
                                   const float* sinks, float scale, void* out, int T_, int Hq, int Hkv, int hd, int dtype,
                                   cudaStream_t st) {
@@ -110,6 +110,6 @@ Q6K_API int q6k_attention_generic(const void* q, const void* k_pages, const void
     dim3 grid(T_, Hkv);
     Q6K_DISPATCH(dtype, attention_generic_kernel<T><<<grid, warps * 32, warps * hd * sizeof(float), st>>>(
                             (const T*)q, (const T*)k_pages, (const T*)v_pages, block_table, max_blocks, page_size,
-                            req_of_token, positions, window, sinks, scale, (T*)out, Hq, Hkv, hd););
+                            num_pages, req_of_token, positions, window, sinks, scale, (T*)out, Hq, Hkv, hd););
     return q6k_check_launch("attention_generic");
 }

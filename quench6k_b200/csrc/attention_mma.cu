@@ -14,8 +14,10 @@
 // (16 keys each), then merge their partial softmax states through shared memory.  Wide tiles
 // (prompt portions): 8 warps, each owning 16 rows and walking all 64 keys of a tile.
 // K and V tiles travel through a ring of shared-memory stages.  With pages of 8 rows or a multiple
-// (the usual case) a producer warp brings each page's [rows x 64] boxes in by TMA (one tensor map
-// over a layer's K or V pool, 128-byte swizzle, zero fill for keys that have no page) and signals
+// (the usual case) a producer warp brings each page's [rows x 64] boxes in by TMA (tensor maps over
+// a layer's K and V pool, 128-byte swizzle, zero fill for keys that have no page; when the pages of
+// a key tile have consecutive numbers, which the head-major pool makes contiguous, one box of 64
+// keys per half replaces the boxes per page: far fewer TMA operations) and signals
 // the four consumer warps through mbarriers (full: transaction bytes; empty: one arrival per
 // warp); every wait is bounded and records a code in a status word when it runs out.  With other
 // page sizes the consumer warps copy the rows themselves with 16-byte cp.async into two stages.
@@ -33,7 +35,7 @@ constexpr float LOG2E = 1.4426950408889634f;
 
 struct AttnParams {
     const __nv_bfloat16* q;                  // [T, Hq, HD]
-    const __nv_bfloat16* k_pages;            // [pages, Hkv, page_size, HD]
+    const __nv_bfloat16* k_pages;            // [Hkv, pages, page_size, HD]
     const __nv_bfloat16* v_pages;
     const int* block_table;                  // [R, max_blocks]
     const int* req_of_token;
@@ -46,7 +48,8 @@ struct AttnParams {
     float* part_ml;                          // [T*Hq, max_splits, 2]
     int max_blocks, page_size, window, Hq, Hkv, G, max_splits, min_tiles;
     float scale_log2;
-    int pool_rows;                           // rows of the [pages * Hkv * page_size, HD] view of a pool (TMA path)
+    int pool_rows;                           // rows of the [Hkv * pages * page_size, HD] view of a pool (TMA path)
+    int num_pages;                           // pages of a pool (per KV head)
 };
 
 __device__ int g_attn_status = 0;
@@ -93,7 +96,9 @@ __device__ __forceinline__ uint32_t swk(int r, int c) { return (uint32_t)((c >> 
 
 template <int HD, bool WIDE, bool TMA>
 __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0)) attention_mma_kernel(const __grid_constant__ CUtensorMap tm_k,
-                                                                        const __grid_constant__ CUtensorMap tm_v, const AttnParams p) {
+                                                                        const __grid_constant__ CUtensorMap tm_v,
+                                                                        const __grid_constant__ CUtensorMap tm_k_run,
+                                                                        const __grid_constant__ CUtensorMap tm_v_run, const AttnParams p) {
     constexpr int CW = WIDE ? 8 : 4;         // consumer warps
     constexpr int CT = CW * 32;              // consumer threads
     constexpr int ROWS = WIDE ? 128 : 16;
@@ -131,6 +136,8 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0)) attentio
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_v) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k_run) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_v_run) : "memory");
     }
     // ---- Q tile into shared memory (zero rows past the tile's tokens)
     if (warp < CW) {
@@ -147,7 +154,7 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0)) attentio
             const bool in = j >= k_lo && j <= pos_last;
             int page = in ? bt[j / p.page_size] : -1;
             const bool valid = page >= 0;
-            const size_t off = valid ? (((size_t)page * p.Hkv + kh) * p.page_size + j % p.page_size) * HD + c * 8 : 0;
+            const size_t off = valid ? (((size_t)kh * p.num_pages + page) * p.page_size + j % p.page_size) * HD + c * 8 : 0;
             cp_async16(k_s + stage * TILE_BYTES + swk(r, c), p.k_pages + off, valid);
             cp_async16(v_s + stage * TILE_BYTES + swk(r, c), p.v_pages + off, valid);
         }
@@ -170,12 +177,31 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0)) attentio
                 const uint32_t fb = full0 + 8 * s2;
                 mbar_expect_tx(fb, 2 * TILE_BYTES);
                 const int j0 = (t_begin + i) * KT;
+                // pages with consecutive numbers are contiguous for one head: when the tile's pages form
+                // such a run, each half comes in as one box of 64 keys instead of one box per page
+                bool run = ps < KT && j0 >= k_lo && j0 / ps + KT / ps <= p.max_blocks;
+                int first = -1;
+                if (run) {
+                    first = bt[j0 / ps];
+                    run = first >= 0;
+                    for (int b = 1; b < KT / ps && run; ++b) run = bt[j0 / ps + b] == first + b;
+                }
+                if (run) {
+                    const int y = (kh * p.num_pages + first) * ps;
+#pragma unroll
+                    for (int h = 0; h < HD / 64; ++h) {
+                        const uint32_t off = s2 * TILE_BYTES + h * (KT * 128);
+                        tma_load_2d(k_s + off, &tm_k_run, h * 64, y, fb);
+                        tma_load_2d(v_s + off, &tm_v_run, h * 64, y, fb);
+                    }
+                    continue;
+                }
                 for (int b = 0; b < KT / box; ++b) {
                     const int j = j0 + b * box;
                     int y = p.pool_rows;                                 // out of range: the box is filled with zeros
                     if (j + box > k_lo && j <= pos_last) {
                         const int page = bt[j / ps];
-                        if (page >= 0) y = (page * p.Hkv + kh) * ps + j % ps;
+                        if (page >= 0) y = (kh * p.num_pages + page) * ps + j % ps;
                     }
 #pragma unroll
                     for (int h = 0; h < HD / 64; ++h) {
@@ -433,7 +459,7 @@ int pool_map(CUtensorMap* out, const void* base, long long rows, int hd, int box
 }
 
 template <int HD, bool WIDE, bool TMA>
-int launch(const AttnParams& p, const CUtensorMap& tk, const CUtensorMap& tv, int n_tiles, cudaStream_t st) {
+int launch(const AttnParams& p, const CUtensorMap* maps, int n_tiles, cudaStream_t st) {
     constexpr int ROWS = WIDE ? 128 : 16;
     constexpr int STAGES = TMA ? (HD == 128 ? 3 : 4) : 2;
     const size_t ring = 2 * STAGES * KT * HD * 2 + ROWS * HD * 2;
@@ -445,7 +471,7 @@ int launch(const AttnParams& p, const CUtensorMap& tk, const CUtensorMap& tv, in
             return q6k_check_launch("attention_mma: shared memory attribute");
         configured = true;
     }
-    attention_mma_kernel<HD, WIDE, TMA><<<dim3(p.max_splits, p.Hkv, n_tiles), (WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0), smem, st>>>(tk, tv, p);
+    attention_mma_kernel<HD, WIDE, TMA><<<dim3(p.max_splits, p.Hkv, n_tiles), (WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0), smem, st>>>(maps[0], maps[1], maps[2], maps[3], p);
     if (int rc = q6k_check_launch("attention_mma")) return rc;
     if (p.max_splits > 1) {
         attention_merge_kernel<HD><<<dim3(n_tiles, p.Hkv, ROWS), HD, 0, st>>>(p);
@@ -455,9 +481,9 @@ int launch(const AttnParams& p, const CUtensorMap& tk, const CUtensorMap& tv, in
 }
 
 template <int HD>
-int launch_hd(const AttnParams& p, const CUtensorMap& tk, const CUtensorMap& tv, bool wide, bool tma, int n_tiles, cudaStream_t st) {
-    if (tma) return wide ? launch<HD, true, true>(p, tk, tv, n_tiles, st) : launch<HD, false, true>(p, tk, tv, n_tiles, st);
-    return wide ? launch<HD, true, false>(p, tk, tv, n_tiles, st) : launch<HD, false, false>(p, tk, tv, n_tiles, st);
+int launch_hd(const AttnParams& p, const CUtensorMap* maps, bool wide, bool tma, int n_tiles, cudaStream_t st) {
+    if (tma) return wide ? launch<HD, true, true>(p, maps, n_tiles, st) : launch<HD, false, true>(p, maps, n_tiles, st);
+    return wide ? launch<HD, true, false>(p, maps, n_tiles, st) : launch<HD, false, false>(p, maps, n_tiles, st);
 }
 
 }  // namespace
@@ -465,7 +491,7 @@ int launch_hd(const AttnParams& p, const CUtensorMap& tk, const CUtensorMap& tv,
 // Rows per tile for a group size: 16 (narrow) or 128 (wide) query rows hold rows/G tokens.
 Q6K_API int q6k_attention_mma_supported(int hd, int G, int wide) { return (hd == 64 || hd == 128) && G >= 1 && G <= (wide ? 128 : 16); }
 
-// q: bfloat16 [T, Hq, hd]; pages: bfloat16 [*, Hkv, page_size, hd]; tiles: tile_tok0/tile_ntok [n_tiles], the
+// q: bfloat16 [T, Hq, hd]; pages: bfloat16 [Hkv, num_pages, page_size, hd]; tiles: tile_tok0/tile_ntok [n_tiles], the
 // tokens of a tile being consecutive positions of one request, at most (wide ? 128 : 16) / G of them.
 // part_o: FP32 [T*Hq*max_splits*hd], part_ml: FP32 [T*Hq*max_splits*2] (unused when max_splits == 1).
 Q6K_API int q6k_attention_status() {
@@ -474,7 +500,7 @@ Q6K_API int q6k_attention_status() {
     return v;
 }
 
-// num_pages: pages in each pool (the TMA path addresses a pool as one [num_pages * Hkv * page_size, hd] matrix).
+// num_pages: pages in each pool (the TMA path addresses a pool as one [Hkv * num_pages * page_size, hd] matrix).
 Q6K_API int q6k_attention_mma(const void* q, const void* k_pages, const void* v_pages, long long num_pages, const int* block_table,
                               int max_blocks, int page_size, const int* req_of_token, const int* positions, const int* tile_tok0,
                               const int* tile_ntok, int n_tiles, int wide, int window, const float* sinks, float scale, void* out,
@@ -496,15 +522,18 @@ Q6K_API int q6k_attention_mma(const void* q, const void* k_pages, const void* v_
     p.max_blocks = max_blocks, p.page_size = page_size, p.window = window, p.Hq = Hq, p.Hkv = Hkv, p.G = G;
     p.max_splits = max_splits, p.min_tiles = min_tiles, p.scale_log2 = scale * LOG2E;
     // pages of 8, 16, 32, 64 keys (or whole multiples of 64) are boxes TMA can place on the swizzle pattern
+    p.num_pages = (int)num_pages;
     const long long pool_rows = num_pages * Hkv * page_size;
     const bool tma = page_size % 8 == 0 && (KT % page_size == 0 || page_size % KT == 0) && pool_rows < (1LL << 31) &&
                      ((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0;
-    CUtensorMap tk{}, tv{};
+    CUtensorMap maps[4] = {};                  // K and V by the page, K and V by the run of 64 keys
     if (tma) {
         const int box = page_size < KT ? page_size : KT;
         p.pool_rows = (int)pool_rows;
-        if (int rc = pool_map(&tk, k_pages, pool_rows, hd, box)) return rc;
-        if (int rc = pool_map(&tv, v_pages, pool_rows, hd, box)) return rc;
+        if (int rc = pool_map(&maps[0], k_pages, pool_rows, hd, box)) return rc;
+        if (int rc = pool_map(&maps[1], v_pages, pool_rows, hd, box)) return rc;
+        if (int rc = pool_map(&maps[2], k_pages, pool_rows, hd, KT)) return rc;
+        if (int rc = pool_map(&maps[3], v_pages, pool_rows, hd, KT)) return rc;
     }
-    return hd == 128 ? launch_hd<128>(p, tk, tv, wide, tma, n_tiles, st) : launch_hd<64>(p, tk, tv, wide, tma, n_tiles, st);
+    return hd == 128 ? launch_hd<128>(p, maps, wide, tma, n_tiles, st) : launch_hd<64>(p, maps, wide, tma, n_tiles, st);
 }

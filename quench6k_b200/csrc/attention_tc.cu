@@ -47,7 +47,7 @@ struct TcAttnParams {
     const int* tile_ntok;
     const float* sinks;                      // [Hq] or null
     __nv_bfloat16* out;                      // [T, Hq*HD]
-    int max_blocks, page_size, window, Hq, Hkv, G, pool_rows;
+    int max_blocks, page_size, window, Hq, Hkv, G, pool_rows, num_pages;
     float scale_log2;
 };
 
@@ -143,7 +143,8 @@ __device__ __forceinline__ float ex2_approx(float x) {
 __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)((c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)); }
 
 __global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                                                           const TcAttnParams p) {
+                                                           const __grid_constant__ CUtensorMap tm_k_run,
+                                                           const __grid_constant__ CUtensorMap tm_v_run, const TcAttnParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     // [Q][P][K0][K1][K2][V0][V1], each a [2][128][128 B] tile of 32 KB: K is free again as soon as
@@ -179,6 +180,8 @@ __global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_v) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k_run) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_v_run) : "memory");
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(512) : "memory");
@@ -194,9 +197,11 @@ __global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant
         // ---- producers: lane 0 brings the K tiles, lane 1 the V tiles (each at its ring's pace)
         if (lane < 2) {
             const bool is_k = lane == 0;
-            const int ps = p.page_size, box = ps < BN ? ps : BN, ring = is_k ? KS : VS;
+            const int ps = p.page_size, ring = is_k ? KS : VS;
             const uint32_t full0 = is_k ? k_full0 : v_full0, empty0 = is_k ? k_empty0 : v_empty0, base = is_k ? k_s : v_s;
             const CUtensorMap* map = is_k ? &tm_k : &tm_v;
+            const CUtensorMap* map_run = is_k ? &tm_k_run : &tm_v_run;
+            constexpr int RUN = 64;                                      // keys per run box
             for (int i = 0; i < n_tiles; ++i) {
                 const int s = i % ring;
                 if (!mbar_wait(empty0 + 8 * s, ((i / ring) & 1) ^ 1)) {
@@ -207,15 +212,34 @@ __global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant
                 mbar_expect_tx(fb, TILE_BYTES);
                 const int j0 = (first_tile + i) * BN;
                 const uint32_t dst = base + s * TILE_BYTES;
-                for (int b = 0; b < BN / box; ++b) {
-                    const int j = j0 + b * box;
-                    int y = p.pool_rows;                                 // out of range: zeros
-                    if (j + box > k_lo && j <= pos_last) {
-                        const int page = bt[j / ps];
-                        if (page >= 0) y = (page * p.Hkv + kh) * ps + j % ps;
+                // pages with consecutive numbers are contiguous for one head (head-major pools): where the
+                // pages of 64 keys form such a run, each half comes in as one box instead of one per page
+                for (int r = 0; r < BN / RUN; ++r) {
+                    const int jr = j0 + r * RUN;
+                    bool run = ps < RUN && jr >= k_lo && jr / ps + RUN / ps <= p.max_blocks;
+                    int first = -1;
+                    if (run) {
+                        first = bt[jr / ps];
+                        run = first >= 0;
+                        for (int b = 1; b < RUN / ps && run; ++b) run = bt[jr / ps + b] == first + b;
                     }
+                    if (run) {
+                        const int y = (kh * p.num_pages + first) * ps;
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) tma_load_2d(dst + h * HALF_BYTES + b * box * 128, map, h * 64, y, fb);
+                        for (int h = 0; h < 2; ++h) tma_load_2d(dst + h * HALF_BYTES + r * RUN * 128, map_run, h * 64, y, fb);
+                        continue;
+                    }
+                    const int per = ps < RUN ? RUN / ps : 1, bx = ps < RUN ? ps : RUN;      // boxes of this 64-key part
+                    for (int b = 0; b < per; ++b) {
+                        const int j = jr + b * bx;
+                        int y = p.pool_rows;                             // out of range: zeros
+                        if (j + bx > k_lo && j <= pos_last) {
+                            const int page = bt[j / ps];
+                            if (page >= 0) y = (kh * p.num_pages + page) * ps + j % ps;
+                        }
+#pragma unroll
+                        for (int h = 0; h < 2; ++h) tma_load_2d(dst + h * HALF_BYTES + (r * RUN + b * bx) * 128, map, h * 64, y, fb);
+                    }
                 }
             }
         }
@@ -463,7 +487,7 @@ Q6K_API int q6k_attention_tc_supported(int hd, int G, int page_size) {
     return hd == HD && G >= 1 && G <= BM && page_size >= 8 && page_size <= BN && BN % page_size == 0;
 }
 
-// q: bfloat16 [T, Hq, 128]; pages: bfloat16 [num_pages, Hkv, page_size, 128]; tiles of at most 128 / G
+// q: bfloat16 [T, Hq, 128]; pages: bfloat16 [Hkv, num_pages, page_size, 128]; tiles of at most 128 / G
 // tokens (consecutive positions of one request); out: bfloat16 [T, Hq*128].  Every tile reads its whole
 // key range (no key splits): the kernel for prompt portions.
 Q6K_API int q6k_attention_tc(const void* q, const void* k_pages, const void* v_pages, long long num_pages, const int* block_table,
@@ -483,10 +507,13 @@ Q6K_API int q6k_attention_tc(const void* q, const void* k_pages, const void* v_p
     p.q = (const __nv_bfloat16*)q, p.block_table = block_table, p.req_of_token = req_of_token, p.positions = positions;
     p.tile_tok0 = tile_tok0, p.tile_ntok = tile_ntok, p.sinks = sinks, p.out = (__nv_bfloat16*)out;
     p.max_blocks = max_blocks, p.page_size = page_size, p.window = window, p.Hq = Hq, p.Hkv = Hkv, p.G = G;
-    p.pool_rows = (int)pool_rows, p.scale_log2 = scale * LOG2E;
-    CUtensorMap tk, tv;
-    if (int rc = tc_pool_map(&tk, k_pages, pool_rows, page_size)) return rc;
-    if (int rc = tc_pool_map(&tv, v_pages, pool_rows, page_size)) return rc;
+    p.pool_rows = (int)pool_rows, p.num_pages = (int)num_pages, p.scale_log2 = scale * LOG2E;
+    CUtensorMap tk, tv, tk_run, tv_run;
+    const int box = page_size < 64 ? page_size : 64;       // pages of 128 keys are fetched as two boxes of 64
+    if (int rc = tc_pool_map(&tk, k_pages, pool_rows, box)) return rc;
+    if (int rc = tc_pool_map(&tv, v_pages, pool_rows, box)) return rc;
+    if (int rc = tc_pool_map(&tk_run, k_pages, pool_rows, 64)) return rc;
+    if (int rc = tc_pool_map(&tv_run, v_pages, pool_rows, 64)) return rc;
     const size_t smem = (2 + KS + VS) * TILE_BYTES + 1024;
     static bool configured = false;
     if (!configured) {
@@ -494,6 +521,6 @@ Q6K_API int q6k_attention_tc(const void* q, const void* k_pages, const void* v_p
             return q6k_check_launch("attention_tc: shared memory attribute");
         configured = true;
     }
-    attention_tc_kernel<<<dim3(n_tiles, Hkv), 192, smem, st>>>(tk, tv, p);
+    attention_tc_kernel<<<dim3(n_tiles, Hkv), 192, smem, st>>>(tk, tv, tk_run, tv_run, p);
     return q6k_check_launch("attention_tc");
 }

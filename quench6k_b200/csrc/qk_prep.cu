@@ -2,7 +2,8 @@
 // the pages of the cache.  Reference: crates/cuda/kernels/flint.cu:125-173 (there for one
 // sequence, a contiguous cache, head size 128 and theta 10000 compiled in).
 //
-// Page layout of one layer's K (and V) plane: [num_pages, kv_heads, page_size, head_dim].
+// Page layout of one layer's K (and V) plane: [kv_heads, num_pages, page_size, head_dim] (head-major,
+// so that pages with consecutive numbers are contiguous for one head and can be fetched as one TMA box).
 // The row of position p of request r is page block_table[r][p / page_size], offset p % page_size.
 #include "common.cuh"
 
@@ -13,7 +14,7 @@ namespace {
 template <typename T>
 __global__ void qk_prep_kernel(const float* qkv, int ld, int splits, size_t split_stride, int Hq, int Hkv, int hd, const float* q_norm, const float* k_norm,
                                float eps, int rope, float log2_theta, const int* positions, const int* req_of_token,
-                               const int* block_table, int max_blocks, int page_size, T* q_out, T* k_pages, T* v_pages) {
+                               const int* block_table, int max_blocks, int page_size, int num_pages, T* q_out, T* k_pages, T* v_pages) {
     extern __shared__ float xs[];            // hd floats
     __shared__ float red[32];
     const int t = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
@@ -48,7 +49,7 @@ __global__ void qk_prep_kernel(const float* qkv, int ld, int splits, size_t spli
         const int kh = h - Hq;
         const int page = block_table[(size_t)req_of_token[t] * max_blocks + pos / page_size];
         if (page < 0) return;                 // no page behind this position: nothing is written
-        const size_t row = (((size_t)page * Hkv + kh) * page_size + pos % page_size) * hd + d;
+        const size_t row = (((size_t)kh * num_pages + page) * page_size + pos % page_size) * hd + d;
         k_pages[row] = from_f32<T>(x);
         float v = 0.0f;
         for (int s = 0; s < splits; ++s) v += qkv[s * split_stride + (size_t)t * ld + (size_t)(Hq + Hkv + kh) * hd + d];
@@ -63,8 +64,8 @@ template <typename T, int EPL>
 __global__ void __launch_bounds__(256) qk_prep_warp_kernel(const float* qkv, int ld, int splits, size_t split_stride, int Hq, int Hkv, const float* q_norm,
                                                            const float* k_norm, float eps, int rope, float log2_theta,
                                                            const int* positions, const int* req_of_token, const int* block_table,
-                                                           int max_blocks, int page_size, T* q_out, T* k_pages, T* v_pages,
-                                                           int heads) {
+                                                           int max_blocks, int page_size, int num_pages, T* q_out, T* k_pages,
+                                                           T* v_pages, int heads) {
     constexpr int hd = EPL * 32, half = hd / 2;
     const int t = blockIdx.x, h = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (h >= heads) return;
@@ -104,7 +105,7 @@ __global__ void __launch_bounds__(256) qk_prep_warp_kernel(const float* qkv, int
         const int kh = h - Hq;
         const int page = block_table[(size_t)req_of_token[t] * max_blocks + pos / page_size];
         if (page < 0) return;
-        const size_t row = (((size_t)page * Hkv + kh) * page_size + pos % page_size) * hd;
+        const size_t row = (((size_t)kh * num_pages + page) * page_size + pos % page_size) * hd;
         const float* vsrc = qkv + (size_t)t * ld + (size_t)(Hq + Hkv + kh) * hd;
 #pragma unroll
         for (int i = 0; i < EPL; ++i) {
@@ -124,8 +125,8 @@ __global__ void __launch_bounds__(256) qk_prep_warp_kernel(const float* qkv, int
 // splits > 1: qkv is [splits, T, ld] (slices split_stride floats apart) and the slices are summed in order first.
 Q6K_API int q6k_qk_prep(const float* qkv, int ld, int splits, long long split_stride, int T_, int Hq, int Hkv, int hd, const float* q_norm, const float* k_norm,
                         float eps, int rope, float theta, const int* positions, const int* req_of_token,
-                        const int* block_table, int max_blocks, int page_size, void* q_out, void* k_pages, void* v_pages,
-                        int write_kv, int dtype, cudaStream_t st) {
+                        const int* block_table, int max_blocks, int page_size, int num_pages, void* q_out, void* k_pages,
+                        void* v_pages, int write_kv, int dtype, cudaStream_t st) {
     if (T_ == 0) return 0;
     Q6K_REQUIRE(T_ > 0 && Hq > 0 && Hkv > 0 && hd > 0, "qk_prep: bad sizes T=%d Hq=%d Hkv=%d hd=%d", T_, Hq, Hkv, hd);
     Q6K_REQUIRE(splits >= 1, "qk_prep: bad split count %d", splits);
@@ -139,7 +140,7 @@ Q6K_API int q6k_qk_prep(const float* qkv, int ld, int splits, long long split_st
         Q6K_REQUIRE(wgrid.y <= 65535, "qk_prep: %d heads exceed the grid limit", heads);
 #define WARP_LAUNCH(EPL)                                                                                                    \
     qk_prep_warp_kernel<T, EPL><<<wgrid, 256, 0, st>>>(qkv, ld, splits, (size_t)split_stride, Hq, Hkv, q_norm, k_norm, eps, rope, l2t, positions, req_of_token, \
-                                                       block_table, max_blocks, page_size, (T*)q_out, (T*)k_pages, (T*)v_pages, heads)
+                                                       block_table, max_blocks, page_size, num_pages, (T*)q_out, (T*)k_pages, (T*)v_pages, heads)
         Q6K_DISPATCH(dtype, {
             if (hd == 64) WARP_LAUNCH(2);
             else if (hd == 128) WARP_LAUNCH(4);
@@ -152,6 +153,6 @@ Q6K_API int q6k_qk_prep(const float* qkv, int ld, int splits, long long split_st
     dim3 grid(T_, heads);
     Q6K_DISPATCH(dtype, qk_prep_kernel<T><<<grid, threads, hd * sizeof(float), st>>>(
                             qkv, ld, splits, (size_t)split_stride, Hq, Hkv, hd, q_norm, k_norm, eps, rope, l2t, positions, req_of_token, block_table,
-                            max_blocks, page_size, (T*)q_out, (T*)k_pages, (T*)v_pages););
+                            max_blocks, page_size, num_pages, (T*)q_out, (T*)k_pages, (T*)v_pages););
     return q6k_check_launch("qk_prep");
 }

@@ -83,7 +83,7 @@ class Engine:
         seed = params.seed if params.seed is not None else random.getrandbits(64)
         req = Request(rid, [int(t) for t in prompt], params, output=[int(first_token)], rng=SplitMix64(seed))
         self.runner.add_request(rid)
-        step = 1 << 16
+        step = self.scheduler.max_batch_tokens          # pages are taken as portions of a chunked prefill would take them
         for at in range(0, len(req.prompt), step):
             self.runner.assume_cached(rid, min(step, len(req.prompt) - at))
         req.num_computed = len(req.prompt)

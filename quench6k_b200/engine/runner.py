@@ -68,7 +68,7 @@ class ModelRunner:
                 self.caches.append(None)
             else:
                 g = self.group_of[p]
-                shape = (pages[g], r.kv_heads, page_size, r.head_dim)
+                shape = (r.kv_heads, pages[g], page_size, r.head_dim)      # head-major: a head's pages are contiguous
                 self.caches.append(LayerCache(g, torch.zeros(shape, dtype=rt.dtype, device=rt.device),
                                               torch.zeros(shape, dtype=rt.dtype, device=rt.device), page_size))
         self.states = [None if s is None else torch.zeros((max_requests, *s), dtype=torch.float32, device=rt.device)

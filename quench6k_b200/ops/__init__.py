@@ -327,8 +327,8 @@ def qk_prep(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, q_norm, k_norm, eps: 
         _need(k_pages, "k_pages", out_dtype)
         _need(v_pages, "v_pages", out_dtype, k_pages.shape)
         _need(block_table, "block_table", torch.int32)
-        if tuple(k_pages.shape[1:]) != (Hkv, page_size, hd):
-            raise KernelError(f"qk_prep: pages have shape {tuple(k_pages.shape)}, expected [*, {Hkv}, {page_size}, {hd}]")
+        if k_pages.dim() != 4 or k_pages.shape[0] != Hkv or tuple(k_pages.shape[2:]) != (page_size, hd):
+            raise KernelError(f"qk_prep: pages have shape {tuple(k_pages.shape)}, expected [{Hkv}, *, {page_size}, {hd}]")
     for nm, w in (("q_norm", q_norm), ("k_norm", k_norm)):
         if w is not None:
             _need(w, nm, torch.float32, (hd,))
@@ -336,8 +336,8 @@ def qk_prep(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, q_norm, k_norm, eps: 
     max_blocks = block_table.shape[1] if block_table is not None else 1
     _call("q6k_qk_prep", _ptr(qkv), _i(qkv.stride(0)), _i(splits), _ll(split_stride), _i(T), _i(Hq), _i(Hkv), _i(hd), _ptr(q_norm), _ptr(k_norm), _f(eps),
           _i(1 if rope_theta is not None else 0), _f(rope_theta or 0.0), _ptr(positions), _ptr(req_of_token), _ptr(block_table),
-          _i(max_blocks), _i(page_size), _ptr(q), _ptr(k_pages), _ptr(v_pages), _i(1 if write else 0),
-          _i(dtype_code(out_dtype)), _stream())
+          _i(max_blocks), _i(page_size), _i(k_pages.shape[1] if write else 0), _ptr(q), _ptr(k_pages), _ptr(v_pages),
+          _i(1 if write else 0), _i(dtype_code(out_dtype)), _stream())
     return q
 
 
@@ -349,7 +349,7 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
     T, Hq, hd = q.shape
     _need(k_pages, "k_pages", q.dtype)
     _need(v_pages, "v_pages", q.dtype, k_pages.shape)
-    _, Hkv, page_size, hd2 = k_pages.shape
+    Hkv, num_pages, page_size, hd2 = k_pages.shape
     if hd2 != hd:
         raise KernelError(f"attention: q has head_dim {hd}, the pages {hd2}")
     _need(block_table, "block_table", torch.int32)
@@ -358,7 +358,7 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
     if sinks is not None:
         _need(sinks, "sinks", torch.float32, (Hq,))
     out = torch.empty((T, Hq * hd), dtype=q.dtype, device=q.device)
-    _call("q6k_attention_generic", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(block_table), _i(block_table.shape[1]),
+    _call("q6k_attention_generic", _ptr(q), _ptr(k_pages), _ptr(v_pages), _i(num_pages), _ptr(block_table), _i(block_table.shape[1]),
           _i(page_size), _ptr(req_of_token), _ptr(positions), _i(window or 0), _ptr(sinks),
           _f(scale if scale is not None else 1.0 / math.sqrt(hd)), _ptr(out), _i(T), _i(Hq), _i(Hkv), _i(hd),
           _i(dtype_code(q.dtype)), _stream())
@@ -381,7 +381,7 @@ def attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, 
     T, Hq, hd = q.shape
     _need(k_pages, "k_pages", torch.bfloat16)
     _need(v_pages, "v_pages", torch.bfloat16, k_pages.shape)
-    _, Hkv, page_size, hd2 = k_pages.shape
+    Hkv, num_pages, page_size, hd2 = k_pages.shape
     if hd2 != hd:
         raise KernelError(f"attention: q has head_dim {hd}, the pages {hd2}")
     for nm, t in (("block_table", block_table), ("req_of_token", req_of_token), ("positions", positions),
@@ -390,7 +390,7 @@ def attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, 
     if sinks is not None:
         _need(sinks, "sinks", torch.float32, (Hq,))
     out = torch.empty((T, Hq * hd), dtype=torch.bfloat16, device=q.device)
-    _call("q6k_attention_tc", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ll(k_pages.shape[0]), _ptr(block_table),
+    _call("q6k_attention_tc", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ll(num_pages), _ptr(block_table),
           _i(block_table.shape[1]), _i(page_size), _ptr(req_of_token), _ptr(positions), _ptr(tile_tok0), _ptr(tile_ntok),
           _i(tile_tok0.numel()), _i(window or 0), _ptr(sinks), _f(scale if scale is not None else 1.0 / math.sqrt(hd)), _ptr(out),
           _i(Hq), _i(Hkv), _i(hd), _stream())
@@ -414,7 +414,7 @@ def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
     T, Hq, hd = q.shape
     _need(k_pages, "k_pages", torch.bfloat16)
     _need(v_pages, "v_pages", torch.bfloat16, k_pages.shape)
-    _, Hkv, page_size, hd2 = k_pages.shape
+    Hkv, num_pages, page_size, hd2 = k_pages.shape
     if hd2 != hd:
         raise KernelError(f"attention: q has head_dim {hd}, the pages {hd2}")
     for nm, t in (("block_table", block_table), ("req_of_token", req_of_token), ("positions", positions),
@@ -429,7 +429,7 @@ def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
         ws = _workspace(T * Hq * max_splits * (hd + 2) * 4, q.device)
         part_o = ws[: T * Hq * max_splits * hd]
         part_ml = ws[T * Hq * max_splits * hd: T * Hq * max_splits * (hd + 2)]
-    _call("q6k_attention_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ll(k_pages.shape[0]), _ptr(block_table),
+    _call("q6k_attention_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ll(num_pages), _ptr(block_table),
           _i(block_table.shape[1]), _i(page_size),
           _ptr(req_of_token), _ptr(positions), _ptr(tile_tok0), _ptr(tile_ntok), _i(n_tiles), _i(1 if wide else 0), _i(window or 0),
           _ptr(sinks), _f(scale if scale is not None else 1.0 / math.sqrt(hd)), _ptr(out), _ptr(part_o), _ptr(part_ml),

@@ -56,7 +56,8 @@ class CacheRequest:
 
 @dataclass
 class LayerCache:
-    """The pages of one executed layer position.  k, v: [num_pages, kv_heads, page_size, head_dim]."""
+    """The pages of one executed layer position.  k, v: [kv_heads, num_pages, page_size, head_dim]
+    (head-major, so that pages with consecutive numbers lie next to each other for one head)."""
     group: int
     k: torch.Tensor
     v: torch.Tensor

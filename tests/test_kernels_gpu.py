@@ -124,11 +124,11 @@ def _paged(k, v, page_size, num_pages, dtype, seed):
     nb = (T + page_size - 1) // page_size
     g = torch.Generator().manual_seed(seed)
     table = torch.randperm(num_pages, generator=g)[:nb].to(torch.int32)
-    kp = torch.full((num_pages, Hkv, page_size, hd), float("nan"), dtype=dtype)
-    vp = torch.full((num_pages, Hkv, page_size, hd), float("nan"), dtype=dtype)
+    kp = torch.full((Hkv, num_pages, page_size, hd), float("nan"), dtype=dtype)
+    vp = torch.full((Hkv, num_pages, page_size, hd), float("nan"), dtype=dtype)
     for t in range(T):
-        kp[table[t // page_size], :, t % page_size] = k[t].to(dtype)
-        vp[table[t // page_size], :, t % page_size] = v[t].to(dtype)
+        kp[:, table[t // page_size], t % page_size] = k[t].to(dtype)
+        vp[:, table[t // page_size], t % page_size] = v[t].to(dtype)
     return kp.to(DEV), vp.to(DEV), table
 
 
@@ -176,7 +176,7 @@ def test_qk_prep(dtype, Hq, Hkv, hd, ps, norm, theta):
     rot = torch.zeros(T, dtype=torch.int32, device=DEV)
     nb = (pos0 + T + ps - 1) // ps
     table = torch.randperm(40)[:nb].to(torch.int32).view(1, nb).to(DEV)
-    kp = torch.zeros(40, Hkv, ps, hd, dtype=dtype, device=DEV)
+    kp = torch.zeros(Hkv, 40, ps, hd, dtype=dtype, device=DEV)
     vp = torch.zeros_like(kp)
     q = ops.qk_prep(qkv, Hq, Hkv, hd, qn, kn, eps, theta, pos, rot, table, ps, kp, vp, dtype)
     x = qkv.double().cpu()
@@ -192,8 +192,8 @@ def test_qk_prep(dtype, Hq, Hkv, hd, ps, norm, theta):
     for t in range(T):
         p = pos0 + t
         page = int(table[0, p // ps])
-        assert (kp[page, :, p % ps].double().cpu() - rk[t]).abs().max() <= tol * rk.abs().max()
-        assert (vp[page, :, p % ps].double().cpu() - rv[t]).abs().max() <= tol * rv.abs().max()
+        assert (kp[:, page, p % ps].double().cpu() - rk[t]).abs().max() <= tol * rk.abs().max()
+        assert (vp[:, page, p % ps].double().cpu() - rv[t]).abs().max() <= tol * rv.abs().max()
     # read-only layers produce the same q and leave the pages alone
     k0 = kp.clone()
     q2 = ops.qk_prep(qkv[:, :Hq * hd].contiguous(), Hq, Hkv, hd, qn, kn, eps, theta, pos, rot, None, ps, None, None, dtype)
@@ -223,7 +223,7 @@ def test_argmax_and_topk_pool(rows, V):
 def test_kernels_refuse_what_they_cannot_do():
     from quench6k_b200 import ops
     q = torch.zeros(1, 2, 24, device=DEV)
-    pages = torch.zeros(2, 1, 4, 24, device=DEV)
+    pages = torch.zeros(1, 2, 4, 24, device=DEV)
     z = torch.zeros(1, dtype=torch.int32, device=DEV)
     with pytest.raises(ops.KernelError, match="multiple of 16"):
         ops.attention_generic(q, pages, pages, z.view(1, 1), z, z, None, None)
@@ -310,9 +310,13 @@ def test_attention_mma(Hq, Hkv, hd, ps, window, sinks, mode):
     g = torch.Generator().manual_seed(Hq * 1000 + hd + (window or 0))
     lens = [700, 150, 333, 64, 65]
     num_pages = sum(-(-n // ps) for n in lens) + 5
-    perm = torch.randperm(num_pages, generator=g).tolist()
-    kp = torch.full((num_pages, Hkv, ps, hd), float("nan"), dtype=torch.bfloat16)
-    vp = torch.full((num_pages, Hkv, ps, hd), float("nan"), dtype=torch.bfloat16)
+    # requests 0 and 2 hold runs of consecutive pages (fetched as whole boxes), the others scattered ones
+    need = [-(-n // ps) for n in lens]
+    runs = {0: list(range(3, 3 + need[0])), 2: list(range(3 + need[0] + 1, 3 + need[0] + 1 + need[2]))}
+    taken = set(runs[0]) | set(runs[2])
+    perm = [x for x in torch.randperm(num_pages, generator=g).tolist() if x not in taken]
+    kp = torch.full((Hkv, num_pages, ps, hd), float("nan"), dtype=torch.bfloat16)
+    vp = torch.full((Hkv, num_pages, ps, hd), float("nan"), dtype=torch.bfloat16)
     tables, refs, qs = [], [], []
     for n in lens:
         q, k, v = (torch.randn(n, h, hd, generator=g) for h in (Hq, Hkv, Hkv))
@@ -323,10 +327,10 @@ def test_attention_mma(Hq, Hkv, hd, ps, window, sinks, mode):
         if sinks and tables:
             sk = refs[0][1]                                # one sink vector per layer
         refs.append((P.attention(qd.double(), kd.double(), vd.double(), window, sk.double() if sinks else None, True), sk))
-        table = [perm.pop() for _ in range(-(-n // ps))]
+        table = runs[len(tables)] if len(tables) in runs else [perm.pop() for _ in range(-(-n // ps))]
         for t in range(n):
-            kp[table[t // ps], :, t % ps] = kd[t]
-            vp[table[t // ps], :, t % ps] = vd[t]
+            kp[:, table[t // ps], t % ps] = kd[t]
+            vp[:, table[t // ps], t % ps] = vd[t]
         tables.append(table)
         qs.append(qd)
     width = max(len(t) for t in tables)
@@ -397,9 +401,13 @@ def test_attention_tc(Hq, Hkv, ps, window, sinks):
     g = torch.Generator().manual_seed(Hq * 1000 + ps + (window or 0))
     lens = [700, 150, 333, 64, 129]
     num_pages = sum(-(-n // ps) for n in lens) + 5
-    perm = torch.randperm(num_pages, generator=g).tolist()
-    kp = torch.full((num_pages, Hkv, ps, hd), float("nan"), dtype=torch.bfloat16)
-    vp = torch.full((num_pages, Hkv, ps, hd), float("nan"), dtype=torch.bfloat16)
+    # requests 0 and 2 hold runs of consecutive pages (fetched as whole boxes), the others scattered ones
+    need = [-(-n // ps) for n in lens]
+    runs = {0: list(range(3, 3 + need[0])), 2: list(range(3 + need[0] + 1, 3 + need[0] + 1 + need[2]))}
+    taken = set(runs[0]) | set(runs[2])
+    perm = [x for x in torch.randperm(num_pages, generator=g).tolist() if x not in taken]
+    kp = torch.full((Hkv, num_pages, ps, hd), float("nan"), dtype=torch.bfloat16)
+    vp = torch.full((Hkv, num_pages, ps, hd), float("nan"), dtype=torch.bfloat16)
     tables, refs, qs = [], [], []
     sk = torch.randn(Hq, generator=g) if sinks else None
     for n in lens:
@@ -408,10 +416,10 @@ def test_attention_tc(Hq, Hkv, ps, window, sinks):
         q[-20:] += 1.5 * k[3].repeat_interleave(G, 0) / k[3].norm()
         qd, kd, vd = (x.to(torch.bfloat16) for x in (q, k, v))
         refs.append(P.attention(qd.double(), kd.double(), vd.double(), window, sk.double() if sinks else None, True))
-        table = [perm.pop() for _ in range(-(-n // ps))]
+        table = runs[len(tables)] if len(tables) in runs else [perm.pop() for _ in range(-(-n // ps))]
         for t in range(n):
-            kp[table[t // ps], :, t % ps] = kd[t]
-            vp[table[t // ps], :, t % ps] = vd[t]
+            kp[:, table[t // ps], t % ps] = kd[t]
+            vp[:, table[t // ps], t % ps] = vd[t]
         tables.append(table)
         qs.append(qd)
     width = max(len(t) for t in tables)

@@ -82,7 +82,7 @@ def test_attention_part_over_pages(dtype, window, sinks, qk_norm, rope):
     assert (req.kind, req.window, req.kv_heads, req.head_dim) == ("sliding" if window else "full", window, Hkv, hd)
     lens = [19, 11]
     xs = [(torch.randn(n, D) * 0.8).to(dtype) for n in lens]
-    cache = LayerCache(0, torch.zeros(16, Hkv, ps, hd, dtype=dtype, device=DEV), torch.zeros(16, Hkv, ps, hd, dtype=dtype, device=DEV), ps)
+    cache = LayerCache(0, torch.zeros(Hkv, 16, ps, hd, dtype=dtype, device=DEV), torch.zeros(Hkv, 16, ps, hd, dtype=dtype, device=DEV), ps)
     tables = [[[9, 2, 14, 5, 0], [7, 3, 11]]]
     # step 1: the first 13 tokens of request 0; step 2: its last 6 beside all of request 1
     def run(x, ctx):

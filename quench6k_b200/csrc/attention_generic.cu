@@ -23,6 +23,7 @@ __global__ void __launch_bounds__(128) attention_generic_kernel(const T* q, cons
                                                                 int num_pages, const int* req_of_token, const int* positions, int window,
                                                                 const float* sinks, float scale, T* out, int Hq, int Hkv,
                                                                 int hd) {
+    pdl_enter();
     extern __shared__ float qs[];             // [warps][hd]
     const int t = blockIdx.x, kh = blockIdx.y, G = Hq / Hkv;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -108,7 +109,7 @@ Q6K_API int q6k_attention_generic(const void* q, const void* k_pages, const void
     const int G = Hq / Hkv;
     const int warps = G < 4 ? G : 4;
     dim3 grid(T_, Hkv);
-    Q6K_DISPATCH(dtype, attention_generic_kernel<T><<<grid, warps * 32, warps * hd * sizeof(float), st>>>(
+    Q6K_DISPATCH(dtype, q6k_launch(attention_generic_kernel<T>, grid, warps * 32, warps * hd * sizeof(float), st, 
                             (const T*)q, (const T*)k_pages, (const T*)v_pages, block_table, max_blocks, page_size,
                             num_pages, req_of_token, positions, window, sinks, scale, (T*)out, Hq, Hkv, hd););
     return q6k_check_launch("attention_generic");

@@ -99,6 +99,7 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0)) attentio
                                                                         const __grid_constant__ CUtensorMap tm_v,
                                                                         const __grid_constant__ CUtensorMap tm_k_run,
                                                                         const __grid_constant__ CUtensorMap tm_v_run, const AttnParams p) {
+    pdl_enter();
     constexpr int CW = WIDE ? 8 : 4;         // consumer warps
     constexpr int CT = CW * 32;              // consumer threads
     constexpr int ROWS = WIDE ? 128 : 16;
@@ -415,6 +416,7 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0)) attentio
 // the tile), one thread per head dimension; the splits' values are fetched with independent loads.
 template <int HD>
 __global__ void __launch_bounds__(HD) attention_merge_kernel(const AttnParams p) {
+    pdl_enter();
     const int tile = blockIdx.x, kh = blockIdx.y, r = blockIdx.z, G = p.G, d = threadIdx.x;
     const int tok0 = p.tile_tok0[tile], ntok = p.tile_ntok[tile];
     const int tt = r / G, hg = r % G;
@@ -471,10 +473,10 @@ int launch(const AttnParams& p, const CUtensorMap* maps, int n_tiles, cudaStream
             return q6k_check_launch("attention_mma: shared memory attribute");
         configured = true;
     }
-    attention_mma_kernel<HD, WIDE, TMA><<<dim3(p.max_splits, p.Hkv, n_tiles), (WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0), smem, st>>>(maps[0], maps[1], maps[2], maps[3], p);
+    q6k_launch(attention_mma_kernel<HD, WIDE, TMA>, dim3(p.max_splits, p.Hkv, n_tiles), (WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0), smem, st, maps[0], maps[1], maps[2], maps[3], p);
     if (int rc = q6k_check_launch("attention_mma")) return rc;
     if (p.max_splits > 1) {
-        attention_merge_kernel<HD><<<dim3(n_tiles, p.Hkv, ROWS), HD, 0, st>>>(p);
+        q6k_launch(attention_merge_kernel<HD>, dim3(n_tiles, p.Hkv, ROWS), HD, 0, st, p);
         return q6k_check_launch("attention_merge");
     }
     return 0;

@@ -145,6 +145,7 @@ __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)((c >> 
 __global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                                                            const __grid_constant__ CUtensorMap tm_k_run,
                                                            const __grid_constant__ CUtensorMap tm_v_run, const TcAttnParams p) {
+    pdl_enter();
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     // [Q][P][K0][K1][K2][V0][V1], each a [2][128][128 B] tile of 32 KB: K is free again as soon as
@@ -521,6 +522,6 @@ Q6K_API int q6k_attention_tc(const void* q, const void* k_pages, const void* v_p
             return q6k_check_launch("attention_tc: shared memory attribute");
         configured = true;
     }
-    attention_tc_kernel<<<dim3(n_tiles, Hkv), 192, smem, st>>>(tk, tv, tk_run, tv_run, p);
+    q6k_launch(attention_tc_kernel, dim3(n_tiles, Hkv), 192, smem, st, tk, tv, tk_run, tv_run, p);
     return q6k_check_launch("attention_tc");
 }

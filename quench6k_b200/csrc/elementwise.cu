@@ -7,6 +7,7 @@ namespace {
 
 template <typename T>
 __global__ void embed_kernel(const int* tokens, const T* table, float* h, int D, int V) {
+    pdl_enter();
     const int t = blockIdx.x;
     int tok = tokens[t];
     tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);      // ids are validated on the host; never read outside the table
@@ -21,6 +22,7 @@ __global__ void embed_kernel(const int* tokens, const T* table, float* h, int D,
 template <typename T>
 __global__ void __launch_bounds__(256) rmsnorm_kernel(float* x, const float* add, const int* rows, const float* w, float eps,
                                                       T* out, int D) {
+    pdl_enter();
     __shared__ float red[32];
     const int r = blockIdx.x;
     float* xr = x + (size_t)(rows ? rows[r] : r) * D;
@@ -43,6 +45,7 @@ __global__ void __launch_bounds__(256) rmsnorm_kernel(float* x, const float* add
 // h[t, d] += sum_s w[t, s] * y[pair_row[t*S + s], d], slots in order (so the result does not
 // depend on where the permutation put the rows).  pair_row == null: rows are in pair order.
 __global__ void combine_kernel(const float* y, const int* pair_row, const float* sel_w, int S, int D, float* h) {
+    pdl_enter();
     const int t = blockIdx.x, d = blockIdx.y * blockDim.x + threadIdx.x;
     if (d >= D) return;
     float acc = 0.0f;
@@ -56,6 +59,7 @@ __global__ void combine_kernel(const float* y, const int* pair_row, const float*
 template <typename T, int V4>
 __global__ void __launch_bounds__(256) rmsnorm_reg_kernel(float* x, const float* add, int add_splits, size_t add_stride, const int* rows,
                                                           const float* w, float eps, T* out, int D) {
+    pdl_enter();
     __shared__ float red[32];
     const int r = blockIdx.x, nv = D >> 2;
     float4* xr = reinterpret_cast<float4*>(x + (size_t)(rows ? rows[r] : r) * D);
@@ -95,6 +99,7 @@ __global__ void __launch_bounds__(256) rmsnorm_reg_kernel(float* x, const float*
 // act[r, i] = T(silu(g[r, i]) * u[r, i]) for gu = [rows, 2*I] (gate columns first).
 template <typename T>
 __global__ void swiglu_kernel(const float* gu, T* act, int I, size_t count) {
+    pdl_enter();
     const size_t idx = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
     if (idx >= count) return;
     const size_t r = idx / I;
@@ -105,6 +110,7 @@ __global__ void swiglu_kernel(const float* gu, T* act, int I, size_t count) {
 
 // out[r, :] = x[idx[r], :] for rows of `bytes` bytes (a multiple of 16), 16 bytes per thread step.
 __global__ void gather_rows_kernel(const uint4* x, const int* idx, uint4* out, int vec_per_row) {
+    pdl_enter();
     const size_t src = (size_t)idx[blockIdx.x] * vec_per_row, dst = (size_t)blockIdx.x * vec_per_row;
     for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) out[dst + i] = x[src + i];
 }
@@ -116,14 +122,14 @@ Q6K_API int q6k_gather_rows(const void* x, const int* idx, void* out, int rows, 
     if (rows == 0) return 0;
     Q6K_REQUIRE(rows > 0 && row_bytes > 0 && row_bytes % 16 == 0, "gather_rows: rows of %d bytes are not a multiple of 16", row_bytes);
     Q6K_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0, "gather_rows: buffers must be 16-byte aligned");
-    gather_rows_kernel<<<rows, 128, 0, st>>>((const uint4*)x, idx, (uint4*)out, row_bytes / 16);
+    q6k_launch(gather_rows_kernel, rows, 128, 0, st, (const uint4*)x, idx, (uint4*)out, row_bytes / 16);
     return q6k_check_launch("gather_rows");
 }
 
 Q6K_API int q6k_embed(const int* tokens, const void* table, float* h, int T_, int D, int V, int dtype, cudaStream_t st) {
     if (T_ == 0) return 0;
     Q6K_REQUIRE(T_ > 0 && D > 0 && V > 0, "embed: bad sizes T=%d D=%d V=%d", T_, D, V);
-    Q6K_DISPATCH(dtype, embed_kernel<T><<<T_, 256, 0, st>>>(tokens, (const T*)table, h, D, V););
+    Q6K_DISPATCH(dtype, q6k_launch(embed_kernel<T>, T_, 256, 0, st, tokens, (const T*)table, h, D, V););
     return q6k_check_launch("embed");
 }
 
@@ -140,14 +146,14 @@ Q6K_API int q6k_rmsnorm(float* x, const float* add, int add_splits, long long ad
     if (vec) {
         const int v4 = (D / 4 + 255) / 256;
         Q6K_DISPATCH(dtype, {
-            if (v4 <= 1) rmsnorm_reg_kernel<T, 1><<<R, 256, 0, st>>>(x, add, add_splits, (size_t)add_stride, rows, w, eps, (T*)out, D);
-            else if (v4 <= 2) rmsnorm_reg_kernel<T, 2><<<R, 256, 0, st>>>(x, add, add_splits, (size_t)add_stride, rows, w, eps, (T*)out, D);
-            else rmsnorm_reg_kernel<T, 4><<<R, 256, 0, st>>>(x, add, add_splits, (size_t)add_stride, rows, w, eps, (T*)out, D);
+            if (v4 <= 1) q6k_launch(rmsnorm_reg_kernel<T, 1>, R, 256, 0, st, x, add, add_splits, (size_t)add_stride, rows, w, eps, (T*)out, D);
+            else if (v4 <= 2) q6k_launch(rmsnorm_reg_kernel<T, 2>, R, 256, 0, st, x, add, add_splits, (size_t)add_stride, rows, w, eps, (T*)out, D);
+            else q6k_launch(rmsnorm_reg_kernel<T, 4>, R, 256, 0, st, x, add, add_splits, (size_t)add_stride, rows, w, eps, (T*)out, D);
         });
         return q6k_check_launch("rmsnorm");
     }
     Q6K_REQUIRE(add_splits == 1, "rmsnorm: summing split partials needs a width that is a multiple of 4 and at most 4096 (got %d)", D);
-    Q6K_DISPATCH(dtype, rmsnorm_kernel<T><<<R, 256, 0, st>>>(x, add, rows, w, eps, (T*)out, D););
+    Q6K_DISPATCH(dtype, q6k_launch(rmsnorm_kernel<T>, R, 256, 0, st, x, add, rows, w, eps, (T*)out, D););
     return q6k_check_launch("rmsnorm");
 }
 
@@ -155,7 +161,7 @@ Q6K_API int q6k_combine(const float* y, const int* pair_row, const float* sel_w,
                         cudaStream_t st) {
     if (T_ == 0) return 0;
     Q6K_REQUIRE(T_ > 0 && S > 0 && D > 0, "combine: bad sizes T=%d S=%d D=%d", T_, S, D);
-    combine_kernel<<<dim3(T_, (D + 255) / 256), 256, 0, st>>>(y, pair_row, sel_w, S, D, h);
+    q6k_launch(combine_kernel, dim3(T_, (D + 255) / 256), 256, 0, st, y, pair_row, sel_w, S, D, h);
     return q6k_check_launch("combine");
 }
 
@@ -163,6 +169,6 @@ Q6K_API int q6k_swiglu(const float* gu, void* act, int rows, int I, int dtype, c
     if (rows == 0) return 0;
     Q6K_REQUIRE(rows > 0 && I > 0, "swiglu: bad sizes rows=%d I=%d", rows, I);
     const size_t count = (size_t)rows * I;
-    Q6K_DISPATCH(dtype, swiglu_kernel<T><<<(unsigned)((count + 255) / 256), 256, 0, st>>>(gu, (T*)act, I, count););
+    Q6K_DISPATCH(dtype, q6k_launch(swiglu_kernel<T>, (unsigned)((count + 255) / 256), 256, 0, st, gu, (T*)act, I, count););
     return q6k_check_launch("swiglu");
 }

@@ -1,4 +1,6 @@
 // Error text of the exported launchers (one message per host thread).
+#include <cstdlib>
+
 #include "common.cuh"
 
 static thread_local char g_msg[512] = "";
@@ -15,6 +17,14 @@ int q6k_check_launch(const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e == cudaSuccess) return 0;
     return q6k_fail("%s: %s", what, cudaGetErrorString(e));
+}
+
+bool q6k_pdl_enabled() {
+    static const bool on = [] {
+        const char* v = getenv("Q6K_PDL");
+        return v && v[0] == '1';
+    }();
+    return on;
 }
 
 Q6K_API const char* q6k_last_error() { return g_msg; }

@@ -23,6 +23,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* A, int lda, con
                                                         size_t w_group_stride, void* out_, int ldo, int M, int N, int K,
                                                         const int* tile_group, const int* tile_row0,
                                                         const int* group_offsets, const int* num_tiles) {
+    pdl_enter();
     constexpr bool DUAL = EPI == EPI_SWIGLU;
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
@@ -103,6 +104,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* A, int lda, con
 // One block; groups are walked in order so the list is a function of the offsets only.
 __global__ void tile_list_kernel(const int* offsets, int G, int bm, int* tile_group, int* tile_row0, int* num_tiles,
                                  int max_tiles) {
+    pdl_enter();
     __shared__ int base;
     if (threadIdx.x == 0) base = 0;
     __syncthreads();
@@ -144,7 +146,7 @@ Q6K_API int q6k_gemm_tile_rows() { return BM; }
 Q6K_API int q6k_tile_list(const int* offsets, int G, int bm, int* tile_group, int* tile_row0, int* num_tiles,
                           int max_tiles, cudaStream_t st) {
     Q6K_REQUIRE(G > 0 && bm > 0 && max_tiles > 0, "tile_list: bad sizes G=%d bm=%d max_tiles=%d", G, bm, max_tiles);
-    tile_list_kernel<<<1, 256, 0, st>>>(offsets, G, bm, tile_group, tile_row0, num_tiles, max_tiles);
+    q6k_launch(tile_list_kernel, 1, 256, 0, st, offsets, G, bm, tile_group, tile_row0, num_tiles, max_tiles);
     return q6k_check_launch("tile_list");
 }
 
@@ -163,7 +165,7 @@ Q6K_API int q6k_gemm_simt(const void* A, int lda, const int* a_rows, const void*
     Q6K_REQUIRE(ytiles <= 65535, "gemm: %d row tiles exceed the grid limit", ytiles);
     dim3 grid((N + BN - 1) / BN, ytiles);
 #define LAUNCH(EPI)                                                                                                     \
-    gemm_simt_kernel<T, EPI><<<grid, 256, 0, st>>>((const T*)A, lda, a_rows, (const T*)W, (const T*)W2,                 \
+    q6k_launch(gemm_simt_kernel<T, EPI>, grid, 256, 0, st, (const T*)A, lda, a_rows, (const T*)W, (const T*)W2,                 \
                                                    (size_t)w_group_stride, out, ldo, M, N, K, tile_group, tile_row0, \
                                                    group_offsets, num_tiles)
     Q6K_DISPATCH(dtype, {

@@ -137,6 +137,7 @@ __device__ __forceinline__ bool decode_tile(const Params& p, int t, int n_x, int
 template <int BT, bool DUAL>
 __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_w2,
                                                        const __grid_constant__ CUtensorMap tm_a, const Params p) {
+    pdl_enter();
     const int n_x = (p.N + WM - 1) / WM;
     const int n_y = p.pair_div > 0 ? p.n_y : (p.tile_group ? *p.num_tiles : p.n_y);
     const int total = n_x * n_y * p.n_z;
@@ -303,6 +304,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
 
 // out[r, n] (=|+=) sum_s partial[s, r, n], s ascending.
 __global__ void splitk_reduce_kernel(const float* partial, int splits, size_t count, float* out, int N, int ldo, int add) {
+    pdl_enter();
     const size_t i = blockIdx.x * (size_t)blockDim.x + threadIdx.x;
     if (i >= count) return;
     float acc = 0.0f;
@@ -364,7 +366,7 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tw2, const CUtensorMap& ta,
     const long long total = (long long)((p.N + WM - 1) / WM) * n_y * n_z;
     const int slots = sm_count() * per_sm;
     const int grid = (int)(total < slots ? total : slots);
-    gemm_tc_kernel<BT, DUAL><<<grid, 192, smem, st>>>(tw, tw2, ta, p);
+    q6k_launch(gemm_tc_kernel<BT, DUAL>, grid, 192, smem, st, tw, tw2, ta, p);
     return q6k_check_launch("gemm_tc");
 }
 
@@ -481,7 +483,7 @@ Q6K_API int q6k_gemm_tc(const void* A, long long lda, int rows_total, const void
     if (rc) return rc;
     if (splits > 1 && !keep_partials) {
         const size_t count = (size_t)rows_total * N;
-        splitk_reduce_kernel<<<(unsigned)((count + 255) / 256), 256, 0, st>>>(workspace, splits, count, (float*)out, N, ldo,
+        q6k_launch(splitk_reduce_kernel, (unsigned)((count + 255) / 256), 256, 0, st, workspace, splits, count, (float*)out, N, ldo,
                                                                              epilogue == EPI_ADD);
         return q6k_check_launch("gemm_tc split-K reduce");
     }

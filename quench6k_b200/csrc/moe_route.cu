@@ -14,6 +14,7 @@
 namespace {
 
 __global__ void route_kernel(const float* logits, int T_, int E, int k, int sigmoid, int renorm, int* sel_e, float* sel_w) {
+    pdl_enter();
     extern __shared__ float sc[];             // [warps][E]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = blockIdx.x * (blockDim.x >> 5) + warp;
@@ -107,6 +108,7 @@ constexpr int SMALL_T = 16;
 __global__ void __launch_bounds__(512) router_small_kernel(const __nv_bfloat16* xn, const __nv_bfloat16* w, int T_, int E, int D, int k,
                                                            int sigmoid, int renorm, float* logits, int* sel_e, float* sel_w,
                                                            int* order, unsigned* ticket) {
+    pdl_enter();
     extern __shared__ float sc[];             // the last block: [16 warps][E] scores
     __shared__ float red[16][SMALL_T];
     __shared__ int is_last;
@@ -205,6 +207,7 @@ constexpr int PERM_CHUNK = 1024;           // pairs per chunk of the permutation
 
 // One warp per (expert, chunk of pairs): how many pairs of the chunk chose the expert.
 __global__ void count_kernel(const int* sel_e, int pairs, int E, int* counts) {
+    pdl_enter();
     const int lane = threadIdx.x & 31;
     const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), c = blockIdx.y;
     if (e >= E) return;
@@ -220,6 +223,7 @@ __global__ void count_kernel(const int* sel_e, int pairs, int E, int* counts) {
 // counts[c, e] -> the chunk's first row within its expert (in place), and offsets = exclusive
 // scan over the experts of their totals (E + 1 entries).  One block.
 __global__ void offsets_kernel(int* counts, int chunks, int E, int* offsets) {
+    pdl_enter();
     __shared__ int part[1024];
     const int tid = threadIdx.x, n = blockDim.x;
     const int per = (E + n - 1) / n;
@@ -262,6 +266,7 @@ __global__ void offsets_kernel(int* counts, int chunks, int E, int* offsets) {
 // number of earlier pairs of the same expert; row_token[row] = pair / k.
 __global__ void rank_kernel(const int* sel_e, const int* chunk_base, const int* offsets, int pairs, int k, int E, int* pair_row,
                             int* row_token) {
+    pdl_enter();
     const int lane = threadIdx.x & 31;
     const int e = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), c = blockIdx.y;
     if (e >= E) return;
@@ -289,7 +294,7 @@ Q6K_API int q6k_route(const float* logits, int T_, int E, int k, int sigmoid, in
     Q6K_REQUIRE(E <= 8192, "route: %d experts exceed the supported 8192", E);
     const int warps = E <= 2048 ? 4 : 1;
     const size_t smem = (size_t)warps * E * sizeof(float);
-    route_kernel<<<(T_ + warps - 1) / warps, warps * 32, smem, st>>>(logits, T_, E, k, sigmoid, renorm, sel_e, sel_w);
+    q6k_launch(route_kernel, (T_ + warps - 1) / warps, warps * 32, smem, st, logits, T_, E, k, sigmoid, renorm, sel_e, sel_w);
     return q6k_check_launch("route");
 }
 
@@ -302,7 +307,7 @@ Q6K_API int q6k_router_small(const void* xn, const void* w, int T_, int E, int D
     Q6K_REQUIRE(T_ > 0 && T_ <= SMALL_T, "router_small: %d tokens exceed %d", T_, SMALL_T);
     Q6K_REQUIRE(E > 0 && k > 0 && k <= E && E <= 704, "router_small: bad sizes E=%d k=%d (at most 704 experts)", E, k);
     Q6K_REQUIRE(D > 0 && D % 8 == 0 && ((uintptr_t)xn & 15) == 0 && ((uintptr_t)w & 15) == 0, "router_small: D=%d must be a multiple of 8 and the operands 16-byte aligned", D);
-    router_small_kernel<<<E, 512, 16 * E * sizeof(float), st>>>((const __nv_bfloat16*)xn, (const __nv_bfloat16*)w, T_, E, D, k,
+    q6k_launch(router_small_kernel, E, 512, 16 * E * sizeof(float), st, (const __nv_bfloat16*)xn, (const __nv_bfloat16*)w, T_, E, D, k,
                                                                        sigmoid, renorm, logits, sel_e, sel_w, order, ticket);
     return q6k_check_launch("router_small");
 }
@@ -317,8 +322,8 @@ Q6K_API int q6k_moe_permute(const int* sel_e, int pairs, int k, int E, int* scra
     const int chunks = (pairs + PERM_CHUNK - 1) / PERM_CHUNK;
     Q6K_REQUIRE(chunks <= 65535, "moe_permute: %d pairs exceed the grid limit", pairs);
     const dim3 grid((E + 7) / 8, chunks);
-    count_kernel<<<grid, 256, 0, st>>>(sel_e, pairs, E, scratch);
-    offsets_kernel<<<1, 256, 0, st>>>(scratch, chunks, E, offsets);
-    rank_kernel<<<grid, 256, 0, st>>>(sel_e, scratch, offsets, pairs, k, E, pair_row, row_token);
+    q6k_launch(count_kernel, grid, 256, 0, st, sel_e, pairs, E, scratch);
+    q6k_launch(offsets_kernel, 1, 256, 0, st, scratch, chunks, E, offsets);
+    q6k_launch(rank_kernel, grid, 256, 0, st, sel_e, scratch, offsets, pairs, k, E, pair_row, row_token);
     return q6k_check_launch("moe_permute");
 }

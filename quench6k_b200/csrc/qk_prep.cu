@@ -15,6 +15,7 @@ template <typename T>
 __global__ void qk_prep_kernel(const float* qkv, int ld, int splits, size_t split_stride, int Hq, int Hkv, int hd, const float* q_norm, const float* k_norm,
                                float eps, int rope, float log2_theta, const int* positions, const int* req_of_token,
                                const int* block_table, int max_blocks, int page_size, int num_pages, T* q_out, T* k_pages, T* v_pages) {
+    pdl_enter();
     extern __shared__ float xs[];            // hd floats
     __shared__ float red[32];
     const int t = blockIdx.x, h = blockIdx.y, d = threadIdx.x;
@@ -66,6 +67,7 @@ __global__ void __launch_bounds__(256) qk_prep_warp_kernel(const float* qkv, int
                                                            const int* positions, const int* req_of_token, const int* block_table,
                                                            int max_blocks, int page_size, int num_pages, T* q_out, T* k_pages,
                                                            T* v_pages, int heads) {
+    pdl_enter();
     constexpr int hd = EPL * 32, half = hd / 2;
     const int t = blockIdx.x, h = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (h >= heads) return;
@@ -139,7 +141,7 @@ Q6K_API int q6k_qk_prep(const float* qkv, int ld, int splits, long long split_st
         dim3 wgrid(T_, (heads + 7) / 8);
         Q6K_REQUIRE(wgrid.y <= 65535, "qk_prep: %d heads exceed the grid limit", heads);
 #define WARP_LAUNCH(EPL)                                                                                                    \
-    qk_prep_warp_kernel<T, EPL><<<wgrid, 256, 0, st>>>(qkv, ld, splits, (size_t)split_stride, Hq, Hkv, q_norm, k_norm, eps, rope, l2t, positions, req_of_token, \
+    q6k_launch(qk_prep_warp_kernel<T, EPL>, wgrid, 256, 0, st, qkv, ld, splits, (size_t)split_stride, Hq, Hkv, q_norm, k_norm, eps, rope, l2t, positions, req_of_token, \
                                                        block_table, max_blocks, page_size, num_pages, (T*)q_out, (T*)k_pages, (T*)v_pages, heads)
         Q6K_DISPATCH(dtype, {
             if (hd == 64) WARP_LAUNCH(2);
@@ -151,7 +153,7 @@ Q6K_API int q6k_qk_prep(const float* qkv, int ld, int splits, long long split_st
     }
     const int threads = (hd + 31) / 32 * 32;
     dim3 grid(T_, heads);
-    Q6K_DISPATCH(dtype, qk_prep_kernel<T><<<grid, threads, hd * sizeof(float), st>>>(
+    Q6K_DISPATCH(dtype, q6k_launch(qk_prep_kernel<T>, grid, threads, hd * sizeof(float), st, 
                             qkv, ld, splits, (size_t)split_stride, Hq, Hkv, hd, q_norm, k_norm, eps, rope, l2t, positions, req_of_token, block_table,
                             max_blocks, page_size, num_pages, (T*)q_out, (T*)k_pages, (T*)v_pages););
     return q6k_check_launch("qk_prep");

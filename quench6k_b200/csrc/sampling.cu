@@ -46,6 +46,7 @@ constexpr int ARGMAX_SLICE = 8192;
 
 // Stage 1: block (slice, row) finds the best of its slice of the row.
 __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* logits, int V, int slices, unsigned* pk, int* pi) {
+    pdl_enter();
     __shared__ unsigned bk[32];
     __shared__ int bi[32];
     const float* row = logits + (size_t)blockIdx.y * V;
@@ -75,6 +76,7 @@ __global__ void __launch_bounds__(256) argmax_partial_kernel(const float* logits
 
 // Stage 2: one warp per row picks among the slices' winners.
 __global__ void argmax_final_kernel(const unsigned* pk, const int* pi, int slices, int* out) {
+    pdl_enter();
     unsigned best = 0u;
     int best_i = 0x7fffffff;
     for (int s = threadIdx.x; s < slices; s += 32) {
@@ -97,6 +99,7 @@ constexpr int POOL_MAX = 256;
 // everything above it is taken, ties at it are taken in ascending id order, and the K candidates
 // are sorted by (key descending, id ascending) with a bitonic network.
 __global__ void __launch_bounds__(1024) topk_pool_kernel(const float* logits, int V, int K, int* out_ids, float* out_vals) {
+    pdl_enter();
     __shared__ int hist[256];
     __shared__ unsigned s_prefix;
     __shared__ int s_need, s_count;
@@ -201,8 +204,8 @@ Q6K_API int q6k_argmax(const float* logits, int rows, int V, int* out, void* scr
     const int slices = (V + ARGMAX_SLICE - 1) / ARGMAX_SLICE;
     unsigned* pk = (unsigned*)scratch;
     int* pi = (int*)scratch + (size_t)rows * slices;
-    argmax_partial_kernel<<<dim3(slices, rows), 256, 0, st>>>(logits, V, slices, pk, pi);
-    argmax_final_kernel<<<rows, 32, 0, st>>>(pk, pi, slices, out);
+    q6k_launch(argmax_partial_kernel, dim3(slices, rows), 256, 0, st, logits, V, slices, pk, pi);
+    q6k_launch(argmax_final_kernel, rows, 32, 0, st, pk, pi, slices, out);
     return q6k_check_launch("argmax");
 }
 
@@ -211,7 +214,7 @@ Q6K_API int q6k_topk_pool(const float* logits, int rows, int V, int K, int* ids,
     if (rows == 0) return 0;
     Q6K_REQUIRE(rows > 0 && V > 0, "topk_pool: bad sizes rows=%d V=%d", rows, V);
     Q6K_REQUIRE(K >= 1 && K <= POOL_MAX && K <= V, "topk_pool: K=%d outside 1..min(%d, V=%d)", K, POOL_MAX, V);
-    topk_pool_kernel<<<rows, 1024, 0, st>>>(logits, V, K, ids, vals);
+    q6k_launch(topk_pool_kernel, rows, 1024, 0, st, logits, V, K, ids, vals);
     return q6k_check_launch("topk_pool");
 }
 
@@ -248,7 +251,7 @@ Q6K_API int q6k_argmax_noalloc(const float* logits, int rows, int vocab, int* ou
     const int slices = (vocab + ARGMAX_SLICE - 1) / ARGMAX_SLICE;
     unsigned* pk = (unsigned*)g_noalloc_ptr[dev];
     int* pi = (int*)g_noalloc_ptr[dev] + (size_t)rows * slices;
-    argmax_partial_kernel<<<dim3(slices, rows), 256, 0, st>>>(logits, vocab, slices, pk, pi);
-    argmax_final_kernel<<<rows, 32, 0, st>>>(pk, pi, slices, out);
+    q6k_launch(argmax_partial_kernel, dim3(slices, rows), 256, 0, st, logits, vocab, slices, pk, pi);
+    q6k_launch(argmax_final_kernel, rows, 32, 0, st, pk, pi, slices, out);
     return q6k_check_launch("argmax_noalloc");
 }

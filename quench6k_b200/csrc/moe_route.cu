@@ -13,6 +13,38 @@
 
 namespace {
 
+// Top-k of one token's scores held in shared memory v[0..E) by one warp: ties to the lower index.
+// Writes the chosen experts and weights (renormalised if asked).  `total` divides softmax scores.
+__device__ __forceinline__ void warp_topk(float* v, int E, int k, int sigmoid, int renorm, float total, int* sel_e, float* sel_w) {
+    const int lane = threadIdx.x & 31;
+    float chosen_sum = 0.0f, mine = 0.0f;
+    for (int r = 0; r < k; ++r) {
+        float best = -1.0f;
+        int best_i = 0x7fffffff;
+        for (int e = lane; e < E; e += 32)
+            if (v[e] > best) best = v[e], best_i = e;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+            if (ob > best || (ob == best && oi < best_i)) best = ob, best_i = oi;
+        }
+        const float score = sigmoid ? best : best / total;
+        chosen_sum += score;
+        if (lane == 0) {
+            sel_e[r] = best_i;
+            v[best_i] = -2.0f;
+        }
+        if (lane == r) mine = score;                 // lane r keeps the r-th score (r < 32; later ones: below)
+        if (r >= 32 && lane == 0) sel_w[r] = score;
+        __syncwarp();
+    }
+    const float den = !renorm ? 1.0f : (sigmoid ? chosen_sum + 1e-20f : chosen_sum);
+    if (lane < k && lane < 32) sel_w[lane] = mine / den;
+    if (k > 32 && renorm && lane == 0)
+        for (int r = 32; r < k; ++r) sel_w[r] /= den;
+}
+
 __global__ void route_kernel(const float* logits, int T_, int E, int k, int sigmoid, int renorm, int* sel_e, float* sel_w) {
     pdl_enter();
     extern __shared__ float sc[];             // [warps][E]
@@ -41,63 +73,7 @@ __global__ void route_kernel(const float* logits, int T_, int E, int k, int sigm
         total = warp_sum(sum);
     }
     __syncwarp();
-    float chosen_sum = 0.0f;
-    for (int r = 0; r < k; ++r) {
-        float best = -1.0f;
-        int best_i = 0x7fffffff;
-        for (int e = lane; e < E; e += 32)
-            if (v[e] > best) best = v[e], best_i = e;       // ascending e: the lowest index of a tie wins
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-            if (ob > best || (ob == best && oi < best_i)) best = ob, best_i = oi;
-        }
-        const float score = sigmoid ? best : best / total;
-        chosen_sum += score;
-        if (lane == 0) {
-            sel_e[(size_t)t * k + r] = best_i;
-            sel_w[(size_t)t * k + r] = score;
-            v[best_i] = -2.0f;
-        }
-        __syncwarp();
-    }
-    if (renorm && lane == 0) {
-        const float den = sigmoid ? chosen_sum + 1e-20f : chosen_sum;
-        for (int r = 0; r < k; ++r) sel_w[(size_t)t * k + r] /= den;
-    }
-}
-
-// Top-k of one token's scores held in shared memory v[0..E) by one warp: ties to the lower index.
-// Writes the chosen experts and weights (renormalised if asked).  `total` divides softmax scores.
-__device__ __forceinline__ void warp_topk(float* v, int E, int k, int sigmoid, int renorm, float total, int* sel_e, float* sel_w) {
-    const int lane = threadIdx.x & 31;
-    float chosen_sum = 0.0f, mine = 0.0f;
-    for (int r = 0; r < k; ++r) {
-        float best = -1.0f;
-        int best_i = 0x7fffffff;
-        for (int e = lane; e < E; e += 32)
-            if (v[e] > best) best = v[e], best_i = e;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-            if (ob > best || (ob == best && oi < best_i)) best = ob, best_i = oi;
-        }
-        const float score = sigmoid ? best : best / total;
-        chosen_sum += score;
-        if (lane == 0) {
-            sel_e[r] = best_i;
-            v[best_i] = -2.0f;
-        }
-        if (lane == (r & 31)) mine = score;          // lane r keeps the r-th score (k <= 32 here; larger k: below)
-        if (r >= 32 && lane == 0) sel_w[r] = score;
-        __syncwarp();
-    }
-    const float den = !renorm ? 1.0f : (sigmoid ? chosen_sum + 1e-20f : chosen_sum);
-    if (lane < k && lane < 32) sel_w[lane] = mine / den;
-    if (k > 32 && renorm && lane == 0)
-        for (int r = 32; r < k; ++r) sel_w[r] /= den;
+    warp_topk(v, E, k, sigmoid, renorm, total, sel_e + (size_t)t * k, sel_w + (size_t)t * k);
 }
 
 // Router of a decode step in one launch (reference: router_kernel, crates/cuda/kernels/flint.cu:1002-1055,

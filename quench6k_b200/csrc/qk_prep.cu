@@ -69,10 +69,19 @@ __global__ void __launch_bounds__(256) qk_prep_warp_kernel(const float* qkv, int
                                                            T* v_pages, int heads) {
     pdl_enter();
     constexpr int hd = EPL * 32, half = hd / 2;
+    __shared__ float rot_cos[half], rot_sin[half];
     const int t = blockIdx.x, h = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    const int pos = positions[t];
+    if (rope) {
+        // the angles depend on the position and the dimension only: once per block, not once per head
+        for (int d = threadIdx.x; d < half; d += blockDim.x) {
+            const float inv = exp2f(-(float)(2 * d) / (float)hd * log2_theta);
+            sincosf((float)pos * inv, &rot_sin[d], &rot_cos[d]);
+        }
+        __syncthreads();
+    }
     if (h >= heads) return;
     const bool is_q = h < Hq;
-    const int pos = positions[t];
     const float* src = qkv + (size_t)t * ld + (size_t)h * hd;           // q heads then k heads are contiguous in a row
     float x[EPL], ss = 0.0f;
 #pragma unroll
@@ -91,9 +100,7 @@ __global__ void __launch_bounds__(256) qk_prep_warp_kernel(const float* qkv, int
 #pragma unroll
         for (int i = 0; i < EPL / 2; ++i) {
             const int d = lane + 32 * i;                                 // d < half; partner d + half is element i + EPL/2
-            const float inv = exp2f(-(float)(2 * d) / (float)hd * log2_theta);
-            float sn, cs;
-            sincosf((float)pos * inv, &sn, &cs);
+            const float sn = rot_sin[d], cs = rot_cos[d];
             const float lo = x[i], hi = x[i + EPL / 2];
             x[i] = lo * cs - hi * sn;
             x[i + EPL / 2] = hi * cs + lo * sn;

@@ -256,6 +256,61 @@ class CacheManager:
         reused by its next step or returned by remove)."""
         self.requests[rid].reserved = 0
 
+    # ------------------------------------------------------------------ the step's description
+    def pack_step(self, rids: Sequence[Hashable], tokens: Sequence[Sequence[int]], want: Sequence[Sequence[int]],
+                  widths: Sequence[int], vocab_size: int, out: np.ndarray) -> Tuple[int, int, int, int, int]:
+        """Write the step's int32 block into `out`:
+        [tokens T | positions T | request of token T | q_start R+1 | pos_start R | slot R | logit rows |
+        one R x widths[g] block table per group].  Returns (ints written, T, wanted rows, longest
+        context, longest entry)."""
+        R = len(rids)
+        q_lens = [len(t) for t in tokens]
+        T, W = sum(q_lens), sum(len(w) for w in want)
+        total = 3 * T + (R + 1) + 2 * R + W + sum(R * w for w in widths)
+        if total > out.size:
+            raise ValueError(f"the step needs {total} ints, the block holds {out.size}")
+        o = 0
+
+        def take(n):
+            nonlocal o
+            v = out[o:o + n]
+            o += n
+            return v
+
+        tok, pos, rot = take(T), take(T), take(T)
+        qs, psv, sl, lr = take(R + 1), take(R), take(R), take(W)
+        t = w = 0
+        qs[0] = 0
+        max_ctx = max_q = 0
+        for r, rid in enumerate(rids):
+            req = self.requests[rid]
+            n = q_lens[r]
+            arr = np.asarray(tokens[r], dtype=np.int64)
+            if n and (arr.min() < 0 or arr.max() >= vocab_size):
+                raise ValueError(f"request {rid!r}: token id outside 0..{vocab_size - 1}")
+            tok[t:t + n] = arr
+            pos[t:t + n] = np.arange(req.length, req.length + n)
+            rot[t:t + n] = r
+            for i in want[r]:
+                if not 0 <= i < n:
+                    raise ValueError(f"request {rid!r}: wanted place {i} outside its {n} tokens")
+                lr[w] = t + i
+                w += 1
+            t += n
+            qs[r + 1] = t
+            psv[r] = req.length
+            sl[r] = req.slot
+            max_ctx, max_q = max(max_ctx, req.length + n), max(max_q, n)
+        for g, wd in enumerate(widths):
+            tb = take(R * wd).reshape(R, wd)
+            tb[:] = -1
+            for r, rid in enumerate(rids):
+                row = self.requests[rid].tables[g].array()
+                if len(row) > wd:
+                    raise ValueError(f"request {rid!r} holds {len(row)} blocks in group {g}, the table is {wd} wide")
+                tb[r, :len(row)] = row
+        return total, T, W, max_ctx, max_q
+
     # ------------------------------------------------------------------ invariants (tests)
     def check(self) -> None:
         for g, pool in enumerate(self.pools):

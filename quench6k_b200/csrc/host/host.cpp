@@ -1,0 +1,627 @@
+// The host side of the engine in C++: the paged cache manager, the continuous-batching scheduler
+// and the packing of a step's description, behind a C interface that Python calls through ctypes.
+//
+// The reference's host is Rust (crates/engine/src/flint.rs: contiguous per-sequence caches, one
+// request at a time; crates/engine/src/session.rs and crates/cli/src/serve.rs: admission by memory
+// plan, finish reasons Stop / Length / Cancelled).  The rules implemented here are this engine's own
+// and are stated at each class; quench6k_b200/cache/manager.py and engine/scheduler.py hold a Python
+// twin with the same rules, and the tests run both.
+//
+// Every exported function returns 0 or an error kind after storing a message:
+//   1 runtime error, 2 out of pages, 3 out of slots, 4 unknown or duplicate request, 5 bad value.
+#include <algorithm>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <cstring>
+#include <deque>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#define API extern "C" __attribute__((visibility("default")))
+
+namespace {
+
+enum { OK = 0, E_RUNTIME = 1, E_PAGES = 2, E_SLOTS = 3, E_KEY = 4, E_VALUE = 5 };
+
+thread_local char g_msg[512] = "";
+
+int fail(int kind, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_msg, sizeof g_msg, fmt, ap);
+    va_end(ap);
+    return kind;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Pages of one cache group: ids 0..n-1, a LIFO free list (a page that was just given back is the
+// next one handed out; a request that takes several pages at once gets ascending numbers whenever
+// they were returned in descending order), every page free or owned by exactly one request.
+struct PagePool {
+    int n = 0;
+    std::vector<int> free_;
+    std::vector<int64_t> owner;          // -1: free
+    explicit PagePool(int count) : n(count), owner(count, -1) {
+        free_.reserve(count);
+        for (int p = count - 1; p >= 0; --p) free_.push_back(p);
+    }
+    int num_free() const { return (int)free_.size(); }
+    int take(int64_t who) {
+        const int page = free_.back();
+        free_.pop_back();
+        owner[page] = who;
+        return page;
+    }
+    int give_back(int page, int64_t who) {
+        if (page < 0 || page >= n) return fail(E_VALUE, "page %d outside the pool", page);
+        if (owner[page] < 0) return fail(E_RUNTIME, "page %d freed twice", page);
+        if (owner[page] != who) return fail(E_RUNTIME, "page %d belongs to request %lld, not %lld", page, (long long)owner[page], (long long)who);
+        owner[page] = -1;
+        free_.push_back(page);
+        return OK;
+    }
+};
+
+struct BlockTable {
+    std::vector<int32_t> pages;          // by logical block; -1 where the page was given back
+    int first_held = 0;                  // blocks [0, first_held) were given back
+};
+
+struct CacheRequest {
+    int slot = -1;
+    int64_t length = 0;                  // tokens whose keys are in the cache
+    int reserved = 0;                    // tokens of the step in flight
+    std::vector<BlockTable> tables;      // per group
+};
+
+struct Group {
+    int sliding = 0;                     // 0: a request holds pages for every position; 1: only for the last `window`
+    int window = 0;
+};
+
+// Keys and values in pages with a block table per request and group; a sliding group gives pages
+// back as soon as no later query can see them; one state slot per request.
+struct CacheManager {
+    int page_size;
+    std::vector<Group> groups;
+    std::vector<PagePool> pools;
+    int num_slots;
+    std::vector<int> free_slots;
+    std::unordered_map<int64_t, CacheRequest> requests;
+
+    CacheRequest* find(int64_t id) {
+        auto it = requests.find(id);
+        return it == requests.end() ? nullptr : &it->second;
+    }
+    int first_needed_block(int g, int64_t start) const {
+        if (!groups[g].sliding) return 0;
+        const int64_t lo = start - groups[g].window + 1;
+        return (int)((lo < 0 ? 0 : lo) / page_size);
+    }
+    int add(int64_t id, int* slot) {
+        if (requests.count(id)) return fail(E_KEY, "request %lld is already live", (long long)id);
+        if (free_slots.empty()) return fail(E_SLOTS, "all %d request slots are in use", num_slots);
+        CacheRequest r;
+        r.slot = free_slots.back();
+        free_slots.pop_back();
+        r.tables.resize(groups.size());
+        *slot = r.slot;
+        requests.emplace(id, std::move(r));
+        return OK;
+    }
+    int remove(int64_t id) {
+        CacheRequest* r = find(id);
+        if (!r) return fail(E_KEY, "request %lld is not live", (long long)id);
+        for (size_t g = 0; g < groups.size(); ++g) {
+            BlockTable& t = r->tables[g];
+            for (int b = (int)t.pages.size() - 1; b >= t.first_held; --b)
+                if (int rc = pools[g].give_back(t.pages[b], id)) return rc;
+        }
+        free_slots.push_back(r->slot);
+        requests.erase(id);
+        return OK;
+    }
+    // Pages each pool must supply so that the request can run n_new more tokens: a table holds a
+    // page for every block from the first one the next step reads up to its end, so the need is the
+    // blocks past the table's end.
+    int pages_needed(int64_t id, int n_new, int* out) {
+        CacheRequest* r = find(id);
+        if (!r) return fail(E_KEY, "request %lld is not live", (long long)id);
+        const int64_t end = r->length + n_new;
+        const int last = end > 0 ? (int)((end - 1) / page_size) : -1;
+        for (size_t g = 0; g < groups.size(); ++g) {
+            if (first_needed_block((int)g, r->length) < r->tables[g].first_held)
+                return fail(E_RUNTIME, "a block the next step of request %lld reads was given back", (long long)id);
+            const int have = (int)r->tables[g].pages.size();
+            out[g] = last + 1 > have ? last + 1 - have : 0;
+        }
+        return OK;
+    }
+    int can_reserve(const int64_t* ids, const int* ns, int m, int* yes) {
+        std::vector<int> total(groups.size(), 0), need(groups.size());
+        for (int i = 0; i < m; ++i) {
+            if (int rc = pages_needed(ids[i], ns[i], need.data())) return rc;
+            for (size_t g = 0; g < groups.size(); ++g) total[g] += need[g];
+        }
+        *yes = 1;
+        for (size_t g = 0; g < groups.size(); ++g)
+            if (total[g] > pools[g].num_free()) *yes = 0;
+        return OK;
+    }
+    // All groups or none: on failure nothing has changed.
+    int reserve(int64_t id, int n_new) {
+        CacheRequest* r = find(id);
+        if (!r) return fail(E_KEY, "request %lld is not live", (long long)id);
+        if (r->reserved) return fail(E_RUNTIME, "request %lld already has a step in flight", (long long)id);
+        std::vector<int> need(groups.size());
+        if (int rc = pages_needed(id, n_new, need.data())) return rc;
+        for (size_t g = 0; g < groups.size(); ++g)
+            if (need[g] > pools[g].num_free())
+                return fail(E_PAGES, "group %d (%s) needs %d pages for request %lld, %d are free", (int)g,
+                            groups[g].sliding ? "sliding" : "full", need[g], (long long)id, pools[g].num_free());
+        for (size_t g = 0; g < groups.size(); ++g)
+            for (int i = 0; i < need[g]; ++i) r->tables[g].pages.push_back(pools[g].take(id));
+        r->reserved = n_new;
+        return OK;
+    }
+    int commit(int64_t id) {
+        CacheRequest* r = find(id);
+        if (!r) return fail(E_KEY, "request %lld is not live", (long long)id);
+        r->length += r->reserved;
+        r->reserved = 0;
+        for (size_t g = 0; g < groups.size(); ++g) {
+            if (!groups[g].sliding) continue;
+            // the next query sits at position `length` and sees keys > length - window
+            const int64_t lo = r->length - groups[g].window + 1;
+            BlockTable& t = r->tables[g];
+            int dead = (int)((lo < 0 ? 0 : lo) / page_size);
+            if (dead > (int)t.pages.size()) dead = (int)t.pages.size();
+            for (int b = t.first_held; b < dead; ++b) {
+                if (int rc = pools[g].give_back(t.pages[b], id)) return rc;
+                t.pages[b] = -1;
+            }
+            if (dead > t.first_held) t.first_held = dead;
+        }
+        return OK;
+    }
+    int cancel(int64_t id) {
+        CacheRequest* r = find(id);
+        if (!r) return fail(E_KEY, "request %lld is not live", (long long)id);
+        r->reserved = 0;
+        return OK;
+    }
+    // No page lost, held twice, or both free and held; no slot lost or held twice.
+    int check() {
+        for (size_t g = 0; g < groups.size(); ++g) {
+            PagePool& pool = pools[g];
+            std::vector<int> seen(pool.n, 0);
+            int held = 0;
+            for (auto& kv : requests) {
+                const BlockTable& t = kv.second.tables[g];
+                for (int b = 0; b < (int)t.pages.size(); ++b) {
+                    const int page = t.pages[b];
+                    if ((page < 0) != (b < t.first_held))
+                        return fail(E_RUNTIME, "group %d: request %lld block %d page %d first_held %d", (int)g, (long long)kv.first, b, page, t.first_held);
+                    if (page < 0) continue;
+                    if (page >= pool.n || seen[page]++) return fail(E_RUNTIME, "group %d: page %d held twice", (int)g, page);
+                    if (pool.owner[page] != kv.first) return fail(E_RUNTIME, "group %d: page %d owner %lld != %lld", (int)g, page, (long long)pool.owner[page], (long long)kv.first);
+                    ++held;
+                }
+            }
+            for (int page : pool.free_) {
+                if (seen[page] == 1) return fail(E_RUNTIME, "group %d: page %d is both free and held", (int)g, page);
+                if (seen[page] == 2) return fail(E_RUNTIME, "group %d: page %d is twice in the free list", (int)g, page);
+                seen[page] = 2;
+            }
+            if ((int)pool.free_.size() + held != pool.n) return fail(E_RUNTIME, "group %d: %d pages lost", (int)g, pool.n - (int)pool.free_.size() - held);
+        }
+        std::vector<int> slot_seen(num_slots, 0);
+        for (auto& kv : requests)
+            if (slot_seen[kv.second.slot]++) return fail(E_RUNTIME, "state slot %d is held twice", kv.second.slot);
+        if ((int)requests.size() + (int)free_slots.size() != num_slots) return fail(E_RUNTIME, "a state slot is lost");
+        return OK;
+    }
+};
+
+// ---------------------------------------------------------------------------------------------
+enum { FINISH_NONE = 0, FINISH_STOP = 1, FINISH_LENGTH = 2, FINISH_CANCELLED = 3 };
+
+struct SchedRequest {
+    int64_t id = 0;
+    std::vector<int32_t> prompt, output, stops;
+    int max_tokens = 0;
+    int64_t num_computed = 0;
+    int preemptions = 0;
+    int finish = FINISH_NONE;
+    int64_t num_tokens() const { return (int64_t)prompt.size() + (int64_t)output.size(); }
+    int32_t token(int64_t i) const { return i < (int64_t)prompt.size() ? prompt[i] : output[i - prompt.size()]; }
+};
+
+struct Entry {
+    int64_t id;
+    int64_t start;
+    int count;
+    int samples;
+};
+
+// Continuous batching under a token budget: every running request whose prompt is in the cache
+// decodes one token; what is left goes to prompt portions, first of running requests that are
+// still prefilling (admission order), then of waiting requests, admitted first come first served
+// while a slot, budget and pages for the portion are there (a portion shrinks to what the pools
+// hold).  When pages run out for the decode tokens the most recently admitted running request is
+// preempted (pages and slot back, to the front of the queue, recomputed from its tokens); a
+// request running alone that cannot get a page ends with reason "length".
+struct Scheduler {
+    CacheManager* cm;
+    int max_batch_tokens, max_running;
+    std::deque<int64_t> waiting;
+    std::vector<int64_t> running;                 // admission order
+    std::unordered_map<int64_t, SchedRequest> by_id;
+    std::vector<Entry> last;                      // the entries of the step in flight
+
+    int64_t capacity_tokens() const {
+        int64_t least = INT64_MAX;
+        for (auto& p : cm->pools) least = std::min<int64_t>(least, p.n);
+        return cm->pools.empty() ? (int64_t)1 << 60 : least * cm->page_size;
+    }
+    int release(int64_t id) { return cm->remove(id); }
+    int finish(SchedRequest& r, int reason) {
+        r.finish = reason;
+        auto it = std::find(running.begin(), running.end(), r.id);
+        if (it != running.end()) {
+            running.erase(it);
+            if (int rc = release(r.id)) return rc;
+        } else {
+            auto w = std::find(waiting.begin(), waiting.end(), r.id);
+            if (w != waiting.end()) waiting.erase(w);
+        }
+        return OK;
+    }
+    int preempt(SchedRequest& r) {
+        running.erase(std::find(running.begin(), running.end(), r.id));
+        if (int rc = release(r.id)) return rc;
+        r.num_computed = 0;
+        r.preemptions += 1;
+        waiting.push_front(r.id);
+        return OK;
+    }
+    bool fits(std::vector<int64_t>& ids, std::vector<int>& ns, int64_t id, int n) {
+        ids.push_back(id), ns.push_back(n);
+        int yes = 0;
+        cm->can_reserve(ids.data(), ns.data(), (int)ids.size(), &yes);
+        ids.pop_back(), ns.pop_back();
+        return yes != 0;
+    }
+    // Largest n <= want such that the pools hold the chosen entries plus n tokens of id.
+    int fit(std::vector<int64_t>& ids, std::vector<int>& ns, int64_t id, int want) {
+        if (want <= 0) return 0;
+        if (fits(ids, ns, id, want)) return want;
+        int lo = 0, hi = want;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) / 2;
+            if (fits(ids, ns, id, mid)) lo = mid;
+            else hi = mid - 1;
+        }
+        return lo;
+    }
+    int schedule(std::vector<Entry>& entries, std::vector<int64_t>& preempted, std::vector<int64_t>& finished,
+                 std::vector<int64_t>& admitted, std::vector<int>& admitted_slots) {
+        int budget = max_batch_tokens;
+        std::vector<int64_t> ids;
+        std::vector<int> ns;
+        std::vector<SchedRequest*> decoding;
+        while (true) {
+            decoding.clear(), ids.clear(), ns.clear();
+            for (int64_t id : running) {
+                SchedRequest& r = by_id[id];
+                if (r.num_computed == r.num_tokens() - 1 && !r.output.empty() && (int)decoding.size() < budget) decoding.push_back(&r);
+            }
+            for (auto* r : decoding) ids.push_back(r->id), ns.push_back(1);
+            int yes = 0;
+            if (int rc = cm->can_reserve(ids.data(), ns.data(), (int)ids.size(), &yes)) return rc;
+            if (yes) break;
+            if (running.size() == 1) {
+                SchedRequest& lone = by_id[running[0]];
+                if (int rc = finish(lone, FINISH_LENGTH)) return rc;
+                finished.push_back(lone.id);
+                continue;
+            }
+            SchedRequest& victim = by_id[running.back()];
+            if (int rc = preempt(victim)) return rc;
+            preempted.push_back(victim.id);
+        }
+        for (auto* r : decoding) entries.push_back({r->id, r->num_computed, 1, 1});
+        budget -= (int)decoding.size();
+        std::vector<int64_t> in_step(ids);
+        // prompt portions of running requests still prefilling
+        for (int64_t id : running) {
+            if (budget <= 0) break;
+            if (std::find(in_step.begin(), in_step.end(), id) != in_step.end()) continue;
+            SchedRequest& r = by_id[id];
+            const int64_t left = r.num_tokens() - r.num_computed;
+            const int n = fit(ids, ns, id, (int)std::min<int64_t>(left, budget));
+            if (n <= 0) continue;
+            entries.push_back({id, r.num_computed, n, n == left});
+            ids.push_back(id), ns.push_back(n), in_step.push_back(id);
+            budget -= n;
+        }
+        // admit waiting requests, first come first served
+        while (!waiting.empty() && budget > 0 && (int)running.size() < max_running && !cm->free_slots.empty()) {
+            SchedRequest& r = by_id[waiting.front()];
+            int slot = -1;
+            if (int rc = cm->add(r.id, &slot)) return rc;
+            const int64_t left = r.num_tokens();
+            const int n = fit(ids, ns, r.id, (int)std::min<int64_t>(left, budget));
+            if (n <= 0) {
+                if (int rc = cm->remove(r.id)) return rc;
+                break;                   // the head of the queue waits; nobody overtakes it
+            }
+            waiting.pop_front();
+            running.push_back(r.id);
+            admitted.push_back(r.id), admitted_slots.push_back(slot);
+            entries.push_back({r.id, 0, n, n == left});
+            ids.push_back(r.id), ns.push_back(n);
+            budget -= n;
+        }
+        if (entries.empty() && finished.empty() && !running.empty()) {
+            // every running request is mid-prefill and no page is free: make room from the back
+            if (running.size() > 1) {
+                SchedRequest& victim = by_id[running.back()];
+                if (int rc = preempt(victim)) return rc;
+                preempted.push_back(victim.id);
+                return schedule(entries, preempted, finished, admitted, admitted_slots);
+            }
+            SchedRequest& lone = by_id[running[0]];
+            if (int rc = finish(lone, FINISH_LENGTH)) return rc;
+            finished.push_back(lone.id);
+        }
+        return OK;
+    }
+    // One sampled token per entry with samples = 1, in order.
+    int update(const int32_t* sampled, int n_sampled, std::vector<int64_t>& done, std::vector<int>& reasons) {
+        int at = 0;
+        const int64_t cap = capacity_tokens();
+        for (const Entry& e : last) {
+            auto it = by_id.find(e.id);
+            if (it == by_id.end() || it->second.finish != FINISH_NONE) {      // aborted while the step ran
+                if (e.samples) ++at;
+                continue;
+            }
+            SchedRequest& r = it->second;
+            r.num_computed += e.count;
+            if (!e.samples) continue;
+            if (at >= n_sampled) return fail(E_VALUE, "update got %d sampled tokens, the step has more sampling entries", n_sampled);
+            const int32_t tok = sampled[at++];
+            r.output.push_back(tok);
+            int reason = FINISH_NONE;
+            if (std::find(r.stops.begin(), r.stops.end(), tok) != r.stops.end()) reason = FINISH_STOP;
+            else if ((int)r.output.size() >= r.max_tokens) reason = FINISH_LENGTH;
+            else if (r.num_tokens() + 1 > cap) reason = FINISH_LENGTH;
+            if (reason != FINISH_NONE) {
+                if (int rc = finish(r, reason)) return rc;
+                done.push_back(r.id), reasons.push_back(reason);
+            }
+        }
+        last.clear();
+        return OK;
+    }
+};
+
+template <typename T>
+int copy_out(const std::vector<T>& v, T* out, int cap, int* n, const char* what) {
+    if ((int)v.size() > cap) return fail(E_VALUE, "%s: %d results exceed the caller's room for %d", what, (int)v.size(), cap);
+    std::copy(v.begin(), v.end(), out);
+    *n = (int)v.size();
+    return OK;
+}
+
+}  // namespace
+
+API const char* q6k_host_last_error() { return g_msg; }
+API int q6k_host_abi_version() { return 1; }
+
+// ------------------------------------------------------------------------------- cache manager
+API void* q6k_cm_create(int n_groups, const int* sliding, const int* windows, int page_size, const int* num_pages, int max_requests) {
+    if (page_size <= 0 || n_groups < 0 || max_requests <= 0) {
+        fail(E_VALUE, "cache manager: bad sizes (page_size %d, groups %d, requests %d)", page_size, n_groups, max_requests);
+        return nullptr;
+    }
+    auto* cm = new CacheManager();
+    cm->page_size = page_size;
+    for (int g = 0; g < n_groups; ++g) {
+        if (sliding[g] && windows[g] <= 0) {
+            fail(E_VALUE, "a sliding group needs a positive window");
+            delete cm;
+            return nullptr;
+        }
+        cm->groups.push_back({sliding[g], windows[g]});
+        cm->pools.emplace_back(num_pages[g]);
+    }
+    cm->num_slots = max_requests;
+    for (int s = max_requests - 1; s >= 0; --s) cm->free_slots.push_back(s);
+    return cm;
+}
+API void q6k_cm_destroy(void* h) { delete (CacheManager*)h; }
+API int q6k_cm_add(void* h, int64_t id, int* slot) { return ((CacheManager*)h)->add(id, slot); }
+API int q6k_cm_remove(void* h, int64_t id) { return ((CacheManager*)h)->remove(id); }
+API int q6k_cm_info(void* h, int64_t id, int64_t* length, int* slot) {
+    CacheRequest* r = ((CacheManager*)h)->find(id);
+    if (!r) return fail(E_KEY, "request %lld is not live", (long long)id);
+    *length = r->length, *slot = r->slot;
+    return OK;
+}
+API int q6k_cm_pages_needed(void* h, int64_t id, int n_new, int* out) { return ((CacheManager*)h)->pages_needed(id, n_new, out); }
+API int q6k_cm_can_reserve(void* h, const int64_t* ids, const int* ns, int m, int* yes) { return ((CacheManager*)h)->can_reserve(ids, ns, m, yes); }
+API int q6k_cm_reserve(void* h, int64_t id, int n) { return ((CacheManager*)h)->reserve(id, n); }
+API int q6k_cm_commit(void* h, int64_t id) { return ((CacheManager*)h)->commit(id); }
+API int q6k_cm_cancel(void* h, int64_t id) { return ((CacheManager*)h)->cancel(id); }
+API int q6k_cm_check(void* h) { return ((CacheManager*)h)->check(); }
+API int q6k_cm_num_free(void* h, int group) { return ((CacheManager*)h)->pools[group].num_free(); }
+API int q6k_cm_slots_free(void* h) { return (int)((CacheManager*)h)->free_slots.size(); }
+API int q6k_cm_num_live(void* h) { return (int)((CacheManager*)h)->requests.size(); }
+// A view of a request's block table in one group: valid until the request's next reserve or removal.
+API int q6k_cm_table(void* h, int64_t id, int group, const int32_t** pages, int* len) {
+    CacheRequest* r = ((CacheManager*)h)->find(id);
+    if (!r) return fail(E_KEY, "request %lld is not live", (long long)id);
+    *pages = r->tables[group].pages.data();
+    *len = (int)r->tables[group].pages.size();
+    return OK;
+}
+
+// The step's description as one int32 block (what the step function uploads in one copy):
+// [tokens T | positions T | request of token T | q_start R+1 | pos_start R | slot R | logit rows W |
+//  block table of group 0: R x widths[0] | group 1 ...], -1 where a table has no page.
+// tokens: the entries' tokens back to back; want: for each entry want_counts[r] indices into its
+// tokens.  meta: [total ints, T, wanted rows, max context, max q_len].
+API int q6k_cm_fill_step(void* h, int R, const int64_t* ids, const int* q_lens, const int32_t* tokens, const int* want,
+                         const int* want_counts, const int* widths, int vocab, int32_t* out, int64_t capacity, int64_t* meta) {
+    CacheManager* cm = (CacheManager*)h;
+    int64_t T = 0, W = 0;
+    for (int r = 0; r < R; ++r) T += q_lens[r], W += want_counts[r];
+    int64_t total = 3 * T + (R + 1) + 2 * R + W;
+    for (size_t g = 0; g < cm->groups.size(); ++g) total += (int64_t)R * widths[g];
+    if (total > capacity) return fail(E_VALUE, "the step needs %lld ints, the block holds %lld", (long long)total, (long long)capacity);
+    int32_t *tok = out, *pos = tok + T, *rot = pos + T, *qs = rot + T, *ps = qs + R + 1, *sl = ps + R, *lr = sl + R, *tab = lr + W;
+    int64_t t = 0, w = 0, max_ctx = 0, max_q = 0, wi = 0;
+    qs[0] = 0;
+    for (int r = 0; r < R; ++r) {
+        CacheRequest* cr = cm->find(ids[r]);
+        if (!cr) return fail(E_KEY, "request %lld is not live", (long long)ids[r]);
+        const int n = q_lens[r];
+        for (int i = 0; i < n; ++i) {
+            const int32_t v = tokens[t + i];
+            if (v < 0 || v >= vocab) return fail(E_VALUE, "request %lld: token id %d outside 0..%d", (long long)ids[r], v, vocab - 1);
+            tok[t + i] = v, pos[t + i] = (int32_t)(cr->length + i), rot[t + i] = r;
+        }
+        for (int i = 0; i < want_counts[r]; ++i) {
+            const int at = want[wi++];
+            if (at < 0 || at >= n) return fail(E_VALUE, "request %lld: wanted place %d outside its %d tokens", (long long)ids[r], at, n);
+            lr[w++] = (int32_t)(t + at);
+        }
+        t += n;
+        qs[r + 1] = (int32_t)t, ps[r] = (int32_t)cr->length, sl[r] = cr->slot;
+        max_ctx = std::max<int64_t>(max_ctx, cr->length + n), max_q = std::max<int64_t>(max_q, n);
+    }
+    for (size_t g = 0; g < cm->groups.size(); ++g) {
+        const int wd = widths[g];
+        for (int r = 0; r < R; ++r) {
+            const std::vector<int32_t>& pages = cm->find(ids[r])->tables[g].pages;
+            if ((int)pages.size() > wd) return fail(E_VALUE, "request %lld holds %d blocks in group %d, the table is %d wide", (long long)ids[r], (int)pages.size(), (int)g, wd);
+            std::copy(pages.begin(), pages.end(), tab);
+            std::fill(tab + pages.size(), tab + wd, -1);
+            tab += wd;
+        }
+    }
+    meta[0] = total, meta[1] = T, meta[2] = W, meta[3] = max_ctx, meta[4] = max_q;
+    return OK;
+}
+
+// ------------------------------------------------------------------------------- scheduler
+API void* q6k_sched_create(void* cm, int max_batch_tokens, int max_running) {
+    if (max_batch_tokens < 1) {
+        fail(E_VALUE, "max_batch_tokens must be at least 1");
+        return nullptr;
+    }
+    auto* s = new Scheduler();
+    s->cm = (CacheManager*)cm, s->max_batch_tokens = max_batch_tokens, s->max_running = max_running;
+    return s;
+}
+API void q6k_sched_destroy(void* h) { delete (Scheduler*)h; }
+API int q6k_sched_add(void* h, int64_t id, const int32_t* prompt, int n, int max_tokens, const int32_t* stops, int n_stops) {
+    Scheduler* s = (Scheduler*)h;
+    if (s->by_id.count(id)) return fail(E_KEY, "request %lld already exists", (long long)id);
+    if (n < 1) return fail(E_VALUE, "a request needs at least one prompt token");
+    if (max_tokens < 1) return fail(E_VALUE, "max_tokens must be at least 1");
+    if (n + 1 > s->capacity_tokens()) return fail(E_VALUE, "prompt of %d tokens exceeds the cache capacity of %lld tokens", n, (long long)s->capacity_tokens());
+    SchedRequest r;
+    r.id = id, r.prompt.assign(prompt, prompt + n), r.stops.assign(stops, stops + n_stops), r.max_tokens = max_tokens;
+    s->by_id.emplace(id, std::move(r));
+    s->waiting.push_back(id);
+    return OK;
+}
+// A request whose prompt is taken to be in the cache already (the caller has reserved and committed
+// its pages) with its first generated token given: it decodes from its next step on.
+API int q6k_sched_adopt(void* h, int64_t id, const int32_t* prompt, int n, int32_t first_token, int max_tokens, const int32_t* stops, int n_stops) {
+    Scheduler* s = (Scheduler*)h;
+    if (s->by_id.count(id)) return fail(E_KEY, "request %lld already exists", (long long)id);
+    SchedRequest r;
+    r.id = id, r.prompt.assign(prompt, prompt + n), r.stops.assign(stops, stops + n_stops), r.max_tokens = max_tokens;
+    r.output.push_back(first_token);
+    r.num_computed = n;
+    s->by_id.emplace(id, std::move(r));
+    s->running.push_back(id);
+    return OK;
+}
+API int q6k_sched_abort(void* h, int64_t id, int* was_live) {
+    Scheduler* s = (Scheduler*)h;
+    auto it = s->by_id.find(id);
+    *was_live = 0;
+    if (it == s->by_id.end() || it->second.finish != FINISH_NONE) return OK;
+    *was_live = 1;
+    if (int rc = s->finish(it->second, FINISH_CANCELLED)) return rc;
+    s->by_id.erase(it);
+    return OK;
+}
+API int q6k_sched_counts(void* h, int* waiting, int* running) {
+    Scheduler* s = (Scheduler*)h;
+    *waiting = (int)s->waiting.size(), *running = (int)s->running.size();
+    return OK;
+}
+API int q6k_sched_queue(void* h, int which, int64_t* out, int cap, int* n) {
+    Scheduler* s = (Scheduler*)h;
+    std::vector<int64_t> v;
+    if (which == 0) v.assign(s->waiting.begin(), s->waiting.end());
+    else v = s->running;
+    return copy_out(v, out, cap, n, "queue");
+}
+API int q6k_sched_request(void* h, int64_t id, int64_t* num_computed, int* n_output, int* preemptions, int* finish) {
+    Scheduler* s = (Scheduler*)h;
+    auto it = s->by_id.find(id);
+    if (it == s->by_id.end()) return fail(E_KEY, "request %lld is unknown", (long long)id);
+    *num_computed = it->second.num_computed, *n_output = (int)it->second.output.size();
+    *preemptions = it->second.preemptions, *finish = it->second.finish;
+    return OK;
+}
+// Builds one step.  entries: per entry (id, start, count, samples).  A request that ends here
+// (cache exhausted) or is preempted is reported; admitted requests come with their state slots so
+// that the caller can clear per-request state before the step runs.
+API int q6k_sched_schedule(void* h, int cap, int64_t* ids, int64_t* starts, int* counts, int* samples, int* n_entries,
+                           int64_t* preempted, int* n_preempted, int64_t* finished, int* n_finished, int64_t* admitted,
+                           int* admitted_slots, int* n_admitted) {
+    Scheduler* s = (Scheduler*)h;
+    std::vector<Entry> entries;
+    std::vector<int64_t> pre, fin, adm;
+    std::vector<int> adm_slots;
+    if (int rc = s->schedule(entries, pre, fin, adm, adm_slots)) return rc;
+    if ((int)entries.size() > cap) return fail(E_VALUE, "schedule: %d entries exceed the caller's room for %d", (int)entries.size(), cap);
+    for (size_t i = 0; i < entries.size(); ++i) ids[i] = entries[i].id, starts[i] = entries[i].start, counts[i] = entries[i].count, samples[i] = entries[i].samples;
+    *n_entries = (int)entries.size();
+    if (int rc = copy_out(pre, preempted, cap, n_preempted, "preempted")) return rc;
+    if (int rc = copy_out(fin, finished, cap, n_finished, "finished")) return rc;
+    if (int rc = copy_out(adm, admitted, cap, n_admitted, "admitted")) return rc;
+    std::copy(adm_slots.begin(), adm_slots.end(), admitted_slots);
+    for (int64_t id : fin) s->by_id.erase(id);
+    s->last = entries;
+    return OK;
+}
+// Copies tokens[start, start + count) of a request (prompt then output) into out.
+API int q6k_sched_tokens(void* h, int64_t id, int64_t start, int count, int32_t* out) {
+    Scheduler* s = (Scheduler*)h;
+    auto it = s->by_id.find(id);
+    if (it == s->by_id.end()) return fail(E_KEY, "request %lld is unknown", (long long)id);
+    if (start < 0 || start + count > it->second.num_tokens()) return fail(E_VALUE, "request %lld has no tokens %lld..%lld", (long long)id, (long long)start, (long long)(start + count));
+    for (int i = 0; i < count; ++i) out[i] = it->second.token(start + i);
+    return OK;
+}
+API int q6k_sched_update(void* h, const int32_t* sampled, int n_sampled, int cap, int64_t* done, int* reasons, int* n_done) {
+    Scheduler* s = (Scheduler*)h;
+    std::vector<int64_t> d;
+    std::vector<int> why;
+    if (int rc = s->update(sampled, n_sampled, d, why)) return rc;
+    if (int rc = copy_out(d, done, cap, n_done, "finished")) return rc;
+    std::copy(why.begin(), why.end(), reasons);
+    for (int64_t id : d) s->by_id.erase(id);
+    return OK;
+}

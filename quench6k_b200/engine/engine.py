@@ -33,8 +33,7 @@ class RequestOutput:
 class Engine:
     def __init__(self, runner: ModelRunner, max_batch_tokens: int = 2048, max_running: Optional[int] = None):
         self.runner = runner
-        self.scheduler = Scheduler(runner.manager, max_batch_tokens, max_running,
-                                   admit=runner.add_request, release=runner.end_request)
+        self.scheduler = Scheduler(runner.manager, max_batch_tokens, max_running, on_admit=runner.reset_slot)
         self.sampler = Sampler()
         self._ids = itertools.count()
         self.eos = list(runner.model.spec.eos_token_ids)
@@ -86,9 +85,7 @@ class Engine:
         step = self.scheduler.max_batch_tokens          # pages are taken as portions of a chunked prefill would take them
         for at in range(0, len(req.prompt), step):
             self.runner.assume_cached(rid, min(step, len(req.prompt) - at))
-        req.num_computed = len(req.prompt)
-        self.scheduler.by_id[rid] = req
-        self.scheduler.running.append(req)
+        self.scheduler.adopt(req)
         return rid
 
     def abort(self, rid: Hashable) -> None:

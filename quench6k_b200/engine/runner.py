@@ -111,7 +111,10 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ requests
     def add_request(self, rid: Hashable) -> None:
-        slot = self.manager.add(rid)
+        self.reset_slot(self.manager.add(rid))
+
+    def reset_slot(self, slot: int) -> None:
+        """Clear the per-request state a new request finds in its slot."""
         for s in self.states:
             if s is not None:
                 s[slot].zero_()
@@ -134,58 +137,24 @@ class ModelRunner:
                  static: Optional[torch.Tensor] = None) -> StepContext:
         """The step's description: built on the host in one pinned block, uploaded in one copy
         (into `static` when given: a device block a CUDA graph reads)."""
-        mgr, ps = self.manager, self.page_size
         R = len(entries)
         q_lens = [len(e.tokens) for e in entries]
-        T = sum(q_lens)
-        pos_starts = [mgr.length(e.rid) for e in entries]
-        slots = [mgr.slot(e.rid) for e in entries]
         if widths is None:
             widths = self._widths(entries)
         n_want = sum(len(e.want) for e in entries)
-        total = 3 * T + (R + 1) + 2 * R + n_want + sum(R * w for w in widths)
+        total = 3 * sum(q_lens) + (R + 1) + 2 * R + n_want + sum(R * w for w in widths)
         if self._pinned_free is not None:
             self._pinned_free.synchronize()
         if self._pinned is None or self._pinned.numel() < total:
             self._pinned = torch.empty(max(total, 4096), dtype=torch.int32, pin_memory=True)
+        written, T, n_want, max_context, max_q_len = self.manager.pack_step(
+            [e.rid for e in entries], [e.tokens for e in entries], [e.want for e in entries], widths, self.vocab_size,
+            self._pinned.numpy())
+        assert written == total
+        o = 3 * T
         host = self._pinned.numpy()
-        o = 0
-
-        def take(n):
-            nonlocal o
-            v = host[o:o + n]
-            o += n
-            return v
-
-        tok, pos, rot = take(T), take(T), take(T)
-        qs, psv, sl, lr = take(R + 1), take(R), take(R), take(n_want)
-        t = w = 0
-        qs[0] = 0
-        for r, e in enumerate(entries):
-            n = q_lens[r]
-            arr = np.asarray(e.tokens, dtype=np.int64)
-            if n and (arr.min() < 0 or arr.max() >= self.vocab_size):
-                raise ValueError(f"request {e.rid!r}: token id outside 0..{self.vocab_size - 1}")
-            tok[t:t + n] = arr
-            pos[t:t + n] = np.arange(pos_starts[r], pos_starts[r] + n)
-            rot[t:t + n] = r
-            for i in e.want:
-                if not 0 <= i < n:
-                    raise ValueError(f"request {e.rid!r}: wanted place {i} outside its {n} tokens")
-                lr[w] = t + i
-                w += 1
-            t += n
-            qs[r + 1] = t
-            psv[r] = pos_starts[r]
-            sl[r] = slots[r]
-        tabs = []
-        for g, wd in enumerate(widths):
-            tb = take(R * wd).reshape(R, wd)
-            tb[:] = -1
-            for r, e in enumerate(entries):
-                row = mgr.table_array(e.rid, g)
-                tb[r, :len(row)] = row
-            tabs.append((tb, wd))
+        pos_starts = host[o + R + 1:o + 2 * R + 1].tolist()
+        slots = host[o + 2 * R + 1:o + 3 * R + 1].tolist()
         dev = static if static is not None else torch.empty(total, dtype=torch.int32, device=self.rt.device)
         if dev.numel() != total:
             raise RuntimeError("the static step block does not match this step's layout")
@@ -203,11 +172,11 @@ class ModelRunner:
 
         d_tok, d_pos, d_rot = view(T), view(T), view(T)
         d_qs, d_ps, d_sl, d_lr = view(R + 1), view(R), view(R), view(n_want)
-        d_tabs = [view(R * wd).view(R, wd) for _, wd in tabs]
+        d_tabs = [view(R * wd).view(R, wd) for wd in widths]
         return StepContext(T=T, R=R, token_ids=d_tok, positions=d_pos, req_of_token=d_rot, q_start=d_qs, pos_start=d_ps,
                            slot_ids=d_sl, block_tables=d_tabs, logit_rows=d_lr, n_logit_rows=n_want, q_lens=q_lens,
                            pos_starts=pos_starts, slots=slots,
-                           max_context=max(p + n for p, n in zip(pos_starts, q_lens)), max_q_len=max(q_lens))
+                           max_context=max_context, max_q_len=max_q_len)
 
     def _widths(self, entries: Sequence[StepEntry]) -> List[int]:
         mgr = self.manager

@@ -19,6 +19,9 @@ other model, admits a request only if its memory plan fits and fails requests wh
 by running ones (crates/engine/src/session.rs:824-904); finish reasons are its Stop, Length and
 Cancelled (crates/engine/src/session.rs:162-169).  This scheduler is host logic only and runs
 against the cache manager without a GPU.
+
+`Scheduler` is the C++ one (csrc/host/host.cpp, wrapped by NativeScheduler below) when the cache
+manager is the C++ one, else PyScheduler, its Python twin with the same rules; the tests run both.
 """
 from __future__ import annotations
 
@@ -26,7 +29,12 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Callable, Deque, Dict, Hashable, List, Optional, Sequence
 
-from ..cache import CacheManager
+import ctypes
+
+import numpy as np
+
+from ..cache import NativeCacheManager
+from ..cache.native import host_lib, i32, ptr32, ptr64, raise_for
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import SplitMix64
 from .batch import StepEntry
@@ -93,16 +101,20 @@ class ScheduledStep:
         return sum(e.count for e in self.entries)
 
 
-class Scheduler:
-    def __init__(self, manager: CacheManager, max_batch_tokens: int = 2048, max_running: Optional[int] = None,
-                 admit: Optional[Callable[[Hashable], None]] = None, release: Optional[Callable[[Hashable], None]] = None):
+class PyScheduler:
+    """`on_admit(slot)` is called for every request admitted by `schedule()`, before it returns, so
+    that the caller can clear the per-request state in that slot."""
+
+    def __init__(self, manager, max_batch_tokens: int = 2048, max_running: Optional[int] = None,
+                 on_admit: Optional[Callable[[int], None]] = None):
         if max_batch_tokens < 1:
             raise ValueError("max_batch_tokens must be at least 1")
         self.manager = manager
         self.max_batch_tokens = max_batch_tokens
         self.max_running = max_running if max_running is not None else manager.slots.num_slots
-        self._admit = admit or manager.add
-        self._release = release or manager.remove
+        self._admit = manager.add
+        self._release = manager.remove
+        self._on_admit = on_admit
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []          # admission order
         self.by_id: Dict[Hashable, Request] = {}
@@ -122,6 +134,16 @@ class Scheduler:
             raise ValueError(f"prompt of {len(req.prompt)} tokens exceeds the cache capacity of {self.capacity_tokens()} tokens")
         self.by_id[req.rid] = req
         self.waiting.append(req)
+
+    def adopt(self, req: Request) -> None:
+        """Take a request that is live in the cache manager with its whole prompt counted as cached
+        and its first output token given: it decodes from the next step on."""
+        if req.rid in self.by_id:
+            raise KeyError(f"request {req.rid!r} already exists")
+        req.params.validate()
+        req.num_computed = len(req.prompt)
+        self.by_id[req.rid] = req
+        self.running.append(req)
 
     def abort(self, rid: Hashable) -> Optional[Request]:
         req = self.by_id.get(rid)
@@ -205,7 +227,7 @@ class Scheduler:
         # 3. admit waiting requests, first come first served
         while self.waiting and budget > 0 and len(self.running) < self.max_running and self.manager.slots.num_free > 0:
             r = self.waiting[0]
-            self._admit(r.rid)
+            slot = self._admit(r.rid)
             left = r.num_tokens
             n = self._fit(chosen, r.rid, min(left, budget))
             if n <= 0:
@@ -213,6 +235,8 @@ class Scheduler:
                 break                      # the head of the queue waits; nobody overtakes it
             self.waiting.popleft()
             self.running.append(r)
+            if self._on_admit is not None:
+                self._on_admit(slot)
             step.entries.append(ScheduledEntry(r, 0, n, n == left))
             chosen.append((r.rid, n))
             budget -= n
@@ -255,3 +279,160 @@ class Scheduler:
             if r.finished:
                 done.append(r)
         return done
+
+
+_REASONS = {1: FINISH_STOP, 2: FINISH_LENGTH, 3: FINISH_CANCELLED}
+
+
+class NativeScheduler:
+    """The C++ scheduler behind PyScheduler's interface.  Queues, token lists and decisions live in
+    C++; the `Request` objects here mirror what the caller reads (output, counts, finish reason)
+    and carry what only Python needs (sampling parameters, the random stream)."""
+
+    def __init__(self, manager: NativeCacheManager, max_batch_tokens: int = 2048, max_running: Optional[int] = None,
+                 on_admit: Optional[Callable[[int], None]] = None):
+        if max_batch_tokens < 1:
+            raise ValueError("max_batch_tokens must be at least 1")
+        self.manager = manager
+        self.max_batch_tokens = max_batch_tokens
+        self.max_running = max_running if max_running is not None else manager.slots.num_slots
+        self._on_admit = on_admit
+        self._lib = host_lib()
+        self._h = self._lib.q6k_sched_create(manager._h, max_batch_tokens, self.max_running)
+        if not self._h:
+            raise ValueError(self._lib.q6k_host_last_error().decode())
+        self.by_id: Dict[Hashable, Request] = {}
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.q6k_sched_destroy(h)
+
+    # ------------------------------------------------------------------ queue
+    def capacity_tokens(self) -> int:
+        return min(p.num_pages for p in self.manager.pools) * self.manager.page_size if self.manager.pools else 1 << 60
+
+    def _queue(self, which: int) -> List[Request]:
+        cap = len(self.by_id) + 1
+        ids, n = np.zeros(cap, dtype=np.int64), ctypes.c_int32()
+        raise_for(self._lib.q6k_sched_queue(self._h, which, ptr64(ids), cap, ctypes.byref(n)))
+        return [self.by_id[self.manager.rid_of(int(i))] for i in ids[:n.value]]
+
+    @property
+    def waiting(self) -> List[Request]:
+        return self._queue(0)
+
+    @property
+    def running(self) -> List[Request]:
+        return self._queue(1)
+
+    def _drop(self, req: Request) -> None:
+        self.by_id.pop(req.rid, None)
+        self.manager.forget(req.rid)
+
+    def _register(self, req: Request, call) -> None:
+        if req.rid in self.by_id:
+            raise KeyError(f"request {req.rid!r} already exists")
+        req.params.validate()
+        known = req.rid in self.manager._nid
+        nid = self.manager.intern(req.rid)
+        rc = call(nid, i32(req.prompt), i32(req.params.stop_tokens))
+        if rc:
+            if not known:
+                self.manager.forget(req.rid)
+            raise_for(rc)
+        self.manager._held.add(req.rid)
+        self.by_id[req.rid] = req
+
+    def add(self, req: Request) -> None:
+        if not req.prompt:
+            raise ValueError("a request needs at least one prompt token")
+        self._register(req, lambda nid, prompt, stops: self._lib.q6k_sched_add(
+            self._h, nid, ptr32(prompt), len(prompt), req.params.max_tokens, ptr32(stops), len(stops)))
+
+    def adopt(self, req: Request) -> None:
+        """Take a request that is live in the cache manager with its whole prompt counted as cached
+        and its first output token given: it decodes from the next step on."""
+        if len(req.output) != 1:
+            raise ValueError("an adopted request brings exactly its first output token")
+        self._register(req, lambda nid, prompt, stops: self._lib.q6k_sched_adopt(
+            self._h, nid, ptr32(prompt), len(prompt), req.output[0], req.params.max_tokens, ptr32(stops), len(stops)))
+        req.num_computed = len(req.prompt)
+
+    def abort(self, rid: Hashable) -> Optional[Request]:
+        req = self.by_id.get(rid)
+        if req is None or req.finished:
+            return None
+        live = ctypes.c_int32()
+        raise_for(self._lib.q6k_sched_abort(self._h, self.manager._nid[rid], ctypes.byref(live)))
+        req.finish_reason = FINISH_CANCELLED
+        self._drop(req)
+        return req
+
+    def has_work(self) -> bool:
+        w, r = ctypes.c_int32(), ctypes.c_int32()
+        raise_for(self._lib.q6k_sched_counts(self._h, ctypes.byref(w), ctypes.byref(r)))
+        return bool(w.value or r.value)
+
+    # ------------------------------------------------------------------ one step
+    def schedule(self) -> ScheduledStep:
+        cap = len(self.by_id) + 1
+        ids, starts = np.zeros(cap, dtype=np.int64), np.zeros(cap, dtype=np.int64)
+        counts, samples = np.zeros(cap, dtype=np.int32), np.zeros(cap, dtype=np.int32)
+        pre, fin, adm = (np.zeros(cap, dtype=np.int64) for _ in range(3))
+        adm_slots = np.zeros(cap, dtype=np.int32)
+        n, n_pre, n_fin, n_adm = (ctypes.c_int32() for _ in range(4))
+        raise_for(self._lib.q6k_sched_schedule(self._h, cap, ptr64(ids), ptr64(starts), ptr32(counts), ptr32(samples), ctypes.byref(n),
+                                               ptr64(pre), ctypes.byref(n_pre), ptr64(fin), ctypes.byref(n_fin),
+                                               ptr64(adm), ptr32(adm_slots), ctypes.byref(n_adm)))
+        rid_of = self.manager.rid_of
+        step = ScheduledStep([])
+        for i in pre[:n_pre.value]:
+            r = self.by_id[rid_of(int(i))]
+            r.num_computed = 0
+            r.preemptions += 1
+            step.preempted.append(r)
+        for i in fin[:n_fin.value]:
+            r = self.by_id[rid_of(int(i))]
+            r.finish_reason = FINISH_LENGTH
+            step.finished.append(r)
+            self._drop(r)
+        if self._on_admit is not None:
+            for slot in adm_slots[:n_adm.value]:
+                self._on_admit(int(slot))
+        for k in range(n.value):
+            r = self.by_id[rid_of(int(ids[k]))]
+            step.entries.append(ScheduledEntry(r, int(starts[k]), int(counts[k]), bool(samples[k])))
+        return step
+
+    def update(self, step: ScheduledStep, sampled: Sequence[int]) -> List[Request]:
+        """Account for a finished step.  `sampled` holds one token for every entry with
+        samples=True, in order.  Returns the requests that ended."""
+        toks = i32([int(t) for t in sampled])
+        cap = len(step.entries) + 1
+        done_ids, reasons, n_done = np.zeros(cap, dtype=np.int64), np.zeros(cap, dtype=np.int32), ctypes.c_int32()
+        raise_for(self._lib.q6k_sched_update(self._h, ptr32(toks), len(toks), cap, ptr64(done_ids), ptr32(reasons), ctypes.byref(n_done)))
+        it = iter(toks.tolist())
+        for e in step.entries:
+            r = e.request
+            if r.finished:                 # aborted while the step ran
+                if e.samples:
+                    next(it)
+                continue
+            r.num_computed += e.count
+            if e.samples:
+                r.output.append(next(it))
+        done: List[Request] = []
+        for i, why in zip(done_ids[:n_done.value], reasons[:n_done.value]):
+            r = self.by_id[self.manager.rid_of(int(i))]
+            r.finish_reason = _REASONS[int(why)]
+            done.append(r)
+            self._drop(r)
+        return done
+
+
+def Scheduler(manager, max_batch_tokens: int = 2048, max_running: Optional[int] = None,
+              on_admit: Optional[Callable[[int], None]] = None):
+    """The scheduler that matches the cache manager: C++ for the C++ manager, Python for the Python one."""
+    cls = NativeScheduler if isinstance(manager, NativeCacheManager) else PyScheduler
+    return cls(manager, max_batch_tokens, max_running, on_admit)

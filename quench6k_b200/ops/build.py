@@ -1,4 +1,6 @@
-"""Compiles the CUDA sources under csrc/ for sm_100a into one shared library and loads it.
+"""Compiles the CUDA sources under csrc/ for sm_100a into one shared library and loads it; the
+C++ host sources under csrc/host/ (cache manager, scheduler, step packing: no CUDA in them) become
+a second library built with the C++ compiler alone, so host-only tests need no nvcc.
 
 The sources include no torch header, so a fresh checkout builds in well under a minute with plain
 nvcc; the launchers are `extern "C"` and are called through ctypes with raw device pointers and
@@ -25,8 +27,12 @@ LIB_NAME = "libq6k_b200.so"
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
+HOST_LIB_NAME = "libq6k_host.so"
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
+
 _lock = threading.Lock()
 _lib: Optional[ctypes.CDLL] = None
+_host_lib: Optional[ctypes.CDLL] = None
 
 
 class BuildError(RuntimeError):
@@ -140,3 +146,55 @@ def library() -> ctypes.CDLL:
             except OSError as e:
                 raise BuildError(f"cannot load {path}: {e}") from None
         return _lib
+
+
+# ---------------------------------------------------------------------------------- host library
+def host_sources() -> List[str]:
+    folder = os.path.join(CSRC, "host")
+    return sorted(os.path.join(folder, f) for f in os.listdir(folder) if f.endswith((".cpp", ".h")))
+
+
+def _cxx() -> str:
+    for cand in (os.environ.get("CXX"), "g++", "c++", "clang++"):
+        path = shutil.which(cand) if cand else None
+        if path:
+            return path
+    raise BuildError("no C++ compiler found (looked at $CXX, g++, c++, clang++): the host library cannot be built")
+
+
+def build_host(verbose: bool = True) -> str:
+    lib_dir, _ = _build_dirs()
+    lib_path = os.path.join(lib_dir, HOST_LIB_NAME)
+    stamp = lib_path + ".digest"
+    h = hashlib.sha256()
+    for p in host_sources():
+        with open(p, "rb") as f:
+            h.update(os.path.basename(p).encode() + f.read())
+    h.update(" ".join(HOST_FLAGS).encode())
+    digest = h.hexdigest()[:16]
+    if os.path.exists(lib_path) and os.path.exists(stamp) and open(stamp).read().strip() == digest:
+        return lib_path
+    if verbose:
+        _say(f"compiling the C++ host library into {lib_path}")
+    tmp = lib_path + f".tmp{os.getpid()}"
+    cpps = [p for p in host_sources() if p.endswith(".cpp")]
+    r = subprocess.run([_cxx(), *HOST_FLAGS, "-o", tmp, *cpps], capture_output=True, text=True)
+    if r.returncode != 0:
+        raise BuildError(f"building {HOST_LIB_NAME} failed:\n{r.stdout}\n{r.stderr}")
+    os.replace(tmp, lib_path)
+    with open(stamp, "w") as f:
+        f.write(digest)
+    return lib_path
+
+
+def host_library() -> ctypes.CDLL:
+    """The loaded host library (cache manager, scheduler, step packing)."""
+    global _host_lib
+    with _lock:
+        if _host_lib is None:
+            path = build_host()
+            try:
+                _host_lib = ctypes.CDLL(path)
+            except OSError as e:
+                raise BuildError(f"cannot load {path}: {e}") from None
+        return _host_lib

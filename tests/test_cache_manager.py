@@ -1,8 +1,18 @@
 import random
+import sys
 
+import numpy as np
 import pytest
 
-from quench6k_b200.cache import CacheManager, GroupSpec, OutOfPages, OutOfSlots, PagePool
+from quench6k_b200.cache import (CacheManager, GroupSpec, NativeCacheManager, OutOfPages, OutOfSlots, PagePool,
+                                 PyCacheManager)
+
+
+@pytest.fixture(params=["native", "python"], autouse=True)
+def backend(request, monkeypatch):
+    """Every test of this file runs against the C++ cache manager and against its Python twin."""
+    monkeypatch.setattr(sys.modules[__name__], "CacheManager", NativeCacheManager if request.param == "native" else PyCacheManager)
+    return request.param
 
 
 def test_pool_lifo_and_double_free():
@@ -121,3 +131,70 @@ def test_random_orders_lose_no_page(seed):
         m.remove(rid)
     m.check()
     assert m.pools[0].num_free == 40 and m.pools[1].num_free == 24 and m.slots.num_free == 4
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_both_managers_agree_on_tables_and_packed_steps(seed):
+    """The same random traffic through the C++ manager and the Python one: the same pages in the
+    same blocks, the same free counts, and the same packed step description."""
+    rng = random.Random(100 + seed)
+    ps = rng.choice([2, 4, 16])
+    groups = [GroupSpec("full"), GroupSpec("sliding", rng.choice([3, 9, 33]))]
+    pair = [cls(groups, page_size=ps, num_pages=[40, 24], max_requests=4) for cls in (NativeCacheManager, PyCacheManager)]
+    live, n = [], 0
+    for _ in range(400):
+        op = rng.random()
+        if op < 0.15 and len(live) < 4:
+            rid = ("r", n)
+            n += 1
+            assert len({m.add(rid) for m in pair}) == 1
+            live.append(rid)
+        elif op < 0.25 and live:
+            rid = live.pop(rng.randrange(len(live)))
+            for m in pair:
+                m.remove(rid)
+        elif live:
+            rid = rng.choice(live)
+            k = rng.choice([1, 1, 2, 5, 13])
+            assert pair[0].pages_needed(rid, k) == pair[1].pages_needed(rid, k)
+            ok = {m.can_reserve([(rid, k)]) for m in pair}
+            assert len(ok) == 1
+            if ok.pop():
+                # the packed description of a step over every live request that can run one token more
+                for m in pair:
+                    m.reserve(rid, k)
+                others = [r for r in live if r != rid and pair[1].pages_needed(r, 1) == [0, 0]][:2]
+                rids = [rid] + others
+                toks = [[rng.randrange(50) for _ in range(k)]] + [[rng.randrange(50)] for _ in others]
+                want = [[k - 1]] + [[0] for _ in others]
+                widths = [max(1, max(pair[1].table_len(r, g) for r in rids)) + g for g in range(2)]
+                blocks = []
+                for m in pair:
+                    out = np.full(4096, -7, dtype=np.int32)
+                    meta = m.pack_step(rids, toks, want, widths, 50, out)
+                    blocks.append((meta, out[:meta[0]].tolist()))
+                assert blocks[0] == blocks[1]
+                for m in pair:
+                    m.commit(rid)
+        for rid in live:
+            assert [pair[0].table(rid, g) for g in range(2)] == [pair[1].table(rid, g) for g in range(2)]
+            assert pair[0].length(rid) == pair[1].length(rid) and pair[0].slot(rid) == pair[1].slot(rid)
+        assert [p.num_free for p in pair[0].pools] == [p.num_free for p in pair[1].pools]
+        for m in pair:
+            m.check()
+
+
+def test_pack_step_refuses_bad_tokens_and_places():
+    m = CacheManager([GroupSpec("full")], page_size=4, num_pages=[8], max_requests=2)
+    m.add("a")
+    m.reserve("a", 3)
+    out = np.zeros(256, dtype=np.int32)
+    with pytest.raises(ValueError, match="token id outside"):
+        m.pack_step(["a"], [[1, 99, 2]], [[2]], [1], 50, out)
+    with pytest.raises(ValueError, match="wanted place 3"):
+        m.pack_step(["a"], [[1, 2, 3]], [[3]], [1], 50, out)
+    with pytest.raises(ValueError):
+        m.pack_step(["a"], [[1, 2, 3]], [[2]], [1], 50, out[:5])
+    total, T, W, ctx, q = m.pack_step(["a"], [[1, 2, 3]], [[0, 2]], [2], 50, out)
+    assert (T, W, ctx, q) == (3, 2, 3, 3)
+    assert out[:total].tolist() == [1, 2, 3, 0, 1, 2, 0, 0, 0, 0, 3, 0, m.slot("a"), 0, 2, 0, -1]

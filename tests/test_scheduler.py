@@ -1,12 +1,21 @@
 """The scheduler's decisions, against the cache manager alone (no GPU): a stand-in for the step
 function reserves and commits the pages and hands back made-up tokens."""
 import random
+import sys
 
 import pytest
 
-from quench6k_b200.cache import CacheManager, GroupSpec
-from quench6k_b200.engine.scheduler import (FINISH_CANCELLED, FINISH_LENGTH, FINISH_STOP, Request, Scheduler)
+from quench6k_b200.cache import CacheManager, GroupSpec, NativeCacheManager, PyCacheManager
+from quench6k_b200.engine.scheduler import (FINISH_CANCELLED, FINISH_LENGTH, FINISH_STOP, NativeScheduler, PyScheduler,
+                                            Request, Scheduler)
 from quench6k_b200.sampling import SamplingParams
+
+
+@pytest.fixture(params=["native", "python"], autouse=True)
+def backend(request, monkeypatch):
+    """Every test of this file runs against the C++ cache manager and against its Python twin."""
+    monkeypatch.setattr(sys.modules[__name__], "CacheManager", NativeCacheManager if request.param == "native" else PyCacheManager)
+    return request.param
 
 
 def make(pages=16, page_size=4, budget=16, max_requests=4, sliding=None):
@@ -149,3 +158,51 @@ def test_random_traffic_finishes_everything(seed):
     for r in finished:
         assert r.finish_reason in (FINISH_STOP, FINISH_LENGTH)
         assert 1 <= len(r.output) <= r.params.max_tokens
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_both_schedulers_decide_alike(seed):
+    """The same random traffic (arrivals, sampled tokens, aborts) through the C++ scheduler and the
+    Python one: the same entries, preemptions and endings in every step."""
+    rng = random.Random(500 + seed)
+    pages, ps = rng.choice([6, 12, 24]), rng.choice([2, 4])
+    budget, sliding = rng.choice([3, 7, 16, 40]), rng.choice([None, 5])
+    groups = [GroupSpec("full")] + ([GroupSpec("sliding", sliding)] if sliding else [])
+    pair = []
+    for cm, sc in ((NativeCacheManager, NativeScheduler), (PyCacheManager, PyScheduler)):
+        m = cm(groups, ps, [pages] * len(groups), 4)
+        admitted = []
+        pair.append((m, sc(m, max_batch_tokens=budget, on_admit=admitted.append), admitted))
+    total = 0
+    for step in range(1500):
+        if total < 30 and rng.random() < 0.35:
+            n, mt = rng.randint(1, pages * ps - 1), rng.randint(1, 25)
+            for m, s, _ in pair:
+                s.add(req(("r", total), n, max_tokens=mt, stop_tokens=[3]))
+            total += 1
+        if rng.random() < 0.03 and pair[1][1].running:
+            k = rng.randrange(len(pair[1][1].running))
+            assert [r.rid for r in pair[0][1].running] == [r.rid for r in pair[1][1].running]
+            for m, s, _ in pair:
+                s.abort(s.running[k].rid)
+        if rng.random() < 0.02 and pair[1][1].waiting:
+            for m, s, _ in pair:
+                s.abort(s.waiting[-1].rid)
+        assert pair[0][1].has_work() == pair[1][1].has_work()
+        if not pair[1][1].has_work():
+            if total >= 30:
+                break
+            continue
+        toks = [rng.randint(0, 9) for _ in range(8)]
+        seen = []
+        for m, s, admitted in pair:
+            del admitted[:]
+            it = iter(toks)
+            plan, done = run_step(m, s, lambda r: next(it))
+            seen.append(([(e.request.rid, e.start, e.count, e.samples) for e in plan.entries],
+                         [r.rid for r in plan.preempted], [r.rid for r in plan.finished],
+                         [(r.rid, r.finish_reason, list(r.output), r.preemptions) for r in done],
+                         sorted(admitted), [p.num_free for p in m.pools], m.slots.num_free,
+                         [(r.rid, r.num_computed, list(r.output)) for r in s.running], [r.rid for r in s.waiting]))
+        assert seen[0] == seen[1], f"step {step}"
+    assert total == 30 and not pair[0][1].has_work()

@@ -413,11 +413,20 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0)) attentio
 }
 
 // out[row] = sum_s 2^(m_s - M) o_s / (sum_s 2^(m_s - M) l_s + 2^(sink - M)); one block per (tile, KV head, row of
-// the tile), one thread per head dimension; the splits' values are fetched with independent loads.
+// the tile).  A thread owns four head dimensions of every GROUPS-th split, so that the many splits
+// of a long context at a small batch are fetched side by side; the groups' sums meet in shared
+// memory and are added in group order (a fixed order for a given number of splits).
+constexpr int MERGE_THREADS = 256;
 template <int HD>
-__global__ void __launch_bounds__(HD) attention_merge_kernel(const AttnParams p) {
+__global__ void __launch_bounds__(MERGE_THREADS) attention_merge_kernel(const AttnParams p) {
     pdl_enter();
-    const int tile = blockIdx.x, kh = blockIdx.y, r = blockIdx.z, G = p.G, d = threadIdx.x;
+    constexpr int LPR = HD / 4;                   // threads that cover one row of HD values
+    constexpr int GROUPS = MERGE_THREADS / LPR;
+    __shared__ float red[32];
+    __shared__ float4 acc_s[GROUPS][LPR];
+    __shared__ float den_s[GROUPS];
+    const int tile = blockIdx.x, kh = blockIdx.y, r = blockIdx.z, G = p.G;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int tok0 = p.tile_tok0[tile], ntok = p.tile_ntok[tile];
     const int tt = r / G, hg = r % G;
     if (tt >= ntok) return;
@@ -431,16 +440,41 @@ __global__ void __launch_bounds__(HD) attention_merge_kernel(const AttnParams p)
     const float* po = p.part_o + row * p.max_splits * HD;
     const float sk = p.sinks ? p.sinks[kh * G + hg] * LOG2E : -INFINITY;
     float M = sk;
-    for (int s = 0; s < se; ++s) M = fmaxf(M, ml[s * 2]);
-    float den = p.sinks ? exp2f(sk - M) : 0.0f, num = 0.0f;
-#pragma unroll 8
-    for (int s = 0; s < se; ++s) {
-        const float ms = ml[s * 2];
-        const float w = ms == -INFINITY ? 0.0f : exp2f(ms - M);
-        den = fmaf(w, ms == -INFINITY ? 0.0f : ml[s * 2 + 1], den);
-        num = fmaf(w, po[(size_t)s * HD + d], num);
+    for (int s = tid; s < se; s += MERGE_THREADS) M = fmaxf(M, ml[s * 2]);
+    M = warp_max(M);
+    if (lane == 0) red[warp] = M;
+    __syncthreads();
+#pragma unroll
+    for (int w = 0; w < MERGE_THREADS / 32; ++w) M = fmaxf(M, red[w]);
+    const int g = tid / LPR, c = tid % LPR;
+    float4 num = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    float den = 0.0f;
+#pragma unroll 4
+    for (int s = g; s < se; s += GROUPS) {
+        const float2 v = *reinterpret_cast<const float2*>(ml + s * 2);
+        const float4 o = *reinterpret_cast<const float4*>(po + (size_t)s * HD + c * 4);
+        const float w = v.x == -INFINITY ? 0.0f : exp2f(v.x - M);
+        den = fmaf(w, v.x == -INFINITY ? 0.0f : v.y, den);
+        num.x = fmaf(w, o.x, num.x), num.y = fmaf(w, o.y, num.y), num.z = fmaf(w, o.z, num.z), num.w = fmaf(w, o.w, num.w);
     }
-    p.out[row * HD + d] = __float2bfloat16_rn(num / den);
+    acc_s[g][c] = num;
+    if (c == 0) den_s[g] = den;
+    __syncthreads();
+    if (tid < LPR) {
+        float4 t = acc_s[0][tid];
+        float d = (p.sinks ? exp2f(sk - M) : 0.0f) + den_s[0];
+#pragma unroll
+        for (int q = 1; q < GROUPS; ++q) {
+            const float4 u = acc_s[q][tid];
+            t.x += u.x, t.y += u.y, t.z += u.z, t.w += u.w;
+            d += den_s[q];
+        }
+        const float inv = 1.0f / d;
+        __nv_bfloat162 lo = __floats2bfloat162_rn(t.x * inv, t.y * inv), hi = __floats2bfloat162_rn(t.z * inv, t.w * inv);
+        uint2 pk;
+        pk.x = *reinterpret_cast<uint32_t*>(&lo), pk.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p.out + row * HD + tid * 4) = pk;
+    }
 }
 
 // Tensor maps over the K and V pools of a layer do not change: keep them by (address, rows, box).
@@ -476,7 +510,7 @@ int launch(const AttnParams& p, const CUtensorMap* maps, int n_tiles, cudaStream
     q6k_launch(attention_mma_kernel<HD, WIDE, TMA>, dim3(p.max_splits, p.Hkv, n_tiles), (WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0), smem, st, maps[0], maps[1], maps[2], maps[3], p);
     if (int rc = q6k_check_launch("attention_mma")) return rc;
     if (p.max_splits > 1) {
-        q6k_launch(attention_merge_kernel<HD>, dim3(n_tiles, p.Hkv, ROWS), HD, 0, st, p);
+        q6k_launch(attention_merge_kernel<HD>, dim3(n_tiles, p.Hkv, ROWS), MERGE_THREADS, 0, st, p);
         return q6k_check_launch("attention_merge");
     }
     return 0;

@@ -57,29 +57,44 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 // Programmatic dependent launch (the reference launches every Flint kernel this way,
-// crates/cuda/kernels/common.cuh:82-99): a kernel lets the next one in the stream be scheduled as
-// soon as all of its own blocks are resident, and itself touches no global memory before every
-// earlier kernel has completed.  Every kernel calls pdl_enter() first, so stream order holds for
-// memory while launch latency and block scheduling overlap the predecessor's tail.  Measured on
-// B200 under CUDA-graph replay the attribute made a decode step 3 % slower (5.00 vs 4.85 ms), so it
-// is off unless Q6K_PDL=1 is set; without the attribute both instructions are no-ops.
+// crates/cuda/kernels/common.cuh:82-99).  A launch that carries the attribute may begin as soon as
+// every block of the kernel before it has executed pdl_launch() (or ended); it must execute
+// pdl_wait() before it touches anything an earlier kernel writes or reads, since pdl_wait() returns
+// only when the kernel before it has completed and its memory is visible.  Every kernel calls
+// pdl_enter() (both, in this order) first unless it has work that needs no earlier result: the
+// dense tensor-core GEMM sets itself up and fetches weights before it waits.  A kernel that
+// allocates tensor memory calls pdl_launch() only after the allocation, so that a successor cannot
+// take the columns one of its own blocks still needs.  Without the attribute both are no-ops.
+//
+// Measured on B200 under CUDA-graph replay, the attribute costs about 0.3 us per launch when the
+// kernel has nothing to overlap (a decode step with it on every launch: 4.93 vs 4.86 ms), so only
+// launches that have such work carry it.  The environment variable Q6K_PDL overrides:
+// "0" no launch, "1" every launch, unset or "gemm" only those marked.
+__device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_enter() {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    pdl_launch();
+    pdl_wait();
 }
 
-bool q6k_pdl_enabled();       // Q6K_PDL=1 in the environment switches the launch attribute on
+int q6k_pdl_mode();           // 0: never, 1: every launch, 2: launches marked as overlapping
 
 template <typename... KArgs, typename... Args>
-cudaError_t q6k_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+cudaError_t q6k_launch_as(bool overlaps, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid, cfg.blockDim = block, cfg.dynamicSmemBytes = smem, cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = q6k_pdl_enabled() ? 1 : 0;
+    const int mode = q6k_pdl_mode();
+    cfg.numAttrs = (mode == 1 || (mode == 2 && overlaps)) ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+cudaError_t q6k_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    return q6k_launch_as(false, kernel, grid, block, smem, st, static_cast<Args&&>(args)...);
 }
 
 // Dispatch on a dtype code: body sees `T`.

@@ -19,12 +19,13 @@ int q6k_check_launch(const char* what) {
     return q6k_fail("%s: %s", what, cudaGetErrorString(e));
 }
 
-bool q6k_pdl_enabled() {
-    static const bool on = [] {
+int q6k_pdl_mode() {
+    static const int mode = [] {
         const char* v = getenv("Q6K_PDL");
-        return v && v[0] == '1';
+        if (!v || !v[0]) return 2;
+        return v[0] == '0' ? 0 : v[0] == '1' ? 1 : 2;
     }();
-    return on;
+    return mode;
 }
 
 Q6K_API const char* q6k_last_error() { return g_msg; }

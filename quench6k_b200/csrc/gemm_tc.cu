@@ -48,6 +48,7 @@ struct Params {
     const int* group_offsets;
     const int* num_tiles;
     const int* pair_order;             // pair mode: tile y works on pair pair_order[y] (null: pair y)
+    unsigned* tickets;                 // pair mode with K slices: one arrival counter per (pair, n-tile), zero between launches
     int rows_total, N, K, ldo;
     int epilogue, stages, kb_per_split;
     int pair_div;                      // > 0: one tile per (token, slot) pair, see q6k_gemm_tc_pairs
@@ -137,7 +138,10 @@ __device__ __forceinline__ bool decode_tile(const Params& p, int t, int n_x, int
 template <int BT, bool DUAL>
 __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_w2,
                                                        const __grid_constant__ CUtensorMap tm_a, const Params p) {
-    pdl_enter();
+    // Dense tiles follow from the launch alone, so their weights can be on the way before the kernel
+    // that makes the activations has ended; tile lists and pair lists come from earlier kernels.
+    const bool early = p.tile_group == nullptr;
+    if (!early) pdl_wait();
     const int n_x = (p.N + WM - 1) / WM;
     const int n_y = p.pair_div > 0 ? p.n_y : (p.tile_group ? *p.num_tiles : p.n_y);
     const int total = n_x * n_y * p.n_z;
@@ -151,6 +155,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
     constexpr int COLS = tmem_cols(2 * ACC_COLS);
     __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 4];
     __shared__ uint32_t tmem_base_slot;
+    __shared__ int fix_last;
     const int stages = p.stages;
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[MAX_STAGES]);
     const uint32_t acc_full0 = smem_u32(&bars[2 * MAX_STAGES]), acc_empty0 = smem_u32(&bars[2 * MAX_STAGES + 2]);
@@ -179,9 +184,27 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
+    pdl_launch();                                          // this block holds its tensor memory: a successor may come
 
     if (warp == 0) {
         if (lane == 0) {
+            int pre = 0;                                   // k-blocks whose weights went out before the wait
+            if (early) {
+                for (int t = blockIdx.x; t < total && pre < stages; t += gridDim.x) {
+                    Tile tl;
+                    if (!decode_tile<BT>(p, t, n_x, n_y, tl)) continue;
+                    const int wy = tl.g * p.N + tl.n0;
+                    for (int i = 0; i < tl.nkb && pre < stages; ++i, ++pre) {
+                        const uint32_t st = smem_u32(smem + (size_t)pre * STAGE_BYTES);
+                        const uint32_t fb = full0 + 8 * pre;
+                        mbar_expect_tx(fb, STAGE_BYTES);
+                        const int kx = (tl.kb0 + i) * BK;
+                        tma_load_2d(st, &tm_w, kx, wy, fb);
+                        if (DUAL) tma_load_2d(st + W_BYTES, &tm_w2, kx, wy, fb);
+                    }
+                }
+                pdl_wait();
+            }
             int it = 0;                                    // k-blocks issued so far, over all tiles
             bool ok = true;
             for (int t = blockIdx.x; t < total && ok; t += gridDim.x) {
@@ -190,17 +213,19 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
                 const int wy = tl.g * p.N + tl.n0;
                 for (int i = 0; i < tl.nkb; ++i, ++it) {
                     const int s = it % stages;
-                    if (!mbar_wait(empty0 + 8 * s, ((it / stages) & 1) ^ 1)) {
-                        atomicExch(&g_tc_status, 1);
-                        ok = false;
-                        break;
-                    }
                     const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
                     const uint32_t fb = full0 + 8 * s;
-                    mbar_expect_tx(fb, STAGE_BYTES);
                     const int kx = (tl.kb0 + i) * BK;
-                    tma_load_2d(st, &tm_w, kx, wy, fb);
-                    if (DUAL) tma_load_2d(st + W_BYTES, &tm_w2, kx, wy, fb);
+                    if (it >= pre) {
+                        if (!mbar_wait(empty0 + 8 * s, ((it / stages) & 1) ^ 1)) {
+                            atomicExch(&g_tc_status, 1);
+                            ok = false;
+                            break;
+                        }
+                        mbar_expect_tx(fb, STAGE_BYTES);
+                        tma_load_2d(st, &tm_w, kx, wy, fb);
+                        if (DUAL) tma_load_2d(st + W_BYTES, &tm_w2, kx, wy, fb);
+                    }
                     tma_load_2d(st + W_BYTES * (DUAL ? 2 : 1), &tm_a, kx, tl.row0, fb);
                 }
             }
@@ -249,6 +274,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
         const int quarter = warp & 3;
         const int n_local = quarter * 32 + lane;
         int nt = 0;
+        if (early) pdl_wait();                             // the output may still be in use by the kernel before
         for (int t = blockIdx.x; t < total; t += gridDim.x) {
             Tile tl;
             if (!decode_tile<BT>(p, t, n_x, n_y, tl)) continue;
@@ -261,6 +287,48 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
             const int n = tl.n0 + n_local;
             const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * ACC_COLS;
             const int valid = min(BT, tl.row_end - tl.row0);
+            if (p.pair_div > 0 && p.n_z > 1) {
+                // A pair's K slices run in different CTAs.  Each leaves its slice's sums in global
+                // memory and takes a ticket; the one that comes last adds the slices in their order
+                // (whoever it is: the result does not depend on the arrival order) and finishes the tile.
+                float v[16], u[16];
+                tmem_ld16(lane_addr, v);
+                if (DUAL) tmem_ld16(lane_addr + BT, u);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
+                constexpr int PARTS = DUAL ? 2 : 1;
+                const size_t slice = (size_t)p.n_y * PARTS * p.N;          // floats per K slice
+                float* mine = p.partial + (size_t)tl.out0 * PARTS * p.N;
+                if (n < p.N) {
+                    __stcg(mine + tl.z * slice + n, v[0]);
+                    if (DUAL) __stcg(mine + tl.z * slice + p.N + n, u[0]);
+                }
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (threadIdx.x == 64) {
+                    unsigned* tk = p.tickets + (size_t)tl.out0 * n_x + tl.n0 / WM;
+                    const int last = atomicAdd(tk, 1u) == (unsigned)(p.n_z - 1);
+                    if (last) *tk = 0;                                    // nobody else comes: ready for the next launch
+                    fix_last = last;
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const int last = fix_last;
+                asm volatile("bar.sync 1, 128;" ::: "memory");             // fix_last may be rewritten for the next tile
+                if (last && n < p.N) {
+                    __threadfence();
+                    float a = 0.0f, b = 0.0f;
+                    for (int z = 0; z < p.n_z; ++z) {
+                        a += __ldcg(mine + z * slice + n);
+                        if (DUAL) b += __ldcg(mine + z * slice + p.N + n);
+                    }
+                    const size_t row = (size_t)tl.out0;
+                    if (p.epilogue == EPI_SWIGLU) ((__nv_bfloat16*)p.out)[row * p.ldo + n] = __float2bfloat16_rn(a / (1.0f + expf(-a)) * b);
+                    else ((float*)p.out)[row * p.ldo + n] = a;
+                }
+                ++nt;
+                continue;
+            }
 #pragma unroll 1
             for (int c0 = 0; c0 < valid; c0 += 16) {
                 float v[16], u[16];
@@ -352,6 +420,11 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tw2, const CUtensorMap& ta,
     // wide ones: one CTA per SM whose ring takes all of it
     int per_sm = BT <= 64 ? (220 * 1024) / (stage * 3) : 1;
     per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
+    const long long total = (long long)((p.N + WM - 1) / WM) * n_y * n_z;
+    // fewer tiles than that: the CTAs an SM really gets share its memory, so a lone CTA has a ring
+    // deep enough to have its whole K slice on the way at once
+    const int need = (int)((total + sm_count() - 1) / sm_count());
+    if (need < per_sm) per_sm = need < 1 ? 1 : need;
     int stages = ((220 / per_sm) * 1024) / stage;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     p.stages = stages;
@@ -363,10 +436,9 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tw2, const CUtensorMap& ta,
             return q6k_check_launch("gemm_tc: shared memory attribute");
         configured = true;
     }
-    const long long total = (long long)((p.N + WM - 1) / WM) * n_y * n_z;
     const int slots = sm_count() * per_sm;
     const int grid = (int)(total < slots ? total : slots);
-    q6k_launch(gemm_tc_kernel<BT, DUAL>, grid, 192, smem, st, tw, tw2, ta, p);
+    q6k_launch_as(p.tile_group == nullptr, gemm_tc_kernel<BT, DUAL>, grid, 192, smem, st, tw, tw2, ta, p);
     return q6k_check_launch("gemm_tc");
 }
 
@@ -497,9 +569,30 @@ Q6K_API int q6k_gemm_tc(const void* A, long long lda, int rows_total, const void
 // pair_order (int32 [pairs] or null): the order in which the pairs are worked on; sorted by expert
 // it lets the tiles of one expert run side by side and find its weights in L2.
 // epilogue: 0 store FP32, 2 SwiGLU -> bfloat16.
+// K slices of a pair product: only when the pairs are so few that most SMs would have no tile.
+static int pair_splits(int pairs, int N, int K) {
+    const int tiles = pairs * ((N + WM - 1) / WM), kb = (K + BK - 1) / BK;
+    if (tiles * 2 > sm_count() || kb < 8) return 1;
+    int s = sm_count() / tiles;
+    if (s > kb / 4) s = kb / 4;
+    if (s > 8) s = 8;
+    if (s < 1) s = 1;
+    const int per = (kb + s - 1) / s;
+    return (kb + per - 1) / per;
+}
+
+// Scratch the pair product below needs when it slices K: floats for the slices' sums and counters
+// (which must be zero before the first call; the kernel leaves them zero).
+Q6K_API int q6k_gemm_tc_pairs_scratch(int pairs, int N, int K, int dual, long long* floats, int* counters) {
+    const int s = pair_splits(pairs, N, K);
+    *floats = s > 1 ? (long long)s * pairs * (dual ? 2 : 1) * N : 0;
+    *counters = s > 1 ? pairs * ((N + WM - 1) / WM) : 0;
+    return 0;
+}
+
 Q6K_API int q6k_gemm_tc_pairs(const void* A, long long lda, int a_rows, const void* W, const void* W2, int groups, int N, int K,
                               void* out, int ldo, int epilogue, const int* pair_expert, const int* pair_order, int pairs, int pair_div,
-                              cudaStream_t st) {
+                              float* partial, long long partial_floats, unsigned* tickets, int n_tickets, cudaStream_t st) {
     if (pairs == 0 || N == 0) return 0;
     Q6K_REQUIRE(a_rows > 0 && N > 0 && K > 0 && groups > 0 && pairs > 0 && pair_div > 0, "gemm_tc_pairs: bad sizes rows=%d N=%d K=%d pairs=%d", a_rows, N, K, pairs);
     Q6K_REQUIRE(K % 8 == 0 && lda % 8 == 0, "gemm_tc_pairs: K=%d and the row pitch %lld must be multiples of 8", K, lda);
@@ -516,8 +609,17 @@ Q6K_API int q6k_gemm_tc_pairs(const void* A, long long lda, int a_rows, const vo
     if (int rc = make_map(&ta, A, a_rows, K, lda, 16, false)) return rc;
     Params p{};
     p.out = out, p.tile_group = pair_expert, p.rows_total = a_rows, p.N = N, p.K = K, p.ldo = ldo, p.epilogue = epilogue;
-    p.kb_per_split = (K + BK - 1) / BK;
+    const int kb = (K + BK - 1) / BK;
+    int splits = pair_splits(pairs, N, K);
+    if (splits > 1) {
+        long long need_f;
+        int need_c;
+        q6k_gemm_tc_pairs_scratch(pairs, N, K, dual, &need_f, &need_c);
+        if (!partial || !tickets || partial_floats < need_f || n_tickets < need_c) splits = 1;      // no scratch given: whole K per tile
+    }
+    p.kb_per_split = (kb + splits - 1) / splits;
+    p.partial = partial, p.tickets = tickets;
     p.pair_div = pair_div;
     p.pair_order = pair_order;
-    return dual ? launch<16, true>(tw, tw2, ta, p, pairs, 1, st) : launch<16, false>(tw, tw2, ta, p, pairs, 1, st);
+    return dual ? launch<16, true>(tw, tw2, ta, p, pairs, splits, st) : launch<16, false>(tw, tw2, ta, p, pairs, splits, st);
 }

@@ -49,7 +49,7 @@ def _need(t: torch.Tensor, name: str, dtype=None, shape=None):
 
 
 # kernels launched per exported function (for launch accounting in benchmarks)
-_LAUNCHES = {"q6k_moe_permute": 3, "q6k_gemm_tc": 1, "q6k_attention_mma": 2, "q6k_argmax": 2}
+_LAUNCHES = {"q6k_moe_permute": 3, "q6k_gemm_tc": 1, "q6k_attention_mma": 2, "q6k_argmax": 2, "q6k_gemm_tc_pairs_scratch": 0}
 launch_count = 0
 
 
@@ -234,12 +234,15 @@ def tc_status() -> int:
 
 
 _workspaces = {}
+_retired = []                             # outgrown scratch stays allocated: recorded CUDA graphs still point at it
 
 
 def _workspace(nbytes: int, device) -> torch.Tensor:
     key = str(device)                     # one scratch buffer per device: the engine runs on one stream
     ws = _workspaces.get(key)
     if ws is None or ws.numel() * 4 < nbytes:
+        if ws is not None:
+            _retired.append(ws)
         ws = torch.empty(max(nbytes // 4, 1 << 20), dtype=torch.float32, device=device)
         _workspaces[key] = ws
     return ws
@@ -477,6 +480,9 @@ def router_small(xn: torch.Tensor, w: torch.Tensor, k: int, scoring: str, renorm
     return sel_e, sel_w, order
 
 
+_pair_scratch = {}
+
+
 def gemm_tc_pairs(a: torch.Tensor, w: torch.Tensor, pair_expert: torch.Tensor, pair_div: int, w2: Optional[torch.Tensor] = None,
                   order: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Expert products of a decode step without a permutation: pair y (= token * slots + slot)
@@ -494,9 +500,22 @@ def gemm_tc_pairs(a: torch.Tensor, w: torch.Tensor, pair_expert: torch.Tensor, p
     if w2 is not None:
         _need(w2, "w2", torch.bfloat16, w.shape)
     out = torch.empty((pairs, N), dtype=torch.bfloat16 if w2 is not None else torch.float32, device=a.device)
+    # a few pairs only: K is sliced over CTAs, which meet through scratch kept per device (one stream uses it at a time)
+    floats, counters = ctypes.c_longlong(), ctypes.c_int()
+    _call("q6k_gemm_tc_pairs_scratch", _i(pairs), _i(N), _i(K), _i(1 if w2 is not None else 0), ctypes.byref(floats), ctypes.byref(counters))
+    partial = tickets = None
+    if floats.value:
+        key = str(a.device)
+        partial, tickets = _pair_scratch.get(key, (None, None))
+        if partial is None or partial.numel() < floats.value or tickets.numel() < counters.value:
+            _retired.append((partial, tickets))
+            partial = torch.empty(max(floats.value, 1 << 18), dtype=torch.float32, device=a.device)
+            tickets = torch.zeros(max(counters.value, 1024), dtype=torch.int32, device=a.device)
+            _pair_scratch[key] = (partial, tickets)
     _call("q6k_gemm_tc_pairs", _ptr(a), _ll(a.stride(0)), _i(a.shape[0]), _ptr(w), _ptr(w2), _i(G), _i(N), _i(K), _ptr(out),
           _i(out.stride(0)), _i(EPI_SWIGLU if w2 is not None else EPI_STORE), _ptr(pair_expert), _ptr(order), _i(pairs), _i(pair_div),
-          _stream())
+          _ptr(partial), _ll(partial.numel() if partial is not None else 0), _ptr(tickets),
+          _i(tickets.numel() if tickets is not None else 0), _stream())
     return out
 
 

@@ -129,16 +129,61 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0)) attentio
     if (split >= se) return;
     const int t_begin = first_tile + split * per, t_end = min(end_tile, t_begin + per);
 
+    // ---- the producer (one thread) brings every tile of this CTA's key range into the ring
+    auto issue = [&](int i) {
+        const int ps = p.page_size, box = ps < KT ? ps : KT;            // keys per TMA box
+        const int s2 = i % STAGES;
+        const uint32_t fb = full0 + 8 * s2;
+        mbar_expect_tx(fb, 2 * TILE_BYTES);
+        const int j0 = (t_begin + i) * KT;
+        // pages with consecutive numbers are contiguous for one head: when the tile's pages form
+        // such a run, each half comes in as one box of 64 keys instead of one box per page
+        bool run = ps < KT && j0 >= k_lo && j0 / ps + KT / ps <= p.max_blocks;
+        int first = -1;
+        if (run) {
+            first = bt[j0 / ps];
+            run = first >= 0;
+            for (int b = 1; b < KT / ps && run; ++b) run = bt[j0 / ps + b] == first + b;
+        }
+        if (run) {
+            const int y = (kh * p.num_pages + first) * ps;
+#pragma unroll
+            for (int h = 0; h < HD / 64; ++h) {
+                const uint32_t off = s2 * TILE_BYTES + h * (KT * 128);
+                tma_load_2d(k_s + off, &tm_k_run, h * 64, y, fb);
+                tma_load_2d(v_s + off, &tm_v_run, h * 64, y, fb);
+            }
+            return;
+        }
+        for (int b = 0; b < KT / box; ++b) {
+            const int j = j0 + b * box;
+            int y = p.pool_rows;                                         // out of range: the box is filled with zeros
+            if (j + box > k_lo && j <= pos_last) {
+                const int page = bt[j / ps];
+                if (page >= 0) y = (kh * p.num_pages + page) * ps + j % ps;
+            }
+#pragma unroll
+            for (int h = 0; h < HD / 64; ++h) {
+                const uint32_t off = s2 * TILE_BYTES + h * (KT * 128) + b * box * 128;
+                tma_load_2d(k_s + off, &tm_k, h * 64, y, fb);
+                tma_load_2d(v_s + off, &tm_v, h * 64, y, fb);
+            }
+        }
+    };
     if (TMA && tid == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_v) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k_run) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_v_run) : "memory");
+    }
+    if (TMA && tid == CW * 32) {
+        // the first tiles are on their way while the consumers still fetch Q
         for (int s2 = 0; s2 < STAGES; ++s2) {
             mbar_init(full0 + 8 * s2, 1);
             mbar_init(empty0 + 8 * s2, CW);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_v) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k_run) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_v_run) : "memory");
+        for (int i = 0; i < STAGES && i < t_end - t_begin; ++i) issue(i);
     }
     // ---- Q tile into shared memory (zero rows past the tile's tokens)
     if (warp < CW) {
@@ -166,51 +211,13 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0)) attentio
     __syncthreads();
 
     if (TMA && warp == CW) {
-        // ---- producer: one thread brings every tile of this CTA's key range into the ring
         if (lane == 0) {
-            const int ps = p.page_size, box = ps < KT ? ps : KT;        // keys per TMA box
-            for (int i = 0; i < t_end - t_begin; ++i) {
-                const int s2 = i % STAGES;
-                if (!mbar_wait(empty0 + 8 * s2, ((i / STAGES) & 1) ^ 1)) {
+            for (int i = STAGES; i < t_end - t_begin; ++i) {
+                if (!mbar_wait(empty0 + 8 * (i % STAGES), ((i / STAGES) & 1) ^ 1)) {
                     atomicExch(&g_attn_status, 1);
                     break;
                 }
-                const uint32_t fb = full0 + 8 * s2;
-                mbar_expect_tx(fb, 2 * TILE_BYTES);
-                const int j0 = (t_begin + i) * KT;
-                // pages with consecutive numbers are contiguous for one head: when the tile's pages form
-                // such a run, each half comes in as one box of 64 keys instead of one box per page
-                bool run = ps < KT && j0 >= k_lo && j0 / ps + KT / ps <= p.max_blocks;
-                int first = -1;
-                if (run) {
-                    first = bt[j0 / ps];
-                    run = first >= 0;
-                    for (int b = 1; b < KT / ps && run; ++b) run = bt[j0 / ps + b] == first + b;
-                }
-                if (run) {
-                    const int y = (kh * p.num_pages + first) * ps;
-#pragma unroll
-                    for (int h = 0; h < HD / 64; ++h) {
-                        const uint32_t off = s2 * TILE_BYTES + h * (KT * 128);
-                        tma_load_2d(k_s + off, &tm_k_run, h * 64, y, fb);
-                        tma_load_2d(v_s + off, &tm_v_run, h * 64, y, fb);
-                    }
-                    continue;
-                }
-                for (int b = 0; b < KT / box; ++b) {
-                    const int j = j0 + b * box;
-                    int y = p.pool_rows;                                 // out of range: the box is filled with zeros
-                    if (j + box > k_lo && j <= pos_last) {
-                        const int page = bt[j / ps];
-                        if (page >= 0) y = (kh * p.num_pages + page) * ps + j % ps;
-                    }
-#pragma unroll
-                    for (int h = 0; h < HD / 64; ++h) {
-                        const uint32_t off = s2 * TILE_BYTES + h * (KT * 128) + b * box * 128;
-                        tma_load_2d(k_s + off, &tm_k, h * 64, y, fb);
-                        tma_load_2d(v_s + off, &tm_v, h * 64, y, fb);
-                    }
-                }
+                issue(i);
             }
         }
         return;
@@ -439,6 +446,20 @@ __global__ void __launch_bounds__(MERGE_THREADS) attention_merge_kernel(const At
     const float* ml = p.part_ml + row * p.max_splits * 2;
     const float* po = p.part_o + row * p.max_splits * HD;
     const float sk = p.sinks ? p.sinks[kh * G + hg] * LOG2E : -INFINITY;
+    // every load of the first round goes out before the maximum is known: the values and the
+    // (m, l) pairs do not depend on it
+    constexpr int U = 4;
+    const int g = tid / LPR, c = tid % LPR;
+    float2 v0[U];
+    float4 o0[U];
+#pragma unroll
+    for (int j = 0; j < U; ++j) {
+        const int s = g + j * GROUPS;
+        if (s < se) {
+            v0[j] = *reinterpret_cast<const float2*>(ml + s * 2);
+            o0[j] = *reinterpret_cast<const float4*>(po + (size_t)s * HD + c * 4);
+        }
+    }
     float M = sk;
     for (int s = tid; s < se; s += MERGE_THREADS) M = fmaxf(M, ml[s * 2]);
     M = warp_max(M);
@@ -446,16 +467,30 @@ __global__ void __launch_bounds__(MERGE_THREADS) attention_merge_kernel(const At
     __syncthreads();
 #pragma unroll
     for (int w = 0; w < MERGE_THREADS / 32; ++w) M = fmaxf(M, red[w]);
-    const int g = tid / LPR, c = tid % LPR;
     float4 num = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
     float den = 0.0f;
-#pragma unroll 4
-    for (int s = g; s < se; s += GROUPS) {
-        const float2 v = *reinterpret_cast<const float2*>(ml + s * 2);
-        const float4 o = *reinterpret_cast<const float4*>(po + (size_t)s * HD + c * 4);
+    auto take = [&](const float2 v, const float4 o) {
         const float w = v.x == -INFINITY ? 0.0f : exp2f(v.x - M);
         den = fmaf(w, v.x == -INFINITY ? 0.0f : v.y, den);
         num.x = fmaf(w, o.x, num.x), num.y = fmaf(w, o.y, num.y), num.z = fmaf(w, o.z, num.z), num.w = fmaf(w, o.w, num.w);
+    };
+#pragma unroll
+    for (int j = 0; j < U; ++j)
+        if (g + j * GROUPS < se) take(v0[j], o0[j]);
+    for (int s0 = g + U * GROUPS; s0 < se; s0 += U * GROUPS) {
+        float2 v[U];
+        float4 o[U];
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+            const int s = s0 + j * GROUPS;
+            if (s < se) {
+                v[j] = *reinterpret_cast<const float2*>(ml + s * 2);
+                o[j] = *reinterpret_cast<const float4*>(po + (size_t)s * HD + c * 4);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < U; ++j)
+            if (s0 + j * GROUPS < se) take(v[j], o[j]);
     }
     acc_s[g][c] = num;
     if (c == 0) den_s[g] = den;

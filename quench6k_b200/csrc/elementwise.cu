@@ -63,18 +63,26 @@ __global__ void __launch_bounds__(256) rmsnorm_reg_kernel(float* x, const float*
     __shared__ float red[32];
     const int r = blockIdx.x, nv = D >> 2;
     float4* xr = reinterpret_cast<float4*>(x + (size_t)(rows ? rows[r] : r) * D);
-    float4 v[V4];
+    float4 v[V4], g[V4];
     float ss = 0.0f;
 #pragma unroll
     for (int i = 0; i < V4; ++i) {
         const int c = threadIdx.x + 256 * i;
         if (c < nv) {
             v[i] = xr[c];
+            g[i] = reinterpret_cast<const float4*>(w)[c];
             if (add) {
-                float4 a = reinterpret_cast<const float4*>(add + (size_t)r * D)[c];
-                for (int s = 1; s < add_splits; ++s) {
-                    const float4 b = reinterpret_cast<const float4*>(add + s * add_stride + (size_t)r * D)[c];
-                    a.x += b.x, a.y += b.y, a.z += b.z, a.w += b.w;
+                // the slices are fetched eight at a time (independent loads) and added in their order
+                const float4* ar = reinterpret_cast<const float4*>(add + (size_t)r * D) + c;
+                float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int s0 = 0; s0 < add_splits; s0 += 8) {
+                    float4 b[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (s0 + j < add_splits) b[j] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(ar) + (size_t)(s0 + j) * add_stride);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (s0 + j < add_splits) a.x += b[j].x, a.y += b[j].y, a.z += b[j].z, a.w += b[j].w;
                 }
                 v[i].x += a.x, v[i].y += a.y, v[i].z += a.z, v[i].w += a.w;
                 xr[c] = v[i];
@@ -88,10 +96,9 @@ __global__ void __launch_bounds__(256) rmsnorm_reg_kernel(float* x, const float*
     for (int i = 0; i < V4; ++i) {
         const int c = threadIdx.x + 256 * i;
         if (c < nv) {
-            const float4 g = reinterpret_cast<const float4*>(w)[c];
             T* o = out + (size_t)r * D + 4 * c;
-            o[0] = from_f32<T>(v[i].x * inv * g.x), o[1] = from_f32<T>(v[i].y * inv * g.y);
-            o[2] = from_f32<T>(v[i].z * inv * g.z), o[3] = from_f32<T>(v[i].w * inv * g.w);
+            o[0] = from_f32<T>(v[i].x * inv * g[i].x), o[1] = from_f32<T>(v[i].y * inv * g[i].y);
+            o[2] = from_f32<T>(v[i].z * inv * g[i].z), o[3] = from_f32<T>(v[i].w * inv * g[i].w);
         }
     }
 }

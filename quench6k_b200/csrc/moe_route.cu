@@ -167,11 +167,14 @@ __global__ void __launch_bounds__(512) router_small_kernel(const __nv_bfloat16* 
     // pairs sorted by expert (stable): tiles of one expert run side by side and share its weights in L2
     __syncthreads();
     const int pairs = T_ * k;
+    int* sel_s = reinterpret_cast<int*>(sc);      // the scores are done with: T_ * k <= 16 * E ints fit
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) sel_s[p] = sel_e[p];
+    __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
-        const int e = sel_e[p];
+        const int e = sel_s[p];
         int rank = 0;
         for (int q = 0; q < pairs; ++q) {
-            const int eq = sel_e[q];
+            const int eq = sel_s[q];
             rank += (eq < e) || (eq == e && q < p);
         }
         order[rank] = p;

@@ -71,7 +71,29 @@ __global__ void __launch_bounds__(256) qk_prep_warp_kernel(const float* qkv, int
     constexpr int hd = EPL * 32, half = hd / 2;
     __shared__ float rot_cos[half], rot_sin[half];
     const int t = blockIdx.x, h = blockIdx.y * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    const bool valid = h < heads, is_q = h < Hq;
+    const int kh = h - Hq;
+    const bool writes_kv = valid && !is_q;
+    // everything that does not depend on another load goes out first: the position, the request, this
+    // head's slices of q or k and of v; then the page (position and request) and the angles (position)
     const int pos = positions[t];
+    const int req = writes_kv ? req_of_token[t] : 0;
+    const float* src = qkv + (size_t)t * ld + (size_t)(valid ? h : 0) * hd;           // q heads then k heads are contiguous in a row
+    const float* vsrc = qkv + (size_t)t * ld + (size_t)(Hq + Hkv + (writes_kv ? kh : 0)) * hd;
+    float x[EPL], v[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+        x[i] = valid ? src[lane + 32 * i] : 0.0f;
+        v[i] = writes_kv ? vsrc[lane + 32 * i] : 0.0f;
+    }
+    for (int s = 1; s < splits; ++s) {                                               // split-K partials, in order
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+            if (valid) x[i] += src[s * split_stride + lane + 32 * i];
+            if (writes_kv) v[i] += vsrc[s * split_stride + lane + 32 * i];
+        }
+    }
+    const int page = writes_kv ? block_table[(size_t)req * max_blocks + pos / page_size] : -1;
     if (rope) {
         // the angles depend on the position and the dimension only: once per block, not once per head
         for (int d = threadIdx.x; d < half; d += blockDim.x) {
@@ -80,16 +102,10 @@ __global__ void __launch_bounds__(256) qk_prep_warp_kernel(const float* qkv, int
         }
         __syncthreads();
     }
-    if (h >= heads) return;
-    const bool is_q = h < Hq;
-    const float* src = qkv + (size_t)t * ld + (size_t)h * hd;           // q heads then k heads are contiguous in a row
-    float x[EPL], ss = 0.0f;
+    if (!valid) return;
+    float ss = 0.0f;
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) {
-        x[i] = src[lane + 32 * i];
-        for (int s = 1; s < splits; ++s) x[i] += src[s * split_stride + lane + 32 * i];     // split-K partials, in order
-        ss = fmaf(x[i], x[i], ss);
-    }
+    for (int i = 0; i < EPL; ++i) ss = fmaf(x[i], x[i], ss);
     const float* nw = is_q ? q_norm : k_norm;
     if (nw) {
         const float inv = rsqrtf(warp_sum(ss) / (float)hd + eps);
@@ -111,17 +127,12 @@ __global__ void __launch_bounds__(256) qk_prep_warp_kernel(const float* qkv, int
 #pragma unroll
         for (int i = 0; i < EPL; ++i) dst[lane + 32 * i] = from_f32<T>(x[i]);
     } else {
-        const int kh = h - Hq;
-        const int page = block_table[(size_t)req_of_token[t] * max_blocks + pos / page_size];
         if (page < 0) return;
         const size_t row = (((size_t)kh * num_pages + page) * page_size + pos % page_size) * hd;
-        const float* vsrc = qkv + (size_t)t * ld + (size_t)(Hq + Hkv + kh) * hd;
 #pragma unroll
         for (int i = 0; i < EPL; ++i) {
-            float v = vsrc[lane + 32 * i];
-            for (int s = 1; s < splits; ++s) v += vsrc[s * split_stride + lane + 32 * i];
             k_pages[row + lane + 32 * i] = from_f32<T>(x[i]);
-            v_pages[row + lane + 32 * i] = from_f32<T>(v);
+            v_pages[row + lane + 32 * i] = from_f32<T>(v[i]);
         }
     }
 }

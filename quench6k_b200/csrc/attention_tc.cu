@@ -7,20 +7,21 @@
 // probabilities rounded to bfloat16 before they are summed, the sink added to the denominator at
 // the end (:505-526).  The reference computes it with mma.sync tiles of 64 or 128 rows; here:
 //
-// A CTA takes one tile of up to 128 query rows (row = token_in_tile * G + head_in_group, one
-// request, one KV head) and walks key tiles of 128 keys.
+// A CTA takes up to 256 query rows of one request and one KV head as two halves of 128 (row =
+// token_in_half * G + head_in_group) and walks key tiles of 128 keys, which both halves share.
 //   warp 0      producers: one lane brings the K tiles, another the V tiles, as TMA boxes
 //               [page rows x 64] into rings of three and two tiles ([2 column halves][128 keys]
 //               [128 bytes], 128-byte swizzle; keys without a page are zero-filled through an
-//               out-of-range coordinate); a K tile is free again as soon as its scores exist
-//   warp 1      one thread issues the MMAs: S_i = Q K_i^T (8 x K=16, both operands K-major) into one
-//               of two S buffers in tensor memory, one tile ahead of the softmax; then, when P_i is
-//               in shared memory, O += P_i V_i (8 x K=16, V as an MN-major operand)
-//   warps 2-5   softmax: one thread per query row reads its row of S from tensor memory
-//               (tcgen05.ld, no shuffles), keeps the running max and sum, rescales O in tensor
-//               memory when the max has grown by more than 2^8 (tcgen05.ld / tcgen05.st), writes P as bfloat16 into shared
-//               memory in the K-major swizzled layout the MMA reads, and finally normalises O
-// Tensor memory: S0 at columns 0..127, S1 at 128..255, O at 256..383.
+//               out-of-range coordinate)
+//   warp 1      one thread issues the MMAs, for each half in turn: S_h = Q_h K_i^T (8 x K=16, both
+//               operands K-major in shared memory) and, when P_h is in tensor memory, O_h += P_h V_i
+//               (8 x K=16, P as the operand from tensor memory, V as an MN-major operand)
+//   warps 2-5   softmax of half 0, warps 6-9 of half 1: one thread per query row reads its row of S
+//               from tensor memory (tcgen05.ld, no shuffles), keeps the running max and sum, rescales
+//               O in tensor memory when the max has grown by more than 2^8, writes P as bfloat16
+//               into tensor memory over the scores (tcgen05.st), and finally normalises O.  While one
+//               half's softmax runs, the other half's products keep the tensor pipe busy.
+// Tensor memory: S_0 (and P_0) at columns 0..127, S_1 at 128..255, O_0 at 256..383, O_1 at 384..511.
 // Every wait on an mbarrier is bounded and records a code in a status word when it runs out.
 #include <map>
 #include <tuple>
@@ -142,42 +143,72 @@ __device__ __forceinline__ float ex2_approx(float x) {
 // Byte offset of 16-byte chunk c (0..15) of row r in a [2 halves][128 rows][128 bytes] swizzled tile.
 __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)((c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)); }
 
-__global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                                                           const __grid_constant__ CUtensorMap tm_k_run,
-                                                           const __grid_constant__ CUtensorMap tm_v_run, const TcAttnParams p) {
+// O += P V with P read from tensor memory (lanes = query rows, two keys per 32-bit column).
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %6, %7, %8}, p;\n\t}" ::"r"(tmem_d),
+        "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]),
+        "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+        : "memory");
+}
+
+constexpr int TC_THREADS = 320;
+
+__global__ void __launch_bounds__(TC_THREADS) attention_tc_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                                                                  const __grid_constant__ CUtensorMap tm_k_run,
+                                                                  const __grid_constant__ CUtensorMap tm_v_run, const TcAttnParams p) {
     pdl_enter();
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    // [Q][P][K0][K1][K2][V0][V1], each a [2][128][128 B] tile of 32 KB: K is free again as soon as
-    // its scores are computed and runs three tiles deep, V waits for the softmax and runs two deep
-    const uint32_t q_s = smem_u32(smem), p_s = q_s + TILE_BYTES, k_s = p_s + TILE_BYTES, v_s = k_s + KS * TILE_BYTES;
-    __shared__ __align__(8) uint64_t bars[16];
+    // [Q of half 0][Q of half 1][K0][K1][K2][V0][V1], each a [2][128][128 B] tile of 32 KB
+    const uint32_t q_s = smem_u32(smem), k_s = q_s + 2 * TILE_BYTES, v_s = k_s + KS * TILE_BYTES;
+    __shared__ __align__(8) uint64_t bars[20];
     __shared__ uint32_t tmem_slot;
     const uint32_t k_full0 = smem_u32(&bars[0]), k_empty0 = smem_u32(&bars[3]), v_full0 = smem_u32(&bars[6]), v_empty0 = smem_u32(&bars[8]);
-    const uint32_t s_full0 = smem_u32(&bars[10]), p_full = smem_u32(&bars[12]), pv_done = smem_u32(&bars[13]), q_full = smem_u32(&bars[14]);
+    const uint32_t s_full0 = smem_u32(&bars[10]), p_full0 = smem_u32(&bars[12]), pv_done0 = smem_u32(&bars[14]), q_full0 = smem_u32(&bars[16]);
 
     const int tile = gridDim.x - 1 - blockIdx.x, kh = blockIdx.y;      // later tiles see more keys: start them first
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int G = p.G;
+    const int G = p.G, TPH = BM / G;                                   // tokens per half
     const int tok0 = p.tile_tok0[tile], ntok = p.tile_ntok[tile];
     const int pos_first = p.positions[tok0], pos_last = pos_first + ntok - 1;
     const int* bt = p.block_table + (size_t)p.req_of_token[tok0] * p.max_blocks;
+    // the two halves: their tokens, positions and ranges of key tiles (half 1 may be empty)
+    int nt_h[2], pf[2], pl[2], first_h[2], end_h[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        nt_h[h] = h == 0 ? min(ntok, TPH) : max(0, ntok - TPH);
+        pf[h] = pos_first + h * TPH;
+        pl[h] = pf[h] + nt_h[h] - 1;
+        const int lo = p.window > 0 ? max(0, pf[h] - p.window + 1) : 0;
+        first_h[h] = nt_h[h] > 0 ? lo / BN : 0;
+        end_h[h] = nt_h[h] > 0 ? pl[h] / BN + 1 : 0;
+    }
     const int k_lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
-    const int first_tile = k_lo / BN, n_tiles = pos_last / BN + 1 - first_tile;
+    const int u_first = first_h[0], u_end = max(end_h[0], end_h[1]), n_union = u_end - u_first;
+    auto active = [&](int h, int i) { return i >= first_h[h] && i < end_h[h]; };
 
     if (tid == 0) {
         for (int s = 0; s < KS; ++s) {
             mbar_init(k_full0 + 8 * s, 1);
             mbar_init(k_empty0 + 8 * s, 1);
         }
-        for (int s = 0; s < VS; ++s) {
+        for (int s = 0; s < 2; ++s) {
             mbar_init(v_full0 + 8 * s, 1);
             mbar_init(v_empty0 + 8 * s, 1);
             mbar_init(s_full0 + 8 * s, 1);
+            mbar_init(p_full0 + 8 * s, 128);
+            mbar_init(pv_done0 + 8 * s, 1);
+            mbar_init(q_full0 + 8 * s, 128);
         }
-        mbar_init(p_full, 128);
-        mbar_init(pv_done, 1);
-        mbar_init(q_full, 128);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_v) : "memory");
@@ -192,7 +223,6 @@ __global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
-    const uint32_t tmem_o = tmem + 256;
 
     if (warp == 0) {
         // ---- producers: lane 0 brings the K tiles, lane 1 the V tiles (each at its ring's pace)
@@ -203,7 +233,7 @@ __global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant
             const CUtensorMap* map = is_k ? &tm_k : &tm_v;
             const CUtensorMap* map_run = is_k ? &tm_k_run : &tm_v_run;
             constexpr int RUN = 64;                                      // keys per run box
-            for (int i = 0; i < n_tiles; ++i) {
+            for (int i = 0; i < n_union; ++i) {
                 const int s = i % ring;
                 if (!mbar_wait(empty0 + 8 * s, ((i / ring) & 1) ^ 1)) {
                     atomicExch(&g_attn_tc_status, 1);
@@ -211,7 +241,7 @@ __global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant
                 }
                 const uint32_t fb = full0 + 8 * s;
                 mbar_expect_tx(fb, TILE_BYTES);
-                const int j0 = (first_tile + i) * BN;
+                const int j0 = (u_first + i) * BN;
                 const uint32_t dst = base + s * TILE_BYTES;
                 // pages with consecutive numbers are contiguous for one head (head-major pools): where the
                 // pages of 64 keys form such a run, each half comes in as one box instead of one per page
@@ -245,100 +275,129 @@ __global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant
             }
         }
     } else if (warp == 1) {
-        // ---- MMA issuer
+        // ---- MMA issuer.  For key tile r: O_h += P_h V_r as soon as half h's probabilities are in
+        // tensor memory, then at once S_h = Q_h K_(r+1)^T into the columns P_h has just been read
+        // from (the tensor pipe runs its instructions in the order of issue), half 0 and half 1 in
+        // turn: while one half's softmax runs, the other half's products do.
         if (lane == 0) {
             constexpr uint32_t idesc_s = idesc_128x128(false), idesc_o = idesc_128x128(true);
-            bool ok = mbar_wait(q_full, 0);
-            if (!ok) atomicExch(&g_attn_tc_status, 2);
-            auto issue_s = [&](int i) -> bool {
-                const int ks = i % KS, sb = i & 1;
-                if (!mbar_wait(k_full0 + 8 * ks, (i / KS) & 1)) {
-                    atomicExch(&g_attn_tc_status, 3);
-                    return false;
+            int pv_cnt[2] = {0, 0};
+            bool q_ready[2] = {false, false}, ok = true;
+            auto issue_qk = [&](int h, int r) {
+                if (!q_ready[h]) {
+                    if (!mbar_wait(q_full0 + 8 * h, 0)) {
+                        atomicExch(&g_attn_tc_status, 2);
+                        ok = false;
+                        return;
+                    }
+                    q_ready[h] = true;
+                    tc_fence_after();
                 }
-                tc_fence_after();
-                const uint32_t k_src = k_s + ks * TILE_BYTES;
+                const uint32_t k_src = k_s + (r % KS) * TILE_BYTES, q_src = q_s + h * TILE_BYTES;
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
                     const uint32_t off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-                    umma(tmem + sb * BN, desc_k_major(q_s + off), desc_k_major(k_src + off), idesc_s, k != 0);
+                    umma(tmem + h * BN, desc_k_major(q_src + off), desc_k_major(k_src + off), idesc_s, k != 0);
                 }
-                umma_commit(k_empty0 + 8 * ks);                     // the K tile is free once its scores exist
-                umma_commit(s_full0 + 8 * sb);
-                return true;
+                umma_commit(s_full0 + 8 * h);
             };
-            if (ok) ok = issue_s(0);
-            for (int i = 0; i < n_tiles && ok; ++i) {
-                if (i + 1 < n_tiles) ok = issue_s(i + 1);           // one tile ahead of the softmax
-                if (!ok) break;
-                const int vs = i % VS;
-                if (!mbar_wait(p_full, i & 1) || !mbar_wait(v_full0 + 8 * vs, (i / VS) & 1)) {
-                    atomicExch(&g_attn_tc_status, 4);
+            if (n_union > 0) {
+                if (!mbar_wait(k_full0, 0)) {
+                    atomicExch(&g_attn_tc_status, 3);
+                    ok = false;
+                }
+                tc_fence_after();
+                for (int h = 0; h < 2 && ok; ++h)
+                    if (active(h, u_first)) issue_qk(h, 0);
+                if (ok) umma_commit(k_empty0);
+            }
+            for (int r = 0; r < n_union && ok; ++r) {
+                const int i = u_first + r, vs = r % VS;
+                const bool next = r + 1 < n_union;
+                if (!mbar_wait(v_full0 + 8 * vs, (r / VS) & 1) || (next && !mbar_wait(k_full0 + 8 * ((r + 1) % KS), ((r + 1) / KS) & 1))) {
+                    atomicExch(&g_attn_tc_status, 3);
                     break;
                 }
                 tc_fence_after();
                 const uint32_t v_src = v_s + vs * TILE_BYTES;
+                for (int h = 0; h < 2 && ok; ++h) {
+                    if (active(h, i)) {
+                        if (!mbar_wait(p_full0 + 8 * h, pv_cnt[h] & 1)) {
+                            atomicExch(&g_attn_tc_status, 4);
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
 #pragma unroll
-                for (int k = 0; k < BN / 16; ++k) {
-                    // A: P, K-major over the keys; B: V, MN-major, 16 keys = 2048 bytes per step
-                    const uint32_t a_off = (k >> 2) * HALF_BYTES + (k & 3) * 32;
-                    umma(tmem_o, desc_k_major(p_s + a_off), desc_mn_major(v_src + k * 2048), idesc_o, (i | k) != 0);
+                        for (int k = 0; k < BN / 16; ++k)     // A: 16 keys = 8 columns of P; B: V, MN-major, 16 keys = 2048 bytes
+                            umma_ts(tmem + 256 + h * HD, tmem + h * BN + k * 8, desc_mn_major(v_src + k * 2048), idesc_o, (pv_cnt[h] | k) != 0);
+                        umma_commit(pv_done0 + 8 * h);
+                        ++pv_cnt[h];
+                    }
+                    if (next && active(h, i + 1)) issue_qk(h, r + 1);
                 }
+                if (!ok) break;
                 umma_commit(v_empty0 + 8 * vs);
-                umma_commit(pv_done);
+                if (next) umma_commit(k_empty0 + 8 * ((r + 1) % KS));
             }
         }
     } else {
-        // ---- softmax, correction, epilogue: thread = query row
-        const int quarter = warp & 3, row = quarter * 32 + lane, st = tid - 64;
+        // ---- softmax, correction, epilogue: two warpgroups, one per half; thread = query row
+        const int h = (warp - 2) >> 2;
+        const int quarter = warp & 3, row = quarter * 32 + lane, st = tid - 64 - 128 * h;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-        // Q tile (zero rows past the tile's tokens), by cp.async into the swizzled layout
+        const uint32_t s_addr = tmem + lane_base + h * BN, o_addr = tmem + lane_base + 256 + h * HD;
+        const int ntk = nt_h[h], tokh = tok0 + h * TPH;
+        // Q of this half (zero rows past its tokens), by cp.async into the swizzled layout
         for (int idx = st; idx < BM * 16; idx += 128) {
             const int r = idx >> 4, c = idx & 15, tt = r / G, hg = r % G;
-            const bool valid = tt < ntok;
-            const __nv_bfloat16* src = p.q + ((size_t)(tok0 + (valid ? tt : 0)) * p.Hq + kh * G + hg) * HD + c * 8;
-            cp_async16(q_s + swz(r, c), src, valid);
+            const bool valid = tt < ntk;
+            const __nv_bfloat16* src = p.q + ((size_t)(valid ? tokh + tt : tok0) * p.Hq + kh * G + hg) * HD + c * 8;
+            cp_async16(q_s + h * TILE_BYTES + swz(r, c), src, valid);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
         asm volatile("cp.async.wait_group 0;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_arrive(q_full);
+        mbar_arrive(q_full0 + 8 * h);
 
         const int tt = row / G, hg = row % G;
-        const bool row_valid = tt < ntok;
-        const int pos = pos_first + tt;
+        const bool row_valid = tt < ntk;
+        const int pos = pf[h] + tt;
         const int lim_hi = row_valid ? pos : -1, lim_lo = p.window > 0 ? pos - p.window + 1 : 0;
+        const int n_mine = end_h[h] - first_h[h];
         float m = -INFINITY, l = 0.0f;
         bool ok = true;
-        for (int i = 0; i < n_tiles; ++i) {
-            const int sb = i & 1, j0 = (first_tile + i) * BN;
-            if (!mbar_wait(s_full0 + 8 * sb, (i >> 1) & 1)) {
+        for (int t = 0; t < n_mine; ++t) {
+            const int i = first_h[h] + t, j0 = i * BN;
+            // S of this tile exists; the commit that says so came after every earlier product of the
+            // issuer, so O holds the previous tile's sum and the previous P has been read
+            if (!mbar_wait(s_full0 + 8 * h, t & 1)) {
                 if (lane == 0) atomicExch(&g_attn_tc_status, 5);
                 ok = false;
                 break;
             }
             tc_fence_after();
-            const uint32_t s_addr = tmem + lane_base + sb * BN;
-            // tiles that every row of the CTA sees whole (below the diagonal, inside the window) need no mask
-            const bool whole = j0 + BN - 1 <= pos_first && (p.window == 0 || j0 >= pos_last - p.window + 1);
-            // pass 1: the row's maximum over this tile, 32 scores at a time (loops kept rolled: the
-            // code of a tile has to stay in the instruction cache)
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                float v[32];
-                tmem_ld32(s_addr + c * 32, v);
-                if (whole) {
+            // tiles that every row of the half sees whole (below the diagonal, inside the window) need no mask
+            const bool whole = j0 + BN - 1 <= pf[h] && (p.window == 0 || j0 >= pl[h] - p.window + 1);
+            // the row's 128 scores come into registers with one wait; masked ones become -inf
+            float v[BN];
 #pragma unroll
-                    for (int x = 0; x < 32; ++x) mx = fmaxf(mx, v[x]);
-                } else {
+            for (int c = 0; c < BN / 32; ++c) tmem_ld32_issue(s_addr + c * 32, v + c * 32);
+            tmem_ld_wait();
+            if (!whole) {
 #pragma unroll
-                    for (int x = 0; x < 32; ++x) {
-                        const int j = j0 + c * 32 + x;
-                        if (j <= lim_hi && j >= lim_lo) mx = fmaxf(mx, v[x]);
-                    }
+                for (int x = 0; x < BN; ++x) {
+                    const int j = j0 + x;
+                    v[x] = (j <= lim_hi && j >= lim_lo) ? v[x] : -INFINITY;
                 }
             }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int x = 0; x < BN; x += 4) {
+                mx4[0] = fmaxf(mx4[0], v[x]), mx4[1] = fmaxf(mx4[1], v[x + 1]);
+                mx4[2] = fmaxf(mx4[2], v[x + 2]), mx4[3] = fmaxf(mx4[3], v[x + 3]);
+            }
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             mx *= p.scale_log2;                          // the scale is positive: max commutes with it
             // The reference point of the exponentials follows the running maximum lazily: it moves
             // only when the maximum has grown by more than 2^8, so O in tensor memory is rescaled
@@ -348,81 +407,67 @@ __global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant
                 ref = fmaxf(m, mx);
                 corr = (m == -INFINITY) ? 1.0f : exp2f(m - ref);
             }
-            // P and O of the previous tile must be consumed before either is touched
-            if (i > 0 && !mbar_wait(pv_done, (i - 1) & 1)) {
-                if (lane == 0) atomicExch(&g_attn_tc_status, 6);
-                ok = false;
-                break;
-            }
-            tc_fence_after();
-            if (i > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
+            if (t > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll 1
                 for (int c = 0; c < HD / 32; ++c) {
                     float o[32];
-                    tmem_ld32(tmem_o + lane_base + c * 32, o);
+                    tmem_ld32(o_addr + c * 32, o);
 #pragma unroll
                     for (int x = 0; x < 32; ++x) o[x] *= corr;
-                    tmem_st32(tmem_o + lane_base + c * 32, o);
+                    tmem_st32(o_addr + c * 32, o);
                 }
-                tmem_st_wait();
             }
-            // pass 2: probabilities p = 2^(s * scale - ref), rounded to bfloat16 before they are summed,
-            // into shared memory; a masked score counts as -inf and gives 0; so does a row without any
-            // key yet (ref = -inf)
+            // probabilities p = 2^(s * scale - ref), rounded to bfloat16 before they are summed, into
+            // tensor memory over the scores they came from (two keys per column: the 32 keys of chunk c
+            // go to columns 16c..16c+15); a masked score is -inf and gives 0; so does a row without
+            // any key yet (ref = -inf)
             const float neg_ref = ref == -INFINITY ? 0.0f : -ref;
-            float sum = 0.0f;
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                float v[32];
-                tmem_ld32(s_addr + c * 32, v);
-                if (!whole) {
+            float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-                    for (int x = 0; x < 32; ++x) {
-                        const int j = j0 + c * 32 + x;
-                        v[x] = (j <= lim_hi && j >= lim_lo) ? v[x] : -INFINITY;
-                    }
-                }
+            for (int c = 0; c < BN / 32; ++c) {
                 uint32_t packed[16];
 #pragma unroll
                 for (int x = 0; x < 32; x += 2) {
-                    const float p0 = ex2_approx(fmaf(v[x], p.scale_log2, neg_ref));
-                    const float p1 = ex2_approx(fmaf(v[x + 1], p.scale_log2, neg_ref));
+                    const float p0 = ex2_approx(fmaf(v[c * 32 + x], p.scale_log2, neg_ref));
+                    const float p1 = ex2_approx(fmaf(v[c * 32 + x + 1], p.scale_log2, neg_ref));
                     const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
                     const uint32_t bits = *reinterpret_cast<const uint32_t*>(&pb);
-                    sum += __uint_as_float(bits << 16) + __uint_as_float(bits & 0xffff0000u);
+                    sum4[(x >> 1) & 1] += __uint_as_float(bits << 16);
+                    sum4[2 + ((x >> 1) & 1)] += __uint_as_float(bits & 0xffff0000u);
                     packed[x >> 1] = bits;
                 }
-#pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4)           // 32 keys = 4 chunks of 16 bytes
-                    *reinterpret_cast<uint4*>(smem + (p_s - q_s) + swz(row, c * 4 + q4)) =
-                        make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+                tmem_st16(s_addr + c * 16, packed);
             }
+            const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             l = l * corr + sum;
             m = ref;
-            if (i == n_tiles - 1 && (pos_last + 1) % BN != 0) {
-                // the last page came in whole: clear the V rows past the last key (0 * stale NaN)
-                if (!mbar_wait(v_full0 + 8 * (i % VS), (i / VS) & 1)) {
+            if (i == u_end - 1 && (pos_last + 1) % BN != 0) {
+                // the last page came in whole: clear the V rows past the last key (0 * stale NaN); both
+                // halves may do so, with the same zeros, before either lets its product start
+                const int r = i - u_first;
+                if (!mbar_wait(v_full0 + 8 * (r % VS), (r / VS) & 1)) {
                     if (lane == 0) atomicExch(&g_attn_tc_status, 7);
                     ok = false;
                     break;
                 }
-                const uint32_t v_off = (v_s - q_s) + (i % VS) * TILE_BYTES;
+                const uint32_t v_off = (v_s - q_s) + (r % VS) * TILE_BYTES;
                 const int r0 = pos_last + 1 - j0;
                 for (int idx = r0 * 16 + st; idx < BN * 16; idx += 128)
                     *reinterpret_cast<uint4*>(smem + v_off + swz(idx >> 4, idx & 15)) = make_uint4(0, 0, 0, 0);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(p_full);
+            mbar_arrive(p_full0 + 8 * h);
         }
-        if (ok && n_tiles > 0) {
-            if (!mbar_wait(pv_done, (n_tiles - 1) & 1)) {
+        if (ok && n_mine > 0) {
+            if (!mbar_wait(pv_done0 + 8 * h, (n_mine - 1) & 1)) {
                 if (lane == 0) atomicExch(&g_attn_tc_status, 8);
                 ok = false;
             }
             tc_fence_after();
         }
-        if (ok) {
+        if (ok && n_mine > 0) {
             // every lane takes part in the aligned tensor-memory loads; only rows of real tokens store
             float osc = 1.0f, den = l;
             if (p.sinks && row_valid) {
@@ -431,11 +476,11 @@ __global__ void __launch_bounds__(192) attention_tc_kernel(const __grid_constant
                 den = l * osc + exp2f(sk - Mx);
             }
             const float inv = row_valid ? osc / den : 0.0f;
-            __nv_bfloat16* dst = p.out + ((size_t)(tok0 + (row_valid ? tt : 0)) * p.Hq + kh * G + hg) * HD;
+            __nv_bfloat16* dst = p.out + ((size_t)(row_valid ? tokh + tt : tok0) * p.Hq + kh * G + hg) * HD;
 #pragma unroll 1
             for (int c = 0; c < HD / 32; ++c) {
                 float o[32];
-                tmem_ld32(tmem_o + lane_base + c * 32, o);
+                tmem_ld32(o_addr + c * 32, o);
                 uint32_t packed[16];
 #pragma unroll
                 for (int x = 0; x < 32; x += 2) {
@@ -482,14 +527,17 @@ Q6K_API int q6k_attention_tc_status() {
     return v;
 }
 
-// Whether the kernel covers these sizes: head size 128, up to 128 rows per tile (G <= 128), pages
+// Tokens a tile of this kernel may hold: two halves of 128 // G tokens.
+Q6K_API int q6k_attention_tc_tile_tokens(int G) { return G >= 1 && G <= BM ? 2 * (BM / G) : 0; }
+
+// Whether the kernel covers these sizes: head size 128, up to 128 rows per half (G <= 128), pages
 // of 8, 16, 32, 64 or 128 keys.
 Q6K_API int q6k_attention_tc_supported(int hd, int G, int page_size) {
     return hd == HD && G >= 1 && G <= BM && page_size >= 8 && page_size <= BN && BN % page_size == 0;
 }
 
-// q: bfloat16 [T, Hq, 128]; pages: bfloat16 [Hkv, num_pages, page_size, 128]; tiles of at most 128 / G
-// tokens (consecutive positions of one request); out: bfloat16 [T, Hq*128].  Every tile reads its whole
+// q: bfloat16 [T, Hq, 128]; pages: bfloat16 [Hkv, num_pages, page_size, 128]; tiles of at most
+// q6k_attention_tc_tile_tokens(G) tokens (consecutive positions of one request); out: bfloat16 [T, Hq*128].  Every tile reads its whole
 // key range (no key splits): the kernel for prompt portions.
 Q6K_API int q6k_attention_tc(const void* q, const void* k_pages, const void* v_pages, long long num_pages, const int* block_table,
                              int max_blocks, int page_size, const int* req_of_token, const int* positions, const int* tile_tok0,
@@ -522,6 +570,6 @@ Q6K_API int q6k_attention_tc(const void* q, const void* k_pages, const void* v_p
             return q6k_check_launch("attention_tc: shared memory attribute");
         configured = true;
     }
-    q6k_launch(attention_tc_kernel, dim3(n_tiles, Hkv), 192, smem, st, tk, tv, tk_run, tv_run, p);
+    q6k_launch(attention_tc_kernel, dim3(n_tiles, Hkv), TC_THREADS, smem, st, tk, tv, tk_run, tv_run, p);
     return q6k_check_launch("attention_tc");
 }

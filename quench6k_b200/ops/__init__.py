@@ -374,12 +374,20 @@ def attention_tc_supported(hd: int, G: int, page_size: int) -> bool:
     return bool(lib.q6k_attention_tc_supported(_i(hd), _i(G), _i(page_size)))
 
 
+def attention_tc_tile_tokens(G: int) -> int:
+    """Tokens a tile of attention_tc may hold (two halves of 128 // G tokens)."""
+    lib = library()
+    lib.q6k_attention_tc_tile_tokens.restype = ctypes.c_int
+    return lib.q6k_attention_tc_tile_tokens(_i(G))
+
+
 def attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                  req_of_token: torch.Tensor, positions: torch.Tensor, tile_tok0: torch.Tensor, tile_ntok: torch.Tensor,
                  window: Optional[int], sinks: Optional[torch.Tensor], scale: Optional[float] = None) -> torch.Tensor:
     """bfloat16 attention for prompt portions with both products on tcgen05 tensor cores
-    (accumulators in tensor memory, K/V pages by TMA).  Head size 128; tiles of at most 128 // G
-    tokens (consecutive positions of one request); each tile reads its whole key range."""
+    (accumulators and probabilities in tensor memory, K/V pages by TMA).  Head size 128; tiles of
+    at most attention_tc_tile_tokens(G) tokens (consecutive positions of one request); each tile
+    reads its whole key range."""
     _need(q, "q", torch.bfloat16)
     T, Hq, hd = q.shape
     _need(k_pages, "k_pages", torch.bfloat16)

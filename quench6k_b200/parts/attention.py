@@ -87,11 +87,13 @@ class Attention(Mixer):
         wide = ctx.max_q_len > max(1, 16 // G) or not ops.attention_mma_supported(self.hd, G, False)
         if not ops.attention_mma_supported(self.hd, G, wide):
             return ops.attention_generic(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, self.window, self.sinks, self.scale)
+        if wide and ops.attention_tc_supported(self.hd, G, cache.page_size):
+            tok0, ntok, n_tiles = ctx.query_tiles(ops.attention_tc_tile_tokens(G))
+            if 2 * n_tiles * self.Hkv >= self._sm_count():
+                # prompt portions with enough tiles for at least half of the SMs: both products on tcgen05, no key splits
+                return ops.attention_tc(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, tok0, ntok, self.window,
+                                        self.sinks, scale=self.scale)
         tok0, ntok, n_tiles = ctx.query_tiles((128 if wide else 16) // G)
-        if wide and ops.attention_tc_supported(self.hd, G, cache.page_size) and n_tiles * self.Hkv >= self._sm_count():
-            # prompt portions with enough tiles to fill the GPU: both products on tcgen05, no key splits
-            return ops.attention_tc(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, tok0, ntok, self.window,
-                                    self.sinks, scale=self.scale)
         # split the keys over CTAs until the GPU is full, and no further: one wave of resident CTAs
         # (a second, partly filled wave would cost as much as a full one)
         span = ctx.max_context if self.window is None else min(ctx.max_context, self.window + ctx.max_q_len)

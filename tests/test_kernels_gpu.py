@@ -430,7 +430,7 @@ def test_attention_tc(Hq, Hkv, ps, window, sinks):
     starts = [n - ql for n, ql in zip(lens, q_lens)]
     ctx = helpers.make_context(q_lens, starts, [tables])
     q = torch.cat([qs[r][starts[r]:] for r in range(len(lens))]).contiguous().to(DEV)
-    tok0, ntok, n_tiles = ctx.query_tiles(128 // G)
+    tok0, ntok, n_tiles = ctx.query_tiles(ops.attention_tc_tile_tokens(G))
     want = torch.cat([refs[r][starts[r]:] for r in range(len(lens))]).reshape(-1, Hq * hd)
     out = ops.attention_tc(q, kp.to(DEV), vp.to(DEV), bt, ctx.req_of_token, ctx.positions, tok0, ntok, window,
                            sk.to(DEV) if sinks else None)

@@ -140,6 +140,20 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
+// 2^x on the FMA pipe for x <= 8: round(x) goes into the exponent, a cubic gives 2^f on [-0.5, 0.5]
+// (relative error 7.5e-5, far below the bfloat16 rounding that follows).  x below -126 counts as
+// -126 (2^-126 instead of 0: nothing a sum or a product can see).  A quarter of a tile's
+// exponentials go this way so that the special-function unit is not the only one that works.
+__device__ __forceinline__ float ex2_poly(float x) {
+    x = fmaxf(x, -126.0f);
+    const float t = x + 12582912.0f;              // 1.5 * 2^23: the integer nearest to x in the low mantissa bits
+    const float f = x - (t - 12582912.0f);
+    float q = fmaf(0.05517157f, f, 0.24261111f);
+    q = fmaf(q, f, 0.69326103f);
+    q = fmaf(q, f, 0.99992806f);
+    return __int_as_float(__float_as_int(q) + (__float_as_int(t) << 23));
+}
+
 // Byte offset of 16-byte chunk c (0..15) of row r in a [2 halves][128 rows][128 bytes] swizzled tile.
 __device__ __forceinline__ uint32_t swz(int r, int c) { return (uint32_t)((c >> 3) * HALF_BYTES + r * 128 + (((c & 7) ^ (r & 7)) << 4)); }
 
@@ -170,10 +184,10 @@ __global__ void __launch_bounds__(TC_THREADS) attention_tc_kernel(const __grid_c
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     // [Q of half 0][Q of half 1][K0][K1][K2][V0][V1], each a [2][128][128 B] tile of 32 KB
     const uint32_t q_s = smem_u32(smem), k_s = q_s + 2 * TILE_BYTES, v_s = k_s + KS * TILE_BYTES;
-    __shared__ __align__(8) uint64_t bars[20];
+    __shared__ __align__(8) uint64_t bars[22];
     __shared__ uint32_t tmem_slot;
     const uint32_t k_full0 = smem_u32(&bars[0]), k_empty0 = smem_u32(&bars[3]), v_full0 = smem_u32(&bars[6]), v_empty0 = smem_u32(&bars[8]);
-    const uint32_t s_full0 = smem_u32(&bars[10]), p_full0 = smem_u32(&bars[12]), pv_done0 = smem_u32(&bars[14]), q_full0 = smem_u32(&bars[16]);
+    const uint32_t s_full0 = smem_u32(&bars[10]), p_full0 = smem_u32(&bars[12]), pv_done0 = smem_u32(&bars[14]), q_full0 = smem_u32(&bars[16]), p_full1 = smem_u32(&bars[18]);
 
     const int tile = gridDim.x - 1 - blockIdx.x, kh = blockIdx.y;      // later tiles see more keys: start them first
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -206,6 +220,7 @@ __global__ void __launch_bounds__(TC_THREADS) attention_tc_kernel(const __grid_c
             mbar_init(v_empty0 + 8 * s, 1);
             mbar_init(s_full0 + 8 * s, 1);
             mbar_init(p_full0 + 8 * s, 128);
+            mbar_init(p_full1 + 8 * s, 128);
             mbar_init(pv_done0 + 8 * s, 1);
             mbar_init(q_full0 + 8 * s, 128);
         }
@@ -329,8 +344,17 @@ __global__ void __launch_bounds__(TC_THREADS) attention_tc_kernel(const __grid_c
                         }
                         tc_fence_after();
 #pragma unroll
-                        for (int k = 0; k < BN / 16; ++k)     // A: 16 keys = 8 columns of P; B: V, MN-major, 16 keys = 2048 bytes
+                        for (int k = 0; k < BN / 32; ++k)     // A: 16 keys = 8 columns of P; B: V, MN-major, 16 keys = 2048 bytes
                             umma_ts(tmem + 256 + h * HD, tmem + h * BN + k * 8, desc_mn_major(v_src + k * 2048), idesc_o, (pv_cnt[h] | k) != 0);
+                        if (!mbar_wait(p_full1 + 8 * h, pv_cnt[h] & 1)) {      // the second 64 keys
+                            atomicExch(&g_attn_tc_status, 4);
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+#pragma unroll
+                        for (int k = BN / 32; k < BN / 16; ++k)
+                            umma_ts(tmem + 256 + h * HD, tmem + h * BN + k * 8, desc_mn_major(v_src + k * 2048), idesc_o, 1u);
                         umma_commit(pv_done0 + 8 * h);
                         ++pv_cnt[h];
                     }
@@ -391,13 +415,20 @@ __global__ void __launch_bounds__(TC_THREADS) attention_tc_kernel(const __grid_c
                     v[x] = (j <= lim_hi && j >= lim_lo) ? v[x] : -INFINITY;
                 }
             }
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            float mx16[16];                              // sixteen independent chains, then a tree
 #pragma unroll
-            for (int x = 0; x < BN; x += 4) {
-                mx4[0] = fmaxf(mx4[0], v[x]), mx4[1] = fmaxf(mx4[1], v[x + 1]);
-                mx4[2] = fmaxf(mx4[2], v[x + 2]), mx4[3] = fmaxf(mx4[3], v[x + 3]);
+            for (int x = 0; x < 16; ++x) mx16[x] = fmaxf(v[x], v[x + 16]);
+#pragma unroll
+            for (int y = 32; y < BN; y += 16) {
+#pragma unroll
+                for (int x = 0; x < 16; ++x) mx16[x] = fmaxf(mx16[x], v[y + x]);
             }
-            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+#pragma unroll
+            for (int w = 8; w >= 1; w >>= 1) {
+#pragma unroll
+                for (int x = 0; x < w; ++x) mx16[x] = fmaxf(mx16[x], mx16[x + w]);
+            }
+            float mx = mx16[0];
             mx *= p.scale_log2;                          // the scale is positive: max commutes with it
             // The reference point of the exponentials follows the running maximum lazily: it moves
             // only when the maximum has grown by more than 2^8, so O in tensor memory is rescaled
@@ -422,14 +453,31 @@ __global__ void __launch_bounds__(TC_THREADS) attention_tc_kernel(const __grid_c
             // go to columns 16c..16c+15); a masked score is -inf and gives 0; so does a row without
             // any key yet (ref = -inf)
             const float neg_ref = ref == -INFINITY ? 0.0f : -ref;
+            const bool last_tile_zero = i == u_end - 1 && (pos_last + 1) % BN != 0;
+            auto zero_v_tail = [&]() {
+                // the last page came in whole: clear the V rows past the last key (0 * stale NaN); both
+                // halves may do so, with the same zeros, before either lets its product start
+                const int r = i - u_first;
+                if (!mbar_wait(v_full0 + 8 * (r % VS), (r / VS) & 1)) {
+                    if (lane == 0) atomicExch(&g_attn_tc_status, 7);
+                    ok = false;
+                    return;
+                }
+                const uint32_t v_off = (v_s - q_s) + (r % VS) * TILE_BYTES;
+                const int r0 = pos_last + 1 - j0;
+                for (int idx = r0 * 16 + st; idx < BN * 16; idx += 128)
+                    *reinterpret_cast<uint4*>(smem + v_off + swz(idx >> 4, idx & 15)) = make_uint4(0, 0, 0, 0);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            };
             float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t packed[16];
 #pragma unroll
                 for (int x = 0; x < 32; x += 2) {
-                    const float p0 = ex2_approx(fmaf(v[c * 32 + x], p.scale_log2, neg_ref));
-                    const float p1 = ex2_approx(fmaf(v[c * 32 + x + 1], p.scale_log2, neg_ref));
+                    const float x0 = fmaf(v[c * 32 + x], p.scale_log2, neg_ref), x1 = fmaf(v[c * 32 + x + 1], p.scale_log2, neg_ref);
+                    const bool poly = ((x >> 1) & 3) == 3;          // known at compile time: the loop is unrolled
+                    const float p0 = poly ? ex2_poly(x0) : ex2_approx(x0), p1 = poly ? ex2_poly(x1) : ex2_approx(x1);
                     const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
                     const uint32_t bits = *reinterpret_cast<const uint32_t*>(&pb);
                     sum4[(x >> 1) & 1] += __uint_as_float(bits << 16);
@@ -437,28 +485,24 @@ __global__ void __launch_bounds__(TC_THREADS) attention_tc_kernel(const __grid_c
                     packed[x >> 1] = bits;
                 }
                 tmem_st16(s_addr + c * 16, packed);
+                if (c == 1) {
+                    // the first 64 keys' probabilities are complete: their part of the product may start
+                    if (last_tile_zero) {
+                        zero_v_tail();
+                        if (!ok) break;
+                    }
+                    tmem_st_wait();
+                    tc_fence_before();
+                    mbar_arrive(p_full0 + 8 * h);
+                }
             }
+            if (!ok) break;
             const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
             l = l * corr + sum;
             m = ref;
-            if (i == u_end - 1 && (pos_last + 1) % BN != 0) {
-                // the last page came in whole: clear the V rows past the last key (0 * stale NaN); both
-                // halves may do so, with the same zeros, before either lets its product start
-                const int r = i - u_first;
-                if (!mbar_wait(v_full0 + 8 * (r % VS), (r / VS) & 1)) {
-                    if (lane == 0) atomicExch(&g_attn_tc_status, 7);
-                    ok = false;
-                    break;
-                }
-                const uint32_t v_off = (v_s - q_s) + (r % VS) * TILE_BYTES;
-                const int r0 = pos_last + 1 - j0;
-                for (int idx = r0 * 16 + st; idx < BN * 16; idx += 128)
-                    *reinterpret_cast<uint4*>(smem + v_off + swz(idx >> 4, idx & 15)) = make_uint4(0, 0, 0, 0);
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            }
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(p_full0 + 8 * h);
+            mbar_arrive(p_full1 + 8 * h);
         }
         if (ok && n_mine > 0) {
             if (!mbar_wait(pv_done0 + 8 * h, (n_mine - 1) & 1)) {

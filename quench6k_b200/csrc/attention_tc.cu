@@ -191,23 +191,24 @@ __global__ void __launch_bounds__(TC_THREADS) attention_tc_kernel(const __grid_c
 
     const int tile = gridDim.x - 1 - blockIdx.x, kh = blockIdx.y;      // later tiles see more keys: start them first
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int G = p.G, TPH = BM / G;                                   // tokens per half
-    const int tok0 = p.tile_tok0[tile], ntok = p.tile_ntok[tile];
-    const int pos_first = p.positions[tok0], pos_last = pos_first + ntok - 1;
-    const int* bt = p.block_table + (size_t)p.req_of_token[tok0] * p.max_blocks;
-    // the two halves: their tokens, positions and ranges of key tiles (half 1 may be empty)
-    int nt_h[2], pf[2], pl[2], first_h[2], end_h[2];
+    const int G = p.G;
+    // the two halves: two tiles of one request (their tokens, positions and ranges of key tiles);
+    // the second may be empty.  The K/V stream covers the union of the ranges.
+    const int tok_h0 = p.tile_tok0[2 * tile], tok_h1 = p.tile_tok0[2 * tile + 1];
+    int nt_h[2] = {p.tile_ntok[2 * tile], p.tile_ntok[2 * tile + 1]}, pf[2], pl[2], first_h[2], end_h[2], lo_h[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
-        nt_h[h] = h == 0 ? min(ntok, TPH) : max(0, ntok - TPH);
-        pf[h] = pos_first + h * TPH;
+        pf[h] = nt_h[h] > 0 ? p.positions[h == 0 ? tok_h0 : tok_h1] : 0;
         pl[h] = pf[h] + nt_h[h] - 1;
-        const int lo = p.window > 0 ? max(0, pf[h] - p.window + 1) : 0;
-        first_h[h] = nt_h[h] > 0 ? lo / BN : 0;
+        lo_h[h] = p.window > 0 ? max(0, pf[h] - p.window + 1) : 0;
+        first_h[h] = nt_h[h] > 0 ? lo_h[h] / BN : 0;
         end_h[h] = nt_h[h] > 0 ? pl[h] / BN + 1 : 0;
     }
-    const int k_lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
-    const int u_first = first_h[0], u_end = max(end_h[0], end_h[1]), n_union = u_end - u_first;
+    const int* bt = p.block_table + (size_t)p.req_of_token[tok_h0] * p.max_blocks;
+    const bool two = nt_h[1] > 0;
+    const int pos_last = two ? max(pl[0], pl[1]) : pl[0];
+    const int k_lo = two ? min(lo_h[0], lo_h[1]) : lo_h[0];
+    const int u_first = two ? min(first_h[0], first_h[1]) : first_h[0], u_end = max(end_h[0], end_h[1]), n_union = u_end - u_first;
     auto active = [&](int h, int i) { return i >= first_h[h] && i < end_h[h]; };
 
     if (tid == 0) {
@@ -371,7 +372,7 @@ __global__ void __launch_bounds__(TC_THREADS) attention_tc_kernel(const __grid_c
         const int quarter = warp & 3, row = quarter * 32 + lane, st = tid - 64 - 128 * h;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
         const uint32_t s_addr = tmem + lane_base + h * BN, o_addr = tmem + lane_base + 256 + h * HD;
-        const int ntk = nt_h[h], tokh = tok0 + h * TPH;
+        const int ntk = nt_h[h], tokh = h == 0 ? tok_h0 : tok_h1, tok0 = tok_h0;
         // Q of this half (zero rows past its tokens), by cp.async into the swizzled layout
         for (int idx = st; idx < BM * 16; idx += 128) {
             const int r = idx >> 4, c = idx & 15, tt = r / G, hg = r % G;
@@ -571,8 +572,8 @@ Q6K_API int q6k_attention_tc_status() {
     return v;
 }
 
-// Tokens a tile of this kernel may hold: two halves of 128 // G tokens.
-Q6K_API int q6k_attention_tc_tile_tokens(int G) { return G >= 1 && G <= BM ? 2 * (BM / G) : 0; }
+// Tokens one half of a CTA may hold: 128 // G (128 query rows).
+Q6K_API int q6k_attention_tc_tile_tokens(int G) { return G >= 1 && G <= BM ? BM / G : 0; }
 
 // Whether the kernel covers these sizes: head size 128, up to 128 rows per half (G <= 128), pages
 // of 8, 16, 32, 64 or 128 keys.
@@ -580,8 +581,10 @@ Q6K_API int q6k_attention_tc_supported(int hd, int G, int page_size) {
     return hd == HD && G >= 1 && G <= BM && page_size >= 8 && page_size <= BN && BN % page_size == 0;
 }
 
-// q: bfloat16 [T, Hq, 128]; pages: bfloat16 [Hkv, num_pages, page_size, 128]; tiles of at most
-// q6k_attention_tc_tile_tokens(G) tokens (consecutive positions of one request); out: bfloat16 [T, Hq*128].  Every tile reads its whole
+// q: bfloat16 [T, Hq, 128]; pages: bfloat16 [Hkv, num_pages, page_size, 128]; tile_tok0 / tile_ntok:
+// [n_tiles, 2], for each CTA two tiles of one request, each of at most q6k_attention_tc_tile_tokens(G)
+// tokens at consecutive positions (the second may have no tokens); tiles whose key ranges overlap
+// share the K/V stream (for causal attention without a window: a late tile with an early one); out: bfloat16 [T, Hq*128].  Every tile reads its whole
 // key range (no key splits): the kernel for prompt portions.
 Q6K_API int q6k_attention_tc(const void* q, const void* k_pages, const void* v_pages, long long num_pages, const int* block_table,
                              int max_blocks, int page_size, const int* req_of_token, const int* positions, const int* tile_tok0,

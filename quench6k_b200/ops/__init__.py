@@ -375,7 +375,7 @@ def attention_tc_supported(hd: int, G: int, page_size: int) -> bool:
 
 
 def attention_tc_tile_tokens(G: int) -> int:
-    """Tokens a tile of attention_tc may hold (two halves of 128 // G tokens)."""
+    """Tokens one tile of attention_tc may hold (128 // G: 128 query rows)."""
     lib = library()
     lib.q6k_attention_tc_tile_tokens.restype = ctypes.c_int
     return lib.q6k_attention_tc_tile_tokens(_i(G))
@@ -385,9 +385,10 @@ def attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, 
                  req_of_token: torch.Tensor, positions: torch.Tensor, tile_tok0: torch.Tensor, tile_ntok: torch.Tensor,
                  window: Optional[int], sinks: Optional[torch.Tensor], scale: Optional[float] = None) -> torch.Tensor:
     """bfloat16 attention for prompt portions with both products on tcgen05 tensor cores
-    (accumulators and probabilities in tensor memory, K/V pages by TMA).  Head size 128; tiles of
-    at most attention_tc_tile_tokens(G) tokens (consecutive positions of one request); each tile
-    reads its whole key range."""
+    (accumulators and probabilities in tensor memory, K/V pages by TMA).  Head size 128.
+    tile_tok0 / tile_ntok: [n, 2], two tiles of one request per CTA (StepContext.query_tile_pairs),
+    each of at most attention_tc_tile_tokens(G) tokens at consecutive positions; the second may be
+    empty.  Each tile reads its whole key range; the two share the K/V stream."""
     _need(q, "q", torch.bfloat16)
     T, Hq, hd = q.shape
     _need(k_pages, "k_pages", torch.bfloat16)
@@ -398,12 +399,14 @@ def attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, 
     for nm, t in (("block_table", block_table), ("req_of_token", req_of_token), ("positions", positions),
                   ("tile_tok0", tile_tok0), ("tile_ntok", tile_ntok)):
         _need(t, nm, torch.int32)
+    if tile_tok0.dim() != 2 or tile_tok0.shape[1] != 2 or tile_ntok.shape != tile_tok0.shape:
+        raise KernelError("attention_tc: tile_tok0 and tile_ntok must be [pairs, 2]")
     if sinks is not None:
         _need(sinks, "sinks", torch.float32, (Hq,))
     out = torch.empty((T, Hq * hd), dtype=torch.bfloat16, device=q.device)
     _call("q6k_attention_tc", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ll(num_pages), _ptr(block_table),
           _i(block_table.shape[1]), _i(page_size), _ptr(req_of_token), _ptr(positions), _ptr(tile_tok0), _ptr(tile_ntok),
-          _i(tile_tok0.numel()), _i(window or 0), _ptr(sinks), _f(scale if scale is not None else 1.0 / math.sqrt(hd)), _ptr(out),
+          _i(tile_tok0.shape[0]), _i(window or 0), _ptr(sinks), _f(scale if scale is not None else 1.0 / math.sqrt(hd)), _ptr(out),
           _i(Hq), _i(Hkv), _i(hd), _stream())
     return out
 

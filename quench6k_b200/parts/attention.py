@@ -88,7 +88,7 @@ class Attention(Mixer):
         if not ops.attention_mma_supported(self.hd, G, wide):
             return ops.attention_generic(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, self.window, self.sinks, self.scale)
         if wide and ops.attention_tc_supported(self.hd, G, cache.page_size):
-            tok0, ntok, n_tiles = ctx.query_tiles(ops.attention_tc_tile_tokens(G))
+            tok0, ntok, n_tiles = ctx.query_tile_pairs(ops.attention_tc_tile_tokens(G), zigzag=False)
             if 2 * n_tiles * self.Hkv >= self._sm_count():
                 # prompt portions with enough tiles for at least half of the SMs: both products on tcgen05, no key splits
                 return ops.attention_tc(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, tok0, ntok, self.window,

@@ -430,10 +430,11 @@ def test_attention_tc(Hq, Hkv, ps, window, sinks):
     starts = [n - ql for n, ql in zip(lens, q_lens)]
     ctx = helpers.make_context(q_lens, starts, [tables])
     q = torch.cat([qs[r][starts[r]:] for r in range(len(lens))]).contiguous().to(DEV)
-    tok0, ntok, n_tiles = ctx.query_tiles(ops.attention_tc_tile_tokens(G))
     want = torch.cat([refs[r][starts[r]:] for r in range(len(lens))]).reshape(-1, Hq * hd)
-    out = ops.attention_tc(q, kp.to(DEV), vp.to(DEV), bt, ctx.req_of_token, ctx.positions, tok0, ntok, window,
-                           sk.to(DEV) if sinks else None)
-    assert ops.tc_status() == 0
-    err = (out.double().cpu() - want).abs().max() / want.abs().max()
-    assert err <= 1.5e-2, err
+    for zigzag in (False, True):                 # neighbours together; a late tile with an early one
+        tok0, ntok, n_tiles = ctx.query_tile_pairs(ops.attention_tc_tile_tokens(G), zigzag)
+        out = ops.attention_tc(q, kp.to(DEV), vp.to(DEV), bt, ctx.req_of_token, ctx.positions, tok0, ntok, window,
+                               sk.to(DEV) if sinks else None)
+        assert ops.tc_status() == 0
+        err = (out.double().cpu() - want).abs().max() / want.abs().max()
+        assert err <= 1.5e-2, (zigzag, err)

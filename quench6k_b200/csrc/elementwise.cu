@@ -56,13 +56,18 @@ __global__ void combine_kernel(const float* y, const int* pair_row, const float*
 // The same with the row held in registers (D <= 256 * 4 * V4, D a multiple of 4): one pass over
 // the row, 16-byte loads.  `add_splits` > 1: add is [add_splits, R, D] and its slices are summed in
 // order first (the split-K partials of the product that feeds the residual add).
+// `pair_y`: the routed experts' results come in unsummed, x[t] += sum_s pair_w[t, s] * y[row(t, s)]
+// with row(t, s) = pair_row[t*S + s] (or t*S + s), slots in order: the arithmetic of combine4_kernel
+// below, which this replaces together with one pass over x.
 template <typename T, int V4>
 __global__ void __launch_bounds__(256) rmsnorm_reg_kernel(float* x, const float* add, int add_splits, size_t add_stride, const int* rows,
-                                                          const float* w, float eps, T* out, int D) {
+                                                          const float* w, float eps, T* out, int D, const float* pair_y,
+                                                          const int* pair_row, const float* pair_w, int S) {
     pdl_enter();
     __shared__ float red[32];
     const int r = blockIdx.x, nv = D >> 2;
-    float4* xr = reinterpret_cast<float4*>(x + (size_t)(rows ? rows[r] : r) * D);
+    const int t = rows ? rows[r] : r;
+    float4* xr = reinterpret_cast<float4*>(x + (size_t)t * D);
     float4 v[V4], g[V4];
     float ss = 0.0f;
 #pragma unroll
@@ -83,6 +88,26 @@ __global__ void __launch_bounds__(256) rmsnorm_reg_kernel(float* x, const float*
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
                         if (s0 + j < add_splits) a.x += b[j].x, a.y += b[j].y, a.z += b[j].z, a.w += b[j].w;
+                }
+                v[i].x += a.x, v[i].y += a.y, v[i].z += a.z, v[i].w += a.w;
+                xr[c] = v[i];
+            }
+            if (pair_y) {
+                float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                for (int s0 = 0; s0 < S; s0 += 8) {
+                    float4 b[8];
+                    float ws[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (s0 + j < S) {
+                            const int pr = pair_row ? pair_row[t * S + s0 + j] : t * S + s0 + j;
+                            ws[j] = pair_w[t * S + s0 + j];
+                            b[j] = reinterpret_cast<const float4*>(pair_y + (size_t)pr * D)[c];
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        if (s0 + j < S) a.x = fmaf(ws[j], b[j].x, a.x), a.y = fmaf(ws[j], b[j].y, a.y), a.z = fmaf(ws[j], b[j].z, a.z), a.w = fmaf(ws[j], b[j].w, a.w);
                 }
                 v[i].x += a.x, v[i].y += a.y, v[i].z += a.z, v[i].w += a.w;
                 xr[c] = v[i];
@@ -158,23 +183,30 @@ Q6K_API int q6k_embed(const int* tokens, const void* table, float* h, int T_, in
 
 // add: FP32 [R, D] or null; when given, x[row] += add[r] is stored before normalising (rows must then be null).
 // add_splits > 1: add is [add_splits, R, D] (slices add_stride floats apart), summed in order.
+// pair_y != null: x[t] += sum_s pair_w[t, s] * pair_y[pair_row ? pair_row[t*S + s] : t*S + s] first (t = rows[r] or r);
+// needs the register kernel (D a multiple of 4, at most 4096): q6k_rmsnorm_fuses_pairs tells.
+Q6K_API int q6k_rmsnorm_fuses_pairs(int D) { return D % 4 == 0 && D <= 256 * 4 * 4; }
+
 Q6K_API int q6k_rmsnorm(float* x, const float* add, int add_splits, long long add_stride, const int* rows, const float* w, float eps,
-                        void* out, int R, int D, int dtype, cudaStream_t st) {
+                        void* out, int R, int D, int dtype, const float* pair_y, const int* pair_row, const float* pair_w, int S,
+                        cudaStream_t st) {
     if (R == 0) return 0;
     Q6K_REQUIRE(R > 0 && D > 0, "rmsnorm: bad sizes R=%d D=%d", R, D);
     Q6K_REQUIRE(!(add && rows), "rmsnorm: the fused add takes no row selection");
     Q6K_REQUIRE(add_splits >= 1, "rmsnorm: bad split count %d", add_splits);
+    Q6K_REQUIRE(!pair_y || (pair_w && S > 0), "rmsnorm: weighted rows need their weights");
     const bool vec = D % 4 == 0 && D <= 256 * 4 * 4 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && (!add || ((uintptr_t)add & 15) == 0) &&
-                     (add_stride % 4 == 0);
+                     (add_stride % 4 == 0) && (!pair_y || ((uintptr_t)pair_y & 15) == 0);
     if (vec) {
         const int v4 = (D / 4 + 255) / 256;
         Q6K_DISPATCH(dtype, {
-            if (v4 <= 1) q6k_launch(rmsnorm_reg_kernel<T, 1>, R, 256, 0, st, x, add, add_splits, (size_t)add_stride, rows, w, eps, (T*)out, D);
-            else if (v4 <= 2) q6k_launch(rmsnorm_reg_kernel<T, 2>, R, 256, 0, st, x, add, add_splits, (size_t)add_stride, rows, w, eps, (T*)out, D);
-            else q6k_launch(rmsnorm_reg_kernel<T, 4>, R, 256, 0, st, x, add, add_splits, (size_t)add_stride, rows, w, eps, (T*)out, D);
+            if (v4 <= 1) q6k_launch(rmsnorm_reg_kernel<T, 1>, R, 256, 0, st, x, add, add_splits, (size_t)add_stride, rows, w, eps, (T*)out, D, pair_y, pair_row, pair_w, S);
+            else if (v4 <= 2) q6k_launch(rmsnorm_reg_kernel<T, 2>, R, 256, 0, st, x, add, add_splits, (size_t)add_stride, rows, w, eps, (T*)out, D, pair_y, pair_row, pair_w, S);
+            else q6k_launch(rmsnorm_reg_kernel<T, 4>, R, 256, 0, st, x, add, add_splits, (size_t)add_stride, rows, w, eps, (T*)out, D, pair_y, pair_row, pair_w, S);
         });
         return q6k_check_launch("rmsnorm");
     }
+    Q6K_REQUIRE(!pair_y, "rmsnorm: weighted rows need a width that is a multiple of 4 and at most 4096 (got %d)", D);
     Q6K_REQUIRE(add_splits == 1, "rmsnorm: summing split partials needs a width that is a multiple of 4 and at most 4096 (got %d)", D);
     Q6K_DISPATCH(dtype, q6k_launch(rmsnorm_kernel<T>, R, 256, 0, st, x, add, rows, w, eps, (T*)out, D););
     return q6k_check_launch("rmsnorm");

@@ -87,9 +87,13 @@ class DecoderModel:
         """Runs the tokens of `ctx` through the executed layers; returns FP32 logits
         [len(ctx.logit_rows), vocab] or None when no row is wanted."""
         h = ops.embed(ctx.token_ids, self.embed)
+        pending = None                      # an add into h that a block has left to the next norm
         for p, i in enumerate(self.order):
-            self.blocks[i].forward(h, ctx, caches[p], states[p])
+            pending = self.blocks[i].forward(h, ctx, caches[p], states[p], pending)
         if ctx.n_logit_rows == 0:
             return None
-        xn = self.final_norm.forward(h, rows=ctx.logit_rows)
+        if pending is not None and not self.final_norm.fuses_weighted_rows:
+            pending.apply(h)
+            pending = None
+        xn = self.final_norm.forward(h, rows=ctx.logit_rows, add=pending)
         return linear.matmul(xn, self.head, self.rt)

@@ -85,9 +85,12 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor]
 
 
 def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None,
-            out: Optional[torch.Tensor] = None, add: Optional[torch.Tensor] = None) -> torch.Tensor:
+            out: Optional[torch.Tensor] = None, add: Optional[torch.Tensor] = None, weighted=None) -> torch.Tensor:
     """out[r] = out_dtype(x[row] * rsqrt(mean(x[row]^2) + eps) * w); row = rows[r] if given.
-    With `add` (float32, x's shape), x += add is stored first: the block's residual add, fused."""
+    With `add` (float32, x's shape, or [splits, R, D] partial sums added in order), x += add is
+    stored first: the block's residual add, fused.  With `weighted` = (y [pairs, D], pair_row [T, S]
+    or None, weights [T, S]), x[t] += sum_s weights[t, s] * y[pair_row[t, s] or t*S + s] is stored
+    first: the routed experts' combination (the arithmetic of `combine`)."""
     _need(x, "x", torch.float32)
     D = x.shape[-1]
     _need(w, "w", torch.float32, (D,))
@@ -106,9 +109,29 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype
                 raise KernelError("rmsnorm: the partial sums do not match x")
         elif tuple(add.shape) != tuple(x.shape):
             raise KernelError("rmsnorm: add does not match x")
+    y = pair_row = pair_w = None
+    S = 0
+    if weighted is not None:
+        y, pair_row, pair_w = weighted
+        T, S = pair_w.shape
+        _need(y, "weighted rows", torch.float32)
+        _need(pair_w, "weights", torch.float32)
+        if pair_row is not None:
+            _need(pair_row, "pair_row", torch.int32)
+        if T != x.shape[0] or y.shape[1] != D or y.shape[0] < T * S or (pair_row is not None and pair_row.numel() != T * S):
+            raise KernelError("rmsnorm: the weighted rows do not match x")
+        if not rmsnorm_fuses_weighted(D):
+            combine(y, pair_row, pair_w, x)      # widths the register kernel does not take: two passes
+            y = pair_row = pair_w = None
     _call("q6k_rmsnorm", _ptr(x), _ptr(add), _i(splits), _ll(stride), _ptr(rows), _ptr(w), _f(eps), _ptr(out), _i(R), _i(D),
-          _i(dtype_code(out_dtype)), _stream())
+          _i(dtype_code(out_dtype)), _ptr(y), _ptr(pair_row), _ptr(pair_w), _i(S), _stream())
     return out
+
+
+def rmsnorm_fuses_weighted(D: int) -> bool:
+    lib = library()
+    lib.q6k_rmsnorm_fuses_pairs.restype = ctypes.c_int
+    return bool(lib.q6k_rmsnorm_fuses_pairs(_i(D)))
 
 
 def combine(y: torch.Tensor, pair_row: torch.Tensor, sel_w: torch.Tensor, h: torch.Tensor) -> None:

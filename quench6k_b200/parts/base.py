@@ -80,8 +80,26 @@ class Part:
         self.rt = rt
 
 
+@dataclass
+class WeightedRows:
+    """A residual add that has not been made yet: h[t] += sum_s weights[t, s] * y[pair_row[t, s]]
+    (pair_row None: row t*S + s).  A feed-forward may return it instead of adding, and the next
+    norm (the next block's first, or the model's last) makes the add in the pass that normalises."""
+    y: torch.Tensor                       # FP32 [pairs, D]
+    weights: torch.Tensor                 # FP32 [T, S]
+    pair_row: Optional[torch.Tensor] = None
+
+    def apply(self, h: torch.Tensor) -> None:
+        from .. import ops
+        ops.combine(self.y, self.pair_row, self.weights, h)
+
+
 class Norm(Part):
-    def forward(self, h: torch.Tensor, rows: Optional[torch.Tensor] = None, add: Optional[torch.Tensor] = None) -> torch.Tensor:
+    fuses_weighted_rows = False           # forward(..., add=WeightedRows) is understood
+
+    def forward(self, h: torch.Tensor, rows: Optional[torch.Tensor] = None, add=None) -> torch.Tensor:
+        """Normalised rows of h in the operand dtype.  `add`: FP32 of h's shape, or [slices, T, D]
+        partial sums, or (if fuses_weighted_rows) a WeightedRows: added into h first, in place."""
         raise NotImplementedError
 
 
@@ -106,6 +124,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    defers_add = False                    # forward(..., defer=True) may return a WeightedRows instead of adding
+
     def forward(self, xn, ctx, out: torch.Tensor) -> None:
         raise NotImplementedError
 
@@ -114,7 +134,9 @@ class Block:
     def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, ffn: FeedForward):
         self.norm1, self.mixer, self.norm2, self.ffn = norm1, mixer, norm2, ffn
 
-    def forward(self, h, ctx, cache, state) -> None:
+    def forward(self, h, ctx, cache, state, pending=None):
+        """Runs the block on the stream h in place.  `pending`: an add into h the block before has
+        left to this block's first norm; returns the add this block leaves to the next norm, or None."""
         raise NotImplementedError
 
 

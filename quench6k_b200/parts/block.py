@@ -7,8 +7,14 @@ from .base import Block, register_block
 
 @register_block("prenorm")
 class PreNormBlock(Block):
-    def forward(self, h, ctx, cache, state):
-        xn = self.norm1.forward(h)
+    def forward(self, h, ctx, cache, state, pending=None):
+        if pending is not None and not self.norm1.fuses_weighted_rows:
+            pending.apply(h)
+            pending = None
+        xn = self.norm1.forward(h, add=pending)         # the add the block before left is made here
         delta = self.mixer.forward(xn, ctx, cache, state, h)
         xn = self.norm2.forward(h, add=delta)           # h += delta inside the norm when the mixer returned its result
+        if self.ffn.defers_add:
+            return self.ffn.forward(xn, ctx, h, defer=True)
         self.ffn.forward(xn, ctx, h)
+        return None

@@ -14,7 +14,7 @@ import torch
 from .. import ops
 from ..spec import TensorSpec
 from . import linear
-from .base import FeedForward, register_feed_forward, to_operand
+from .base import FeedForward, WeightedRows, register_feed_forward, to_operand
 
 
 @register_feed_forward("dense")
@@ -69,10 +69,15 @@ class RoutedExperts(FeedForward):
         if self.shared is not None:
             self.shared.bind(lambda n: get("shared_experts." + n), rt)
 
-    def forward(self, xn, ctx, out):
+    defers_add = True
+
+    def forward(self, xn, ctx, out, defer=False):
+        """Adds the experts' weighted results into `out`; with defer=True and no shared expert it
+        returns them unsummed (WeightedRows) for the next norm to add."""
         rt = self.rt
         T = xn.shape[0]
         pairs = T * self.k
+        defer = defer and self.shared is None
         if (T <= ops.SMALL_T and rt.tensor_cores and not rt.is_fp32 and self.E <= 704 and ops.tc_supported(xn, self.w_gate)
                 and self.I % 8 == 0):
             # a decode step: router and top-k in one launch, then one weight tile stream per
@@ -80,16 +85,21 @@ class RoutedExperts(FeedForward):
             sel_e, sel_w, order = ops.router_small(xn, self.w_router, self.k, self.scoring, self.renorm)
             act = ops.gemm_tc_pairs(xn, self.w_gate, sel_e, self.k, w2=self.w_up, order=order)      # [pairs, I]
             y = ops.gemm_tc_pairs(act, self.w_down, sel_e, 1, order=order)                           # FP32 [pairs, D]
+            if defer:
+                return WeightedRows(y, sel_w)
             ops.combine(y, None, sel_w, out)
             if self.shared is not None:
                 self.shared.forward(xn, ctx, out)
-            return
+            return None
         logits = linear.matmul(xn, self.w_router, rt)                       # FP32 [T, E]
         sel_e, sel_w = ops.route(logits, self.k, self.scoring, self.renorm)
         offsets, pair_row, row_token = ops.moe_permute(sel_e, self.E)
         plan = linear.group_plan(xn, self.w_gate, offsets, row_token, pairs, rt)
         act = linear.grouped_swiglu(xn, plan, self.w_gate, self.w_up, rt)                         # [pairs, I]
         y = linear.grouped_matmul(act, plan, self.w_down, rt)                                     # FP32 [pairs, D]
+        if defer:
+            return WeightedRows(y, sel_w, pair_row)
         ops.combine(y, pair_row, sel_w, out)
         if self.shared is not None:
             self.shared.forward(xn, ctx, out)
+        return None

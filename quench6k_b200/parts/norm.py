@@ -4,7 +4,7 @@ from __future__ import annotations
 
 from .. import ops
 from ..spec import TensorSpec
-from .base import Norm, register_norm, to_f32
+from .base import Norm, WeightedRows, register_norm, to_f32
 
 
 @register_norm("rmsnorm")
@@ -22,5 +22,9 @@ class RMSNorm(Norm):
         self.rt = rt
         self.weight = to_f32(get("weight"), rt)
 
+    fuses_weighted_rows = True
+
     def forward(self, h, rows=None, add=None):
+        if isinstance(add, WeightedRows):
+            return ops.rmsnorm(h, self.weight, self.eps, self.rt.dtype, rows=rows, weighted=(add.y, add.pair_row, add.weights))
         return ops.rmsnorm(h, self.weight, self.eps, self.rt.dtype, rows=rows, add=add)

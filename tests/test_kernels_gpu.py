@@ -44,6 +44,19 @@ def test_rmsnorm(dtype, R, D, eps):
     fused = ops.rmsnorm(x2, w, eps, dtype, add=add)
     assert torch.equal(x2, x + add)
     assert torch.equal(fused, ops.rmsnorm(x + add, w, eps, dtype))
+    # the routed experts' results added inside the norm: the same values as combine followed by the norm
+    S = 3
+    y, sw = _t(R * S + 2, D, seed=4), _t(R, S, seed=5)
+    perm = torch.randperm(R * S, generator=torch.Generator().manual_seed(6)).to(torch.int32).view(R, S).to(DEV)
+    for pair_row in (None, perm):
+        for sel in (None, rows):
+            xa, xb = x.clone(), x.clone()
+            ops.combine(y, pair_row, sw, xa)
+            want = ops.rmsnorm(xa, w, eps, dtype, rows=sel)
+            got = ops.rmsnorm(xb, w, eps, dtype, rows=sel, weighted=(y, pair_row, sw))
+            assert torch.equal(got, want)
+            touched = torch.arange(R, device=DEV) if sel is None else sel.long()
+            assert torch.equal(xb[touched], xa[touched])
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])

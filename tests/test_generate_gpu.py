@@ -122,3 +122,45 @@ def test_graph_replay_equals_eager_steps(tmp_path, dtype):
             assert torch.equal(a, b)
         else:
             assert (a - b).abs().max() <= 1e-2 * a.abs().max()
+
+
+_LAUNCH_MODE_SCRIPT = r"""
+import sys, hashlib, torch
+sys.path.insert(0, sys.argv[1])
+from quench6k_b200.config import FlintConfig
+from quench6k_b200.engine import ModelRunner, StepEntry
+# wide enough for the tensor-core products with sliced K and for the decode path of the experts
+cfg = FlintConfig.from_dict(dict(architectures=["FlintForCausalLM"], hidden_size=512, num_hidden_layers=3, num_attention_heads=8,
+                                 num_key_value_heads=2, head_dim=128, vocab_size=1000, n_routed_experts=16, num_experts_per_tok=4,
+                                 moe_intermediate_size=128, rms_norm_eps=1e-6, rope_theta=10000.0, qk_norm=True, kv_page_size=16))
+runner = ModelRunner.from_random(cfg, 5, dtype="bfloat16", num_pages=64, max_requests=4)
+g = torch.Generator().manual_seed(9)
+h = hashlib.sha256()
+for rid, n in (("a", 150), ("b", 37)):
+    runner.add_request(rid)
+    h.update(runner.step([StepEntry(rid, torch.randint(0, 1000, (n,), generator=g).tolist(), [n - 1])]).cpu().numpy().tobytes())
+for i in range(20):
+    toks = torch.randint(0, 1000, (2,), generator=g).tolist()
+    h.update(runner.step([StepEntry("a", [toks[0]], [0]), StepEntry("b", [toks[1]], [0])]).cpu().numpy().tobytes())
+torch.cuda.synchronize()
+print("digest", h.hexdigest(), runner.graph_replays)
+"""
+
+
+def test_launch_modes_give_the_same_logits(tmp_path):
+    """Programmatic dependent launch lets the dense tensor-core product fetch weights while the
+    kernel before it still runs.  With it off, on for the marked launches (the default) and on for
+    every launch, the same steps (eager prompts, then decode steps replayed from a graph) must give
+    the same bits: nothing may be read before it is written."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = tmp_path / "launch_modes.py"
+    script.write_text(_LAUNCH_MODE_SCRIPT)
+    digests = {}
+    for mode in ("0", "gemm", "1"):
+        env = dict(os.environ, Q6K_PDL=mode)
+        proc = subprocess.run([sys.executable, str(script), root], capture_output=True, text=True, timeout=600, env=env)
+        assert proc.returncode == 0, proc.stderr[-2000:]
+        line = [ln for ln in proc.stdout.splitlines() if ln.startswith("digest")][-1].split()
+        digests[mode] = line[1]
+        assert int(line[2]) > 0                          # the decode steps did replay a graph
+    assert digests["0"] == digests["gemm"] == digests["1"], digests

@@ -45,6 +45,73 @@ __device__ __forceinline__ void warp_topk(float* v, int E, int k, int sigmoid, i
         for (int r = 32; r < k; ++r) sel_w[r] /= den;
 }
 
+// The same with the scores in registers (lane l holds experts l, l + 32, ...; NL of them, E <= 32 NL):
+// a round is a maximum over the lane's registers, one warp reduction of the score (the bits of a
+// non-negative float order like a signed integer) and one of the index among the lanes that hold it.
+template <int NL>
+__device__ __forceinline__ void warp_topk_regs(float (&val)[NL], int E, int k, int sigmoid, int renorm, float total, int* sel_e, float* sel_w) {
+    const int lane = threadIdx.x & 31;
+    int bits[NL];
+#pragma unroll
+    for (int i = 0; i < NL; ++i) bits[i] = lane + 32 * i < E ? __float_as_int(val[i]) : -1;      // -1: no expert / taken
+    float chosen_sum = 0.0f, mine = 0.0f;
+    for (int r = 0; r < k; ++r) {
+        int best = -1, best_i = 0;
+#pragma unroll
+        for (int i = 0; i < NL; ++i)
+            if (bits[i] > best) best = bits[i], best_i = i;
+        const int top = __reduce_max_sync(0xffffffffu, best);
+        const int idx = __reduce_min_sync(0xffffffffu, best == top ? lane + 32 * best_i : 0x7fffffff);      // ties: the lower expert
+        if ((idx & 31) == lane) {
+#pragma unroll
+            for (int i = 0; i < NL; ++i)
+                if (i == (idx >> 5)) bits[i] = -1;
+        }
+        const float best_f = __int_as_float(top);
+        const float score = sigmoid ? best_f : best_f / total;
+        chosen_sum += score;
+        if (lane == 0) sel_e[r] = idx;
+        if (lane == r) mine = score;                 // lane r keeps the r-th score (r < 32; later ones: below)
+        if (r >= 32 && lane == 0) sel_w[r] = score;
+    }
+    const float den = !renorm ? 1.0f : (sigmoid ? chosen_sum + 1e-20f : chosen_sum);
+    if (lane < k && lane < 32) sel_w[lane] = mine / den;
+    if (k > 32 && renorm && lane == 0)
+        for (int r = 32; r < k; ++r) sel_w[r] /= den;
+}
+
+// One token's scores from its logits (sigmoid, or the numerators of the softmax and their sum), then the top-k.
+template <int NL>
+__device__ __forceinline__ void warp_route_regs(const float* z, int E, int k, int sigmoid, int renorm, int* sel_e, float* sel_w) {
+    const int lane = threadIdx.x & 31;
+    float val[NL];
+#pragma unroll
+    for (int i = 0; i < NL; ++i) val[i] = lane + 32 * i < E ? __ldcg(z + lane + 32 * i) : -INFINITY;
+    float total = 1.0f;
+    if (sigmoid) {
+#pragma unroll
+        for (int i = 0; i < NL; ++i) {
+            const float s = 1.0f / (1.0f + expf(-val[i]));
+            val[i] = s >= 0.0f ? s : 0.0f;
+        }
+    } else {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int i = 0; i < NL; ++i) mx = fmaxf(mx, val[i]);
+        mx = warp_max(mx);
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NL; ++i) {
+            float s = lane + 32 * i < E ? expf(val[i] - mx) : 0.0f;
+            s = s >= 0.0f ? s : 0.0f;
+            val[i] = s;
+            sum += s;
+        }
+        total = warp_sum(sum);
+    }
+    warp_topk_regs<NL>(val, E, k, sigmoid, renorm, total, sel_e, sel_w);
+}
+
 __global__ void route_kernel(const float* logits, int T_, int E, int k, int sigmoid, int renorm, int* sel_e, float* sel_w) {
     pdl_enter();
     extern __shared__ float sc[];             // [warps][E]
@@ -139,30 +206,10 @@ __global__ void __launch_bounds__(512) router_small_kernel(const __nv_bfloat16* 
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    for (int t = warp; t < T_; t += 16) {        // a warp per token
-        float* v = sc + (size_t)warp * E;
+    for (int t = warp; t < T_; t += 16) {        // a warp per token, its scores in registers
         const float* z = logits + (size_t)t * E;
-        float total = 1.0f;
-        if (sigmoid) {
-            for (int x = lane; x < E; x += 32) {
-                const float s = 1.0f / (1.0f + expf(-__ldcg(z + x)));
-                v[x] = s >= 0.0f ? s : 0.0f;
-            }
-        } else {
-            float mx = -INFINITY;
-            for (int x = lane; x < E; x += 32) mx = fmaxf(mx, __ldcg(z + x));
-            mx = warp_max(mx);
-            float sum = 0.0f;
-            for (int x = lane; x < E; x += 32) {
-                float s = expf(__ldcg(z + x) - mx);
-                s = s >= 0.0f ? s : 0.0f;
-                v[x] = s;
-                sum += s;
-            }
-            total = warp_sum(sum);
-        }
-        __syncwarp();
-        warp_topk(v, E, k, sigmoid, renorm, total, sel_e + (size_t)t * k, sel_w + (size_t)t * k);
+        if (E <= 256) warp_route_regs<8>(z, E, k, sigmoid, renorm, sel_e + (size_t)t * k, sel_w + (size_t)t * k);
+        else warp_route_regs<22>(z, E, k, sigmoid, renorm, sel_e + (size_t)t * k, sel_w + (size_t)t * k);
     }
     // pairs sorted by expert (stable): tiles of one expert run side by side and share its weights in L2
     __syncthreads();

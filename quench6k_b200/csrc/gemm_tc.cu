@@ -476,6 +476,14 @@ static void dense_plan(int rows, int N, int K, bool dual, int* bt, int* splits) 
     int b = q6k_tc_token_tile(rows, dual);
     const int n_tiles = (N + WM - 1) / WM;
     while (b > 32 && rows > b && n_tiles * ((rows + b - 1) / b) * 2 < sm_count()) b /= 2;
+    if (b == 256 && !dual && rows > 256) {
+        // the persistent CTAs work in rounds of one tile each: a tile of 192 tokens can need the same
+        // number of rounds as one of 256 (q/k/v at 2,048 tokens: 440 tiles against 320, three rounds
+        // either way) and then ends a quarter earlier; its narrower MMAs are taken as a tenth dearer
+        const long long r256 = ((long long)n_tiles * ((rows + 255) / 256) + sm_count() - 1) / sm_count();
+        const long long r192 = ((long long)n_tiles * ((rows + 191) / 192) + sm_count() - 1) / sm_count();
+        if (r192 * 192 * 11 < r256 * 256 * 10) b = 192;
+    }
     *bt = b;
     *splits = dual ? 1 : splits_for(rows, N, K, b);
 }
@@ -514,7 +522,7 @@ Q6K_API int q6k_gemm_tc(const void* A, long long lda, int rows_total, const void
     const bool grouped = tile_group != nullptr;
     int planned_splits = 1;
     if (!grouped) dense_plan(rows_total, N, K, dual, &bt, &planned_splits);
-    Q6K_REQUIRE(bt == 16 || bt == 32 || bt == 64 || bt == 128 || (bt == 256 && !dual), "gemm_tc: token tile %d is not supported", bt);
+    Q6K_REQUIRE(bt == 16 || bt == 32 || bt == 64 || bt == 128 || ((bt == 192 || bt == 256) && !dual), "gemm_tc: token tile %d is not supported", bt);
     Q6K_REQUIRE((long long)groups * N < (1LL << 31), "gemm_tc: weight rows exceed the TMA coordinate range");
 
     CUtensorMap tw, tw2, ta;
@@ -548,7 +556,7 @@ Q6K_API int q6k_gemm_tc(const void* A, long long lda, int rows_total, const void
                   : launch<BT_, false>(tw, tw2, ta, p, ytiles, splits, st);                   \
         break;
     switch (bt) {
-        GO(16) GO(32) GO(64) GO(128) GO(256)
+        GO(16) GO(32) GO(64) GO(128) GO(192) GO(256)
         default: return q6k_fail("gemm_tc: token tile %d", bt);
     }
 #undef GO

@@ -59,7 +59,9 @@ __global__ void combine_kernel(const float* y, const int* pair_row, const float*
 // `pair_y`: the routed experts' results come in unsummed, x[t] += sum_s pair_w[t, s] * y[row(t, s)]
 // with row(t, s) = pair_row[t*S + s] (or t*S + s), slots in order: the arithmetic of combine4_kernel
 // below, which this replaces together with one pass over x.
-template <typename T, int V4>
+// NB: loads kept in flight per accumulation (8 for the few rows of a decode step, whose time is
+// latency; 2 for many rows, where the registers they cost would halve the blocks per SM).
+template <typename T, int V4, int NB>
 __global__ void __launch_bounds__(256) rmsnorm_reg_kernel(float* x, const float* add, int add_splits, size_t add_stride, const int* rows,
                                                           const float* w, float eps, T* out, int D, const float* pair_y,
                                                           const int* pair_row, const float* pair_w, int S) {
@@ -80,13 +82,13 @@ __global__ void __launch_bounds__(256) rmsnorm_reg_kernel(float* x, const float*
                 // the slices are fetched eight at a time (independent loads) and added in their order
                 const float4* ar = reinterpret_cast<const float4*>(add + (size_t)r * D) + c;
                 float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                for (int s0 = 0; s0 < add_splits; s0 += 8) {
-                    float4 b[8];
+                for (int s0 = 0; s0 < add_splits; s0 += NB) {
+                    float4 b[NB];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)
+                    for (int j = 0; j < NB; ++j)
                         if (s0 + j < add_splits) b[j] = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(ar) + (size_t)(s0 + j) * add_stride);
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)
+                    for (int j = 0; j < NB; ++j)
                         if (s0 + j < add_splits) a.x += b[j].x, a.y += b[j].y, a.z += b[j].z, a.w += b[j].w;
                 }
                 v[i].x += a.x, v[i].y += a.y, v[i].z += a.z, v[i].w += a.w;
@@ -94,11 +96,11 @@ __global__ void __launch_bounds__(256) rmsnorm_reg_kernel(float* x, const float*
             }
             if (pair_y) {
                 float4 a = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-                for (int s0 = 0; s0 < S; s0 += 8) {
-                    float4 b[8];
-                    float ws[8];
+                for (int s0 = 0; s0 < S; s0 += NB) {
+                    float4 b[NB];
+                    float ws[NB];
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
+                    for (int j = 0; j < NB; ++j) {
                         if (s0 + j < S) {
                             const int pr = pair_row ? pair_row[t * S + s0 + j] : t * S + s0 + j;
                             ws[j] = pair_w[t * S + s0 + j];
@@ -106,7 +108,7 @@ __global__ void __launch_bounds__(256) rmsnorm_reg_kernel(float* x, const float*
                         }
                     }
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)
+                    for (int j = 0; j < NB; ++j)
                         if (s0 + j < S) a.x = fmaf(ws[j], b[j].x, a.x), a.y = fmaf(ws[j], b[j].y, a.y), a.z = fmaf(ws[j], b[j].z, a.z), a.w = fmaf(ws[j], b[j].w, a.w);
                 }
                 v[i].x += a.x, v[i].y += a.y, v[i].z += a.z, v[i].w += a.w;
@@ -199,11 +201,19 @@ Q6K_API int q6k_rmsnorm(float* x, const float* add, int add_splits, long long ad
                      (add_stride % 4 == 0) && (!pair_y || ((uintptr_t)pair_y & 15) == 0);
     if (vec) {
         const int v4 = (D / 4 + 255) / 256;
+#define Q6K_NORM_GO(V4_, NB_) q6k_launch(rmsnorm_reg_kernel<T, V4_, NB_>, R, 256, 0, st, x, add, add_splits, (size_t)add_stride, rows, w, eps, (T*)out, D, pair_y, pair_row, pair_w, S)
         Q6K_DISPATCH(dtype, {
-            if (v4 <= 1) q6k_launch(rmsnorm_reg_kernel<T, 1>, R, 256, 0, st, x, add, add_splits, (size_t)add_stride, rows, w, eps, (T*)out, D, pair_y, pair_row, pair_w, S);
-            else if (v4 <= 2) q6k_launch(rmsnorm_reg_kernel<T, 2>, R, 256, 0, st, x, add, add_splits, (size_t)add_stride, rows, w, eps, (T*)out, D, pair_y, pair_row, pair_w, S);
-            else q6k_launch(rmsnorm_reg_kernel<T, 4>, R, 256, 0, st, x, add, add_splits, (size_t)add_stride, rows, w, eps, (T*)out, D, pair_y, pair_row, pair_w, S);
+            if (R <= 64) {
+                if (v4 <= 1) Q6K_NORM_GO(1, 8);
+                else if (v4 <= 2) Q6K_NORM_GO(2, 8);
+                else Q6K_NORM_GO(4, 8);
+            } else {
+                if (v4 <= 1) Q6K_NORM_GO(1, 2);
+                else if (v4 <= 2) Q6K_NORM_GO(2, 2);
+                else Q6K_NORM_GO(4, 2);
+            }
         });
+#undef Q6K_NORM_GO
         return q6k_check_launch("rmsnorm");
     }
     Q6K_REQUIRE(!pair_y, "rmsnorm: weighted rows need a width that is a multiple of 4 and at most 4096 (got %d)", D);

@@ -126,6 +126,46 @@ def prefill_flops(cfg, layers, T):
     return matmul + attention
 
 
+def kernel_attention_prefill(args):
+    """The prompt-portion attention kernel alone: T query tokens of one request whose last token stands
+    at position `context - 1`, over a cache of `context` keys (so T = context is a whole prompt from
+    position 0); FLOPs counted under the causal mask; CUDA events, warm-up, cache larger than L2 from
+    32,768 keys on."""
+    import torch
+    from quench6k_b200 import ops
+    from quench6k_b200.engine.batch import StepContext
+    c = CONFIG2
+    Hq, Hkv, hd, ps = c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"], args.page_size or c["kv_page_size"]
+    n, T, dev = args.context, min(args.prefill_tokens, args.context), "cuda:0"
+    pages = (n + ps - 1) // ps
+    kp = torch.randn(Hkv, pages, ps, hd, device=dev).to(torch.bfloat16)
+    vp = torch.randn(Hkv, pages, ps, hd, device=dev).to(torch.bfloat16)
+    q = torch.randn(T, Hq, hd, device=dev).to(torch.bfloat16)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    ctx = StepContext(T=T, R=1, token_ids=i32([0] * T), positions=i32(list(range(n - T, n))), req_of_token=i32([0] * T), q_start=i32([0, T]),
+                      pos_start=i32([n - T]), slot_ids=i32([0]), block_tables=[i32([list(range(pages))])], logit_rows=i32([]), n_logit_rows=0,
+                      q_lens=[T], pos_starts=[n - T], slots=[0], max_context=n, max_q_len=T)
+    tok0, ntok, n_tiles = ctx.query_tile_pairs(ops.attention_tc_tile_tokens(Hq // Hkv), False)
+    run = lambda: ops.attention_tc(q, kp, vp, ctx.block_tables[0], ctx.req_of_token, ctx.positions, tok0, ntok, None, None)
+    for _ in range(max(3, args.warmup)):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    assert ops.tc_status() == 0
+    ms = e0.elapsed_time(e1) / args.steps
+    flops = 4.0 * Hq * hd * T * (n - T + (T + 1) / 2.0)
+    pk = peaks()
+    print(json.dumps({"kernel": "attention_tc (prompt portions)", "tokens": T, "context": n, "us": round(ms * 1e3, 1),
+                      "tflops": round(flops / ms / 1e9, 1), "frac_of_bf16_peak": round(flops / ms / 1e9 / pk["bf16_tflops"], 3),
+                      "peaks": pk["source"], "ctas": n_tiles * Hkv, "steps": args.steps}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -139,6 +179,9 @@ def main():
     ap.add_argument("--points", default="1,64", help="further decode batch sizes, comma separated ('' for none)")
     ap.add_argument("--dtype", default="bfloat16")
     ap.add_argument("--page-size", type=int, default=None, help="KV page size (default: the configuration's 16)")
+    ap.add_argument("--kernel", default=None, choices=["attention_prefill"],
+                    help="time one kernel alone at the configuration's head sizes instead of the model: attention_prefill runs "
+                         "--prefill-tokens query tokens that end at position --context (one request, contiguous pages)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -157,6 +200,8 @@ def main():
     from quench6k_b200.engine import StepEntry
 
     assert torch.cuda.is_available(), "bench.py needs a CUDA device"
+    if args.kernel == "attention_prefill":
+        return kernel_attention_prefill(args)
     torch.cuda.set_device(0)
     pk = peaks()
     cfg_d = dict(CONFIG2)

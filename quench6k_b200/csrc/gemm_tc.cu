@@ -23,6 +23,7 @@
 //              as its values are in registers, so the next tile's MMAs overlap the stores
 // Every wait on an mbarrier is bounded; a wait that runs out records a code in a status word that
 // q6k_tc_status() returns, the roles fall through to the common exit, and tensor memory is freed.
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <tuple>
@@ -370,6 +371,190 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
     }
 }
 
+// ------------------------------------------------------------------------- a pair of CTAs per tile
+// Dense products with many rows: two CTAs of a cluster work on one tile of [256 weights x BT2 tokens]
+// with tcgen05.mma.cta_group::2.  Each CTA brings its 128 weight rows and its half of the token tile
+// into its own shared memory, the leader (rank 0) issues the MMAs, which read both CTAs' shared
+// memory and write each CTA's half of the accumulator (its 128 weight rows x BT2 tokens) into that
+// CTA's tensor memory.  Per MMA and SM that is half the token-tile traffic of the one-CTA kernel,
+// whose MMAs wait for shared memory.  Barriers: both CTAs' TMA loads count their bytes on the
+// leader's "full" barrier (the .cta_group::2 form of the copy takes a barrier of the pair's other
+// CTA); the leader's tcgen05.commit arrives on "empty" and "accumulator full" in both CTAs; the
+// epilogue warps of both arrive on the leader's "accumulator empty".
+constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;    // a shared-memory address of either CTA of a pair -> the same offset in the even one
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(bar & PEER_MASK)
+        : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n\t}" ::"r"(tmem_d),
+        "l"(da), "l"(db), "r"(idesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {          // arrives at this offset in both CTAs
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                 "h"((uint16_t)3)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_leader(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar & PEER_MASK) : "memory");
+}
+// D FP32, A and B bfloat16, both K-major, M = 256 over the pair, N = n.
+__host__ __device__ constexpr uint32_t umma_idesc_pair(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+template <int BT2>
+__global__ void __launch_bounds__(192) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a,
+                                                           const Params p) {
+    pdl_wait();
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int n_x = (p.N + 2 * WM - 1) / (2 * WM), total = n_x * p.n_y;
+    const int kb_total = (p.K + BK - 1) / BK;
+
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    constexpr uint32_t W_BYTES = WM * BK * 2, A_BYTES = (BT2 / 2) * BK * 2, STAGE_BYTES = W_BYTES + A_BYTES;
+    constexpr int ACC_COLS = BT2;
+    __shared__ __align__(8) uint64_t bars[2 * MAX_STAGES + 4];
+    __shared__ uint32_t tmem_base_slot;
+    const int stages = p.stages;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[MAX_STAGES]);
+    const uint32_t acc_full0 = smem_u32(&bars[2 * MAX_STAGES]), acc_empty0 = smem_u32(&bars[2 * MAX_STAGES + 2]);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(full0 + 8 * s, 1);                   // the leader's: its producer's arrival with both CTAs' bytes
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(acc_full0 + 8 * b, 1);
+            mbar_init(acc_empty0 + 8 * b, 8);              // the leader's: four epilogue warps of each CTA
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_w) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_a) : "memory");
+    }
+    if (warp == 1) {                                       // the same warp of both CTAs allocates for the pair
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                    // both CTAs' barriers exist before either signals the other
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    pdl_launch();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int t = pair; t < total && ok; t += n_pairs) {
+                const int n0 = (t % n_x) * 2 * WM + (int)rank * WM, row0 = (t / n_x) * BT2 + (int)rank * (BT2 / 2);
+                for (int i = 0; i < kb_total; ++i, ++it) {
+                    const int s = it % stages;
+                    if (!mbar_wait(empty0 + 8 * s, ((it / stages) & 1) ^ 1)) {
+                        atomicExch(&g_tc_status, 11);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES), fb = full0 + 8 * s;
+                    if (rank == 0) mbar_expect_tx(fb, 2 * STAGE_BYTES);
+                    tma_load_2d_pair(st, &tm_w, i * BK, n0, fb);
+                    tma_load_2d_pair(st + W_BYTES, &tm_a, i * BK, row0, fb);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = umma_idesc_pair(BT2);
+            int it = 0, nt = 0;
+            bool ok = true;
+            for (int t = pair; t < total && ok; t += n_pairs, ++nt) {
+                const int buf = nt & 1;
+                if (!mbar_wait(acc_empty0 + 8 * buf, ((nt >> 1) & 1) ^ 1)) {
+                    atomicExch(&g_tc_status, 14);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t acc_addr = tmem_base + buf * ACC_COLS;
+                for (int i = 0; i < kb_total; ++i, ++it) {
+                    const int s = it % stages;
+                    if (!mbar_wait(full0 + 8 * s, (it / stages) & 1)) {
+                        atomicExch(&g_tc_status, 12);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES);
+                    const uint64_t dw = umma_desc_sw128(st), da = umma_desc_sw128(st + W_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k) umma_bf16_pair(acc_addr, dw + 2 * k, da + 2 * k, idesc, (i | k) != 0);
+                    umma_commit_pair(empty0 + 8 * s);
+                }
+                if (!ok) break;
+                umma_commit_pair(acc_full0 + 8 * buf);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        int nt = 0;
+        for (int t = pair; t < total; t += n_pairs, ++nt) {
+            const int buf = nt & 1;
+            if (!mbar_wait(acc_full0 + 8 * buf, (nt >> 1) & 1)) {
+                if (lane == 0) atomicExch(&g_tc_status, 13);
+                break;
+            }
+            tc_fence_after();
+            const int n = (t % n_x) * 2 * WM + (int)rank * WM + quarter * 32 + lane, tok0 = (t / n_x) * BT2;
+            const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * ACC_COLS;
+            const int valid = min(BT2, p.rows_total - tok0);
+#pragma unroll 1
+            for (int c0 = 0; c0 < valid; c0 += 16) {
+                float v[16];
+                tmem_ld16(lane_addr + c0, v);
+                if (c0 + 16 >= valid) {
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_leader(acc_empty0 + 8 * buf);
+                }
+                if (n < p.N) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (c0 + j >= valid) break;
+                        float* o = (float*)p.out + (size_t)(tok0 + c0 + j) * p.ldo + n;
+                        *o = p.epilogue == EPI_ADD ? *o + v[j] : v[j];
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                                    // the peer has no MMA, copy or arrival of ours in flight
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
 // out[r, n] (=|+=) sum_s partial[s, r, n], s ascending.
 __global__ void splitk_reduce_kernel(const float* partial, int splits, size_t count, float* out, int N, int ldo, int add) {
     pdl_enter();
@@ -440,6 +625,47 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tw2, const CUtensorMap& ta,
     const int grid = (int)(total < slots ? total : slots);
     q6k_launch_as(p.tile_group == nullptr, gemm_tc_kernel<BT, DUAL>, grid, 192, smem, st, tw, tw2, ta, p);
     return q6k_check_launch("gemm_tc");
+}
+
+// The CTA-pair kernel: tiles of [256 weights x BT2 tokens], one cluster of two CTAs per SM pair.
+template <int BT2>
+int launch_pair(const CUtensorMap& tw, const CUtensorMap& ta, Params p, cudaStream_t st) {
+    constexpr int stage = WM * BK * 2 + (BT2 / 2) * BK * 2;
+    int stages = (200 * 1024) / stage;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    p.stages = stages;
+    p.n_y = (p.rows_total + BT2 - 1) / BT2;
+    const size_t smem = (size_t)stages * stage + 1024;
+    static bool configured = false;
+    if (!configured) {
+        if (cudaFuncSetAttribute(gemm_tc_pair_kernel<BT2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024) != cudaSuccess)
+            return q6k_check_launch("gemm_tc pair: shared memory attribute");
+        configured = true;
+    }
+    const long long total = (long long)((p.N + 2 * WM - 1) / (2 * WM)) * p.n_y;
+    const int pairs = sm_count() / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * (unsigned)(total < pairs ? total : pairs)), cfg.blockDim = dim3(192), cfg.dynamicSmemBytes = smem, cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<BT2>, tw, ta, p);
+    return q6k_check_launch("gemm_tc pair");
+}
+
+// Token tile of the pair kernel for (rows, N), or 0 when the one-CTA kernel serves the product:
+// plain dense products with at least 512 rows and 256 weight rows.  Q6K_TC_PAIR=0 switches it off.
+static int pair_plan(int rows, int N, int K) {
+    static const bool off = [] {
+        const char* v = getenv("Q6K_TC_PAIR");
+        return v && v[0] == '0';
+    }();
+    if (off || rows < 512 || N < 2 * WM || K % 8 != 0) return 0;
+    const long long n_x = (N + 2 * WM - 1) / (2 * WM), pairs = sm_count() / 2;
+    if (n_x * ((rows + 255) / 256) * 2 < pairs) return 0;   // too few tiles for the pairs: the one-CTA kernel narrows its tile
+    const long long r256 = (n_x * ((rows + 255) / 256) + pairs - 1) / pairs, r192 = (n_x * ((rows + 191) / 192) + pairs - 1) / pairs;
+    return r192 * 192 < r256 * 256 ? 192 : 256;            // the tile that ends the last round earlier
 }
 
 }  // namespace
@@ -530,6 +756,14 @@ Q6K_API int q6k_gemm_tc(const void* A, long long lda, int rows_total, const void
     tw2 = tw;
     if (dual)
         if (int rc = weight_map(&tw2, W2, (long long)groups * N, K)) return rc;
+    if (!grouped && !dual && planned_splits == 1) {
+        if (const int bt2 = pair_plan(rows_total, N, K)) {
+            if (int rc = make_map(&ta, A, rows_total, K, lda, bt2 / 2, false)) return rc;
+            Params pp{};
+            pp.out = out, pp.rows_total = rows_total, pp.N = N, pp.K = K, pp.ldo = ldo, pp.epilogue = epilogue;
+            return bt2 == 192 ? launch_pair<192>(tw, ta, pp, st) : launch_pair<256>(tw, ta, pp, st);
+        }
+    }
     if (int rc = make_map(&ta, A, rows_total, K, lda, bt, false)) return rc;
 
     Params p{};

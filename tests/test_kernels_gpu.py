@@ -251,7 +251,7 @@ def test_kernels_refuse_what_they_cannot_do():
 # --------------------------------------------------------------------------- tcgen05 tensor-core products
 @pytest.mark.parametrize("M,N,K", [(1, 256, 64), (8, 5120, 2048), (16, 100, 72), (17, 384, 200), (70, 130, 1024),
                                    (200, 512, 136), (300, 1000, 4096), (2048, 640, 512), (5, 2048, 4096), (2048, 5120, 256),
-                                   (700, 2000, 264)])
+                                   (700, 2000, 264), (1100, 2304, 1032), (1300, 2200, 512), (2048, 2048, 4096)])
 def test_gemm_tc_dense(M, N, K):
     from quench6k_b200 import ops
     a, w = _t(M, K, dtype=torch.bfloat16), _t(N, K, dtype=torch.bfloat16, seed=1)

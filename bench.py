@@ -55,14 +55,29 @@ def peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks and throttle reasons, sampled every 200 ms while a timed region runs."""
+    """SM clock and throttle reasons of GPU 0 while a timed region runs: read through NVML every
+    5 ms when its Python binding is there (a timed region of a few dozen milliseconds still gets
+    several samples), else from `nvidia-smi -lms 200`.  Reading only; nothing is set."""
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self):
-        self.lines, self.proc = [], None
+        self.lines, self.proc, self.nvml, self.samples, self.stop_flag = [], None, None, [], False
 
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(int(os.environ.get("CUDA_VISIBLE_DEVICES", "0").split(",")[0] or 0)
+                                                            if os.environ.get("CUDA_VISIBLE_DEVICES", "0").split(",")[0].isdigit() else 0)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
                                           "-lms", "200"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
@@ -71,11 +86,34 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def _poll(self):
+        nv = self.nvml
+        bits = {"hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+                "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+                "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+                "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4)}
+        reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        while not self.stop_flag:
+            try:
+                mhz = float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                mask = int(reasons_fn(self.handle))
+                self.samples.append((mhz, {n for n, b in bits.items() if mask & b}))
+            except Exception:
+                pass
+            time.sleep(0.005)
+
     def _read(self):
         for line in self.proc.stdout:
             self.lines.append(line.strip())
 
     def stop(self):
+        if self.nvml is not None:
+            self.stop_flag = True
+            self.thread.join(timeout=1)
+            sm = sorted(m for m, _ in self.samples)
+            reasons = set().union(*[r for _, r in self.samples]) if self.samples else set()
+            return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(reasons),
+                    "samples": len(sm), "source": "nvml"}
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -84,7 +122,6 @@ class ClockSampler:
         except Exception:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in self.lines:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
@@ -93,12 +130,12 @@ class ClockSampler:
                 sm.append(float(parts[0])), mx.append(float(parts[1]))
             except ValueError:
                 continue
-            for n, v in zip(names, parts[2:6]):
+            for n, v in zip(self.NAMES, parts[2:6]):
                 if v.lower().startswith("active"):
                     reasons.add(n)
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "source": "nvidia-smi"}
 
 
 def expected_experts(E, k, B):
@@ -233,7 +270,7 @@ def main():
     def rand_ids(n):
         return torch.randint(0, V, (n,), generator=gen).tolist()
 
-    def timed_decode(B, steps, warmup):
+    def timed_decode(B, steps, warmup, sampler=None):
         """Device-timed decode steps of B requests standing at `ctx` cached tokens."""
         rids = [f"d{B}_{i}" for i in range(B)]
         for r in rids:
@@ -253,11 +290,15 @@ def main():
         torch.cuda.synchronize()
         l0 = ops.launch_count
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        if sampler is not None:
+            sampler.start()                      # the clocks are read while the timed steps run, and only then
         a.record()
         for i in range(warmup, warmup + steps):
             one(i)
         b.record()
         torch.cuda.synchronize()
+        if sampler is not None:
+            sampler.result = sampler.stop()
         ms = a.elapsed_time(b) / steps
         launches = ops.launch_count - l0
         for r in rids:
@@ -265,9 +306,8 @@ def main():
         return ms, launches
 
     clocks = ClockSampler()
-    clocks.start()
-    ms, launches = timed_decode(args.batch, args.steps, args.warmup)
-    clock_info = clocks.stop()
+    ms, launches = timed_decode(args.batch, args.steps, args.warmup, clocks)
+    clock_info = clocks.result
     value = args.batch * 1000.0 / ms
     total_b, w_b, kv_b = decode_bytes(cfg_d, layers, args.batch, ctx)
     achieved = total_b / (ms * 1e-3) / 1e9

@@ -1,0 +1,59 @@
+"""The step's launch plans that are made on the host: query tiles and their pairs."""
+import random
+
+import pytest
+import torch
+
+from quench6k_b200.engine.batch import StepContext
+
+
+def make_ctx(q_lens):
+    T, R = sum(q_lens), len(q_lens)
+    z = torch.zeros(0, dtype=torch.int32)
+    return StepContext(T=T, R=R, token_ids=torch.zeros(T, dtype=torch.int32), positions=z, req_of_token=z, q_start=z, pos_start=z,
+                       slot_ids=z, block_tables=[], logit_rows=z, n_logit_rows=0, q_lens=list(q_lens), pos_starts=[0] * R,
+                       slots=list(range(R)), max_context=max(q_lens), max_q_len=max(q_lens))
+
+
+def request_of(row, q_lens):
+    at = 0
+    for r, n in enumerate(q_lens):
+        if row < at + n:
+            return r
+        at += n
+    raise AssertionError(row)
+
+
+@pytest.mark.parametrize("seed", range(5))
+@pytest.mark.parametrize("zigzag", [False, True])
+def test_tile_pairs_cover_every_token_once(seed, zigzag):
+    rng = random.Random(seed)
+    q_lens = [rng.choice([1, 2, 15, 16, 17, 100, 333]) for _ in range(rng.randint(1, 6))]
+    per = rng.choice([1, 5, 16, 128])
+    ctx = make_ctx(q_lens)
+    tok0, ntok, n = ctx.query_tile_pairs(per, zigzag)
+    assert tuple(tok0.shape) == (n, 2) and tuple(ntok.shape) == (n, 2)
+    seen = [0] * sum(q_lens)
+    for (a0, b0), (an, bn) in zip(tok0.tolist(), ntok.tolist()):
+        assert 1 <= an <= per and 0 <= bn <= per           # the first tile of a pair is never empty
+        for t0, tn in ((a0, an), (b0, bn)):
+            for row in range(t0, t0 + tn):
+                seen[row] += 1
+            if tn:                                          # a tile stays inside one request
+                assert request_of(t0, q_lens) == request_of(t0 + tn - 1, q_lens)
+        if bn:
+            assert request_of(a0, q_lens) == request_of(b0, q_lens) and a0 > b0      # one request; the later tile first
+            if not zigzag:
+                assert b0 + bn == a0                        # neighbours
+    assert seen == [1] * sum(q_lens)
+    # the same tiles as the single-tile plan
+    s0, sn, m = ctx.query_tiles(per)
+    singles = sorted(zip(s0.tolist(), sn.tolist()))
+    paired = sorted((t0, tn) for (a0, b0), (an, bn) in zip(tok0.tolist(), ntok.tolist()) for t0, tn in ((a0, an), (b0, bn)) if tn)
+    assert singles == paired and m == len(singles)
+
+
+def test_zigzag_pairs_the_last_tile_with_the_first():
+    ctx = make_ctx([70])
+    tok0, ntok, n = ctx.query_tile_pairs(16, True)          # tiles at 0, 16, 32, 48, 64 (6 tokens)
+    assert tok0.tolist() == [[64, 0], [48, 16], [32, 32]] and ntok.tolist() == [[6, 16], [16, 16], [16, 0]] and n == 3

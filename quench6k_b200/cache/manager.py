@@ -258,7 +258,7 @@ class CacheManager:
 
     # ------------------------------------------------------------------ the step's description
     def pack_step(self, rids: Sequence[Hashable], tokens: Sequence[Sequence[int]], want: Sequence[Sequence[int]],
-                  widths: Sequence[int], vocab_size: int, out: np.ndarray) -> Tuple[int, int, int, int, int]:
+                  widths: Sequence[int], vocab_size: int, out: np.ndarray, feed_limit: int = 0) -> Tuple[int, int, int, int, int]:
         """Write the step's int32 block into `out`:
         [tokens T | positions T | request of token T | q_start R+1 | pos_start R | slot R | logit rows |
         one R x widths[g] block table per group].  Returns (ints written, T, wanted rows, longest
@@ -286,7 +286,7 @@ class CacheManager:
             req = self.requests[rid]
             n = q_lens[r]
             arr = np.asarray(tokens[r], dtype=np.int64)
-            if n and (arr.min() < 0 or arr.max() >= vocab_size):
+            if n and (arr.min() < -feed_limit or arr.max() >= vocab_size):      # -1 .. -feed_limit: tokens still on the device
                 raise ValueError(f"request {rid!r}: token id outside 0..{vocab_size - 1}")
             tok[t:t + n] = arr
             pos[t:t + n] = np.arange(req.length, req.length + n)

@@ -43,7 +43,7 @@ def host_lib():
         "q6k_cm_slots_free": (i, [vp]),
         "q6k_cm_num_live": (i, [vp]),
         "q6k_cm_table": (i, [vp, i64, i, ctypes.POINTER(_i32p), _i32p]),
-        "q6k_cm_fill_step": (i, [vp, i, _i64p, _i32p, _i32p, _i32p, _i32p, _i32p, i, _i32p, i64, _i64p]),
+        "q6k_cm_fill_step": (i, [vp, i, _i64p, _i32p, _i32p, _i32p, _i32p, _i32p, i, i, _i32p, i64, _i64p]),
         "q6k_sched_create": (vp, [vp, i, i]),
         "q6k_sched_destroy": (None, [vp]),
         "q6k_sched_add": (i, [vp, i64, _i32p, i, i, _i32p, i]),
@@ -55,6 +55,8 @@ def host_lib():
         "q6k_sched_schedule": (i, [vp, i, _i64p, _i64p, _i32p, _i32p, _i32p, _i64p, _i32p, _i64p, _i32p, _i64p, _i32p, _i32p]),
         "q6k_sched_tokens": (i, [vp, i64, i64, i, _i32p]),
         "q6k_sched_update": (i, [vp, _i32p, i, i, _i64p, _i32p, _i32p]),
+        "q6k_sched_set_output_token": (i, [vp, i64, i, ctypes.c_int32]),
+        "q6k_sched_stop": (i, [vp, i64, i]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
@@ -258,17 +260,18 @@ class NativeCacheManager:
 
     # ------------------------------------------------------------------ the step's description
     def pack_step(self, rids: Sequence[Hashable], tokens: Sequence[Sequence[int]], want: Sequence[Sequence[int]],
-                  widths: Sequence[int], vocab_size: int, out: np.ndarray) -> Tuple[int, int, int, int, int]:
+                  widths: Sequence[int], vocab_size: int, out: np.ndarray, feed_limit: int = 0) -> Tuple[int, int, int, int, int]:
         """Write the step's int32 block into `out`:
         [tokens T | positions T | request of token T | q_start R+1 | pos_start R | slot R | logit rows |
         one R x widths[g] block table per group].  Returns (ints written, T, wanted rows, longest
-        context, longest entry)."""
+        context, longest entry).  feed_limit > 0 admits token ids -1 .. -feed_limit, which stand for
+        tokens the step before has sampled and which are resolved on the device."""
         R = len(rids)
         ids = np.array([self._known(r) for r in rids], dtype=np.int64)
         q_lens = i32([len(t) for t in tokens])
         flat = np.concatenate([np.asarray(t, dtype=np.int64) for t in tokens]) if R else np.zeros(0, dtype=np.int64)
-        if flat.size and (flat.min() < 0 or flat.max() >= vocab_size):
-            bad = next(r for r, t in zip(rids, tokens) if len(t) and (min(t) < 0 or max(t) >= vocab_size))
+        if flat.size and (flat.min() < -feed_limit or flat.max() >= vocab_size):
+            bad = next(r for r, t in zip(rids, tokens) if len(t) and (min(t) < -feed_limit or max(t) >= vocab_size))
             raise ValueError(f"request {bad!r}: token id outside 0..{vocab_size - 1}")
         flat = i32(flat)
         wc = i32([len(w) for w in want])
@@ -276,7 +279,7 @@ class NativeCacheManager:
         wd = i32(list(widths) or [0])
         meta = np.zeros(5, dtype=np.int64)
         rc = host_lib().q6k_cm_fill_step(self._h, R, ptr64(ids), ptr32(q_lens), ptr32(flat), ptr32(wflat), ptr32(wc), ptr32(wd),
-                                         vocab_size, ptr32(out), out.size, ptr64(meta))
+                                         vocab_size, feed_limit, ptr32(out), out.size, ptr64(meta))
         if rc == 5 and "wanted place" in host_lib().q6k_host_last_error().decode():
             for r, t, w in zip(rids, tokens, want):
                 for i in w:

@@ -5,11 +5,14 @@
 
 namespace {
 
+// A token id -(i + 1) stands for fed[i], the i-th token the step before has sampled, which the host
+// may not have seen yet (fed: up to n_fed ids on the device).
 template <typename T>
-__global__ void embed_kernel(const int* tokens, const T* table, float* h, int D, int V) {
+__global__ void embed_kernel(const int* tokens, const T* table, float* h, int D, int V, const int* fed, int n_fed) {
     pdl_enter();
     const int t = blockIdx.x;
     int tok = tokens[t];
+    if (tok < 0 && fed != nullptr && -tok - 1 < n_fed) tok = fed[-tok - 1];
     tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);      // ids are validated on the host; never read outside the table
     const T* row = table + (size_t)tok * D;
     for (int i = threadIdx.x; i < D; i += blockDim.x) h[(size_t)t * D + i] = to_f32(row[i]);
@@ -176,10 +179,11 @@ Q6K_API int q6k_gather_rows(const void* x, const int* idx, void* out, int rows, 
     return q6k_check_launch("gather_rows");
 }
 
-Q6K_API int q6k_embed(const int* tokens, const void* table, float* h, int T_, int D, int V, int dtype, cudaStream_t st) {
+Q6K_API int q6k_embed(const int* tokens, const void* table, float* h, int T_, int D, int V, int dtype, const int* fed, int n_fed,
+                      cudaStream_t st) {
     if (T_ == 0) return 0;
-    Q6K_REQUIRE(T_ > 0 && D > 0 && V > 0, "embed: bad sizes T=%d D=%d V=%d", T_, D, V);
-    Q6K_DISPATCH(dtype, q6k_launch(embed_kernel<T>, T_, 256, 0, st, tokens, (const T*)table, h, D, V););
+    Q6K_REQUIRE(T_ > 0 && D > 0 && V > 0 && n_fed >= 0, "embed: bad sizes T=%d D=%d V=%d", T_, D, V);
+    Q6K_DISPATCH(dtype, q6k_launch(embed_kernel<T>, T_, 256, 0, st, tokens, (const T*)table, h, D, V, fed, n_fed););
     return q6k_check_launch("embed");
 }
 

@@ -474,9 +474,11 @@ API int q6k_cm_table(void* h, int64_t id, int group, const int32_t** pages, int*
 // [tokens T | positions T | request of token T | q_start R+1 | pos_start R | slot R | logit rows W |
 //  block table of group 0: R x widths[0] | group 1 ...], -1 where a table has no page.
 // tokens: the entries' tokens back to back; want: for each entry want_counts[r] indices into its
-// tokens.  meta: [total ints, T, wanted rows, max context, max q_len].
+// tokens.  meta: [total ints, T, wanted rows, max context, max q_len].  feed_limit > 0 admits token
+// ids -1 .. -feed_limit: "the i-th token the step before has sampled", resolved on the device.
 API int q6k_cm_fill_step(void* h, int R, const int64_t* ids, const int* q_lens, const int32_t* tokens, const int* want,
-                         const int* want_counts, const int* widths, int vocab, int32_t* out, int64_t capacity, int64_t* meta) {
+                         const int* want_counts, const int* widths, int vocab, int feed_limit, int32_t* out, int64_t capacity,
+                         int64_t* meta) {
     CacheManager* cm = (CacheManager*)h;
     int64_t T = 0, W = 0;
     for (int r = 0; r < R; ++r) T += q_lens[r], W += want_counts[r];
@@ -492,7 +494,7 @@ API int q6k_cm_fill_step(void* h, int R, const int64_t* ids, const int* q_lens, 
         const int n = q_lens[r];
         for (int i = 0; i < n; ++i) {
             const int32_t v = tokens[t + i];
-            if (v < 0 || v >= vocab) return fail(E_VALUE, "request %lld: token id %d outside 0..%d", (long long)ids[r], v, vocab - 1);
+            if (v < -feed_limit || v >= vocab) return fail(E_VALUE, "request %lld: token id %d outside 0..%d", (long long)ids[r], v, vocab - 1);
             tok[t + i] = v, pos[t + i] = (int32_t)(cr->length + i), rot[t + i] = r;
         }
         for (int i = 0; i < want_counts[r]; ++i) {
@@ -613,6 +615,28 @@ API int q6k_sched_tokens(void* h, int64_t id, int64_t start, int count, int32_t*
     if (it == s->by_id.end()) return fail(E_KEY, "request %lld is unknown", (long long)id);
     if (start < 0 || start + count > it->second.num_tokens()) return fail(E_VALUE, "request %lld has no tokens %lld..%lld", (long long)id, (long long)start, (long long)(start + count));
     for (int i = 0; i < count; ++i) out[i] = it->second.token(start + i);
+    return OK;
+}
+// A token that was entered as a placeholder (the step that samples it was still running) gets its value.
+API int q6k_sched_set_output_token(void* h, int64_t id, int index, int32_t tok) {
+    Scheduler* s = (Scheduler*)h;
+    auto it = s->by_id.find(id);
+    if (it == s->by_id.end()) return fail(E_KEY, "request %lld is unknown", (long long)id);
+    if (index < 0 || index >= (int)it->second.output.size()) return fail(E_VALUE, "request %lld has no output token %d", (long long)id, index);
+    it->second.output[index] = tok;
+    return OK;
+}
+// The request turns out to have ended with its n_keep-th output token (a stop token that was still
+// a placeholder when later steps were planned): what came after is dropped, it ends with "stop".
+API int q6k_sched_stop(void* h, int64_t id, int n_keep) {
+    Scheduler* s = (Scheduler*)h;
+    auto it = s->by_id.find(id);
+    if (it == s->by_id.end()) return fail(E_KEY, "request %lld is unknown", (long long)id);
+    SchedRequest& r = it->second;
+    if (n_keep < 1 || n_keep > (int)r.output.size()) return fail(E_VALUE, "request %lld has %d output tokens, cannot keep %d", (long long)id, (int)r.output.size(), n_keep);
+    r.output.resize(n_keep);
+    if (int rc = s->finish(r, FINISH_STOP)) return rc;
+    s->by_id.erase(it);
     return OK;
 }
 API int q6k_sched_update(void* h, const int32_t* sampled, int n_sampled, int cap, int64_t* done, int* reasons, int* n_done) {

@@ -41,6 +41,7 @@ class StepContext:
     max_context: int = 0                  # largest position + 1 in the step
     max_q_len: int = 0
     plans: dict = field(default_factory=dict)     # per-step launch plans that parts share across layers (keyed by the part)
+    fed: Optional[torch.Tensor] = None            # int32 ids the step before sampled: a token id -(i + 1) stands for fed[i]
 
     def query_tiles(self, tokens_per_tile: int):
         """Tiles of at most `tokens_per_tile` consecutive tokens of one request, as device arrays

@@ -6,6 +6,14 @@
 Token ids in, token ids out (the reference's tokenizer and chat template,
 crates/cli/src/chat.rs, are outside this engine).  `step()` runs one scheduled batch;
 `generate()` runs until every given prompt has finished.
+
+While every live request decodes greedily, `step()` does not wait for the tokens of the step it has
+just launched: the argmax stays on the device, the next step's embedding reads it there, and the
+host plans that next step with placeholders, reading the real ids (one step late) while the GPU
+already works.  What the host needs a token's value for is the stop test; a request that turns out
+to have produced a stop token is ended then, the one token computed beyond it is dropped, and the
+tokens it returns are the same as without the look-ahead (the tests compare both).  A request with
+host-side sampling (temperature, penalties) switches the engine back to waiting for each step.
 """
 from __future__ import annotations
 
@@ -16,9 +24,14 @@ from typing import Dict, Hashable, List, Optional, Sequence, Union
 
 import torch
 
+from .. import ops
 from ..sampling import Sampler, SamplingParams, SplitMix64
+from ..sampling.sampler import pool_size
+from .batch import StepEntry
 from .runner import ModelRunner
-from .scheduler import Request, ScheduledStep, Scheduler
+from .scheduler import FINISH_CANCELLED, FINISH_STOP, Request, ScheduledStep, Scheduler
+
+PENDING = -1          # an output token whose value is still on the device
 
 
 @dataclass
@@ -30,29 +43,44 @@ class RequestOutput:
     preemptions: int = 0
 
 
+@dataclass
+class _InFlight:
+    """A launched step whose sampled ids the host has not read yet."""
+    samplers: List[Request]
+    index: List[int]                      # where each sampler's placeholder sits in its output
+    host: torch.Tensor                    # pinned int32, filled by a copy enqueued behind the step
+    ready: "torch.cuda.Event"
+
+
 class Engine:
-    def __init__(self, runner: ModelRunner, max_batch_tokens: int = 2048, max_running: Optional[int] = None):
+    def __init__(self, runner: ModelRunner, max_batch_tokens: int = 2048, max_running: Optional[int] = None,
+                 lookahead: bool = True):
         self.runner = runner
         self.scheduler = Scheduler(runner.manager, max_batch_tokens, max_running, on_admit=runner.reset_slot)
         self.sampler = Sampler()
         self._ids = itertools.count()
         self.eos = list(runner.model.spec.eos_token_ids)
-        self.stats = {"steps": 0, "tokens": 0, "preemptions": 0}
+        self.stats = {"steps": 0, "tokens": 0, "preemptions": 0, "lookahead_steps": 0}
+        self.lookahead = lookahead
+        self._inflight: Optional[_InFlight] = None
+        self._held: List[Request] = []     # ended, but their last token is still a placeholder
+        self._pinned_ids = [None, None]
+        self._flip = 0
 
     # ------------------------------------------------------------------ construction
     @classmethod
     def from_folder(cls, folder: str, dtype="bfloat16", device="cuda:0", page_size: Optional[int] = None,
                     num_pages: Union[int, Sequence[int]] = 256, max_requests: int = 64, max_batch_tokens: int = 2048,
-                    tensor_cores: bool = True) -> "Engine":
+                    tensor_cores: bool = True, lookahead: bool = True) -> "Engine":
         runner = ModelRunner.from_folder(folder, dtype, device, page_size, num_pages, max_requests, tensor_cores)
-        return cls(runner, max_batch_tokens)
+        return cls(runner, max_batch_tokens, lookahead=lookahead)
 
     @classmethod
     def from_random(cls, config, seed: int = 0, dtype="bfloat16", device="cuda:0", page_size: Optional[int] = None,
                     num_pages: Union[int, Sequence[int]] = 256, max_requests: int = 64, max_batch_tokens: int = 2048,
-                    tensor_cores: bool = True) -> "Engine":
+                    tensor_cores: bool = True, lookahead: bool = True) -> "Engine":
         runner = ModelRunner.from_random(config, seed, dtype, device, page_size, num_pages, max_requests, tensor_cores)
-        return cls(runner, max_batch_tokens)
+        return cls(runner, max_batch_tokens, lookahead=lookahead)
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt: Sequence[int], params: Optional[SamplingParams] = None, rid: Optional[Hashable] = None) -> Hashable:
@@ -89,27 +117,96 @@ class Engine:
         return rid
 
     def abort(self, rid: Hashable) -> None:
+        self._ended_early = getattr(self, "_ended_early", []) + self._resolve()     # every token known before the queue changes
         self.scheduler.abort(rid)
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._inflight is not None or bool(self._held)
 
     # ------------------------------------------------------------------ stepping
+    def _all_greedy(self) -> bool:
+        vocab = self.runner.vocab_size
+        return all(pool_size(r.params, vocab) == 1 for r in self.scheduler.by_id.values())
+
+    def _resolve(self) -> List[Request]:
+        """Read the ids of the step in flight (waits for that step only), put them where their
+        placeholders stand, end the requests that turn out to have stopped; returns the requests
+        that have ended and whose tokens are all known."""
+        flight, self._inflight = self._inflight, None
+        if flight is not None:
+            flight.ready.synchronize()
+            toks = flight.host[:len(flight.samplers)].tolist()
+            for req, at, tok in zip(flight.samplers, flight.index, toks):
+                if at >= len(req.output) or req.finish_reason == FINISH_CANCELLED:
+                    continue                   # dropped since: the request had stopped before, or was aborted
+                self.scheduler.set_output_token(req, at, tok)
+                if tok in req.params.stop_tokens:
+                    ended_before = req.finished
+                    self.scheduler.stop_at(req, at + 1)       # also outranks a provisional "length" at the same token
+                    if not ended_before:
+                        self._held.append(req)
+        out = [r for r in self._held if PENDING not in r.output]
+        self._held = [r for r in self._held if PENDING in r.output]
+        return out
+
+    def _entries(self, plan: ScheduledStep) -> List[StepEntry]:
+        """The plan's tokens; a placeholder becomes the code of the device id that stands for it."""
+        source = {id(r): i for i, r in enumerate(self._inflight.samplers)} if self._inflight is not None else {}
+        out = []
+        for e in plan.entries:
+            toks = e.request.token_slice(e.start, e.count)
+            if PENDING in toks:
+                toks = [t if t != PENDING else -(source[id(e.request)] + 1) for t in toks]
+            out.append(StepEntry(e.request.rid, toks, [e.count - 1] if e.samples else []))
+        return out
+
     def step(self) -> List[RequestOutput]:
-        """Schedule and run one batch; returns the requests that ended in it."""
+        """Schedule and run one batch; returns the requests that ended and whose tokens are all known
+        (with the look-ahead, a request is reported one call after the step that ended it)."""
+        ended: List[Request] = getattr(self, "_ended_early", [])
+        self._ended_early = []
+        ahead = self.lookahead and self._all_greedy()
+        if self._inflight is not None and not ahead:
+            ended += self._resolve()           # the host samples the next tokens itself: it needs every earlier one
         plan: ScheduledStep = self.scheduler.schedule()
         self.stats["preemptions"] += len(plan.preempted)
-        ended = list(plan.finished)
+        self._held += plan.finished
+        before = self._inflight
         if plan.entries:
-            logits = self.runner.step(plan.step_entries())
+            entries = self._entries(plan)
+            logits = self.runner.step(entries, feed_limit=len(before.samplers) if before is not None else 0)
             samplers = [e.request for e in plan.entries if e.samples]
-            sampled: List[int] = []
-            if samplers:
-                sampled = self.sampler.sample(logits, [r.params for r in samplers], [r.output for r in samplers],
-                                              [r.rng for r in samplers])
-            ended += self.scheduler.update(plan, sampled)
+            if samplers and ahead:
+                ids = ops.argmax(logits, out=self.runner.sampled)          # stays on the device for the next step's embedding
+                self._flip ^= 1
+                host = self._pinned_ids[self._flip]
+                if host is None or host.numel() < len(samplers):
+                    host = self._pinned_ids[self._flip] = torch.empty(max(64, len(samplers)), dtype=torch.int32, pin_memory=True)
+                host[:len(samplers)].copy_(ids, non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record()
+                self._held += self.scheduler.update(plan, [PENDING] * len(samplers))      # ends by length are known without the values
+                self._inflight = _InFlight(samplers, [len(r.output) - 1 for r in samplers], host, ready)
+                self.stats["lookahead_steps"] += 1
+            else:
+                sampled: List[int] = []
+                if samplers:
+                    sampled = self.sampler.sample(logits, [r.params for r in samplers], [r.output for r in samplers],
+                                                  [r.rng for r in samplers])
+                self._held += self.scheduler.update(plan, sampled)
+                self._inflight = None
             self.stats["steps"] += 1
             self.stats["tokens"] += plan.num_tokens
+        else:
+            self._inflight = None
+        # the step before: its ids have reached the host while this one was planned and launched
+        if before is not None:
+            now, self._inflight = self._inflight, before
+            ended += self._resolve()
+            self._inflight = now
+        else:
+            ended += [r for r in self._held if PENDING not in r.output]
+            self._held = [r for r in self._held if PENDING in r.output]
         return [RequestOutput(r.rid, r.prompt, list(r.output), r.finish_reason, r.preemptions) for r in ended]
 
     def generate(self, prompts: Sequence[Sequence[int]], params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> List[RequestOutput]:
@@ -121,7 +218,7 @@ class Engine:
         rids = [self.add_request(p, sp) for p, sp in zip(prompts, params)]
         results: Dict[Hashable, RequestOutput] = {}
         while len(results) < len(rids):
-            if not self.scheduler.has_work():
+            if not self.has_unfinished():
                 raise RuntimeError("the scheduler has no work left but requests are unfinished")
             for out in self.step():
                 results[out.rid] = out

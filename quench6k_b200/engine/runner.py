@@ -80,6 +80,9 @@ class ModelRunner:
         self._shapes_seen: Dict = {}
         self.max_graphs = 64
         self.graph_replays = 0
+        # ids sampled on the device by the step before (greedy decoding that does not wait for the host)
+        self.sampled = torch.zeros(max(64, max_requests), dtype=torch.int32, device=rt.device)
+        self._feed_limit = 0
         self._pinned: Optional[torch.Tensor] = None
         self._pinned_free: Optional[torch.cuda.Event] = None      # set once the last upload has left the pinned block
 
@@ -149,7 +152,7 @@ class ModelRunner:
             self._pinned = torch.empty(max(total, 4096), dtype=torch.int32, pin_memory=True)
         written, T, n_want, max_context, max_q_len = self.manager.pack_step(
             [e.rid for e in entries], [e.tokens for e in entries], [e.want for e in entries], widths, self.vocab_size,
-            self._pinned.numpy())
+            self._pinned.numpy(), self._feed_limit)
         assert written == total
         o = 3 * T
         host = self._pinned.numpy()
@@ -176,7 +179,7 @@ class ModelRunner:
         return StepContext(T=T, R=R, token_ids=d_tok, positions=d_pos, req_of_token=d_rot, q_start=d_qs, pos_start=d_ps,
                            slot_ids=d_sl, block_tables=d_tabs, logit_rows=d_lr, n_logit_rows=n_want, q_lens=q_lens,
                            pos_starts=pos_starts, slots=slots,
-                           max_context=max_context, max_q_len=max_q_len)
+                           max_context=max_context, max_q_len=max_q_len, fed=self.sampled)
 
     def _widths(self, entries: Sequence[StepEntry]) -> List[int]:
         mgr = self.manager
@@ -228,10 +231,12 @@ class ModelRunner:
     def can_run(self, entries: Sequence[StepEntry]) -> bool:
         return self.manager.can_reserve([(e.rid, len(e.tokens)) for e in entries])
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], feed_limit: int = 0) -> Optional[torch.Tensor]:
         """Run the entries' tokens as one batch; FP32 logits [wanted, vocab] in the order of the
         entries and of their `want` (None if nothing is wanted).  Raises OutOfPages, leaving every
-        request as it was, if the pools cannot hold the step."""
+        request as it was, if the pools cannot hold the step.  feed_limit > 0: a token id -(i + 1),
+        i < feed_limit, stands for self.sampled[i], an id the step before left on the device."""
+        self._feed_limit = feed_limit
         entries = [e for e in entries if len(e.tokens)]
         if not entries:
             return None

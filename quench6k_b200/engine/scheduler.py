@@ -155,6 +155,18 @@ class PyScheduler:
     def has_work(self) -> bool:
         return bool(self.waiting or self.running)
 
+    def set_output_token(self, req: Request, index: int, token: int) -> None:
+        """A token that was entered as a placeholder (the step that samples it was still running) gets its value."""
+        req.output[index] = int(token)
+
+    def stop_at(self, req: Request, n_keep: int) -> None:
+        """The request turns out to have ended with its n_keep-th output token (a stop token that
+        was still a placeholder when later steps were planned): what came after is dropped."""
+        del req.output[n_keep:]
+        if req.rid in self.by_id and not req.finished:
+            self._finish(req, FINISH_STOP)
+        req.finish_reason = FINISH_STOP
+
     def _finish(self, req: Request, reason: str) -> None:
         req.finish_reason = reason
         if req in self.running:
@@ -373,6 +385,21 @@ class NativeScheduler:
         w, r = ctypes.c_int32(), ctypes.c_int32()
         raise_for(self._lib.q6k_sched_counts(self._h, ctypes.byref(w), ctypes.byref(r)))
         return bool(w.value or r.value)
+
+    def set_output_token(self, req: Request, index: int, token: int) -> None:
+        """A token that was entered as a placeholder (the step that samples it was still running) gets its value."""
+        req.output[index] = int(token)
+        if req.rid in self.by_id:
+            raise_for(self._lib.q6k_sched_set_output_token(self._h, self.manager._nid[req.rid], index, int(token)))
+
+    def stop_at(self, req: Request, n_keep: int) -> None:
+        """The request turns out to have ended with its n_keep-th output token (a stop token that
+        was still a placeholder when later steps were planned): what came after is dropped."""
+        del req.output[n_keep:]
+        if req.rid in self.by_id:
+            raise_for(self._lib.q6k_sched_stop(self._h, self.manager._nid[req.rid], n_keep))
+            self._drop(req)
+        req.finish_reason = FINISH_STOP
 
     # ------------------------------------------------------------------ one step
     def schedule(self) -> ScheduledStep:

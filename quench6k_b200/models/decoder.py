@@ -86,7 +86,7 @@ class DecoderModel:
     def forward(self, ctx, caches: List[Optional[LayerCache]], states: List[Optional[torch.Tensor]]) -> Optional[torch.Tensor]:
         """Runs the tokens of `ctx` through the executed layers; returns FP32 logits
         [len(ctx.logit_rows), vocab] or None when no row is wanted."""
-        h = ops.embed(ctx.token_ids, self.embed)
+        h = ops.embed(ctx.token_ids, self.embed, fed=ctx.fed)
         pending = None                      # an add into h that a block has left to the next norm
         for p, i in enumerate(self.order):
             pending = self.blocks[i].forward(h, ctx, caches[p], states[p], pending)

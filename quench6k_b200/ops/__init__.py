@@ -71,16 +71,20 @@ _ll = ctypes.c_longlong
 
 
 # --------------------------------------------------------------------------- elementwise
-def embed(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """h[t] = float32(table[tokens[t]])."""
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: Optional[torch.Tensor] = None, fed: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """h[t] = float32(table[tokens[t]]).  With `fed` (int32 on the device), a token id -(i + 1)
+    stands for fed[i]: a token the step before has sampled and the host has not read yet."""
     T = tokens.numel()
     V, D = table.shape
     _need(tokens, "tokens", torch.int32)
     _need(table, "table")
+    if fed is not None:
+        _need(fed, "fed", torch.int32)
     if out is None:
         out = torch.empty((T, D), dtype=torch.float32, device=table.device)
     _need(out, "out", torch.float32, (T, D))
-    _call("q6k_embed", _ptr(tokens), _ptr(table), _ptr(out), _i(T), _i(D), _i(V), _i(dtype_code(table.dtype)), _stream())
+    _call("q6k_embed", _ptr(tokens), _ptr(table), _ptr(out), _i(T), _i(D), _i(V), _i(dtype_code(table.dtype)), _ptr(fed),
+          _i(fed.numel() if fed is not None else 0), _stream())
     return out
 
 
@@ -571,11 +575,17 @@ def moe_permute(sel_e: torch.Tensor, E: int):
 
 
 # --------------------------------------------------------------------------- sampling
-def argmax(logits: torch.Tensor) -> torch.Tensor:
-    """int32 [rows]; ties go to the lower id."""
+def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """int32 [rows]; ties go to the lower id.  `out`: an int32 buffer of at least `rows` entries to write into."""
     _need(logits, "logits", torch.float32)
     rows, V = logits.shape
-    out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    else:
+        _need(out, "out", torch.int32)
+        if out.numel() < rows:
+            raise KernelError(f"argmax: the output buffer holds {out.numel()} ids, {rows} rows are asked for")
+        out = out[:rows]
     lib = library()
     lib.q6k_argmax_scratch_ints.restype = ctypes.c_int
     scratch = torch.empty(lib.q6k_argmax_scratch_ints(_i(rows), _i(V)), dtype=torch.int32, device=logits.device)

@@ -164,3 +164,40 @@ def test_launch_modes_give_the_same_logits(tmp_path):
         digests[mode] = line[1]
         assert int(line[2]) > 0                          # the decode steps did replay a graph
     assert digests["0"] == digests["gemm"] == digests["1"], digests
+
+
+@pytest.mark.parametrize("name,pages,preempts", [("A", 64, False), ("A", 14, True), ("B", 24, False)])
+def test_lookahead_gives_the_same_tokens(tmp_path, name, pages, preempts):
+    """Greedy decoding without waiting for each step's tokens (they stay on the device, the host
+    reads them one step late) against the engine that waits: the same tokens, finish reasons and
+    preemption-safe bookkeeping, with stop tokens that do occur, ends by length, prompts cut into
+    portions, and (14 pages) so few pages that requests are preempted."""
+    import random
+    from quench6k_b200 import Engine, SamplingParams
+    cfg, _ = helpers.make_model_folder(str(tmp_path), name, seed=41)
+    rng = random.Random(7)
+    prompts = [helpers.random_tokens(rng.randint(3, 25), cfg["vocab_size"], 900 + i) for i in range(7)]
+    plain = Engine.from_folder(str(tmp_path), dtype="float32", num_pages=pages, max_batch_tokens=9, lookahead=False)
+    free = plain.generate(prompts, SamplingParams(max_tokens=18, temperature=0.0))
+    # stop tokens taken from what the requests really produce, at different depths; some never stop
+    params = []
+    for i, o in enumerate(free):
+        stops = [o.tokens[2 + i % 9]] if i % 3 != 2 else []
+        params.append(SamplingParams(max_tokens=5 + 3 * i, temperature=0.0, stop_tokens=stops))
+    want = plain.generate(prompts, params)
+    assert plain.stats["lookahead_steps"] == 0
+    ahead = Engine.from_folder(str(tmp_path), dtype="float32", num_pages=pages, max_batch_tokens=9)
+    got = ahead.generate(prompts, params)
+    assert ahead.stats["lookahead_steps"] > 0
+    for w, g in zip(want, got):
+        assert (g.tokens, g.finish_reason) == (w.tokens, w.finish_reason)
+    assert {o.finish_reason for o in got} == {"stop", "length"}
+    for eng in (plain, ahead):
+        eng.runner.manager.check()
+        assert not eng.runner.manager.requests and not eng.has_unfinished()
+    if preempts:
+        assert ahead.stats["preemptions"] > 0 and plain.stats["preemptions"] > 0
+    # a request that samples on the host switches the engine back to waiting for each step
+    mixed = Engine.from_folder(str(tmp_path), dtype="float32", num_pages=64, max_batch_tokens=9)
+    outs = mixed.generate(prompts[:3], [params[0], SamplingParams(max_tokens=6, temperature=0.9, seed=3), params[2]])
+    assert (outs[0].tokens, outs[2].tokens) == (want[0].tokens, want[2].tokens) and len(outs[1].tokens) == 6

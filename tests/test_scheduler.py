@@ -206,3 +206,35 @@ def test_both_schedulers_decide_alike(seed):
                          [(r.rid, r.num_computed, list(r.output)) for r in s.running], [r.rid for r in s.waiting]))
         assert seen[0] == seen[1], f"step {step}"
     assert total == 30 and not pair[0][1].has_work()
+
+
+def test_placeholder_tokens_are_patched_and_a_late_stop_ends_the_request():
+    """What the engine's look-ahead needs: a step is planned while the token before it is still a
+    placeholder (-1); the value arrives later; a stop token found then ends the request at that
+    token, whatever was planned or produced after it."""
+    m, s = make(pages=32, budget=8)
+    a, b = req("a", 5, max_tokens=10, stop_tokens=[3]), req("b", 6, max_tokens=2, stop_tokens=[3])
+    s.add(a), s.add(b)
+    run_step(m, s, lambda q: -1)                             # a's prompt and first token; three tokens of b's prompt
+    plan, done = run_step(m, s, lambda q: -1)                # a decodes from a placeholder; b's prompt ends
+    assert a.output == [-1, -1] and b.output == [-1] and not done
+    assert [t for e in plan.step_entries() if e.rid == "a" for t in e.tokens] == [-1]
+    s.set_output_token(a, 0, 7)
+    s.set_output_token(b, 0, 3)                              # b's first token was a stop token: it ends there
+    s.stop_at(b, 1)
+    assert b.finish_reason == FINISH_STOP and b.output == [3] and m.slots.num_free == 3
+    plan, done = run_step(m, s, lambda q: -1)
+    assert [e.request.rid for e in plan.entries] == ["a"] and a.output == [7, -1, -1]
+    s.set_output_token(a, 1, 3)                              # found a step late: the token after it is dropped
+    s.stop_at(a, 2)
+    assert a.finish_reason == FINISH_STOP and a.output == [7, 3]
+    assert not s.has_work() and m.pools[0].num_free == 32 and m.slots.num_free == 4
+    m.check()
+    # a request that had already ended by length at the very token that turns out to be a stop token
+    c = req("c", 3, max_tokens=1, stop_tokens=[3])
+    s.add(c)
+    plan, done = run_step(m, s, lambda q: -1)
+    assert done == [c] and c.finish_reason == FINISH_LENGTH
+    s.set_output_token(c, 0, 3)
+    s.stop_at(c, 1)
+    assert c.finish_reason == FINISH_STOP and c.output == [3] and not s.has_work()

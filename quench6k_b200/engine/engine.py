@@ -66,6 +66,7 @@ class Engine:
         self._held: List[Request] = []     # ended, but their last token is still a placeholder
         self._pinned_ids = [None, None]
         self._flip = 0
+        self._ended_early: List[Request] = []     # ended outside step() (resolved by abort), reported by the next step()
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -117,7 +118,7 @@ class Engine:
         return rid
 
     def abort(self, rid: Hashable) -> None:
-        self._ended_early = getattr(self, "_ended_early", []) + self._resolve()     # every token known before the queue changes
+        self._ended_early += self._resolve()     # every token known before the queue changes
         self.scheduler.abort(rid)
 
     def has_unfinished(self) -> bool:
@@ -163,8 +164,7 @@ class Engine:
     def step(self) -> List[RequestOutput]:
         """Schedule and run one batch; returns the requests that ended and whose tokens are all known
         (with the look-ahead, a request is reported one call after the step that ended it)."""
-        ended: List[Request] = getattr(self, "_ended_early", [])
-        self._ended_early = []
+        ended, self._ended_early = self._ended_early, []
         ahead = self.lookahead and self._all_greedy()
         if self._inflight is not None and not ahead:
             ended += self._resolve()           # the host samples the next tokens itself: it needs every earlier one

@@ -201,3 +201,50 @@ def test_lookahead_gives_the_same_tokens(tmp_path, name, pages, preempts):
     mixed = Engine.from_folder(str(tmp_path), dtype="float32", num_pages=64, max_batch_tokens=9)
     outs = mixed.generate(prompts[:3], [params[0], SamplingParams(max_tokens=6, temperature=0.9, seed=3), params[2]])
     assert (outs[0].tokens, outs[2].tokens) == (want[0].tokens, want[2].tokens) and len(outs[1].tokens) == 6
+
+
+@pytest.mark.parametrize("seed", [0, 1])
+def test_random_traffic_with_and_without_lookahead(tmp_path, seed):
+    """Requests arriving over time (greedy and sampled ones mixed, stop tokens, aborts, so few pages
+    that some are preempted) through an engine that waits for each step and one that looks ahead:
+    every request that was not aborted ends with the same tokens and reason, the cache manager's
+    invariants hold after every step, nothing is left behind."""
+    import random
+    from quench6k_b200 import Engine, SamplingParams, ops
+    helpers.make_model_folder(str(tmp_path), "A", seed=5)
+
+    def run(lookahead):
+        rng = random.Random(seed)
+        eng = Engine.from_folder(str(tmp_path), dtype="float32", num_pages=30, max_requests=6, max_batch_tokens=rng.choice([7, 16, 40]),
+                                 lookahead=lookahead)
+        V, n, results, live, aborted = eng.runner.vocab_size, 0, {}, set(), set()
+        for step in range(160):
+            if n < 28 and rng.random() < 0.3:
+                sp = SamplingParams(max_tokens=rng.randint(1, 20), temperature=0.0 if rng.random() < 0.8 else 0.8, seed=rng.randrange(1 << 30),
+                                    stop_tokens=[rng.randrange(V) for _ in range(rng.choice([0, 0, 3, 40]))])
+                eng.add_request([rng.randrange(V) for _ in range(rng.randint(1, 30))], sp, rid=n)
+                live.add(n)
+                n += 1
+            victim = rng.randrange(max(1, n)) if rng.random() < 0.05 else None
+            if victim in live and victim not in results:
+                eng.abort(victim)
+                aborted.add(victim)
+                live.discard(victim)
+            if eng.has_unfinished():
+                for o in eng.step():
+                    results[o.rid] = (o.tokens, o.finish_reason)
+            eng.runner.manager.check()
+        while eng.has_unfinished():
+            for o in eng.step():
+                results[o.rid] = (o.tokens, o.finish_reason)
+        eng.runner.manager.check()
+        assert not eng.runner.manager.requests and ops.tc_status() == 0
+        return results, aborted, eng.stats
+
+    waits, aborted_w, _ = run(False)
+    ahead, aborted_a, stats = run(True)
+    assert stats["lookahead_steps"] > 10
+    same = [k for k in waits if k not in aborted_w and k not in aborted_a]
+    assert len(same) >= 15
+    for k in same:
+        assert ahead[k] == waits[k], k

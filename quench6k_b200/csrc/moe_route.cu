@@ -248,7 +248,10 @@ __global__ void count_kernel(const int* sel_e, int pairs, int E, int* counts) {
 
 // counts[c, e] -> the chunk's first row within its expert (in place), and offsets = exclusive
 // scan over the experts of their totals (E + 1 entries).  One block.
-__global__ void offsets_kernel(int* counts, int chunks, int E, int* offsets) {
+__device__ void tiles_in_block(const int* offsets, int G, int bm, int* tile_group, int* tile_row0, int* num_tiles, int max_tiles);
+
+__global__ void offsets_kernel(int* counts, int chunks, int E, int* offsets, int bm, int* tile_group, int* tile_row0, int* num_tiles,
+                               int max_tiles) {
     pdl_enter();
     __shared__ int part[1024];
     const int tid = threadIdx.x, n = blockDim.x;
@@ -286,6 +289,10 @@ __global__ void offsets_kernel(int* counts, int chunks, int E, int* offsets) {
         offsets[e] = run;
         run += total;
     }
+    if (tile_group != nullptr) {
+        __syncthreads();                       // this block's offsets are complete and visible to it
+        tiles_in_block(offsets, E, bm, tile_group, tile_row0, num_tiles, max_tiles);
+    }
 }
 
 // One warp per (expert, chunk): the row of each of its pairs is the expert's offset plus the
@@ -309,6 +316,42 @@ __global__ void rank_kernel(const int* sel_e, const int* chunk_base, const int* 
         }
         base += __popc(mask);
     }
+}
+
+// The list of row tiles of `bm` rows of the groups, made by the block that has just made the offsets
+// (the arithmetic of tile_list_kernel of the CUDA-core product file).
+__device__ void tiles_in_block(const int* offsets, int G, int bm, int* tile_group, int* tile_row0, int* num_tiles, int max_tiles) {
+    __shared__ int base;
+    __shared__ int scan[256];
+    if (threadIdx.x == 0) base = 0;
+    __syncthreads();
+    for (int g0 = 0; g0 < G; g0 += blockDim.x) {
+        const int g = g0 + threadIdx.x;
+        int mine = 0;
+        if (g < G) mine = (offsets[g + 1] - offsets[g] + bm - 1) / bm;
+        scan[threadIdx.x] = mine;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            int run = base;
+            for (int i = 0; i < (int)blockDim.x; ++i) {
+                const int cnt = scan[i];
+                scan[i] = run;
+                run += cnt;
+            }
+            base = run;
+        }
+        __syncthreads();
+        if (g < G) {
+            const int first = scan[threadIdx.x];
+            for (int i = 0; i < mine; ++i)
+                if (first + i < max_tiles) {
+                    tile_group[first + i] = g;
+                    tile_row0[first + i] = offsets[g] + i * bm;
+                }
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) *num_tiles = base < max_tiles ? base : max_tiles;
 }
 
 }  // namespace
@@ -349,7 +392,22 @@ Q6K_API int q6k_moe_permute(const int* sel_e, int pairs, int k, int E, int* scra
     Q6K_REQUIRE(chunks <= 65535, "moe_permute: %d pairs exceed the grid limit", pairs);
     const dim3 grid((E + 7) / 8, chunks);
     q6k_launch(count_kernel, grid, 256, 0, st, sel_e, pairs, E, scratch);
-    q6k_launch(offsets_kernel, 1, 256, 0, st, scratch, chunks, E, offsets);
+    q6k_launch(offsets_kernel, 1, 256, 0, st, scratch, chunks, E, offsets, 0, (int*)nullptr, (int*)nullptr, (int*)nullptr, 0);
     q6k_launch(rank_kernel, grid, 256, 0, st, sel_e, scratch, offsets, pairs, k, E, pair_row, row_token);
     return q6k_check_launch("moe_permute");
+}
+
+// The permutation and the list of row tiles of bm rows (tile_group, tile_row0: max_tiles entries; num_tiles: 1) in
+// three launches (the block that makes the offsets also makes the tile list).
+Q6K_API int q6k_moe_plan(const int* sel_e, int pairs, int k, int E, int* scratch, int* offsets, int* pair_row, int* row_token, int bm,
+                         int* tile_group, int* tile_row0, int* num_tiles, int max_tiles, cudaStream_t st) {
+    if (pairs == 0) return 0;
+    Q6K_REQUIRE(pairs > 0 && k > 0 && E > 0 && bm > 0 && max_tiles > 0, "moe_plan: bad sizes pairs=%d k=%d E=%d bm=%d", pairs, k, E, bm);
+    const int chunks = (pairs + PERM_CHUNK - 1) / PERM_CHUNK;
+    Q6K_REQUIRE(chunks <= 65535, "moe_plan: %d pairs exceed the grid limit", pairs);
+    const dim3 grid((E + 7) / 8, chunks);
+    q6k_launch(count_kernel, grid, 256, 0, st, sel_e, pairs, E, scratch);
+    q6k_launch(offsets_kernel, 1, 256, 0, st, scratch, chunks, E, offsets, bm, tile_group, tile_row0, num_tiles, max_tiles);
+    q6k_launch(rank_kernel, grid, 256, 0, st, sel_e, scratch, offsets, pairs, k, E, pair_row, row_token);
+    return q6k_check_launch("moe_plan");
 }

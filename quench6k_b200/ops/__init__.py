@@ -49,7 +49,7 @@ def _need(t: torch.Tensor, name: str, dtype=None, shape=None):
 
 
 # kernels launched per exported function (for launch accounting in benchmarks)
-_LAUNCHES = {"q6k_moe_permute": 3, "q6k_gemm_tc": 1, "q6k_attention_mma": 2, "q6k_argmax": 2, "q6k_gemm_tc_pairs_scratch": 0}
+_LAUNCHES = {"q6k_moe_permute": 3, "q6k_moe_plan": 3, "q6k_gemm_tc": 1, "q6k_attention_mma": 2, "q6k_argmax": 2, "q6k_gemm_tc_pairs_scratch": 0}
 launch_count = 0
 
 
@@ -572,6 +572,28 @@ def moe_permute(sel_e: torch.Tensor, E: int):
     _call("q6k_moe_permute", _ptr(sel_e), _i(pairs), _i(k), _i(E), _ptr(scratch), _ptr(offsets), _ptr(pair_row),
           _ptr(row_token), _stream())
     return offsets, pair_row, row_token
+
+
+def moe_plan(sel_e: torch.Tensor, E: int, bm: int):
+    """The permutation of `moe_permute` and the row tiles of `tile_list(offsets, pairs, bm)` in three
+    launches instead of four: (offsets, pair_row, row_token, (offsets, tile_group, tile_row0, num_tiles))."""
+    _need(sel_e, "sel_e", torch.int32)
+    T, k = sel_e.shape
+    pairs = T * k
+    dev = sel_e.device
+    lib = library()
+    lib.q6k_moe_permute_scratch_ints.restype = ctypes.c_int
+    scratch = torch.empty(lib.q6k_moe_permute_scratch_ints(_i(pairs), _i(E)), dtype=torch.int32, device=dev)
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    pair_row = torch.empty((T, k), dtype=torch.int32, device=dev)
+    row_token = torch.empty(pairs, dtype=torch.int32, device=dev)
+    max_tiles = pairs // bm + min(pairs, E)          # full tiles plus at most one ragged tile per non-empty group
+    tile_group = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+    tile_row0 = torch.empty(max_tiles, dtype=torch.int32, device=dev)
+    num_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+    _call("q6k_moe_plan", _ptr(sel_e), _i(pairs), _i(k), _i(E), _ptr(scratch), _ptr(offsets), _ptr(pair_row), _ptr(row_token), _i(bm),
+          _ptr(tile_group), _ptr(tile_row0), _ptr(num_tiles), _i(max_tiles), _stream())
+    return offsets, pair_row, row_token, (offsets, tile_group, tile_row0, num_tiles)
 
 
 # --------------------------------------------------------------------------- sampling

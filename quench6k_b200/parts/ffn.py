@@ -93,13 +93,12 @@ class RoutedExperts(FeedForward):
             return None
         logits = linear.matmul(xn, self.w_router, rt)                       # FP32 [T, E]
         sel_e, sel_w = ops.route(logits, self.k, self.scoring, self.renorm)
-        offsets, pair_row, row_token = ops.moe_permute(sel_e, self.E)
-        plan = linear.group_plan(xn, self.w_gate, offsets, row_token, pairs, rt)
+        plan = linear.group_plan(xn, self.w_gate, sel_e, rt)             # permutation by expert, row tiles, gathered rows
         act = linear.grouped_swiglu(xn, plan, self.w_gate, self.w_up, rt)                         # [pairs, I]
         y = linear.grouped_matmul(act, plan, self.w_down, rt)                                     # FP32 [pairs, D]
         if defer:
-            return WeightedRows(y, sel_w, pair_row)
-        ops.combine(y, pair_row, sel_w, out)
+            return WeightedRows(y, sel_w, plan.pair_row)
+        ops.combine(y, plan.pair_row, sel_w, out)
         if self.shared is not None:
             self.shared.forward(xn, ctx, out)
         return None

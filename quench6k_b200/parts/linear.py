@@ -37,29 +37,32 @@ def swiglu_matmul(a: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, rt)
 
 
 class GroupPlan:
-    """Row tiles of the experts' groups for one permutation, for whichever kernel runs them."""
+    """The permutation of a step's (token, slot) pairs by expert and the row tiles of the experts'
+    groups, for whichever kernel runs them; on the tensor-core path also the gathered input rows."""
 
-    def __init__(self, offsets: torch.Tensor, row_token: torch.Tensor, pairs: int, num_groups: int, rt, tc: bool):
-        self.pairs, self.row_token, self.tc = pairs, row_token, tc
+    def __init__(self, a: torch.Tensor, sel_e: torch.Tensor, num_groups: int, rt, tc: bool):
+        self.pairs, self.tc, self.xs = sel_e.numel(), tc, None
         if tc:
-            avg = max(1, pairs // max(1, num_groups))
+            avg = max(1, self.pairs // max(1, num_groups))
             want = avg + avg // 2
             self.bt_dual = ops.tc_token_tile(want, True)
             self.bt = self.bt_dual
-            self.tiles = ops.tile_list(offsets, pairs, self.bt)
+            # permutation and tile list in three launches; the gather of the input rows stays a launch of its own (a
+            # block per row: folded into the ranking warps it was measured 6 ms slower per 2,048-token prefill)
+            self.offsets, self.pair_row, self.row_token, self.tiles = ops.moe_plan(sel_e, num_groups, self.bt)
+            self.xs = ops.gather_rows(a, self.row_token)
         else:
-            self.tiles = ops.tile_list(offsets, pairs, ops.simt_tile_rows())
+            self.offsets, self.pair_row, self.row_token, self.tiles = ops.moe_plan(sel_e, num_groups, ops.simt_tile_rows())
 
 
-def group_plan(a: torch.Tensor, w: torch.Tensor, offsets, row_token, pairs: int, rt) -> GroupPlan:
-    return GroupPlan(offsets, row_token, pairs, w.shape[0], rt, _tc(a, w, rt))
+def group_plan(a: torch.Tensor, w: torch.Tensor, sel_e: torch.Tensor, rt) -> GroupPlan:
+    return GroupPlan(a, sel_e, w.shape[0], rt, _tc(a, w, rt) and a.is_contiguous())
 
 
 def grouped_swiglu(a: torch.Tensor, plan: GroupPlan, w_gate: torch.Tensor, w_up: torch.Tensor, rt) -> torch.Tensor:
     """act[row] = SwiGLU of a[row_token[row]] with the weights of the row's group; [pairs, I]."""
     if plan.tc:
-        xs = ops.gather_rows(a, plan.row_token)
-        return ops.gemm_tc(xs, w_gate, w2=w_up, groups=plan.tiles, bt=plan.bt, rows=plan.pairs)
+        return ops.gemm_tc(plan.xs, w_gate, w2=w_up, groups=plan.tiles, bt=plan.bt, rows=plan.pairs)
     return ops.gemm_simt(a, w_gate, w2=w_up, a_rows=plan.row_token, groups=plan.tiles, rows=plan.pairs)
 
 

@@ -117,6 +117,20 @@ def test_grouped_gemm_and_permutation(dtype):
     assert (h.double().cpu() - want).abs().max() <= 1e-5 * want.abs().max()
 
 
+@pytest.mark.parametrize("T,k,E,D,bm", [(37, 3, 10, 56, 16), (2048, 8, 256, 64, 128), (300, 1, 7, 8, 32), (1500, 6, 33, 24, 64)])
+def test_moe_plan_equals_its_parts(T, k, E, D, bm):
+    """Permutation and tile list in three launches against the four single ones: the same arrays."""
+    from quench6k_b200 import ops
+    g = torch.Generator().manual_seed(T + E)
+    sel = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32).to(DEV)
+    offsets, pair_row, row_token = ops.moe_permute(sel, E)
+    tiles = ops.tile_list(offsets, T * k, bm)
+    o2, p2, r2, t2 = ops.moe_plan(sel, E, bm)
+    assert torch.equal(o2, offsets) and torch.equal(p2, pair_row) and torch.equal(r2, row_token)
+    n = int(tiles[3])
+    assert int(t2[3]) == n and torch.equal(t2[1][:n], tiles[1][:n]) and torch.equal(t2[2][:n], tiles[2][:n])
+
+
 @pytest.mark.parametrize("scoring", ["softmax", "sigmoid"])
 @pytest.mark.parametrize("renorm", [True, False])
 @pytest.mark.parametrize("T,E,k", [(9, 6, 3), (40, 256, 8), (5, 100, 100), (3, 3000, 6)])

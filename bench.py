@@ -252,7 +252,8 @@ def main():
     point_batches = [int(x) for x in args.points.split(",") if x.strip()]
     max_b = max([args.batch] + point_batches)
     ctx = args.context
-    pages_per_req = (ctx + 64 + page - 1) // page + 1
+    headroom = max(64, args.steps + args.warmup + 16)            # every timed request decodes that many tokens past its context
+    pages_per_req = (ctx + headroom + page - 1) // page + 1
     num_pages = max(max_b * pages_per_req, (args.prefill_tokens + page - 1) // page + 1)
     t0 = time.time()
     eng = Engine.from_random(cfg, seed=0, dtype=args.dtype, page_size=page, num_pages=num_pages, max_requests=max_b,

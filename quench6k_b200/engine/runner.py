@@ -9,6 +9,7 @@ crates/engine/src/flint.rs:699-771; batches of one-token segments, crates/engine
 from __future__ import annotations
 
 import os
+from collections import OrderedDict
 from typing import Dict, Hashable, List, Optional, Sequence, Union
 
 import numpy as np
@@ -76,7 +77,7 @@ class ModelRunner:
         # steps whose shape repeats (above all decode steps) replay a CUDA graph per shape; the
         # reference captures one per sequence and token count (crates/engine/src/flint.rs:735-771)
         self.cuda_graphs = cuda_graphs and model.graph_safe()
-        self._graphs: Dict = {}
+        self._graphs: "OrderedDict" = OrderedDict()       # least recently replayed first; at most max_graphs are kept
         self._shapes_seen: Dict = {}
         self.max_graphs = 64
         self.graph_replays = 0
@@ -200,7 +201,7 @@ class ModelRunner:
             decode = all(len(e.tokens) == 1 for e in entries)
             seen = self._shapes_seen.get(key, 0) + 1
             self._shapes_seen[key] = seen
-            if not decode and (seen < 2 or len(self._graphs) >= self.max_graphs):
+            if not decode and seen < 2:
                 if len(self._shapes_seen) > 4096:
                     self._shapes_seen.clear()
                 return self.model.forward(self._context(entries), self.caches, self.states)
@@ -220,7 +221,10 @@ class ModelRunner:
             with torch.cuda.graph(graph):
                 out = self.model.forward(ctx, self.caches, self.states)
             self._graphs[key] = (graph, ctx, static, out, ops.launch_count - before)
+            while len(self._graphs) > self.max_graphs:              # the graph replayed longest ago goes, with its buffers
+                self._graphs.popitem(last=False)
             return result
+        self._graphs.move_to_end(key)
         graph, ctx, static, out, launches = slot
         self._context(entries, widths, static)
         graph.replay()

@@ -248,3 +248,27 @@ def test_random_traffic_with_and_without_lookahead(tmp_path, seed):
     assert len(same) >= 15
     for k in same:
         assert ahead[k] == waits[k], k
+
+
+def test_graph_cache_is_bounded(tmp_path):
+    """Only the most recently replayed step shapes keep their CUDA graph; a shape whose graph was
+    dropped is recorded again and gives the same logits as eager steps."""
+    from quench6k_b200.engine import ModelRunner, StepEntry
+    cfg, _ = helpers.make_model_folder(str(tmp_path), "A", seed=33)
+    prompts = {f"r{i}": helpers.random_tokens(5 + i, cfg["vocab_size"], 800 + i) for i in range(3)}
+    tails = {rid: helpers.random_tokens(12, cfg["vocab_size"], 900 + i) for i, rid in enumerate(prompts)}
+    outs = {}
+    for graphs in (False, True):
+        runner = ModelRunner.from_folder(str(tmp_path), dtype="float32", num_pages=32, cuda_graphs=graphs)
+        runner.max_graphs = 2
+        for rid, p in prompts.items():
+            runner.add_request(rid)
+            runner.step([StepEntry(rid, p, [])])
+        got = []
+        for i in range(12):
+            live = list(prompts)[: 1 + i % 3]                                # three batch sizes in turn: three shapes
+            got.append(runner.step([StepEntry(rid, [tails[rid][i]], [0]) for rid in live]).clone().cpu())
+            assert len(runner._graphs) <= 2
+        outs[graphs] = got
+    for a, b in zip(outs[False], outs[True]):
+        assert torch.equal(a, b)

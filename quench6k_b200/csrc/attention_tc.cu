@@ -189,7 +189,9 @@ __global__ void __launch_bounds__(TC_THREADS) attention_tc_kernel(const __grid_c
     const uint32_t k_full0 = smem_u32(&bars[0]), k_empty0 = smem_u32(&bars[3]), v_full0 = smem_u32(&bars[6]), v_empty0 = smem_u32(&bars[8]);
     const uint32_t s_full0 = smem_u32(&bars[10]), p_full0 = smem_u32(&bars[12]), pv_done0 = smem_u32(&bars[14]), q_full0 = smem_u32(&bars[16]), p_full1 = smem_u32(&bars[18]);
 
-    const int tile = gridDim.x - 1 - blockIdx.x, kh = blockIdx.y;      // later tiles see more keys: start them first
+    // the KV heads of a tile side by side, the tiles in the order of the list (the host puts those with the
+    // most keys first, so that the long ones of every head start in the first wave of CTAs)
+    const int tile = blockIdx.y, kh = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = p.G;
     // the two halves: two tiles of one request (their tokens, positions and ranges of key tiles);
@@ -594,7 +596,7 @@ Q6K_API int q6k_attention_tc(const void* q, const void* k_pages, const void* v_p
     Q6K_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention_tc: bad head counts Hq=%d Hkv=%d", Hq, Hkv);
     const int G = Hq / Hkv;
     Q6K_REQUIRE(q6k_attention_tc_supported(hd, G, page_size), "attention_tc: head_dim %d / group size %d / page size %d is not covered", hd, G, page_size);
-    Q6K_REQUIRE(max_blocks > 0 && window >= 0 && Hkv <= 65535, "attention_tc: bad max_blocks %d / window %d / Hkv %d", max_blocks, window, Hkv);
+    Q6K_REQUIRE(max_blocks > 0 && window >= 0 && n_tiles <= 65535, "attention_tc: bad max_blocks %d / window %d / %d tiles", max_blocks, window, n_tiles);
     const long long pool_rows = num_pages * Hkv * page_size;
     Q6K_REQUIRE(pool_rows < (1LL << 31) && ((uintptr_t)k_pages & 15) == 0 && ((uintptr_t)v_pages & 15) == 0 && ((uintptr_t)q & 15) == 0 &&
                     ((uintptr_t)out & 15) == 0,
@@ -617,6 +619,6 @@ Q6K_API int q6k_attention_tc(const void* q, const void* k_pages, const void* v_p
             return q6k_check_launch("attention_tc: shared memory attribute");
         configured = true;
     }
-    q6k_launch(attention_tc_kernel, dim3(n_tiles, Hkv), TC_THREADS, smem, st, tk, tv, tk_run, tv_run, p);
+    q6k_launch(attention_tc_kernel, dim3(Hkv, n_tiles), TC_THREADS, smem, st, tk, tv, tk_run, tv_run, p);
     return q6k_check_launch("attention_tc");
 }

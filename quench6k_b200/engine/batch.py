@@ -63,22 +63,25 @@ class StepContext:
         token count; a lone tile's partner has no tokens) and their number.  zigzag: a request's
         last tile goes with its first, the one before with the second, ... (under a causal mask
         the late tile's keys include the early tile's, and every pair has the same amount of work);
-        else neighbours go together (their key ranges nearly coincide: the choice for a window)."""
+        else neighbours go together (their key ranges nearly coincide: the choice for a window).
+        The pairs come sorted by the number of keys they see, most first."""
         key = ("query_tile_pairs", tokens_per_tile, zigzag)
         if key not in self.plans:
-            first, count, at = [], [], 0
-            for n in self.q_lens:
+            pairs, at = [], 0                            # (keys the pair's later tile sees, first rows, counts)
+            for r, n in enumerate(self.q_lens):
                 tiles = [(at + i, min(tokens_per_tile, n - i)) for i in range(0, n, tokens_per_tile)]
                 k = len(tiles)
+                start = self.pos_starts[r] if r < len(self.pos_starts) else 0
+                keys = lambda t: start + (t[0] - at) + t[1]
                 order = [(k - 1 - j, j) for j in range(k // 2)] if zigzag else [(j + 1, j) for j in range(0, k - 1, 2)]
                 for a, b in order:                       # the later tile first: it decides the pair's key range
-                    first.append([tiles[a][0], tiles[b][0]])
-                    count.append([tiles[a][1], tiles[b][1]])
+                    pairs.append((keys(tiles[a]), [tiles[a][0], tiles[b][0]], [tiles[a][1], tiles[b][1]]))
                 if k % 2:
                     lone = tiles[k // 2] if zigzag else tiles[k - 1]
-                    first.append([lone[0], lone[0]])
-                    count.append([lone[1], 0])
+                    pairs.append((keys(lone), [lone[0], lone[0]], [lone[1], 0]))
                 at += n
+            pairs.sort(key=lambda p: -p[0])              # the pairs with the most keys first (stable: ties keep their order)
+            first, count = [p[1] for p in pairs], [p[2] for p in pairs]
             both = torch.tensor([first, count], dtype=torch.int32).to(self.token_ids.device, non_blocking=True)
             self.plans[key] = (both[0].contiguous(), both[1].contiguous(), len(first))
         return self.plans[key]

@@ -39,6 +39,11 @@ CONFIG2 = {
 }
 
 
+# the further shapes this file can run: the full-depth model (about 80 GB of weights) at 8,192 cached tokens
+SHAPES = {2: {"layers": 24, "context": 32768, "label": "Recursive Flint MoE, half-depth shape"},
+          3: {"layers": 48, "context": 8192, "label": "Recursive Flint MoE, 40B-A2.5B shape"}}
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -203,6 +208,75 @@ def kernel_attention_prefill(args):
     return 0
 
 
+def workload_stress(args, shape):
+    """A long prompt beside many short sampled requests, through the engine's own scheduler and
+    paged cache: one request of `--context` (131,072) uniform-random tokens, greedy, 128 new tokens;
+    `--batch - 1` (63) requests of 256 to 16,384 tokens at temperature 1.0, 128 new tokens each.
+    Host wall clock around Engine.step() until everything has finished; one JSON line."""
+    import torch
+    from quench6k_b200 import Engine, SamplingParams, ops
+    from quench6k_b200.config import FlintConfig
+    torch.cuda.set_device(0)
+    long_len, n_req, new = args.context or 131072, args.batch or 64, 128
+    cfg_d = dict(CONFIG2)
+    layers = args.layers or shape["layers"]
+    cfg_d["num_hidden_layers"] = layers
+    if args.page_size:
+        cfg_d["kv_page_size"] = args.page_size
+    cfg = FlintConfig.from_dict(cfg_d)
+    page, budget = cfg.kv_page_size, args.prefill_tokens
+    gen = torch.Generator().manual_seed(4)
+    lens = [long_len] + [int(x) for x in torch.randint(256, min(16384, long_len) + 1, (n_req - 1,), generator=gen)]
+    num_pages = sum((n + new + page - 1) // page + 1 for n in lens)      # every request fits at once: no preemption is forced
+    t0 = time.time()
+    eng = Engine.from_random(cfg, seed=0, dtype=args.dtype, page_size=page, num_pages=num_pages, max_requests=n_req,
+                             max_batch_tokens=budget)
+    torch.cuda.synchronize()
+    print(f"[bench] model and cache ready in {time.time() - t0:.1f}s ({torch.cuda.memory_allocated() / 2**30:.1f} GiB on the device)",
+          file=sys.stderr, flush=True)
+    V = cfg.vocab_size
+    ids = lambda n: torch.randint(0, V, (n,), generator=gen).tolist()
+    warm = eng.generate([ids(budget), ids(300)], SamplingParams(max_tokens=4, temperature=0.0))      # first-call costs stay outside
+    assert all(len(o.tokens) == 4 for o in warm)
+    torch.cuda.synchronize()
+    base = dict(eng.stats)
+    clocks = ClockSampler()
+    clocks.start()
+    t1 = time.perf_counter()
+    rids = [eng.add_request(ids(n), SamplingParams(max_tokens=new, temperature=0.0 if i == 0 else 1.0, seed=100 + i), rid=f"s{i}")
+            for i, n in enumerate(lens)]
+    done, first_long, decode_only_s, decode_only_tokens, last = {}, None, 0.0, 0, t1
+    while len(done) < len(rids):
+        prompts_left = any(not r.output for r in list(eng.scheduler.running) + list(eng.scheduler.waiting))
+        tokens_before = eng.stats["tokens"]
+        for out in eng.step():
+            done[out.rid] = out
+        now = time.perf_counter()
+        if not prompts_left:                      # a step of decode tokens only
+            decode_only_s += now - last
+            decode_only_tokens += eng.stats["tokens"] - tokens_before
+        if first_long is None and any(r.rid == "s0" and r.output for r in eng.scheduler.running):
+            first_long = now - t1
+        last = now
+    torch.cuda.synchronize()
+    total_s = time.perf_counter() - t1
+    clock_info = clocks.stop()
+    assert ops.tc_status() == 0
+    generated = sum(len(o.tokens) for o in done.values())
+    print(json.dumps({
+        "workload": "stress: a long greedy prompt in portions beside sampled requests, continuous batching", "impl": "ours",
+        "config": {"model": shape["label"], "layers": layers, "layers_full": shape["layers"], "requests": n_req, "long_prompt": long_len,
+                   "other_prompts": "uniform 256..16384", "new_tokens": new, "token_budget": budget, "page_size": page,
+                   "pages": num_pages, "dtype": args.dtype},
+        "prompt_tokens": sum(lens), "generated_tokens": generated, "seconds": round(total_s, 3),
+        "tokens_per_s": round((sum(lens) + generated) / total_s, 1),
+        "long_prompt_first_token_s": None if first_long is None else round(first_long, 3),
+        "decode_only": {"tokens": decode_only_tokens, "tok_per_s": round(decode_only_tokens / decode_only_s, 1) if decode_only_s else None},
+        "steps": eng.stats["steps"] - base["steps"], "preemptions": eng.stats["preemptions"] - base["preemptions"],
+        "gib_on_device": round(torch.cuda.max_memory_allocated() / 2**30, 1), "clocks": clock_info}))
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -210,8 +284,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (both numbers are reported)")
-    ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--context", type=int, default=32768)
+    ap.add_argument("--config", type=int, default=2, choices=sorted(SHAPES),
+                    help="2: 24 layers at 32,768 cached tokens (the default run); 3: the full 48 layers at 8,192 cached tokens")
+    ap.add_argument("--workload", default="decode", choices=["decode", "stress"],
+                    help="stress: one 131,072-token prompt in 2,048-token portions and 128 decoded tokens beside 63 sampled requests "
+                         "of 256 to 16,384 tokens, all through Engine.step() (its own JSON line; --context and --batch scale it down)")
+    ap.add_argument("--batch", type=int, default=None)
+    ap.add_argument("--context", type=int, default=None)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--points", default="1,64", help="further decode batch sizes, comma separated ('' for none)")
     ap.add_argument("--dtype", default="bfloat16")
@@ -241,8 +320,13 @@ def main():
         return kernel_attention_prefill(args)
     torch.cuda.set_device(0)
     pk = peaks()
+    shape = SHAPES[args.config]
+    if args.workload == "stress":
+        return workload_stress(args, shape)
+    args.batch = args.batch or 8
+    args.context = args.context or shape["context"]
     cfg_d = dict(CONFIG2)
-    full_layers = cfg_d["num_hidden_layers"]
+    full_layers = shape["layers"]
     layers = args.layers or full_layers
     cfg_d["num_hidden_layers"] = layers
     if args.page_size:
@@ -362,7 +446,7 @@ def main():
         "ms_per_step": round(ms, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16" if args.dtype in ("bfloat16", "bf16") else "fp32",
         "data": "synthetic: seeded random weights N(0,0.02), uniform-random token ids, caches filled with random values",
-        "config": {"model": "Recursive Flint MoE, half-depth shape", "layers": layers, "layers_full": full_layers,
+        "config": {"model": shape["label"], "layers": layers, "layers_full": full_layers,
                    "hidden": cfg.hidden_size, "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "experts": cfg.n_routed_experts, "top_k": cfg.num_experts_per_tok,
                    "expert_width": cfg.moe_intermediate_size, "vocab": cfg.vocab_size, "rope_theta": cfg.rope_theta,

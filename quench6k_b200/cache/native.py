@@ -14,6 +14,8 @@ from .manager import GroupSpec, OutOfPages, OutOfSlots
 
 _i32p = ctypes.POINTER(ctypes.c_int32)
 _i64p = ctypes.POINTER(ctypes.c_int64)
+_f32p = ctypes.POINTER(ctypes.c_float)
+_f64p = ctypes.POINTER(ctypes.c_double)
 _lib = None
 
 
@@ -57,11 +59,12 @@ def host_lib():
         "q6k_sched_update": (i, [vp, _i32p, i, i, _i64p, _i32p, _i32p]),
         "q6k_sched_set_output_token": (i, [vp, i64, i, ctypes.c_int32]),
         "q6k_sched_stop": (i, [vp, i64, i]),
+        "q6k_sample_rows": (i, [i, i, _i32p, _f32p, _i32p, _f32p, _i32p, _f32p, _f32p, _f32p, _f32p, _i32p, _i64p, _f64p, _i32p]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
         fn.restype, fn.argtypes = res, args
-    if lib.q6k_host_abi_version() != 1:
+    if lib.q6k_host_abi_version() != 2:
         raise RuntimeError("the host library does not match this package")
     _lib = lib
     return lib

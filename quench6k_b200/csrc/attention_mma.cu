@@ -44,8 +44,9 @@ struct AttnParams {
     const int* tile_ntok;                    // tokens of each tile (consecutive positions of one request)
     const float* sinks;                      // [Hq] or null
     __nv_bfloat16* out;                      // [T, Hq*HD]
-    float* part_o;                           // [T*Hq, max_splits, HD]
-    float* part_ml;                          // [T*Hq, max_splits, 2]
+    float* part_o;                           // [rows*Hq, max_splits, HD], rows counted from part_row0
+    float* part_ml;                          // [rows*Hq, max_splits, 2]
+    int part_row0;                           // first token row that the partial buffers cover
     int max_blocks, page_size, window, Hq, Hkv, G, max_splits, min_tiles;
     float scale_log2;
     int pool_rows;                           // rows of the [Hkv * pages * page_size, HD] view of a pool (TMA path)
@@ -383,11 +384,11 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0)) attentio
 #pragma unroll
             for (int w = 0; w < 4; ++w) acc += wgt[w] * red[((size_t)w * 16 + r) * LD + d];
             if (se == 1) p.out[row * HD + d] = __float2bfloat16_rn(acc * osc / den);
-            else p.part_o[(row * p.max_splits + split) * HD + d] = acc;
+            else p.part_o[((row - (size_t)p.part_row0 * p.Hq) * p.max_splits + split) * HD + d] = acc;
         }
         if (se > 1 && sub == 0) {
-            p.part_ml[(row * p.max_splits + split) * 2] = M;
-            p.part_ml[(row * p.max_splits + split) * 2 + 1] = L;
+            p.part_ml[((row - (size_t)p.part_row0 * p.Hq) * p.max_splits + split) * 2] = M;
+            p.part_ml[((row - (size_t)p.part_row0 * p.Hq) * p.max_splits + split) * 2 + 1] = L;
         }
     } else {
 #pragma unroll
@@ -407,12 +408,12 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0)) attentio
                 for (int n = 0; n < DB; ++n)
                     *reinterpret_cast<uint32_t*>(p.out + row * HD + n * 8 + 2 * t4) = pack_bf16(o[n][hr * 2] * inv, o[n][hr * 2 + 1] * inv);
             } else {
-                float* po = p.part_o + (row * p.max_splits + split) * HD;
+                float* po = p.part_o + ((row - (size_t)p.part_row0 * p.Hq) * p.max_splits + split) * HD;
 #pragma unroll
                 for (int n = 0; n < DB; ++n) *reinterpret_cast<float2*>(po + n * 8 + 2 * t4) = make_float2(o[n][hr * 2], o[n][hr * 2 + 1]);
                 if (t4 == 0) {
-                    p.part_ml[(row * p.max_splits + split) * 2] = m[hr];
-                    p.part_ml[(row * p.max_splits + split) * 2 + 1] = l[hr];
+                    p.part_ml[((row - (size_t)p.part_row0 * p.Hq) * p.max_splits + split) * 2] = m[hr];
+                    p.part_ml[((row - (size_t)p.part_row0 * p.Hq) * p.max_splits + split) * 2 + 1] = l[hr];
                 }
             }
         }
@@ -443,8 +444,8 @@ __global__ void __launch_bounds__(MERGE_THREADS) attention_merge_kernel(const At
     split_plan(k_lo / KT, pos_last / KT + 1, p.max_splits, p.min_tiles, per, se);
     if (se == 1) return;                      // the attention kernel wrote the output itself
     const size_t row = (size_t)(tok0 + tt) * p.Hq + kh * G + hg;
-    const float* ml = p.part_ml + row * p.max_splits * 2;
-    const float* po = p.part_o + row * p.max_splits * HD;
+    const float* ml = p.part_ml + (row - (size_t)p.part_row0 * p.Hq) * p.max_splits * 2;
+    const float* po = p.part_o + (row - (size_t)p.part_row0 * p.Hq) * p.max_splits * HD;
     const float sk = p.sinks ? p.sinks[kh * G + hg] * LOG2E : -INFINITY;
     // every load of the first round goes out before the maximum is known: the values and the
     // (m, l) pairs do not depend on it
@@ -564,7 +565,8 @@ Q6K_API int q6k_attention_mma_supported(int hd, int G, int wide) { return (hd ==
 
 // q: bfloat16 [T, Hq, hd]; pages: bfloat16 [Hkv, num_pages, page_size, hd]; tiles: tile_tok0/tile_ntok [n_tiles], the
 // tokens of a tile being consecutive positions of one request, at most (wide ? 128 : 16) / G of them.
-// part_o: FP32 [T*Hq*max_splits*hd], part_ml: FP32 [T*Hq*max_splits*2] (unused when max_splits == 1).
+// part_o: FP32 [rows*Hq*max_splits*hd], part_ml: FP32 [rows*Hq*max_splits*2] (unused when max_splits == 1), rows
+// being the token rows from part_row0 to the last row of any tile.
 Q6K_API int q6k_attention_status() {
     int v = -1;
     if (cudaMemcpyFromSymbol(&v, g_attn_status, sizeof v) != cudaSuccess) return -1;
@@ -575,21 +577,21 @@ Q6K_API int q6k_attention_status() {
 Q6K_API int q6k_attention_mma(const void* q, const void* k_pages, const void* v_pages, long long num_pages, const int* block_table,
                               int max_blocks, int page_size, const int* req_of_token, const int* positions, const int* tile_tok0,
                               const int* tile_ntok, int n_tiles, int wide, int window, const float* sinks, float scale, void* out,
-                              float* part_o, float* part_ml, int max_splits, int min_tiles, int Hq, int Hkv, int hd,
-                              cudaStream_t st) {
+                              float* part_o, float* part_ml, int part_row0, int max_splits, int min_tiles, int Hq, int Hkv,
+                              int hd, cudaStream_t st) {
     if (n_tiles == 0) return 0;
     Q6K_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention_mma: bad head counts Hq=%d Hkv=%d", Hq, Hkv);
     const int G = Hq / Hkv;
     Q6K_REQUIRE(q6k_attention_mma_supported(hd, G, wide), "attention_mma: head_dim %d / group size %d is not covered by the tensor-core kernel", hd, G);
     Q6K_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0 && max_splits >= 1 && max_splits <= 65535 && min_tiles >= 1,
                 "attention_mma: bad page_size %d / max_blocks %d / window %d / splits %d", page_size, max_blocks, window, max_splits);
-    Q6K_REQUIRE(max_splits == 1 || (part_o && part_ml), "attention_mma: splitting the keys needs the partial buffers");
+    Q6K_REQUIRE(max_splits == 1 || (part_o && part_ml && part_row0 >= 0), "attention_mma: splitting the keys needs the partial buffers");
     Q6K_REQUIRE(Hkv <= 65535 && n_tiles <= 65535, "attention_mma: grid limit exceeded (Hkv=%d, tiles=%d)", Hkv, n_tiles);
     AttnParams p{};
     p.q = (const __nv_bfloat16*)q, p.k_pages = (const __nv_bfloat16*)k_pages, p.v_pages = (const __nv_bfloat16*)v_pages;
     p.block_table = block_table, p.req_of_token = req_of_token, p.positions = positions;
     p.tile_tok0 = tile_tok0, p.tile_ntok = tile_ntok, p.sinks = sinks, p.out = (__nv_bfloat16*)out;
-    p.part_o = part_o, p.part_ml = part_ml;
+    p.part_o = part_o, p.part_ml = part_ml, p.part_row0 = part_row0;
     p.max_blocks = max_blocks, p.page_size = page_size, p.window = window, p.Hq = Hq, p.Hkv = Hkv, p.G = G;
     p.max_splits = max_splits, p.min_tiles = min_tiles, p.scale_log2 = scale * LOG2E;
     // pages of 8, 16, 32, 64 keys (or whole multiples of 64) are boxes TMA can place on the swizzle pattern

@@ -1,5 +1,6 @@
-// The host side of the engine in C++: the paged cache manager, the continuous-batching scheduler
-// and the packing of a step's description, behind a C interface that Python calls through ctypes.
+// The host side of the engine in C++: the paged cache manager, the continuous-batching scheduler,
+// the packing of a step's description and the choice of a token from a candidate pool, behind a
+// C interface that Python calls through ctypes.
 //
 // The reference's host is Rust (crates/engine/src/flint.rs: contiguous per-sequence caches, one
 // request at a time; crates/engine/src/session.rs and crates/cli/src/serve.rs: admission by memory
@@ -10,6 +11,7 @@
 // Every exported function returns 0 or an error kind after storing a message:
 //   1 runtime error, 2 out of pages, 3 out of slots, 4 unknown or duplicate request, 5 bad value.
 #include <algorithm>
+#include <cmath>
 #include <cstdarg>
 #include <cstdint>
 #include <cstdio>
@@ -420,7 +422,7 @@ int copy_out(const std::vector<T>& v, T* out, int cap, int* n, const char* what)
 }  // namespace
 
 API const char* q6k_host_last_error() { return g_msg; }
-API int q6k_host_abi_version() { return 1; }
+API int q6k_host_abi_version() { return 2; }
 
 // ------------------------------------------------------------------------------- cache manager
 API void* q6k_cm_create(int n_groups, const int* sliding, const int* windows, int page_size, const int* num_pages, int max_requests) {
@@ -647,5 +649,78 @@ API int q6k_sched_update(void* h, const int32_t* sampled, int n_sampled, int cap
     if (int rc = copy_out(d, done, cap, n_done, "finished")) return rc;
     std::copy(why.begin(), why.end(), reasons);
     for (int64_t id : d) s->by_id.erase(id);
+    return OK;
+}
+
+// ------------------------------------------------------------------------------------ sampling
+// One token per row from its candidate pool (ids and logits in any order), the way the reference's
+// host does it (crates/cli/src/flint.rs:359-431): presence and repetition penalties on candidates
+// the request has generated before; order by (logit descending, id ascending); greedy rows
+// (temperature <= 0 or top_k == 1) take the first; the others compute p_i = exp((l_i - l_0) /
+// temperature) in double precision from a 32-bit quotient, drop p_i < min_p, keep the shortest
+// prefix whose normalised mass reaches top_p, and invert the CDF with u[row] * total.
+// sizes[row] candidates of row `row` start at ids/vals + row * stride; sizes[row] <= 0 skips the
+// row; generated[gen_start[row] .. gen_start[row + 1]) are the row's earlier output tokens.
+API int q6k_sample_rows(int rows, int stride, const int32_t* ids, const float* vals, const int32_t* sizes, const float* temperature,
+                        const int32_t* top_k, const float* top_p, const float* min_p, const float* presence, const float* repetition,
+                        const int32_t* generated, const int64_t* gen_start, const double* u, int32_t* out) {
+    std::vector<float> v;
+    std::vector<int> order;
+    std::vector<double> probs;
+    for (int row = 0; row < rows; ++row) {
+        const int n = sizes[row];
+        if (n <= 0) continue;
+        if (n > stride) return fail(E_VALUE, "row %d: %d candidates in a pool of %d", row, n, stride);
+        const int32_t* id = ids + (size_t)row * stride;
+        v.assign(vals + (size_t)row * stride, vals + (size_t)row * stride + n);
+        if (presence[row] != 0.0f || repetition[row] != 1.0f) {
+            const int32_t* g0 = generated + gen_start[row];
+            const int32_t* g1 = generated + gen_start[row + 1];
+            for (int i = 0; i < n; ++i)
+                if (std::find(g0, g1, id[i]) != g1) {
+                    float x = v[i] - presence[row];
+                    v[i] = x > 0.0f ? x / repetition[row] : x * repetition[row];
+                }
+        }
+        order.resize(n);
+        for (int i = 0; i < n; ++i) order[i] = i;
+        std::sort(order.begin(), order.end(), [&](int a, int b) { return v[a] != v[b] ? v[a] > v[b] : id[a] < id[b]; });
+        if (temperature[row] <= 0.0f || top_k[row] == 1) {
+            out[row] = id[order[0]];
+            continue;
+        }
+        const int keep = top_k[row] == 0 ? n : std::min(top_k[row], n);
+        const float top = v[order[0]];
+        probs.resize(keep);
+        for (int i = 0; i < keep; ++i) probs[i] = std::exp((double)((v[order[i]] - top) / temperature[row]));
+        if (min_p[row] > 0.0f)
+            for (double& q : probs)
+                if (q < (double)min_p[row]) q = 0.0;
+        double total = 0.0;
+        for (double q : probs) total += q;
+        int cut = keep;
+        if (top_p[row] < 1.0f) {
+            double acc = 0.0;
+            for (int i = 0; i < keep; ++i) {
+                acc += probs[i] / total;
+                if (acc >= (double)top_p[row]) {
+                    cut = i + 1;
+                    break;
+                }
+            }
+        }
+        total = 0.0;
+        for (int i = 0; i < cut; ++i) total += probs[i];
+        double r = u[row] * total;
+        int pick = cut - 1;
+        for (int i = 0; i < cut; ++i) {
+            r -= probs[i];
+            if (r <= 0.0) {
+                pick = i;
+                break;
+            }
+        }
+        out[row] = id[order[pick]];
+    }
     return OK;
 }

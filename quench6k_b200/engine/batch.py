@@ -42,33 +42,77 @@ class StepContext:
     max_q_len: int = 0
     plans: dict = field(default_factory=dict)     # per-step launch plans that parts share across layers (keyed by the part)
     fed: Optional[torch.Tensor] = None            # int32 ids the step before sampled: a token id -(i + 1) stands for fed[i]
+    bounds_only: bool = False             # the launches are recorded and replayed for other positions: plans may use only
+                                          # the token counts and max_context, not where each request stands now
 
-    def query_tiles(self, tokens_per_tile: int):
+    def query_tiles(self, tokens_per_tile: int, at_most: Optional[int] = None):
         """Tiles of at most `tokens_per_tile` consecutive tokens of one request, as device arrays
-        (first row, token count) and their number; made once per step and size."""
-        key = ("query_tiles", tokens_per_tile)
+        (first row, token count) and their number; made once per step and size.  at_most: only
+        the requests that bring at most that many tokens to the step."""
+        key = ("query_tiles", tokens_per_tile, at_most)
         if key not in self.plans:
             first, count, at = [], [], 0
             for n in self.q_lens:
-                for i in range(0, n, tokens_per_tile):
-                    first.append(at + i)
-                    count.append(min(tokens_per_tile, n - i))
+                if at_most is None or n <= at_most:
+                    for i in range(0, n, tokens_per_tile):
+                        first.append(at + i)
+                        count.append(min(tokens_per_tile, n - i))
                 at += n
-            both = torch.tensor([first, count], dtype=torch.int32).to(self.token_ids.device, non_blocking=True)
+            both = torch.tensor([first, count], dtype=torch.int32).reshape(2, -1).to(self.token_ids.device, non_blocking=True)
             self.plans[key] = (both[0], both[1], len(first))
         return self.plans[key]
 
-    def query_tile_pairs(self, tokens_per_tile: int, zigzag: bool):
+    def key_tiles(self, tokens_per_tile: int, keys_per_tile: int, window: Optional[int] = None, at_most: Optional[int] = None):
+        """(sum, largest) of the numbers of key tiles that the query tiles of query_tiles(tokens_per_tile,
+        at_most) walk through, a key tile being `keys_per_tile` keys at a multiple of that number
+        (with bounds_only: as if every request ended at max_context)."""
+        key = ("key_tiles", tokens_per_tile, keys_per_tile, window, at_most)
+        if key not in self.plans:
+            total = longest = 0
+            for r, n in enumerate(self.q_lens):
+                if at_most is not None and n > at_most:
+                    continue
+                start = self.pos_starts[r] if r < len(self.pos_starts) else 0
+                if self.bounds_only:
+                    start = max(0, self.max_context - n)
+                for i in range(0, n, tokens_per_tile):
+                    first, last = start + i, start + min(n, i + tokens_per_tile) - 1
+                    lo = max(0, first - window + 1) if window else 0
+                    tiles = last // keys_per_tile + 1 - lo // keys_per_tile
+                    total, longest = total + tiles, max(longest, tiles)
+            self.plans[key] = (total, longest)
+        return self.plans[key]
+
+    def short_requests(self, at_most: int):
+        """The requests that bring at most `at_most` tokens to the step: (how many, first row,
+        end row, most tokens of one, largest position + 1); rows of other requests may lie between."""
+        key = ("short_requests", at_most)
+        if key not in self.plans:
+            count, lo, hi, most, reach, at = 0, 0, 0, 0, 0, 0
+            for r, n in enumerate(self.q_lens):
+                if n <= at_most:
+                    lo = at if count == 0 else lo
+                    count, hi, most = count + 1, at + n, max(most, n)
+                    reach = max(reach, (self.pos_starts[r] if r < len(self.pos_starts) else 0) + n)
+                at += n
+            self.plans[key] = (count, lo, hi, most, reach)
+        return self.plans[key]
+
+    def query_tile_pairs(self, tokens_per_tile: int, zigzag: bool, more_than: int = 0):
         """The same tiles two by two, both of one request, as device arrays [pairs, 2] (first row,
         token count; a lone tile's partner has no tokens) and their number.  zigzag: a request's
         last tile goes with its first, the one before with the second, ... (under a causal mask
         the late tile's keys include the early tile's, and every pair has the same amount of work);
         else neighbours go together (their key ranges nearly coincide: the choice for a window).
-        The pairs come sorted by the number of keys they see, most first."""
-        key = ("query_tile_pairs", tokens_per_tile, zigzag)
+        The pairs come sorted by the number of keys they see, most first.  more_than: only the
+        requests that bring more than that many tokens to the step."""
+        key = ("query_tile_pairs", tokens_per_tile, zigzag, more_than)
         if key not in self.plans:
             pairs, at = [], 0                            # (keys the pair's later tile sees, first rows, counts)
             for r, n in enumerate(self.q_lens):
+                if n <= more_than:
+                    at += n
+                    continue
                 tiles = [(at + i, min(tokens_per_tile, n - i)) for i in range(0, n, tokens_per_tile)]
                 k = len(tiles)
                 start = self.pos_starts[r] if r < len(self.pos_starts) else 0
@@ -82,6 +126,6 @@ class StepContext:
                 at += n
             pairs.sort(key=lambda p: -p[0])              # the pairs with the most keys first (stable: ties keep their order)
             first, count = [p[1] for p in pairs], [p[2] for p in pairs]
-            both = torch.tensor([first, count], dtype=torch.int32).to(self.token_ids.device, non_blocking=True)
+            both = torch.tensor([first, count], dtype=torch.int32).reshape(2, -1, 2).to(self.token_ids.device, non_blocking=True)
             self.plans[key] = (both[0].contiguous(), both[1].contiguous(), len(first))
         return self.plans[key]

@@ -80,6 +80,7 @@ class ModelRunner:
         self._graphs: "OrderedDict" = OrderedDict()       # least recently replayed first; at most max_graphs are kept
         self._shapes_seen: Dict = {}
         self.max_graphs = 64
+        self.graph_max_tokens = 256
         self.graph_replays = 0
         # ids sampled on the device by the step before (greedy decoding that does not wait for the host)
         self.sampled = torch.zeros(max(64, max_requests), dtype=torch.int32, device=rt.device)
@@ -189,9 +190,11 @@ class ModelRunner:
     def _forward(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Eager for steps of a new shape; a step whose shape (tokens and wanted places per entry,
         block-table widths) has been seen before replays a CUDA graph recorded for that shape.
-        Decode steps are recorded at once; other shapes when they come a second time (a prompt
-        cut into equal portions repeats its shape, a one-off mix does not)."""
-        if not self.cuda_graphs:
+        Decode steps are recorded at once; other shapes when they come a second time.  Steps of
+        more than graph_max_tokens tokens always run eagerly: their kernels are long enough to
+        hide the launches, and in mixed traffic their shapes seldom repeat often enough to repay
+        a recording."""
+        if not self.cuda_graphs or sum(len(e.tokens) for e in entries) > self.graph_max_tokens:
             return self.model.forward(self._context(entries), self.caches, self.states)
         widths = [(w + 63) // 64 * 64 for w in self._widths(entries)]
         shape = tuple((len(e.tokens), tuple(e.want)) for e in entries)
@@ -213,6 +216,7 @@ class ModelRunner:
             static = torch.empty(total, dtype=torch.int32, device=self.rt.device)
             ctx = self._context(entries, widths, static)
             ctx.max_context = max(widths) * self.page_size          # launch plans must hold for every replay
+            ctx.bounds_only = True
             logits = self.model.forward(ctx, self.caches, self.states)
             result = logits.clone() if logits is not None else None
             torch.cuda.synchronize()

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import math
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -410,12 +410,14 @@ def attention_tc_tile_tokens(G: int) -> int:
 
 def attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                  req_of_token: torch.Tensor, positions: torch.Tensor, tile_tok0: torch.Tensor, tile_ntok: torch.Tensor,
-                 window: Optional[int], sinks: Optional[torch.Tensor], scale: Optional[float] = None) -> torch.Tensor:
+                 window: Optional[int], sinks: Optional[torch.Tensor], scale: Optional[float] = None,
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """bfloat16 attention for prompt portions with both products on tcgen05 tensor cores
     (accumulators and probabilities in tensor memory, K/V pages by TMA).  Head size 128.
     tile_tok0 / tile_ntok: [n, 2], two tiles of one request per CTA (StepContext.query_tile_pairs),
     each of at most attention_tc_tile_tokens(G) tokens at consecutive positions; the second may be
-    empty.  Each tile reads its whole key range; the two share the K/V stream."""
+    empty.  Each tile reads its whole key range; the two share the K/V stream.  Only the rows of
+    the listed tiles are written (into `out` [T, Hq*hd] when given)."""
     _need(q, "q", torch.bfloat16)
     T, Hq, hd = q.shape
     _need(k_pages, "k_pages", torch.bfloat16)
@@ -430,7 +432,10 @@ def attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, 
         raise KernelError("attention_tc: tile_tok0 and tile_ntok must be [pairs, 2]")
     if sinks is not None:
         _need(sinks, "sinks", torch.float32, (Hq,))
-    out = torch.empty((T, Hq * hd), dtype=torch.bfloat16, device=q.device)
+    if out is None:
+        out = torch.empty((T, Hq * hd), dtype=torch.bfloat16, device=q.device)
+    else:
+        _need(out, "out", torch.bfloat16, (T, Hq * hd))
     _call("q6k_attention_tc", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ll(num_pages), _ptr(block_table),
           _i(block_table.shape[1]), _i(page_size), _ptr(req_of_token), _ptr(positions), _ptr(tile_tok0), _ptr(tile_ntok),
           _i(tile_tok0.shape[0]), _i(window or 0), _ptr(sinks), _f(scale if scale is not None else 1.0 / math.sqrt(hd)), _ptr(out),
@@ -447,10 +452,13 @@ def attention_mma_supported(hd: int, G: int, wide: bool) -> bool:
 def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                   req_of_token: torch.Tensor, positions: torch.Tensor, tile_tok0: torch.Tensor, tile_ntok: torch.Tensor,
                   wide: bool, window: Optional[int], sinks: Optional[torch.Tensor], max_splits: int = 1, min_tiles: int = 2,
-                  scale: Optional[float] = None) -> torch.Tensor:
+                  scale: Optional[float] = None, out: Optional[torch.Tensor] = None, rows: Optional[Tuple[int, int]] = None) -> torch.Tensor:
     """bfloat16 tensor-core attention over the pages.  Tiles: tile_tok0[i] is the first row and
     tile_ntok[i] the number of tokens (consecutive positions of one request, at most
-    (128 if wide else 16) // G) of tile i.  max_splits: upper bound of key splits per tile."""
+    (128 if wide else 16) // G) of tile i.  max_splits: upper bound of key splits per tile.
+    Only the rows of the listed tiles are written (into `out` [T, Hq*hd] when given); rows: the
+    range (first, end) of token rows the tiles lie in, when they are a part of the step (the
+    buffers for the key splits are sized by it)."""
     _need(q, "q", torch.bfloat16)
     T, Hq, hd = q.shape
     _need(k_pages, "k_pages", torch.bfloat16)
@@ -464,16 +472,23 @@ def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
     if sinks is not None:
         _need(sinks, "sinks", torch.float32, (Hq,))
     n_tiles = tile_tok0.numel()
-    out = torch.empty((T, Hq * hd), dtype=torch.bfloat16, device=q.device)
+    if out is None:
+        out = torch.empty((T, Hq * hd), dtype=torch.bfloat16, device=q.device)
+    else:
+        _need(out, "out", torch.bfloat16, (T, Hq * hd))
+    row0, row1 = rows if rows is not None else (0, T)
+    if not 0 <= row0 <= row1 <= T:
+        raise KernelError(f"attention_mma: rows {rows} outside the step's {T} rows")
     part_o = part_ml = None
     if max_splits > 1:
-        ws = _workspace(T * Hq * max_splits * (hd + 2) * 4, q.device)
-        part_o = ws[: T * Hq * max_splits * hd]
-        part_ml = ws[T * Hq * max_splits * hd: T * Hq * max_splits * (hd + 2)]
+        n = max(1, row1 - row0)
+        ws = _workspace(n * Hq * max_splits * (hd + 2) * 4, q.device)
+        part_o = ws[: n * Hq * max_splits * hd]
+        part_ml = ws[n * Hq * max_splits * hd: n * Hq * max_splits * (hd + 2)]
     _call("q6k_attention_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ll(num_pages), _ptr(block_table),
           _i(block_table.shape[1]), _i(page_size),
           _ptr(req_of_token), _ptr(positions), _ptr(tile_tok0), _ptr(tile_ntok), _i(n_tiles), _i(1 if wide else 0), _i(window or 0),
-          _ptr(sinks), _f(scale if scale is not None else 1.0 / math.sqrt(hd)), _ptr(out), _ptr(part_o), _ptr(part_ml),
+          _ptr(sinks), _f(scale if scale is not None else 1.0 / math.sqrt(hd)), _ptr(out), _ptr(part_o), _ptr(part_ml), _i(row0),
           _i(max_splits), _i(min_tiles), _i(Hq), _i(Hkv), _i(hd), _stream())
     return out
 

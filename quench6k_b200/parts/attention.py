@@ -84,23 +84,40 @@ class Attention(Mixer):
         rt, G = self.rt, self.Hq // self.Hkv
         if rt.is_fp32 or not rt.tensor_cores:
             return ops.attention_generic(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, self.window, self.sinks, self.scale)
-        wide = ctx.max_q_len > max(1, 16 // G) or not ops.attention_mma_supported(self.hd, G, False)
+        narrow_tokens = max(1, 16 // G)
+        wide = ctx.max_q_len > narrow_tokens or not ops.attention_mma_supported(self.hd, G, False)
         if not ops.attention_mma_supported(self.hd, G, wide):
             return ops.attention_generic(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, self.window, self.sinks, self.scale)
         if wide and ops.attention_tc_supported(self.hd, G, cache.page_size):
-            tok0, ntok, n_tiles = ctx.query_tile_pairs(ops.attention_tc_tile_tokens(G), zigzag=False)
-            if 2 * n_tiles * self.Hkv >= self._sm_count():
+            tile = ops.attention_tc_tile_tokens(G)
+            # beside prompt portions, requests with a few tokens (decoded tokens, the stub of a prompt) go to the kernel
+            # that splits the keys over CTAs: as a tile of their own they would walk their whole context in one CTA
+            cut = tile // 2 if ctx.R > 1 else 0
+            tok0, ntok, n_pairs = ctx.query_tile_pairs(tile, zigzag=False, more_than=cut)
+            if 2 * n_pairs * self.Hkv >= self._sm_count():
                 # prompt portions with enough tiles for at least half of the SMs: both products on tcgen05, no key splits
-                return ops.attention_tc(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, tok0, ntok, self.window,
-                                        self.sinks, scale=self.scale)
-        tok0, ntok, n_tiles = ctx.query_tiles((128 if wide else 16) // G)
+                out = ops.attention_tc(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, tok0, ntok, self.window,
+                                       self.sinks, scale=self.scale)
+                count, row0, row1, most, reach = ctx.short_requests(cut)
+                if count:
+                    self._split_keys(q, cache, table, ctx, most > narrow_tokens or not ops.attention_mma_supported(self.hd, G, False),
+                                     at_most=cut, out=out, rows=(row0, row1))
+                return out
+        return self._split_keys(q, cache, table, ctx, wide)
+
+    def _split_keys(self, q, cache, table, ctx, wide, at_most=None, out=None, rows=None):
+        """The mma.sync kernel over all requests of the step, or over those with at most `at_most` tokens."""
+        G = self.Hq // self.Hkv
+        tokens = (128 if wide else 16) // G
+        tok0, ntok, n_tiles = ctx.query_tiles(tokens, at_most)
         # split the keys over CTAs until the GPU is full, and no further: one wave of resident CTAs
-        # (a second, partly filled wave would cost as much as a full one)
-        span = ctx.max_context if self.window is None else min(ctx.max_context, self.window + ctx.max_q_len)
-        key_tiles = (span + 63) // 64 + 1
-        max_splits = max(1, min(64, self._resident_ctas(wide) // (n_tiles * self.Hkv), key_tiles // 2))
+        # (a second, partly filled wave would cost as much as a full one).  Every CTA gets about the
+        # same number of key tiles, so a request deep in its context is split more often than the others.
+        total, longest = ctx.key_tiles(tokens, 64, self.window, at_most)
+        per = max(2, -(-total * self.Hkv // self._resident_ctas(wide)))
+        max_splits = max(1, min(128, longest // per))
         return ops.attention_mma(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, tok0, ntok, wide, self.window,
-                                 self.sinks, max_splits=max_splits, min_tiles=2, scale=self.scale)
+                                 self.sinks, max_splits=max_splits, min_tiles=per, scale=self.scale, out=out, rows=rows)
 
     def _sm_count(self) -> int:
         if "_sms" not in self.__dict__:

@@ -66,18 +66,23 @@ def pick_from_pool(ids: Sequence[int], vals: Sequence[float], p: SamplingParams,
     top = vals[order[0]]
     scaled = ((vals[order] - top) / np.float32(p.temperature)).astype(np.float32)
     probs = [math.exp(float(s)) for s in scaled]
-    if p.min_p > 0.0:
-        probs = [q if q >= p.min_p else 0.0 for q in probs]
-    total = sum(probs)
+    min_p, top_p = float(np.float32(p.min_p)), float(np.float32(p.top_p))      # the options are 32-bit values
+    if min_p > 0.0:
+        probs = [q if q >= min_p else 0.0 for q in probs]
+    total = 0.0
+    for q in probs:                       # a plain running sum, as the reference's
+        total += q
     cut = len(probs)
-    if p.top_p < 1.0:
+    if top_p < 1.0:
         acc = 0.0
         for i, q in enumerate(probs):
             acc += q / total
-            if acc >= p.top_p:
+            if acc >= top_p:
                 cut = i + 1
                 break
-    total = sum(probs[:cut])
+    total = 0.0
+    for q in probs[:cut]:
+        total += q
     r = rng.uniform() * total
     for i in range(cut):
         r -= probs[i]
@@ -86,8 +91,48 @@ def pick_from_pool(ids: Sequence[int], vals: Sequence[float], p: SamplingParams,
     return int(ids[order[cut - 1]])
 
 
+def pick_rows_native(ids: np.ndarray, vals: np.ndarray, sizes: Sequence[int], params: Sequence[SamplingParams],
+                     generated: Sequence[Sequence[int]], rngs: Sequence[SplitMix64]) -> List[int]:
+    """pick_from_pool for every row with sizes[row] > 0 in one call of the C++ host library
+    (csrc/host/host.cpp, q6k_sample_rows); ids / vals: int32 / float32 [rows, pool].  A row's
+    random stream advances exactly when pick_from_pool would advance it."""
+    from ..cache.native import host_lib, raise_for
+    import ctypes
+    rows, stride = ids.shape
+    f32 = lambda xs: np.ascontiguousarray(xs, dtype=np.float32)
+    sizes_a = np.ascontiguousarray(sizes, dtype=np.int32)
+    u = np.zeros(rows, dtype=np.float64)
+    starts = np.zeros(rows + 1, dtype=np.int64)
+    gen: List[int] = []
+    for i, p in enumerate(params):
+        if sizes_a[i] > 0:
+            if p.penalized:
+                gen.extend(generated[i])
+            if not p.greedy:
+                u[i] = rngs[i].uniform()
+        starts[i + 1] = len(gen)
+    gen_a = np.ascontiguousarray(gen if gen else [0], dtype=np.int32)
+    out = np.zeros(rows, dtype=np.int32)
+    ptr = lambda a, t: a.ctypes.data_as(ctypes.POINTER(t))
+    cols = [f32([getattr(p, name) for p in params]) for name in ("temperature", "top_p", "min_p", "presence_penalty", "repetition_penalty")]
+    top_k = np.ascontiguousarray([p.top_k for p in params], dtype=np.int32)
+    ids, vals = np.ascontiguousarray(ids, dtype=np.int32), np.ascontiguousarray(vals, dtype=np.float32)
+    raise_for(host_lib().q6k_sample_rows(rows, stride, ptr(ids, ctypes.c_int32), ptr(vals, ctypes.c_float), ptr(sizes_a, ctypes.c_int32),
+                                         ptr(cols[0], ctypes.c_float), ptr(top_k, ctypes.c_int32), ptr(cols[1], ctypes.c_float),
+                                         ptr(cols[2], ctypes.c_float), ptr(cols[3], ctypes.c_float), ptr(cols[4], ctypes.c_float),
+                                         ptr(gen_a, ctypes.c_int32), ptr(starts, ctypes.c_int64), ptr(u, ctypes.c_double),
+                                         ptr(out, ctypes.c_int32)))
+    return out.tolist()
+
+
 class Sampler:
-    """Chooses the next token of each row of a logits block [rows, vocab] (device, FP32)."""
+    """Chooses the next token of each row of a logits block [rows, vocab] (device, FP32).  The
+    choice from the pools runs in the C++ host library unless Q6K_HOST=python asks for the
+    Python twin (pick_from_pool)."""
+
+    def __init__(self):
+        import os
+        self.native = os.environ.get("Q6K_HOST", "").lower() != "python"
 
     def sample(self, logits: torch.Tensor, params: List[SamplingParams], generated: List[Sequence[int]],
                rngs: List[SplitMix64]) -> List[int]:
@@ -104,9 +149,15 @@ class Sampler:
                 out[i] = int(picked[i])
         k = max(sizes)
         ids, vals = ops.topk_pool(logits, k)
-        ids, vals = ids.tolist(), vals.tolist()
+        ids, vals = ids.cpu().numpy(), vals.cpu().numpy()
+        if self.native:
+            chosen = pick_rows_native(ids, vals, [0 if s == 1 else s for s in sizes], params, generated, rngs)
+            for i, s in enumerate(sizes):
+                if s != 1:
+                    out[i] = int(chosen[i])
+            return out
         for i, s in enumerate(sizes):
             if s == 1:
                 continue
-            out[i] = pick_from_pool(ids[i][:s], vals[i][:s], params[i], generated[i], rngs[i])
+            out[i] = pick_from_pool(ids[i, :s], vals[i, :s], params[i], generated[i], rngs[i])
         return out

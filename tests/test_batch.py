@@ -7,11 +7,11 @@ import torch
 from quench6k_b200.engine.batch import StepContext
 
 
-def make_ctx(q_lens):
+def make_ctx(q_lens, pos_starts=None):
     T, R = sum(q_lens), len(q_lens)
     z = torch.zeros(0, dtype=torch.int32)
     return StepContext(T=T, R=R, token_ids=torch.zeros(T, dtype=torch.int32), positions=z, req_of_token=z, q_start=z, pos_start=z,
-                       slot_ids=z, block_tables=[], logit_rows=z, n_logit_rows=0, q_lens=list(q_lens), pos_starts=[0] * R,
+                       slot_ids=z, block_tables=[], logit_rows=z, n_logit_rows=0, q_lens=list(q_lens), pos_starts=list(pos_starts or [0] * R),
                        slots=list(range(R)), max_context=max(q_lens), max_q_len=max(q_lens))
 
 
@@ -57,3 +57,29 @@ def test_zigzag_pairs_the_last_tile_with_the_first():
     ctx = make_ctx([70])
     tok0, ntok, n = ctx.query_tile_pairs(16, True)          # tiles at 0, 16, 32, 48, 64 (6 tokens)
     assert tok0.tolist() == [[64, 0], [48, 16], [32, 32]] and ntok.tolist() == [[6, 16], [16, 16], [16, 0]] and n == 3
+
+
+def test_short_requests_go_one_way_and_the_others_another():
+    ctx = make_ctx([1, 40, 5, 1, 33], [100, 0, 7, 9, 64])
+    assert ctx.short_requests(8) == (3, 0, 47, 5, 101)            # rows 0..46 span them; deepest position 100
+    tok0, ntok, n = ctx.query_tiles(2, at_most=8)
+    assert n == 5 and tok0.tolist() == [0, 41, 43, 45, 46] and ntok.tolist() == [1, 2, 2, 1, 1]
+    p0, pn, pairs = ctx.query_tile_pairs(16, False, more_than=8)
+    # request 4 (positions 64..96) sees the most keys: its pairs come first
+    assert pairs == 4 and p0.tolist() == [[79, 79], [63, 47], [33, 33], [17, 1]] and pn.tolist() == [[1, 0], [16, 16], [8, 0], [16, 16]]
+    covered = sorted(r for a, c in zip(tok0.tolist(), ntok.tolist()) for r in range(a, a + c)) + sorted(
+        r for a2, c2 in zip(p0.tolist(), pn.tolist()) for a, c in zip(a2, c2) for r in range(a, a + c))
+    assert sorted(covered) == list(range(80))                      # every row of the step exactly once
+    none0, nonen, zero = ctx.query_tile_pairs(16, False, more_than=64)
+    assert zero == 0 and tuple(none0.shape) == (0, 2)
+
+
+def test_key_tiles_counts_what_each_query_tile_walks_through():
+    ctx = make_ctx([1, 40, 1], [1000, 0, 63])
+    # one token at position 1000: key tiles 0..15; 40 tokens from 0 in tiles of 16: 1, 1, 1; one token at 63: 1
+    assert ctx.key_tiles(16, 64) == (16 + 3 + 1, 16)
+    assert ctx.key_tiles(16, 64, at_most=8) == (17, 16)
+    assert ctx.key_tiles(16, 64, window=100) == (2 + 3 + 1, 2)          # positions 901..1000 lie in key tiles 14 and 15
+    ctx.plans.clear()
+    ctx.bounds_only, ctx.max_context = True, 2048                       # recorded steps: every request as if it ended at max_context
+    assert ctx.key_tiles(16, 64) == (32 + (32 + 32 + 32) + 32, 32)

@@ -466,3 +466,21 @@ def test_attention_tc(Hq, Hkv, ps, window, sinks):
         assert ops.tc_status() == 0
         err = (out.double().cpu() - want).abs().max() / want.abs().max()
         assert err <= 1.5e-2, (zigzag, err)
+    # the step in two parts that write one output: the requests with more than half a tile of tokens here, the others
+    # through the kernel that splits the keys (its partial sums sized for the rows it covers)
+    tile = ops.attention_tc_tile_tokens(G)
+    cut = tile // 2
+    count, row0, row1, most, reach = ctx.short_requests(cut)
+    wide = most > max(1, 16 // G) or not ops.attention_mma_supported(hd, G, False)
+    if count and ops.attention_mma_supported(hd, G, wide):
+        assert count == sum(1 for n in q_lens if n <= cut) and (row0, row1) == (sum(q_lens[:2]) if q_lens[2] <= cut else sum(q_lens[:3]), sum(q_lens[:4]))
+        out = torch.full((q.shape[0], Hq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+        tok0, ntok, n_pairs = ctx.query_tile_pairs(tile, False, more_than=cut)
+        ops.attention_tc(q, kp.to(DEV), vp.to(DEV), bt, ctx.req_of_token, ctx.positions, tok0, ntok, window, sk.to(DEV) if sinks else None, out=out)
+        assert torch.isnan(out[row0:row1].float()).any() and not torch.isnan(out[:row0].float()).any()
+        s0, sn, n_short = ctx.query_tiles((128 if wide else 16) // G, at_most=cut)
+        ops.attention_mma(q, kp.to(DEV), vp.to(DEV), bt, ctx.req_of_token, ctx.positions, s0, sn, wide, window,
+                          sk.to(DEV) if sinks else None, max_splits=3, min_tiles=1, out=out, rows=(row0, row1))
+        assert ops.tc_status() == 0
+        err = (out.double().cpu() - want).abs().max() / want.abs().max()
+        assert err <= 1.5e-2, ("two kernels", err)

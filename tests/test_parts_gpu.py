@@ -111,6 +111,69 @@ def test_attention_part_over_pages(dtype, window, sinks, qk_norm, rope):
         assert err <= (1e-4 if dtype == torch.float32 else 3e-2), (r, err)
 
 
+def test_attention_part_mixed_step_at_head_size_128():
+    """A prompt portion large enough for the tcgen05 attention kernel beside a decoded token and the
+    five-token stub of a prompt that stand deep in their contexts: the short ones go to the kernel
+    that splits the keys, the portion to the other, and every row of the step is written once."""
+    from quench6k_b200.parts import MIXERS, LayerCache, make_part
+    from quench6k_b200.spec import PartSpec
+    D, Hq, Hkv, hd, ps = 64, 8, 1, 128, 16
+    att = make_part(MIXERS, "mixer", PartSpec("attention", {"num_heads": Hq, "num_kv_heads": Hkv, "head_dim": hd, "eps": 1e-6,
+                    "pos": PartSpec("rope", {"head_dim": hd, "theta": 10000.0}), "window": None, "sinks": True, "qk_norm": True,
+                    "norm_init": "random"}), hidden_size=D)
+    st = _bind(att, _rt(torch.bfloat16), seed=8, std=0.3)
+    lens = [2400, 1501, 705]
+    xs = [(torch.randn(n, D, generator=torch.Generator().manual_seed(60 + i)) * 0.8).to(torch.bfloat16) for i, n in enumerate(lens)]
+    pages = sum(-(-n // ps) for n in lens) + 3
+    cache = LayerCache(0, torch.zeros(Hkv, pages, ps, hd, dtype=torch.bfloat16, device=DEV),
+                       torch.zeros(Hkv, pages, ps, hd, dtype=torch.bfloat16, device=DEV), ps)
+    order = torch.randperm(pages, generator=torch.Generator().manual_seed(3)).tolist()
+    tables = [[order.pop() for _ in range(-(-n // ps))] for n in lens]
+
+    def run(x, ctx):
+        out = torch.zeros(x.shape[0], D, device=DEV)
+        delta = att.forward(x.to(DEV), ctx, cache, None, out)
+        if delta is None:
+            return out
+        return delta.sum(0) if delta.dim() == 3 else delta
+
+    calls = []
+    from quench6k_b200 import ops
+    real_tc, real_mma = ops.attention_tc, ops.attention_mma
+    try:
+        ops.attention_tc = lambda *a, **k: (calls.append(("tc", a[6].shape[0])), real_tc(*a, **k))[1]
+        ops.attention_mma = lambda *a, **k: (calls.append(("mma", a[6].numel(), k.get("rows"))), real_mma(*a, **k))[1]
+        got = {}
+        got[1] = [run(xs[1][:1500], helpers.make_context([1500], [0], [[tables[1]]]))]
+        got[2] = [run(xs[2][:700], helpers.make_context([700], [0], [[tables[2]]]))]
+        before = len(calls)
+        mixed = run(torch.cat([xs[1][1500:], xs[0], xs[2][700:]]), helpers.make_context([1, 2400, 5], [1500, 0, 700], [[tables[1], tables[0], tables[2]]]))
+        assert ops.tc_status() == 0
+        # the portion's 150 tiles as 75 pairs on tcgen05; the decoded token and the stub as tiles of the other kernel, rows 0..2406
+        assert calls[before:] == [("tc", 75), ("mma", 2, (0, 2406))], calls[before:]
+    finally:
+        ops.attention_tc, ops.attention_mma = real_tc, real_mma
+    got[1].append(mixed[:1])
+    got[0] = [mixed[1:2401]]
+    got[2].append(mixed[2401:])
+    for r, n in enumerate(lens):
+        x = xs[r].double()
+        q = (x @ st["q_proj.weight"].double().T).view(n, Hq, hd)
+        k = (x @ st["k_proj.weight"].double().T).view(n, Hkv, hd)
+        v = (x @ st["v_proj.weight"].double().T).view(n, Hkv, hd)
+        q, k = P.rmsnorm(q, st["q_norm.weight"].double(), 1e-6), P.rmsnorm(k, st["k_norm.weight"].double(), 1e-6)
+        q, k = P.rope_neox(q, torch.arange(n), 10000.0), P.rope_neox(k, torch.arange(n), 10000.0)
+        q, k, v = P._r(q, True), P._r(k, True), P._r(v, True)
+        a = P._r(P.attention(q, k, v, None, st["sinks"].double(), True), True).reshape(n, Hq * hd)
+        ref = a @ st["o_proj.weight"].double().T
+        have = torch.cat(got[r]).double().cpu()
+        assert have.shape == ref.shape
+        err = (have - ref).abs().max() / ref.abs().max()
+        assert err <= 3e-2, (r, err)
+        tail = (have[-5:] - ref[-5:]).abs().max() / ref[-5:].abs().max()       # the rows of the mixed step
+        assert tail <= 3e-2, (r, tail)
+
+
 def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
     """A mixer that keeps a running mean of its inputs per request (fixed-size state, no keys),
     and an architecture that alternates it with attention, are defined here and run through the

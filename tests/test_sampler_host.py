@@ -46,3 +46,36 @@ def test_penalties():
     assert pick_from_pool(ids, vals, p, [0, 1], SplitMix64(0)) == 0       # 1.0 vs 0.95
     assert pick_from_pool([0, 2], [-0.4, -1.0], p, [0], SplitMix64(0)) == 0   # -0.8 still above -1.0
     assert pick_from_pool([0, 2], [-0.6, -1.0], p, [0], SplitMix64(0)) == 2   # -1.2 below -1.0
+
+
+def test_native_rows_match_the_python_twin():
+    """The C++ choice over a block of rows against pick_from_pool row by row: greedy and sampled
+    rows, penalties, rows that are skipped, ties, and the same advance of each row's random stream."""
+    import numpy as np
+    from quench6k_b200.sampling.sampler import pick_rows_native
+    rng = random.Random(5)
+    for case in range(60):
+        rows, pool = rng.randint(1, 9), rng.choice([4, 64, 256])
+        ids = np.zeros((rows, pool), dtype=np.int32)
+        vals = np.zeros((rows, pool), dtype=np.float32)
+        params, sizes, generated, seeds = [], [], [], []
+        for r in range(rows):
+            n = rng.randint(1, pool)
+            cand = rng.sample(range(5000), n)
+            ids[r, :n] = cand
+            vals[r, :n] = [round(rng.gauss(0, 2), rng.choice([1, 5])) for _ in range(n)]
+            params.append(SamplingParams(temperature=rng.choice([0.0, 0.3, 1.0, 2.5]), top_k=rng.choice([0, 1, 5, 40]),
+                                         top_p=rng.choice([1.0, 0.9, 0.3]), min_p=rng.choice([0.0, 0.05, 0.1]),
+                                         presence_penalty=rng.choice([0.0, 0.7]), repetition_penalty=rng.choice([1.0, 1.3])))
+            sizes.append(0 if rng.random() < 0.15 else n)
+            generated.append(rng.sample(cand, min(n, 3)) + [7777])
+            seeds.append(rng.getrandbits(64))
+        a, b = [SplitMix64(s) for s in seeds], [SplitMix64(s) for s in seeds]
+        got = pick_rows_native(ids, vals, sizes, params, generated, a)
+        for r in range(rows):
+            if sizes[r] == 0:
+                assert a[r].state == seeds[r]                     # a skipped row draws nothing
+                continue
+            want = pick_from_pool(ids[r, :sizes[r]], vals[r, :sizes[r]], params[r], generated[r], b[r])
+            assert got[r] == want, (case, r, params[r])
+            assert a[r].state == b[r].state

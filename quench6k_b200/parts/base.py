@@ -68,8 +68,10 @@ class LayerCache:
 class Part:
     # True if forward() launches the same kernels with the same arguments whenever the step has
     # the same number of rows and the same block-table widths (everything else read on the device):
-    # such steps may be replayed from a CUDA graph.  Parts that look at the step's host fields
-    # (q_lens, pos_starts, slots) must leave this False.
+    # such steps may be replayed from a CUDA graph.  The token counts (q_lens) are part of a
+    # recorded step's identity and may shape the launches; where the requests stand (pos_starts)
+    # and their slots are not: a part that needs them on the host must leave this False, or use
+    # them only while ctx.bounds_only is False (StepContext.key_tiles does so).
     graph_safe = False
 
     def tensors(self) -> List[TensorSpec]:

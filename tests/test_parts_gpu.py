@@ -266,3 +266,123 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
         assert (g - whole[rid]).abs().max() <= 1e-5 * whole[rid].abs().max()
     runner.end_request("a"), runner.end_request("b")
     runner.manager.check()
+
+
+def test_toy_feed_forward_with_routing_and_toy_position_encoding(tmp_path):
+    """A feed-forward that routes each token to one of three linear maps, and a rotary encoding
+    that pairs neighbouring dimensions, are defined here, registered, chosen by a PartSpec and run
+    through the unchanged framework (model folder, loader, step function, cache), in one step and
+    cut into portions, against the same model written out in plain tensor code."""
+    from dataclasses import dataclass
+    from quench6k_b200.config import register_architecture
+    from quench6k_b200.engine import ModelRunner, StepEntry
+    from quench6k_b200.models.decoder import DecoderModel
+    from quench6k_b200.parts import FeedForward, PositionEncoding, register_feed_forward, register_position_encoding
+    from quench6k_b200.spec import LayerSpec, ModelSpec, PartSpec, TensorSpec
+    from quench6k_b200.weights import index_folder, write_model_folder
+
+    def rotate_pairs(x, positions, theta):
+        """(x[2i], x[2i+1]) turned by position * theta^(-2i/hd)."""
+        hd = x.shape[-1]
+        inv = theta ** (-torch.arange(0, hd, 2, dtype=torch.float64, device=x.device) / hd)
+        ang = positions.double()[:, None] * inv
+        c, s = torch.cos(ang)[:, None, :].to(x.dtype), torch.sin(ang)[:, None, :].to(x.dtype)
+        a, b = x[..., 0::2].clone(), x[..., 1::2].clone()
+        out = torch.empty_like(x)
+        out[..., 0::2], out[..., 1::2] = a * c - b * s, a * s + b * c
+        return out
+
+    @register_position_encoding("toy_pairwise_rotary")
+    class PairwiseRotary(PositionEncoding):
+        def __init__(self, head_dim, theta):
+            self.hd, self.theta = head_dim, theta
+
+        def fused_rope_theta(self):
+            return None                       # not the rotation the fused kernel applies
+
+        def apply(self, x, positions):
+            x.copy_(rotate_pairs(x, positions, self.theta))
+
+    @register_feed_forward("toy_switch")
+    class Switch(FeedForward):
+        """y = p_e * (W_e x), e the most likely of `n` maps under softmax(R x)."""
+        def __init__(self, hidden_size, n):
+            self.D, self.n = hidden_size, n
+
+        def tensors(self):
+            return [TensorSpec("router.weight", (self.n, self.D), "f32", ("normal", 0.5)),
+                    TensorSpec("maps.weight", (self.n, self.D, self.D), "f32", ("normal", 0.2))]
+
+        def bind(self, get, rt):
+            self.rt = rt
+            self.r, self.w = get("router.weight").to(rt.device, torch.float32), get("maps.weight").to(rt.device, torch.float32)
+
+        def forward(self, xn, ctx, out):
+            x = xn.float()
+            p = torch.softmax(x @ self.r.T, -1)
+            top, e = p.max(-1)
+            out += top[:, None] * torch.einsum("tij,tj->ti", self.w[e], x)
+
+    @dataclass
+    class ToyConfig:
+        hidden_size: int
+        vocab_size: int
+        architectures: list
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d["hidden_size"], d["vocab_size"], d["architectures"])
+
+        def to_dict(self):
+            return dict(self.__dict__)
+
+        def save(self, folder):
+            import json, os
+            with open(os.path.join(folder, "config.json"), "w") as f:
+                json.dump(self.to_dict(), f)
+
+    D, V, Hq, Hkv, hd, eps, theta = 40, 61, 3, 1, 16, 1e-5, 500.0
+
+    def build(cfg):
+        norm = PartSpec("rmsnorm", {"eps": eps, "init": "random"})
+        attn = PartSpec("attention", {"num_heads": Hq, "num_kv_heads": Hkv, "head_dim": hd, "eps": eps,
+                                      "pos": PartSpec("toy_pairwise_rotary", {"head_dim": hd, "theta": theta})})
+        layers = [LayerSpec("model.layers.0.", attn, PartSpec("toy_switch", {"n": 3}), norm)]
+        return ModelSpec(cfg.hidden_size, cfg.vocab_size, layers, order=[0], kv_source=[None], final_norm=norm, init_std=0.2)
+
+    register_architecture("ToySwitchLM", ToyConfig, build)
+    cfg = ToyConfig(D, V, ["ToySwitchLM"])
+    spec = build(cfg)
+    write_model_folder(str(tmp_path), cfg, DecoderModel(spec).tensors(), 3, spec.init_std)
+    w = {n: f.read(n).double() for n, (f, e) in index_folder(str(tmp_path)).items()}
+    runner = ModelRunner.from_folder(str(tmp_path), dtype="float32", page_size=4, num_pages=16, max_requests=2)
+    toks = helpers.random_tokens(23, V, 5)
+
+    # the same model in plain tensor code
+    L = "model.layers.0."
+    h = P.embed(torch.tensor(toks), w["model.embed_tokens.weight"])
+    x = P.rmsnorm(h, w[L + "input_layernorm.weight"], eps)
+    n = len(toks)
+    q = (x @ w[L + "self_attn.q_proj.weight"].T).view(n, Hq, hd)
+    k = (x @ w[L + "self_attn.k_proj.weight"].T).view(n, Hkv, hd)
+    v = (x @ w[L + "self_attn.v_proj.weight"].T).view(n, Hkv, hd)
+    q, k = rotate_pairs(q, torch.arange(n), theta), rotate_pairs(k, torch.arange(n), theta)
+    h = h + P.attention(q, k, v, None, None, False).reshape(n, Hq * hd) @ w[L + "self_attn.o_proj.weight"].T
+    x = P.rmsnorm(h, w[L + "post_attention_layernorm.weight"], eps)
+    p = torch.softmax(x @ w[L + "mlp.router.weight"].T, -1)
+    top, e = p.max(-1)
+    assert len(set(e.tolist())) > 1                        # the routing does choose different maps
+    h = h + top[:, None] * torch.einsum("tij,tj->ti", w[L + "mlp.maps.weight"][e], x)
+    want = P.rmsnorm(h, w["model.norm.weight"], eps) @ w["lm_head.weight"].T
+
+    runner.add_request("w")
+    whole = runner.step([StepEntry("w", toks, list(range(n)))]).double().cpu()
+    runner.end_request("w")
+    runner.add_request("c")
+    parts = []
+    for a, b in ((0, 9), (9, 11), (11, 12), (12, 23)):
+        parts.append(runner.step([StepEntry("c", toks[a:b], list(range(b - a)))]).double().cpu())
+    runner.end_request("c")
+    runner.manager.check()
+    for got in (whole, torch.cat(parts)):
+        assert (got - want).abs().max() <= 1e-4 * want.abs().max()

@@ -33,7 +33,13 @@ def _ptr(t: Optional[torch.Tensor]):
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream():
+    """The current stream's handle (the short way where this torch has it: a launch costs the host a few microseconds)."""
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -53,14 +59,19 @@ _LAUNCHES = {"q6k_moe_permute": 3, "q6k_moe_plan": 3, "q6k_gemm_tc": 1, "q6k_att
 launch_count = 0
 
 
+_functions = {}
+
+
 def _call(fn_name: str, *args):
     global launch_count
     launch_count += _LAUNCHES.get(fn_name, 1)
-    lib = library()
-    fn = getattr(lib, fn_name)
-    fn.restype = ctypes.c_int
+    fn = _functions.get(fn_name)
+    if fn is None:
+        fn = _functions[fn_name] = getattr(library(), fn_name)
+        fn.restype = ctypes.c_int
     rc = fn(*args)
     if rc != 0:
+        lib = library()
         lib.q6k_last_error.restype = ctypes.c_char_p
         raise KernelError(lib.q6k_last_error().decode())
 

@@ -22,6 +22,7 @@
 // warp); every wait is bounded and records a code in a status word when it runs out.  With other
 // page sizes the consumer warps copy the rows themselves with 16-byte cp.async into two stages.
 // Either way the 16-byte chunks are XOR-swizzled by the row, so ldmatrix reads are conflict-free.
+#include <climits>
 #include <map>
 #include <tuple>
 
@@ -38,16 +39,14 @@ struct AttnParams {
     const __nv_bfloat16* k_pages;            // [Hkv, pages, page_size, HD]
     const __nv_bfloat16* v_pages;
     const int* block_table;                  // [R, max_blocks]
-    const int* req_of_token;
-    const int* positions;
-    const int* tile_tok0;                    // first row of each tile
-    const int* tile_ntok;                    // tokens of each tile (consecutive positions of one request)
     const float* sinks;                      // [Hq] or null
     __nv_bfloat16* out;                      // [T, Hq*HD]
-    float* part_o;                           // [rows*Hq, max_splits, HD], rows counted from part_row0
-    float* part_ml;                          // [rows*Hq, max_splits, 2]
-    int part_row0;                           // first token row that the partial buffers cover
-    int max_blocks, page_size, window, Hq, Hkv, G, max_splits, min_tiles;
+    float* part_o;                           // [work items, Hkv, rows of a tile, HD]: what each CTA of a split tile found
+    float* part_ml;                          // [work items, Hkv, rows of a tile, 2]: its maximum and sum
+    const int* work;                         // [n_work, 8] from attention_plan_kernel: one record per CTA column
+    const int* tile_plan;                    // [n_tiles, 4]: first row, tokens, splits, first work item
+    int n_work;
+    int max_blocks, page_size, window, Hq, Hkv, G;
     float scale_log2;
     int pool_rows;                           // rows of the [Hkv * pages * page_size, HD] view of a pool (TMA path)
     int num_pages;                           // pages of a pool (per KV head)
@@ -79,14 +78,86 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-// Effective number of key splits of a tile: a function of its key range and the launch only,
-// computed alike by the attention and the merge kernel.
-__device__ __forceinline__ void split_plan(int first_tile, int end_tile, int max_splits, int min_tiles, int& per, int& se) {
-    const int n = end_tile - first_tile;
-    int want = n / min_tiles;
-    want = want < 1 ? 1 : (want > max_splits ? max_splits : want);
-    per = (n + want - 1) / want;
-    se = (n + per - 1) / per;
+// ---------------------------------------------------------------------------------------------
+// The plan of a launch: which CTA walks which key tiles.  Made on the device from the positions the
+// step really has (so a step replayed from a CUDA graph is balanced for its own contexts), once per
+// step and window; every layer's launch reads it.
+//
+// Tile i sees n_i key tiles.  With a budget of n_work CTAs per KV head, every CTA should walk about
+// per = sum(n_i) / n_work of them: tile i is split into n_i / per parts (at least one), each of
+// ceil(n_i / parts) key tiles.  If the parts do not fit the budget, per grows until they do
+// (n_work >= n_tiles, so one part per tile always fits).
+// work[w] = {first row, tokens, first position, request, part, parts, first work item, key tiles per part};
+// first row -1: no work.  tile_plan[i] = {first row, tokens, parts, first work item}.
+constexpr int PLAN_THREADS = 256;
+
+__device__ __forceinline__ int plan_block_sum(int v, int* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();                          // red may still be read from the call before
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    int t = 0;
+#pragma unroll
+    for (int w = 0; w < PLAN_THREADS / 32; ++w) t += red[w];
+    return t;
+}
+
+__global__ void __launch_bounds__(PLAN_THREADS) attention_plan_kernel(const int* __restrict__ positions, const int* __restrict__ req_of_token,
+                                                                       const int* __restrict__ tile_tok0, const int* __restrict__ tile_ntok,
+                                                                       int n_tiles, int window, int n_work, int min_per, int* __restrict__ work,
+                                                                       int* __restrict__ tile_plan) {
+    pdl_enter();
+    __shared__ int red[PLAN_THREADS / 32];
+    __shared__ int scan[PLAN_THREADS];
+    const int tid = threadIdx.x;
+    const int chunk = (n_tiles + PLAN_THREADS - 1) / PLAN_THREADS, i0 = tid * chunk, i1 = min(n_tiles, i0 + chunk);
+    auto key_tiles = [&](int i) {
+        const int tok0 = tile_tok0[i], first = positions[tok0], last = first + tile_ntok[i] - 1;
+        const int k_lo = window > 0 ? max(0, first - window + 1) : 0;
+        return last / KT + 1 - k_lo / KT;
+    };
+    long long mine = 0;
+    for (int i = i0; i < i1; ++i) mine += key_tiles(i);
+    const int total = plan_block_sum((int)min(mine, (long long)(INT_MAX / PLAN_THREADS)), red);      // clamped: the block's sum cannot overflow
+    int per = max(max(1, min_per), (total + n_work - 1) / n_work);
+    for (int round = 0; round < 64; ++round) {
+        int parts = 0;
+        for (int i = i0; i < i1; ++i) parts += max(1, key_tiles(i) / per);
+        if (plan_block_sum(parts, red) <= n_work) break;
+        per = round < 62 ? per + per / 4 + 1 : INT_MAX / 2;      // in the end one part per tile, which fits
+    }
+    int parts_mine = 0;
+    for (int i = i0; i < i1; ++i) parts_mine += max(1, key_tiles(i) / per);
+    __syncthreads();
+    scan[tid] = parts_mine;
+    __syncthreads();
+    for (int o = 1; o < PLAN_THREADS; o <<= 1) {                  // inclusive scan over the threads' chunks
+        const int v = tid >= o ? scan[tid - o] : 0;
+        __syncthreads();
+        scan[tid] += v;
+        __syncthreads();
+    }
+    int at = scan[tid] - parts_mine;
+    const int used = scan[PLAN_THREADS - 1];
+    for (int i = i0; i < i1; ++i) {
+        const int n = key_tiles(i), room = max(1, n / per);
+        const int each = (n + room - 1) / room, parts = (n + each - 1) / each;       // parts <= room
+        const int tok0 = tile_tok0[i], ntok = tile_ntok[i];
+        reinterpret_cast<int4*>(tile_plan)[i] = make_int4(tok0, ntok, parts, at);
+        const int first = positions[tok0], req = req_of_token[tok0];
+        for (int s = 0; s < room; ++s) {
+            int4* w = reinterpret_cast<int4*>(work) + 2 * (size_t)(at + s);
+            w[0] = make_int4(s < parts ? tok0 : -1, ntok, first, req);
+            w[1] = make_int4(s, parts, at, each);
+        }
+        at += room;
+    }
+    for (int w = used + tid; w < n_work; w += PLAN_THREADS) {
+        reinterpret_cast<int4*>(work)[2 * (size_t)w] = make_int4(-1, 0, 0, 0);
+        reinterpret_cast<int4*>(work)[2 * (size_t)w + 1] = make_int4(0, 1, 0, 1);
+    }
 }
 
 // Byte offset of 16-byte chunk c of row r in a swizzled [rows][HD] bf16 tile (the Q tile).
@@ -117,18 +188,21 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0)) attentio
     __shared__ __align__(8) uint64_t bars[8];
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[4]);
 
-    const int tile = blockIdx.z, kh = blockIdx.y, split = blockIdx.x;
+    const int kh = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g8 = lane >> 2, t4 = lane & 3;
     const int G = p.G;
-    const int tok0 = p.tile_tok0[tile], ntok = p.tile_ntok[tile];
-    const int pos_first = p.positions[tok0], pos_last = pos_first + ntok - 1;
-    const int* bt = p.block_table + (size_t)p.req_of_token[tok0] * p.max_blocks;
+    // this CTA's record of the plan: everything about its tile in one load
+    const int4 wa = reinterpret_cast<const int4*>(p.work)[2 * (size_t)blockIdx.x];
+    const int4 wb = reinterpret_cast<const int4*>(p.work)[2 * (size_t)blockIdx.x + 1];
+    const int tok0 = wa.x, ntok = wa.y, pos_first = wa.z, split = wb.x, se = wb.y, per = wb.w;
+    if (tok0 < 0) return;
+    const int pos_last = pos_first + ntok - 1;
+    const int* bt = p.block_table + (size_t)wa.w * p.max_blocks;
     const int k_lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
     const int first_tile = k_lo / KT, end_tile = pos_last / KT + 1;
-    int per, se;
-    split_plan(first_tile, end_tile, p.max_splits, p.min_tiles, per, se);
-    if (split >= se) return;
     const int t_begin = first_tile + split * per, t_end = min(end_tile, t_begin + per);
+    // where this CTA's partial results go: [work item][KV head][row of the tile]
+    const size_t part_row0 = ((size_t)blockIdx.x * p.Hkv + kh) * ROWS;
 
     // ---- the producer (one thread) brings every tile of this CTA's key range into the ring
     auto issue = [&](int i) {
@@ -384,11 +458,11 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0)) attentio
 #pragma unroll
             for (int w = 0; w < 4; ++w) acc += wgt[w] * red[((size_t)w * 16 + r) * LD + d];
             if (se == 1) p.out[row * HD + d] = __float2bfloat16_rn(acc * osc / den);
-            else p.part_o[((row - (size_t)p.part_row0 * p.Hq) * p.max_splits + split) * HD + d] = acc;
+            else p.part_o[(part_row0 + r) * HD + d] = acc;
         }
         if (se > 1 && sub == 0) {
-            p.part_ml[((row - (size_t)p.part_row0 * p.Hq) * p.max_splits + split) * 2] = M;
-            p.part_ml[((row - (size_t)p.part_row0 * p.Hq) * p.max_splits + split) * 2 + 1] = L;
+            p.part_ml[(part_row0 + r) * 2] = M;
+            p.part_ml[(part_row0 + r) * 2 + 1] = L;
         }
     } else {
 #pragma unroll
@@ -408,12 +482,12 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0)) attentio
                 for (int n = 0; n < DB; ++n)
                     *reinterpret_cast<uint32_t*>(p.out + row * HD + n * 8 + 2 * t4) = pack_bf16(o[n][hr * 2] * inv, o[n][hr * 2 + 1] * inv);
             } else {
-                float* po = p.part_o + ((row - (size_t)p.part_row0 * p.Hq) * p.max_splits + split) * HD;
+                float* po = p.part_o + (part_row0 + r) * HD;
 #pragma unroll
                 for (int n = 0; n < DB; ++n) *reinterpret_cast<float2*>(po + n * 8 + 2 * t4) = make_float2(o[n][hr * 2], o[n][hr * 2 + 1]);
                 if (t4 == 0) {
-                    p.part_ml[((row - (size_t)p.part_row0 * p.Hq) * p.max_splits + split) * 2] = m[hr];
-                    p.part_ml[((row - (size_t)p.part_row0 * p.Hq) * p.max_splits + split) * 2 + 1] = l[hr];
+                    p.part_ml[(part_row0 + r) * 2] = m[hr];
+                    p.part_ml[(part_row0 + r) * 2 + 1] = l[hr];
                 }
             }
         }
@@ -435,17 +509,16 @@ __global__ void __launch_bounds__(MERGE_THREADS) attention_merge_kernel(const At
     __shared__ float den_s[GROUPS];
     const int tile = blockIdx.x, kh = blockIdx.y, r = blockIdx.z, G = p.G;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int tok0 = p.tile_tok0[tile], ntok = p.tile_ntok[tile];
+    const int4 tp = reinterpret_cast<const int4*>(p.tile_plan)[tile];
+    const int tok0 = tp.x, ntok = tp.y, se = tp.z;
     const int tt = r / G, hg = r % G;
-    if (tt >= ntok) return;
-    const int pos_first = p.positions[tok0], pos_last = pos_first + ntok - 1;
-    const int k_lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
-    int per, se;
-    split_plan(k_lo / KT, pos_last / KT + 1, p.max_splits, p.min_tiles, per, se);
-    if (se == 1) return;                      // the attention kernel wrote the output itself
+    if (tt >= ntok || se == 1) return;        // one part: the attention kernel wrote the output itself
     const size_t row = (size_t)(tok0 + tt) * p.Hq + kh * G + hg;
-    const float* ml = p.part_ml + (row - (size_t)p.part_row0 * p.Hq) * p.max_splits * 2;
-    const float* po = p.part_o + (row - (size_t)p.part_row0 * p.Hq) * p.max_splits * HD;
+    // the parts of a tile are consecutive work items: from one part to the next it is a whole [Hkv, rows] block
+    const size_t rows_t = gridDim.z, first = ((size_t)tp.w * p.Hkv + kh) * rows_t + r;
+    const size_t ml_step = (size_t)p.Hkv * rows_t * 2, po_step = (size_t)p.Hkv * rows_t * HD;
+    const float* ml = p.part_ml + first * 2;
+    const float* po = p.part_o + first * HD;
     const float sk = p.sinks ? p.sinks[kh * G + hg] * LOG2E : -INFINITY;
     // every load of the first round goes out before the maximum is known: the values and the
     // (m, l) pairs do not depend on it
@@ -457,12 +530,12 @@ __global__ void __launch_bounds__(MERGE_THREADS) attention_merge_kernel(const At
     for (int j = 0; j < U; ++j) {
         const int s = g + j * GROUPS;
         if (s < se) {
-            v0[j] = *reinterpret_cast<const float2*>(ml + s * 2);
-            o0[j] = *reinterpret_cast<const float4*>(po + (size_t)s * HD + c * 4);
+            v0[j] = *reinterpret_cast<const float2*>(ml + s * ml_step);
+            o0[j] = *reinterpret_cast<const float4*>(po + s * po_step + c * 4);
         }
     }
     float M = sk;
-    for (int s = tid; s < se; s += MERGE_THREADS) M = fmaxf(M, ml[s * 2]);
+    for (int s = tid; s < se; s += MERGE_THREADS) M = fmaxf(M, ml[s * ml_step]);
     M = warp_max(M);
     if (lane == 0) red[warp] = M;
     __syncthreads();
@@ -485,8 +558,8 @@ __global__ void __launch_bounds__(MERGE_THREADS) attention_merge_kernel(const At
         for (int j = 0; j < U; ++j) {
             const int s = s0 + j * GROUPS;
             if (s < se) {
-                v[j] = *reinterpret_cast<const float2*>(ml + s * 2);
-                o[j] = *reinterpret_cast<const float4*>(po + (size_t)s * HD + c * 4);
+                v[j] = *reinterpret_cast<const float2*>(ml + s * ml_step);
+                o[j] = *reinterpret_cast<const float4*>(po + s * po_step + c * 4);
             }
         }
 #pragma unroll
@@ -543,9 +616,9 @@ int launch(const AttnParams& p, const CUtensorMap* maps, int n_tiles, cudaStream
             return q6k_check_launch("attention_mma: shared memory attribute");
         configured = true;
     }
-    q6k_launch(attention_mma_kernel<HD, WIDE, TMA>, dim3(p.max_splits, p.Hkv, n_tiles), (WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0), smem, st, maps[0], maps[1], maps[2], maps[3], p);
+    q6k_launch(attention_mma_kernel<HD, WIDE, TMA>, dim3(p.n_work, p.Hkv), (WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0), smem, st, maps[0], maps[1], maps[2], maps[3], p);
     if (int rc = q6k_check_launch("attention_mma")) return rc;
-    if (p.max_splits > 1) {
+    if (p.n_work > n_tiles) {                 // some tile may have more than one part
         q6k_launch(attention_merge_kernel<HD>, dim3(n_tiles, p.Hkv, ROWS), MERGE_THREADS, 0, st, p);
         return q6k_check_launch("attention_merge");
     }
@@ -563,37 +636,50 @@ int launch_hd(const AttnParams& p, const CUtensorMap* maps, bool wide, bool tma,
 // Rows per tile for a group size: 16 (narrow) or 128 (wide) query rows hold rows/G tokens.
 Q6K_API int q6k_attention_mma_supported(int hd, int G, int wide) { return (hd == 64 || hd == 128) && G >= 1 && G <= (wide ? 128 : 16); }
 
-// q: bfloat16 [T, Hq, hd]; pages: bfloat16 [Hkv, num_pages, page_size, hd]; tiles: tile_tok0/tile_ntok [n_tiles], the
-// tokens of a tile being consecutive positions of one request, at most (wide ? 128 : 16) / G of them.
-// part_o: FP32 [rows*Hq*max_splits*hd], part_ml: FP32 [rows*Hq*max_splits*2] (unused when max_splits == 1), rows
-// being the token rows from part_row0 to the last row of any tile.
 Q6K_API int q6k_attention_status() {
     int v = -1;
     if (cudaMemcpyFromSymbol(&v, g_attn_status, sizeof v) != cudaSuccess) return -1;
     return v;
 }
 
-// num_pages: pages in each pool (the TMA path addresses a pool as one [Hkv * num_pages * page_size, hd] matrix).
+// The plan of a step's launches for one tile list and window: tiles are tile_tok0/tile_ntok [n_tiles] (first row and
+// token count, consecutive positions of one request); work: int32 [n_work, 8], tile_plan: int32 [n_tiles, 4], both
+// 16-byte aligned; n_work >= n_tiles CTAs per KV head share the key tiles, none walking fewer than min_per unless
+// its tile has no more.
+Q6K_API int q6k_attention_plan(const int* positions, const int* req_of_token, const int* tile_tok0, const int* tile_ntok, int n_tiles,
+                               int window, int n_work, int min_per, int* work, int* tile_plan, cudaStream_t st) {
+    if (n_tiles == 0) return 0;
+    Q6K_REQUIRE(n_work >= n_tiles && window >= 0 && min_per >= 1, "attention_plan: %d work items for %d tiles (window %d, at least %d key tiles each)",
+                n_work, n_tiles, window, min_per);
+    Q6K_REQUIRE(((uintptr_t)work & 15) == 0 && ((uintptr_t)tile_plan & 15) == 0, "attention_plan: the plan's arrays must start on 16 bytes");
+    q6k_launch(attention_plan_kernel, 1, PLAN_THREADS, 0, st, positions, req_of_token, tile_tok0, tile_ntok, n_tiles, window, n_work, min_per,
+               work, tile_plan);
+    return q6k_check_launch("attention_plan");
+}
+
+// q: bfloat16 [T, Hq, hd]; pages: bfloat16 [Hkv, num_pages, page_size, hd] (num_pages: pages in each pool; the TMA path
+// addresses a pool as one [Hkv * num_pages * page_size, hd] matrix); work / tile_plan: what q6k_attention_plan made for
+// these tiles (of at most (wide ? 128 : 16) / G tokens each) and this window; part_o: FP32 [n_work * Hkv * rows * hd],
+// part_ml: FP32 [n_work * Hkv * rows * 2] with rows = wide ? 128 : 16 (unused when n_work == n_tiles).
 Q6K_API int q6k_attention_mma(const void* q, const void* k_pages, const void* v_pages, long long num_pages, const int* block_table,
-                              int max_blocks, int page_size, const int* req_of_token, const int* positions, const int* tile_tok0,
-                              const int* tile_ntok, int n_tiles, int wide, int window, const float* sinks, float scale, void* out,
-                              float* part_o, float* part_ml, int part_row0, int max_splits, int min_tiles, int Hq, int Hkv,
+                              int max_blocks, int page_size, const int* work, const int* tile_plan, int n_work, int n_tiles, int wide,
+                              int window, const float* sinks, float scale, void* out, float* part_o, float* part_ml, int Hq, int Hkv,
                               int hd, cudaStream_t st) {
     if (n_tiles == 0) return 0;
     Q6K_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention_mma: bad head counts Hq=%d Hkv=%d", Hq, Hkv);
     const int G = Hq / Hkv;
     Q6K_REQUIRE(q6k_attention_mma_supported(hd, G, wide), "attention_mma: head_dim %d / group size %d is not covered by the tensor-core kernel", hd, G);
-    Q6K_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0 && max_splits >= 1 && max_splits <= 65535 && min_tiles >= 1,
-                "attention_mma: bad page_size %d / max_blocks %d / window %d / splits %d", page_size, max_blocks, window, max_splits);
-    Q6K_REQUIRE(max_splits == 1 || (part_o && part_ml && part_row0 >= 0), "attention_mma: splitting the keys needs the partial buffers");
+    Q6K_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0 && n_work >= n_tiles && work && tile_plan,
+                "attention_mma: bad page_size %d / max_blocks %d / window %d / %d work items for %d tiles", page_size, max_blocks, window, n_work, n_tiles);
+    Q6K_REQUIRE(n_work == n_tiles || (part_o && part_ml), "attention_mma: splitting the keys needs the partial buffers");
     Q6K_REQUIRE(Hkv <= 65535 && n_tiles <= 65535, "attention_mma: grid limit exceeded (Hkv=%d, tiles=%d)", Hkv, n_tiles);
     AttnParams p{};
     p.q = (const __nv_bfloat16*)q, p.k_pages = (const __nv_bfloat16*)k_pages, p.v_pages = (const __nv_bfloat16*)v_pages;
-    p.block_table = block_table, p.req_of_token = req_of_token, p.positions = positions;
-    p.tile_tok0 = tile_tok0, p.tile_ntok = tile_ntok, p.sinks = sinks, p.out = (__nv_bfloat16*)out;
-    p.part_o = part_o, p.part_ml = part_ml, p.part_row0 = part_row0;
+    p.block_table = block_table, p.sinks = sinks, p.out = (__nv_bfloat16*)out;
+    p.work = work, p.tile_plan = tile_plan, p.n_work = n_work;
+    p.part_o = part_o, p.part_ml = part_ml;
     p.max_blocks = max_blocks, p.page_size = page_size, p.window = window, p.Hq = Hq, p.Hkv = Hkv, p.G = G;
-    p.max_splits = max_splits, p.min_tiles = min_tiles, p.scale_log2 = scale * LOG2E;
+    p.scale_log2 = scale * LOG2E;
     // pages of 8, 16, 32, 64 keys (or whole multiples of 64) are boxes TMA can place on the swizzle pattern
     p.num_pages = (int)num_pages;
     const long long pool_rows = num_pages * Hkv * page_size;

@@ -42,8 +42,6 @@ class StepContext:
     max_q_len: int = 0
     plans: dict = field(default_factory=dict)     # per-step launch plans that parts share across layers (keyed by the part)
     fed: Optional[torch.Tensor] = None            # int32 ids the step before sampled: a token id -(i + 1) stands for fed[i]
-    bounds_only: bool = False             # the launches are recorded and replayed for other positions: plans may use only
-                                          # the token counts and max_context, not where each request stands now
 
     def query_tiles(self, tokens_per_tile: int, at_most: Optional[int] = None):
         """Tiles of at most `tokens_per_tile` consecutive tokens of one request, as device arrays
@@ -60,27 +58,6 @@ class StepContext:
                 at += n
             both = torch.tensor([first, count], dtype=torch.int32).reshape(2, -1).to(self.token_ids.device, non_blocking=True)
             self.plans[key] = (both[0], both[1], len(first))
-        return self.plans[key]
-
-    def key_tiles(self, tokens_per_tile: int, keys_per_tile: int, window: Optional[int] = None, at_most: Optional[int] = None):
-        """(sum, largest) of the numbers of key tiles that the query tiles of query_tiles(tokens_per_tile,
-        at_most) walk through, a key tile being `keys_per_tile` keys at a multiple of that number
-        (with bounds_only: as if every request ended at max_context)."""
-        key = ("key_tiles", tokens_per_tile, keys_per_tile, window, at_most)
-        if key not in self.plans:
-            total = longest = 0
-            for r, n in enumerate(self.q_lens):
-                if at_most is not None and n > at_most:
-                    continue
-                start = self.pos_starts[r] if r < len(self.pos_starts) else 0
-                if self.bounds_only:
-                    start = max(0, self.max_context - n)
-                for i in range(0, n, tokens_per_tile):
-                    first, last = start + i, start + min(n, i + tokens_per_tile) - 1
-                    lo = max(0, first - window + 1) if window else 0
-                    tiles = last // keys_per_tile + 1 - lo // keys_per_tile
-                    total, longest = total + tiles, max(longest, tiles)
-            self.plans[key] = (total, longest)
         return self.plans[key]
 
     def short_requests(self, at_most: int):

@@ -216,7 +216,6 @@ class ModelRunner:
             static = torch.empty(total, dtype=torch.int32, device=self.rt.device)
             ctx = self._context(entries, widths, static)
             ctx.max_context = max(widths) * self.page_size          # launch plans must hold for every replay
-            ctx.bounds_only = True
             logits = self.model.forward(ctx, self.caches, self.states)
             result = logits.clone() if logits is not None else None
             torch.cuda.synchronize()

@@ -460,16 +460,34 @@ def attention_mma_supported(hd: int, G: int, wide: bool) -> bool:
     return bool(lib.q6k_attention_mma_supported(_i(hd), _i(G), _i(1 if wide else 0)))
 
 
+def attention_plan(positions: torch.Tensor, req_of_token: torch.Tensor, tile_tok0: torch.Tensor, tile_ntok: torch.Tensor,
+                   window: Optional[int], n_work: int, min_per: int = 2):
+    """Which CTA of attention_mma walks which key tiles, made on the device from the step's
+    positions: (work int32 [n_work, 8], tile_plan int32 [n_tiles, 4]).  n_work (at least the number
+    of tiles) CTAs per KV head share the key tiles about evenly; a tile's keys are split into
+    parts of at least min_per key tiles (of 64 keys).  One plan serves every layer with this
+    window; recorded into a CUDA graph it is remade from the positions of each replay."""
+    for nm, t in (("req_of_token", req_of_token), ("positions", positions), ("tile_tok0", tile_tok0), ("tile_ntok", tile_ntok)):
+        _need(t, nm, torch.int32)
+    n_tiles = tile_tok0.numel()
+    n_work = max(int(n_work), n_tiles)
+    work = torch.empty((n_work, 8), dtype=torch.int32, device=positions.device)
+    tile_plan = torch.empty((n_tiles, 4), dtype=torch.int32, device=positions.device)
+    _call("q6k_attention_plan", _ptr(positions), _ptr(req_of_token), _ptr(tile_tok0), _ptr(tile_ntok), _i(n_tiles), _i(window or 0),
+          _i(n_work), _i(min_per), _ptr(work), _ptr(tile_plan), _stream())
+    return work, tile_plan
+
+
 def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                   req_of_token: torch.Tensor, positions: torch.Tensor, tile_tok0: torch.Tensor, tile_ntok: torch.Tensor,
                   wide: bool, window: Optional[int], sinks: Optional[torch.Tensor], max_splits: int = 1, min_tiles: int = 2,
-                  scale: Optional[float] = None, out: Optional[torch.Tensor] = None, rows: Optional[Tuple[int, int]] = None) -> torch.Tensor:
+                  scale: Optional[float] = None, out: Optional[torch.Tensor] = None, plan=None) -> torch.Tensor:
     """bfloat16 tensor-core attention over the pages.  Tiles: tile_tok0[i] is the first row and
     tile_ntok[i] the number of tokens (consecutive positions of one request, at most
-    (128 if wide else 16) // G) of tile i.  max_splits: upper bound of key splits per tile.
-    Only the rows of the listed tiles are written (into `out` [T, Hq*hd] when given); rows: the
-    range (first, end) of token rows the tiles lie in, when they are a part of the step (the
-    buffers for the key splits are sized by it)."""
+    (128 if wide else 16) // G) of tile i.  plan: attention_plan(...) of these tiles and this
+    window; without one it is made here for max_splits CTAs per tile on average, none with fewer
+    than min_tiles key tiles.  Only the rows of the listed tiles are written (into `out`
+    [T, Hq*hd] when given)."""
     _need(q, "q", torch.bfloat16)
     T, Hq, hd = q.shape
     _need(k_pages, "k_pages", torch.bfloat16)
@@ -477,30 +495,30 @@ def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
     Hkv, num_pages, page_size, hd2 = k_pages.shape
     if hd2 != hd:
         raise KernelError(f"attention: q has head_dim {hd}, the pages {hd2}")
-    for nm, t in (("block_table", block_table), ("req_of_token", req_of_token), ("positions", positions),
-                  ("tile_tok0", tile_tok0), ("tile_ntok", tile_ntok)):
-        _need(t, nm, torch.int32)
+    _need(block_table, "block_table", torch.int32)
     if sinks is not None:
         _need(sinks, "sinks", torch.float32, (Hq,))
     n_tiles = tile_tok0.numel()
+    if plan is None:
+        plan = attention_plan(positions, req_of_token, tile_tok0, tile_ntok, window, n_tiles * max(1, max_splits), min_tiles)
+    work, tile_plan = plan
+    _need(work, "work", torch.int32)
+    _need(tile_plan, "tile_plan", torch.int32, (n_tiles, 4))
+    n_work = work.shape[0]
     if out is None:
         out = torch.empty((T, Hq * hd), dtype=torch.bfloat16, device=q.device)
     else:
         _need(out, "out", torch.bfloat16, (T, Hq * hd))
-    row0, row1 = rows if rows is not None else (0, T)
-    if not 0 <= row0 <= row1 <= T:
-        raise KernelError(f"attention_mma: rows {rows} outside the step's {T} rows")
     part_o = part_ml = None
-    if max_splits > 1:
-        n = max(1, row1 - row0)
-        ws = _workspace(n * Hq * max_splits * (hd + 2) * 4, q.device)
-        part_o = ws[: n * Hq * max_splits * hd]
-        part_ml = ws[n * Hq * max_splits * hd: n * Hq * max_splits * (hd + 2)]
+    if n_work > n_tiles:
+        rows = n_work * Hkv * (128 if wide else 16)
+        ws = _workspace(rows * (hd + 2) * 4, q.device)
+        part_o = ws[: rows * hd]
+        part_ml = ws[rows * hd: rows * (hd + 2)]
     _call("q6k_attention_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ll(num_pages), _ptr(block_table),
-          _i(block_table.shape[1]), _i(page_size),
-          _ptr(req_of_token), _ptr(positions), _ptr(tile_tok0), _ptr(tile_ntok), _i(n_tiles), _i(1 if wide else 0), _i(window or 0),
-          _ptr(sinks), _f(scale if scale is not None else 1.0 / math.sqrt(hd)), _ptr(out), _ptr(part_o), _ptr(part_ml), _i(row0),
-          _i(max_splits), _i(min_tiles), _i(Hq), _i(Hkv), _i(hd), _stream())
+          _i(block_table.shape[1]), _i(page_size), _ptr(work), _ptr(tile_plan), _i(n_work), _i(n_tiles), _i(1 if wide else 0),
+          _i(window or 0), _ptr(sinks), _f(scale if scale is not None else 1.0 / math.sqrt(hd)), _ptr(out), _ptr(part_o), _ptr(part_ml),
+          _i(Hq), _i(Hkv), _i(hd), _stream())
     return out
 
 

@@ -101,23 +101,23 @@ class Attention(Mixer):
                 count, row0, row1, most, reach = ctx.short_requests(cut)
                 if count:
                     self._split_keys(q, cache, table, ctx, most > narrow_tokens or not ops.attention_mma_supported(self.hd, G, False),
-                                     at_most=cut, out=out, rows=(row0, row1))
+                                     at_most=cut, out=out)
                 return out
         return self._split_keys(q, cache, table, ctx, wide)
 
-    def _split_keys(self, q, cache, table, ctx, wide, at_most=None, out=None, rows=None):
+    def _split_keys(self, q, cache, table, ctx, wide, at_most=None, out=None):
         """The mma.sync kernel over all requests of the step, or over those with at most `at_most` tokens."""
         G = self.Hq // self.Hkv
         tokens = (128 if wide else 16) // G
         tok0, ntok, n_tiles = ctx.query_tiles(tokens, at_most)
-        # split the keys over CTAs until the GPU is full, and no further: one wave of resident CTAs
-        # (a second, partly filled wave would cost as much as a full one).  Every CTA gets about the
-        # same number of key tiles, so a request deep in its context is split more often than the others.
-        total, longest = ctx.key_tiles(tokens, 64, self.window, at_most)
-        per = max(2, -(-total * self.Hkv // self._resident_ctas(wide)))
-        max_splits = max(1, min(128, longest // per))
+        # the keys are split over one wave of resident CTAs, and no further (a second, partly filled wave would cost as
+        # much as a full one); the plan is made on the device, once per step for all layers with this window
+        key = ("attention_plan", tokens, at_most, self.window, self.Hkv)
+        if key not in ctx.plans:
+            ctx.plans[key] = ops.attention_plan(ctx.positions, ctx.req_of_token, tok0, ntok, self.window,
+                                                self._resident_ctas(wide) // self.Hkv, min_per=2)
         return ops.attention_mma(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, tok0, ntok, wide, self.window,
-                                 self.sinks, max_splits=max_splits, min_tiles=per, scale=self.scale, out=out, rows=rows)
+                                 self.sinks, scale=self.scale, out=out, plan=ctx.plans[key])
 
     def _sm_count(self) -> int:
         if "_sms" not in self.__dict__:

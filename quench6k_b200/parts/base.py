@@ -70,8 +70,9 @@ class Part:
     # the same number of rows and the same block-table widths (everything else read on the device):
     # such steps may be replayed from a CUDA graph.  The token counts (q_lens) are part of a
     # recorded step's identity and may shape the launches; where the requests stand (pos_starts)
-    # and their slots are not: a part that needs them on the host must leave this False, or use
-    # them only while ctx.bounds_only is False (StepContext.key_tiles does so).
+    # and their slots are not: a part whose launches depend on them must leave this False (the
+    # attention part plans its key splits on the device for that reason; the order of its
+    # prompt tiles, which only balances the load, is the one thing it takes from pos_starts).
     graph_safe = False
 
     def tensors(self) -> List[TensorSpec]:

@@ -72,14 +72,3 @@ def test_short_requests_go_one_way_and_the_others_another():
     assert sorted(covered) == list(range(80))                      # every row of the step exactly once
     none0, nonen, zero = ctx.query_tile_pairs(16, False, more_than=64)
     assert zero == 0 and tuple(none0.shape) == (0, 2)
-
-
-def test_key_tiles_counts_what_each_query_tile_walks_through():
-    ctx = make_ctx([1, 40, 1], [1000, 0, 63])
-    # one token at position 1000: key tiles 0..15; 40 tokens from 0 in tiles of 16: 1, 1, 1; one token at 63: 1
-    assert ctx.key_tiles(16, 64) == (16 + 3 + 1, 16)
-    assert ctx.key_tiles(16, 64, at_most=8) == (17, 16)
-    assert ctx.key_tiles(16, 64, window=100) == (2 + 3 + 1, 2)          # positions 901..1000 lie in key tiles 14 and 15
-    ctx.plans.clear()
-    ctx.bounds_only, ctx.max_context = True, 2048                       # recorded steps: every request as if it ended at max_context
-    assert ctx.key_tiles(16, 64) == (32 + (32 + 32 + 32) + 32, 32)

@@ -382,6 +382,51 @@ def test_attention_mma(Hq, Hkv, hd, ps, window, sinks, mode):
         assert err <= 1.5e-2, (max_splits, err)
     gen = ops.attention_generic(q, kp.to(DEV), vp.to(DEV), bt, ctx.req_of_token, ctx.positions, window, sk)
     assert (out.float() - gen.float()).abs().max() <= 2e-2 * gen.float().abs().max()
+    # a plan made once and handed in, with a budget of CTAs that the long request gets most of
+    plan = ops.attention_plan(ctx.positions, ctx.req_of_token, tok0, ntok, window, n_work=n_tiles + 9, min_per=2)
+    out = ops.attention_mma(q, kp.to(DEV), vp.to(DEV), bt, ctx.req_of_token, ctx.positions, tok0, ntok, wide, window, sk, plan=plan)
+    err = (out.double().cpu() - want).abs().max() / want.abs().max()
+    assert err <= 1.5e-2, ("plan", err)
+
+
+@pytest.mark.parametrize("window", [None, 300])
+@pytest.mark.parametrize("n_work,min_per", [(7, 2), (8, 1), (40, 2), (296, 2), (1000, 3)])
+def test_attention_plan_shares_the_key_tiles(window, n_work, min_per):
+    """The device-made plan of the key splits: every tile's key tiles are covered once by its
+    parts, the parts are consecutive work items, no more work items are used than given, and a
+    request deep in its context gets more of them than the others."""
+    from quench6k_b200 import ops
+    q_lens = [1, 2, 1, 40, 1, 1, 2]
+    starts = [70000, 130, 0, 5000, 63, 64, 2047]
+    tables = [[list(range(-(-(a + n) // 16))) for a, n in zip(starts, q_lens)]]
+    ctx = helpers.make_context(q_lens, starts, tables)
+    tok0, ntok, n_tiles = ctx.query_tiles(16)
+    work, tiles = ops.attention_plan(ctx.positions, ctx.req_of_token, tok0, ntok, window, n_work, min_per)
+    work, tiles = work.cpu().tolist(), tiles.cpu().tolist()
+    assert len(work) == max(n_work, n_tiles) and len(tiles) == n_tiles
+    pos = ctx.positions.cpu().tolist()
+    req = ctx.req_of_token.cpu().tolist()
+    used, biggest = 0, {}
+    for i, (t0, nt, parts, w0) in enumerate(tiles):
+        assert (t0, nt) == (tok0[i].item(), ntok[i].item())
+        first, last = pos[t0], pos[t0] + nt - 1
+        lo = max(0, first - window + 1) if window else 0
+        n = last // 64 + 1 - lo // 64
+        covered = 0
+        for s in range(parts):
+            a, b = work[w0 + s][:4], work[w0 + s][4:]
+            assert a == [t0, nt, first, req[t0]] and b[:3] == [s, parts, w0]
+            each = b[3]
+            covered += min(each, n - s * each)
+            assert n - s * each > 0                                  # no part without keys
+            assert each >= min(min_per, n)
+        assert covered == n
+        used = max(used, w0 + parts)
+        biggest[i] = parts
+    live = [w for w in work if w[0] >= 0]
+    assert len(live) == sum(biggest.values()) and used <= len(work)
+    if n_work >= 40 and window is None:
+        assert biggest[0] == max(biggest.values()) and biggest[0] > 4 * biggest[2]      # 70,000 keys against one
 
 
 @pytest.mark.parametrize("scoring,renorm", [("softmax", True), ("sigmoid", False)])
@@ -480,7 +525,7 @@ def test_attention_tc(Hq, Hkv, ps, window, sinks):
         assert torch.isnan(out[row0:row1].float()).any() and not torch.isnan(out[:row0].float()).any()
         s0, sn, n_short = ctx.query_tiles((128 if wide else 16) // G, at_most=cut)
         ops.attention_mma(q, kp.to(DEV), vp.to(DEV), bt, ctx.req_of_token, ctx.positions, s0, sn, wide, window,
-                          sk.to(DEV) if sinks else None, max_splits=3, min_tiles=1, out=out, rows=(row0, row1))
+                          sk.to(DEV) if sinks else None, max_splits=3, min_tiles=1, out=out)
         assert ops.tc_status() == 0
         err = (out.double().cpu() - want).abs().max() / want.abs().max()
         assert err <= 1.5e-2, ("two kernels", err)

@@ -142,15 +142,15 @@ def test_attention_part_mixed_step_at_head_size_128():
     real_tc, real_mma = ops.attention_tc, ops.attention_mma
     try:
         ops.attention_tc = lambda *a, **k: (calls.append(("tc", a[6].shape[0])), real_tc(*a, **k))[1]
-        ops.attention_mma = lambda *a, **k: (calls.append(("mma", a[6].numel(), k.get("rows"))), real_mma(*a, **k))[1]
+        ops.attention_mma = lambda *a, **k: (calls.append(("mma", a[6].numel())), real_mma(*a, **k))[1]
         got = {}
         got[1] = [run(xs[1][:1500], helpers.make_context([1500], [0], [[tables[1]]]))]
         got[2] = [run(xs[2][:700], helpers.make_context([700], [0], [[tables[2]]]))]
         before = len(calls)
         mixed = run(torch.cat([xs[1][1500:], xs[0], xs[2][700:]]), helpers.make_context([1, 2400, 5], [1500, 0, 700], [[tables[1], tables[0], tables[2]]]))
         assert ops.tc_status() == 0
-        # the portion's 150 tiles as 75 pairs on tcgen05; the decoded token and the stub as tiles of the other kernel, rows 0..2406
-        assert calls[before:] == [("tc", 75), ("mma", 2, (0, 2406))], calls[before:]
+        # the portion's 150 tiles as 75 pairs on tcgen05; the decoded token and the stub as two tiles of the other kernel
+        assert calls[before:] == [("tc", 75), ("mma", 2)], calls[before:]
     finally:
         ops.attention_tc, ops.attention_mma = real_tc, real_mma
     got[1].append(mixed[:1])

@@ -82,6 +82,7 @@ class ModelRunner:
         self.max_graphs = 64
         self.graph_max_tokens = 256
         self.graph_replays = 0
+        self.graph_captures = 0
         # ids sampled on the device by the step before (greedy decoding that does not wait for the host)
         self.sampled = torch.zeros(max(64, max_requests), dtype=torch.int32, device=rt.device)
         self._feed_limit = 0
@@ -224,6 +225,7 @@ class ModelRunner:
             with torch.cuda.graph(graph):
                 out = self.model.forward(ctx, self.caches, self.states)
             self._graphs[key] = (graph, ctx, static, out, ops.launch_count - before)
+            self.graph_captures += 1
             while len(self._graphs) > self.max_graphs:              # the graph replayed longest ago goes, with its buffers
                 self._graphs.popitem(last=False)
             return result

@@ -293,6 +293,7 @@ def main():
     ap.add_argument("--context", type=int, default=None)
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--points", default="1,64", help="further decode batch sizes, comma separated ('' for none)")
+    ap.add_argument("--temperature", type=float, default=0.0, help="sampling temperature of the end-to-end part (0: greedy, the headline)")
     ap.add_argument("--dtype", default="bfloat16")
     ap.add_argument("--page-size", type=int, default=None, help="KV page size (default: the configuration's 16)")
     ap.add_argument("--kernel", default=None, choices=["attention_prefill"],
@@ -422,8 +423,8 @@ def main():
                "frac": round(pf / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
 
     # end to end: Engine.step() with host ids in and sampled ids out each step
-    sp = SamplingParams(max_tokens=args.steps + args.warmup + 8, temperature=0.0)
     for i in range(args.batch):
+        sp = SamplingParams(max_tokens=args.steps + args.warmup + 8, temperature=args.temperature, seed=1000 + i)
         eng.adopt_request(rand_ids(ctx), rand_ids(1)[0], sp)
     for _ in range(args.warmup):
         eng.step()
@@ -439,6 +440,9 @@ def main():
     h2d = 4 * (3 * R + (R + 1) + 2 * R + R + R * ((ctx + 64 + page - 1) // page))       # the step's int32 block, tables included
     e2e = {"value": round(args.batch * args.steps / e2e_s, 1), "unit": "tok/s", "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": 4 * R}
+    if args.temperature > 0:
+        e2e["temperature"] = args.temperature
+        e2e["h2d_bytes_per_step"] += 32 * R               # the rows' sampling records
 
     out = {
         "metric": f"decode tok/s at batch {args.batch} (context {ctx}); prefill tok/s at {T} tokens; % of roofline",

@@ -4,6 +4,8 @@
 // (crates/cuda/kernels/topk.cu:212-303), and samples from a pool of the top candidates that an
 // exact device top-k delivers to the host (crates/cli/src/flint.rs:339-353, topk.cu:28-146).
 // Both are kept: the pool comes back sorted by (logit descending, id ascending).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "no_alloc.h"
 
@@ -193,6 +195,129 @@ __global__ void __launch_bounds__(1024) topk_pool_kernel(const float* logits, in
     }
 }
 
+// The same selection for long rows by a cluster of eight CTAs: each CTA reads an eighth of the row
+// once and keeps its keys in shared memory; the histograms of the radix passes meet in CTA 0's
+// shared memory (distributed shared memory: remote atomics and stores), which picks the bin; the
+// candidates are written into CTA 0's arrays, ties at the K-th key in ascending id order (the CTAs'
+// slices are consecutive id ranges); CTA 0 sorts and stores.  One pass over global memory
+// instead of six by one CTA.
+constexpr int TOPK_CLUSTER = 8;
+constexpr int TOPK_CLUSTER_MIN_V = 8192;                 // shorter rows: one CTA does as well
+constexpr int TOPK_CLUSTER_MAX_SLICE = 48 * 1024;        // keys of a slice (192 KB of shared memory)
+
+__global__ void __cluster_dims__(TOPK_CLUSTER, 1, 1) __launch_bounds__(1024, 1)
+    topk_pool_cluster_kernel(const float* __restrict__ logits, int V, int K, int slice, int* out_ids, float* out_vals) {
+    pdl_enter();
+    namespace cg = cooperative_groups;
+    extern __shared__ unsigned keys[];
+    __shared__ int hist[256];
+    __shared__ unsigned s_prefix;
+    __shared__ int s_need, s_count;
+    __shared__ unsigned ck[POOL_MAX];
+    __shared__ int ci[POOL_MAX];
+    __shared__ int seg_eq[1024];
+    __shared__ int cta_eq[TOPK_CLUSTER];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank(), tid = threadIdx.x, n = blockDim.x;
+    const float* row = logits + (size_t)(blockIdx.x / TOPK_CLUSTER) * V;
+    const int i0 = rank * slice, cnt = max(0, min(V, i0 + slice) - i0);
+    // CTA 0's copies are the cluster's
+    int* l_hist = cluster.map_shared_rank(hist, 0);
+    unsigned* l_prefix = cluster.map_shared_rank(&s_prefix, 0);
+    int* l_need = cluster.map_shared_rank(&s_need, 0);
+    int* l_count = cluster.map_shared_rank(&s_count, 0);
+    unsigned* l_ck = cluster.map_shared_rank(ck, 0);
+    int* l_ci = cluster.map_shared_rank(ci, 0);
+    int* l_cta_eq = cluster.map_shared_rank(cta_eq, 0);
+
+    for (int i = tid; i < cnt; i += n) keys[i] = key_of(row[i0 + i]);
+    if (tid == 0) s_prefix = 0u, s_need = K, s_count = 0;
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        const unsigned himask = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+        if (tid < 256) hist[tid] = 0;
+        cluster.sync();                                  // histograms are empty, the prefix of the pass before is out
+        const unsigned prefix = *l_prefix;
+        for (int i = tid; i < cnt; i += n) {
+            const unsigned k = keys[i];
+            if ((k & himask) == prefix) atomicAdd(&hist[(k >> shift) & 255], 1);
+        }
+        __syncthreads();
+        if (rank != 0 && tid < 256 && hist[tid] != 0) atomicAdd(&l_hist[tid], hist[tid]);
+        cluster.sync();                                  // CTA 0's histogram holds the whole row
+        if (rank == 0 && tid == 0) {
+            int need = s_need, b = 255;
+            for (; b > 0; --b) {
+                if (hist[b] >= need) break;
+                need -= hist[b];
+            }
+            s_need = need;
+            s_prefix = prefix | ((unsigned)b << shift);
+        }
+        __syncthreads();                                 // the bin is chosen before the histogram is cleared again
+    }
+    cluster.sync();
+    const unsigned kth = *l_prefix;
+    const int need_eq = *l_need;
+    // strictly greater: any order (sorted below)
+    for (int i = tid; i < cnt; i += n) {
+        const unsigned k = keys[i];
+        if (k > kth) {
+            const int at = atomicAdd(l_count, 1);
+            if (at < POOL_MAX) l_ck[at] = k, l_ci[at] = i0 + i;
+        }
+    }
+    // equal: the lowest ids.  Thread t owns a contiguous run of this CTA's slice.
+    const int seg = (cnt + n - 1) / n;
+    const int b0 = min(cnt, tid * seg), b1 = min(cnt, b0 + seg);
+    int mine = 0;
+    for (int i = b0; i < b1; ++i) mine += keys[i] == kth;
+    seg_eq[tid] = mine;
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0;
+        for (int i = 0; i < n; ++i) {
+            const int c = seg_eq[i];
+            seg_eq[i] = run;
+            run += c;
+        }
+        l_cta_eq[rank] = run;
+    }
+    cluster.sync();                                      // every greater key is in, every CTA's count of equal keys is known
+    const int gt = *l_count;
+    int r = seg_eq[tid];
+    for (int c = 0; c < rank; ++c) r += l_cta_eq[c];
+    for (int i = b0; i < b1 && r < need_eq; ++i)
+        if (keys[i] == kth) {
+            if (gt + r < POOL_MAX) l_ck[gt + r] = kth, l_ci[gt + r] = i0 + i;
+            ++r;
+        }
+    cluster.sync();                                      // nothing is written into CTA 0's memory after this
+    if (rank != 0) return;
+    for (int i = tid; i < POOL_MAX; i += n)
+        if (i >= K) ck[i] = 0u, ci[i] = 0x7fffffff;
+    __syncthreads();
+    for (int size = 2; size <= POOL_MAX; size <<= 1)
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            if (tid < POOL_MAX / 2) {
+                const int lo = 2 * tid - (tid & (stride - 1));
+                const int hi = lo + stride;
+                const bool desc = (lo & size) == 0;
+                const bool lo_first = ck[lo] > ck[hi] || (ck[lo] == ck[hi] && ci[lo] < ci[hi]);
+                if (lo_first != desc) {
+                    const unsigned tk = ck[lo]; ck[lo] = ck[hi]; ck[hi] = tk;
+                    const int ti = ci[lo]; ci[lo] = ci[hi]; ci[hi] = ti;
+                }
+            }
+            __syncthreads();
+        }
+    const size_t out0 = (size_t)(blockIdx.x / TOPK_CLUSTER) * K;
+    for (int i = tid; i < K; i += n) {
+        out_ids[out0 + i] = ci[i];
+        out_vals[out0 + i] = row[ci[i]];
+    }
+}
+
 }  // namespace
 
 Q6K_API int q6k_argmax_scratch_ints(int rows, int V) { return 2 * rows * ((V + ARGMAX_SLICE - 1) / ARGMAX_SLICE); }
@@ -214,8 +339,99 @@ Q6K_API int q6k_topk_pool(const float* logits, int rows, int V, int K, int* ids,
     if (rows == 0) return 0;
     Q6K_REQUIRE(rows > 0 && V > 0, "topk_pool: bad sizes rows=%d V=%d", rows, V);
     Q6K_REQUIRE(K >= 1 && K <= POOL_MAX && K <= V, "topk_pool: K=%d outside 1..min(%d, V=%d)", K, POOL_MAX, V);
+    const int slice = ((V + TOPK_CLUSTER - 1) / TOPK_CLUSTER + 3) & ~3;
+    if (V >= TOPK_CLUSTER_MIN_V && slice <= TOPK_CLUSTER_MAX_SLICE && (long long)rows * TOPK_CLUSTER <= 0x7fffffffLL) {
+        const size_t smem = (size_t)slice * sizeof(unsigned);
+        static bool configured = false;
+        if (!configured) {
+            if (cudaFuncSetAttribute(topk_pool_cluster_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)(TOPK_CLUSTER_MAX_SLICE * sizeof(unsigned))) != cudaSuccess)
+                return q6k_check_launch("topk_pool: shared memory attribute");
+            configured = true;
+        }
+        q6k_launch(topk_pool_cluster_kernel, rows * TOPK_CLUSTER, 1024, smem, st, logits, V, K, slice, ids, vals);
+        return q6k_check_launch("topk_pool");
+    }
     q6k_launch(topk_pool_kernel, rows, 1024, 0, st, logits, V, K, ids, vals);
     return q6k_check_launch("topk_pool");
+}
+
+// ---------------------------------------------------------------------------------------------
+// The choice of a token from a row's pool on the device, for requests without penalties: the same
+// arithmetic as the host's (crates/cli/src/flint.rs:384-431 in the reference; q6k_sample_rows in
+// the host library): p_i = exp((l_i - l_0) / temperature) in double precision from a 32-bit quotient,
+// p_i < min_p dropped, the shortest prefix whose normalised mass reaches top_p, the CDF inverted with
+// u * total by plain running sums.  The pool comes sorted from topk_pool_kernel.  One block per row:
+// every thread one exponential, thread 0 the sums.
+namespace {
+
+struct SampleRow {                  // 32 bytes per row, written by the host
+    int size, top_k;                // candidates to consider (<= 0: leave the row's output alone); 0: the whole pool
+    float temperature, top_p, min_p;
+    int pad;
+    double u;                       // the request's next uniform in [0, 1)
+};
+
+__global__ void __launch_bounds__(POOL_MAX) sample_pool_kernel(const int* __restrict__ ids, const float* __restrict__ vals, int stride,
+                                                               const SampleRow* __restrict__ rows, int* __restrict__ out) {
+    pdl_enter();
+    __shared__ double probs[POOL_MAX];
+    const int row = blockIdx.x, tid = threadIdx.x;
+    const SampleRow r = rows[row];
+    const int n = min(r.size, stride);
+    if (n <= 0) return;
+    ids += (size_t)row * stride, vals += (size_t)row * stride;
+    if (r.temperature <= 0.0f || r.top_k == 1 || n == 1) {
+        if (tid == 0) out[row] = ids[0];
+        return;
+    }
+    const int keep = r.top_k == 0 ? n : min(r.top_k, n);
+    const float top = vals[0];
+    if (tid < keep) {
+        double q = exp((double)((vals[tid] - top) / r.temperature));
+        if (r.min_p > 0.0f && q < (double)r.min_p) q = 0.0;
+        probs[tid] = q;
+    }
+    __syncthreads();
+    if (tid != 0) return;
+    double total = 0.0;
+    for (int i = 0; i < keep; ++i) total += probs[i];
+    int cut = keep;
+    if (r.top_p < 1.0f) {
+        double acc = 0.0;
+        for (int i = 0; i < keep; ++i) {
+            acc += probs[i] / total;
+            if (acc >= (double)r.top_p) {
+                cut = i + 1;
+                break;
+            }
+        }
+    }
+    total = 0.0;
+    for (int i = 0; i < cut; ++i) total += probs[i];
+    double left = r.u * total;
+    int pick = cut - 1;
+    for (int i = 0; i < cut; ++i) {
+        left -= probs[i];
+        if (left <= 0.0) {
+            pick = i;
+            break;
+        }
+    }
+    out[row] = ids[pick];
+}
+
+}  // namespace
+
+// ids / vals: what q6k_topk_pool wrote ([rows, K], sorted); params: [rows] records of 32 bytes on the device
+// {int32 size, int32 top_k, float temperature, float top_p, float min_p, int32 unused, double u}; out: int32 [rows].
+Q6K_API int q6k_sample_pool(const int* ids, const float* vals, int rows, int K, const void* params, int* out, cudaStream_t st) {
+    if (rows == 0) return 0;
+    Q6K_REQUIRE(rows > 0 && K >= 1 && K <= POOL_MAX, "sample_pool: bad sizes rows=%d K=%d", rows, K);
+    Q6K_REQUIRE(((uintptr_t)params & 7) == 0, "sample_pool: the rows' records must start on 8 bytes");
+    static_assert(sizeof(SampleRow) == 32, "the host writes records of 32 bytes");
+    q6k_launch(sample_pool_kernel, rows, POOL_MAX, 0, st, ids, vals, K, (const SampleRow*)params, out);
+    return q6k_check_launch("sample_pool");
 }
 
 // ---------------------------------------------------------------------------------------------

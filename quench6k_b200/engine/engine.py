@@ -7,13 +7,15 @@ Token ids in, token ids out (the reference's tokenizer and chat template,
 crates/cli/src/chat.rs, are outside this engine).  `step()` runs one scheduled batch;
 `generate()` runs until every given prompt has finished.
 
-While every live request decodes greedily, `step()` does not wait for the tokens of the step it has
-just launched: the argmax stays on the device, the next step's embedding reads it there, and the
-host plans that next step with placeholders, reading the real ids (one step late) while the GPU
-already works.  What the host needs a token's value for is the stop test; a request that turns out
-to have produced a stop token is ended then, the one token computed beyond it is dropped, and the
-tokens it returns are the same as without the look-ahead (the tests compare both).  A request with
-host-side sampling (temperature, penalties) switches the engine back to waiting for each step.
+While no live request uses penalties, `step()` does not wait for the tokens of the step it has just
+launched: the choice (argmax, or the sampler's arithmetic on the candidate pools with a uniform the
+host has drawn from the request's stream) is made on the device and stays there, the next step's
+embedding reads it, and the host plans that next step with placeholders, reading the real ids (one
+step late) while the GPU already works.  What the host needs a token's value for is the stop test;
+a request that turns out to have produced a stop token is ended then, the one token computed
+beyond it is dropped, and the tokens it returns are the same as without the look-ahead (the tests
+compare both).  A request with penalties is chosen by the host sampler, which needs the tokens it
+has generated: while one lives, the engine waits for each step.
 """
 from __future__ import annotations
 
@@ -26,7 +28,7 @@ import torch
 
 from .. import ops
 from ..sampling import Sampler, SamplingParams, SplitMix64
-from ..sampling.sampler import pool_size
+from ..sampling.sampler import ROW_RECORD, device_rows, pool_size
 from .batch import StepEntry
 from .runner import ModelRunner
 from .scheduler import FINISH_CANCELLED, FINISH_STOP, Request, ScheduledStep, Scheduler
@@ -66,6 +68,8 @@ class Engine:
         self._held: List[Request] = []     # ended, but their last token is still a placeholder
         self._pinned_ids = [None, None]
         self._flip = 0
+        self._pinned_rows = [None, None]   # sampling records of the steps in flight (two: one is read while the next is written)
+        self._flip_rows = 0
         self._ended_early: List[Request] = []     # ended outside step() (resolved by abort), reported by the next step()
 
     # ------------------------------------------------------------------ construction
@@ -125,9 +129,25 @@ class Engine:
         return self.scheduler.has_work() or self._inflight is not None or bool(self._held)
 
     # ------------------------------------------------------------------ stepping
-    def _all_greedy(self) -> bool:
+    def _device_picks(self) -> bool:
+        """Whether every live request's next token can be chosen on the device (greedy, or sampled
+        without penalties): then a step need not wait for the one before."""
+        return not any(r.params.penalized for r in self.scheduler.by_id.values())
+
+    def _pick_on_device(self, logits: torch.Tensor, samplers: List[Request]) -> torch.Tensor:
+        """The step's next tokens into runner.sampled, without a word to the host."""
         vocab = self.runner.vocab_size
-        return all(pool_size(r.params, vocab) == 1 for r in self.scheduler.by_id.values())
+        if all(pool_size(r.params, vocab) == 1 for r in samplers):
+            return ops.argmax(logits, out=self.runner.sampled)
+        n = len(samplers)
+        self._flip_rows ^= 1
+        host = self._pinned_rows[self._flip_rows]
+        if host is None or host.shape[0] < n:
+            host = self._pinned_rows[self._flip_rows] = torch.empty((max(64, n), 8), dtype=torch.int32, pin_memory=True)
+        k = device_rows([r.params for r in samplers], [r.rng for r in samplers], vocab, host.numpy().view(ROW_RECORD).reshape(-1))
+        rows = host[:n].to(logits.device, non_blocking=True)
+        ids, vals = ops.topk_pool(logits, k)
+        return ops.sample_pool(ids, vals, rows, out=self.runner.sampled)
 
     def _resolve(self) -> List[Request]:
         """Read the ids of the step in flight (waits for that step only), put them where their
@@ -165,7 +185,7 @@ class Engine:
         """Schedule and run one batch; returns the requests that ended and whose tokens are all known
         (with the look-ahead, a request is reported one call after the step that ended it)."""
         ended, self._ended_early = self._ended_early, []
-        ahead = self.lookahead and self._all_greedy()
+        ahead = self.lookahead and self._device_picks()
         if self._inflight is not None and not ahead:
             ended += self._resolve()           # the host samples the next tokens itself: it needs every earlier one
         plan: ScheduledStep = self.scheduler.schedule()
@@ -177,7 +197,7 @@ class Engine:
             logits = self.runner.step(entries, feed_limit=len(before.samplers) if before is not None else 0)
             samplers = [e.request for e in plan.entries if e.samples]
             if samplers and ahead:
-                ids = ops.argmax(logits, out=self.runner.sampled)          # stays on the device for the next step's embedding
+                ids = self._pick_on_device(logits, samplers)               # stays on the device for the next step's embedding
                 self._flip ^= 1
                 host = self._pinned_ids[self._flip]
                 if host is None or host.numel() < len(samplers):

@@ -659,6 +659,25 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
     return out
 
 
+def sample_pool(ids: torch.Tensor, vals: torch.Tensor, rows: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row from the sorted pools topk_pool made, chosen on the device with the
+    host sampler's arithmetic (no penalties).  rows: int32 [n, 8] on the device, per row the
+    32-byte record {int32 candidates, int32 top_k, float32 temperature, top_p, min_p, unused,
+    float64 uniform}; a row with no candidates keeps what `out` held."""
+    _need(ids, "ids", torch.int32)
+    n, K = ids.shape
+    _need(vals, "vals", torch.float32, (n, K))
+    _need(rows, "rows", torch.int32, (n, 8))
+    if out is None:
+        out = torch.empty(n, dtype=torch.int32, device=ids.device)
+    else:
+        _need(out, "out", torch.int32)
+        if out.numel() < n:
+            raise KernelError(f"sample_pool: out holds {out.numel()} ids, {n} rows are sampled")
+    _call("q6k_sample_pool", _ptr(ids), _ptr(vals), _i(n), _i(K), _ptr(rows), _ptr(out), _stream())
+    return out[:n]
+
+
 def topk_pool(logits: torch.Tensor, k: int):
     """(ids int32 [rows, k], vals float32 [rows, k]) sorted by (logit descending, id ascending); k <= 256."""
     _need(logits, "logits", torch.float32)

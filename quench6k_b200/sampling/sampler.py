@@ -125,6 +125,24 @@ def pick_rows_native(ids: np.ndarray, vals: np.ndarray, sizes: Sequence[int], pa
     return out.tolist()
 
 
+ROW_RECORD = np.dtype([("size", np.int32), ("top_k", np.int32), ("temperature", np.float32), ("top_p", np.float32),
+                       ("min_p", np.float32), ("pad", np.int32), ("u", np.float64)])     # 32 bytes, as ops.sample_pool reads them
+
+
+def device_rows(params: Sequence[SamplingParams], rngs: Sequence[SplitMix64], vocab: int, into: np.ndarray) -> int:
+    """Fill `into` (ROW_RECORD per row) for ops.sample_pool and return the pool size to fetch.
+    None of the requests may use penalties (those are applied on the host).  A row's random stream
+    advances exactly when the host sampler would advance it."""
+    k = 1
+    for i, p in enumerate(params):
+        if p.penalized:
+            raise ValueError("penalties are applied by the host sampler")
+        size = pool_size(p, vocab)
+        k = max(k, size)
+        into[i] = (size, p.top_k, p.temperature, p.top_p, p.min_p, 0, 0.0 if p.greedy else rngs[i].uniform())
+    return k
+
+
 class Sampler:
     """Chooses the next token of each row of a logits block [rows, vocab] (device, FP32).  The
     choice from the pools runs in the C++ host library unless Q6K_HOST=python asks for the

@@ -197,10 +197,20 @@ def test_lookahead_gives_the_same_tokens(tmp_path, name, pages, preempts):
         assert not eng.runner.manager.requests and not eng.has_unfinished()
     if preempts:
         assert ahead.stats["preemptions"] > 0 and plain.stats["preemptions"] > 0
-    # a request that samples on the host switches the engine back to waiting for each step
+    # sampled requests without penalties are chosen on the device and run ahead too: the same tokens as from the host sampler
+    trio = [params[0], SamplingParams(max_tokens=9, temperature=0.9, top_k=0, top_p=0.8, min_p=0.02, seed=3), params[2]]
+    host_side = plain.generate(prompts[:3], trio)
     mixed = Engine.from_folder(str(tmp_path), dtype="float32", num_pages=64, max_batch_tokens=9)
-    outs = mixed.generate(prompts[:3], [params[0], SamplingParams(max_tokens=6, temperature=0.9, seed=3), params[2]])
-    assert (outs[0].tokens, outs[2].tokens) == (want[0].tokens, want[2].tokens) and len(outs[1].tokens) == 6
+    outs = mixed.generate(prompts[:3], trio)
+    assert mixed.stats["lookahead_steps"] > 0
+    assert [o.tokens for o in outs] == [o.tokens for o in host_side] and len(outs[1].tokens) == 9
+    assert (outs[0].tokens, outs[2].tokens) == (want[0].tokens, want[2].tokens)
+    # a request with penalties is chosen on the host: while it lives the engine waits for each step
+    trio[1] = SamplingParams(max_tokens=6, temperature=0.9, repetition_penalty=1.2, seed=3)
+    before = dict(mixed.stats)
+    outs = mixed.generate(prompts[:3], trio)
+    assert [o.tokens for o in outs] == [o.tokens for o in plain.generate(prompts[:3], trio)]
+    assert mixed.stats["lookahead_steps"] - before["lookahead_steps"] <= mixed.stats["steps"] - before["steps"] - 6
 
 
 @pytest.mark.parametrize("seed", [0, 1])
@@ -220,7 +230,9 @@ def test_random_traffic_with_and_without_lookahead(tmp_path, seed):
         V, n, results, live, aborted = eng.runner.vocab_size, 0, {}, set(), set()
         for step in range(160):
             if n < 28 and rng.random() < 0.3:
-                sp = SamplingParams(max_tokens=rng.randint(1, 20), temperature=0.0 if rng.random() < 0.8 else 0.8, seed=rng.randrange(1 << 30),
+                sp = SamplingParams(max_tokens=rng.randint(1, 20), temperature=0.0 if rng.random() < 0.6 else 0.8, seed=rng.randrange(1 << 30),
+                                    top_k=rng.choice([20, 0, 5]), top_p=rng.choice([0.95, 1.0, 0.5]), min_p=rng.choice([0.0, 0.05]),
+                                    presence_penalty=0.5 if rng.random() < 0.1 else 0.0,
                                     stop_tokens=[rng.randrange(V) for _ in range(rng.choice([0, 0, 3, 40]))])
                 eng.add_request([rng.randrange(V) for _ in range(rng.randint(1, 30))], sp, rid=n)
                 live.add(n)

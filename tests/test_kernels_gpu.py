@@ -227,7 +227,7 @@ def test_qk_prep(dtype, Hq, Hkv, hd, ps, norm, theta):
     assert torch.equal(q2, q) and torch.equal(kp, k0)
 
 
-@pytest.mark.parametrize("rows,V", [(1, 10), (5, 384), (3, 151936), (2, 70001)])
+@pytest.mark.parametrize("rows,V", [(1, 10), (5, 384), (3, 151936), (2, 70001), (2, 8191), (9, 8192), (1, 8199), (1, 393216), (1, 400000)])
 def test_argmax_and_topk_pool(rows, V):
     from quench6k_b200 import ops
     x = _t(rows, V, scale=3.0, seed=V)
@@ -245,6 +245,38 @@ def test_argmax_and_topk_pool(rows, V):
             want = sorted(range(V), key=lambda i: (-row[i], i))[:k]
             assert ids[r].cpu().tolist() == want
             assert vals[r].cpu().tolist() == [row[i] for i in want]
+
+
+def test_sample_pool_matches_the_host_sampler():
+    """The choice from sorted candidate pools on the device against the host's pick_from_pool:
+    greedy rows, every sampling option, pools smaller than the fetched width, rows left alone."""
+    import random
+    import numpy as np
+    from quench6k_b200 import ops
+    from quench6k_b200.sampling import SamplingParams, SplitMix64
+    from quench6k_b200.sampling.sampler import ROW_RECORD, device_rows, pick_from_pool, pool_size
+    rng = random.Random(11)
+    for case in range(12):
+        rows, V = rng.randint(1, 40), rng.choice([300, 5000])
+        logits = torch.tensor([[round(rng.gauss(0, 3), rng.choice([1, 5])) for _ in range(V)] for _ in range(rows)], dtype=torch.float32)
+        params = [SamplingParams(temperature=rng.choice([0.0, 0.4, 1.0, 3.0]), top_k=rng.choice([0, 1, 7, 20, 200]),
+                                 top_p=rng.choice([1.0, 0.95, 0.4]), min_p=rng.choice([0.0, 0.03, 0.2])) for _ in range(rows)]
+        seeds = [rng.getrandbits(64) for _ in range(rows)]
+        a, b = [SplitMix64(x) for x in seeds], [SplitMix64(x) for x in seeds]
+        rec = np.zeros(rows, dtype=ROW_RECORD)
+        k = device_rows(params, a, V, rec)
+        skip = rng.randrange(rows)
+        rec[skip]["size"] = 0
+        ids, vals = ops.topk_pool(logits.to(DEV), k)
+        out = torch.full((rows + 3,), -5, dtype=torch.int32, device=DEV)
+        got = ops.sample_pool(ids, vals, torch.from_numpy(rec.view(np.int32).reshape(rows, 8)).to(DEV), out=out).cpu().tolist()
+        ids, vals = ids.cpu().numpy(), vals.cpu().numpy()
+        for r in range(rows):
+            n = pool_size(params[r], V)
+            want = pick_from_pool(ids[r, :n], vals[r, :n], params[r], [], b[r])
+            assert a[r].state == b[r].state
+            assert got[r] == (want if r != skip else -5), (case, r, params[r])
+        assert out[rows:].cpu().tolist() == [-5, -5, -5]
 
 
 def test_kernels_refuse_what_they_cannot_do():

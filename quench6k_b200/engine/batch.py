@@ -41,6 +41,9 @@ class StepContext:
     max_context: int = 0                  # largest position + 1 in the step
     max_q_len: int = 0
     plans: dict = field(default_factory=dict)     # per-step launch plans that parts share across layers (keyed by the part)
+    made: set = field(default_factory=set)        # keys of plans whose device-side part has been launched in this pass over the
+                                                  # layers: the runner empties it before it records the step, so that a kernel
+                                                  # that fills a plan from the step's positions is part of the recording
     fed: Optional[torch.Tensor] = None            # int32 ids the step before sampled: a token id -(i + 1) stands for fed[i]
 
     def query_tiles(self, tokens_per_tile: int, at_most: Optional[int] = None):

@@ -222,6 +222,7 @@ class ModelRunner:
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count
+            ctx.made.clear()                        # plans filled on the device are filled again inside the recording
             with torch.cuda.graph(graph):
                 out = self.model.forward(ctx, self.caches, self.states)
             self._graphs[key] = (graph, ctx, static, out, ops.launch_count - before)

@@ -461,18 +461,24 @@ def attention_mma_supported(hd: int, G: int, wide: bool) -> bool:
 
 
 def attention_plan(positions: torch.Tensor, req_of_token: torch.Tensor, tile_tok0: torch.Tensor, tile_ntok: torch.Tensor,
-                   window: Optional[int], n_work: int, min_per: int = 2):
+                   window: Optional[int], n_work: int, min_per: int = 2, into=None):
     """Which CTA of attention_mma walks which key tiles, made on the device from the step's
     positions: (work int32 [n_work, 8], tile_plan int32 [n_tiles, 4]).  n_work (at least the number
     of tiles) CTAs per KV head share the key tiles about evenly; a tile's keys are split into
     parts of at least min_per key tiles (of 64 keys).  One plan serves every layer with this
-    window; recorded into a CUDA graph it is remade from the positions of each replay."""
+    window; recorded into a CUDA graph it is remade from the positions of each replay.
+    into: the pair of tensors of an earlier call with the same sizes, to be filled again."""
     for nm, t in (("req_of_token", req_of_token), ("positions", positions), ("tile_tok0", tile_tok0), ("tile_ntok", tile_ntok)):
         _need(t, nm, torch.int32)
     n_tiles = tile_tok0.numel()
     n_work = max(int(n_work), n_tiles)
-    work = torch.empty((n_work, 8), dtype=torch.int32, device=positions.device)
-    tile_plan = torch.empty((n_tiles, 4), dtype=torch.int32, device=positions.device)
+    if into is not None:
+        work, tile_plan = into
+        _need(work, "work", torch.int32, (n_work, 8))
+        _need(tile_plan, "tile_plan", torch.int32, (n_tiles, 4))
+    else:
+        work = torch.empty((n_work, 8), dtype=torch.int32, device=positions.device)
+        tile_plan = torch.empty((n_tiles, 4), dtype=torch.int32, device=positions.device)
     _call("q6k_attention_plan", _ptr(positions), _ptr(req_of_token), _ptr(tile_tok0), _ptr(tile_ntok), _i(n_tiles), _i(window or 0),
           _i(n_work), _i(min_per), _ptr(work), _ptr(tile_plan), _stream())
     return work, tile_plan

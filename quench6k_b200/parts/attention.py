@@ -113,9 +113,10 @@ class Attention(Mixer):
         # the keys are split over one wave of resident CTAs, and no further (a second, partly filled wave would cost as
         # much as a full one); the plan is made on the device, once per step for all layers with this window
         key = ("attention_plan", tokens, at_most, self.window, self.Hkv)
-        if key not in ctx.plans:
+        if key not in ctx.made:                     # the first layer of this pass with these tiles and this window
             ctx.plans[key] = ops.attention_plan(ctx.positions, ctx.req_of_token, tok0, ntok, self.window,
-                                                self._resident_ctas(wide) // self.Hkv, min_per=2)
+                                                self._resident_ctas(wide) // self.Hkv, min_per=2, into=ctx.plans.get(key))
+            ctx.made.add(key)
         return ops.attention_mma(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, tok0, ntok, wide, self.window,
                                  self.sinks, scale=self.scale, out=out, plan=ctx.plans[key])
 

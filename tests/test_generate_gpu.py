@@ -95,18 +95,20 @@ def test_command_line(tmp_path):
     assert f"ids: {want}" in r.stdout
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_graph_replay_equals_eager_steps(tmp_path, dtype):
+@pytest.mark.parametrize("name,dtype,lengths", [("B", "float32", (9, 21, 14)), ("B", "bfloat16", (9, 21, 14)),
+                                                ("D", "bfloat16", (300, 700, 140))])
+def test_graph_replay_equals_eager_steps(tmp_path, name, dtype, lengths):
     """Decode-only steps replay a CUDA graph; the logits must equal those of the same steps run
     eagerly (the reference checks graph decoding against eager decoding the same way,
-    crates/cli/src/flint.rs:116-131)."""
+    crates/cli/src/flint.rs:116-131).  D: the head size at which the key splits of decode
+    attention are planned on the device; a replay must plan them from its own positions."""
     from quench6k_b200.engine import ModelRunner, StepEntry
-    cfg, _ = helpers.make_model_folder(str(tmp_path), "B", seed=31)
-    prompts = {f"r{i}": helpers.random_tokens(n, cfg["vocab_size"], 600 + n) for i, n in enumerate((9, 21, 14))}
+    cfg, _ = helpers.make_model_folder(str(tmp_path), name, seed=31)
+    prompts = {f"r{i}": helpers.random_tokens(n, cfg["vocab_size"], 600 + n) for i, n in enumerate(lengths)}
     tails = {rid: helpers.random_tokens(12, cfg["vocab_size"], 700 + i) for i, rid in enumerate(prompts)}
     outs = {}
     for graphs in (False, True):
-        runner = ModelRunner.from_folder(str(tmp_path), dtype=dtype, num_pages=32, cuda_graphs=graphs)
+        runner = ModelRunner.from_folder(str(tmp_path), dtype=dtype, num_pages=32 if name == "B" else 96, cuda_graphs=graphs)
         assert runner.cuda_graphs == graphs
         for rid, p in prompts.items():
             runner.add_request(rid)

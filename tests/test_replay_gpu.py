@@ -107,6 +107,55 @@ def test_first_tokens_and_long_decoding(model):
         helpers.assert_close(got, ref, dtype, f"{model['name']} {dtype} long decoding", max(8, cfg.get("sliding_window") or 0))
 
 
+def test_tensor_core_kernels_inside_the_model(tmp_path):
+    """A configuration with head size 128 and widths the tcgen05 products take, in bfloat16: a
+    2,400-token prompt in one step (prompt-portion attention on tensor cores) beside a decoded
+    token and the stub of another prompt (the key-splitting kernel writes their rows), prompts
+    alone (wide tiles), decoding in a changing batch (narrow tiles, the decode router and the
+    per-pair expert products), against the plain implementation.
+
+    Measured on this model: positions whose routing agrees differ from the plain implementation by
+    2.5e-3 of the scale in the median and 6.8e-3 at most (TOL is 1e-2, as everywhere); positions
+    where a near-tie of two router logits went the other way differ by 1e-2 to 6e-2, and their
+    margins reach 0.0100 of the rms of the token's router logits (sums over four times the width of
+    the tiny configurations carry more rounding), so a margin below 1.5e-2 counts as a possible
+    flip here; no more than 3 % of the positions may need that explanation."""
+    cfg, weights = helpers.make_model_folder(str(tmp_path), "D", seed=23)
+    V = cfg["vocab_size"]
+    reqs = {"long": helpers.random_tokens(2400, V, 1), "r1": helpers.random_tokens(300, V, 2), "r2": helpers.random_tokens(150, V, 3),
+            "r3": helpers.random_tokens(90, V, 4)}
+    every = lambda n: list(range(n))
+    steps = [{"step": 0, "entries": [{"id": "r1", "tokens": reqs["r1"][:280], "want": every(280)}], "end": []},
+             {"step": 1, "entries": [{"id": "r2", "tokens": reqs["r2"][:140], "want": every(140)}], "end": []},
+             {"step": 2, "entries": [{"id": "r1", "tokens": reqs["r1"][280:281], "want": [0]},
+                                     {"id": "long", "tokens": reqs["long"], "want": every(2400)},
+                                     {"id": "r2", "tokens": reqs["r2"][140:145], "want": every(5)}], "end": ["long"]},
+             {"step": 3, "entries": [{"id": "r3", "tokens": reqs["r3"][:80], "want": every(80)},
+                                     {"id": "r1", "tokens": reqs["r1"][281:282], "want": [0]}], "end": []}]
+    at = {"r1": 282, "r2": 145, "r3": 80}
+    n = 4
+    while at:
+        entries, end = [], []
+        for rid in list(at):
+            entries.append({"id": rid, "tokens": reqs[rid][at[rid]:at[rid] + 1], "want": [0]})
+            at[rid] += 1
+            if at[rid] == len(reqs[rid]):
+                end.append(rid)
+                del at[rid]
+        steps.append({"step": n, "entries": entries, "end": end})
+        n += 1
+    outputs, runner = helpers.run_replay(str(tmp_path), "bfloat16", steps, 2432 + 320 + 192 + 128)
+    got = helpers.collect(reqs, steps, outputs)
+    for rid, toks in reqs.items():
+        ref = helpers.plain_logits(cfg, weights, toks, True)
+        worst = helpers.assert_close(got[rid], ref, "bfloat16", f"D bfloat16 {rid}", 16, fragile=1.5e-2)
+        print(f"D bfloat16 {rid}: worst error {worst:.3e}")
+        err = (got[rid].double() - ref[0].double()).abs().reshape(len(toks), -1).max(-1).values / float(ref[0].abs().max())
+        assert int((err > helpers.TOL["bfloat16"]).sum()) <= 0.03 * len(toks) + 1, f"{rid}: too many positions beyond the tolerance"
+    from quench6k_b200 import ops
+    assert ops.tc_status() == 0
+
+
 def test_trace_run_program(model, tmp_path):
     """The program itself, as a user runs it: JSON lines in, `done` lines and .f32 files out."""
     if model["name"] != "B":

@@ -32,10 +32,20 @@ TINY_C = {
     "layer_order": [0, 1, 0, 1], "kv_source": [None, None, 0, None], "kv_page_size": 16,
 }
 
-ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# the head size and widths at which the bfloat16 path runs its tcgen05 / TMA kernels (not among the fixtures' names:
+# one test replays it)
+SMALL_D = {
+    "architectures": ["FlintForCausalLM"],
+    "hidden_size": 256, "num_hidden_layers": 2, "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 128,
+    "vocab_size": 1000, "n_routed_experts": 16, "num_experts_per_tok": 4, "moe_intermediate_size": 128,
+    "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "tie_word_embeddings": False, "scoring_func": "softmax",
+    "norm_topk_prob": True, "qk_norm": True, "attn_sinks": True, "kv_page_size": 16,
+}
+
+ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": SMALL_D}
 # norm weights: ones for A (as its description says), 1 + noise for the others so that a missing
 # multiplication by the weight shows
-NORM_INIT = {"A": "ones", "B": "random", "C": "random"}
+NORM_INIT = {"A": "ones", "B": "random", "C": "random", "D": "random"}
 
 
 def get(name):

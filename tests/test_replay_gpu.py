@@ -107,8 +107,11 @@ def test_first_tokens_and_long_decoding(model):
         helpers.assert_close(got, ref, dtype, f"{model['name']} {dtype} long decoding", max(8, cfg.get("sliding_window") or 0))
 
 
-def test_tensor_core_kernels_inside_the_model(tmp_path):
-    """A configuration with head size 128 and widths the tcgen05 products take, in bfloat16: a
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_tensor_core_kernels_inside_the_model(tmp_path, name):
+    """Configurations with head size 128 and widths the tcgen05 products take (D; E has every option
+    the other way: windows, groups of 8, sigmoid scores, a shared expert, a dense layer, tied
+    embeddings, pages of 32), in bfloat16: a
     2,400-token prompt in one step (prompt-portion attention on tensor cores) beside a decoded
     token and the stub of another prompt (the key-splitting kernel writes their rows), prompts
     alone (wide tiles), decoding in a changing batch (narrow tiles, the decode router and the
@@ -120,7 +123,7 @@ def test_tensor_core_kernels_inside_the_model(tmp_path):
     margins reach 0.0100 of the rms of the token's router logits (sums over four times the width of
     the tiny configurations carry more rounding), so a margin below 1.5e-2 counts as a possible
     flip here; no more than 3 % of the positions may need that explanation."""
-    cfg, weights = helpers.make_model_folder(str(tmp_path), "D", seed=23)
+    cfg, weights = helpers.make_model_folder(str(tmp_path), name, seed=23)
     V = cfg["vocab_size"]
     reqs = {"long": helpers.random_tokens(2400, V, 1), "r1": helpers.random_tokens(300, V, 2), "r2": helpers.random_tokens(150, V, 3),
             "r3": helpers.random_tokens(90, V, 4)}
@@ -148,12 +151,17 @@ def test_tensor_core_kernels_inside_the_model(tmp_path):
     got = helpers.collect(reqs, steps, outputs)
     for rid, toks in reqs.items():
         ref = helpers.plain_logits(cfg, weights, toks, True)
-        worst = helpers.assert_close(got[rid], ref, "bfloat16", f"D bfloat16 {rid}", 16, fragile=1.5e-2)
-        print(f"D bfloat16 {rid}: worst error {worst:.3e}")
+        worst = helpers.assert_close(got[rid], ref, "bfloat16", f"{name} bfloat16 {rid}", 16, fragile=1.5e-2)
+        print(f"{name} bfloat16 {rid}: worst error {worst:.3e}")
         err = (got[rid].double() - ref[0].double()).abs().reshape(len(toks), -1).max(-1).values / float(ref[0].abs().max())
         assert int((err > helpers.TOL["bfloat16"]).sum()) <= 0.03 * len(toks) + 1, f"{rid}: too many positions beyond the tolerance"
     from quench6k_b200 import ops
     assert ops.tc_status() == 0
+    # the same steps in true 32-bit arithmetic: no flips to explain, every position within 5e-6
+    outputs, _ = helpers.run_replay(str(tmp_path), "float32", steps, 2432 + 320 + 192 + 128)
+    got = helpers.collect(reqs, steps, outputs)
+    for rid, toks in reqs.items():
+        helpers.assert_close(got[rid], helpers.plain_logits(cfg, weights, toks, False), "float32", f"{name} float32 {rid}")
 
 
 def test_trace_run_program(model, tmp_path):

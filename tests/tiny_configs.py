@@ -42,10 +42,23 @@ SMALL_D = {
     "norm_topk_prob": True, "qk_norm": True, "attn_sinks": True, "kv_page_size": 16,
 }
 
-ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": SMALL_D}
+# the same with every option the other way: a window on two of three layers, groups of 8 query heads, sigmoid scores
+# without renormalisation, a shared expert, a dense first layer, tied embeddings, pages of 32, no power of two in sight
+SMALL_E = {
+    "architectures": ["FlintForCausalLM"],
+    "hidden_size": 384, "num_hidden_layers": 3, "num_attention_heads": 16, "num_key_value_heads": 2, "head_dim": 128,
+    "vocab_size": 777, "n_routed_experts": 24, "num_experts_per_tok": 6, "moe_intermediate_size": 192,
+    "rms_norm_eps": 1e-5, "rope_theta": 500000.0, "tie_word_embeddings": True, "scoring_func": "sigmoid",
+    "norm_topk_prob": False, "qk_norm": False, "attn_sinks": False,
+    "sliding_window": 500, "sliding_window_pattern": [True, False, True], "rope_pattern": [True, False, True],
+    "n_shared_experts": 1, "shared_expert_intermediate_size": 256,
+    "first_k_dense_replace": 1, "intermediate_size": 320, "kv_page_size": 32,
+}
+
+ALL = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": SMALL_D, "E": SMALL_E}
 # norm weights: ones for A (as its description says), 1 + noise for the others so that a missing
 # multiplication by the weight shows
-NORM_INIT = {"A": "ones", "B": "random", "C": "random", "D": "random"}
+NORM_INIT = {"A": "ones", "B": "random", "C": "random", "D": "random", "E": "random"}
 
 
 def get(name):

@@ -168,8 +168,9 @@ def test_launch_modes_give_the_same_logits(tmp_path):
     assert digests["0"] == digests["gemm"] == digests["1"], digests
 
 
-@pytest.mark.parametrize("name,pages,preempts", [("A", 64, False), ("A", 14, True), ("B", 24, False)])
-def test_lookahead_gives_the_same_tokens(tmp_path, name, pages, preempts):
+@pytest.mark.parametrize("name,pages,preempts,dtype", [("A", 64, False, "float32"), ("A", 14, True, "float32"), ("B", 24, False, "float32"),
+                                                       ("D", 64, False, "bfloat16")])
+def test_lookahead_gives_the_same_tokens(tmp_path, name, pages, preempts, dtype):
     """Greedy decoding without waiting for each step's tokens (they stay on the device, the host
     reads them one step late) against the engine that waits: the same tokens, finish reasons and
     preemption-safe bookkeeping, with stop tokens that do occur, ends by length, prompts cut into
@@ -179,7 +180,7 @@ def test_lookahead_gives_the_same_tokens(tmp_path, name, pages, preempts):
     cfg, _ = helpers.make_model_folder(str(tmp_path), name, seed=41)
     rng = random.Random(7)
     prompts = [helpers.random_tokens(rng.randint(3, 25), cfg["vocab_size"], 900 + i) for i in range(7)]
-    plain = Engine.from_folder(str(tmp_path), dtype="float32", num_pages=pages, max_batch_tokens=9, lookahead=False)
+    plain = Engine.from_folder(str(tmp_path), dtype=dtype, num_pages=pages, max_batch_tokens=9, lookahead=False)
     free = plain.generate(prompts, SamplingParams(max_tokens=18, temperature=0.0))
     # stop tokens taken from what the requests really produce, at different depths; some never stop
     params = []
@@ -188,7 +189,7 @@ def test_lookahead_gives_the_same_tokens(tmp_path, name, pages, preempts):
         params.append(SamplingParams(max_tokens=5 + 3 * i, temperature=0.0, stop_tokens=stops))
     want = plain.generate(prompts, params)
     assert plain.stats["lookahead_steps"] == 0
-    ahead = Engine.from_folder(str(tmp_path), dtype="float32", num_pages=pages, max_batch_tokens=9)
+    ahead = Engine.from_folder(str(tmp_path), dtype=dtype, num_pages=pages, max_batch_tokens=9)
     got = ahead.generate(prompts, params)
     assert ahead.stats["lookahead_steps"] > 0
     for w, g in zip(want, got):
@@ -202,7 +203,7 @@ def test_lookahead_gives_the_same_tokens(tmp_path, name, pages, preempts):
     # sampled requests without penalties are chosen on the device and run ahead too: the same tokens as from the host sampler
     trio = [params[0], SamplingParams(max_tokens=9, temperature=0.9, top_k=0, top_p=0.8, min_p=0.02, seed=3), params[2]]
     host_side = plain.generate(prompts[:3], trio)
-    mixed = Engine.from_folder(str(tmp_path), dtype="float32", num_pages=64, max_batch_tokens=9)
+    mixed = Engine.from_folder(str(tmp_path), dtype=dtype, num_pages=64, max_batch_tokens=9)
     outs = mixed.generate(prompts[:3], trio)
     assert mixed.stats["lookahead_steps"] > 0
     assert [o.tokens for o in outs] == [o.tokens for o in host_side] and len(outs[1].tokens) == 9

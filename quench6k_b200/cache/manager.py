@@ -258,14 +258,20 @@ class CacheManager:
 
     # ------------------------------------------------------------------ the step's description
     def pack_step(self, rids: Sequence[Hashable], tokens: Sequence[Sequence[int]], want: Sequence[Sequence[int]],
-                  widths: Sequence[int], vocab_size: int, out: np.ndarray, feed_limit: int = 0) -> Tuple[int, int, int, int, int]:
+                  widths: Sequence[int], vocab_size: int, out: np.ndarray, feed_limit: int = 0, pad: int = 0,
+                  pad_pages: Sequence[int] = (), pad_slot: int = 0) -> Tuple[int, int, int, int, int]:
         """Write the step's int32 block into `out`:
         [tokens T | positions T | request of token T | q_start R+1 | pos_start R | slot R | logit rows |
         one R x widths[g] block table per group].  Returns (ints written, T, wanted rows, longest
-        context, longest entry)."""
-        R = len(rids)
+        context, longest entry).  pad > 0 appends that many filler entries (counted in R, T and the
+        wanted rows): token 0 at position 0, its logits wanted, slot pad_slot and the single page
+        pad_pages[g] in group g."""
+        if pad < 0 or (pad and len(pad_pages) != len(widths)):
+            raise ValueError("one filler page per cache group is needed")
+        real = len(rids)
+        R = real + pad
         q_lens = [len(t) for t in tokens]
-        T, W = sum(q_lens), sum(len(w) for w in want)
+        T, W = sum(q_lens) + pad, sum(len(w) for w in want) + pad
         total = 3 * T + (R + 1) + 2 * R + W + sum(R * w for w in widths)
         if total > out.size:
             raise ValueError(f"the step needs {total} ints, the block holds {out.size}")
@@ -301,9 +307,16 @@ class CacheManager:
             psv[r] = req.length
             sl[r] = req.slot
             max_ctx, max_q = max(max_ctx, req.length + n), max(max_q, n)
+        for r in range(real, R):
+            tok[t], pos[t], rot[t], lr[w] = 0, 0, r, t
+            t, w = t + 1, w + 1
+            qs[r + 1], psv[r], sl[r] = t, 0, pad_slot
+            max_ctx, max_q = max(max_ctx, 1), max(max_q, 1)
         for g, wd in enumerate(widths):
             tb = take(R * wd).reshape(R, wd)
             tb[:] = -1
+            if pad:
+                tb[real:, 0] = pad_pages[g]
             for r, rid in enumerate(rids):
                 row = self.requests[rid].tables[g].array()
                 if len(row) > wd:

@@ -45,7 +45,7 @@ def host_lib():
         "q6k_cm_slots_free": (i, [vp]),
         "q6k_cm_num_live": (i, [vp]),
         "q6k_cm_table": (i, [vp, i64, i, ctypes.POINTER(_i32p), _i32p]),
-        "q6k_cm_fill_step": (i, [vp, i, _i64p, _i32p, _i32p, _i32p, _i32p, _i32p, i, i, _i32p, i64, _i64p]),
+        "q6k_cm_fill_step": (i, [vp, i, _i64p, _i32p, _i32p, _i32p, _i32p, _i32p, i, i, i, _i32p, i, _i32p, i64, _i64p]),
         "q6k_sched_create": (vp, [vp, i, i]),
         "q6k_sched_destroy": (None, [vp]),
         "q6k_sched_add": (i, [vp, i64, _i32p, i, i, _i32p, i]),
@@ -64,7 +64,7 @@ def host_lib():
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
         fn.restype, fn.argtypes = res, args
-    if lib.q6k_host_abi_version() != 2:
+    if lib.q6k_host_abi_version() != 3:
         raise RuntimeError("the host library does not match this package")
     _lib = lib
     return lib
@@ -263,12 +263,15 @@ class NativeCacheManager:
 
     # ------------------------------------------------------------------ the step's description
     def pack_step(self, rids: Sequence[Hashable], tokens: Sequence[Sequence[int]], want: Sequence[Sequence[int]],
-                  widths: Sequence[int], vocab_size: int, out: np.ndarray, feed_limit: int = 0) -> Tuple[int, int, int, int, int]:
+                  widths: Sequence[int], vocab_size: int, out: np.ndarray, feed_limit: int = 0, pad: int = 0,
+                  pad_pages: Sequence[int] = (), pad_slot: int = 0) -> Tuple[int, int, int, int, int]:
         """Write the step's int32 block into `out`:
         [tokens T | positions T | request of token T | q_start R+1 | pos_start R | slot R | logit rows |
         one R x widths[g] block table per group].  Returns (ints written, T, wanted rows, longest
         context, longest entry).  feed_limit > 0 admits token ids -1 .. -feed_limit, which stand for
-        tokens the step before has sampled and which are resolved on the device."""
+        tokens the step before has sampled and which are resolved on the device.  pad > 0 appends
+        that many filler entries (counted in R, T and the wanted rows): token 0 at position 0, its
+        logits wanted, slot pad_slot and the single page pad_pages[g] in group g."""
         R = len(rids)
         ids = np.array([self._known(r) for r in rids], dtype=np.int64)
         q_lens = i32([len(t) for t in tokens])
@@ -281,8 +284,11 @@ class NativeCacheManager:
         wflat = i32([i for w in want for i in w])
         wd = i32(list(widths) or [0])
         meta = np.zeros(5, dtype=np.int64)
+        pp = i32(list(pad_pages) or [0])
+        if pad and len(pad_pages) != len(widths):
+            raise ValueError("one filler page per cache group is needed")
         rc = host_lib().q6k_cm_fill_step(self._h, R, ptr64(ids), ptr32(q_lens), ptr32(flat), ptr32(wflat), ptr32(wc), ptr32(wd),
-                                         vocab_size, feed_limit, ptr32(out), out.size, ptr64(meta))
+                                         vocab_size, feed_limit, pad, ptr32(pp), pad_slot, ptr32(out), out.size, ptr64(meta))
         if rc == 5 and "wanted place" in host_lib().q6k_host_last_error().decode():
             for r, t, w in zip(rids, tokens, want):
                 for i in w:

@@ -422,7 +422,7 @@ int copy_out(const std::vector<T>& v, T* out, int cap, int* n, const char* what)
 }  // namespace
 
 API const char* q6k_host_last_error() { return g_msg; }
-API int q6k_host_abi_version() { return 2; }
+API int q6k_host_abi_version() { return 3; }
 
 // ------------------------------------------------------------------------------- cache manager
 API void* q6k_cm_create(int n_groups, const int* sliding, const int* windows, int page_size, const int* num_pages, int max_requests) {
@@ -478,19 +478,25 @@ API int q6k_cm_table(void* h, int64_t id, int group, const int32_t** pages, int*
 // tokens: the entries' tokens back to back; want: for each entry want_counts[r] indices into its
 // tokens.  meta: [total ints, T, wanted rows, max context, max q_len].  feed_limit > 0 admits token
 // ids -1 .. -feed_limit: "the i-th token the step before has sampled", resolved on the device.
+// pad > 0 appends that many filler entries after the R real ones (so that batches of nearby sizes share one recorded
+// shape): one token 0 at position 0 each, its logits wanted, state slot pad_slot, one page pad_pages[g] per group
+// (a page and a slot outside the manager's pools, which the caller sets aside; what the fillers compute is dropped).
 API int q6k_cm_fill_step(void* h, int R, const int64_t* ids, const int* q_lens, const int32_t* tokens, const int* want,
-                         const int* want_counts, const int* widths, int vocab, int feed_limit, int32_t* out, int64_t capacity,
-                         int64_t* meta) {
+                         const int* want_counts, const int* widths, int vocab, int feed_limit, int pad, const int* pad_pages,
+                         int pad_slot, int32_t* out, int64_t capacity, int64_t* meta) {
     CacheManager* cm = (CacheManager*)h;
-    int64_t T = 0, W = 0;
+    if (pad < 0 || (pad > 0 && !pad_pages)) return fail(E_VALUE, "bad number of filler entries %d", pad);
+    int64_t T = pad, W = pad;
     for (int r = 0; r < R; ++r) T += q_lens[r], W += want_counts[r];
+    const int real = R;
+    R += pad;
     int64_t total = 3 * T + (R + 1) + 2 * R + W;
     for (size_t g = 0; g < cm->groups.size(); ++g) total += (int64_t)R * widths[g];
     if (total > capacity) return fail(E_VALUE, "the step needs %lld ints, the block holds %lld", (long long)total, (long long)capacity);
     int32_t *tok = out, *pos = tok + T, *rot = pos + T, *qs = rot + T, *ps = qs + R + 1, *sl = ps + R, *lr = sl + R, *tab = lr + W;
     int64_t t = 0, w = 0, max_ctx = 0, max_q = 0, wi = 0;
     qs[0] = 0;
-    for (int r = 0; r < R; ++r) {
+    for (int r = 0; r < real; ++r) {
         CacheRequest* cr = cm->find(ids[r]);
         if (!cr) return fail(E_KEY, "request %lld is not live", (long long)ids[r]);
         const int n = q_lens[r];
@@ -508,13 +514,25 @@ API int q6k_cm_fill_step(void* h, int R, const int64_t* ids, const int* q_lens, 
         qs[r + 1] = (int32_t)t, ps[r] = (int32_t)cr->length, sl[r] = cr->slot;
         max_ctx = std::max<int64_t>(max_ctx, cr->length + n), max_q = std::max<int64_t>(max_q, n);
     }
+    for (int r = real; r < R; ++r) {
+        tok[t] = 0, pos[t] = 0, rot[t] = r, lr[w++] = (int32_t)t;
+        ++t;
+        qs[r + 1] = (int32_t)t, ps[r] = 0, sl[r] = pad_slot;
+        max_ctx = std::max<int64_t>(max_ctx, 1), max_q = std::max<int64_t>(max_q, 1);
+    }
     for (size_t g = 0; g < cm->groups.size(); ++g) {
         const int wd = widths[g];
-        for (int r = 0; r < R; ++r) {
+        if (wd < 1) return fail(E_VALUE, "the table of group %d is %d wide", (int)g, wd);
+        for (int r = 0; r < real; ++r) {
             const std::vector<int32_t>& pages = cm->find(ids[r])->tables[g].pages;
             if ((int)pages.size() > wd) return fail(E_VALUE, "request %lld holds %d blocks in group %d, the table is %d wide", (long long)ids[r], (int)pages.size(), (int)g, wd);
             std::copy(pages.begin(), pages.end(), tab);
             std::fill(tab + pages.size(), tab + wd, -1);
+            tab += wd;
+        }
+        for (int r = real; r < R; ++r) {
+            tab[0] = pad_pages[g];
+            std::fill(tab + 1, tab + wd, -1);
             tab += wd;
         }
     }

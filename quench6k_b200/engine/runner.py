@@ -69,11 +69,13 @@ class ModelRunner:
                 self.caches.append(None)
             else:
                 g = self.group_of[p]
-                shape = (r.kv_heads, pages[g], page_size, r.head_dim)      # head-major: a head's pages are contiguous
+                # head-major: a head's pages are contiguous; one page beyond the manager's pool takes what filler entries write
+                shape = (r.kv_heads, pages[g] + 1, page_size, r.head_dim)
                 self.caches.append(LayerCache(g, torch.zeros(shape, dtype=rt.dtype, device=rt.device),
                                               torch.zeros(shape, dtype=rt.dtype, device=rt.device), page_size))
-        self.states = [None if s is None else torch.zeros((max_requests, *s), dtype=torch.float32, device=rt.device)
+        self.states = [None if s is None else torch.zeros((max_requests + 1, *s), dtype=torch.float32, device=rt.device)
                        for s in model.state_shapes()]
+        self._pad_pages, self._pad_slot = list(pages), max_requests      # the page and the slot no request ever holds
         # steps whose shape repeats (above all decode steps) replay a CUDA graph per shape; the
         # reference captures one per sequence and token count (crates/engine/src/flint.rs:735-771)
         self.cuda_graphs = cuda_graphs and model.graph_safe()
@@ -140,14 +142,15 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ the step
     def _context(self, entries: Sequence[StepEntry], widths: Optional[List[int]] = None,
-                 static: Optional[torch.Tensor] = None) -> StepContext:
+                 static: Optional[torch.Tensor] = None, pad: int = 0) -> StepContext:
         """The step's description: built on the host in one pinned block, uploaded in one copy
-        (into `static` when given: a device block a CUDA graph reads)."""
-        R = len(entries)
-        q_lens = [len(e.tokens) for e in entries]
+        (into `static` when given: a device block a CUDA graph reads).  pad: filler entries after
+        the real ones (one token each at position 0 of a page no request holds, logits wanted)."""
+        R = len(entries) + pad
+        q_lens = [len(e.tokens) for e in entries] + [1] * pad
         if widths is None:
             widths = self._widths(entries)
-        n_want = sum(len(e.want) for e in entries)
+        n_want = sum(len(e.want) for e in entries) + pad
         total = 3 * sum(q_lens) + (R + 1) + 2 * R + n_want + sum(R * w for w in widths)
         if self._pinned_free is not None:
             self._pinned_free.synchronize()
@@ -155,7 +158,7 @@ class ModelRunner:
             self._pinned = torch.empty(max(total, 4096), dtype=torch.int32, pin_memory=True)
         written, T, n_want, max_context, max_q_len = self.manager.pack_step(
             [e.rid for e in entries], [e.tokens for e in entries], [e.want for e in entries], widths, self.vocab_size,
-            self._pinned.numpy(), self._feed_limit)
+            self._pinned.numpy(), self._feed_limit, pad, self._pad_pages, self._pad_slot)
         assert written == total
         o = 3 * T
         host = self._pinned.numpy()
@@ -199,10 +202,15 @@ class ModelRunner:
             return self.model.forward(self._context(entries), self.caches, self.states)
         widths = [(w + 63) // 64 * 64 for w in self._widths(entries)]
         shape = tuple((len(e.tokens), tuple(e.want)) for e in entries)
+        decode = all(len(e.tokens) == 1 for e in entries)
+        # decode batches of nearby sizes share one recording: filler entries bring the batch to the next size of a short
+        # list, so that a request that ends or arrives seldom means a new recording (their rows are dropped below)
+        pad = self.decode_bucket(len(entries)) - len(entries) if decode and all(tuple(e.want) == (0,) for e in entries) else 0
+        real_rows = sum(len(e.want) for e in entries)
+        shape += ((1, (0,)),) * pad
         key = (shape, tuple(widths))
         slot = self._graphs.get(key)
         if slot is None:
-            decode = all(len(e.tokens) == 1 for e in entries)
             seen = self._shapes_seen.get(key, 0) + 1
             self._shapes_seen[key] = seen
             if not decode and seen < 2:
@@ -211,14 +219,14 @@ class ModelRunner:
                 return self.model.forward(self._context(entries), self.caches, self.states)
             # run the step eagerly from a static block, then record the same launches into a graph
             # (recording executes nothing)
-            R, T = len(entries), sum(len(e.tokens) for e in entries)
-            n_want = sum(len(e.want) for e in entries)
+            R, T = len(entries) + pad, sum(len(e.tokens) for e in entries) + pad
+            n_want = real_rows + pad
             total = 3 * T + (R + 1) + 2 * R + n_want + sum(R * w for w in widths)
             static = torch.empty(total, dtype=torch.int32, device=self.rt.device)
-            ctx = self._context(entries, widths, static)
+            ctx = self._context(entries, widths, static, pad)
             ctx.max_context = max(widths) * self.page_size          # launch plans must hold for every replay
             logits = self.model.forward(ctx, self.caches, self.states)
-            result = logits.clone() if logits is not None else None
+            result = logits[:real_rows].clone() if logits is not None else None
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count
@@ -232,11 +240,20 @@ class ModelRunner:
             return result
         self._graphs.move_to_end(key)
         graph, ctx, static, out, launches = slot
-        self._context(entries, widths, static)
+        self._context(entries, widths, static, pad)
         graph.replay()
         self.graph_replays += 1
         ops.launch_count += launches
-        return out
+        return out[:real_rows] if out is not None else None
+
+    @staticmethod
+    def decode_bucket(n: int) -> int:
+        """The batch size a decode step of n requests is recorded at: n up to 8, then the next
+        multiple of 4 up to 32, of 8 up to 64, of 16 beyond (at most a seventh more rows)."""
+        if n <= 8:
+            return n
+        unit = 4 if n <= 32 else 8 if n <= 64 else 16
+        return (n + unit - 1) // unit * unit
 
     def can_run(self, entries: Sequence[StepEntry]) -> bool:
         return self.manager.can_reserve([(e.rid, len(e.tokens)) for e in entries])

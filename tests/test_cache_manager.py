@@ -169,9 +169,10 @@ def test_both_managers_agree_on_tables_and_packed_steps(seed):
                 want = [[k - 1]] + [[0] for _ in others]
                 widths = [max(1, max(pair[1].table_len(r, g) for r in rids)) + g for g in range(2)]
                 blocks = []
+                pad = rng.choice([0, 0, 1, 3])
                 for m in pair:
                     out = np.full(4096, -7, dtype=np.int32)
-                    meta = m.pack_step(rids, toks, want, widths, 50, out)
+                    meta = m.pack_step(rids, toks, want, widths, 50, out, 0, pad, [31, 32], 9)
                     blocks.append((meta, out[:meta[0]].tolist()))
                 assert blocks[0] == blocks[1]
                 for m in pair:
@@ -198,3 +199,23 @@ def test_pack_step_refuses_bad_tokens_and_places():
     total, T, W, ctx, q = m.pack_step(["a"], [[1, 2, 3]], [[0, 2]], [2], 50, out)
     assert (T, W, ctx, q) == (3, 2, 3, 3)
     assert out[:total].tolist() == [1, 2, 3, 0, 1, 2, 0, 0, 0, 0, 3, 0, m.slot("a"), 0, 2, 0, -1]
+
+
+@pytest.mark.parametrize("backend", ["python", "native"])
+def test_pack_step_appends_filler_entries(backend):
+    """Filler entries after the real ones: one token 0 at position 0 each, its logits wanted, the
+    given slot, and one page per group that the manager never hands out."""
+    from quench6k_b200.cache import NativeCacheManager, PyCacheManager
+    cls = PyCacheManager if backend == "python" else NativeCacheManager
+    m = cls([GroupSpec("full"), GroupSpec("sliding", 8)], page_size=4, num_pages=[8, 6], max_requests=2)
+    m.add("a")
+    m.reserve("a", 3)
+    out = np.full(256, -7, dtype=np.int32)
+    total, T, W, ctx, q = m.pack_step(["a"], [[4, 5, 6]], [[2]], [2, 3], 50, out, 0, 2, [8, 6], 2)
+    assert (T, W, ctx, q) == (5, 3, 3, 3)
+    a0, a1 = m.table("a", 0)[0], m.table("a", 1)[0]
+    assert out[:total].tolist() == ([4, 5, 6, 0, 0] + [0, 1, 2, 0, 0] + [0, 0, 0, 1, 2] + [0, 3, 4, 5] + [0, 0, 0] + [m.slot("a"), 2, 2]
+                                    + [2, 3, 4] + [a0, -1, 8, -1, 8, -1] + [a1, -1, -1, 6, -1, -1, 6, -1, -1])
+    with pytest.raises(ValueError):
+        m.pack_step(["a"], [[4, 5, 6]], [[2]], [2, 3], 50, out, 0, 1, [8], 2)
+

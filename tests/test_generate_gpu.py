@@ -96,29 +96,36 @@ def test_command_line(tmp_path):
 
 
 @pytest.mark.parametrize("name,dtype,lengths", [("B", "float32", (9, 21, 14)), ("B", "bfloat16", (9, 21, 14)),
-                                                ("D", "bfloat16", (300, 700, 140))])
+                                                ("D", "bfloat16", (300, 700, 140)),
+                                                ("B", "float32", (9, 21, 14, 5, 8, 11, 6, 17, 10, 12, 7)),
+                                                ("D", "bfloat16", (30, 70, 140, 9, 200, 33, 64, 65, 17, 90))])
 def test_graph_replay_equals_eager_steps(tmp_path, name, dtype, lengths):
     """Decode-only steps replay a CUDA graph; the logits must equal those of the same steps run
     eagerly (the reference checks graph decoding against eager decoding the same way,
     crates/cli/src/flint.rs:116-131).  D: the head size at which the key splits of decode
-    attention are planned on the device; a replay must plan them from its own positions."""
+    attention are planned on the device; a replay must plan them from its own positions.  Batches
+    of 9 to 12 requests share one recording: filler entries bring them to 12 rows, which must not
+    change the rows of the real requests (bit for bit in float32)."""
     from quench6k_b200.engine import ModelRunner, StepEntry
     cfg, _ = helpers.make_model_folder(str(tmp_path), name, seed=31)
     prompts = {f"r{i}": helpers.random_tokens(n, cfg["vocab_size"], 600 + n) for i, n in enumerate(lengths)}
     tails = {rid: helpers.random_tokens(12, cfg["vocab_size"], 700 + i) for i, rid in enumerate(prompts)}
     outs = {}
     for graphs in (False, True):
-        runner = ModelRunner.from_folder(str(tmp_path), dtype=dtype, num_pages=32 if name == "B" else 96, cuda_graphs=graphs)
+        runner = ModelRunner.from_folder(str(tmp_path), dtype=dtype, num_pages=(32 if name == "B" else 96) * (1 + len(lengths) // 4),
+                                         max_requests=len(lengths), cuda_graphs=graphs)
         assert runner.cuda_graphs == graphs
         for rid, p in prompts.items():
             runner.add_request(rid)
         runner.step([StepEntry(rid, p, []) for rid, p in prompts.items()])
         got = []
         for i in range(12):
-            live = list(prompts)[: 3 if i < 8 else 2]                       # the batch shrinks: another graph
+            live = list(prompts)[: len(prompts) - (0 if i < 4 else 1 if i < 8 else 2)]      # the batch shrinks
             got.append(runner.step([StepEntry(rid, [tails[rid][i]], [0]) for rid in live]).clone().cpu())
         outs[graphs] = got
         assert (runner.graph_replays > 0) == graphs
+        if graphs:                # 3 then 2 requests: two recordings; 11, 10, 9 requests: one of 12 rows; 10, 9, 8: one of 12 rows and one of 8
+            assert runner.graph_captures == {3: 2, 11: 1, 10: 2}[len(lengths)]
     for a, b in zip(outs[False], outs[True]):
         if dtype == "float32":
             assert torch.equal(a, b)

@@ -124,8 +124,8 @@ def test_graph_replay_equals_eager_steps(tmp_path, name, dtype, lengths):
             got.append(runner.step([StepEntry(rid, [tails[rid][i]], [0]) for rid in live]).clone().cpu())
         outs[graphs] = got
         assert (runner.graph_replays > 0) == graphs
-        if graphs:                # 3 then 2 requests: two recordings; 11, 10, 9 requests: one of 12 rows; 10, 9, 8: one of 12 rows and one of 8
-            assert runner.graph_captures == {3: 2, 11: 1, 10: 2}[len(lengths)]
+        if graphs:                # 3, 2, 1 requests: three recordings; 11, 10, 9 requests: one of 12 rows; 10, 9, 8: one of 12 rows and one of 8
+            assert runner.graph_captures == {3: 3, 11: 1, 10: 2}[len(lengths)]
     for a, b in zip(outs[False], outs[True]):
         if dtype == "float32":
             assert torch.equal(a, b)

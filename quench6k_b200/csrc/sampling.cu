@@ -201,6 +201,67 @@ __global__ void __launch_bounds__(1024) topk_pool_kernel(const float* logits, in
 // candidates are written into CTA 0's arrays, ties at the K-th key in ascending id order (the CTAs'
 // slices are consecutive id ranges); CTA 0 sorts and stores.  One pass over global memory
 // instead of six by one CTA.
+// The bin in which the need-th largest key lies, by one warp: lane l owns the 8 bins 255 - 8 l ... 248 - 8 l
+// (counted from the top); returns the bin and leaves in `need` how many keys are wanted from it.
+__device__ __forceinline__ int select_bin_warp(const int* hist, int& need) {
+    const int lane = threadIdx.x & 31, top = 255 - 8 * lane;
+    int c[8], mine = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) c[j] = hist[top - j], mine += c[j];
+    int incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += v;
+    }
+    const int before = incl - mine;                       // keys in the bins above this lane's
+    const bool here = before < need && incl >= need;
+    const unsigned who = __ballot_sync(0xffffffffu, here);
+    int bin = 0, left = 0;
+    if (who == 0u) {                                      // fewer keys than wanted (cannot happen for K <= V): the lowest bin
+        bin = 0, left = need;
+    } else if (here) {
+        left = need - before;
+        int j = 0;
+        for (; j < 7; ++j) {
+            if (c[j] >= left) break;
+            left -= c[j];
+        }
+        bin = top - j;
+    }
+    const int src = who == 0u ? 0 : __ffs(who) - 1;
+    bin = __shfl_sync(0xffffffffu, bin, src), left = __shfl_sync(0xffffffffu, left, src);
+    need = left;
+    return bin;
+}
+
+// Exclusive prefix sum of one value per thread over a block of 1024 threads; `total` gets the sum.
+__device__ __forceinline__ int block_exclusive_scan_1024(int v, int* warp_sums, int& total) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int incl = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int u = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += u;
+    }
+    if (lane == 31) warp_sums[warp] = incl;
+    __syncthreads();
+    if (warp == 0) {
+        const int w = warp_sums[lane];
+        int wi = w;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int u = __shfl_up_sync(0xffffffffu, wi, o);
+            if (lane >= o) wi += u;
+        }
+        warp_sums[lane] = wi - w;
+        if (lane == 31) warp_sums[32] = wi;
+    }
+    __syncthreads();
+    total = warp_sums[32];
+    return warp_sums[warp] + incl - v;
+}
+
 constexpr int TOPK_CLUSTER = 8;
 constexpr int TOPK_CLUSTER_MIN_V = 8192;                 // shorter rows: one CTA does as well
 constexpr int TOPK_CLUSTER_MAX_SLICE = 48 * 1024;        // keys of a slice (192 KB of shared memory)
@@ -238,21 +299,24 @@ __global__ void __cluster_dims__(TOPK_CLUSTER, 1, 1) __launch_bounds__(1024, 1)
         if (tid < 256) hist[tid] = 0;
         cluster.sync();                                  // histograms are empty, the prefix of the pass before is out
         const unsigned prefix = *l_prefix;
-        for (int i = tid; i < cnt; i += n) {
-            const unsigned k = keys[i];
-            if ((k & himask) == prefix) atomicAdd(&hist[(k >> shift) & 255], 1);
+        // logits share their leading bits: the lanes of a warp that hit the same bin add once, together
+        for (int i0w = 0; i0w < cnt; i0w += n) {
+            const int i = i0w + tid;
+            int bin = -1;
+            if (i < cnt) {
+                const unsigned k = keys[i];
+                if ((k & himask) == prefix) bin = (int)((k >> shift) & 255);
+            }
+            const unsigned same = __match_any_sync(0xffffffffu, bin);
+            if (bin >= 0 && (tid & 31) == __ffs(same) - 1) atomicAdd(&hist[bin], __popc(same));
         }
         __syncthreads();
         if (rank != 0 && tid < 256 && hist[tid] != 0) atomicAdd(&l_hist[tid], hist[tid]);
         cluster.sync();                                  // CTA 0's histogram holds the whole row
-        if (rank == 0 && tid == 0) {
-            int need = s_need, b = 255;
-            for (; b > 0; --b) {
-                if (hist[b] >= need) break;
-                need -= hist[b];
-            }
-            s_need = need;
-            s_prefix = prefix | ((unsigned)b << shift);
+        if (rank == 0 && tid < 32) {
+            int need = s_need;
+            const int b = select_bin_warp(hist, need);
+            if (tid == 0) s_need = need, s_prefix = prefix | ((unsigned)b << shift);
         }
         __syncthreads();                                 // the bin is chosen before the histogram is cleared again
     }
@@ -272,20 +336,12 @@ __global__ void __cluster_dims__(TOPK_CLUSTER, 1, 1) __launch_bounds__(1024, 1)
     const int b0 = min(cnt, tid * seg), b1 = min(cnt, b0 + seg);
     int mine = 0;
     for (int i = b0; i < b1; ++i) mine += keys[i] == kth;
-    seg_eq[tid] = mine;
-    __syncthreads();
-    if (tid == 0) {
-        int run = 0;
-        for (int i = 0; i < n; ++i) {
-            const int c = seg_eq[i];
-            seg_eq[i] = run;
-            run += c;
-        }
-        l_cta_eq[rank] = run;
-    }
+    int eq_total;
+    const int eq_before = block_exclusive_scan_1024(mine, seg_eq, eq_total);
+    if (tid == 0) l_cta_eq[rank] = eq_total;
     cluster.sync();                                      // every greater key is in, every CTA's count of equal keys is known
     const int gt = *l_count;
-    int r = seg_eq[tid];
+    int r = eq_before;
     for (int c = 0; c < rank; ++c) r += l_cta_eq[c];
     for (int i = b0; i < b1 && r < need_eq; ++i)
         if (keys[i] == kth) {

@@ -701,6 +701,15 @@ static int splits_for(int rows, int N, int K, int bt) {
 static void dense_plan(int rows, int N, int K, bool dual, int* bt, int* splits) {
     int b = q6k_tc_token_tile(rows, dual);
     const int n_tiles = (N + WM - 1) / WM;
+    if (!dual && rows >= 512 && n_tiles * ((rows + 127) / 128) * 2 < sm_count()) {
+        // many rows on few weight tiles (the router of a prompt portion): tiles of 128 tokens with K sliced over the
+        // idle SMs keep the MMAs wide; narrow tiles with the whole K in a row per CTA took 18 us for 2 GFLOP
+        const int s = splits_for(rows, N, K, 128);
+        if (s > 1) {
+            *bt = 128, *splits = s;
+            return;
+        }
+    }
     while (b > 32 && rows > b && n_tiles * ((rows + b - 1) / b) * 2 < sm_count()) b /= 2;
     if (b == 256 && !dual && rows > 256) {
         // the persistent CTAs work in rounds of one tile each: a tile of 192 tokens can need the same

@@ -112,7 +112,9 @@ __device__ __forceinline__ void warp_route_regs(const float* z, int E, int k, in
     warp_topk_regs<NL>(val, E, k, sigmoid, renorm, total, sel_e, sel_w);
 }
 
-__global__ void route_kernel(const float* logits, int T_, int E, int k, int sigmoid, int renorm, int* sel_e, float* sel_w) {
+// logits: [slices, T, E]; the slices (split-K partial products of the router) are summed in order first.
+__global__ void route_kernel(const float* logits, int slices, size_t slice_stride, int T_, int E, int k, int sigmoid, int renorm, int* sel_e,
+                             float* sel_w) {
     pdl_enter();
     extern __shared__ float sc[];             // [warps][E]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -120,19 +122,22 @@ __global__ void route_kernel(const float* logits, int T_, int E, int k, int sigm
     if (t >= T_) return;
     float* v = sc + (size_t)warp * E;
     const float* z = logits + (size_t)t * E;
+    for (int e = lane; e < E; e += 32) v[e] = z[e];
+    for (int s = 1; s < slices; ++s)                     // slice by slice: a lane's loads of one slice do not wait for one another
+        for (int e = lane; e < E; e += 32) v[e] += z[s * slice_stride + e];
     float total = 1.0f;
     if (sigmoid) {
         for (int e = lane; e < E; e += 32) {
-            float s = 1.0f / (1.0f + expf(-z[e]));
+            float s = 1.0f / (1.0f + expf(-v[e]));
             v[e] = s >= 0.0f ? s : 0.0f;
         }
     } else {
         float mx = -INFINITY;
-        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+        for (int e = lane; e < E; e += 32) mx = fmaxf(mx, v[e]);
         mx = warp_max(mx);
         float sum = 0.0f;
         for (int e = lane; e < E; e += 32) {
-            float s = expf(z[e] - mx);
+            float s = expf(v[e] - mx);
             s = s >= 0.0f ? s : 0.0f;
             v[e] = s;
             sum += s;
@@ -356,14 +361,16 @@ __device__ void tiles_in_block(const int* offsets, int G, int bm, int* tile_grou
 
 }  // namespace
 
-Q6K_API int q6k_route(const float* logits, int T_, int E, int k, int sigmoid, int renorm, int* sel_e, float* sel_w,
+// logits: FP32 [slices, T, E] (slices >= 1: split-K partial products, summed in order).
+Q6K_API int q6k_route(const float* logits, int slices, int T_, int E, int k, int sigmoid, int renorm, int* sel_e, float* sel_w,
                       cudaStream_t st) {
     if (T_ == 0) return 0;
-    Q6K_REQUIRE(T_ > 0 && E > 0 && k > 0 && k <= E, "route: bad sizes T=%d E=%d k=%d", T_, E, k);
+    Q6K_REQUIRE(T_ > 0 && E > 0 && k > 0 && k <= E && slices >= 1, "route: bad sizes T=%d E=%d k=%d slices=%d", T_, E, k, slices);
     Q6K_REQUIRE(E <= 8192, "route: %d experts exceed the supported 8192", E);
     const int warps = E <= 2048 ? 4 : 1;
     const size_t smem = (size_t)warps * E * sizeof(float);
-    q6k_launch(route_kernel, (T_ + warps - 1) / warps, warps * 32, smem, st, logits, T_, E, k, sigmoid, renorm, sel_e, sel_w);
+    q6k_launch(route_kernel, (T_ + warps - 1) / warps, warps * 32, smem, st, logits, slices, (size_t)T_ * E, T_, E, k, sigmoid, renorm, sel_e,
+               sel_w);
     return q6k_check_launch("route");
 }
 

@@ -530,14 +530,16 @@ def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
 
 # --------------------------------------------------------------------------- routing
 def route(logits: torch.Tensor, k: int, scoring: str, renorm: bool):
-    """(sel_e int32 [T, k], sel_w float32 [T, k])."""
+    """(sel_e int32 [T, k], sel_w float32 [T, k]).  logits: [T, E], or [slices, T, E] split-K
+    partial products of the router, which are summed in order first."""
     _need(logits, "logits", torch.float32)
-    T, E = logits.shape
+    slices = logits.shape[0] if logits.dim() == 3 else 1
+    T, E = logits.shape[-2:]
     if scoring not in ("softmax", "sigmoid"):
         raise KernelError(f"route: unknown scoring {scoring!r}")
     sel_e = torch.empty((T, k), dtype=torch.int32, device=logits.device)
     sel_w = torch.empty((T, k), dtype=torch.float32, device=logits.device)
-    _call("q6k_route", _ptr(logits), _i(T), _i(E), _i(k), _i(1 if scoring == "sigmoid" else 0), _i(1 if renorm else 0),
+    _call("q6k_route", _ptr(logits), _i(slices), _i(T), _i(E), _i(k), _i(1 if scoring == "sigmoid" else 0), _i(1 if renorm else 0),
           _ptr(sel_e), _ptr(sel_w), _stream())
     return sel_e, sel_w
 

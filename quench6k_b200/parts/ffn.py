@@ -91,7 +91,7 @@ class RoutedExperts(FeedForward):
             if self.shared is not None:
                 self.shared.forward(xn, ctx, out)
             return None
-        logits = linear.matmul(xn, self.w_router, rt)                       # FP32 [T, E]
+        logits = linear.matmul(xn, self.w_router, rt, partials_ok=True)    # FP32 [T, E], or split-K slices of it that route() sums
         sel_e, sel_w = ops.route(logits, self.k, self.scoring, self.renorm)
         plan = linear.group_plan(xn, self.w_gate, sel_e, rt)             # permutation by expert, row tiles, gathered rows
         act = linear.grouped_swiglu(xn, plan, self.w_gate, self.w_up, rt)                         # [pairs, I]

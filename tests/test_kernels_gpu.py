@@ -143,6 +143,10 @@ def test_route(scoring, renorm, T, E, k):
     rsel, rw = P.route(z.cpu().float(), scoring, k, renorm)
     assert torch.equal(sel.cpu().long(), rsel)
     assert (w.cpu() - rw).abs().max() <= 1e-5 * rw.abs().max()
+    # the same logits as three split-K slices (quarters of the values, which add up exactly)
+    parts = torch.stack([z / 2, z / 4, z / 4]).contiguous()
+    sel3, w3 = ops.route(parts, k, scoring, renorm)
+    assert torch.equal(sel3, sel) and torch.equal(w3, w)
 
 
 def _paged(k, v, page_size, num_pages, dtype, seed):

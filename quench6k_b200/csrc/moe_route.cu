@@ -251,6 +251,72 @@ __global__ void count_kernel(const int* sel_e, int pairs, int E, int* counts) {
     if (lane == 0) counts[c * E + e] = n;
 }
 
+// The same counts by one block per chunk, a thread per pair, with each pair's rank among the earlier pairs of its
+// chunk that chose the same expert (local[p]; the order is the order of the pairs, so the permutation stays the
+// deterministic one): lanes with the same expert find one another with match.any, the warps' counts per expert
+// stand in shared memory ([32][E] bytes, a warp has at most 32 pairs), a pair adds those of the warps before its own.
+constexpr int COUNT_RANK_MAX_E = 1024;
+__global__ void __launch_bounds__(PERM_CHUNK) count_rank_kernel(const int* __restrict__ sel_e, int pairs, int E, int* __restrict__ counts,
+                                                                int* __restrict__ local) {
+    pdl_enter();
+    extern __shared__ unsigned char warp_cnt[];          // [32][E]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, c = blockIdx.x;
+    for (int i = tid; i < 8 * E; i += PERM_CHUNK) reinterpret_cast<unsigned*>(warp_cnt)[i] = 0u;      // 32 E bytes
+    __syncthreads();
+    const int p = c * PERM_CHUNK + tid;
+    const int e = p < pairs ? sel_e[p] : -1;
+    const unsigned same = __match_any_sync(0xffffffffu, e);
+    const int in_warp = __popc(same & ((1u << lane) - 1u));
+    if (e >= 0 && in_warp == 0) warp_cnt[warp * E + e] = (unsigned char)__popc(same);
+    __syncthreads();
+    if (e >= 0) {
+        int before = in_warp;
+        for (int w = 0; w < warp; ++w) before += warp_cnt[w * E + e];
+        local[p] = before;
+    }
+    for (int x = tid; x < E; x += PERM_CHUNK) {
+        int n = 0;
+#pragma unroll 8
+        for (int w = 0; w < 32; ++w) n += warp_cnt[w * E + x];
+        counts[c * E + x] = n;
+    }
+}
+
+// out[r, :] = x[idx[r], :] (rows of vec_per_row 16-byte words), for the path with more experts than count_rank_kernel takes.
+__global__ void gather_pairs_kernel(const uint4* __restrict__ x, const int* __restrict__ idx, uint4* __restrict__ out, int vec_per_row) {
+    pdl_enter();
+    const size_t src = (size_t)idx[blockIdx.x] * vec_per_row, dst = (size_t)blockIdx.x * vec_per_row;
+    for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) out[dst + i] = x[src + i];
+}
+
+// After the offsets: a pair's row is its expert's offset plus its chunk's first row within the expert plus its
+// rank within the chunk (which stands in pair_row); row_token[row] = pair / k.
+__global__ void finish_rank_kernel(const int* __restrict__ sel_e, const int* __restrict__ chunk_base, const int* __restrict__ offsets,
+                                   int pairs, int k, int E, int* __restrict__ pair_row, int* __restrict__ row_token) {
+    pdl_enter();
+    const int p = blockIdx.x * blockDim.x + threadIdx.x;
+    if (p >= pairs) return;
+    const int e = sel_e[p];
+    const int row = offsets[e] + chunk_base[(p / PERM_CHUNK) * E + e] + pair_row[p];
+    pair_row[p] = row;
+    row_token[row] = p / k;
+}
+
+// The same with the copy of the pair's input row: out[row, :] = x[pair / k, :] (rows of vec_per_row 16-byte words), a
+// block per pair.
+__global__ void finish_rank_gather_kernel(const int* __restrict__ sel_e, const int* __restrict__ chunk_base, const int* __restrict__ offsets,
+                                          int k, int E, int* __restrict__ pair_row, int* __restrict__ row_token, const uint4* __restrict__ x,
+                                          uint4* __restrict__ out, int vec_per_row) {
+    pdl_enter();
+    const int p = blockIdx.x;
+    const int e = sel_e[p];
+    const int row = offsets[e] + chunk_base[(p / PERM_CHUNK) * E + e] + pair_row[p];
+    __syncthreads();                                     // every thread has read the rank before thread 0 replaces it
+    if (threadIdx.x == 0) pair_row[p] = row, row_token[row] = p / k;
+    const size_t src = (size_t)(p / k) * vec_per_row, dst = (size_t)row * vec_per_row;
+    for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) out[dst + i] = x[src + i];
+}
+
 // counts[c, e] -> the chunk's first row within its expert (in place), and offsets = exclusive
 // scan over the experts of their totals (E + 1 entries).  One block.
 __device__ void tiles_in_block(const int* offsets, int G, int bm, int* tile_group, int* tile_row0, int* num_tiles, int max_tiles);
@@ -266,10 +332,16 @@ __global__ void offsets_kernel(int* counts, int chunks, int E, int* offsets, int
         const int e = tid * per + i;
         if (e >= E) break;
         int run = 0;
-        for (int c = 0; c < chunks; ++c) {
-            const int v = counts[c * E + e];
-            counts[c * E + e] = run;
-            run += v;
+        for (int c0 = 0; c0 < chunks; c0 += 8) {         // eight loads on the way at a time
+            int v[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = c0 + j < chunks ? counts[(c0 + j) * E + e] : 0;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (c0 + j < chunks) {
+                    counts[(c0 + j) * E + e] = run;
+                    run += v[j];
+                }
         }
         offsets[e] = run;                      // the expert's total, replaced by its offset below
         sum += run;
@@ -406,15 +478,33 @@ Q6K_API int q6k_moe_permute(const int* sel_e, int pairs, int k, int E, int* scra
 
 // The permutation and the list of row tiles of bm rows (tile_group, tile_row0: max_tiles entries; num_tiles: 1) in
 // three launches (the block that makes the offsets also makes the tile list).
+// x != null: the pairs' input rows (row_bytes bytes each, a multiple of 16; x: [pairs / k rows]) are copied into
+// gathered[row] by the launch that finishes the ranks.
 Q6K_API int q6k_moe_plan(const int* sel_e, int pairs, int k, int E, int* scratch, int* offsets, int* pair_row, int* row_token, int bm,
-                         int* tile_group, int* tile_row0, int* num_tiles, int max_tiles, cudaStream_t st) {
+                         int* tile_group, int* tile_row0, int* num_tiles, int max_tiles, const void* x, void* gathered, int row_bytes,
+                         cudaStream_t st) {
     if (pairs == 0) return 0;
     Q6K_REQUIRE(pairs > 0 && k > 0 && E > 0 && bm > 0 && max_tiles > 0, "moe_plan: bad sizes pairs=%d k=%d E=%d bm=%d", pairs, k, E, bm);
     const int chunks = (pairs + PERM_CHUNK - 1) / PERM_CHUNK;
     Q6K_REQUIRE(chunks <= 65535, "moe_plan: %d pairs exceed the grid limit", pairs);
+    Q6K_REQUIRE(!x || (gathered && row_bytes > 0 && row_bytes % 16 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)gathered & 15) == 0),
+                "moe_plan: rows of %d bytes cannot be gathered (multiples of 16 bytes, 16-byte aligned buffers)", row_bytes);
+    if (E <= COUNT_RANK_MAX_E) {
+        q6k_launch(count_rank_kernel, chunks, PERM_CHUNK, (size_t)32 * E, st, sel_e, pairs, E, scratch, pair_row);
+        q6k_launch(offsets_kernel, 1, 256, 0, st, scratch, chunks, E, offsets, bm, tile_group, tile_row0, num_tiles, max_tiles);
+        if (x)
+            q6k_launch(finish_rank_gather_kernel, pairs, 128, 0, st, sel_e, scratch, offsets, k, E, pair_row, row_token, (const uint4*)x,
+                       (uint4*)gathered, row_bytes / 16);
+        else
+            q6k_launch(finish_rank_kernel, (pairs + 255) / 256, 256, 0, st, sel_e, scratch, offsets, pairs, k, E, pair_row, row_token);
+        return q6k_check_launch("moe_plan");
+    }
     const dim3 grid((E + 7) / 8, chunks);
     q6k_launch(count_kernel, grid, 256, 0, st, sel_e, pairs, E, scratch);
     q6k_launch(offsets_kernel, 1, 256, 0, st, scratch, chunks, E, offsets, bm, tile_group, tile_row0, num_tiles, max_tiles);
     q6k_launch(rank_kernel, grid, 256, 0, st, sel_e, scratch, offsets, pairs, k, E, pair_row, row_token);
+    if (x) {
+        q6k_launch(gather_pairs_kernel, pairs, 128, 0, st, (const uint4*)x, row_token, (uint4*)gathered, row_bytes / 16);
+    }
     return q6k_check_launch("moe_plan");
 }

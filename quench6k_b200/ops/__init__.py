@@ -626,9 +626,11 @@ def moe_permute(sel_e: torch.Tensor, E: int):
     return offsets, pair_row, row_token
 
 
-def moe_plan(sel_e: torch.Tensor, E: int, bm: int):
+def moe_plan(sel_e: torch.Tensor, E: int, bm: int, x: Optional[torch.Tensor] = None):
     """The permutation of `moe_permute` and the row tiles of `tile_list(offsets, pairs, bm)` in three
-    launches instead of four: (offsets, pair_row, row_token, (offsets, tile_group, tile_row0, num_tiles))."""
+    launches instead of four: (offsets, pair_row, row_token, (offsets, tile_group, tile_row0, num_tiles)).
+    With x [T, D] (rows of a multiple of 16 bytes) the last launch also copies each pair's input
+    row into its place, and the gathered rows [pairs, D] are returned as a fifth value."""
     _need(sel_e, "sel_e", torch.int32)
     T, k = sel_e.shape
     pairs = T * k
@@ -643,9 +645,19 @@ def moe_plan(sel_e: torch.Tensor, E: int, bm: int):
     tile_group = torch.empty(max_tiles, dtype=torch.int32, device=dev)
     tile_row0 = torch.empty(max_tiles, dtype=torch.int32, device=dev)
     num_tiles = torch.empty(1, dtype=torch.int32, device=dev)
+    gathered, row_bytes = None, 0
+    if x is not None:
+        _need(x, "x")
+        if x.dim() != 2 or x.shape[0] != T:
+            raise KernelError(f"moe_plan: x has shape {tuple(x.shape)}, expected [{T}, D]")
+        row_bytes = x.shape[1] * x.element_size()
+        if row_bytes % 16:
+            raise KernelError(f"moe_plan: rows of {row_bytes} bytes cannot be gathered 16 bytes at a time")
+        gathered = torch.empty((pairs, x.shape[1]), dtype=x.dtype, device=dev)
     _call("q6k_moe_plan", _ptr(sel_e), _i(pairs), _i(k), _i(E), _ptr(scratch), _ptr(offsets), _ptr(pair_row), _ptr(row_token), _i(bm),
-          _ptr(tile_group), _ptr(tile_row0), _ptr(num_tiles), _i(max_tiles), _stream())
-    return offsets, pair_row, row_token, (offsets, tile_group, tile_row0, num_tiles)
+          _ptr(tile_group), _ptr(tile_row0), _ptr(num_tiles), _i(max_tiles), _ptr(x), _ptr(gathered), _i(row_bytes), _stream())
+    plan = (offsets, pair_row, row_token, (offsets, tile_group, tile_row0, num_tiles))
+    return plan if x is None else plan + (gathered,)
 
 
 # --------------------------------------------------------------------------- sampling

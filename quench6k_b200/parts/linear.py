@@ -47,10 +47,13 @@ class GroupPlan:
             want = avg + avg // 2
             self.bt_dual = ops.tc_token_tile(want, True)
             self.bt = self.bt_dual
-            # permutation and tile list in three launches; the gather of the input rows stays a launch of its own (a
-            # block per row: folded into the ranking warps it was measured 6 ms slower per 2,048-token prefill)
-            self.offsets, self.pair_row, self.row_token, self.tiles = ops.moe_plan(sel_e, num_groups, self.bt)
-            self.xs = ops.gather_rows(a, self.row_token)
+            # permutation, tile list and the gathered input rows in three launches (the last one, a block per pair,
+            # finishes the pair's rank and copies its row)
+            if a.shape[1] * a.element_size() % 16 == 0:
+                self.offsets, self.pair_row, self.row_token, self.tiles, self.xs = ops.moe_plan(sel_e, num_groups, self.bt, a)
+            else:
+                self.offsets, self.pair_row, self.row_token, self.tiles = ops.moe_plan(sel_e, num_groups, self.bt)
+                self.xs = ops.gather_rows(a, self.row_token)
         else:
             self.offsets, self.pair_row, self.row_token, self.tiles = ops.moe_plan(sel_e, num_groups, ops.simt_tile_rows())
 

@@ -117,7 +117,8 @@ def test_grouped_gemm_and_permutation(dtype):
     assert (h.double().cpu() - want).abs().max() <= 1e-5 * want.abs().max()
 
 
-@pytest.mark.parametrize("T,k,E,D,bm", [(37, 3, 10, 56, 16), (2048, 8, 256, 64, 128), (300, 1, 7, 8, 32), (1500, 6, 33, 24, 64)])
+@pytest.mark.parametrize("T,k,E,D,bm", [(37, 3, 10, 56, 16), (2048, 8, 256, 64, 128), (300, 1, 7, 8, 32), (1500, 6, 33, 24, 64),
+                                        (700, 4, 1024, 16, 32), (515, 5, 1500, 40, 16)])
 def test_moe_plan_equals_its_parts(T, k, E, D, bm):
     """Permutation and tile list in three launches against the four single ones: the same arrays."""
     from quench6k_b200 import ops
@@ -129,6 +130,11 @@ def test_moe_plan_equals_its_parts(T, k, E, D, bm):
     assert torch.equal(o2, offsets) and torch.equal(p2, pair_row) and torch.equal(r2, row_token)
     n = int(tiles[3])
     assert int(t2[3]) == n and torch.equal(t2[1][:n], tiles[1][:n]) and torch.equal(t2[2][:n], tiles[2][:n])
+    # with the pairs' input rows copied into place by the last launch
+    x = _t(T, D, dtype=torch.bfloat16, seed=3)
+    o3, p3, r3, t3, xs = ops.moe_plan(sel, E, bm, x)
+    assert torch.equal(o3, offsets) and torch.equal(p3, pair_row) and torch.equal(r3, row_token) and int(t3[3]) == n
+    assert torch.equal(xs, x[row_token.long()])
 
 
 @pytest.mark.parametrize("scoring", ["softmax", "sigmoid"])

@@ -20,7 +20,6 @@ same.  Inputs are larger than L2: one decode step streams gigabytes of weights a
 """
 import argparse
 import json
-import math
 import os
 import subprocess
 import sys

@@ -10,7 +10,6 @@ this engine takes token ids (`--prompt-ids 1,2,3`, or `--prompt-len N` seeded ra
 from __future__ import annotations
 
 import argparse
-import json
 import sys
 import time
 

@@ -31,7 +31,7 @@ from ..sampling import Sampler, SamplingParams, SplitMix64
 from ..sampling.sampler import ROW_RECORD, device_rows, pool_size
 from .batch import StepEntry
 from .runner import ModelRunner
-from .scheduler import FINISH_CANCELLED, FINISH_STOP, Request, ScheduledStep, Scheduler
+from .scheduler import FINISH_CANCELLED, Request, ScheduledStep, Scheduler
 
 PENDING = -1          # an output token whose value is still on the device
 

@@ -8,11 +8,9 @@ crates/engine/src/flint.rs:699-771; batches of one-token segments, crates/engine
 """
 from __future__ import annotations
 
-import os
 from collections import OrderedDict
 from typing import Dict, Hashable, List, Optional, Sequence, Union
 
-import numpy as np
 import torch
 
 from .. import ops

@@ -7,7 +7,7 @@ names: `<embed_name>`, `<layer prefix>{input_layernorm,post_attention_layernorm}
 """
 from __future__ import annotations
 
-from typing import Callable, Dict, List, Optional
+from typing import Callable, List, Optional
 
 import torch
 

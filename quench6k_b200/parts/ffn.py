@@ -9,7 +9,6 @@ part, added after the routed sum.
 """
 from __future__ import annotations
 
-import torch
 
 from .. import ops
 from ..spec import TensorSpec

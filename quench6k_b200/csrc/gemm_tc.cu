@@ -421,7 +421,8 @@ __host__ __device__ constexpr uint32_t umma_idesc_pair(int n) {
 template <int BT2>
 __global__ void __launch_bounds__(192) gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_a,
                                                            const Params p) {
-    pdl_wait();
+    // The tiles follow from the launch alone: the pair sets itself up and sends for the weights of its first ring of
+    // k-blocks before it waits for the kernel that makes the activations (and whose reader may still use the output).
     const uint32_t rank = cluster_ctarank();
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
     const int n_x = (p.N + 2 * WM - 1) / (2 * WM), total = n_x * p.n_y;
@@ -464,20 +465,32 @@ __global__ void __launch_bounds__(192) gemm_tc_pair_kernel(const __grid_constant
 
     if (warp == 0) {
         if (lane == 0) {
+            int pre = 0;                                   // k-blocks whose weights went out before the wait
+            for (int t = pair; t < total && pre < stages; t += n_pairs) {
+                const int n0 = (t % n_x) * 2 * WM + (int)rank * WM;
+                for (int i = 0; i < kb_total && pre < stages; ++i, ++pre) {
+                    const uint32_t st = smem_u32(smem + (size_t)pre * STAGE_BYTES), fb = full0 + 8 * pre;
+                    if (rank == 0) mbar_expect_tx(fb, 2 * STAGE_BYTES);
+                    tma_load_2d_pair(st, &tm_w, i * BK, n0, fb);
+                }
+            }
+            pdl_wait();
             int it = 0;
             bool ok = true;
             for (int t = pair; t < total && ok; t += n_pairs) {
                 const int n0 = (t % n_x) * 2 * WM + (int)rank * WM, row0 = (t / n_x) * BT2 + (int)rank * (BT2 / 2);
                 for (int i = 0; i < kb_total; ++i, ++it) {
                     const int s = it % stages;
-                    if (!mbar_wait(empty0 + 8 * s, ((it / stages) & 1) ^ 1)) {
-                        atomicExch(&g_tc_status, 11);
-                        ok = false;
-                        break;
-                    }
                     const uint32_t st = smem_u32(smem + (size_t)s * STAGE_BYTES), fb = full0 + 8 * s;
-                    if (rank == 0) mbar_expect_tx(fb, 2 * STAGE_BYTES);
-                    tma_load_2d_pair(st, &tm_w, i * BK, n0, fb);
+                    if (it >= pre) {                       // the first ring's stages are fresh and their weights on the way
+                        if (!mbar_wait(empty0 + 8 * s, ((it / stages) & 1) ^ 1)) {
+                            atomicExch(&g_tc_status, 11);
+                            ok = false;
+                            break;
+                        }
+                        if (rank == 0) mbar_expect_tx(fb, 2 * STAGE_BYTES);
+                        tma_load_2d_pair(st, &tm_w, i * BK, n0, fb);
+                    }
                     tma_load_2d_pair(st + W_BYTES, &tm_a, i * BK, row0, fb);
                 }
             }
@@ -516,6 +529,7 @@ __global__ void __launch_bounds__(192) gemm_tc_pair_kernel(const __grid_constant
     } else {
         const int quarter = warp & 3;
         int nt = 0;
+        pdl_wait();                                        // the output may still be in use by the kernel before
         for (int t = pair; t < total; t += n_pairs, ++nt) {
             const int buf = nt & 1;
             if (!mbar_wait(acc_full0 + 8 * buf, (nt >> 1) & 1)) {
@@ -646,10 +660,12 @@ int launch_pair(const CUtensorMap& tw, const CUtensorMap& ta, Params p, cudaStre
     const int pairs = sm_count() / 2;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * (unsigned)(total < pairs ? total : pairs)), cfg.blockDim = dim3(192), cfg.dynamicSmemBytes = smem, cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2, attr[0].val.clusterDim.y = 1, attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr, cfg.numAttrs = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;      // the weights of the first ring are fetched under the kernel before
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = q6k_pdl_mode() != 0 ? 2 : 1;
     cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel<BT2>, tw, ta, p);
     return q6k_check_launch("gemm_tc pair");
 }

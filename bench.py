@@ -397,11 +397,6 @@ def main():
     total_b, w_b, kv_b = decode_bytes(cfg_d, layers, args.batch, ctx)
     achieved = total_b / (ms * 1e-3) / 1e9
 
-    points = {}
-    for B in point_batches:
-        pms, _ = timed_decode(B, max(4, args.steps // 2), 3)
-        points[f"decode_b{B}"] = round(B * 1000.0 / pms, 1)
-
     # prefill: one prompt of T tokens in one step, the logits of its last token wanted
     T = args.prefill_tokens
     pre_ms = []
@@ -420,6 +415,11 @@ def main():
     pf = prefill_flops(cfg_d, layers, T)
     prefill = {"value": round(T * 1000.0 / pms, 1), "tokens": T, "ms": round(pms, 3),
                "frac": round(pf / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    points = {}
+    for B in point_batches:
+        pms, _ = timed_decode(B, max(4, args.steps // 2), 3)
+        points[f"decode_b{B}"] = round(B * 1000.0 / pms, 1)
 
     # end to end: Engine.step() with host ids in and sampled ids out each step
     for i in range(args.batch):

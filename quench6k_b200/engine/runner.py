@@ -247,7 +247,7 @@ class ModelRunner:
     @staticmethod
     def decode_bucket(n: int) -> int:
         """The batch size a decode step of n requests is recorded at: n up to 8, then the next
-        multiple of 4 up to 32, of 8 up to 64, of 16 beyond (at most a seventh more rows)."""
+        multiple of 4 up to 32, of 8 up to 64, of 16 beyond (at most a third more rows at 9, a quarter beyond 32)."""
         if n <= 8:
             return n
         unit = 4 if n <= 32 else 8 if n <= 64 else 16

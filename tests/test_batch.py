@@ -72,3 +72,11 @@ def test_short_requests_go_one_way_and_the_others_another():
     assert sorted(covered) == list(range(80))                      # every row of the step exactly once
     none0, nonen, zero = ctx.query_tile_pairs(16, False, more_than=64)
     assert zero == 0 and tuple(none0.shape) == (0, 2)
+
+
+def test_decode_batches_are_recorded_at_a_few_sizes():
+    from quench6k_b200.engine.runner import ModelRunner
+    b = ModelRunner.decode_bucket
+    assert [b(n) for n in range(1, 10)] == [1, 2, 3, 4, 5, 6, 7, 8, 12]
+    assert [b(n) for n in (12, 13, 31, 32, 33, 40, 64, 65, 80, 81, 200)] == [12, 16, 32, 32, 40, 40, 64, 80, 80, 96, 208]
+    assert all(n <= b(n) < n + (1 if n <= 8 else 4 if n <= 32 else 8 if n <= 64 else 16) for n in range(1, 600))

@@ -79,3 +79,25 @@ def test_native_rows_match_the_python_twin():
             want = pick_from_pool(ids[r, :sizes[r]], vals[r, :sizes[r]], params[r], generated[r], b[r])
             assert got[r] == want, (case, r, params[r])
             assert a[r].state == b[r].state
+
+
+def test_device_rows_records():
+    """The per-row records of the device sampler: pool sizes, options as 32-bit values, a uniform
+    drawn exactly for the rows that sample, and no penalties."""
+    import numpy as np
+    import pytest
+    from quench6k_b200.sampling.sampler import ROW_RECORD, device_rows
+    assert ROW_RECORD.itemsize == 32
+    params = [SamplingParams(temperature=0.0), SamplingParams(temperature=0.7, top_k=0, top_p=0.9, min_p=0.05),
+              SamplingParams(temperature=1.0, top_k=1), SamplingParams(temperature=1.3, top_k=40)]
+    rngs = [SplitMix64(s) for s in (1, 2, 3, 4)]
+    rec = np.zeros(6, dtype=ROW_RECORD)
+    k = device_rows(params, rngs, 1000, rec)
+    assert k == 256 and rec["size"][:4].tolist() == [1, 256, 1, 40] and rec["top_k"][:4].tolist() == [20, 0, 1, 40]
+    assert rec["u"][0] == 0.0 and rec["u"][2] == 0.0
+    assert rec["u"][1] == P.splitmix64_uniform(2, 1) and rec["u"][3] == P.splitmix64_uniform(4, 1)
+    assert [r.state for r in rngs[::2]] == [1, 3]                     # greedy rows draw nothing
+    assert rec["temperature"][1] == np.float32(0.7) and rec["min_p"][1] == np.float32(0.05)
+    assert device_rows(params[:1], rngs[:1], 100, rec) == 1
+    with pytest.raises(ValueError):
+        device_rows([SamplingParams(temperature=0.5, presence_penalty=0.1)], rngs[:1], 1000, rec)

@@ -95,6 +95,44 @@ def test_command_line(tmp_path):
     assert f"ids: {want}" in r.stdout
 
 
+def test_command_line_bench_and_ppl(tmp_path):
+    """`bench` (prefill and greedy decode rates per context, graph decoding checked against eager
+    decoding, one JSON record per context) and `ppl` (chunks scored on their second half) in the
+    reference's manner, on files of token ids."""
+    import json
+    import math
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg, weights = helpers.make_model_folder(str(tmp_path), "A", seed=26)
+    ids = helpers.random_tokens(90, cfg["vocab_size"], 12)
+    corpus = tmp_path / "ids.txt"
+    corpus.write_text(" ".join(map(str, ids[:45])) + "\n" + ",".join(map(str, ids[45:])))
+    out = tmp_path / "bench.jsonl"
+    run = lambda *args: subprocess.run([sys.executable, "-m", "quench6k_b200", *args], cwd=root, capture_output=True, text=True, timeout=600)
+    r = run("bench", "--model", str(tmp_path), "--ids", str(corpus), "--ctx", "16", "40", "--generate", "8", "--json", str(out),
+            "--dtype", "float32", "--max-batch-tokens", "12")
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert "graph decoding matches eager decoding (8 tokens)" in r.stdout
+    recs = [json.loads(line) for line in out.read_text().splitlines()]
+    assert [x["ctx"] for x in recs] == [16, 40] and all(x["generate"] == 8 and x["kv"] == "fp32" and x["decode_tok_s"] > 0 for x in recs)
+    for x in recs:                                  # the tokens it printed are the plain implementation's greedy continuation
+        want, _ = plain_greedy(cfg, weights, ids[:x["ctx"]], 8)
+        assert f"{want}" in r.stdout
+        assert x["copied"] == sum(1 for a, b in zip(want, ids[x["ctx"]:]) if a == b)
+    r = run("ppl", "--model", str(tmp_path), "--file", str(corpus), "--ctx", "24", "--chunks", "3", "--dtype", "float32",
+            "--max-batch-tokens", "5")
+    assert r.returncode == 0, r.stderr[-2000:]
+    nll, count = 0.0, 0
+    for c in range(3):
+        toks = ids[c * 24:(c + 1) * 24]
+        logits = helpers.plain_logits(cfg, weights, toks, False)[0]
+        for p in range(12, 23):
+            nll += float(torch.logsumexp(logits[p], -1) - logits[p][toks[p + 1]])
+            count += 1
+    got = float(r.stdout.strip().splitlines()[-1].split(":")[1].split("(")[0])
+    assert abs(got - math.exp(nll / count)) <= 2e-4 * got, (got, math.exp(nll / count))
+    assert r.stdout.count("[") == 3
+
+
 @pytest.mark.parametrize("name,dtype,lengths", [("B", "float32", (9, 21, 14)), ("B", "bfloat16", (9, 21, 14)),
                                                 ("D", "bfloat16", (300, 700, 140)),
                                                 ("B", "float32", (9, 21, 14, 5, 8, 11, 6, 17, 10, 12, 7)),

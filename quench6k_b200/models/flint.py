@@ -8,9 +8,39 @@ the Hugging Face style ones listed in `tensor_names` below.
 """
 from __future__ import annotations
 
+import re
+from typing import Optional
+
 from ..config.flint import ARCHITECTURE, FlintConfig
 from ..config.registry import register_architecture
 from ..spec import LayerSpec, ModelSpec, PartSpec
+
+
+# The reference's tensor names (GGUF, crates/engine/src/flint.rs:270-375) -> the names declared here.  Its expert
+# tensors are stacked as [E*I, D] (gate, up) and [E*D, I] (down), which the loader takes for the declared
+# [E, I, D] and [E, D, I].
+_GGUF_TOP = {"token_embd.weight": "model.embed_tokens.weight", "output_norm.weight": "model.norm.weight", "output.weight": "lm_head.weight"}
+_GGUF_LAYER = {
+    "attn_norm.weight": "input_layernorm.weight", "ffn_norm.weight": "post_attention_layernorm.weight",
+    "attn_q.weight": "self_attn.q_proj.weight", "attn_k.weight": "self_attn.k_proj.weight", "attn_v.weight": "self_attn.v_proj.weight",
+    "attn_output.weight": "self_attn.o_proj.weight", "attn_q_norm.weight": "self_attn.q_norm.weight",
+    "attn_k_norm.weight": "self_attn.k_norm.weight", "attn_sinks.weight": "self_attn.sinks", "ffn_gate_inp.weight": "mlp.gate.weight",
+    "ffn_gate_exps.weight": "mlp.experts.gate_proj.weight", "ffn_up_exps.weight": "mlp.experts.up_proj.weight",
+    "ffn_down_exps.weight": "mlp.experts.down_proj.weight", "ffn_gate_shexp.weight": "mlp.shared_experts.gate_proj.weight",
+    "ffn_up_shexp.weight": "mlp.shared_experts.up_proj.weight", "ffn_down_shexp.weight": "mlp.shared_experts.down_proj.weight",
+    "ffn_gate.weight": "mlp.gate_proj.weight", "ffn_up.weight": "mlp.up_proj.weight", "ffn_down.weight": "mlp.down_proj.weight",
+}
+_GGUF_BLOCK = re.compile(r"^blk\.(\d+)\.(.+)$")
+
+
+def gguf_alias(name: str) -> Optional[str]:
+    """The declared name of a tensor stored under the reference's GGUF name, or None."""
+    if name in _GGUF_TOP:
+        return _GGUF_TOP[name]
+    m = _GGUF_BLOCK.match(name)
+    if m and m.group(2) in _GGUF_LAYER:
+        return f"model.layers.{m.group(1)}.{_GGUF_LAYER[m.group(2)]}"
+    return None
 
 
 def build_spec(cfg: FlintConfig, norm_init: str = "ones") -> ModelSpec:
@@ -36,7 +66,7 @@ def build_spec(cfg: FlintConfig, norm_init: str = "ones") -> ModelSpec:
                      order=cfg.execution_order(), kv_source=cfg.kv_sources(),
                      final_norm=PartSpec("rmsnorm", {"eps": cfg.rms_norm_eps, "init": norm_init}),
                      head_name=None if cfg.tie_word_embeddings else "lm_head.weight",
-                     eos_token_ids=tuple(cfg.eos_token_id))
+                     eos_token_ids=tuple(cfg.eos_token_id), name_alias=gguf_alias)
 
 
 register_architecture(ARCHITECTURE, FlintConfig, build_spec, aliases=("flint",))

@@ -7,7 +7,7 @@ works from the ModelSpec alone and never asks which architecture it came from.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Optional, Tuple
+from typing import Any, Callable, Dict, List, Optional, Tuple
 
 
 @dataclass
@@ -40,6 +40,7 @@ class ModelSpec:
     final_norm_prefix: str = "model.norm."
     eos_token_ids: Tuple[int, ...] = ()
     init_std: float = 0.02                 # std of the random-weights mode for matrices
+    name_alias: Optional[Callable[[str], Optional[str]]] = None   # a stored tensor's other name -> the name declared here (or None)
 
 
 @dataclass

@@ -10,7 +10,7 @@ tables become int32.  Conversion to what a kernel consumes happens when a part b
 """
 from __future__ import annotations
 
-from typing import Callable, Dict, List
+from typing import Callable, Dict, List, Optional
 
 import torch
 
@@ -70,14 +70,43 @@ def _stored(t: torch.Tensor) -> torch.Tensor:
     return t
 
 
-def load_folder(folder: str, declared: List[TensorSpec]) -> Callable[[str], torch.Tensor]:
+def load_folder(folder: str, declared: List[TensorSpec],
+                alias: Optional[Callable[[str], Optional[str]]] = None) -> Callable[[str], torch.Tensor]:
     """Check the folder's tensors against the declaration; return `get(name) -> CPU tensor`
-    that reads one tensor at a time (so that a large model never sits in host memory whole)."""
+    that reads one tensor at a time (so that a large model never sits in host memory whole).
+    alias: a stored tensor whose name is not declared is looked up under alias(its name) (an
+    architecture's table of other naming schemes); such a tensor may also be stored with its leading
+    dimensions flattened ([E*I, D] for a declared [E, I, D]) and is reshaped when read."""
     index = index_folder(folder)
-    check_against(declared, {n: (e.dtype, e.shape) for n, (f, e) in index.items()})
+    want = {s.name: s for s in declared}
+    stored_as: Dict[str, str] = {}                       # declared (or unknown) name -> name in the files
+    for n in index:
+        target = n
+        if n not in want and alias is not None:
+            target = alias(n) or n
+        if target in stored_as:
+            raise WeightError([], [], [f"{target}: stored twice, as {stored_as[target]} and as {n}"])
+        stored_as[target] = n
+    found = {}
+    for target, n in stored_as.items():
+        e = index[n][1]
+        shape = tuple(e.shape)
+        spec = want.get(target)
+        if spec is not None and target != n and shape != tuple(spec.shape) and len(shape) >= 1 and len(spec.shape) > len(shape) \
+                and shape[-1] == spec.shape[-1] and _count(shape) == _count(spec.shape):
+            shape = tuple(spec.shape)                    # leading dimensions flattened in the other scheme
+        found[target] = (e.dtype, shape)
+    check_against(declared, found)
 
     def get(name: str) -> torch.Tensor:
-        sf, _ = index[name]
-        return _stored(sf.read(name))
+        sf, _ = index[stored_as[name]]
+        return _stored(sf.read(stored_as[name])).reshape(want[name].shape)
 
     return get
+
+
+def _count(shape) -> int:
+    n = 1
+    for d in shape:
+        n *= int(d)
+    return n

@@ -88,3 +88,46 @@ def test_broken_files(tmp_path):
     write_safetensors(str(tmp_path / "other.safetensors"), [("a", torch.zeros(4))])
     with pytest.raises(SafetensorsError, match="duplicate tensor a"):
         index_folder(str(tmp_path))
+
+
+def test_the_reference_names_are_accepted(tmp_path):
+    """A checkpoint that names its tensors as the reference's GGUF does (blk.N.attn_q.weight, ...,
+    expert tensors stacked as [E*I, D]) loads through the architecture's alias table; a tensor
+    given under both names, or an aliased tensor of the wrong size, is reported."""
+    from quench6k_b200.models.flint import gguf_alias
+    src = tmp_path / "src"
+    src.mkdir()
+    _, weights = helpers.make_model_folder(str(src), "B", seed=4)
+    decl = _decl("B")
+    back = {}
+    for n in weights:
+        for cand in ["token_embd.weight", "output_norm.weight", "output.weight"] + [
+                f"blk.{i}.{leaf}" for i in range(3) for leaf in (
+                    "attn_norm.weight", "ffn_norm.weight", "attn_q.weight", "attn_k.weight", "attn_v.weight", "attn_output.weight",
+                    "attn_q_norm.weight", "attn_k_norm.weight", "attn_sinks.weight", "ffn_gate_inp.weight", "ffn_gate_exps.weight",
+                    "ffn_up_exps.weight", "ffn_down_exps.weight", "ffn_gate_shexp.weight", "ffn_up_shexp.weight", "ffn_down_shexp.weight",
+                    "ffn_gate.weight", "ffn_up.weight", "ffn_down.weight")]:
+            if gguf_alias(cand) == n:
+                back[n] = cand
+    assert set(back) == set(weights)                      # every declared tensor has a name in the other scheme
+    assert gguf_alias("blk.1.something_else") is None and gguf_alias("model.norm.weight") is None
+    flat = lambda n, t: t.reshape(-1, t.shape[-1]) if "_exps" in back[n] else t
+    other = tmp_path / "other"
+    other.mkdir()
+    write_safetensors(str(other / "model.safetensors"), [(back[n], flat(n, t)) for n, t in weights.items()])
+    get = load_folder(str(other), decl, gguf_alias)
+    for spec in decl:
+        assert torch.equal(get(spec.name), weights[spec.name])
+    with pytest.raises(WeightError, match="unexpected"):  # without the table the names mean nothing
+        load_folder(str(other), decl)
+    twice = tmp_path / "twice"
+    twice.mkdir()
+    write_safetensors(str(twice / "model.safetensors"), [(back[n], flat(n, t)) for n, t in weights.items()] +
+                      [("model.norm.weight", weights["model.norm.weight"])])
+    with pytest.raises(WeightError, match="stored twice"):
+        load_folder(str(twice), decl, gguf_alias)
+    wrong = tmp_path / "wrong"
+    wrong.mkdir()
+    write_safetensors(str(wrong / "model.safetensors"), [(back[n], flat(n, t)[:-1] if "_exps" in back[n] else t) for n, t in weights.items()])
+    with pytest.raises(WeightError, match="wrong shape"):
+        load_folder(str(wrong), decl, gguf_alias)

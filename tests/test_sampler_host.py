@@ -101,3 +101,33 @@ def test_device_rows_records():
     assert device_rows(params[:1], rngs[:1], 100, rec) == 1
     with pytest.raises(ValueError):
         device_rows([SamplingParams(temperature=0.5, presence_penalty=0.1)], rngs[:1], 1000, rec)
+
+
+def test_sampled_frequencies_follow_the_distribution():
+    """1,500 draws from one request's stream at min_p 0.2 (the reference's own check of its sampler):
+    candidates below a fifth of the best one's probability never come, the others as often as their
+    renormalised probabilities say (each within four standard deviations)."""
+    import math
+    import numpy as np
+    from quench6k_b200.sampling.sampler import pick_rows_native
+    ids = list(range(100, 112))
+    vals = [2.0, 1.7, 1.5, 1.1, 0.9, 0.4, 0.1, -0.5, -1.0, -2.0, -3.0, -6.0]
+    p = SamplingParams(temperature=0.8, top_k=0, top_p=1.0, min_p=0.2)
+    probs = [math.exp((v - vals[0]) / 0.8) for v in vals]
+    probs = [q if q >= 0.2 else 0.0 for q in probs]
+    total = sum(probs)
+    n = 1500
+    for native in (False, True):
+        rng, counts = SplitMix64(2024), {i: 0 for i in ids}
+        for _ in range(n):
+            if native:
+                tok = pick_rows_native(np.asarray([ids], dtype=np.int32), np.asarray([vals], dtype=np.float32), [len(ids)], [p], [[]], [rng])[0]
+            else:
+                tok = pick_from_pool(ids, vals, p, [], rng)
+            counts[tok] += 1
+        for i, q in zip(ids, probs):
+            expect = n * q / total
+            if q == 0.0:
+                assert counts[i] == 0
+            else:
+                assert abs(counts[i] - expect) <= 4.0 * math.sqrt(expect * (1 - q / total)), (native, i, counts[i], expect)

@@ -98,7 +98,7 @@ class Attention(Mixer):
                 # prompt portions with enough tiles for at least half of the SMs: both products on tcgen05, no key splits
                 out = ops.attention_tc(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, tok0, ntok, self.window,
                                        self.sinks, scale=self.scale)
-                count, row0, row1, most, reach = ctx.short_requests(cut)
+                count, _, _, most, _ = ctx.short_requests(cut)
                 if count:
                     self._split_keys(q, cache, table, ctx, most > narrow_tokens or not ops.attention_mma_supported(self.hd, G, False),
                                      at_most=cut, out=out)

@@ -472,7 +472,7 @@ def test_attention_plan_shares_the_key_tiles(window, n_work, min_per):
 
 
 @pytest.mark.parametrize("scoring,renorm", [("softmax", True), ("sigmoid", False)])
-@pytest.mark.parametrize("T,E,k,D,I", [(1, 256, 8, 2048, 512), (8, 64, 6, 256, 128), (16, 10, 3, 72, 40), (2, 32, 4, 1024, 256),
+@pytest.mark.parametrize("T,E,k,D,I", [(1, 256, 8, 2048, 512), (8, 256, 8, 2048, 512), (16, 256, 8, 2048, 512), (8, 64, 6, 256, 128), (16, 10, 3, 72, 40), (2, 32, 4, 1024, 256),
                                        (3, 16, 2, 640, 1024), (5, 300, 7, 128, 64)])
 def test_decode_moe_path(scoring, renorm, T, E, k, D, I):
     """router_small + per-pair expert tiles against float64.  The first and the last two sizes have

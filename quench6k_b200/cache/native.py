@@ -59,12 +59,17 @@ def host_lib():
         "q6k_sched_update": (i, [vp, _i32p, i, i, _i64p, _i32p, _i32p]),
         "q6k_sched_set_output_token": (i, [vp, i64, i, ctypes.c_int32]),
         "q6k_sched_stop": (i, [vp, i64, i]),
+        "q6k_st_open": (i, [ctypes.c_char_p, ctypes.POINTER(vp)]),
+        "q6k_st_close": (None, [vp]),
+        "q6k_st_count": (i, [vp]),
+        "q6k_st_entry": (i, [vp, i, ctypes.c_char_p, i, ctypes.c_char_p, _i64p, _i32p, _i64p, _i64p]),
+        "q6k_st_read": (i, [vp, i, vp, i64]),
         "q6k_sample_rows": (i, [i, i, _i32p, _f32p, _i32p, _f32p, _i32p, _f32p, _f32p, _f32p, _f32p, _i32p, _i64p, _f64p, _i32p]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
         fn.restype, fn.argtypes = res, args
-    if lib.q6k_host_abi_version() != 3:
+    if lib.q6k_host_abi_version() != 4:
         raise RuntimeError("the host library does not match this package")
     _lib = lib
     return lib

@@ -17,9 +17,14 @@
 #include <cstdio>
 #include <cstring>
 #include <deque>
+#include <memory>
 #include <string>
 #include <unordered_map>
 #include <vector>
+
+#include <fcntl.h>
+#include <sys/stat.h>
+#include <unistd.h>
 
 #define API extern "C" __attribute__((visibility("default")))
 
@@ -422,7 +427,7 @@ int copy_out(const std::vector<T>& v, T* out, int cap, int* n, const char* what)
 }  // namespace
 
 API const char* q6k_host_last_error() { return g_msg; }
-API int q6k_host_abi_version() { return 3; }
+API int q6k_host_abi_version() { return 4; }
 
 // ------------------------------------------------------------------------------- cache manager
 API void* q6k_cm_create(int n_groups, const int* sliding, const int* windows, int page_size, const int* num_pages, int max_requests) {
@@ -739,6 +744,295 @@ API int q6k_sample_rows(int rows, int stride, const int32_t* ids, const float* v
             }
         }
         out[row] = id[order[pick]];
+    }
+    return OK;
+}
+
+// --------------------------------------------------------------------------------- safetensors
+// The index of one safetensors file: 8-byte little-endian header length, a JSON header
+// {name: {"dtype": str, "shape": [ints], "data_offsets": [begin, end]}, "__metadata__": {...}}, then
+// the raw data (the reference's reader: crates/engine/src/checkpoint.rs:174-246).  Byte ranges are
+// checked against the shapes and the file; data is read with pread straight into the caller's memory.
+// quench6k_b200/weights/safetensors_io.py holds a Python twin with the same messages.
+namespace {
+
+struct StEntry {
+    std::string name, dtype;
+    std::vector<int64_t> shape;
+    int64_t begin = 0, end = 0;          // absolute byte offsets in the file
+};
+
+struct StFile {
+    int fd = -1;
+    int64_t size = 0;
+    std::vector<StEntry> entries;
+    ~StFile() {
+        if (fd >= 0) close(fd);
+    }
+};
+
+int dtype_width(const std::string& d) {
+    if (d == "BF16" || d == "F16" || d == "I16") return 2;
+    if (d == "F32" || d == "I32") return 4;
+    if (d == "F64" || d == "I64") return 8;
+    if (d == "I8" || d == "U8" || d == "BOOL") return 1;
+    return 0;
+}
+
+// A JSON reader for what a safetensors header holds; `err` gets a reason when something else comes.
+struct JsonIn {
+    const char* p;
+    const char* end;
+    std::string err;
+    void ws() {
+        while (p < end && (*p == ' ' || *p == '\t' || *p == '\n' || *p == '\r')) ++p;
+    }
+    bool fail_at(const char* what) {
+        if (err.empty()) err = std::string(what) + " at byte " + std::to_string((long long)(p - (end - len)));
+        return false;
+    }
+    int64_t len = 0;
+    bool eat(char c) {
+        ws();
+        if (p < end && *p == c) {
+            ++p;
+            return true;
+        }
+        return false;
+    }
+    bool string(std::string& out) {
+        ws();
+        if (p >= end || *p != '"') return fail_at("expected a string");
+        ++p;
+        out.clear();
+        while (p < end && *p != '"') {
+            unsigned char c = (unsigned char)*p++;
+            if (c < 0x20) return fail_at("control character in a string");
+            if (c != '\\') {
+                out.push_back((char)c);
+                continue;
+            }
+            if (p >= end) return fail_at("unfinished escape");
+            const char e = *p++;
+            switch (e) {
+                case '"': out.push_back('"'); break;
+                case '\\': out.push_back('\\'); break;
+                case '/': out.push_back('/'); break;
+                case 'b': out.push_back('\b'); break;
+                case 'f': out.push_back('\f'); break;
+                case 'n': out.push_back('\n'); break;
+                case 'r': out.push_back('\r'); break;
+                case 't': out.push_back('\t'); break;
+                case 'u': {
+                    if (end - p < 4) return fail_at("unfinished \\u escape");
+                    unsigned v = 0;
+                    for (int i = 0; i < 4; ++i) {
+                        const char h = *p++;
+                        v <<= 4;
+                        if (h >= '0' && h <= '9') v |= (unsigned)(h - '0');
+                        else if (h >= 'a' && h <= 'f') v |= (unsigned)(h - 'a' + 10);
+                        else if (h >= 'A' && h <= 'F') v |= (unsigned)(h - 'A' + 10);
+                        else return fail_at("bad \\u escape");
+                    }
+                    // UTF-8 of the code unit (surrogate pairs are kept as two units: names compare bytewise anyway)
+                    if (v < 0x80) out.push_back((char)v);
+                    else if (v < 0x800) out.push_back((char)(0xC0 | (v >> 6))), out.push_back((char)(0x80 | (v & 0x3F)));
+                    else out.push_back((char)(0xE0 | (v >> 12))), out.push_back((char)(0x80 | ((v >> 6) & 0x3F))), out.push_back((char)(0x80 | (v & 0x3F)));
+                    break;
+                }
+                default: return fail_at("unknown escape");
+            }
+        }
+        if (p >= end) return fail_at("unfinished string");
+        ++p;
+        return true;
+    }
+    bool integer(int64_t& out) {
+        ws();
+        const char* s = p;
+        bool neg = false;
+        if (p < end && *p == '-') neg = true, ++p;
+        if (p >= end || *p < '0' || *p > '9') {
+            p = s;
+            return fail_at("expected an integer");
+        }
+        int64_t v = 0;
+        while (p < end && *p >= '0' && *p <= '9') {
+            if (v > (INT64_MAX - 9) / 10) return fail_at("integer too large");
+            v = v * 10 + (*p++ - '0');
+        }
+        if (p < end && (*p == '.' || *p == 'e' || *p == 'E')) return fail_at("expected an integer");
+        out = neg ? -v : v;
+        return true;
+    }
+    bool int_array(std::vector<int64_t>& out) {
+        out.clear();
+        if (!eat('[')) return fail_at("expected an array");
+        if (eat(']')) return true;
+        do {
+            int64_t v;
+            if (!integer(v)) return false;
+            out.push_back(v);
+        } while (eat(','));
+        return eat(']') || fail_at("expected , or ]");
+    }
+    bool skip_value(int depth = 0) {                 // any JSON value (the metadata, keys this reader does not know)
+        if (depth > 64) return fail_at("nested too deeply");
+        ws();
+        if (p >= end) return fail_at("unexpected end");
+        if (*p == '"') {
+            std::string s;
+            return string(s);
+        }
+        if (*p == '{' || *p == '[') {
+            const char open = *p++, shut = open == '{' ? '}' : ']';
+            if (eat(shut)) return true;
+            do {
+                if (open == '{') {
+                    std::string k;
+                    if (!string(k)) return false;
+                    if (!eat(':')) return fail_at("expected :");
+                }
+                if (!skip_value(depth + 1)) return false;
+            } while (eat(','));
+            return eat(shut) || fail_at("expected , or a closing bracket");
+        }
+        const char* s = p;
+        while (p < end && (*p == '-' || *p == '+' || *p == '.' || (*p >= '0' && *p <= '9') || (*p >= 'a' && *p <= 'z') || (*p >= 'A' && *p <= 'Z'))) ++p;
+        return p > s || fail_at("unexpected character");
+    }
+};
+
+}  // namespace
+
+// Opens a file and indexes its tensors; *handle is set on success.
+API int q6k_st_open(const char* path, void** handle) {
+    *handle = nullptr;
+    auto f = std::make_unique<StFile>();
+    f->fd = open(path, O_RDONLY | O_CLOEXEC);
+    if (f->fd < 0) return fail(E_VALUE, "%s: cannot be opened", path);
+    struct stat sb;
+    if (fstat(f->fd, &sb) != 0) return fail(E_VALUE, "%s: cannot be examined", path);
+    f->size = (int64_t)sb.st_size;
+    unsigned char head[8];
+    if (f->size < 8 || pread(f->fd, head, 8, 0) != 8) return fail(E_VALUE, "%s: shorter than a safetensors header", path);
+    uint64_t n = 0;
+    for (int i = 7; i >= 0; --i) n = (n << 8) | head[i];
+    if (n > (uint64_t)(f->size - 8)) return fail(E_VALUE, "%s: header length %llu exceeds the file (%lld bytes)", path, (unsigned long long)n, (long long)f->size);
+    std::string text((size_t)n, '\0');
+    for (uint64_t got = 0; got < n;) {
+        const ssize_t r = pread(f->fd, &text[(size_t)got], (size_t)(n - got), (off_t)(8 + got));
+        if (r <= 0) return fail(E_VALUE, "%s: the header cannot be read", path);
+        got += (uint64_t)r;
+    }
+    const int64_t base = 8 + (int64_t)n;
+    JsonIn in{text.data(), text.data() + text.size(), std::string()};
+    in.len = (int64_t)text.size();
+    auto bad_json = [&]() { return fail(E_VALUE, "%s: header is not JSON (%s)", path, in.err.empty() ? "unexpected content" : in.err.c_str()); };
+    if (!in.eat('{')) {
+        in.fail_at("expected {");
+        return bad_json();
+    }
+    if (!in.eat('}')) {
+        do {
+            std::string name;
+            if (!in.string(name) || !in.eat(':')) {
+                in.fail_at("expected a name and :");
+                return bad_json();
+            }
+            if (name == "__metadata__") {
+                if (!in.skip_value()) return bad_json();
+                continue;
+            }
+            StEntry e;
+            e.name = name;
+            std::vector<int64_t> offs;
+            bool has_dtype = false, has_shape = false;
+            if (!in.eat('{')) {
+                in.fail_at("expected {");
+                return bad_json();
+            }
+            if (!in.eat('}')) {
+                do {
+                    std::string key;
+                    if (!in.string(key) || !in.eat(':')) {
+                        in.fail_at("expected a key and :");
+                        return bad_json();
+                    }
+                    bool ok;
+                    if (key == "dtype") ok = in.string(e.dtype), has_dtype = true;
+                    else if (key == "shape") ok = in.int_array(e.shape), has_shape = true;
+                    else if (key == "data_offsets") ok = in.int_array(offs);
+                    else ok = in.skip_value();
+                    if (!ok) return bad_json();
+                } while (in.eat(','));
+                if (!in.eat('}')) {
+                    in.fail_at("expected , or }");
+                    return bad_json();
+                }
+            }
+            if (!has_dtype || !has_shape || offs.size() != 2)
+                return fail(E_VALUE, "%s: tensor %s lacks dtype, shape or data_offsets", path, name.c_str());
+            const int width = dtype_width(e.dtype);
+            if (width == 0) return fail(E_VALUE, "%s: tensor %s has unsupported dtype %s", path, name.c_str(), e.dtype.c_str());
+            int64_t count = 1;
+            bool fits = true;
+            for (int64_t d : e.shape) {
+                if (d < 0 || (d > 0 && count > INT64_MAX / 16 / d)) fits = false;
+                else count *= d;
+            }
+            const int64_t b = offs[0], en = offs[1];
+            if (!fits || en - b != count * width || b < 0 || base + en > f->size) {
+                std::string shp = "(";
+                for (size_t i = 0; i < e.shape.size(); ++i) shp += (i ? ", " : "") + std::to_string((long long)e.shape[i]);
+                shp += e.shape.size() == 1 ? ",)" : ")";
+                return fail(E_VALUE, "%s: tensor %s has byte range %lld..%lld for shape %s %s in a file of %lld bytes", path, name.c_str(), (long long)b,
+                            (long long)en, shp.c_str(), e.dtype.c_str(), (long long)f->size);
+            }
+            for (const StEntry& o : f->entries)
+                if (o.name == name) return fail(E_VALUE, "%s: tensor %s is listed twice", path, name.c_str());
+            e.begin = base + b, e.end = base + en;
+            f->entries.push_back(std::move(e));
+        } while (in.eat(','));
+        if (!in.eat('}')) {
+            in.fail_at("expected , or }");
+            return bad_json();
+        }
+    }
+    in.ws();
+    if (in.p != in.end) {
+        in.fail_at("content after the header's object");
+        return bad_json();
+    }
+    *handle = f.release();
+    return OK;
+}
+API void q6k_st_close(void* h) { delete (StFile*)h; }
+API int q6k_st_count(void* h) { return (int)((StFile*)h)->entries.size(); }
+// Entry i: its name (name_cap bytes with the final 0), dtype (at most 7 characters and the 0), up to 8 dimensions,
+// and its absolute byte range.
+API int q6k_st_entry(void* h, int i, char* name, int name_cap, char* dtype, int64_t* shape, int* ndim, int64_t* begin, int64_t* end) {
+    StFile* f = (StFile*)h;
+    if (i < 0 || i >= (int)f->entries.size()) return fail(E_VALUE, "tensor index %d outside 0..%d", i, (int)f->entries.size() - 1);
+    const StEntry& e = f->entries[i];
+    if ((int)e.name.size() + 1 > name_cap) return fail(E_VALUE, "tensor name of %d bytes exceeds the buffer", (int)e.name.size());
+    if (e.shape.size() > 8) return fail(E_VALUE, "tensor %s has %d dimensions (at most 8)", e.name.c_str(), (int)e.shape.size());
+    std::memcpy(name, e.name.c_str(), e.name.size() + 1);
+    std::snprintf(dtype, 8, "%s", e.dtype.c_str());
+    for (size_t d = 0; d < e.shape.size(); ++d) shape[d] = e.shape[d];
+    *ndim = (int)e.shape.size(), *begin = e.begin, *end = e.end;
+    return OK;
+}
+// The bytes of entry i into dst (nbytes must be the entry's size).
+API int q6k_st_read(void* h, int i, void* dst, int64_t nbytes) {
+    StFile* f = (StFile*)h;
+    if (i < 0 || i >= (int)f->entries.size()) return fail(E_VALUE, "tensor index %d outside 0..%d", i, (int)f->entries.size() - 1);
+    const StEntry& e = f->entries[i];
+    if (nbytes != e.end - e.begin) return fail(E_VALUE, "tensor %s holds %lld bytes, %lld were asked for", e.name.c_str(), (long long)(e.end - e.begin), (long long)nbytes);
+    for (int64_t got = 0; got < nbytes;) {
+        const ssize_t r = pread(f->fd, (char*)dst + got, (size_t)std::min<int64_t>(nbytes - got, (int64_t)1 << 30), (off_t)(e.begin + got));
+        if (r <= 0) return fail(E_VALUE, "tensor %s: the file ends early", e.name.c_str());
+        got += r;
     }
     return OK;
 }

@@ -12,7 +12,7 @@ import mmap
 import os
 import struct
 from dataclasses import dataclass
-from typing import Dict, Iterable, List, Tuple
+from typing import Dict, Iterable, List, Optional, Tuple
 
 import torch
 
@@ -39,8 +39,50 @@ class TensorEntry:
 
 
 class SafetensorsFile:
-    def __init__(self, path: str):
+    """One file's tensors by name.  The header is parsed and the data read by the C++ host library
+    (csrc/host/host.cpp, q6k_st_*: pread straight into the tensor's memory) unless Q6K_HOST=python
+    (or native=False) asks for the Python twin below, which gives the same entries and messages."""
+
+    def __init__(self, path: str, native: Optional[bool] = None):
         self.path = path
+        self.entries: Dict[str, TensorEntry] = {}
+        self._h = None
+        self._mm = None
+        if native is None:
+            native = os.environ.get("Q6K_HOST", "").lower() != "python"
+        if native:
+            self._open_native()
+        else:
+            self._open_python()
+
+    # ------------------------------------------------------------------ C++
+    def _open_native(self) -> None:
+        import ctypes
+        from ..cache.native import host_lib
+        lib = host_lib()
+        h = ctypes.c_void_p()
+        if lib.q6k_st_open(os.fsencode(self.path), ctypes.byref(h)):
+            raise SafetensorsError(lib.q6k_host_last_error().decode())
+        self._h, self._lib, self._index = h, lib, {}
+        name, dtype = ctypes.create_string_buffer(4096), ctypes.create_string_buffer(8)
+        shape, ndim = (ctypes.c_int64 * 8)(), ctypes.c_int32()
+        begin, end = ctypes.c_int64(), ctypes.c_int64()
+        for i in range(lib.q6k_st_count(h)):
+            if lib.q6k_st_entry(h, i, name, 4096, dtype, shape, ctypes.byref(ndim), ctypes.byref(begin), ctypes.byref(end)):
+                raise SafetensorsError(f"{self.path}: {lib.q6k_host_last_error().decode()}")
+            n = name.value.decode()
+            self.entries[n] = TensorEntry(n, _DTYPES[dtype.value.decode()][0], tuple(shape[d] for d in range(ndim.value)), self.path,
+                                          begin.value, end.value)
+            self._index[n] = i
+
+    def __del__(self):
+        h, self._h = getattr(self, "_h", None), None
+        if h:
+            self._lib.q6k_st_close(h)
+
+    # ------------------------------------------------------------------ Python twin
+    def _open_python(self) -> None:
+        path = self.path
         size = os.path.getsize(path)
         with open(path, "rb") as f:
             head = f.read(8)
@@ -51,13 +93,16 @@ class SafetensorsFile:
                 raise SafetensorsError(f"{path}: header length {n} exceeds the file ({size} bytes)")
             try:
                 header = json.loads(f.read(n))
-            except json.JSONDecodeError as e:
+            except (json.JSONDecodeError, UnicodeDecodeError) as e:
                 raise SafetensorsError(f"{path}: header is not JSON ({e})") from None
         base = 8 + n
-        self.entries: Dict[str, TensorEntry] = {}
+        if not isinstance(header, dict):
+            raise SafetensorsError(f"{path}: header is not JSON (expected an object)")
         for name, info in header.items():
             if name == "__metadata__":
                 continue
+            if not isinstance(info, dict) or not {"dtype", "shape", "data_offsets"} <= set(info) or len(info["data_offsets"]) != 2:
+                raise SafetensorsError(f"{path}: tensor {name} lacks dtype, shape or data_offsets")
             if info["dtype"] not in _DTYPES:
                 raise SafetensorsError(f"{path}: tensor {name} has unsupported dtype {info['dtype']}")
             dt, width = _DTYPES[info["dtype"]]
@@ -66,20 +111,24 @@ class SafetensorsFile:
             count = 1
             for s in shape:
                 count *= s
-            if e - b != count * width or b < 0 or base + e > size:
+            if min(shape, default=0) < 0 or e - b != count * width or b < 0 or base + e > size:
                 raise SafetensorsError(f"{path}: tensor {name} has byte range {b}..{e} for shape {shape} {info['dtype']} in a file of {size} bytes")
             self.entries[name] = TensorEntry(name, dt, shape, path, base + b, base + e)
-        self._mm = None
 
     def read(self, name: str) -> torch.Tensor:
-        """A CPU tensor with the stored dtype and shape (a copy; the map is not kept alive by it)."""
+        """A CPU tensor with the stored dtype and shape (a copy; nothing of the file is kept alive by it)."""
         ent = self.entries[name]
-        if self._mm is None:
-            self._f = open(self.path, "rb")
-            self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ)
         nbytes = ent.end - ent.begin
         if nbytes == 0:
             return torch.empty(ent.shape, dtype=ent.dtype)
+        if self._h is not None:
+            out = torch.empty(ent.shape, dtype=ent.dtype)
+            if self._lib.q6k_st_read(self._h, self._index[name], out.data_ptr(), nbytes):
+                raise SafetensorsError(f"{self.path}: {self._lib.q6k_host_last_error().decode()}")
+            return out
+        if self._mm is None:
+            self._f = open(self.path, "rb")
+            self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ)
         buf = bytearray(self._mm[ent.begin:ent.end])
         return torch.frombuffer(buf, dtype=ent.dtype).reshape(ent.shape)
 
@@ -122,4 +171,4 @@ def write_safetensors(path: str, tensors: Iterable[Tuple[str, torch.Tensor]]) ->
         f.write(blob)
         for _, t in items:
             if t.numel():
-                f.write(t.view(torch.uint8).numpy().tobytes() if t.dtype != torch.bool else t.numpy().tobytes())
+                f.write(t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.dtype != torch.bool else t.numpy().tobytes())

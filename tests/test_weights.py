@@ -131,3 +131,46 @@ def test_the_reference_names_are_accepted(tmp_path):
     write_safetensors(str(wrong / "model.safetensors"), [(back[n], flat(n, t)[:-1] if "_exps" in back[n] else t) for n, t in weights.items()])
     with pytest.raises(WeightError, match="wrong shape"):
         load_folder(str(wrong), decl, gguf_alias)
+
+
+def test_both_readers_agree(tmp_path):
+    """The C++ reader of safetensors files and its Python twin: the same entries and bytes for a
+    file with metadata, escaped names, empty and scalar tensors; the same refusals for broken files."""
+    import json
+    import struct
+    from quench6k_b200.weights.safetensors_io import SafetensorsFile
+    good = tmp_path / "good.safetensors"
+    tensors = [("plain", torch.randn(3, 5)), ("half.bf16", torch.randn(7).to(torch.bfloat16)), ("ints", torch.arange(12, dtype=torch.int64).reshape(2, 3, 2)),
+               ("empty", torch.zeros(0, 4)), ("scalar", torch.tensor(2.5)), ('odd "name"\\ü\n', torch.ones(2, dtype=torch.uint8))]
+    write_safetensors(str(good), tensors)
+    raw = good.read_bytes()
+    (n,) = struct.unpack("<Q", raw[:8])
+    header = json.loads(raw[8:8 + n])
+    header["__metadata__"] = {"format": "pt", "note": "a \"quoted\" word", "nested": "x"}
+    header["plain"]["extra_key"] = [1, {"a": None}, True, 1.5e3]
+    blob = json.dumps(header, indent=1, ensure_ascii=True).encode()
+    good.write_bytes(struct.pack("<Q", len(blob)) + blob + raw[8 + n:])
+    a, b = SafetensorsFile(str(good), native=True), SafetensorsFile(str(good), native=False)
+    assert a.entries == b.entries and set(a.entries) == {t[0] for t in tensors}
+    for name, t in tensors:
+        assert torch.equal(a.read(name), t) and torch.equal(b.read(name), t)
+
+    def broken(data, match):
+        p = tmp_path / "bad.safetensors"
+        p.write_bytes(data)
+        for native in (True, False):
+            with pytest.raises(SafetensorsError, match=match):
+                SafetensorsFile(str(p), native=native)
+
+    def with_header(h, payload=b""):
+        text = (h if isinstance(h, bytes) else json.dumps(h).encode())
+        return struct.pack("<Q", len(text)) + text + payload
+
+    broken(b"\x01\x02", "shorter than a safetensors header")
+    broken(struct.pack("<Q", 100) + b"{}", "header length 100 exceeds the file")
+    broken(with_header(b'{"a": {"dtype": "F32", "shape": [1], "data_offsets": [0, 4]'), "header is not JSON")
+    broken(with_header(b'[1, 2]'), "header is not JSON")
+    broken(with_header({"a": {"dtype": "F8_E4M3", "shape": [1], "data_offsets": [0, 1]}}, b"\0"), "tensor a has unsupported dtype F8_E4M3")
+    broken(with_header({"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 4]}}, b"\0" * 8), "tensor a has byte range 0..4 for shape \\(2,\\) F32")
+    broken(with_header({"a": {"dtype": "F32", "shape": [2, 1], "data_offsets": [0, 8]}}, b"\0" * 4), "tensor a has byte range 0..8 for shape \\(2, 1\\) F32 in a file of")
+    broken(with_header({"a": {"dtype": "F32", "shape": [1]}}, b"\0" * 4), "tensor a lacks dtype, shape or data_offsets")

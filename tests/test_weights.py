@@ -174,3 +174,56 @@ def test_both_readers_agree(tmp_path):
     broken(with_header({"a": {"dtype": "F32", "shape": [2], "data_offsets": [0, 4]}}, b"\0" * 8), "tensor a has byte range 0..4 for shape \\(2,\\) F32")
     broken(with_header({"a": {"dtype": "F32", "shape": [2, 1], "data_offsets": [0, 8]}}, b"\0" * 4), "tensor a has byte range 0..8 for shape \\(2, 1\\) F32 in a file of")
     broken(with_header({"a": {"dtype": "F32", "shape": [1]}}, b"\0" * 4), "tensor a lacks dtype, shape or data_offsets")
+
+
+def test_header_reader_against_random_headers(tmp_path):
+    """The C++ reader's own JSON reader against Python's on headers with random names (escapes,
+    other scripts), random metadata values and unknown keys, written with random spacing."""
+    import json
+    import random
+    import struct
+    from quench6k_b200.weights.safetensors_io import SafetensorsFile
+    rng = random.Random(17)
+    alphabet = ['a', 'Z', '0', '.', '_', ' ', '"', '\\', '/', '\n', '\t', 'é', 'ß', '中', ' ', '\x7f', '{', ']', ':', ',']
+    widths = {"F32": 4, "BF16": 2, "I64": 8, "U8": 1}
+
+    def value(depth=0):
+        kind = rng.randrange(7 if depth < 3 else 5)
+        if kind == 0:
+            return "".join(rng.choice(alphabet) for _ in range(rng.randrange(6)))
+        if kind == 1:
+            return rng.choice([0, -3, 17, 2.5, -1e-3, 6.02e23])
+        if kind == 2:
+            return rng.choice([True, False, None])
+        if kind in (3, 4):
+            return rng.randrange(1000)
+        if kind == 5:
+            return [value(depth + 1) for _ in range(rng.randrange(4))]
+        return {str(i) + rng.choice(alphabet): value(depth + 1) for i in range(rng.randrange(4))}
+
+    for case in range(40):
+        header, at = {}, 0
+        for t in range(rng.randrange(1, 7)):
+            name = "".join(rng.choice(alphabet) for _ in range(rng.randrange(1, 12))) + str(t)
+            dtype = rng.choice(list(widths))
+            shape = [rng.randrange(0, 4) for _ in range(rng.randrange(0, 4))]
+            n = widths[dtype]
+            for d in shape:
+                n *= d
+            header[name] = {"dtype": dtype, "shape": shape, "data_offsets": [at, at + n]}
+            if rng.random() < 0.3:
+                header[name]["note"] = value()
+            at += n
+        if rng.random() < 0.7:
+            header["__metadata__"] = {"k" + str(i): value() for i in range(rng.randrange(4))}
+        items = list(header.items())
+        rng.shuffle(items)
+        text = json.dumps(dict(items), ensure_ascii=rng.random() < 0.5, indent=rng.choice([None, 0, 3]),
+                          separators=rng.choice([(",", ":"), (", ", ": "), (" ,\t", " :\n")])).encode()
+        p = tmp_path / f"h{case}.safetensors"
+        payload = bytes(rng.randrange(256) for _ in range(at))
+        p.write_bytes(struct.pack("<Q", len(text)) + text + payload)
+        a, b = SafetensorsFile(str(p), native=True), SafetensorsFile(str(p), native=False)
+        assert a.entries == b.entries and len(a.entries) == len(header) - ("__metadata__" in header), case
+        for name in a.entries:
+            assert torch.equal(a.read(name).reshape(-1).view(torch.uint8), b.read(name).reshape(-1).view(torch.uint8))

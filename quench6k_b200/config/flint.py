@@ -45,6 +45,7 @@ class FlintConfig:
     scoring_func: str = "softmax"            # "softmax" | "sigmoid" (reference: flint.cu:829-868)
     norm_topk_prob: bool = True              # divide chosen weights by their sum
     qk_norm: bool = False                    # per-head RMSNorm of q and k before RoPE
+    qk_norm_eps: Optional[float] = None      # eps of that norm; None: rms_norm_eps (the reference's is the literal 1e-6, flint.cu:139)
     attn_sinks: bool = False                 # learned per-head logit in the softmax denominator
     sliding_window: Optional[int] = None     # keys visible to a sliding layer (reference: 513)
     sliding_window_pattern: Optional[List[bool]] = None   # per layer: True = sliding
@@ -113,10 +114,12 @@ class FlintConfig:
             need(isinstance(v, int) and not isinstance(v, bool) and v > 0, f"{k} must be a positive integer, got {v!r}")
         need(self.num_attention_heads % self.num_key_value_heads == 0,
              f"num_attention_heads {self.num_attention_heads} is not a multiple of num_key_value_heads {self.num_key_value_heads}")
-        need(self.head_dim % 2 == 0, f"head_dim {self.head_dim} must be even (RoPE rotates halves)")
+        need(self.head_dim % 16 == 0 and self.head_dim <= 256,
+             f"head_dim {self.head_dim}: the attention kernels take multiples of 16 up to 256")
         need(self.num_experts_per_tok <= self.n_routed_experts,
              f"num_experts_per_tok {self.num_experts_per_tok} exceeds n_routed_experts {self.n_routed_experts}")
         need(self.rms_norm_eps > 0, "rms_norm_eps must be positive")
+        need(self.qk_norm_eps is None or self.qk_norm_eps > 0, "qk_norm_eps must be positive")
         need(self.rope_theta > 0, "rope_theta must be positive")
         need(self.scoring_func in ("softmax", "sigmoid"), f"scoring_func {self.scoring_func!r} is neither 'softmax' nor 'sigmoid'")
         need(self.torch_dtype in ("bfloat16", "float32"), f"torch_dtype {self.torch_dtype!r} is neither 'bfloat16' nor 'float32'")
@@ -132,7 +135,8 @@ class FlintConfig:
         need(0 <= self.first_k_dense_replace <= L, f"first_k_dense_replace {self.first_k_dense_replace} outside 0..{L}")
         if self.first_k_dense_replace > 0:
             need(self.intermediate_size > 0, "first_k_dense_replace > 0 needs intermediate_size")
-        need(self.n_shared_experts >= 0, "n_shared_experts must not be negative")
+        need(self.n_shared_experts in (0, 1),
+             f"n_shared_experts {self.n_shared_experts}: one ungated shared expert (of shared_expert_intermediate_size) or none is built")
         if self.n_shared_experts > 0:
             need(self.shared_expert_intermediate_size > 0, "n_shared_experts > 0 needs shared_expert_intermediate_size")
         for t in self.eos_token_id:

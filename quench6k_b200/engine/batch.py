@@ -45,6 +45,7 @@ class StepContext:
                                                   # layers: the runner empties it before it records the step, so that a kernel
                                                   # that fills a plan from the step's positions is part of the recording
     fed: Optional[torch.Tensor] = None            # int32 ids the step before sampled: a token id -(i + 1) stands for fed[i]
+    position: int = 0                             # the executed position (index into the model's order) whose block is running
 
     def query_tiles(self, tokens_per_tile: int, at_most: Optional[int] = None):
         """Tiles of at most `tokens_per_tile` consecutive tokens of one request, as device arrays

@@ -89,6 +89,7 @@ class DecoderModel:
         h = ops.embed(ctx.token_ids, self.embed, fed=ctx.fed)
         pending = None                      # an add into h that a block has left to the next norm
         for p, i in enumerate(self.order):
+            ctx.position = p
             pending = self.blocks[i].forward(h, ctx, caches[p], states[p], pending)
         if ctx.n_logit_rows == 0:
             return None

@@ -50,7 +50,7 @@ def build_spec(cfg: FlintConfig, norm_init: str = "ones") -> ModelSpec:
                else PartSpec("none", {"head_dim": cfg.head_dim}))
         mixer = PartSpec("attention", {
             "num_heads": cfg.num_attention_heads, "num_kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
-            "eps": cfg.rms_norm_eps, "pos": pos, "window": cfg.sliding_window if cfg.layer_is_sliding(i) else None,
+            "eps": cfg.qk_norm_eps if cfg.qk_norm_eps is not None else cfg.rms_norm_eps, "pos": pos, "window": cfg.sliding_window if cfg.layer_is_sliding(i) else None,
             "sinks": cfg.attn_sinks, "qk_norm": cfg.qk_norm, "norm_init": norm_init})
         if cfg.layer_is_dense(i):
             ffn = PartSpec("dense", {"intermediate_size": cfg.intermediate_size})

@@ -348,10 +348,13 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
 
 
 # --------------------------------------------------------------------------- attention
-def qk_prep(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, q_norm, k_norm, eps: float, rope_theta: Optional[float],
+def qk_prep(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, q_norm, k_norm, eps: float, rotary,
             positions: torch.Tensor, req_of_token: torch.Tensor, block_table: Optional[torch.Tensor], page_size: int,
             k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], out_dtype: torch.dtype) -> torch.Tensor:
-    """QK-norm, RoPE, q -> out_dtype [T, Hq, hd]; k, v -> their pages (when k_pages is given).
+    """QK-norm, rotation, q -> out_dtype [T, Hq, hd]; k, v -> their pages (when k_pages is given).
+    rotary: None, or (inv_freq float32 [rotary_dim / 2] on the device, rotary_dim, neighbours): the
+    first rotary_dim dimensions of every q and k head turn by position * inv_freq[pair], paired by
+    halves (d with d + rotary_dim / 2) or, neighbours=True, 2i with 2i + 1.
     qkv may be [slices, T, width]: split-K partial products, summed in order first."""
     _need(qkv, "qkv", torch.float32)
     splits, split_stride = 1, 0
@@ -373,10 +376,15 @@ def qk_prep(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, q_norm, k_norm, eps: 
     for nm, w in (("q_norm", q_norm), ("k_norm", k_norm)):
         if w is not None:
             _need(w, nm, torch.float32, (hd,))
+    inv_freq, rotary_dim, neighbours = rotary if rotary is not None else (None, 0, False)
+    if inv_freq is not None:
+        if rotary_dim <= 0 or rotary_dim % 2 or rotary_dim > hd:
+            raise KernelError(f"qk_prep: {rotary_dim} rotating dimensions of a head of {hd}")
+        _need(inv_freq, "inv_freq", torch.float32, (rotary_dim // 2,))
     q = torch.empty((T, Hq, hd), dtype=out_dtype, device=qkv.device)
     max_blocks = block_table.shape[1] if block_table is not None else 1
     _call("q6k_qk_prep", _ptr(qkv), _i(qkv.stride(0)), _i(splits), _ll(split_stride), _i(T), _i(Hq), _i(Hkv), _i(hd), _ptr(q_norm), _ptr(k_norm), _f(eps),
-          _i(1 if rope_theta is not None else 0), _f(rope_theta or 0.0), _ptr(positions), _ptr(req_of_token), _ptr(block_table),
+          _ptr(inv_freq), _i(rotary_dim), _i(1 if neighbours else 0), _ptr(positions), _ptr(req_of_token), _ptr(block_table),
           _i(max_blocks), _i(page_size), _i(k_pages.shape[1] if write else 0), _ptr(q), _ptr(k_pages), _ptr(v_pages),
           _i(1 if write else 0), _i(dtype_code(out_dtype)), _stream())
     return q
@@ -548,9 +556,10 @@ SMALL_T = 16
 _tickets = {}
 
 
-def router_small(xn: torch.Tensor, w: torch.Tensor, k: int, scoring: str, renorm: bool):
+def router_small(xn: torch.Tensor, w: torch.Tensor, k: int, scoring: str, renorm: bool, with_logits: bool = False):
     """Router logits, scores and top-k of at most 16 tokens in one launch:
-    (sel_e [T, k], sel_w [T, k], order [T*k]: the pairs sorted by expert)."""
+    (sel_e [T, k], sel_w [T, k], order [T*k]: the pairs sorted by expert); with_logits: also the
+    FP32 router logits [T, E] the kernel left behind."""
     _need(xn, "xn", torch.bfloat16)
     _need(w, "w", torch.bfloat16)
     T, D = xn.shape
@@ -567,7 +576,7 @@ def router_small(xn: torch.Tensor, w: torch.Tensor, k: int, scoring: str, renorm
     order = torch.empty(T * k, dtype=torch.int32, device=dev)
     _call("q6k_router_small", _ptr(xn), _ptr(w), _i(T), _i(E), _i(D), _i(k), _i(1 if scoring == "sigmoid" else 0),
           _i(1 if renorm else 0), _ptr(logits), _ptr(sel_e), _ptr(sel_w), _ptr(order), _ptr(ticket), _stream())
-    return sel_e, sel_w, order
+    return (sel_e, sel_w, order, logits) if with_logits else (sel_e, sel_w, order)
 
 
 _pair_scratch = {}

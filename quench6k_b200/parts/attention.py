@@ -40,6 +40,7 @@ class Attention(Mixer):
             out += [TensorSpec("q_norm.weight", (hd,), "f32", init), TensorSpec("k_norm.weight", (hd,), "f32", init)]
         if self.has_sinks:
             out.append(TensorSpec("sinks", (Hq,), "f32", ("normal", self.sink_std)))
+        out += [TensorSpec("position." + t.name, t.shape, t.role, t.init) for t in self.pos.tensors()]
         return out
 
     def bind(self, get, rt):
@@ -52,6 +53,7 @@ class Attention(Mixer):
         self.q_norm = to_f32(get("q_norm.weight"), rt) if self.qk_norm else None
         self.k_norm = to_f32(get("k_norm.weight"), rt) if self.qk_norm else None
         self.sinks = to_f32(get("sinks"), rt) if self.has_sinks else None
+        self.pos.bind(lambda n: get("position." + n), rt)
 
     def cache_request(self):
         if self.window is not None:
@@ -61,8 +63,8 @@ class Attention(Mixer):
     def forward(self, xn, ctx, cache, state, out):
         rt = self.rt
         write = cache.write
-        theta = self.pos.fused_rope_theta()
-        fused_pos = theta is not None or isinstance(self.pos, POSITION_ENCODINGS["none"])
+        rotary = self.pos.rotary_table()
+        fused_pos = rotary is not None or self.pos.is_identity
         # FP32 [T, (Hq + 2 Hkv) hd] or [T, Hq hd]; for few rows possibly as split-K partials, which qk_prep sums
         qkv = linear.matmul(xn, self.w_qkv if write else self.w_q, rt, partials_ok=fused_pos)
         table = ctx.block_tables[cache.group]
@@ -72,7 +74,7 @@ class Attention(Mixer):
                             table if write else None, cache.page_size, cache.k if write else None,
                             cache.v if write else None, rt.dtype)
         else:
-            q = ops.qk_prep(qkv, self.Hq, self.Hkv, self.hd, self.q_norm, self.k_norm, self.eps, theta, ctx.positions,
+            q = ops.qk_prep(qkv, self.Hq, self.Hkv, self.hd, self.q_norm, self.k_norm, self.eps, rotary, ctx.positions,
                             ctx.req_of_token, table if write else None, cache.page_size, cache.k if write else None,
                             cache.v if write else None, rt.dtype)
         a = self._attend(q, cache, table, ctx)
@@ -137,7 +139,7 @@ class Attention(Mixer):
         return self.__dict__[key]
 
     def _unfused_position(self, qkv, ctx, write):
-        """QK-norm, then a position encoding that is not the fused rotary one, on FP32 q and k."""
+        """QK-norm, then a position encoding that is no rotation of pairs (its own `apply`), on FP32 q and k."""
         T = qkv.shape[0]
         nq, nk = self.Hq * self.hd, self.Hkv * self.hd
         q = qkv[:, :nq].reshape(T * self.Hq, self.hd).contiguous()

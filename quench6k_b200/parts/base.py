@@ -10,8 +10,9 @@ under a name with the matching `register_*`; a spec.PartSpec(kind=name, params=.
   Norm            tensors(); bind(); forward(h_f32 [T, D], rows=None, add=None) -> [R, D] in the operand dtype;
                   with `add` (float32 [T, D], or [slices, T, D] partial sums to be added in order) it
                   first stores h += add (the block's residual add, fused)
-  PositionEncoding  fused_rope_theta() -> float | None (None: not the fused rotary);
-                  apply(x_f32 [T, H, hd], positions_i32 [T]) -> None, in place (used when not fused)
+  PositionEncoding  tensors(); bind(); rotary_table() -> (inv_freq, rotary_dim, neighbours) for a rotation of pairs
+                  of head dimensions (applied inside the q/k kernel), or None and then
+                  apply(x_f32 [T, H, hd], positions_i32 [T]) -> None, in place
   Mixer           tensors(); bind(); cache_request() -> CacheRequest | None; state_shape() -> tuple | None;
                   forward(xn [T, D], ctx: StepContext, cache: LayerCache | None, state: Tensor | None, out_f32 [T, D])
                   adds its result into `out` and returns None, or leaves `out` alone and returns the
@@ -97,6 +98,27 @@ class WeightedRows:
         ops.combine(self.y, self.pair_row, self.weights, h)
 
 
+class Tap:
+    """A debugging aid: a part that is given a Tap copies small per-row results of every forward
+    into it (the routed experts: each row's chosen experts and its router logits), one static
+    device buffer per name and executed position, so that the copies are part of a recorded CUDA
+    graph and a replayed step fills the same buffers.  Off unless a caller sets it; every copy
+    costs a launch."""
+
+    def __init__(self, capacity_rows: int):
+        self.capacity = int(capacity_rows)
+        self.buffers: Dict[Tuple[str, int], torch.Tensor] = {}
+
+    def record(self, what: str, position: int, rows: torch.Tensor) -> None:
+        n = rows.shape[0]
+        if n > self.capacity:
+            raise ValueError(f"tap: a step of {n} rows exceeds the tap's {self.capacity}")
+        buf = self.buffers.get((what, position))
+        if buf is None:
+            buf = self.buffers[(what, position)] = torch.zeros((self.capacity, *rows.shape[1:]), dtype=rows.dtype, device=rows.device)
+        buf[:n].copy_(rows)
+
+
 class Norm(Part):
     fuses_weighted_rows = False           # forward(..., add=WeightedRows) is understood
 
@@ -107,10 +129,16 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    def fused_rope_theta(self) -> Optional[float]:
+    is_identity = False                   # True: q and k stay as they are
+
+    def rotary_table(self):
+        """(inv_freq float32 [rotary_dim / 2] on the device, rotary_dim, neighbours) of an encoding
+        that is a rotation of pairs of head dimensions by position * inv_freq[pair]: the kernel
+        that prepares q and k applies it.  None: not such a rotation; `apply` is called instead."""
         return None
 
     def apply(self, x: torch.Tensor, positions: torch.Tensor) -> None:
+        """In place on FP32 x [T, heads, head_dim] (q, then k) at int32 positions [T]."""
         raise NotImplementedError
 
 

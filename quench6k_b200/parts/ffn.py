@@ -50,6 +50,8 @@ class RoutedExperts(FeedForward):
         self.D, self.E, self.k, self.I = hidden_size, num_experts, top_k, intermediate_size
         self.scoring, self.renorm = scoring, bool(renormalize)
         self.shared = DenseSwiGLU(hidden_size, shared_intermediate_size) if shared_intermediate_size > 0 else None
+        self.routing_tap = None               # a parts.base.Tap: every forward records each row's chosen experts [T, k]
+                                              # ("experts") and its router logits [T, E] ("router_logits") there
 
     def tensors(self):
         E, I, D = self.E, self.I, self.D
@@ -70,6 +72,15 @@ class RoutedExperts(FeedForward):
 
     defers_add = True
 
+    def _tap(self, ctx, sel_e, logits):
+        if logits.dim() == 3:                 # split-K slices of the router product: summed in order, as the routing kernel sums them
+            total = logits[0].clone()
+            for s in range(1, logits.shape[0]):
+                total += logits[s]
+            logits = total
+        self.routing_tap.record("experts", ctx.position, sel_e)
+        self.routing_tap.record("router_logits", ctx.position, logits)
+
     def forward(self, xn, ctx, out, defer=False):
         """Adds the experts' weighted results into `out`; with defer=True and no shared expert it
         returns them unsummed (WeightedRows) for the next norm to add."""
@@ -81,7 +92,9 @@ class RoutedExperts(FeedForward):
                 and self.I % 8 == 0):
             # a decode step: router and top-k in one launch, then one weight tile stream per
             # (token, slot) pair straight from the selection, no permutation and no gather
-            sel_e, sel_w, order = ops.router_small(xn, self.w_router, self.k, self.scoring, self.renorm)
+            sel_e, sel_w, order, logits = ops.router_small(xn, self.w_router, self.k, self.scoring, self.renorm, with_logits=True)
+            if self.routing_tap is not None:
+                self._tap(ctx, sel_e, logits)
             act = ops.gemm_tc_pairs(xn, self.w_gate, sel_e, self.k, w2=self.w_up, order=order)      # [pairs, I]
             y = ops.gemm_tc_pairs(act, self.w_down, sel_e, 1, order=order)                           # FP32 [pairs, D]
             if defer:
@@ -92,6 +105,8 @@ class RoutedExperts(FeedForward):
             return None
         logits = linear.matmul(xn, self.w_router, rt, partials_ok=True)    # FP32 [T, E], or split-K slices of it that route() sums
         sel_e, sel_w = ops.route(logits, self.k, self.scoring, self.renorm)
+        if self.routing_tap is not None:
+            self._tap(ctx, sel_e, logits)
         plan = linear.group_plan(xn, self.w_gate, sel_e, rt)             # permutation by expert, row tiles, gathered rows
         act = linear.grouped_swiglu(xn, plan, self.w_gate, self.w_up, rt)                         # [pairs, I]
         y = linear.grouped_matmul(act, plan, self.w_down, rt)                                     # FP32 [pairs, D]

@@ -9,20 +9,27 @@ import plain_flint
 import tiny_configs
 
 
-def make_model_folder(folder, name, seed=0):
-    """Write config.json + model.safetensors for tiny config `name`; returns (config dict, weights dict)."""
+def make_model_folder(folder, name, seed=0, init_std=None):
+    """Write config.json + model.safetensors for tiny config `name`; returns (config dict, weights dict).
+    The weights handed back are the generated tensors themselves, not what a reader makes of the
+    file, so that the plain implementation does not depend on the product's reader agreeing with
+    its writer.  init_std: standard deviation of the matrices instead of the default 0.02 (larger
+    values make the layers outweigh the embedding, so that greedy continuations vary)."""
     from quench6k_b200.config import FlintConfig
     from quench6k_b200.models.decoder import DecoderModel
     from quench6k_b200.models.flint import build_spec
-    from quench6k_b200.weights import index_folder, write_model_folder
+    from quench6k_b200.weights.random_init import make_tensor
+    from quench6k_b200.weights.safetensors_io import write_safetensors
 
-    cfg_d = tiny_configs.get(name)
+    cfg_d = tiny_configs.get(name) if isinstance(name, str) else name
     cfg = FlintConfig.from_dict(cfg_d)
-    spec = build_spec(cfg, norm_init=tiny_configs.NORM_INIT[name])
+    norm_init = tiny_configs.NORM_INIT[name] if isinstance(name, str) else "random"
+    spec = build_spec(cfg, norm_init=norm_init)
     model = DecoderModel(spec)
-    write_model_folder(folder, cfg, model.tensors(), seed, spec.init_std)
-    idx = index_folder(folder)
-    weights = {n: f.read(n) for n, (f, e) in idx.items()}
+    weights = {t.name: make_tensor(t, seed, init_std or spec.init_std) for t in model.tensors()}
+    os.makedirs(folder, exist_ok=True)
+    cfg.save(folder)
+    write_safetensors(os.path.join(folder, "model.safetensors"), weights.items())
     with open(os.path.join(folder, "config.json")) as f:
         cfg_d = json.load(f)
     return cfg_d, weights
@@ -120,6 +127,33 @@ def schedule_mixed(requests, page, seed=0, max_live=4):
     return steps, peak
 
 
+def schedule_wide_decode(requests, page, per_step=6):
+    """Many requests live at once: the prompts (all but each request's last 6 to 10 tokens) come in
+    steps of `per_step` whole portions, then every live request decodes one token per step until
+    its tokens end, so the batch shrinks."""
+    steps, n = [], 0
+    items = list(requests.items())
+    head = {rid: len(t) - (6 + i % 5) for i, (rid, t) in enumerate(items)}
+    for i in range(0, len(items), per_step):
+        entries = [{"id": rid, "tokens": t[:head[rid]], "want": list(range(head[rid]))} for rid, t in items[i:i + per_step]]
+        steps.append({"step": n, "entries": entries, "end": []})
+        n += 1
+    at = dict(head)
+    while at:
+        entries, end = [], []
+        for rid, t in items:
+            if rid not in at:
+                continue
+            entries.append({"id": rid, "tokens": t[at[rid]:at[rid] + 1], "want": [0]})
+            at[rid] += 1
+            if at[rid] == len(t):
+                end.append(rid)
+                del at[rid]
+        steps.append({"step": n, "entries": entries, "end": end})
+        n += 1
+    return steps, sum(_ceil64(len(t), page) for t in requests.values())
+
+
 def collect(requests, steps, outputs):
     """Per-request logits [len, V] assembled from the per-step outputs (dict step -> tensor [wanted, V])."""
     got = {rid: [None] * len(t) for rid, t in requests.items()}
@@ -135,75 +169,146 @@ def collect(requests, steps, outputs):
     return {rid: torch.stack(rows) for rid, rows in got.items()}
 
 
-def run_replay(folder, dtype, steps, max_tokens, page_size=None):
-    """Replay `steps` through the engine's ModelRunner in this process; returns step -> logits (CPU)."""
+def collect_wanted(rid, steps, outputs):
+    """The logits of one request at the places the steps asked for, in the steps' order: [wanted, V]."""
+    rows = []
+    for msg in steps:
+        out = outputs.get(msg["step"])
+        row = 0
+        for e in msg["entries"]:
+            n = len(e["want"])
+            if e["id"] == rid and n:
+                rows.append(out[row:row + n])
+            row += n
+    return torch.cat(rows)
+
+
+def run_replay(folder, dtype, steps, max_tokens, page_size=None, max_requests=8, runner=None, tap=False):
+    """Replay `steps` through the engine's ModelRunner in this process; returns (step -> logits on
+    the CPU, runner).  tap: also record which experts every routed layer chose for every row; the
+    runner then carries `routing`: request -> {"experts": {executed position: int64 [tokens, k]},
+    "router_logits": {executed position: float32 [tokens, E]}}."""
     from quench6k_b200.config.registry import load_config
     from quench6k_b200.engine import ModelRunner
     from quench6k_b200.engine.replay import pool_pages, replay
 
-    _, cfg = load_config(folder)
-    page = page_size or cfg.kv_page_size or 16
-    runner = ModelRunner.from_folder(folder, dtype=dtype, page_size=page, num_pages=pool_pages(max_tokens, page), max_requests=8)
+    if runner is None:
+        _, cfg = load_config(folder)
+        page = page_size or cfg.kv_page_size or 16
+        runner = ModelRunner.from_folder(folder, dtype=dtype, page_size=page, num_pages=pool_pages(max_tokens, page),
+                                         max_requests=max_requests)
     outputs = {}
+    by_step = {s["step"]: s for s in steps}
+    routing = {}
+    the_tap = attach_routing_tap(runner, max(sum(len(e["tokens"]) for e in s["entries"]) for s in steps)) if tap else None
 
     def emit(step, logits):
         if logits is not None:
             outputs[step] = logits.detach().cpu()
+        if the_tap is not None:
+            row = 0
+            for e in by_step[step]["entries"]:
+                n = len(e["tokens"])
+                for (name, p), buf in the_tap.buffers.items():
+                    part = buf[row:row + n].cpu()
+                    routing.setdefault(e["id"], {}).setdefault(name, {}).setdefault(p, []).append(part.long() if name == "experts" else part)
+                row += n
 
     replay(runner, steps, emit)
     runner.manager.check()
     assert not runner.manager.requests, "requests left alive after the trace"
+    runner.routing = {rid: {name: {p: torch.cat(parts) for p, parts in per.items()} for name, per in names.items()}
+                      for rid, names in routing.items()}
     return outputs, runner
 
 
+def attach_routing_tap(runner, capacity_rows):
+    """Give every routed feed-forward of the runner's model one Tap (the debugging hook of
+    parts.base) and return it."""
+    from quench6k_b200.parts.base import Tap
+    tap = Tap(capacity_rows)
+    for b in runner.model.blocks:
+        if hasattr(b.ffn, "routing_tap"):
+            b.ffn.routing_tap = tap
+    return tap
+
+
 # Tolerances, relative to the largest reference logit of the sequence.  float32: the engine against
-# float64 arithmetic (measured at the first pass: 7e-7).  bfloat16: the engine against the plain implementation rounding to bfloat16
-# at the same places (measured at the first pass: at most 0.6 percent at positions with decisive
-# routing).  They were set when the first kernels passed and are not to be widened.
+# float64 arithmetic (measured at the first pass: 7e-7).  bfloat16: the engine against the plain
+# implementation rounding to bfloat16 at the same places (measured at the first pass: at most 0.6
+# percent).  They were set when the first kernels passed and are not to be widened.
 #
 # A mixture of experts is discontinuous: where the router's last chosen and first rejected logits
-# nearly tie, rounding may choose the other expert, and the logits of that position move by far
-# more than rounding; its changed keys and values then disturb the positions that attend to it
-# (measured: for a sliding window's length), where a second near-tie may flip in turn.  In bfloat16
-# a position may therefore exceed the tolerance only if a routing flip explains it: its own routing
-# margin in the plain implementation (gap of the two router logits over the rms of the token's
-# router logits, smallest over the layers) is below FRAGILE, or a position that exceeded the
-# tolerance lies within `reach` positions before it.  Such positions must still stay within
-# BF16_FLIPPED_TOL.  Every other position, and every position in float32, must meet TOL.
+# nearly tie, bfloat16 rounding may choose the other expert, and the logits of that position (and
+# of those that attend to it) move by far more than rounding.  So in bfloat16 the engine reports
+# its router logits and the experts it chose (parts.base.Tap), and the plain implementation is run
+# on those experts (forced_routing).  Then every position must meet TOL, with no exception, and
+# the routing itself is checked in two parts: the engine's router logits are held to the same TOL
+# against the plain implementation's (relative to the layer's largest router logit), and the
+# engine's experts must be the k best of its own router logits.  The float32 runs are compared the
+# same way with their own TOL: among thousands of tokens and hundreds of experts even float32
+# rounding meets a tie now and then.
 TOL = {"float32": 5e-6, "bfloat16": 1e-2}
-FRAGILE = 1e-2
-BF16_FLIPPED_TOL = 0.5
 
 
-def assert_close(got, ref, dtype, what, reach=16, fragile=FRAGILE):
-    """ref: (logits, margins) from plain_logits, or a plain tensor.  reach: how far a flipped
-    position's keys are seen (the configuration's sliding window, at least 8).  fragile: the
-    routing margin below which a flip may explain a bfloat16 difference (a caller with a wider
-    model states its own and why; TOL and BF16_FLIPPED_TOL are the same for everyone)."""
-    want, margins = ref if isinstance(ref, tuple) else (ref, None)
+def assert_close(got, want, dtype, what):
+    """Every position of `got` within TOL[dtype] of `want`, relative to the largest logit of `want`."""
+    if isinstance(want, tuple):
+        want = want[0]
     want = want.to(torch.float64)
-    got = got.to(torch.float64)
+    got = got.to(device=want.device, dtype=torch.float64)
+    assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} against {tuple(want.shape)}"
     assert torch.isfinite(got).all(), f"{what}: the engine produced non-finite logits"
     scale = float(want.abs().max())
-    per_pos = ((got - want).abs().reshape(want.shape[0], -1).max(dim=-1).values / scale).tolist()
-    tol = TOL[dtype]
-    explained = 0
-    over = [False] * len(per_pos)
-    for p, err in enumerate(per_pos):
-        if err <= tol:
-            continue
-        over[p] = True
-        ok = False
-        if dtype == "bfloat16" and margins is not None and err <= BF16_FLIPPED_TOL:
-            ok = float(margins[p]) < fragile or any(over[max(0, p - reach):p])
-        if not ok:
-            raise AssertionError(f"{what}: error {err:.3e} of scale {scale:.3f} at position {p} exceeds {tol:.1e} "
-                                 f"(routing margin {float(margins[p]) if margins is not None else float('nan'):.4f}; "
-                                 f"{explained} earlier positions were explained by routing flips)")
-        explained += 1
-    if explained > 0.2 * len(per_pos):
-        raise AssertionError(f"{what}: {explained} of {len(per_pos)} positions differ by routing flips: too many to be rounding")
-    return max(per_pos)
+    per_pos = (got - want).abs().reshape(want.shape[0], -1).max(dim=-1).values / scale
+    worst = int(per_pos.argmax())
+    assert float(per_pos[worst]) <= TOL[dtype], (f"{what}: error {float(per_pos[worst]):.3e} of scale {scale:.3f} at position {worst} "
+                                                 f"exceeds {TOL[dtype]:.1e} ({int((per_pos > TOL[dtype]).sum())} of {len(per_pos)} positions do)")
+    return float(per_pos[worst])
+
+
+def assert_matches_plain(cfg_d, weights, tokens, got, dtype, what, routing=None, positions=None, device=None):
+    """The engine's logits of one request against the plain implementation.  `routing`
+    ({"experts" | "router_logits": {executed position: [tokens, ...]}}, from run_replay(tap=True);
+    bfloat16 needs it, float32 may do without) is checked and forced on the plain implementation.  positions: the positions `got` holds
+    (default: all).  Returns (worst error, number of positions at which the plain implementation's
+    own router would have chosen another set of experts)."""
+    flipped = 0
+    if dtype == "bfloat16" or routing is not None:
+        assert routing is not None or not any_routed(cfg_d), f"{what}: a bfloat16 comparison needs the engine's routing"
+        experts = routing["experts"] if routing else {}
+        want, routers = plain_flint.forward(cfg_d, weights, tokens, emulate_bf16=dtype == "bfloat16", forced_routing=experts,
+                                            logit_positions=positions, device=device)
+        differs = torch.zeros(len(tokens), dtype=torch.bool)
+        for p, (z_plain, own) in routers.items():
+            z = routing["router_logits"][p].to(device=z_plain.device, dtype=torch.float64)
+            chosen = experts[p].to(z_plain.device)
+            scale = float(z_plain.abs().max())
+            err = (z - z_plain).abs().max(dim=-1).values / scale
+            # 32-bit rotation angles carry a rounding of pos * 2^-24 rad, which the scores and everything after them inherit:
+            # in float32, where nothing else is as large, the allowance for this intermediate result grows with the position
+            allowed = TOL[dtype] * (1.0 + torch.arange(len(tokens), device=err.device, dtype=torch.float64) / 1024.0 if dtype == "float32" else 1.0)
+            over = err > allowed
+            assert not bool(over.any()), (f"{what}: router logits of executed layer {p} differ by {float(err[over].max()):.3e} of their "
+                                          f"scale {scale:.3f} at position {int(over.nonzero()[0])} ({int(over.sum())} positions beyond the tolerance)")
+            # the k best of the engine's own logits: no chosen logit below an unchosen one (beyond FP32 rounding)
+            picked = torch.zeros_like(z, dtype=torch.bool).scatter_(1, chosen, True)
+            assert int(picked.sum(-1).min()) == chosen.shape[1], f"{what}: layer {p} chose an expert twice"
+            lowest_in = z.masked_fill(~picked, float("inf")).min(-1).values
+            highest_out = z.masked_fill(picked, float("-inf")).max(-1).values
+            bad = lowest_in < highest_out - 1e-6 * scale
+            assert not bool(bad.any()), f"{what}: layer {p}, position {int(bad.nonzero()[0])}: the chosen experts are not the best of the engine's own router logits"
+            differs |= (chosen.sort(-1).values != own.sort(-1).values).any(-1).cpu()
+        flipped = int(differs.sum())
+        if dtype == "float32":
+            assert flipped <= 1 + len(tokens) // 500, f"{what}: {flipped} positions routed differently: more than float32 rounding meets ties"
+    else:
+        want = plain_flint.forward(cfg_d, weights, tokens, logit_positions=positions, device=device)
+    return assert_close(got, want, dtype, what), flipped
+
+
+def any_routed(cfg_d):
+    return cfg_d.get("first_k_dense_replace", 0) < cfg_d["num_hidden_layers"]
 
 
 def make_context(q_lens, pos_starts, tables, n_groups=1, device="cuda"):

@@ -6,7 +6,8 @@ lkarlslund/quench6k).  The reference's own Flint code could not be run here: its
 sizes fixed at compile time, and its Python oracle (tools/ref/ref.py) covers another architecture
 and hard-codes a CUDA device.  So there is no golden output of the reference itself.
 
-Whole sequences, no cache, one function per part, torch on the CPU, float64 by default.  It shares
+Whole sequences, no cache, one function per part, plain tensor arithmetic in float64 by default,
+on the CPU unless a test with large layers asks for the device its weights are on.  It shares
 no code with quench6k_b200: it reads config.json as a plain dict and the weights as a dict of
 tensors by name.
 
@@ -43,12 +44,19 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
 def rope_neox(x: torch.Tensor, positions: torch.Tensor, theta: float) -> torch.Tensor:
     """Rotate-half RoPE over the full head: i = d mod hd/2, inv = theta^(-2i/hd), a = pos * inv;
     d < hd/2: x[d] cos a - x[d+hd/2] sin a; else x[d] cos a + x[d-hd/2] sin a.
-    x: [T, H, hd].  crates/cuda/kernels/flint.cu:141-149"""
+    x: [T, H, hd].  crates/cuda/kernels/flint.cu:141-149
+
+    The angle is a 32-bit quantity there (inv and the product pos * inv are floats) and so it is
+    here: inv is rounded to float32, and so is its product with the position (an angle of
+    thousands of radians carries a rounding of 1e-4 rad that way, which is part of what is
+    computed); the cosine and sine of that angle and the rotation are in x's precision.  (The
+    reference gets inv from exp2f(-(2i/hd) * log2(theta)) on the device, which differs from the
+    rounded exact value by an ulp in half of the dimensions; no output of it exists to compare with.)"""
     hd = x.shape[-1]
     half = hd // 2
-    i = torch.arange(half, dtype=x.dtype)
-    inv = theta ** (-(2.0 * i) / hd)
-    a = positions.to(x.dtype)[:, None] * inv[None, :]          # [T, half]
+    i = torch.arange(half, dtype=torch.float64, device=x.device)
+    inv = (theta ** (-(2.0 * i) / hd)).to(torch.float32)
+    a = (positions.to(torch.float32)[:, None] * inv[None, :]).to(x.dtype)       # [T, half], a float32 product
     cos, sin = torch.cos(a)[:, None, :], torch.sin(a)[:, None, :]
     lo, hi = x[..., :half], x[..., half:]
     return torch.cat([lo * cos - hi * sin, hi * cos + lo * sin], dim=-1)
@@ -65,7 +73,7 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: Optiona
     T, Hq, hd = q.shape
     Hkv = k.shape[1]
     G = Hq // Hkv
-    pos = torch.arange(T)
+    pos = torch.arange(T, device=q.device)
     visible = pos[None, :] <= pos[:, None]
     if window is not None:
         visible &= pos[None, :] > pos[:, None] - window
@@ -88,11 +96,16 @@ def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, window: Optiona
 _last_route_margin = None      # set by route(): per token, (k-th logit - (k+1)-th logit) / rms of the token's router logits
 
 
-def route(logits: torch.Tensor, scoring: str, top_k: int, renorm: bool):
+_last_router = None            # set by route(): (the router logits [T, E], this router's own choice [T, k])
+
+
+def route(logits: torch.Tensor, scoring: str, top_k: int, renorm: bool, forced: Optional[torch.Tensor] = None):
     """Router scores, the top-k experts (ties -> lower expert index) and their weights.
     sigmoid: score = 1/(1+exp(-z)), weights = score / (sum of chosen + 1e-20)
     (crates/cuda/kernels/flint.cu:829-864).  softmax: softmax over all experts, top-k, divided by
-    the chosen sum (crates/cuda/kernels/moe.cu:19-71).  Without renormalisation the scores stand."""
+    the chosen sum (crates/cuda/kernels/moe.cu:19-71).  Without renormalisation the scores stand.
+    forced [T, k]: the experts to use instead of the router's own choice, in this slot order; the
+    weights are still this function's scores of those experts."""
     if scoring == "sigmoid":
         score = 1.0 / (1.0 + torch.exp(-logits))
     elif scoring == "softmax":
@@ -101,14 +114,17 @@ def route(logits: torch.Tensor, scoring: str, top_k: int, renorm: bool):
         raise ValueError(scoring)
     ranked = torch.sort(score, dim=-1, descending=True, stable=True)
     order = ranked.indices[:, :top_k]
+    global _last_route_margin, _last_router
+    _last_router = (logits, order)
+    if forced is not None:
+        order = forced.to(device=order.device, dtype=order.dtype)
     w = torch.gather(score, 1, order)
-    global _last_route_margin
     if score.shape[-1] > top_k:
         # both scorings are monotone in the logit, so the choice is the order of the logits
         z = torch.sort(logits, dim=-1, descending=True).values
         _last_route_margin = (z[:, top_k - 1] - z[:, top_k]) / logits.pow(2).mean(dim=-1).sqrt()
     else:
-        _last_route_margin = torch.full((score.shape[0],), float("inf"), dtype=score.dtype)
+        _last_route_margin = torch.full((score.shape[0],), float("inf"), dtype=score.dtype, device=score.device)
     if renorm:
         s = w.sum(dim=-1, keepdim=True)
         w = w / (s + 1e-20) if scoring == "sigmoid" else w / s
@@ -128,15 +144,16 @@ def swiglu_mlp(x: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor, wd: torch.Te
 
 
 def moe(x: torch.Tensor, router_w: torch.Tensor, wg: torch.Tensor, wu: torch.Tensor, wd: torch.Tensor,
-        scoring: str, top_k: int, renorm: bool, emulate: bool) -> torch.Tensor:
+        scoring: str, top_k: int, renorm: bool, emulate: bool, forced: Optional[torch.Tensor] = None) -> torch.Tensor:
     """sum over the chosen experts, in slot order, of w_r * expert_r(x).
     crates/cuda/kernels/flint.cu:1228-1239 (combine), :829-868 (route).  wg, wu: [E, I, D], wd: [E, D, I]."""
-    sel, w = route(x @ router_w.T, scoring, top_k, renorm)
+    sel, w = route(x @ router_w.T, scoring, top_k, renorm, forced)
     out = torch.zeros_like(x)
+    chosen = sel.tolist()
     for t in range(x.shape[0]):
         acc = torch.zeros_like(x[t])
         for r in range(top_k):
-            e = int(sel[t, r])
+            e = chosen[t][r]
             acc = acc + w[t, r] * swiglu_mlp(x[t:t + 1], wg[e], wu[e], wd[e], emulate)[0]
         out[t] = acc
     return out
@@ -144,38 +161,50 @@ def moe(x: torch.Tensor, router_w: torch.Tensor, wg: torch.Tensor, wu: torch.Ten
 
 # --------------------------------------------------------------------------- whole model
 def forward(cfg: Dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtype=torch.float64,
-            emulate_bf16: bool = False, return_margins: bool = False):
+            emulate_bf16: bool = False, return_margins: bool = False, forced_routing: Optional[Dict[int, torch.Tensor]] = None,
+            logit_positions: Optional[List[int]] = None, device=None):
     """Logits [T, V] of one whole sequence (with return_margins also, per position, the smallest
     gap over the MoE layers between the last chosen and the first rejected router logit, relative to
     the rms of the token's router logits:
     where it is tiny, rounding may legitimately choose another expert); the layer loop of crates/engine/src/flint.rs:775-1117
     (embed, per layer: norm, q/k/v, qk-norm, RoPE, attention, o-proj + residual, norm, router +
-    experts (+ shared expert) or dense MLP + residual; final norm and LM head)."""
-    W = {k: v.to(dtype) for k, v in weights.items()}
+    experts (+ shared expert) or dense MLP + residual; final norm and LM head).
+
+    forced_routing: executed position -> experts [T, k] to use there instead of the router's own
+    choice (another implementation's selection, so that two implementations can be compared on the
+    same experts); the second result is then a dict: executed position -> (this implementation's
+    router logits [T, E], its own choice [T, k]) for the routed layers.
+    logit_positions: only these positions' logits are computed ([len, V]).  device: where the
+    arithmetic runs (default: where the weights are); weights are converted as they are used, so
+    that a large model is never held twice."""
+    dev = torch.device(device) if device is not None else next(iter(weights.values())).device
+    W = lambda name: weights[name].to(device=dev, dtype=dtype)
     em = emulate_bf16
     L = cfg["num_hidden_layers"]
     Hq, Hkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     eps = cfg["rms_norm_eps"]
+    qk_eps = cfg.get("qk_norm_eps") or eps
     order = cfg.get("layer_order") or list(range(L))
     kv_source = cfg.get("kv_source") or [None] * len(order)
     sliding = cfg.get("sliding_window_pattern") or [False] * L
     roped = cfg.get("rope_pattern") or [True] * L
     T = len(tokens)
-    pos = torch.arange(T)
-    h = embed(torch.tensor(tokens), W["model.embed_tokens.weight"])
+    pos = torch.arange(T, device=dev)
+    h = embed(torch.tensor(tokens, device=dev), W("model.embed_tokens.weight"))
     kept = {}
-    margins = torch.full((T,), float("inf"), dtype=dtype)
+    margins = torch.full((T,), float("inf"), dtype=dtype, device=dev)
+    routers = {}
     for p, i in enumerate(order):
         pre = f"model.layers.{i}."
-        xn = _r(rmsnorm(h, W[pre + "input_layernorm.weight"], eps), em)
-        q = (xn @ W[pre + "self_attn.q_proj.weight"].T).view(T, Hq, hd)
+        xn = _r(rmsnorm(h, W(pre + "input_layernorm.weight"), eps), em)
+        q = (xn @ W(pre + "self_attn.q_proj.weight").T).view(T, Hq, hd)
         if kv_source[p] is None:
-            k = (xn @ W[pre + "self_attn.k_proj.weight"].T).view(T, Hkv, hd)
-            v = (xn @ W[pre + "self_attn.v_proj.weight"].T).view(T, Hkv, hd)
+            k = (xn @ W(pre + "self_attn.k_proj.weight").T).view(T, Hkv, hd)
+            v = (xn @ W(pre + "self_attn.v_proj.weight").T).view(T, Hkv, hd)
         if cfg.get("qk_norm"):
-            q = rmsnorm(q, W[pre + "self_attn.q_norm.weight"], eps)
+            q = rmsnorm(q, W(pre + "self_attn.q_norm.weight"), qk_eps)
             if kv_source[p] is None:
-                k = rmsnorm(k, W[pre + "self_attn.k_norm.weight"], eps)
+                k = rmsnorm(k, W(pre + "self_attn.k_norm.weight"), qk_eps)
         if roped[i]:
             q = rope_neox(q, pos, cfg["rope_theta"])
             if kv_source[p] is None:
@@ -187,27 +216,33 @@ def forward(cfg: Dict, weights: Dict[str, torch.Tensor], tokens: List[int], dtyp
         else:
             k, v = kept[kv_source[p]]
         a = attention(q, k, v, cfg["sliding_window"] if sliding[i] else None,
-                      W[pre + "self_attn.sinks"] if cfg.get("attn_sinks") else None, em)
+                      W(pre + "self_attn.sinks") if cfg.get("attn_sinks") else None, em)
         a = _r(a, em).reshape(T, Hq * hd)
-        h = h + a @ W[pre + "self_attn.o_proj.weight"].T
-        xn = _r(rmsnorm(h, W[pre + "post_attention_layernorm.weight"], eps), em)
+        h = h + a @ W(pre + "self_attn.o_proj.weight").T
+        xn = _r(rmsnorm(h, W(pre + "post_attention_layernorm.weight"), eps), em)
         if i < cfg.get("first_k_dense_replace", 0):
-            f = swiglu_mlp(xn, W[pre + "mlp.gate_proj.weight"], W[pre + "mlp.up_proj.weight"],
-                           W[pre + "mlp.down_proj.weight"], em)
+            f = swiglu_mlp(xn, W(pre + "mlp.gate_proj.weight"), W(pre + "mlp.up_proj.weight"),
+                           W(pre + "mlp.down_proj.weight"), em)
         else:
-            f = moe(xn, W[pre + "mlp.gate.weight"], W[pre + "mlp.experts.gate_proj.weight"],
-                    W[pre + "mlp.experts.up_proj.weight"], W[pre + "mlp.experts.down_proj.weight"],
+            forced = forced_routing.get(p) if forced_routing is not None else None
+            f = moe(xn, W(pre + "mlp.gate.weight"), W(pre + "mlp.experts.gate_proj.weight"),
+                    W(pre + "mlp.experts.up_proj.weight"), W(pre + "mlp.experts.down_proj.weight"),
                     cfg.get("scoring_func", "softmax"), cfg["num_experts_per_tok"],
-                    cfg.get("norm_topk_prob", True), em)
+                    cfg.get("norm_topk_prob", True), em, forced)
             margins = torch.minimum(margins, _last_route_margin)
+            routers[p] = _last_router
             if cfg.get("n_shared_experts", 0) > 0:
-                f = f + swiglu_mlp(xn, W[pre + "mlp.shared_experts.gate_proj.weight"],
-                                   W[pre + "mlp.shared_experts.up_proj.weight"],
-                                   W[pre + "mlp.shared_experts.down_proj.weight"], em)
+                f = f + swiglu_mlp(xn, W(pre + "mlp.shared_experts.gate_proj.weight"),
+                                   W(pre + "mlp.shared_experts.up_proj.weight"),
+                                   W(pre + "mlp.shared_experts.down_proj.weight"), em)
         h = h + f
-    xn = _r(rmsnorm(h, W["model.norm.weight"], eps), em)
-    head = W["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings") else W["lm_head.weight"]
+    if logit_positions is not None:
+        h = h[torch.tensor(list(logit_positions), dtype=torch.long, device=dev)]
+    xn = _r(rmsnorm(h, W("model.norm.weight"), eps), em)
+    head = W("model.embed_tokens.weight") if cfg.get("tie_word_embeddings") else W("lm_head.weight")
     logits = xn @ head.T
+    if forced_routing is not None:
+        return logits, routers
     return (logits, margins) if return_margins else logits
 
 

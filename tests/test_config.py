@@ -43,7 +43,11 @@ def test_tiny_b_differs_in_every_size_and_option():
 
 @pytest.mark.parametrize("change, text", [
     ({"num_attention_heads": 5}, "multiple"),
-    ({"head_dim": 15}, "even"),
+    ({"head_dim": 15}, "multiples of 16"),
+    ({"head_dim": 24}, "multiples of 16"),
+    ({"head_dim": 272}, "multiples of 16"),
+    ({"n_shared_experts": 2, "shared_expert_intermediate_size": 32}, "one ungated shared expert"),
+    ({"qk_norm_eps": 0.0}, "qk_norm_eps"),
     ({"num_experts_per_tok": 9}, "exceeds"),
     ({"scoring_func": "tanh"}, "scoring_func"),
     ({"sliding_window_pattern": [True]}, "entries"),

@@ -200,12 +200,36 @@ def test_attention_generic(dtype, Hq, Hkv, hd, ps, window, sinks):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("Hq,Hkv,hd,ps,norm,theta", [(4, 2, 16, 4, False, 10000.0), (6, 3, 48, 8, True, 500000.0),
-                                                      (2, 1, 128, 16, True, None), (32, 4, 128, 16, True, 1e6),
-                                                      (5, 5, 64, 8, False, 10000.0), (3, 1, 256, 16, True, 777.0)])
-def test_qk_prep(dtype, Hq, Hkv, hd, ps, norm, theta):
+@pytest.mark.parametrize("Hq,Hkv,hd,ps,norm,theta,rd,neighbours", [
+    (4, 2, 16, 4, False, 10000.0, 0, False), (6, 3, 48, 8, True, 500000.0, 0, False), (2, 1, 128, 16, True, None, 0, False),
+    (32, 4, 128, 16, True, 1e6, 0, False), (5, 5, 64, 8, False, 10000.0, 0, False), (3, 1, 256, 16, True, 777.0, 0, False),
+    # partial rotary (the warp kernel takes multiples of 64, the block kernel the rest) and pairs of neighbours
+    (8, 2, 128, 16, True, 1e4, 64, False), (4, 2, 128, 16, False, 1e4, 96, False), (6, 3, 48, 8, True, 5e4, 16, False),
+    (8, 2, 128, 16, True, 1e4, 0, True), (4, 1, 64, 8, True, 1e4, 20, True), (6, 3, 48, 8, False, 5e4, 32, True)])
+def test_qk_prep(dtype, Hq, Hkv, hd, ps, norm, theta, rd, neighbours):
     from quench6k_b200 import ops
     T, eps = 21, 1e-5
+    rd = rd or hd
+    rotary = None
+    if theta is not None:
+        inv = (theta ** (-(2.0 * torch.arange(rd // 2, dtype=torch.float64)) / rd)).float()
+        rotary = (inv.to(DEV), rd, neighbours)
+
+    def rotate(x, positions):
+        """Plain restatement for any rotary_dim and pairing (plain_flint.rope_neox is the full-head, halves case)."""
+        if rd == hd and not neighbours:
+            return P.rope_neox(x, positions, theta)
+        a = (positions.float()[:, None] * inv[None, :]).double()[:, None, :]
+        c, s = torch.cos(a), torch.sin(a)
+        out = x.clone()
+        if neighbours:
+            lo, hi = x[..., 0:rd:2], x[..., 1:rd:2]
+            out[..., 0:rd:2], out[..., 1:rd:2] = lo * c - hi * s, hi * c + lo * s
+        else:
+            lo, hi = x[..., :rd // 2], x[..., rd // 2:rd]
+            out[..., :rd // 2], out[..., rd // 2:rd] = lo * c - hi * s, hi * c + lo * s
+        return out
+
     qkv = _t(T, (Hq + 2 * Hkv) * hd, seed=5)
     qn, kn = (_t(hd, seed=6) + 1.0, _t(hd, seed=7) + 1.0) if norm else (None, None)
     pos0 = 37
@@ -215,7 +239,7 @@ def test_qk_prep(dtype, Hq, Hkv, hd, ps, norm, theta):
     table = torch.randperm(40)[:nb].to(torch.int32).view(1, nb).to(DEV)
     kp = torch.zeros(Hkv, 40, ps, hd, dtype=dtype, device=DEV)
     vp = torch.zeros_like(kp)
-    q = ops.qk_prep(qkv, Hq, Hkv, hd, qn, kn, eps, theta, pos, rot, table, ps, kp, vp, dtype)
+    q = ops.qk_prep(qkv, Hq, Hkv, hd, qn, kn, eps, rotary, pos, rot, table, ps, kp, vp, dtype)
     x = qkv.double().cpu()
     rq = x[:, :Hq * hd].view(T, Hq, hd)
     rk = x[:, Hq * hd:(Hq + Hkv) * hd].view(T, Hkv, hd)
@@ -223,7 +247,7 @@ def test_qk_prep(dtype, Hq, Hkv, hd, ps, norm, theta):
     if norm:
         rq, rk = P.rmsnorm(rq, qn.double().cpu(), eps), P.rmsnorm(rk, kn.double().cpu(), eps)
     if theta is not None:
-        rq, rk = P.rope_neox(rq, pos.cpu(), theta), P.rope_neox(rk, pos.cpu(), theta)
+        rq, rk = rotate(rq, pos.cpu()), rotate(rk, pos.cpu())
     tol = 2e-5 if dtype == torch.float32 else 1e-2
     assert (q.double().cpu() - rq).abs().max() <= tol * rq.abs().max()
     for t in range(T):
@@ -233,7 +257,7 @@ def test_qk_prep(dtype, Hq, Hkv, hd, ps, norm, theta):
         assert (vp[:, page, p % ps].double().cpu() - rv[t]).abs().max() <= tol * rv.abs().max()
     # read-only layers produce the same q and leave the pages alone
     k0 = kp.clone()
-    q2 = ops.qk_prep(qkv[:, :Hq * hd].contiguous(), Hq, Hkv, hd, qn, kn, eps, theta, pos, rot, None, ps, None, None, dtype)
+    q2 = ops.qk_prep(qkv[:, :Hq * hd].contiguous(), Hq, Hkv, hd, qn, kn, eps, rotary, pos, rot, None, ps, None, None, dtype)
     assert torch.equal(q2, q) and torch.equal(kp, k0)
 
 

@@ -269,10 +269,12 @@ def test_toy_mixer_with_state_registers_builds_and_steps(tmp_path):
 
 
 def test_toy_feed_forward_with_routing_and_toy_position_encoding(tmp_path):
-    """A feed-forward that routes each token to one of three linear maps, and a rotary encoding
-    that pairs neighbouring dimensions, are defined here, registered, chosen by a PartSpec and run
-    through the unchanged framework (model folder, loader, step function, cache), in one step and
-    cut into portions, against the same model written out in plain tensor code."""
+    """A feed-forward that routes each token to one of three linear maps, and two position
+    encodings (a rotary one that pairs neighbouring dimensions and turns only the first 8 of a
+    head's 16, which hands the q/k kernel its table, and one that is no rotation at all and
+    implements `apply`), are defined here, registered, chosen by a PartSpec and run through the
+    unchanged framework (model folder, loader, step function, cache), in one step and cut into
+    portions, against the same model written out in plain tensor code."""
     from dataclasses import dataclass
     from quench6k_b200.config import register_architecture
     from quench6k_b200.engine import ModelRunner, StepEntry
@@ -281,27 +283,41 @@ def test_toy_feed_forward_with_routing_and_toy_position_encoding(tmp_path):
     from quench6k_b200.spec import LayerSpec, ModelSpec, PartSpec, TensorSpec
     from quench6k_b200.weights import index_folder, write_model_folder
 
+    RD = 8
+
     def rotate_pairs(x, positions, theta):
-        """(x[2i], x[2i+1]) turned by position * theta^(-2i/hd)."""
-        hd = x.shape[-1]
-        inv = theta ** (-torch.arange(0, hd, 2, dtype=torch.float64, device=x.device) / hd)
-        ang = positions.double()[:, None] * inv
+        """(x[2i], x[2i+1]), i < RD/2, turned by position * theta^(-2i/RD); the other dimensions stay."""
+        inv = (theta ** (-torch.arange(0, RD, 2, dtype=torch.float64, device=x.device) / RD)).float()
+        ang = (positions.float()[:, None] * inv).double()
         c, s = torch.cos(ang)[:, None, :].to(x.dtype), torch.sin(ang)[:, None, :].to(x.dtype)
-        a, b = x[..., 0::2].clone(), x[..., 1::2].clone()
-        out = torch.empty_like(x)
-        out[..., 0::2], out[..., 1::2] = a * c - b * s, a * s + b * c
+        a, b = x[..., 0:RD:2].clone(), x[..., 1:RD:2].clone()
+        out = x.clone()
+        out[..., 0:RD:2], out[..., 1:RD:2] = a * c - b * s, a * s + b * c
         return out
+
+    def bump(x, positions):
+        """x[d] + 0.3 sin(position / (d + 1)): no rotation, so no table for the kernel."""
+        d = torch.arange(x.shape[-1], dtype=x.dtype, device=x.device)
+        return x + 0.3 * torch.sin(positions.to(x.dtype)[:, None, None] / (d + 1.0))
 
     @register_position_encoding("toy_pairwise_rotary")
     class PairwiseRotary(PositionEncoding):
         def __init__(self, head_dim, theta):
             self.hd, self.theta = head_dim, theta
 
-        def fused_rope_theta(self):
-            return None                       # not the rotation the fused kernel applies
+        def bind(self, get, rt):
+            self.table = (self.theta ** (-torch.arange(0, RD, 2, dtype=torch.float64) / RD)).float().to(rt.device)
+
+        def rotary_table(self):
+            return self.table, RD, True       # the q/k kernel turns neighbouring pairs of the first RD dimensions
+
+    @register_position_encoding("toy_bump")
+    class Bump(PositionEncoding):
+        def __init__(self, head_dim):
+            self.hd = head_dim
 
         def apply(self, x, positions):
-            x.copy_(rotate_pairs(x, positions, self.theta))
+            x.copy_(bump(x, positions))
 
     @register_feed_forward("toy_switch")
     class Switch(FeedForward):
@@ -345,10 +361,12 @@ def test_toy_feed_forward_with_routing_and_toy_position_encoding(tmp_path):
 
     def build(cfg):
         norm = PartSpec("rmsnorm", {"eps": eps, "init": "random"})
-        attn = PartSpec("attention", {"num_heads": Hq, "num_kv_heads": Hkv, "head_dim": hd, "eps": eps,
-                                      "pos": PartSpec("toy_pairwise_rotary", {"head_dim": hd, "theta": theta})})
-        layers = [LayerSpec("model.layers.0.", attn, PartSpec("toy_switch", {"n": 3}), norm)]
-        return ModelSpec(cfg.hidden_size, cfg.vocab_size, layers, order=[0], kv_source=[None], final_norm=norm, init_std=0.2)
+        attn = lambda pos: PartSpec("attention", {"num_heads": Hq, "num_kv_heads": Hkv, "head_dim": hd, "eps": eps, "pos": pos, "qk_norm": True,
+                                                  "norm_init": "random"})
+        layers = [LayerSpec("model.layers.0.", attn(PartSpec("toy_pairwise_rotary", {"head_dim": hd, "theta": theta})),
+                            PartSpec("toy_switch", {"n": 3}), norm),
+                  LayerSpec("model.layers.1.", attn(PartSpec("toy_bump", {"head_dim": hd})), PartSpec("toy_switch", {"n": 3}), norm)]
+        return ModelSpec(cfg.hidden_size, cfg.vocab_size, layers, order=[0, 1], kv_source=[None, None], final_norm=norm, init_std=0.2)
 
     register_architecture("ToySwitchLM", ToyConfig, build)
     cfg = ToyConfig(D, V, ["ToySwitchLM"])
@@ -359,20 +377,19 @@ def test_toy_feed_forward_with_routing_and_toy_position_encoding(tmp_path):
     toks = helpers.random_tokens(23, V, 5)
 
     # the same model in plain tensor code
-    L = "model.layers.0."
     h = P.embed(torch.tensor(toks), w["model.embed_tokens.weight"])
-    x = P.rmsnorm(h, w[L + "input_layernorm.weight"], eps)
     n = len(toks)
-    q = (x @ w[L + "self_attn.q_proj.weight"].T).view(n, Hq, hd)
-    k = (x @ w[L + "self_attn.k_proj.weight"].T).view(n, Hkv, hd)
-    v = (x @ w[L + "self_attn.v_proj.weight"].T).view(n, Hkv, hd)
-    q, k = rotate_pairs(q, torch.arange(n), theta), rotate_pairs(k, torch.arange(n), theta)
-    h = h + P.attention(q, k, v, None, None, False).reshape(n, Hq * hd) @ w[L + "self_attn.o_proj.weight"].T
-    x = P.rmsnorm(h, w[L + "post_attention_layernorm.weight"], eps)
-    p = torch.softmax(x @ w[L + "mlp.router.weight"].T, -1)
-    top, e = p.max(-1)
-    assert len(set(e.tolist())) > 1                        # the routing does choose different maps
-    h = h + top[:, None] * torch.einsum("tij,tj->ti", w[L + "mlp.maps.weight"][e], x)
+    for L, place in (("model.layers.0.", lambda x: rotate_pairs(x, torch.arange(n), theta)), ("model.layers.1.", lambda x: bump(x, torch.arange(n)))):
+        x = P.rmsnorm(h, w[L + "input_layernorm.weight"], eps)
+        q = P.rmsnorm((x @ w[L + "self_attn.q_proj.weight"].T).view(n, Hq, hd), w[L + "self_attn.q_norm.weight"], eps)
+        k = P.rmsnorm((x @ w[L + "self_attn.k_proj.weight"].T).view(n, Hkv, hd), w[L + "self_attn.k_norm.weight"], eps)
+        v = (x @ w[L + "self_attn.v_proj.weight"].T).view(n, Hkv, hd)
+        h = h + P.attention(place(q), place(k), v, None, None, False).reshape(n, Hq * hd) @ w[L + "self_attn.o_proj.weight"].T
+        x = P.rmsnorm(h, w[L + "post_attention_layernorm.weight"], eps)
+        p = torch.softmax(x @ w[L + "mlp.router.weight"].T, -1)
+        top, e = p.max(-1)
+        assert len(set(e.tolist())) > 1                        # the routing does choose different maps
+        h = h + top[:, None] * torch.einsum("tij,tj->ti", w[L + "mlp.maps.weight"][e], x)
     want = P.rmsnorm(h, w["model.norm.weight"], eps) @ w["lm_head.weight"].T
 
     runner.add_request("w")

@@ -1,6 +1,11 @@
 """Replay of the same requests under every way of cutting the work, in float32 and bfloat16,
 against the plain implementation: whole; most in one step and the last 32 tokens one by one;
-portions of changing size down to two tokens; mixed batches with so few pages that they are reused."""
+portions of changing size down to two tokens; mixed batches with so few pages that they are reused.
+
+A, B, C are the tiny configurations; D and E have head size 128 and widths at which the bfloat16
+path runs its tensor-core kernels (tests/tiny_configs.py).  In bfloat16 the engine's choice of
+router logits and experts are recorded, checked, and the experts forced on the plain implementation
+(tests/helpers.py says why), so every position is held to the tolerance."""
 import json
 import os
 import subprocess
@@ -14,30 +19,31 @@ import helpers
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [71, 130, 45, 96, 64, 33, 120, 58, 77], "B": [85, 140, 37, 101, 66, 50, 90, 125, 44],
-           "C": [90, 57, 129, 48, 75, 40, 110, 66, 83]}
+           "C": [90, 57, 129, 48, 75, 40, 110, 66, 83], "D": [71, 130, 45, 200, 64, 33, 160, 58, 77],
+           "E": [85, 140, 37, 101, 66, 210, 90, 125, 44]}
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D", "E"])
 def model(request, tmp_path_factory):
     name = request.param
     folder = str(tmp_path_factory.mktemp(f"tiny_{name}"))
     cfg, weights = helpers.make_model_folder(folder, name, seed=11)
     reqs = {f"r{i}": helpers.random_tokens(n, cfg["vocab_size"], 100 + i) for i, n in enumerate(LENGTHS[name])}
-    ref = {}
-    for emulate in (False, True):
-        ref[emulate] = {rid: helpers.plain_logits(cfg, weights, t, emulate) for rid, t in reqs.items()}
-    return {"name": name, "folder": folder, "cfg": cfg, "requests": reqs, "ref": ref}
+    return {"name": name, "folder": folder, "cfg": cfg, "weights": weights, "requests": reqs}
 
 
 def _check(model, dtype, steps, max_tokens, what):
-    outputs, runner = helpers.run_replay(model["folder"], dtype, steps, max_tokens)
+    """Replay the steps, compare every request's logits with the plain implementation."""
+    outputs, runner = helpers.run_replay(model["folder"], dtype, steps, max_tokens, tap=True)
     got = helpers.collect(model["requests"], steps, outputs)
-    ref = model["ref"][dtype == "bfloat16"]
-    worst = 0.0
-    reach = max(8, model["cfg"].get("sliding_window") or 0)
-    for rid in model["requests"]:
-        worst = max(worst, helpers.assert_close(got[rid], ref[rid], dtype, f"{model['name']} {dtype} {what} {rid}", reach))
-    print(f"{model['name']} {dtype} {what}: worst error {worst:.3e}")
+    worst, flipped = 0.0, 0
+    for rid, toks in model["requests"].items():
+        err, n = helpers.assert_matches_plain(model["cfg"], model["weights"], toks, got[rid], dtype, f"{model['name']} {dtype} {what} {rid}",
+                                              routing=runner.routing[rid])
+        worst, flipped = max(worst, err), flipped + n
+    print(f"{model['name']} {dtype} {what}: worst error {worst:.3e}, {flipped} positions routed at a near-tie")
+    from quench6k_b200 import ops
+    assert ops.tc_status() == 0
     return got, worst
 
 
@@ -74,8 +80,8 @@ def test_mixed_with_reused_pages(model, dtype):
 
 
 def test_cuts_agree_with_each_other_in_float32(model):
-    """Beyond the comparison with the plain implementation: the same position gives the same
-    logits however the work was cut (to rounding far below the tolerance)."""
+    """Beyond the comparison with the plain implementation: in the 32-bit path the same position
+    gives the same logits, bit for bit, however the work was cut."""
     whole, _ = _check(model, "float32", *helpers.schedule_whole(model["requests"]), "whole")
     page = model["cfg"]["kv_page_size"]
     for what, (steps, mt) in {"tail": helpers.schedule_tail(model["requests"]),
@@ -83,46 +89,56 @@ def test_cuts_agree_with_each_other_in_float32(model):
                               "mixed": helpers.schedule_mixed(model["requests"], page, seed=2)}.items():
         got, _ = _check(model, "float32", steps, mt, what)
         for rid in model["requests"]:
-            scale = whole[rid].abs().max().item()
-            err = (got[rid] - whole[rid]).abs().max().item() / scale
-            assert err < 2e-6, f"{what} {rid}: differs from the whole run by {err:.2e}"
+            same = torch.equal(got[rid], whole[rid])
+            err = (got[rid] - whole[rid]).abs().max().item() / whole[rid].abs().max().item()
+            assert same, f"{what} {rid}: differs from the whole run (by {err:.2e} of the largest logit)"
+
+
+def test_decode_batches_of_17_to_64(model):
+    """Decoding in batches of up to 37 requests (recorded at the next bucket of the runner's
+    list, with filler rows), which shrink as requests end: the grouped expert path above 16 rows."""
+    if model["name"] not in ("B", "D", "E"):
+        pytest.skip("one tiny and the two tensor-core configurations")
+    cfg = model["cfg"]
+    reqs = {f"w{i}": helpers.random_tokens(14 + (i * 7) % 23, cfg["vocab_size"], 900 + i) for i in range(37)}
+    steps, mt = helpers.schedule_wide_decode(reqs, cfg["kv_page_size"])
+    assert max(len(s["entries"]) for s in steps) == 37 and any(17 <= len(s["entries"]) < 37 for s in steps)
+    for dtype in ("float32", "bfloat16"):
+        outputs, runner = helpers.run_replay(model["folder"], dtype, steps, mt, max_requests=40, tap=True)
+        got = helpers.collect(reqs, steps, outputs)
+        for rid, toks in reqs.items():
+            helpers.assert_matches_plain(cfg, model["weights"], toks, got[rid], dtype, f"{model['name']} {dtype} wide decode {rid}",
+                                         routing=runner.routing[rid])
+        assert runner.graph_replays > 0
 
 
 def test_first_tokens_and_long_decoding(model):
     """The first tokens of a sequence (one token, two tokens) and decoding far past the prompt."""
+    if model["name"] == "E":
+        pytest.skip("D covers the head size; E's window is longer than the sequence")
     cfg, folder = model["cfg"], model["folder"]
     toks = helpers.random_tokens(230, cfg["vocab_size"], 77)
-    import plain_flint
-    from quench6k_b200.weights import index_folder
-    weights = {n: f.read(n) for n, (f, e) in index_folder(folder).items()}
     for dtype in ("float32", "bfloat16"):
-        ref = helpers.plain_logits(cfg, weights, toks, dtype == "bfloat16")
         steps = [{"step": 0, "entries": [{"id": "x", "tokens": toks[:1], "want": [0]}], "end": []},
                  {"step": 1, "entries": [{"id": "x", "tokens": toks[1:3], "want": [0, 1]}], "end": []}]
         for i in range(3, len(toks)):
             steps.append({"step": i - 1, "entries": [{"id": "x", "tokens": toks[i:i + 1], "want": [0]}],
                           "end": ["x"] if i == len(toks) - 1 else []})
-        outputs, _ = helpers.run_replay(folder, dtype, steps, len(toks))
+        outputs, runner = helpers.run_replay(folder, dtype, steps, len(toks), tap=True)
         got = helpers.collect({"x": toks}, steps, outputs)["x"]
-        helpers.assert_close(got, ref, dtype, f"{model['name']} {dtype} long decoding", max(8, cfg.get("sliding_window") or 0))
+        helpers.assert_matches_plain(cfg, model["weights"], toks, got, dtype, f"{model['name']} {dtype} long decoding",
+                                     routing=runner.routing.get("x"))
 
 
 @pytest.mark.parametrize("name", ["D", "E"])
 def test_tensor_core_kernels_inside_the_model(tmp_path, name):
     """Configurations with head size 128 and widths the tcgen05 products take (D; E has every option
     the other way: windows, groups of 8, sigmoid scores, a shared expert, a dense layer, tied
-    embeddings, pages of 32), in bfloat16: a
-    2,400-token prompt in one step (prompt-portion attention on tensor cores) beside a decoded
-    token and the stub of another prompt (the key-splitting kernel writes their rows), prompts
-    alone (wide tiles), decoding in a changing batch (narrow tiles, the decode router and the
-    per-pair expert products), against the plain implementation.
-
-    Measured on this model: positions whose routing agrees differ from the plain implementation by
-    2.5e-3 of the scale in the median and 6.8e-3 at most (TOL is 1e-2, as everywhere); positions
-    where a near-tie of two router logits went the other way differ by 1e-2 to 6e-2, and their
-    margins reach 0.0100 of the rms of the token's router logits (sums over four times the width of
-    the tiny configurations carry more rounding), so a margin below 1.5e-2 counts as a possible
-    flip here; no more than 3 % of the positions may need that explanation."""
+    embeddings, pages of 32), in bfloat16: a 2,400-token prompt in one step (prompt-portion
+    attention on tensor cores) beside a decoded token and the stub of another prompt (the
+    key-splitting kernel writes their rows), prompts alone (wide tiles), decoding in a changing
+    batch (narrow tiles, the decode router and the per-pair expert products), against the plain
+    implementation on the experts the engine chose; then the same steps in true 32-bit arithmetic."""
     cfg, weights = helpers.make_model_folder(str(tmp_path), name, seed=23)
     V = cfg["vocab_size"]
     reqs = {"long": helpers.random_tokens(2400, V, 1), "r1": helpers.random_tokens(300, V, 2), "r2": helpers.random_tokens(150, V, 3),
@@ -147,21 +163,16 @@ def test_tensor_core_kernels_inside_the_model(tmp_path, name):
                 del at[rid]
         steps.append({"step": n, "entries": entries, "end": end})
         n += 1
-    outputs, runner = helpers.run_replay(str(tmp_path), "bfloat16", steps, 2432 + 320 + 192 + 128)
-    got = helpers.collect(reqs, steps, outputs)
-    for rid, toks in reqs.items():
-        ref = helpers.plain_logits(cfg, weights, toks, True)
-        worst = helpers.assert_close(got[rid], ref, "bfloat16", f"{name} bfloat16 {rid}", 16, fragile=1.5e-2)
-        print(f"{name} bfloat16 {rid}: worst error {worst:.3e}")
-        err = (got[rid].double() - ref[0].double()).abs().reshape(len(toks), -1).max(-1).values / float(ref[0].abs().max())
-        assert int((err > helpers.TOL["bfloat16"]).sum()) <= 0.03 * len(toks) + 1, f"{rid}: too many positions beyond the tolerance"
+    for dtype in ("bfloat16", "float32"):
+        outputs, runner = helpers.run_replay(str(tmp_path), dtype, steps, 2432 + 320 + 192 + 128, tap=True)
+        got = helpers.collect(reqs, steps, outputs)
+        for rid, toks in reqs.items():
+            worst, flipped = helpers.assert_matches_plain(cfg, weights, toks, got[rid], dtype, f"{name} {dtype} {rid}",
+                                                          routing=runner.routing.get(rid))
+            print(f"{name} {dtype} {rid}: worst error {worst:.3e}, {flipped} positions routed at a near-tie")
+            assert flipped <= 0.03 * len(toks) + 1, f"{rid}: too many positions routed differently to be rounding"
     from quench6k_b200 import ops
     assert ops.tc_status() == 0
-    # the same steps in true 32-bit arithmetic: no flips to explain, every position within 5e-6
-    outputs, _ = helpers.run_replay(str(tmp_path), "float32", steps, 2432 + 320 + 192 + 128)
-    got = helpers.collect(reqs, steps, outputs)
-    for rid, toks in reqs.items():
-        helpers.assert_close(got[rid], helpers.plain_logits(cfg, weights, toks, False), "float32", f"{name} float32 {rid}")
 
 
 def test_trace_run_program(model, tmp_path):
@@ -186,5 +197,5 @@ def test_trace_run_program(model, tmp_path):
         assert data.size == n * V
         outputs[s["step"]] = torch.from_numpy(data.reshape(n, V))
     got = helpers.collect(model["requests"], steps, outputs)
-    for rid in model["requests"]:
-        helpers.assert_close(got[rid], model["ref"][False][rid], "float32", f"trace_run {rid}")
+    for rid, toks in model["requests"].items():
+        helpers.assert_matches_plain(model["cfg"], model["weights"], toks, got[rid], "float32", f"trace_run {rid}")

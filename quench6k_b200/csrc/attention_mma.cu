@@ -1,27 +1,26 @@
-// bfloat16 attention over the paged cache on tensor cores, for decode rows and prompt portions in
-// one launch, with the key range split over CTAs and merged afterwards.
+// bfloat16 attention over the paged cache on tensor cores (mma.sync), for decode rows and prompt
+// portions in one launch, with the key range split over CTAs and merged afterwards.
 //
-// Arithmetic as the reference's attn_kernel / attn_merge_kernel (crates/cuda/kernels/flint.cu:211-561):
-// scores in base 2 (scale * log2 e folded in), causal and window mask per row, online softmax per
-// key tile, probabilities rounded to bfloat16 before they are summed, sinks in the merge's
-// denominator only.  Differences: keys and values come from pages through the block table; a
-// launch covers rows of many requests through a tile list; head size and group size are
-// parameters (head size 64 or 128 here; other sizes run on the generic kernel).
+// The arithmetic is the reference's (crates/cuda/kernels/flint.cu:211-561 computes the same
+// quantities): scores in base 2 (scale * log2 e folded in), causal and window mask per row, online
+// softmax per key tile, probabilities rounded to bfloat16 before they are summed, sinks in the
+// last denominator only.  How it is computed is this file's own: keys and values come from pages
+// through the block table; a launch covers rows of many requests through a tile list and a plan
+// made on the device; the keys are the M side of both products (see the kernel's comment); head
+// size and group size are parameters (head size 64 or 128 here; other sizes run on the generic
+// kernel).
 //
-// A tile is up to ROWS = 16 (narrow) or 128 (wide) query rows of one request and one KV head:
+// A tile is up to 8 or 16 (narrow) or 128 (wide) query rows of one request and one KV head:
 // row = token_in_tile * G + head_in_group.  Key tiles hold 64 keys, aligned to multiples of 64 of
-// the key index.  Narrow tiles (decode): the 4 warps share the 16 rows and split each key tile
-// (16 keys each), then merge their partial softmax states through shared memory.  Wide tiles
-// (prompt portions): 8 warps, each owning 16 rows and walking all 64 keys of a tile.
-// K and V tiles travel through a ring of shared-memory stages.  With pages of 8 rows or a multiple
-// (the usual case) a producer warp brings each page's [rows x 64] boxes in by TMA (tensor maps over
-// a layer's K and V pool, 128-byte swizzle, zero fill for keys that have no page; when the pages of
-// a key tile have consecutive numbers, which the head-major pool makes contiguous, one box of 64
-// keys per half replaces the boxes per page: far fewer TMA operations) and signals
-// the four consumer warps through mbarriers (full: transaction bytes; empty: one arrival per
-// warp); every wait is bounded and records a code in a status word when it runs out.  With other
-// page sizes the consumer warps copy the rows themselves with 16-byte cp.async into two stages.
-// Either way the 16-byte chunks are XOR-swizzled by the row, so ldmatrix reads are conflict-free.
+// the key index, and travel through a ring of shared-memory stages that a producer warp fills.
+// With pages of 8 keys or a multiple (the usual case) it brings each page's [keys x 64] boxes in by
+// TMA (tensor maps over a layer's K and V pool, 128-byte swizzle, zero fill for keys that have no
+// page; when the pages of a key tile have consecutive numbers, which the head-major pool makes
+// contiguous, one box of 64 keys per half replaces the boxes per page: far fewer TMA operations);
+// with other page sizes its lanes copy 16-byte chunks with cp.async into the same XOR-swizzled
+// layout.  Either way a stage is handed over through mbarriers (full: transaction bytes or the
+// copies' arrivals; empty: one arrival per warp that read it); every wait is bounded and records
+// a code in a status word when it runs out.
 #include <climits>
 #include <map>
 #include <tuple>
@@ -58,8 +57,7 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool v
     const int n = valid ? 16 : 0;            // 0 source bytes: the 16 destination bytes become zeros
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t* r, uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -160,336 +158,413 @@ __global__ void __launch_bounds__(PLAN_THREADS) attention_plan_kernel(const int*
     }
 }
 
-// Byte offset of 16-byte chunk c of row r in a swizzled [rows][HD] bf16 tile (the Q tile).
-template <int HD> __device__ __forceinline__ uint32_t sw(int r, int c) { return (uint32_t)(r * HD * 2 + ((c ^ (r & 7)) << 4)); }
-// Byte offset of chunk c of key r in a K or V tile: [HD/64 column halves][64 keys][128 bytes], the
-// layout TMA's 128-byte swizzle produces for boxes that start on multiples of 8 keys.
+// Byte offset of chunk c (16 bytes: 8 head dimensions) of key r in a K or V stage: [HD/64 column halves][64 keys][128 bytes],
+// the layout TMA's 128-byte swizzle produces for boxes that start on multiples of 8 keys.
 __device__ __forceinline__ uint32_t swk(int r, int c) { return (uint32_t)((c >> 3) * (KT * 128) + r * 128 + (((c & 7) ^ (r & 7)) << 4)); }
 
-template <int HD, bool WIDE, bool TMA>
-__global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0)) attention_mma_kernel(const __grid_constant__ CUtensorMap tm_k,
-                                                                        const __grid_constant__ CUtensorMap tm_v,
-                                                                        const __grid_constant__ CUtensorMap tm_k_run,
-                                                                        const __grid_constant__ CUtensorMap tm_v_run, const AttnParams p) {
+// Transpose of an 8x8 matrix of 16-bit values held one row per four lanes (the mma fragment layout).
+__device__ __forceinline__ uint32_t transpose_8x8(uint32_t v) {
+    uint32_t r;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
+    return r;
+}
+
+// ---------------------------------------------------------------------------------------------
+// The attention kernel.  Keys are the M side of the tensor-core products, query rows the N side:
+//
+//   S^T [64 keys x NQ rows]  = K [64 x HD] . Q^T [HD x NQ]        (mma.m16n8k16: four key blocks of 16, NQ/8 row blocks)
+//   O^T [HD x NQ]           += V^T [HD x 64] . P^T [64 x NQ]      (HD/16 blocks of head dimensions, the same row blocks)
+//
+// so a decode step's handful of rows (one token of a group of 8 query heads: NQ = 8) fills the
+// narrow side of the instruction exactly and nothing is padded to 16 rows, and K and V are the
+// operands that come straight from shared memory by ldmatrix (V transposed on the way).  The
+// softmax runs down the key axis: a thread holds, of every key block, two keys for two rows; a
+// row's maximum over the tile takes three shuffles over the lanes that hold the other keys.  The
+// probabilities leave the first product as an accumulator fragment [keys x rows] and enter the
+// second as its B operand [keys x rows] in the other fragment layout: movmatrix transposes the 8x8
+// blocks in registers, nothing goes through shared memory.
+//
+// One warp runs a whole [64 keys x NQ rows] tile by itself with its own running maximum, sum and O^T.
+// Narrow tiles (NQ rows of one request and KV head: decode): the four consumer warps take the key
+// tiles of the CTA's range in turn (tile i belongs to warp i mod 4) and never wait for one another
+// for a tile's arithmetic until the end, where their four states are combined through the then idle ring.  Wide tiles
+// (128 rows: prompt portions): eight consumer warps own 16 rows each and all walk every key tile.
+// A producer warp keeps the ring of K/V stages full: by TMA (one elected lane; pages of 8 keys or
+// a multiple) or, for other page sizes, with 16-byte cp.async copies by all its lanes that arrive
+// on the same full barriers (cp.async.mbarrier.arrive), so the consumers are the same either way.
+template <int HD, int NQ, bool WIDE, bool TMA>
+__global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + 32, WIDE ? 1 : 2) attention_mma_kernel(const __grid_constant__ CUtensorMap tm_k,
+                                                                                 const __grid_constant__ CUtensorMap tm_v,
+                                                                                 const __grid_constant__ CUtensorMap tm_k_run,
+                                                                                 const __grid_constant__ CUtensorMap tm_v_run, const AttnParams p) {
     pdl_enter();
     constexpr int CW = WIDE ? 8 : 4;         // consumer warps
-    constexpr int CT = CW * 32;              // consumer threads
-    constexpr int ROWS = WIDE ? 128 : 16;
-    constexpr int CH = HD / 8;               // 16-byte chunks per row
-    constexpr int KW = WIDE ? KT : 16;       // keys of a tile this warp handles
-    constexpr int NB = KW / 8;               // score n-blocks per warp
-    constexpr int DB = HD / 8;               // output n-blocks
+    constexpr int ROWS = WIDE ? 128 : NQ;    // query rows of the CTA's tile
+    constexpr int NB = NQ / 8;               // row blocks (n = 8) of a warp
+    constexpr int KB = KT / 16;              // key blocks (m = 16) of a key tile
+    constexpr int DB = HD / 16;              // blocks of head dimensions (k = 16 of the first product, m = 16 of the second)
+    constexpr int CH = HD / 8;               // 16-byte chunks per key
     constexpr uint32_t TILE_BYTES = KT * HD * 2;
-    constexpr int STAGES = TMA ? (HD == 128 ? 3 : 4) : 2;
+    constexpr int STAGES = HD == 128 ? 3 : 4;
+    static_assert(NQ == 8 || NQ == 16, "a warp's tile has 8 or 16 query rows");
+    static_assert(!WIDE || NQ == 16, "wide tiles are eight warps of 16 rows");
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    // [K stage 0 .. S-1][V stage 0 .. S-1][Q: ROWS x HD]; stages start on 1024 bytes (swizzle pattern)
-    const uint32_t k_s = smem_u32(smem), v_s = k_s + STAGES * TILE_BYTES, q_s = v_s + STAGES * TILE_BYTES;
+    // [K stage 0 .. S-1][V stage 0 .. S-1]; stages start on 1024 bytes (swizzle pattern)
+    const uint32_t k_s = smem_u32(smem), v_s = k_s + STAGES * TILE_BYTES;
     __shared__ __align__(8) uint64_t bars[8];
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[4]);
 
     const int kh = blockIdx.y;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g8 = lane >> 2, t4 = lane & 3;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = p.G;
     // this CTA's record of the plan: everything about its tile in one load
     const int4 wa = reinterpret_cast<const int4*>(p.work)[2 * (size_t)blockIdx.x];
     const int4 wb = reinterpret_cast<const int4*>(p.work)[2 * (size_t)blockIdx.x + 1];
-    const int tok0 = wa.x, ntok = wa.y, pos_first = wa.z, split = wb.x, se = wb.y, per = wb.w;
+    const int tok0 = wa.x, ntok = wa.y, pos_first = wa.z, part = wb.x, parts = wb.y, per = wb.w;
     if (tok0 < 0) return;
     const int pos_last = pos_first + ntok - 1;
     const int* bt = p.block_table + (size_t)wa.w * p.max_blocks;
-    const int k_lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
+    const int k_lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;        // first key any row of the tile sees
     const int first_tile = k_lo / KT, end_tile = pos_last / KT + 1;
-    const int t_begin = first_tile + split * per, t_end = min(end_tile, t_begin + per);
-    // where this CTA's partial results go: [work item][KV head][row of the tile]
-    const size_t part_row0 = ((size_t)blockIdx.x * p.Hkv + kh) * ROWS;
+    const int t_begin = first_tile + part * per, n_mine = max(0, min(end_tile, t_begin + per) - t_begin);
 
-    // ---- the producer (one thread) brings every tile of this CTA's key range into the ring
-    auto issue = [&](int i) {
-        const int ps = p.page_size, box = ps < KT ? ps : KT;            // keys per TMA box
-        const int s2 = i % STAGES;
-        const uint32_t fb = full0 + 8 * s2;
-        mbar_expect_tx(fb, 2 * TILE_BYTES);
-        const int j0 = (t_begin + i) * KT;
-        // pages with consecutive numbers are contiguous for one head: when the tile's pages form
-        // such a run, each half comes in as one box of 64 keys instead of one box per page
-        bool run = ps < KT && j0 >= k_lo && j0 / ps + KT / ps <= p.max_blocks;
-        int first = -1;
-        if (run) {
-            first = bt[j0 / ps];
-            run = first >= 0;
-            for (int b = 1; b < KT / ps && run; ++b) run = bt[j0 / ps + b] == first + b;
-        }
-        if (run) {
-            const int y = (kh * p.num_pages + first) * ps;
-#pragma unroll
-            for (int h = 0; h < HD / 64; ++h) {
-                const uint32_t off = s2 * TILE_BYTES + h * (KT * 128);
-                tma_load_2d(k_s + off, &tm_k_run, h * 64, y, fb);
-                tma_load_2d(v_s + off, &tm_v_run, h * 64, y, fb);
-            }
-            return;
-        }
-        for (int b = 0; b < KT / box; ++b) {
-            const int j = j0 + b * box;
-            int y = p.pool_rows;                                         // out of range: the box is filled with zeros
-            if (j + box > k_lo && j <= pos_last) {
-                const int page = bt[j / ps];
-                if (page >= 0) y = (kh * p.num_pages + page) * ps + j % ps;
-            }
-#pragma unroll
-            for (int h = 0; h < HD / 64; ++h) {
-                const uint32_t off = s2 * TILE_BYTES + h * (KT * 128) + b * box * 128;
-                tma_load_2d(k_s + off, &tm_k, h * 64, y, fb);
-                tma_load_2d(v_s + off, &tm_v, h * 64, y, fb);
-            }
-        }
-    };
-    if (TMA && tid == 0) {
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_v) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_k_run) : "memory");
-        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_v_run) : "memory");
-    }
-    if (TMA && tid == CW * 32) {
-        // the first tiles are on their way while the consumers still fetch Q
-        for (int s2 = 0; s2 < STAGES; ++s2) {
-            mbar_init(full0 + 8 * s2, 1);
-            mbar_init(empty0 + 8 * s2, CW);
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        for (int i = 0; i < STAGES && i < t_end - t_begin; ++i) issue(i);
-    }
-    // ---- Q tile into shared memory (zero rows past the tile's tokens)
-    if (warp < CW) {
-        for (int idx = tid; idx < ROWS * CH; idx += CT) {
-            const int r = idx / CH, c = idx % CH, tt = r / G, hg = r % G;
-            const bool valid = tt < ntok;
-            const __nv_bfloat16* src = p.q + ((size_t)(tok0 + (valid ? tt : 0)) * p.Hq + kh * G + hg) * HD + c * 8;
-            cp_async16(q_s + sw<HD>(r, c), src, valid);
-        }
-    }
-    auto load_kv = [&](int stage, int kt) {      // the cp.async path: every consumer thread copies its chunks
-        for (int idx = tid; idx < KT * CH; idx += CT) {
-            const int r = idx / CH, c = idx % CH, j = kt * KT + r;
-            const bool in = j >= k_lo && j <= pos_last;
-            int page = in ? bt[j / p.page_size] : -1;
-            const bool valid = page >= 0;
-            const size_t off = valid ? (((size_t)kh * p.num_pages + page) * p.page_size + j % p.page_size) * HD + c * 8 : 0;
-            cp_async16(k_s + stage * TILE_BYTES + swk(r, c), p.k_pages + off, valid);
-            cp_async16(v_s + stage * TILE_BYTES + swk(r, c), p.v_pages + off, valid);
-        }
-    };
-    if (!TMA) load_kv(0, t_begin);
-    cp_async_commit();
-    cp_async_wait<0>();
-    __syncthreads();
-
-    if (TMA && warp == CW) {
+    // ------------------------------------------------------------------ the producer warp
+    if (warp == CW) {
         if (lane == 0) {
-            for (int i = STAGES; i < t_end - t_begin; ++i) {
-                if (!mbar_wait(empty0 + 8 * (i % STAGES), ((i / STAGES) & 1) ^ 1)) {
-                    atomicExch(&g_attn_status, 1);
-                    break;
+            for (int s = 0; s < STAGES; ++s) {
+                mbar_init(full0 + 8 * s, TMA ? 1 : 32);
+                mbar_init(empty0 + 8 * s, CW);
+            }
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+    }
+    __syncthreads();                          // the only block-wide barrier before the warps part ways
+    if (warp == CW) {
+        const int ps = p.page_size;
+        if (TMA && lane != 0) return;         // one elected lane issues the TMA loads; the copies of the other path take all 32
+        for (int i = 0; i < n_mine; ++i) {
+            const int st = i % STAGES;
+            if (i >= STAGES && !mbar_wait(empty0 + 8 * st, ((i / STAGES) & 1) ^ 1)) {
+                if (lane == 0) atomicExch(&g_attn_status, 1);
+                return;
+            }
+            const uint32_t fb = full0 + 8 * st;
+            const int j0 = (t_begin + i) * KT;
+            if (TMA) {
+                const int box = ps < KT ? ps : KT;                               // keys per box of the per-page maps
+                mbar_expect_tx(fb, 2 * TILE_BYTES);
+                // pages with consecutive numbers are contiguous for one head: when the tile's pages form
+                // such a run, each half comes in as one box of 64 keys instead of one box per page
+                bool run = ps < KT && j0 >= k_lo && j0 / ps + KT / ps <= p.max_blocks;
+                int first = -1;
+                if (run) {
+                    first = bt[j0 / ps];
+                    run = first >= 0;
+                    for (int b = 1; b < KT / ps && run; ++b) run = bt[j0 / ps + b] == first + b;
                 }
-                issue(i);
+                if (run) {
+                    const int y = (kh * p.num_pages + first) * ps;
+#pragma unroll
+                    for (int h = 0; h < HD / 64; ++h) {
+                        const uint32_t off = st * TILE_BYTES + h * (KT * 128);
+                        tma_load_2d(k_s + off, &tm_k_run, h * 64, y, fb);
+                        tma_load_2d(v_s + off, &tm_v_run, h * 64, y, fb);
+                    }
+                    continue;
+                }
+                for (int b = 0; b < KT / box; ++b) {
+                    const int j = j0 + b * box;
+                    int y = p.pool_rows;                                         // out of range: the box is filled with zeros
+                    if (j + box > k_lo && j <= pos_last) {
+                        const int page = bt[j / ps];
+                        if (page >= 0) y = (kh * p.num_pages + page) * ps + j % ps;
+                    }
+#pragma unroll
+                    for (int h = 0; h < HD / 64; ++h) {
+                        const uint32_t off = st * TILE_BYTES + h * (KT * 128) + b * box * 128;
+                        tma_load_2d(k_s + off, &tm_k, h * 64, y, fb);
+                        tma_load_2d(v_s + off, &tm_v, h * 64, y, fb);
+                    }
+                }
+            } else {
+                // every lane copies its share of the tile's chunks; keys outside the tile's range or without a page become zeros
+                for (int idx = lane; idx < KT * CH; idx += 32) {
+                    const int r = idx / CH, c = idx % CH, j = j0 + r;
+                    const int page = (j >= k_lo && j <= pos_last) ? bt[j / ps] : -1;
+                    const bool valid = page >= 0;
+                    const size_t off = valid ? (((size_t)kh * p.num_pages + page) * ps + j % ps) * HD + c * 8 : 0;
+                    cp_async16(k_s + st * TILE_BYTES + swk(r, c), p.k_pages + off, valid);
+                    cp_async16(v_s + st * TILE_BYTES + swk(r, c), p.v_pages + off, valid);
+                }
+                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(fb) : "memory");
+            }
+        }
+        if (!TMA) cp_async_wait_all();        // nothing of this warp's is in flight when it leaves
+        return;
+    }
+
+    // ------------------------------------------------------------------ the consumer warps
+    // A thread of the fragment layout: quad = lane / 4 names a key (first product's rows) or a head
+    // dimension (second product's rows), pair = lane % 4 names two neighbouring query rows.
+    const int quad = lane >> 2, pair = lane & 3;
+    const int row0 = WIDE ? warp * NQ : 0;                                   // first row of the CTA's tile this warp works on
+    // the rows this thread holds in the accumulator fragments: block nb, rows nb*8 + 2*pair + {0, 1}
+    int see_to[NB][2], see_from[NB][2];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            const int tt = (row0 + nb * 8 + 2 * pair + c) / G, pos = pos_first + tt;
+            see_to[nb][c] = tt < ntok ? pos : -1;                            // a row past the tile's tokens sees nothing
+            see_from[nb][c] = p.window > 0 ? pos - p.window + 1 : 0;
+        }
+    // Q^T as the first product's B operand, straight from global memory: this thread's row is
+    // nb*8 + quad, its head dimensions 16 ks + 2 pair + {0, 1} and + 8
+    uint32_t qf[DB][NB][2];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+        const int r = row0 + nb * 8 + quad, tt = r / G, hg = r % G;
+        const bool live = tt < ntok;
+        const uint32_t* src = reinterpret_cast<const uint32_t*>(p.q + ((size_t)(tok0 + (live ? tt : 0)) * p.Hq + kh * G + hg) * HD) + pair;
+#pragma unroll
+        for (int ks = 0; ks < DB; ++ks) {
+            qf[ks][nb][0] = live ? src[ks * 8] : 0u;
+            qf[ks][nb][1] = live ? src[ks * 8 + 4] : 0u;
+        }
+    }
+    float top[NB][2], sum[NB][2];              // running maximum (base-2 logits) and sum of the probabilities of this thread's keys
+    float acc[DB][NB][4];                      // O^T: head dimensions 16 db + quad (+ 8 for [2], [3]), rows as above
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+        top[nb][0] = top[nb][1] = -INFINITY;
+        sum[nb][0] = sum[nb][1] = 0.0f;
+#pragma unroll
+        for (int db = 0; db < DB; ++db) acc[db][nb][0] = acc[db][nb][1] = acc[db][nb][2] = acc[db][nb][3] = 0.0f;
+    }
+
+    // Every consumer warp passes every stage's barriers in order, also for the tiles it leaves to the others (it
+    // lets go of those at once): a phase bit tells a phase only from its neighbours, so nobody may skip one.
+    for (int i = 0; i < n_mine; ++i) {
+        const int st = i % STAGES, kt = t_begin + i;
+        if (!mbar_wait(full0 + 8 * st, (i / STAGES) & 1)) {
+            if (lane == 0) atomicExch(&g_attn_status, 2);
+            break;
+        }
+        if (!WIDE && i % CW != warp) {
+            if (lane == 0) mbar_arrive(empty0 + 8 * st);
+            continue;
+        }
+        const uint32_t kb = k_s + st * TILE_BYTES, vb = v_s + st * TILE_BYTES;
+        if (TMA && kt == end_tile - 1 && (pos_last + 1) % KT != 0) {
+            // the last page came in whole: the keys past the last position hold whatever the page held
+            // before.  Their scores are masked, but 0 * V must not meet a stale NaN: clear those V rows.
+            const int r0 = pos_last + 1 - kt * KT;
+            if (WIDE) {
+                for (int idx = r0 * CH + tid; idx < KT * CH; idx += CW * 32)
+                    *reinterpret_cast<uint4*>(smem + (v_s - k_s) + st * TILE_BYTES + swk(idx / CH, idx % CH)) = make_uint4(0, 0, 0, 0);
+                asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");          // all eight warps read this stage
+            } else {
+                for (int idx = r0 * CH + lane; idx < KT * CH; idx += 32)
+                    *reinterpret_cast<uint4*>(smem + (v_s - k_s) + st * TILE_BYTES + swk(idx / CH, idx % CH)) = make_uint4(0, 0, 0, 0);
+                __syncwarp();
+            }
+        }
+        // ---- S^T = K Q^T
+        float sc[KB][NB][4];
+#pragma unroll
+        for (int mb = 0; mb < KB; ++mb) {
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) sc[mb][nb][0] = sc[mb][nb][1] = sc[mb][nb][2] = sc[mb][nb][3] = 0.0f;
+#pragma unroll
+            for (int ks = 0; ks < DB; ++ks) {
+                uint32_t a[4];                 // keys 16 mb + {0..7, 8..15} x head dimensions 16 ks + {0..7, 8..15}
+                ldmatrix_x4(a, kb + swk(mb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)));
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb) mma_bf16(sc[mb][nb], a, qf[ks][nb][0], qf[ks][nb][1]);
+            }
+        }
+        // ---- scale, mask, the rows' maxima over the tile
+        const int j0 = kt * KT + quad;
+        float hi[NB][2];
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            hi[nb][0] = top[nb][0], hi[nb][1] = top[nb][1];
+#pragma unroll
+            for (int mb = 0; mb < KB; ++mb)
+#pragma unroll
+                for (int x = 0; x < 4; ++x) {
+                    const int c = x & 1, j = j0 + mb * 16 + (x >> 1) * 8;
+                    const float v = (j <= see_to[nb][c] && j >= see_from[nb][c]) ? sc[mb][nb][x] * p.scale_log2 : -INFINITY;
+                    sc[mb][nb][x] = v;
+                    hi[nb][c] = fmaxf(hi[nb][c], v);
+                }
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                float v = hi[nb][c];
+                v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+                v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 8));
+                v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 16));
+                const float shrink = v == -INFINITY ? 1.0f : exp2f(top[nb][c] - v);      // nothing seen yet: nothing to rescale
+                top[nb][c] = v;
+                sum[nb][c] *= shrink;
+#pragma unroll
+                for (int db = 0; db < DB; ++db) acc[db][nb][c] *= shrink, acc[db][nb][2 + c] *= shrink;
+            }
+        }
+        // ---- P^T = 2^(S^T - max), rounded to bfloat16 before it is summed (the sum then matches the
+        // P that multiplies V), and turned into the second product's B fragments
+        uint32_t pf[KB][NB][2];
+#pragma unroll
+        for (int mb = 0; mb < KB; ++mb)
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+                float e[4];
+#pragma unroll
+                for (int x = 0; x < 4; ++x) e[x] = top[nb][x & 1] == -INFINITY ? 0.0f : exp2f(sc[mb][nb][x] - top[nb][x & 1]);
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(e[0], e[1]), up = __floats2bfloat162_rn(e[2], e[3]);
+                sum[nb][0] += __low2float(lo) + __low2float(up);
+                sum[nb][1] += __high2float(lo) + __high2float(up);
+                pf[mb][nb][0] = transpose_8x8(*reinterpret_cast<const uint32_t*>(&lo));
+                pf[mb][nb][1] = transpose_8x8(*reinterpret_cast<const uint32_t*>(&up));
+            }
+        // ---- O^T += V^T P^T
+#pragma unroll
+        for (int mb = 0; mb < KB; ++mb)
+#pragma unroll
+            for (int db = 0; db < DB; ++db) {
+                uint32_t a[4];                 // head dimensions 16 db + {0..7, 8..15} x keys 16 mb + {0..7, 8..15}, transposed on load
+                ldmatrix_x4_trans(a, vb + swk(mb * 16 + (lane & 7) + ((lane >> 4) << 3), db * 2 + ((lane >> 3) & 1)));
+#pragma unroll
+                for (int nb = 0; nb < NB; ++nb) mma_bf16(acc[db][nb], a, pf[mb][nb][0], pf[mb][nb][1]);
+            }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + 8 * st);
+    }
+    // a row's sum is spread over the eight lanes that hold its keys
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            float v = sum[nb][c];
+            v += __shfl_xor_sync(0xffffffffu, v, 4);
+            v += __shfl_xor_sync(0xffffffffu, v, 8);
+            v += __shfl_xor_sync(0xffffffffu, v, 16);
+            sum[nb][c] = v;
+        }
+
+    const size_t part_row0 = ((size_t)blockIdx.x * p.Hkv + kh) * ROWS;       // where this CTA's partial results go
+    if (WIDE) {
+        // ---- every warp owns its 16 rows: straight to the output (one part) or to the partial buffers
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            if (parts == 1) {
+                // the output row of the lane after the transposition below: row nb*8 + quad
+                const int r = row0 + nb * 8 + quad, tt = r / G, hg = r % G;
+                float scale[2];
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {                                // this thread's own rows: 1 / denominator, with the sink
+                    const int rr = row0 + nb * 8 + 2 * pair + c;
+                    float shrink = 1.0f, den = sum[nb][c];
+                    if (p.sinks && rr / G < ntok) {
+                        const float sk = p.sinks[kh * G + rr % G] * LOG2E, both = fmaxf(top[nb][c], sk);
+                        shrink = exp2f(top[nb][c] - both);
+                        den = den * shrink + exp2f(sk - both);
+                    }
+                    scale[c] = shrink / den;
+                }
+                __nv_bfloat16* dst = p.out + ((size_t)(tok0 + tt) * p.Hq + kh * G + hg) * HD + 2 * pair;
+#pragma unroll
+                for (int db = 0; db < DB; ++db)
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {                            // head dimensions 16 db + 8 h + quad of rows 2 pair + {0, 1} ...
+                        const uint32_t v = transpose_8x8(pack_bf16(acc[db][nb][2 * h] * scale[0], acc[db][nb][2 * h + 1] * scale[1]));
+                        if (tt < ntok) *reinterpret_cast<uint32_t*>(dst + db * 16 + h * 8) = v;      // ... become dimensions 2 pair + {0, 1} of row quad
+                    }
+            } else {
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    const int r = row0 + nb * 8 + 2 * pair + c;
+                    if (r / G >= ntok) continue;
+                    float* po = p.part_o + (part_row0 + r) * HD + quad;
+#pragma unroll
+                    for (int db = 0; db < DB; ++db) po[db * 16] = acc[db][nb][c], po[db * 16 + 8] = acc[db][nb][2 + c];
+                    if (quad == 0) {
+                        p.part_ml[(part_row0 + r) * 2] = top[nb][c];
+                        p.part_ml[(part_row0 + r) * 2 + 1] = sum[nb][c];
+                    }
+                }
             }
         }
         return;
     }
-
-    // this thread's two rows (g8 and g8 + 8 of the warp's 16) and their key limits
-    const int rbase = WIDE ? warp * 16 : 0, koff = WIDE ? 0 : warp * 16;
-    int lim_hi[2], lim_lo[2];
+    // ---- narrow tiles: the four warps hold the same rows over different keys.  Their maxima and sums meet in shared
+    // memory first; every warp brings its O^T to the common maximum and writes it to a slab of its own; then all 128
+    // threads add the four slabs in warp order.  The ring is idle by now: every tile has been waited for and read.
+    constexpr int LD = HD + 4;                 // row pitch of a slab in floats (the padding spreads a fragment's stores over the banks)
+    float* slab = reinterpret_cast<float*>(smem);                            // [CW][NQ][LD]
+    float* stat = slab + CW * NQ * LD;                                       // [CW][NQ][2]: maximum, sum
+    asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+    if (quad == 0)
 #pragma unroll
-    for (int hr = 0; hr < 2; ++hr) {
-        const int r = rbase + g8 + hr * 8, tt = r / G;
-        const int pos = pos_first + tt;
-        lim_hi[hr] = tt < ntok ? pos : -1;
-        lim_lo[hr] = p.window > 0 ? pos - p.window + 1 : 0;
+        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                float* s2 = stat + ((size_t)warp * NQ + nb * 8 + 2 * pair + c) * 2;
+                s2[0] = top[nb][c], s2[1] = sum[nb][c];
+            }
+    asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+            const int r = nb * 8 + 2 * pair + c;
+            float all = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < CW; ++w) all = fmaxf(all, stat[((size_t)w * NQ + r) * 2]);
+            const float mine = top[nb][c] == -INFINITY ? 0.0f : exp2f(top[nb][c] - all);
+            float* dst = slab + ((size_t)warp * NQ + r) * LD + quad;
+#pragma unroll
+            for (int db = 0; db < DB; ++db) dst[db * 16] = acc[db][nb][c] * mine, dst[db * 16 + 8] = acc[db][nb][2 + c] * mine;
+        }
+    asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+    // thread -> (row, a stretch of head dimensions): 128 threads over NQ rows
+    constexpr int TPR = CW * 32 / NQ, DPT = HD / TPR;                        // threads per row, dimensions per thread
+    const int r = tid / TPR, d0 = (tid % TPR) * DPT, tt = r / G, hg = r % G;
+    if (tt >= ntok) return;
+    float all = -INFINITY, den = 0.0f;
+#pragma unroll
+    for (int w = 0; w < CW; ++w) all = fmaxf(all, stat[((size_t)w * NQ + r) * 2]);
+#pragma unroll
+    for (int w = 0; w < CW; ++w) {
+        const float mw = stat[((size_t)w * NQ + r) * 2];
+        den += mw == -INFINITY ? 0.0f : exp2f(mw - all) * stat[((size_t)w * NQ + r) * 2 + 1];
     }
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
-    float o[DB][4];
+    float o[DPT];
 #pragma unroll
-    for (int n = 0; n < DB; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f;
-
-    uint32_t qa[HD / 16][4];
+    for (int d = 0; d < DPT; ++d) {
+        o[d] = 0.0f;
 #pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks) ldmatrix_x4(qa[ks], q_s + sw<HD>(rbase + (lane & 15), ks * 2 + (lane >> 4)));
-
-    for (int kt = t_begin; kt < t_end; ++kt) {
-        const int it = kt - t_begin, stage = it % STAGES;
-        if (TMA) {
-            if (!mbar_wait(full0 + 8 * stage, (it / STAGES) & 1)) {
-                if (lane == 0) atomicExch(&g_attn_status, 2);
-                break;
-            }
-            if (kt == end_tile - 1 && (pos_last + 1) % KT != 0) {
-                // the last page came in whole: rows past the last key hold whatever the page held
-                // before (masked scores ignore K, but 0 * V must not meet a stale NaN): clear them
-                const int r0 = pos_last + 1 - kt * KT;
-                for (int idx = r0 * CH + tid; idx < KT * CH; idx += CT)
-                    *reinterpret_cast<uint4*>(smem + (v_s - k_s) + stage * TILE_BYTES + swk(idx / CH, idx % CH)) = make_uint4(0, 0, 0, 0);
-                asm volatile("bar.sync 1, %0;" ::"n"(CT) : "memory");
-            }
-        } else {
-            if (kt + 1 < t_end) load_kv(stage ^ 1, kt + 1);
-            cp_async_commit();
-        }
-        const uint32_t kb = k_s + stage * TILE_BYTES, vb = v_s + stage * TILE_BYTES;
-        const int j0 = kt * KT + koff;
-        // ---- S = Q K^T for this warp's keys
-        float s[NB][4];
-#pragma unroll
-        for (int n = 0; n < NB; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.0f;
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-#pragma unroll
-            for (int nj = 0; nj < NB / 2; ++nj) {
-                uint32_t b[4];
-                const int key = koff + nj * 16 + ((lane >> 4) << 3) + (lane & 7);
-                ldmatrix_x4(b, kb + swk(key, ks * 2 + ((lane >> 3) & 1)));
-                mma_bf16(s[2 * nj], qa[ks], b[0], b[1]);
-                mma_bf16(s[2 * nj + 1], qa[ks], b[2], b[3]);
-            }
-        }
-        // ---- mask, online softmax
-        float mx[2] = {m[0], m[1]};
-#pragma unroll
-        for (int n = 0; n < NB; ++n)
-#pragma unroll
-            for (int x = 0; x < 4; ++x) {
-                const int hr = x >> 1, j = j0 + n * 8 + 2 * t4 + (x & 1);
-                const bool ok = j <= lim_hi[hr] && j >= lim_lo[hr];
-                s[n][x] = ok ? s[n][x] * p.scale_log2 : -INFINITY;
-                mx[hr] = fmaxf(mx[hr], s[n][x]);
-            }
-        float corr[2];
-#pragma unroll
-        for (int hr = 0; hr < 2; ++hr) {
-            mx[hr] = fmaxf(mx[hr], __shfl_xor_sync(0xffffffffu, mx[hr], 1));
-            mx[hr] = fmaxf(mx[hr], __shfl_xor_sync(0xffffffffu, mx[hr], 2));
-            corr[hr] = mx[hr] == -INFINITY ? 1.0f : exp2f(m[hr] - mx[hr]);
-            m[hr] = mx[hr];
-            l[hr] *= corr[hr];
-        }
-#pragma unroll
-        for (int n = 0; n < DB; ++n) o[n][0] *= corr[0], o[n][1] *= corr[0], o[n][2] *= corr[1], o[n][3] *= corr[1];
-        uint32_t pa[KW / 16][4];
-#pragma unroll
-        for (int n = 0; n < NB; ++n) {
-            float pr[4];
-#pragma unroll
-            for (int x = 0; x < 4; ++x) pr[x] = m[x >> 1] == -INFINITY ? 0.0f : exp2f(s[n][x] - m[x >> 1]);
-            // rounded to bfloat16 before summing, so that l matches the P that multiplies V
-            const __nv_bfloat162 lo2 = __floats2bfloat162_rn(pr[0], pr[1]), hi2 = __floats2bfloat162_rn(pr[2], pr[3]);
-            const float2 flo = __bfloat1622float2(lo2), fhi = __bfloat1622float2(hi2);
-            l[0] += flo.x + flo.y;
-            l[1] += fhi.x + fhi.y;
-            pa[n / 2][(n % 2) * 2 + 0] = *reinterpret_cast<const uint32_t*>(&lo2);
-            pa[n / 2][(n % 2) * 2 + 1] = *reinterpret_cast<const uint32_t*>(&hi2);
-        }
-        // ---- O += P V
-#pragma unroll
-        for (int ks = 0; ks < KW / 16; ++ks) {
-#pragma unroll
-            for (int dj = 0; dj < DB / 2; ++dj) {
-                uint32_t b[4];
-                const int key = koff + ks * 16 + (((lane >> 3) & 1) << 3) + (lane & 7);
-                ldmatrix_x4_trans(b, vb + swk(key, dj * 2 + (lane >> 4)));
-                mma_bf16(o[2 * dj], pa[ks], b[0], b[1]);
-                mma_bf16(o[2 * dj + 1], pa[ks], b[2], b[3]);
-            }
-        }
-        if (TMA) {
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty0 + 8 * stage);
-        } else {
-            cp_async_wait<0>();
-            asm volatile("bar.sync 1, %0;" ::"n"(CT) : "memory");
-        }
+        for (int w = 0; w < CW; ++w) o[d] += slab[((size_t)w * NQ + r) * LD + d0 + d];
     }
-    // row sums live per thread: add the quad's
-#pragma unroll
-    for (int hr = 0; hr < 2; ++hr) {
-        l[hr] += __shfl_xor_sync(0xffffffffu, l[hr], 1);
-        l[hr] += __shfl_xor_sync(0xffffffffu, l[hr], 2);
-    }
-
-    // ---- results: (m, l, o) per row; narrow tiles first merge the 4 warps' key subsets
-    float* red = reinterpret_cast<float*>(smem);             // reuse the tile ring (all loads have landed, all reads are done)
-    if (!WIDE) {
-        asm volatile("bar.sync 1, 128;" ::: "memory");         // every consumer warp is past its last tile
-        // red: [4 warps][16 rows][HD + 2]
-        constexpr int LD = HD + 2;
-#pragma unroll
-        for (int hr = 0; hr < 2; ++hr) {
-            float* dst = red + ((size_t)warp * 16 + g8 + hr * 8) * LD;
-            if (t4 == 0) dst[HD] = m[hr], dst[HD + 1] = l[hr];
-#pragma unroll
-            for (int n = 0; n < DB; ++n) {
-                dst[n * 8 + 2 * t4] = o[n][hr * 2];
-                dst[n * 8 + 2 * t4 + 1] = o[n][hr * 2 + 1];
-            }
+    if (parts == 1) {
+        float shrink = 1.0f;
+        if (p.sinks) {
+            const float sk = p.sinks[kh * G + hg] * LOG2E, both = fmaxf(all, sk);
+            shrink = exp2f(all - both);
+            den = den * shrink + exp2f(sk - both);
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        // 128 threads: row = tid / 8, 8 threads share a row's HD values
-        const int r = tid >> 3, sub = tid & 7, tt = r / G, hg = r % G;
-        if (tt >= ntok) return;
-        float M = -INFINITY;
+        const float inv = shrink / den;
+        __nv_bfloat16* dst = p.out + ((size_t)(tok0 + tt) * p.Hq + kh * G + hg) * HD + d0;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, red[((size_t)w * 16 + r) * LD + HD]);
-        float wgt[4], L = 0.0f;
-#pragma unroll
-        for (int w = 0; w < 4; ++w) {
-            const float mw = red[((size_t)w * 16 + r) * LD + HD];
-            wgt[w] = mw == -INFINITY ? 0.0f : exp2f(mw - M);
-            L += wgt[w] * red[((size_t)w * 16 + r) * LD + HD + 1];
-        }
-        const size_t row = (size_t)(tok0 + tt) * p.Hq + kh * G + hg;
-        float osc = 1.0f, den = L;
-        if (se == 1 && p.sinks) {
-            const float sk = p.sinks[kh * G + hg] * LOG2E, Mx = fmaxf(M, sk);
-            osc = exp2f(M - Mx);
-            den = L * osc + exp2f(sk - Mx);
-        }
-        for (int d = sub; d < HD; d += 8) {
-            float acc = 0.0f;
-#pragma unroll
-            for (int w = 0; w < 4; ++w) acc += wgt[w] * red[((size_t)w * 16 + r) * LD + d];
-            if (se == 1) p.out[row * HD + d] = __float2bfloat16_rn(acc * osc / den);
-            else p.part_o[(part_row0 + r) * HD + d] = acc;
-        }
-        if (se > 1 && sub == 0) {
-            p.part_ml[(part_row0 + r) * 2] = M;
-            p.part_ml[(part_row0 + r) * 2 + 1] = L;
-        }
+        for (int d = 0; d < DPT; d += 2) *reinterpret_cast<uint32_t*>(dst + d) = pack_bf16(o[d] * inv, o[d + 1] * inv);
     } else {
+        float* po = p.part_o + (part_row0 + r) * HD + d0;
 #pragma unroll
-        for (int hr = 0; hr < 2; ++hr) {
-            const int r = rbase + g8 + hr * 8, tt = r / G, hg = r % G;
-            if (tt >= ntok) continue;
-            const size_t row = (size_t)(tok0 + tt) * p.Hq + kh * G + hg;
-            if (se == 1) {
-                float osc = 1.0f, den = l[hr];
-                if (p.sinks) {
-                    const float sk = p.sinks[kh * G + hg] * LOG2E, Mx = fmaxf(m[hr], sk);
-                    osc = exp2f(m[hr] - Mx);
-                    den = l[hr] * osc + exp2f(sk - Mx);
-                }
-                const float inv = osc / den;
-#pragma unroll
-                for (int n = 0; n < DB; ++n)
-                    *reinterpret_cast<uint32_t*>(p.out + row * HD + n * 8 + 2 * t4) = pack_bf16(o[n][hr * 2] * inv, o[n][hr * 2 + 1] * inv);
-            } else {
-                float* po = p.part_o + (part_row0 + r) * HD;
-#pragma unroll
-                for (int n = 0; n < DB; ++n) *reinterpret_cast<float2*>(po + n * 8 + 2 * t4) = make_float2(o[n][hr * 2], o[n][hr * 2 + 1]);
-                if (t4 == 0) {
-                    p.part_ml[(part_row0 + r) * 2] = m[hr];
-                    p.part_ml[(part_row0 + r) * 2 + 1] = l[hr];
-                }
-            }
+        for (int d = 0; d < DPT; ++d) po[d] = o[d];
+        if (tid % TPR == 0) {
+            p.part_ml[(part_row0 + r) * 2] = all;
+            p.part_ml[(part_row0 + r) * 2 + 1] = den;
         }
     }
 }
@@ -603,20 +678,25 @@ int pool_map(CUtensorMap* out, const void* base, long long rows, int hd, int box
     return 0;
 }
 
-template <int HD, bool WIDE, bool TMA>
+template <int HD, int NQ, bool WIDE, bool TMA>
+constexpr size_t attention_smem() {
+    constexpr int STAGES = HD == 128 ? 3 : 4;
+    constexpr size_t ring = 2 * STAGES * KT * HD * 2;
+    constexpr size_t meet = WIDE ? 0 : 4 * NQ * (HD + 4 + 2) * sizeof(float);       // the narrow tiles' slabs and statistics
+    return (ring > meet ? ring : meet) + 1024;
+}
+
+template <int HD, int NQ, bool WIDE, bool TMA>
 int launch(const AttnParams& p, const CUtensorMap* maps, int n_tiles, cudaStream_t st) {
-    constexpr int ROWS = WIDE ? 128 : 16;
-    constexpr int STAGES = TMA ? (HD == 128 ? 3 : 4) : 2;
-    const size_t ring = 2 * STAGES * KT * HD * 2 + ROWS * HD * 2;
-    const size_t red = WIDE ? 0 : 4 * 16 * (HD + 2) * sizeof(float);
-    const size_t smem = (ring > red ? ring : red) + 1024;
+    constexpr int ROWS = WIDE ? 128 : NQ;
+    constexpr size_t smem = attention_smem<HD, NQ, WIDE, TMA>();
     static bool configured = false;
     if (!configured) {
-        if (cudaFuncSetAttribute(attention_mma_kernel<HD, WIDE, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
+        if (cudaFuncSetAttribute(attention_mma_kernel<HD, NQ, WIDE, TMA>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess)
             return q6k_check_launch("attention_mma: shared memory attribute");
         configured = true;
     }
-    q6k_launch(attention_mma_kernel<HD, WIDE, TMA>, dim3(p.n_work, p.Hkv), (WIDE ? 8 : 4) * 32 + (TMA ? 32 : 0), smem, st, maps[0], maps[1], maps[2], maps[3], p);
+    q6k_launch(attention_mma_kernel<HD, NQ, WIDE, TMA>, dim3(p.n_work, p.Hkv), (WIDE ? 8 : 4) * 32 + 32, smem, st, maps[0], maps[1], maps[2], maps[3], p);
     if (int rc = q6k_check_launch("attention_mma")) return rc;
     if (p.n_work > n_tiles) {                 // some tile may have more than one part
         q6k_launch(attention_merge_kernel<HD>, dim3(n_tiles, p.Hkv, ROWS), MERGE_THREADS, 0, st, p);
@@ -626,15 +706,47 @@ int launch(const AttnParams& p, const CUtensorMap* maps, int n_tiles, cudaStream
 }
 
 template <int HD>
-int launch_hd(const AttnParams& p, const CUtensorMap* maps, bool wide, bool tma, int n_tiles, cudaStream_t st) {
-    if (tma) return wide ? launch<HD, true, true>(p, maps, n_tiles, st) : launch<HD, false, true>(p, maps, n_tiles, st);
-    return wide ? launch<HD, true, false>(p, maps, n_tiles, st) : launch<HD, false, false>(p, maps, n_tiles, st);
+int launch_hd(const AttnParams& p, const CUtensorMap* maps, int rows, bool tma, int n_tiles, cudaStream_t st) {
+    if (rows == 128) return tma ? launch<HD, 16, true, true>(p, maps, n_tiles, st) : launch<HD, 16, true, false>(p, maps, n_tiles, st);
+    if (rows == 16) return tma ? launch<HD, 16, false, true>(p, maps, n_tiles, st) : launch<HD, 16, false, false>(p, maps, n_tiles, st);
+    return tma ? launch<HD, 8, false, true>(p, maps, n_tiles, st) : launch<HD, 8, false, false>(p, maps, n_tiles, st);
+}
+
+// CTAs of the kernel that one SM holds at once (what shared memory and registers allow).
+template <int HD, int NQ, bool WIDE>
+int resident_per_sm() {
+    int n = 0;
+    constexpr size_t smem = attention_smem<HD, NQ, WIDE, true>();
+    if (cudaFuncSetAttribute(attention_mma_kernel<HD, NQ, WIDE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) return 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, attention_mma_kernel<HD, NQ, WIDE, true>, (WIDE ? 8 : 4) * 32 + 32, smem) != cudaSuccess) return 0;
+    return n;
 }
 
 }  // namespace
 
-// Rows per tile for a group size: 16 (narrow) or 128 (wide) query rows hold rows/G tokens.
+// The head sizes and group sizes the kernel takes.  A tile holds the query rows of consecutive tokens of one
+// request for one KV head (row = token * G + head of the group): 8 or 16 rows (narrow: decode and the like) or 128
+// (wide: prompt portions).
 Q6K_API int q6k_attention_mma_supported(int hd, int G, int wide) { return (hd == 64 || hd == 128) && G >= 1 && G <= (wide ? 128 : 16); }
+
+// Rows of the tiles to use when the requests of a step bring at most max_tokens tokens each: the smallest
+// tile that holds them (8, 16 or 128), or 0 when this kernel does not take the head and group size.
+Q6K_API int q6k_attention_mma_tile_rows(int hd, int G, int max_tokens) {
+    if (!q6k_attention_mma_supported(hd, G, 1)) return 0;
+    if ((long long)G * max_tokens <= 8) return 8;
+    if ((long long)G * max_tokens <= 16) return 16;
+    return 128;
+}
+
+// CTAs of the kernel for tiles of `rows` rows that the current device holds at once: the plan of a launch splits the
+// keys over exactly this many, so that one wave does all the work.  0 on an error or an unsupported shape.
+Q6K_API int q6k_attention_mma_resident_ctas(int hd, int rows) {
+    int dev = 0, sms = 0, per = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return 0;
+    if (hd == 128) per = rows == 128 ? resident_per_sm<128, 16, true>() : rows == 16 ? resident_per_sm<128, 16, false>() : resident_per_sm<128, 8, false>();
+    else if (hd == 64) per = rows == 128 ? resident_per_sm<64, 16, true>() : rows == 16 ? resident_per_sm<64, 16, false>() : resident_per_sm<64, 8, false>();
+    return per * sms;
+}
 
 Q6K_API int q6k_attention_status() {
     int v = -1;
@@ -659,16 +771,17 @@ Q6K_API int q6k_attention_plan(const int* positions, const int* req_of_token, co
 
 // q: bfloat16 [T, Hq, hd]; pages: bfloat16 [Hkv, num_pages, page_size, hd] (num_pages: pages in each pool; the TMA path
 // addresses a pool as one [Hkv * num_pages * page_size, hd] matrix); work / tile_plan: what q6k_attention_plan made for
-// these tiles (of at most (wide ? 128 : 16) / G tokens each) and this window; part_o: FP32 [n_work * Hkv * rows * hd],
-// part_ml: FP32 [n_work * Hkv * rows * 2] with rows = wide ? 128 : 16 (unused when n_work == n_tiles).
+// these tiles (of at most rows / G tokens each; rows: 8, 16 or 128) and this window; part_o: FP32 [n_work * Hkv * rows * hd],
+// part_ml: FP32 [n_work * Hkv * rows * 2] (unused when n_work == n_tiles).
 Q6K_API int q6k_attention_mma(const void* q, const void* k_pages, const void* v_pages, long long num_pages, const int* block_table,
-                              int max_blocks, int page_size, const int* work, const int* tile_plan, int n_work, int n_tiles, int wide,
+                              int max_blocks, int page_size, const int* work, const int* tile_plan, int n_work, int n_tiles, int rows,
                               int window, const float* sinks, float scale, void* out, float* part_o, float* part_ml, int Hq, int Hkv,
                               int hd, cudaStream_t st) {
     if (n_tiles == 0) return 0;
     Q6K_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention_mma: bad head counts Hq=%d Hkv=%d", Hq, Hkv);
     const int G = Hq / Hkv;
-    Q6K_REQUIRE(q6k_attention_mma_supported(hd, G, wide), "attention_mma: head_dim %d / group size %d is not covered by the tensor-core kernel", hd, G);
+    Q6K_REQUIRE(rows == 8 || rows == 16 || rows == 128, "attention_mma: tiles of %d rows (8, 16 or 128 are built)", rows);
+    Q6K_REQUIRE(q6k_attention_mma_supported(hd, G, rows == 128) && G <= rows, "attention_mma: head_dim %d / group size %d is not covered by tiles of %d rows", hd, G, rows);
     Q6K_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0 && n_work >= n_tiles && work && tile_plan,
                 "attention_mma: bad page_size %d / max_blocks %d / window %d / %d work items for %d tiles", page_size, max_blocks, window, n_work, n_tiles);
     Q6K_REQUIRE(n_work == n_tiles || (part_o && part_ml), "attention_mma: splitting the keys needs the partial buffers");
@@ -694,5 +807,5 @@ Q6K_API int q6k_attention_mma(const void* q, const void* k_pages, const void* v_
         if (int rc = pool_map(&maps[2], k_pages, pool_rows, hd, KT)) return rc;
         if (int rc = pool_map(&maps[3], v_pages, pool_rows, hd, KT)) return rc;
     }
-    return hd == 128 ? launch_hd<128>(p, maps, wide, tma, n_tiles, st) : launch_hd<64>(p, maps, wide, tma, n_tiles, st);
+    return hd == 128 ? launch_hd<128>(p, maps, rows, tma, n_tiles, st) : launch_hd<64>(p, maps, rows, tma, n_tiles, st);
 }

@@ -268,10 +268,24 @@ struct Scheduler {
     std::unordered_map<int64_t, SchedRequest> by_id;
     std::vector<Entry> last;                      // the entries of the step in flight
 
+    // Most tokens one request can ever hold: the smallest pool of a group that keeps every key bounds it.  A sliding
+    // group holds a window's worth of pages whatever the length, so its (smaller) pool bounds nothing.
     int64_t capacity_tokens() const {
-        int64_t least = INT64_MAX;
-        for (auto& p : cm->pools) least = std::min<int64_t>(least, p.n);
-        return cm->pools.empty() ? (int64_t)1 << 60 : least * cm->page_size;
+        int64_t least = (int64_t)1 << 60;
+        for (size_t g = 0; g < cm->pools.size(); ++g)
+            if (!cm->groups[g].sliding) least = std::min<int64_t>(least, (int64_t)cm->pools[g].n * cm->page_size);
+        return least;
+    }
+    // A sliding group must hold its window and one more token wherever they lie on the pages, or no request could ever advance.
+    int check_pools() const {
+        for (size_t g = 0; g < cm->pools.size(); ++g) {
+            if (!cm->groups[g].sliding) continue;
+            const int need = (cm->groups[g].window + cm->page_size - 1) / cm->page_size + 1;
+            if (cm->pools[g].n < need)
+                return fail(E_VALUE, "cache group %d: %d pages cannot hold a window of %d keys and the next token (%d pages of %d)", (int)g,
+                            cm->pools[g].n, cm->groups[g].window, need, cm->page_size);
+        }
+        return OK;
     }
     int release(int64_t id) { return cm->remove(id); }
     int finish(SchedRequest& r, int reason) {
@@ -553,6 +567,10 @@ API void* q6k_sched_create(void* cm, int max_batch_tokens, int max_running) {
     }
     auto* s = new Scheduler();
     s->cm = (CacheManager*)cm, s->max_batch_tokens = max_batch_tokens, s->max_running = max_running;
+    if (s->check_pools()) {
+        delete s;
+        return nullptr;
+    }
     return s;
 }
 API void q6k_sched_destroy(void* h) { delete (Scheduler*)h; }

@@ -122,11 +122,16 @@ class Engine:
         return rid
 
     def abort(self, rid: Hashable) -> None:
+        """End a live request now (reason "cancelled", the reference's Finish::Cancelled); the next
+        step() reports it with the tokens it had produced."""
         self._ended_early += self._resolve()     # every token known before the queue changes
-        self.scheduler.abort(rid)
+        req = self.scheduler.abort(rid)
+        if req is not None:
+            self._ended_early.append(req)
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_work() or self._inflight is not None or bool(self._held)
+        """Whether step() still has something to run or to report."""
+        return self.scheduler.has_work() or self._inflight is not None or bool(self._held) or bool(self._ended_early)
 
     # ------------------------------------------------------------------ stepping
     def _device_picks(self) -> bool:

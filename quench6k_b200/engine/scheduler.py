@@ -101,6 +101,25 @@ class ScheduledStep:
         return sum(e.count for e in self.entries)
 
 
+def capacity_tokens(manager) -> int:
+    """Most tokens one request can ever hold: the smallest pool of a group that keeps every key
+    bounds it.  A sliding group holds a window's worth of pages whatever the length, so its
+    (possibly much smaller) pool bounds nothing."""
+    full = [p.num_pages for p, g in zip(manager.pools, manager.groups) if g.kind != "sliding"]
+    return min(full) * manager.page_size if full else 1 << 60
+
+
+def check_pools(manager) -> None:
+    """A sliding group must hold its window and one more token wherever they lie on the pages,
+    or no request could ever advance."""
+    for i, (p, g) in enumerate(zip(manager.pools, manager.groups)):
+        if g.kind == "sliding":
+            need = -(-g.window // manager.page_size) + 1
+            if p.num_pages < need:
+                raise ValueError(f"cache group {i}: {p.num_pages} pages cannot hold a window of {g.window} keys and the next token "
+                                 f"({need} pages of {manager.page_size})")
+
+
 class PyScheduler:
     """`on_admit(slot)` is called for every request admitted by `schedule()`, before it returns, so
     that the caller can clear the per-request state in that slot."""
@@ -110,6 +129,7 @@ class PyScheduler:
         if max_batch_tokens < 1:
             raise ValueError("max_batch_tokens must be at least 1")
         self.manager = manager
+        check_pools(manager)
         self.max_batch_tokens = max_batch_tokens
         self.max_running = max_running if max_running is not None else manager.slots.num_slots
         self._admit = manager.add
@@ -121,8 +141,7 @@ class PyScheduler:
 
     # ------------------------------------------------------------------ queue
     def capacity_tokens(self) -> int:
-        """Most tokens one request can ever hold: the smallest pool bounds it."""
-        return min(p.num_pages for p in self.manager.pools) * self.manager.page_size if self.manager.pools else 1 << 60
+        return capacity_tokens(self.manager)
 
     def add(self, req: Request) -> None:
         if req.rid in self.by_id:
@@ -322,7 +341,7 @@ class NativeScheduler:
 
     # ------------------------------------------------------------------ queue
     def capacity_tokens(self) -> int:
-        return min(p.num_pages for p in self.manager.pools) * self.manager.page_size if self.manager.pools else 1 << 60
+        return capacity_tokens(self.manager)
 
     def _queue(self, which: int) -> List[Request]:
         cap = len(self.by_id) + 1

@@ -468,6 +468,32 @@ def attention_mma_supported(hd: int, G: int, wide: bool) -> bool:
     return bool(lib.q6k_attention_mma_supported(_i(hd), _i(G), _i(1 if wide else 0)))
 
 
+def attention_mma_tile_rows(hd: int, G: int, max_tokens: int) -> int:
+    """Query rows of the tiles attention_mma should be given when no request brings more than
+    max_tokens tokens to the step: 8, 16 or 128 (a tile holds rows // G tokens); 0 if the kernel
+    does not take this head and group size."""
+    lib = library()
+    lib.q6k_attention_mma_tile_rows.restype = ctypes.c_int
+    return lib.q6k_attention_mma_tile_rows(_i(hd), _i(G), _i(max_tokens))
+
+
+_resident = {}
+
+
+def attention_mma_resident_ctas(hd: int, rows: int) -> int:
+    """CTAs of attention_mma (tiles of `rows` rows) the current device runs at once: the number of
+    work items per launch (over all KV heads) that makes exactly one wave."""
+    key = (torch.cuda.current_device(), hd, rows)
+    if key not in _resident:
+        lib = library()
+        lib.q6k_attention_mma_resident_ctas.restype = ctypes.c_int
+        n = lib.q6k_attention_mma_resident_ctas(_i(hd), _i(rows))
+        if n <= 0:
+            raise KernelError(f"attention_mma: no resident CTA count for head_dim {hd}, tiles of {rows} rows")
+        _resident[key] = n
+    return _resident[key]
+
+
 def attention_plan(positions: torch.Tensor, req_of_token: torch.Tensor, tile_tok0: torch.Tensor, tile_ntok: torch.Tensor,
                    window: Optional[int], n_work: int, min_per: int = 2, into=None):
     """Which CTA of attention_mma walks which key tiles, made on the device from the step's
@@ -494,11 +520,11 @@ def attention_plan(positions: torch.Tensor, req_of_token: torch.Tensor, tile_tok
 
 def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                   req_of_token: torch.Tensor, positions: torch.Tensor, tile_tok0: torch.Tensor, tile_ntok: torch.Tensor,
-                  wide: bool, window: Optional[int], sinks: Optional[torch.Tensor], max_splits: int = 1, min_tiles: int = 2,
+                  rows: int, window: Optional[int], sinks: Optional[torch.Tensor], max_splits: int = 1, min_tiles: int = 2,
                   scale: Optional[float] = None, out: Optional[torch.Tensor] = None, plan=None) -> torch.Tensor:
     """bfloat16 tensor-core attention over the pages.  Tiles: tile_tok0[i] is the first row and
-    tile_ntok[i] the number of tokens (consecutive positions of one request, at most
-    (128 if wide else 16) // G) of tile i.  plan: attention_plan(...) of these tiles and this
+    tile_ntok[i] the number of tokens (consecutive positions of one request, at most rows // G;
+    rows: 8, 16 or 128, see attention_mma_tile_rows) of tile i.  plan: attention_plan(...) of these tiles and this
     window; without one it is made here for max_splits CTAs per tile on average, none with fewer
     than min_tiles key tiles.  Only the rows of the listed tiles are written (into `out`
     [T, Hq*hd] when given)."""
@@ -525,12 +551,12 @@ def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
         _need(out, "out", torch.bfloat16, (T, Hq * hd))
     part_o = part_ml = None
     if n_work > n_tiles:
-        rows = n_work * Hkv * (128 if wide else 16)
-        ws = _workspace(rows * (hd + 2) * 4, q.device)
-        part_o = ws[: rows * hd]
-        part_ml = ws[rows * hd: rows * (hd + 2)]
+        part_rows = n_work * Hkv * rows
+        ws = _workspace(part_rows * (hd + 2) * 4, q.device)
+        part_o = ws[: part_rows * hd]
+        part_ml = ws[part_rows * hd: part_rows * (hd + 2)]
     _call("q6k_attention_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ll(num_pages), _ptr(block_table),
-          _i(block_table.shape[1]), _i(page_size), _ptr(work), _ptr(tile_plan), _i(n_work), _i(n_tiles), _i(1 if wide else 0),
+          _i(block_table.shape[1]), _i(page_size), _ptr(work), _ptr(tile_plan), _i(n_work), _i(n_tiles), _i(rows),
           _i(window or 0), _ptr(sinks), _f(scale if scale is not None else 1.0 / math.sqrt(hd)), _ptr(out), _ptr(part_o), _ptr(part_ml),
           _i(Hq), _i(Hkv), _i(hd), _stream())
     return out

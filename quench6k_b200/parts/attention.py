@@ -82,61 +82,49 @@ class Attention(Mixer):
         return linear.matmul(a, self.w_o, rt, partials_ok=True)
 
     def _attend(self, q, cache, table, ctx):
-        """Tensor-core kernel for bfloat16 where it covers the head and group size, else the generic one."""
+        """The tensor-core kernels for bfloat16 where they cover the head and group size, else the generic one."""
         rt, G = self.rt, self.Hq // self.Hkv
-        if rt.is_fp32 or not rt.tensor_cores:
+        rows = 0 if rt.is_fp32 or not rt.tensor_cores else ops.attention_mma_tile_rows(self.hd, G, ctx.max_q_len)
+        if not rows:
             return ops.attention_generic(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, self.window, self.sinks, self.scale)
-        narrow_tokens = max(1, 16 // G)
-        wide = ctx.max_q_len > narrow_tokens or not ops.attention_mma_supported(self.hd, G, False)
-        if not ops.attention_mma_supported(self.hd, G, wide):
-            return ops.attention_generic(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, self.window, self.sinks, self.scale)
-        if wide and ops.attention_tc_supported(self.hd, G, cache.page_size):
+        if rows > 16 and ops.attention_tc_supported(self.hd, G, cache.page_size):
             tile = ops.attention_tc_tile_tokens(G)
             # beside prompt portions, requests with a few tokens (decoded tokens, the stub of a prompt) go to the kernel
             # that splits the keys over CTAs: as a tile of their own they would walk their whole context in one CTA
             cut = tile // 2 if ctx.R > 1 else 0
             tok0, ntok, n_pairs = ctx.query_tile_pairs(tile, zigzag=False, more_than=cut)
-            if 2 * n_pairs * self.Hkv >= self._sm_count():
-                # prompt portions with enough tiles for at least half of the SMs: both products on tcgen05, no key splits
+            if n_pairs * self.Hkv >= self.tc_min_fill * self._sm_count():
+                # prompt portions with enough tiles (two to a CTA) to fill that share of the SMs: both products on tcgen05, no key splits
                 out = ops.attention_tc(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, tok0, ntok, self.window,
                                        self.sinks, scale=self.scale)
                 count, _, _, most, _ = ctx.short_requests(cut)
                 if count:
-                    self._split_keys(q, cache, table, ctx, most > narrow_tokens or not ops.attention_mma_supported(self.hd, G, False),
-                                     at_most=cut, out=out)
+                    self._split_keys(q, cache, table, ctx, ops.attention_mma_tile_rows(self.hd, G, most), at_most=cut, out=out)
                 return out
-        return self._split_keys(q, cache, table, ctx, wide)
+        return self._split_keys(q, cache, table, ctx, rows)
 
-    def _split_keys(self, q, cache, table, ctx, wide, at_most=None, out=None):
+    tc_min_fill = 0.5             # the tcgen05 prompt kernel runs when its CTAs (two tiles each) cover at least this share of the SMs
+
+    def _split_keys(self, q, cache, table, ctx, rows, at_most=None, out=None):
         """The mma.sync kernel over all requests of the step, or over those with at most `at_most` tokens."""
         G = self.Hq // self.Hkv
-        tokens = (128 if wide else 16) // G
+        tokens = rows // G
         tok0, ntok, n_tiles = ctx.query_tiles(tokens, at_most)
         # the keys are split over one wave of resident CTAs, and no further (a second, partly filled wave would cost as
         # much as a full one); the plan is made on the device, once per step for all layers with this window
         key = ("attention_plan", tokens, at_most, self.window, self.Hkv)
         if key not in ctx.made:                     # the first layer of this pass with these tiles and this window
             ctx.plans[key] = ops.attention_plan(ctx.positions, ctx.req_of_token, tok0, ntok, self.window,
-                                                self._resident_ctas(wide) // self.Hkv, min_per=2, into=ctx.plans.get(key))
+                                                ops.attention_mma_resident_ctas(self.hd, rows) // self.Hkv, min_per=2,
+                                                into=ctx.plans.get(key))
             ctx.made.add(key)
-        return ops.attention_mma(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, tok0, ntok, wide, self.window,
+        return ops.attention_mma(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, tok0, ntok, rows, self.window,
                                  self.sinks, scale=self.scale, out=out, plan=ctx.plans[key])
 
     def _sm_count(self) -> int:
         if "_sms" not in self.__dict__:
             self._sms = torch.cuda.get_device_properties(self.rt.device).multi_processor_count
         return self._sms
-
-    def _resident_ctas(self, wide: bool) -> int:
-        """CTAs of the tensor-core attention kernel that fit on the GPU at once (shared memory bound)."""
-        key = ("resident", wide)
-        if key not in self.__dict__:
-            props = torch.cuda.get_device_properties(self.rt.device)
-            stages = 3 if self.hd == 128 else 4
-            smem = 2 * stages * 64 * self.hd * 2 + (128 if wide else 16) * self.hd * 2 + 2048
-            per_sm = max(1, min(2 if self.hd == 128 else 3, (props.shared_memory_per_multiprocessor - 1024) // smem))
-            self.__dict__[key] = per_sm * props.multi_processor_count
-        return self.__dict__[key]
 
     def _unfused_position(self, qkv, ctx, write):
         """QK-norm, then a position encoding that is no rotation of pairs (its own `apply`), on FP32 q and k."""

@@ -93,6 +93,31 @@ def test_stop_token_ends_generation(tmp_path):
     assert out.finish_reason == "stop" and out.tokens == free[:free.index(stop) + 1]
 
 
+@pytest.mark.parametrize("lookahead", [False, True])
+def test_abort_reports_the_cancelled_request_and_what_had_just_ended(tmp_path, lookahead):
+    """Aborting the last live request while another has ended but is not yet reported: a caller
+    that loops `while has_unfinished(): step()` gets both, the aborted one with reason "cancelled"."""
+    from quench6k_b200 import Engine, SamplingParams
+    cfg, _ = helpers.make_model_folder(str(tmp_path), "A", seed=27)
+    eng = Engine.from_folder(str(tmp_path), dtype="float32", num_pages=32, lookahead=lookahead)
+    short = eng.add_request(helpers.random_tokens(5, cfg["vocab_size"], 1), SamplingParams(max_tokens=2, temperature=0.0))
+    long = eng.add_request(helpers.random_tokens(6, cfg["vocab_size"], 2), SamplingParams(max_tokens=50, temperature=0.0))
+    outs = []
+    for _ in range(3):                              # prompts, then decode steps: the short request has produced its two tokens
+        outs += eng.step()
+    eng.abort(long)
+    while eng.has_unfinished():
+        outs += eng.step()
+    by = {o.rid: o for o in outs}
+    assert set(by) == {short, long}
+    assert by[short].finish_reason == "length" and len(by[short].tokens) == 2
+    assert by[long].finish_reason == "cancelled" and 1 <= len(by[long].tokens) < 50 and -1 not in by[long].tokens
+    eng.runner.manager.check()
+    assert not eng.runner.manager.requests
+    eng.abort(long)                                 # aborting what has ended is a no-op
+    assert not eng.has_unfinished()
+
+
 def test_command_line(tmp_path):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     cfg, weights = helpers.make_model_folder(str(tmp_path), "A", seed=25)

@@ -394,11 +394,12 @@ def test_gemm_tc_grouped(T, k, E, D, I):
 @pytest.mark.parametrize("Hq,Hkv,hd,ps,window,sinks", [(32, 4, 128, 16, None, False), (8, 2, 64, 8, None, True),
                                                         (6, 2, 128, 16, 100, True), (16, 1, 64, 32, 37, False),
                                                         (5, 5, 128, 4, None, False)])
-@pytest.mark.parametrize("mode", ["decode", "portions"])
+@pytest.mark.parametrize("mode", ["decode", "a few tokens", "portions"])
 def test_attention_mma(Hq, Hkv, hd, ps, window, sinks, mode):
-    """Several requests of different lengths in one launch; decode rows (narrow tiles, keys split
-    over CTAs and merged) or prompt portions (wide tiles); against float64 with one far key made
-    to stand out."""
+    """Several requests of different lengths in one launch; decode rows (narrow tiles of 8 or 16
+    rows, keys split over CTAs and merged), a few tokens per request, or prompt portions (wide
+    tiles); against float64 with one far key made to stand out.  Pages of 4 keys take the
+    producer's cp.async path instead of TMA."""
     from quench6k_b200 import ops
     G = Hq // Hkv
     g = torch.Generator().manual_seed(Hq * 1000 + hd + (window or 0))
@@ -431,6 +432,8 @@ def test_attention_mma(Hq, Hkv, hd, ps, window, sinks, mode):
     bt = torch.tensor([t + [-1] * (width - len(t)) for t in tables], dtype=torch.int32, device=DEV)
     sk = refs[0][1].to(DEV) if sinks else None
     if mode == "decode":
+        q_lens = [1] * len(lens)
+    elif mode == "a few tokens":
         q_lens = [min(2, max(1, 16 // G))] * len(lens) if G <= 8 else [1] * len(lens)
         q_lens[1] = 1
     else:
@@ -438,8 +441,10 @@ def test_attention_mma(Hq, Hkv, hd, ps, window, sinks, mode):
     starts = [n - ql for n, ql in zip(lens, q_lens)]
     ctx = helpers.make_context(q_lens, starts, [tables])
     q = torch.cat([qs[r][starts[r]:] for r in range(len(lens))]).contiguous().to(DEV)
-    wide = mode == "portions"
-    tok0, ntok, n_tiles = ctx.query_tiles((128 if wide else 16) // G)
+    wide = ops.attention_mma_tile_rows(hd, G, max(q_lens))
+    assert wide == (128 if mode == "portions" else 8 if G * max(q_lens) <= 8 else 16)
+    assert ops.attention_mma_resident_ctas(hd, wide) >= torch.cuda.get_device_properties(0).multi_processor_count
+    tok0, ntok, n_tiles = ctx.query_tiles(wide // G)
     want = torch.cat([refs[r][0][starts[r]:] for r in range(len(lens))]).reshape(-1, Hq * hd)
     for max_splits in (1, 4, 64):
         out = ops.attention_mma(q, kp.to(DEV), vp.to(DEV), bt, ctx.req_of_token, ctx.positions, tok0, ntok, wide, window, sk,
@@ -582,14 +587,14 @@ def test_attention_tc(Hq, Hkv, ps, window, sinks):
     tile = ops.attention_tc_tile_tokens(G)
     cut = tile // 2
     count, row0, row1, most, reach = ctx.short_requests(cut)
-    wide = most > max(1, 16 // G) or not ops.attention_mma_supported(hd, G, False)
-    if count and ops.attention_mma_supported(hd, G, wide):
+    wide = ops.attention_mma_tile_rows(hd, G, most)
+    if count and wide:
         assert count == sum(1 for n in q_lens if n <= cut) and (row0, row1) == (sum(q_lens[:2]) if q_lens[2] <= cut else sum(q_lens[:3]), sum(q_lens[:4]))
         out = torch.full((q.shape[0], Hq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
         tok0, ntok, n_pairs = ctx.query_tile_pairs(tile, False, more_than=cut)
         ops.attention_tc(q, kp.to(DEV), vp.to(DEV), bt, ctx.req_of_token, ctx.positions, tok0, ntok, window, sk.to(DEV) if sinks else None, out=out)
         assert torch.isnan(out[row0:row1].float()).any() and not torch.isnan(out[:row0].float()).any()
-        s0, sn, n_short = ctx.query_tiles((128 if wide else 16) // G, at_most=cut)
+        s0, sn, n_short = ctx.query_tiles(wide // G, at_most=cut)
         ops.attention_mma(q, kp.to(DEV), vp.to(DEV), bt, ctx.req_of_token, ctx.positions, s0, sn, wide, window,
                           sk.to(DEV) if sinks else None, max_splits=3, min_tiles=1, out=out)
         assert ops.tc_status() == 0

@@ -238,3 +238,26 @@ def test_placeholder_tokens_are_patched_and_a_late_stop_ends_the_request():
     s.set_output_token(c, 0, 3)
     s.stop_at(c, 1)
     assert c.finish_reason == FINISH_STOP and c.output == [3] and not s.has_work()
+
+
+def test_a_small_sliding_pool_bounds_nothing():
+    """The capacity of a request is what the groups that keep every key can hold; a sliding group
+    with a pool of a window's worth of pages neither refuses a long prompt nor ends a request early."""
+    groups = [GroupSpec("full"), GroupSpec("sliding", 9)]
+    m = CacheManager(groups, 4, [40, 8], 2)                  # 160 token places in the full group, 32 in the sliding one
+    s = Scheduler(m, max_batch_tokens=6)
+    assert s.capacity_tokens() == 160
+    s.add(req("long", 100, max_tokens=20))                   # far beyond the sliding pool's 32 places
+    with pytest.raises(ValueError):
+        s.add(req("too long", 160))
+    done = []
+    for _ in range(200):
+        if not s.has_work():
+            break
+        _, d = run_step(m, s)
+        done += d
+    assert [r.rid for r in done] == ["long"] and done[0].finish_reason == FINISH_LENGTH and len(done[0].output) == 20
+    assert m.pools[0].num_free == 40 and m.pools[1].num_free == 8
+    # a sliding pool that cannot hold its window and one more token is refused when the scheduler is made
+    with pytest.raises(ValueError, match="window of 9 keys"):
+        Scheduler(CacheManager(groups, 4, [40, 3], 2), max_batch_tokens=6)

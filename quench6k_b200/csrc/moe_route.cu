@@ -13,41 +13,13 @@
 
 namespace {
 
-// Top-k of one token's scores held in shared memory v[0..E) by one warp: ties to the lower index.
-// Writes the chosen experts and weights (renormalised if asked).  `total` divides softmax scores.
-__device__ __forceinline__ void warp_topk(float* v, int E, int k, int sigmoid, int renorm, float total, int* sel_e, float* sel_w) {
-    const int lane = threadIdx.x & 31;
-    float chosen_sum = 0.0f, mine = 0.0f;
-    for (int r = 0; r < k; ++r) {
-        float best = -1.0f;
-        int best_i = 0x7fffffff;
-        for (int e = lane; e < E; e += 32)
-            if (v[e] > best) best = v[e], best_i = e;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
-            if (ob > best || (ob == best && oi < best_i)) best = ob, best_i = oi;
-        }
-        const float score = sigmoid ? best : best / total;
-        chosen_sum += score;
-        if (lane == 0) {
-            sel_e[r] = best_i;
-            v[best_i] = -2.0f;
-        }
-        if (lane == r) mine = score;                 // lane r keeps the r-th score (r < 32; later ones: below)
-        if (r >= 32 && lane == 0) sel_w[r] = score;
-        __syncwarp();
-    }
-    const float den = !renorm ? 1.0f : (sigmoid ? chosen_sum + 1e-20f : chosen_sum);
-    if (lane < k && lane < 32) sel_w[lane] = mine / den;
-    if (k > 32 && renorm && lane == 0)
-        for (int r = 32; r < k; ++r) sel_w[r] /= den;
-}
+// How a round of the selection works, in registers or in shared memory: the scores are not negative, so their
+// bits order like signed integers; a lane finds the largest of its own experts (the first of equal ones: its lowest
+// index), one warp reduction gives the largest of all, a second the lowest expert index among the lanes that hold
+// it (ties go to the lower expert), and that lane marks its entry as taken (bits -1).
 
-// The same with the scores in registers (lane l holds experts l, l + 32, ...; NL of them, E <= 32 NL):
-// a round is a maximum over the lane's registers, one warp reduction of the score (the bits of a
-// non-negative float order like a signed integer) and one of the index among the lanes that hold it.
+// Top-k of one token's scores by one warp, the scores in registers (lane l holds experts l, l + 32, ...; NL of
+// them, E <= 32 NL).  Writes the chosen experts and weights (renormalised if asked).  `total` divides softmax scores.
 template <int NL>
 __device__ __forceinline__ void warp_topk_regs(float (&val)[NL], int E, int k, int sigmoid, int renorm, float total, int* sel_e, float* sel_w) {
     const int lane = threadIdx.x & 31;
@@ -80,13 +52,41 @@ __device__ __forceinline__ void warp_topk_regs(float (&val)[NL], int E, int k, i
         for (int r = 32; r < k; ++r) sel_w[r] /= den;
 }
 
+// The same for any number of experts, the scores' bits in shared memory bits[0..E) (lane l looks after l, l + 32, ...).
+__device__ __forceinline__ void warp_topk_shared(int* bits, int E, int k, int sigmoid, int renorm, float total, int* sel_e, float* sel_w) {
+    const int lane = threadIdx.x & 31;
+    float chosen_sum = 0.0f, mine = 0.0f;
+    for (int r = 0; r < k; ++r) {
+        int best = -1, best_e = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const int b = bits[e];
+            if (b > best) best = b, best_e = e;
+        }
+        const int top = __reduce_max_sync(0xffffffffu, best);
+        const int idx = __reduce_min_sync(0xffffffffu, best == top ? best_e : 0x7fffffff);
+        if ((idx & 31) == lane) bits[idx] = -1;
+        const float best_f = __int_as_float(top);
+        const float score = sigmoid ? best_f : best_f / total;
+        chosen_sum += score;
+        if (lane == 0) sel_e[r] = idx;
+        if (lane == r) mine = score;                 // lane r keeps the r-th score (r < 32; later ones: below)
+        if (r >= 32 && lane == 0) sel_w[r] = score;
+    }
+    const float den = !renorm ? 1.0f : (sigmoid ? chosen_sum + 1e-20f : chosen_sum);
+    __syncwarp();
+    if (lane < k && lane < 32) sel_w[lane] = mine / den;
+    if (k > 32 && renorm && lane == 0)
+        for (int r = 32; r < k; ++r) sel_w[r] /= den;
+}
+
 // One token's scores from its logits (sigmoid, or the numerators of the softmax and their sum), then the top-k.
-template <int NL>
+// z: the logits in global memory (written by other blocks of this kernel: read past L1) or, SHARED, in shared memory.
+template <int NL, bool SHARED = false>
 __device__ __forceinline__ void warp_route_regs(const float* z, int E, int k, int sigmoid, int renorm, int* sel_e, float* sel_w) {
     const int lane = threadIdx.x & 31;
     float val[NL];
 #pragma unroll
-    for (int i = 0; i < NL; ++i) val[i] = lane + 32 * i < E ? __ldcg(z + lane + 32 * i) : -INFINITY;
+    for (int i = 0; i < NL; ++i) val[i] = lane + 32 * i < E ? (SHARED ? z[lane + 32 * i] : __ldcg(z + lane + 32 * i)) : -INFINITY;
     float total = 1.0f;
     if (sigmoid) {
 #pragma unroll
@@ -125,6 +125,11 @@ __global__ void route_kernel(const float* logits, int slices, size_t slice_strid
     for (int e = lane; e < E; e += 32) v[e] = z[e];
     for (int s = 1; s < slices; ++s)                     // slice by slice: a lane's loads of one slice do not wait for one another
         for (int e = lane; e < E; e += 32) v[e] += z[s * slice_stride + e];
+    __syncwarp();
+    int* se = sel_e + (size_t)t * k;
+    float* sw = sel_w + (size_t)t * k;
+    if (E <= 256) return warp_route_regs<8, true>(v, E, k, sigmoid, renorm, se, sw);
+    if (E <= 704) return warp_route_regs<22, true>(v, E, k, sigmoid, renorm, se, sw);
     float total = 1.0f;
     if (sigmoid) {
         for (int e = lane; e < E; e += 32) {
@@ -145,7 +150,7 @@ __global__ void route_kernel(const float* logits, int slices, size_t slice_strid
         total = warp_sum(sum);
     }
     __syncwarp();
-    warp_topk(v, E, k, sigmoid, renorm, total, sel_e + (size_t)t * k, sel_w + (size_t)t * k);
+    warp_topk_shared(reinterpret_cast<int*>(v), E, k, sigmoid, renorm, total, se, sw);
 }
 
 // Router of a decode step in one launch (reference: router_kernel, crates/cuda/kernels/flint.cu:1002-1055,
@@ -446,15 +451,20 @@ Q6K_API int q6k_route(const float* logits, int slices, int T_, int E, int k, int
     return q6k_check_launch("route");
 }
 
+// Whether the one-launch decode router takes a step of T tokens with E experts of width D (k of them per token).
+Q6K_API int q6k_router_small_supported(int T_, int E, int D, int k) {
+    return T_ > 0 && T_ <= SMALL_T && E > 0 && E <= 704 && k > 0 && k <= E && D > 0 && D % 8 == 0;
+}
+
 // xn: bfloat16 [T, D], T <= 16, D a multiple of 8; w: bfloat16 [E, D]; logits: FP32 [T, E] scratch;
 // ticket: one zeroed 32-bit word that the kernel leaves zeroed.
 // order: int32 [T*k], the pairs (token * k + slot) sorted by expert, ties in pair order.
 Q6K_API int q6k_router_small(const void* xn, const void* w, int T_, int E, int D, int k, int sigmoid, int renorm, float* logits,
                              int* sel_e, float* sel_w, int* order, unsigned* ticket, cudaStream_t st) {
     if (T_ == 0) return 0;
-    Q6K_REQUIRE(T_ > 0 && T_ <= SMALL_T, "router_small: %d tokens exceed %d", T_, SMALL_T);
-    Q6K_REQUIRE(E > 0 && k > 0 && k <= E && E <= 704, "router_small: bad sizes E=%d k=%d (at most 704 experts)", E, k);
-    Q6K_REQUIRE(D > 0 && D % 8 == 0 && ((uintptr_t)xn & 15) == 0 && ((uintptr_t)w & 15) == 0, "router_small: D=%d must be a multiple of 8 and the operands 16-byte aligned", D);
+    Q6K_REQUIRE(q6k_router_small_supported(T_, E, D, k), "router_small: %d tokens, %d experts of width %d, %d per token (at most %d tokens, 704 experts)",
+                T_, E, D, k, SMALL_T);
+    Q6K_REQUIRE(((uintptr_t)xn & 15) == 0 && ((uintptr_t)w & 15) == 0, "router_small: D=%d must be a multiple of 8 and the operands 16-byte aligned", D);
     q6k_launch(router_small_kernel, E, 512, 16 * E * sizeof(float), st, (const __nv_bfloat16*)xn, (const __nv_bfloat16*)w, T_, E, D, k,
                                                                        sigmoid, renorm, logits, sel_e, sel_w, order, ticket);
     return q6k_check_launch("router_small");

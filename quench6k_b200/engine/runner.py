@@ -68,11 +68,19 @@ class ModelRunner:
             else:
                 g = self.group_of[p]
                 # head-major: a head's pages are contiguous; one page beyond the manager's pool takes what filler entries write
-                shape = (r.kv_heads, pages[g] + 1, page_size, r.head_dim)
-                self.caches.append(LayerCache(g, torch.zeros(shape, dtype=rt.dtype, device=rt.device),
-                                              torch.zeros(shape, dtype=rt.dtype, device=rt.device), page_size))
-        self.states = [None if s is None else torch.zeros((max_requests + 1, *s), dtype=torch.float32, device=rt.device)
-                       for s in model.state_shapes()]
+                lead, dt = (r.kv_heads, pages[g] + 1, page_size), r.dtype or rt.dtype
+                self.caches.append(LayerCache(g, torch.zeros((*lead, r.head_dim), dtype=dt, device=rt.device),
+                                              torch.zeros((*lead, r.v_dim or r.head_dim), dtype=dt, device=rt.device), page_size))
+
+        def state_for(s):
+            """One tensor [slots + 1, *shape] per declared state (the extra slot is the filler entries')."""
+            if s is None:
+                return None
+            if isinstance(s, dict):
+                return {name: torch.zeros((max_requests + 1, *shape), dtype=dt, device=rt.device) for name, (shape, dt) in s.items()}
+            return torch.zeros((max_requests + 1, *s), dtype=torch.float32, device=rt.device)
+
+        self.states = [state_for(s) for s in model.state_shapes()]
         self._pad_pages, self._pad_slot = list(pages), max_requests      # the page and the slot no request ever holds
         # steps whose shape repeats (above all decode steps) replay a CUDA graph per shape; the
         # reference captures one per sequence and token count (crates/engine/src/flint.rs:735-771)
@@ -122,8 +130,8 @@ class ModelRunner:
     def reset_slot(self, slot: int) -> None:
         """Clear the per-request state a new request finds in its slot."""
         for s in self.states:
-            if s is not None:
-                s[slot].zero_()
+            for t in (s.values() if isinstance(s, dict) else () if s is None else (s,)):
+                t[slot].zero_()
 
     def end_request(self, rid: Hashable) -> None:
         self.manager.remove(rid)

@@ -578,8 +578,15 @@ def route(logits: torch.Tensor, k: int, scoring: str, renorm: bool):
     return sel_e, sel_w
 
 
-SMALL_T = 16
 _tickets = {}
+
+
+def router_small_supported(T: int, E: int, D: int, k: int) -> bool:
+    """Whether the one-launch decode router (router_small, and with it the per-pair expert products) takes this step."""
+    lib = library()
+    lib.q6k_router_small_supported.restype = ctypes.c_int
+    return bool(lib.q6k_router_small_supported(_i(T), _i(E), _i(D), _i(k)))
+
 
 
 def router_small(xn: torch.Tensor, w: torch.Tensor, k: int, scoring: str, renorm: bool, with_logits: bool = False):

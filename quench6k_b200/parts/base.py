@@ -13,7 +13,8 @@ under a name with the matching `register_*`; a spec.PartSpec(kind=name, params=.
   PositionEncoding  tensors(); bind(); rotary_table() -> (inv_freq, rotary_dim, neighbours) for a rotation of pairs
                   of head dimensions (applied inside the q/k kernel), or None and then
                   apply(x_f32 [T, H, hd], positions_i32 [T]) -> None, in place
-  Mixer           tensors(); bind(); cache_request() -> CacheRequest | None; state_shape() -> tuple | None;
+  Mixer           tensors(); bind(); cache_request() -> CacheRequest | None (kind, window, heads, key and value widths, dtype);
+                  state_shape() -> None | shape of one float32 tensor | {name: (shape, dtype)};
                   forward(xn [T, D], ctx: StepContext, cache: LayerCache | None, state: Tensor | None, out_f32 [T, D])
                   adds its result into `out` and returns None, or leaves `out` alone and returns the
                   float32 [T, D] result (or [slices, T, D] partial sums) for the block's next norm to add
@@ -49,16 +50,19 @@ class CacheRequest:
     kind: str                           # "full": every key; "sliding": the last `window` keys
     window: Optional[int]
     kv_heads: int
-    head_dim: int
+    head_dim: int                       # width of a key
+    v_dim: Optional[int] = None         # width of a value; None: the key's
+    dtype: Optional[torch.dtype] = None  # what the pages hold; None: the runtime's operand dtype
 
     def key(self) -> Tuple:
-        return (self.kind, self.window, self.kv_heads, self.head_dim)
+        return (self.kind, self.window, self.kv_heads, self.head_dim, self.v_dim or self.head_dim, self.dtype)
 
 
 @dataclass
 class LayerCache:
-    """The pages of one executed layer position.  k, v: [kv_heads, num_pages, page_size, head_dim]
-    (head-major, so that pages with consecutive numbers lie next to each other for one head)."""
+    """The pages of one executed layer position.  k: [kv_heads, num_pages, page_size, head_dim],
+    v: [kv_heads, num_pages, page_size, v_dim] (head-major, so that pages with consecutive numbers
+    lie next to each other for one head)."""
     group: int
     k: torch.Tensor
     v: torch.Tensor
@@ -146,8 +150,10 @@ class Mixer(Part):
     def cache_request(self) -> Optional[CacheRequest]:
         return None
 
-    def state_shape(self) -> Optional[Tuple[int, ...]]:
-        """Shape of this mixer's fixed-size per-request state (float32), or None."""
+    def state_shape(self):
+        """This mixer's fixed-size per-request state: None, the shape of one float32 tensor, or
+        {name: (shape, dtype)} for several.  forward() gets the tensor [slots, *shape] (or the
+        dict of them), indexed by the request's slot; a slot is zeroed when it is handed out."""
         return None
 
     def forward(self, xn, ctx, cache: Optional[LayerCache], state: Optional[torch.Tensor], out: torch.Tensor) -> Optional[torch.Tensor]:

@@ -88,8 +88,8 @@ class RoutedExperts(FeedForward):
         T = xn.shape[0]
         pairs = T * self.k
         defer = defer and self.shared is None
-        if (T <= ops.SMALL_T and rt.tensor_cores and not rt.is_fp32 and self.E <= 704 and ops.tc_supported(xn, self.w_gate)
-                and self.I % 8 == 0):
+        if (rt.tensor_cores and not rt.is_fp32 and ops.router_small_supported(T, self.E, self.D, self.k)
+                and ops.tc_supported(xn, self.w_gate) and self.I % 8 == 0):
             # a decode step: router and top-k in one launch, then one weight tile stream per
             # (token, slot) pair straight from the selection, no permutation and no gather
             sel_e, sel_w, order, logits = ops.router_small(xn, self.w_router, self.k, self.scoring, self.renorm, with_logits=True)

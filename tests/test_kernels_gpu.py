@@ -139,7 +139,7 @@ def test_moe_plan_equals_its_parts(T, k, E, D, bm):
 
 @pytest.mark.parametrize("scoring", ["softmax", "sigmoid"])
 @pytest.mark.parametrize("renorm", [True, False])
-@pytest.mark.parametrize("T,E,k", [(9, 6, 3), (40, 256, 8), (5, 100, 100), (3, 3000, 6)])
+@pytest.mark.parametrize("T,E,k", [(9, 6, 3), (40, 256, 8), (5, 100, 100), (7, 500, 9), (3, 3000, 6), (2, 1500, 40)])
 def test_route(scoring, renorm, T, E, k):
     from quench6k_b200 import ops
     z = _t(T, E, scale=2.0)

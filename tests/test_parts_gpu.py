@@ -403,3 +403,102 @@ def test_toy_feed_forward_with_routing_and_toy_position_encoding(tmp_path):
     runner.manager.check()
     for got in (whole, torch.cat(parts)):
         assert (got - want).abs().max() <= 1e-4 * want.abs().max()
+
+
+def test_toy_mixer_with_unequal_key_and_value_widths_and_named_states(tmp_path):
+    """A mixer whose keys (12 wide) and values (20 wide) differ in width, whose pages are float32
+    whatever the engine's operand dtype, and which keeps two named per-request states of
+    different dtypes (how many tokens it has seen, int32; the last input row, float32), is defined
+    here and run through the unchanged framework in bfloat16: the runner makes its pages and
+    states from what the mixer declares."""
+    from dataclasses import dataclass
+    from quench6k_b200.config import register_architecture
+    from quench6k_b200.engine import ModelRunner, StepEntry
+    from quench6k_b200.parts import CacheRequest, Mixer, register_mixer
+    from quench6k_b200.spec import LayerSpec, ModelSpec, PartSpec, TensorSpec
+
+    KD, VD, PAGE = 12, 20, 4
+
+    @register_mixer("toy_narrow_keys")
+    class NarrowKeys(Mixer):
+        """One head; out = softmax(q k^T / sqrt(KD)) v Wo + 0.1 * (the row before this one), causal."""
+        def __init__(self, hidden_size):
+            self.D = hidden_size
+
+        def tensors(self):
+            return [TensorSpec("q.weight", (KD, self.D), "f32", ("normal", 0.3)), TensorSpec("k.weight", (KD, self.D), "f32", ("normal", 0.3)),
+                    TensorSpec("v.weight", (VD, self.D), "f32", ("normal", 0.3)), TensorSpec("o.weight", (self.D, VD), "f32", ("normal", 0.3))]
+
+        def bind(self, get, rt):
+            self.rt = rt
+            self.wq, self.wk, self.wv, self.wo = (get(n + ".weight").to(rt.device, torch.float32) for n in "qkvo")
+
+        def cache_request(self):
+            return CacheRequest("full", None, 1, KD, v_dim=VD, dtype=torch.float32)
+
+        def state_shape(self):
+            return {"seen": ((1,), torch.int32), "last": ((self.D,), torch.float32)}
+
+        def forward(self, xn, ctx, cache, state, out):
+            assert cache.k.shape[-1] == KD and cache.v.shape[-1] == VD and cache.k.dtype == torch.float32
+            assert state["seen"].dtype == torch.int32 and state["last"].shape[1:] == (self.D,)
+            x = xn.float()
+            table = ctx.block_tables[cache.group]
+            at = 0
+            for r, n in enumerate(ctx.q_lens):
+                p0, slot = ctx.pos_starts[r], ctx.slots[r]
+                assert int(state["seen"][slot]) == p0            # the state followed the request through its steps
+                rows = x[at:at + n]
+                pos = torch.arange(p0, p0 + n, device=x.device)
+                pages = table[r][(pos // PAGE).long()].long()
+                cache.k[0, pages, (pos % PAGE).long()] = rows @ self.wk.T
+                cache.v[0, pages, (pos % PAGE).long()] = rows @ self.wv.T
+                every = torch.arange(p0 + n, device=x.device)
+                k = cache.k[0, table[r][(every // PAGE).long()].long(), (every % PAGE).long()]
+                v = cache.v[0, table[r][(every // PAGE).long()].long(), (every % PAGE).long()]
+                s = (rows @ self.wq.T) @ k.T / math.sqrt(KD)
+                s = s.masked_fill(every[None, :] > pos[:, None], float("-inf"))
+                before = torch.cat([state["last"][slot][None], rows[:-1]])
+                out[at:at + n] += torch.softmax(s, -1) @ v @ self.wo.T + 0.1 * before
+                state["last"][slot] = rows[-1]
+                state["seen"][slot] += n
+                at += n
+
+    @dataclass
+    class ToyConfig:
+        hidden_size: int
+        vocab_size: int
+        architectures: list
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d["hidden_size"], d["vocab_size"], d["architectures"])
+
+    def build(cfg):
+        norm = PartSpec("rmsnorm", {"eps": 1e-5, "init": "random"})
+        layers = [LayerSpec("model.layers.0.", PartSpec("toy_narrow_keys", {}), PartSpec("dense", {"intermediate_size": 24}), norm)]
+        return ModelSpec(cfg.hidden_size, cfg.vocab_size, layers, order=[0, 0], kv_source=[None, None], final_norm=norm, init_std=0.2)
+
+    register_architecture("ToyNarrowKeysLM", ToyConfig, build)
+    runner = ModelRunner.from_random(ToyConfig(32, 50, ["ToyNarrowKeysLM"]), seed=2, dtype="bfloat16", page_size=PAGE, num_pages=16, max_requests=2)
+    assert not runner.cuda_graphs                               # the toy mixer reads host fields of the step: no graph replay
+    for c in runner.caches:
+        assert c.k.shape == (1, 17, PAGE, KD) and c.v.shape == (1, 17, PAGE, VD) and c.k.dtype == torch.float32
+    toks = {"a": helpers.random_tokens(19, 50, 3), "b": helpers.random_tokens(11, 50, 4)}
+    whole = {}
+    for rid, t in toks.items():
+        runner.add_request(rid)
+        whole[rid] = runner.step([StepEntry(rid, t, list(range(len(t))))]).cpu()
+        runner.end_request(rid)
+    runner.add_request("b"), runner.add_request("a")              # the slots the other way round: stale state would show
+    got = {"a": [], "b": []}
+    got["b"].append(runner.step([StepEntry("b", toks["b"][:4], list(range(4)))]).cpu())
+    o = runner.step([StepEntry("a", toks["a"][:13], list(range(13))), StepEntry("b", toks["b"][4:5], [0])]).cpu()
+    got["a"].append(o[:13]), got["b"].append(o[13:])
+    o = runner.step([StepEntry("b", toks["b"][5:], list(range(6))), StepEntry("a", toks["a"][13:], list(range(6)))]).cpu()
+    got["b"].append(o[:6]), got["a"].append(o[6:])
+    for rid in toks:
+        g = torch.cat(got[rid])
+        assert (g - whole[rid]).abs().max() <= 2e-2 * whole[rid].abs().max()
+    runner.end_request("a"), runner.end_request("b")
+    runner.manager.check()

@@ -64,12 +64,14 @@ def host_lib():
         "q6k_st_count": (i, [vp]),
         "q6k_st_entry": (i, [vp, i, ctypes.c_char_p, i, ctypes.c_char_p, _i64p, _i32p, _i64p, _i64p]),
         "q6k_st_read": (i, [vp, i, vp, i64]),
+        "q6k_st_read_range": (i, [vp, i, i64, vp, i64]),
+        "q6k_fill_normal_host": (i, [vp, i, i64, i64, ctypes.c_uint64, ctypes.c_float, ctypes.c_float, i]),
         "q6k_sample_rows": (i, [i, i, _i32p, _f32p, _i32p, _f32p, _i32p, _f32p, _f32p, _f32p, _f32p, _i32p, _i64p, _f64p, _i32p]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)
         fn.restype, fn.argtypes = res, args
-    if lib.q6k_host_abi_version() != 4:
+    if lib.q6k_host_abi_version() != 5:
         raise RuntimeError("the host library does not match this package")
     _lib = lib
     return lib

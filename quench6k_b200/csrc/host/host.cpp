@@ -25,6 +25,11 @@
 #include <fcntl.h>
 #include <sys/stat.h>
 #include <unistd.h>
+#include <cmath>
+#include <thread>
+
+#include "../fill_normal.h"
+
 
 #define API extern "C" __attribute__((visibility("default")))
 
@@ -441,7 +446,7 @@ int copy_out(const std::vector<T>& v, T* out, int cap, int* n, const char* what)
 }  // namespace
 
 API const char* q6k_host_last_error() { return g_msg; }
-API int q6k_host_abi_version() { return 4; }
+API int q6k_host_abi_version() { return 5; }
 
 // ------------------------------------------------------------------------------- cache manager
 API void* q6k_cm_create(int n_groups, const int* sliding, const int* windows, int page_size, const int* num_pages, int max_requests) {
@@ -1041,6 +1046,22 @@ API int q6k_st_entry(void* h, int i, char* name, int name_cap, char* dtype, int6
     *ndim = (int)e.shape.size(), *begin = e.begin, *end = e.end;
     return OK;
 }
+// nbytes of entry i from byte `offset` of its data into dst (a piece of a tensor: the loader streams large tensors through
+// two pinned staging buffers).
+API int q6k_st_read_range(void* h, int i, int64_t offset, void* dst, int64_t nbytes) {
+    StFile* f = (StFile*)h;
+    if (i < 0 || i >= (int)f->entries.size()) return fail(E_VALUE, "tensor index %d outside 0..%d", i, (int)f->entries.size() - 1);
+    const StEntry& e = f->entries[i];
+    if (offset < 0 || nbytes < 0 || offset + nbytes > e.end - e.begin)
+        return fail(E_VALUE, "tensor %s holds %lld bytes, bytes %lld..%lld were asked for", e.name.c_str(), (long long)(e.end - e.begin), (long long)offset,
+                    (long long)(offset + nbytes));
+    for (int64_t got = 0; got < nbytes;) {
+        const ssize_t r = pread(f->fd, (char*)dst + got, (size_t)std::min<int64_t>(nbytes - got, (int64_t)1 << 30), (off_t)(e.begin + offset + got));
+        if (r <= 0) return fail(E_VALUE, "tensor %s: the file ends early", e.name.c_str());
+        got += r;
+    }
+    return OK;
+}
 // The bytes of entry i into dst (nbytes must be the entry's size).
 API int q6k_st_read(void* h, int i, void* dst, int64_t nbytes) {
     StFile* f = (StFile*)h;
@@ -1052,5 +1073,43 @@ API int q6k_st_read(void* h, int i, void* dst, int64_t nbytes) {
         if (r <= 0) return fail(E_VALUE, "tensor %s: the file ends early", e.name.c_str());
         got += r;
     }
+    return OK;
+}
+
+
+// ------------------------------------------------------------------------------- random weights
+namespace q6k_fill {
+double sqrt_exact(double a) { return std::sqrt(a); }       // IEEE 754: correctly rounded
+}
+
+namespace {
+inline uint16_t bf16_bits(float v) {                        // round to nearest, ties to even (NaN stays NaN)
+    uint32_t u;
+    std::memcpy(&u, &v, sizeof u);
+    if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40);
+    return (uint16_t)((u + 0x7fffu + ((u >> 16) & 1u)) >> 16);
+}
+}  // namespace
+
+// out[i] = dtype(normal(key, start + i) * std + mean), i < n, on the host with `threads` threads; dtype 0: float32,
+// 1: bfloat16.  The device twin is q6k_fill_normal (csrc/fill.cu); both include fill_normal.h.
+API int q6k_fill_normal_host(void* out, int dtype, int64_t n, int64_t start, uint64_t key, float std, float mean, int threads) {
+    if (n < 0 || start < 0 || (dtype != 0 && dtype != 1)) return fail(E_VALUE, "fill_normal: bad range or dtype (start %lld, n %lld, dtype %d)", (long long)start, (long long)n, dtype);
+    auto work = [=](int64_t lo, int64_t hi) {
+        for (int64_t i = lo; i < hi; ++i) {
+            const float v = q6k_fill::element(key, (uint64_t)(start + i), std, mean);
+            if (dtype == 0) ((float*)out)[i] = v;
+            else ((uint16_t*)out)[i] = bf16_bits(v);
+        }
+    };
+    const int t = (int)std::max<int64_t>(1, std::min<int64_t>(threads, n / 65536));
+    if (t == 1) {
+        work(0, n);
+        return OK;
+    }
+    std::vector<std::thread> pool;
+    const int64_t per = (n + t - 1) / t;
+    for (int k = 0; k < t; ++k) pool.emplace_back(work, std::min<int64_t>(n, k * per), std::min<int64_t>(n, (k + 1) * per));
+    for (auto& th : pool) th.join();
     return OK;
 }

@@ -105,7 +105,10 @@ class ModelRunner:
         arch, cfg = load_config(folder)
         model = DecoderModel(arch.build_spec(cfg))
         rt = Runtime(torch.device(device), parse_dtype(dtype), tensor_cores)
-        model.bind(load_folder(folder, model.tensors(), model.spec.name_alias), rt)
+        get = load_folder(folder, model.tensors(), model.spec.name_alias, device=rt.device)
+        model.bind(get, rt)
+        if get.uploader is not None:
+            get.uploader.finish()
         ps = page_size or getattr(cfg, "kv_page_size", None) or 16
         return cls(model, rt, ps, num_pages, max_requests, cuda_graphs)
 

@@ -31,10 +31,18 @@ _GGUF_LAYER = {
     "ffn_gate.weight": "mlp.gate_proj.weight", "ffn_up.weight": "mlp.up_proj.weight", "ffn_down.weight": "mlp.down_proj.weight",
 }
 _GGUF_BLOCK = re.compile(r"^blk\.(\d+)\.(.+)$")
+# experts stored one by one, as checkpoints of this family of models usually hold them
+_ONE_EXPERT = re.compile(r"^(model\.layers\.\d+\.mlp\.experts)\.(\d+)\.((?:gate|up|down)_proj\.weight)$")
 
 
-def gguf_alias(name: str) -> Optional[str]:
-    """The declared name of a tensor stored under the reference's GGUF name, or None."""
+def gguf_alias(name: str):
+    """The declared name of a tensor stored under another name, or None: the reference's GGUF
+    names, and `...mlp.experts.{e}.{gate,up,down}_proj.weight` -> (the stacked tensor's name, e),
+    which the loader stacks as it reads (the reference addresses its stacked expert tensors
+    expert by expert the other way round, crates/engine/src/flint.rs:358-364)."""
+    m = _ONE_EXPERT.match(name)
+    if m:
+        return f"{m.group(1)}.{m.group(3)}", int(m.group(2))
     if name in _GGUF_TOP:
         return _GGUF_TOP[name]
     m = _GGUF_BLOCK.match(name)

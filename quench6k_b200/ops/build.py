@@ -28,7 +28,7 @@ NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
 
 HOST_LIB_NAME = "libq6k_host.so"
-HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall"]
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-Wall", "-ffp-contract=off", "-pthread"]
 
 _lock = threading.Lock()
 _lib: Optional[ctypes.CDLL] = None
@@ -167,7 +167,7 @@ def build_host(verbose: bool = True) -> str:
     lib_path = os.path.join(lib_dir, HOST_LIB_NAME)
     stamp = lib_path + ".digest"
     h = hashlib.sha256()
-    for p in host_sources():
+    for p in host_sources() + [os.path.join(CSRC, "fill_normal.h")]:      # the generator's header is shared with the device code
         with open(p, "rb") as f:
             h.update(os.path.basename(p).encode() + f.read())
     h.update(" ".join(HOST_FLAGS).encode())

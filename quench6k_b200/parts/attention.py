@@ -45,10 +45,13 @@ class Attention(Mixer):
 
     def bind(self, get, rt):
         self.rt = rt
-        # q, k and v rows stacked so one product yields [q | k | v] per token
-        self.w_qkv = torch.cat([to_operand(get("q_proj.weight"), rt), to_operand(get("k_proj.weight"), rt),
-                                to_operand(get("v_proj.weight"), rt)], dim=0).contiguous()
-        self.w_q = self.w_qkv[: self.Hq * self.hd]
+        # q, k and v rows stacked so one product yields [q | k | v] per token: each piece is copied into its place
+        # on the device as it arrives, so that no two copies of the three are held at once
+        nq, nk = self.Hq * self.hd, self.Hkv * self.hd
+        self.w_qkv = torch.empty((nq + 2 * nk, self.D), dtype=rt.dtype, device=rt.device)
+        for name, lo, hi in (("q_proj.weight", 0, nq), ("k_proj.weight", nq, nq + nk), ("v_proj.weight", nq + nk, nq + 2 * nk)):
+            self.w_qkv[lo:hi].copy_(get(name))
+        self.w_q = self.w_qkv[:nq]
         self.w_o = to_operand(get("o_proj.weight"), rt)
         self.q_norm = to_f32(get("q_norm.weight"), rt) if self.qk_norm else None
         self.k_norm = to_f32(get("k_norm.weight"), rt) if self.qk_norm else None

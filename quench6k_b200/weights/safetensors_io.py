@@ -133,6 +133,25 @@ class SafetensorsFile:
         return torch.frombuffer(buf, dtype=ent.dtype).reshape(ent.shape)
 
 
+    def read_range(self, name: str, offset: int, out: torch.Tensor) -> None:
+        """out.numel() bytes of the tensor's data from byte `offset` into `out` (uint8, contiguous, on the CPU;
+        pinned memory when it is a staging buffer of an upload)."""
+        ent = self.entries[name]
+        n = out.numel()
+        if out.dtype != torch.uint8 or not out.is_contiguous() or offset < 0 or offset + n > ent.end - ent.begin:
+            raise SafetensorsError(f"{self.path}: bytes {offset}..{offset + n} of tensor {name} ({ent.end - ent.begin} bytes) into {out.dtype}")
+        if n == 0:
+            return
+        if self._h is not None:
+            if self._lib.q6k_st_read_range(self._h, self._index[name], offset, out.data_ptr(), n):
+                raise SafetensorsError(f"{self.path}: {self._lib.q6k_host_last_error().decode()}")
+            return
+        if self._mm is None:
+            self._f = open(self.path, "rb")
+            self._mm = mmap.mmap(self._f.fileno(), 0, access=mmap.ACCESS_READ)
+        out.numpy()[:] = memoryview(self._mm)[ent.begin + offset:ent.begin + offset + n]
+
+
 def index_folder(folder: str) -> Dict[str, Tuple[SafetensorsFile, TensorEntry]]:
     """name -> (file, entry) over a model folder's safetensors files."""
     idx_path = os.path.join(folder, "model.safetensors.index.json")

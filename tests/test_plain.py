@@ -122,3 +122,19 @@ def test_splitmix_and_pick():
     assert P.pick(logits, 1.0, 2, 1.0, 0.0, 0.75) == 2
     assert P.pick(logits, 1.0, 0, 0.5, 0.0, 0.999) == 2                  # top-p 0.5 keeps two candidates
     assert P.pick(logits, 1.0, 0, 1.0, 0.2, 0.999) == 2                  # min-p drops exp(-2) = 0.135 and below
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_two_plain_implementations_agree(tmp_path, name):
+    """tests/plain_flint.py (tensor operations over whole sequences) and tests/numpy_flint.py
+    (loops over tokens and heads), two readings of the reference's formulas that share no code:
+    the same logits to 1e-6 of the largest, on the tiny configurations (C: layers named twice and a
+    borrowed cache), with matrices wide enough apart for every layer to matter."""
+    import helpers
+    import numpy_flint
+    cfg, weights = helpers.make_model_folder(str(tmp_path), name, seed=13, init_std=0.2)
+    toks = helpers.random_tokens(37, cfg["vocab_size"], 5)
+    a = P.forward(cfg, weights, toks).numpy()
+    b = numpy_flint.forward(cfg, weights, toks)
+    assert a.shape == b.shape
+    assert abs(a - b).max() <= 1e-6 * abs(a).max()

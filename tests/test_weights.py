@@ -42,6 +42,35 @@ def test_seed_and_name_decide_the_values():
     assert ones.dtype == torch.float32 and torch.all(ones == 1)
 
 
+def test_host_generator_equals_its_numpy_twin_bit_for_bit():
+    """The C++ host generator against the NumPy twin under tests/: the same float32 bits, also
+    through the scale, the mean and the rounding to bfloat16; and the values are what Box-Muller
+    of the same uniforms gives in library arithmetic, to rounding."""
+    import math
+    import numpy as np
+    import numpy_fill
+    from quench6k_b200.weights.random_init import fill_normal, stream_key
+    for seed, name, start, count in ((0, "a", 0, 5000), (7, "model.layers.3.mlp.experts.gate_proj.weight", 123456789012, 4097), (2**40 + 3, "x", 1 << 33, 1000)):
+        assert stream_key(seed, name) == numpy_fill.stream_key(seed, name)
+        z = standard_normal(seed, name, start, count, "cpu").numpy()
+        twin = numpy_fill.standard_normal(seed, name, start, count)
+        assert np.array_equal(z.view(np.uint32), twin.view(np.uint32))
+        out = fill_normal(torch.empty(count, dtype=torch.float32), seed, name, start, 0.02, 1.0).numpy()
+        assert np.array_equal(out.view(np.uint32), numpy_fill.element_values(seed, name, start, count, 0.02, 1.0).view(np.uint32))
+        bf = fill_normal(torch.empty(count, dtype=torch.bfloat16), seed, name, start, 0.02, 0.0)
+        assert torch.equal(bf, torch.from_numpy(numpy_fill.element_values(seed, name, start, count, 0.02, 0.0)).to(torch.bfloat16))
+    # against the textbook formula with the library's log and cos
+    key = np.uint64(numpy_fill.stream_key(5, "t"))
+    with np.errstate(over="ignore"):
+        j = np.arange(2000, dtype=np.uint64)
+        a, b = numpy_fill._mix(j * np.uint64(2) + key), numpy_fill._mix(j * np.uint64(2) + np.uint64(1) + key)
+    u1 = ((a >> np.uint64(11)).astype(np.float64) + 1.0) / 2.0**53
+    u2 = (b >> np.uint64(11)).astype(np.float64) / 2.0**53
+    want = np.sqrt(-2.0 * np.log(u1)) * np.cos(2.0 * math.pi * u2)
+    got = standard_normal(5, "t", 0, 2000, "cpu").numpy().astype(np.float64)
+    assert np.abs(got - want).max() <= 1e-6
+
+
 def test_one_error_lists_missing_unexpected_and_wrong(tmp_path):
     cfg_d, weights = helpers.make_model_folder(str(tmp_path), "A", seed=0)
     bad = dict(weights)
@@ -227,3 +256,58 @@ def test_header_reader_against_random_headers(tmp_path):
         assert a.entries == b.entries and len(a.entries) == len(header) - ("__metadata__" in header), case
         for name in a.entries:
             assert torch.equal(a.read(name).reshape(-1).view(torch.uint8), b.read(name).reshape(-1).view(torch.uint8))
+
+
+def _one_by_one(weights):
+    """The same checkpoint with every routed expert stored as a tensor of its own."""
+    out = {}
+    for n, t in weights.items():
+        if ".mlp.experts." in n:
+            stem, leaf = n.rsplit(".experts.", 1)
+            for e in range(t.shape[0]):
+                out[f"{stem}.experts.{e}.{leaf}"] = t[e].clone()
+        else:
+            out[n] = t
+    return out
+
+
+def test_experts_stored_one_by_one_are_stacked(tmp_path):
+    """`mlp.experts.{e}.{gate,up,down}_proj.weight` are read into the stacked [E, ...] tensors the
+    model declares; a missing expert, one too many and a wrong shape are all named in one error."""
+    from quench6k_b200.models.flint import gguf_alias
+    cfg_d, weights = helpers.make_model_folder(str(tmp_path), "A", seed=4)
+    split = _one_by_one(weights)
+    assert len(split) == len(weights) + 2 * 3 * (8 - 1)
+    write_safetensors(str(tmp_path / "model.safetensors"), split.items())
+    get = load_folder(str(tmp_path), _decl("A"), gguf_alias)
+    for n, t in weights.items():
+        assert torch.equal(get(n), t), n
+    with pytest.raises(WeightError):                          # without the table of other names: 48 unexpected, 6 missing
+        load_folder(str(tmp_path), _decl("A"))
+    bad = dict(split)
+    del bad["model.layers.1.mlp.experts.5.up_proj.weight"]
+    bad["model.layers.0.mlp.experts.8.gate_proj.weight"] = torch.zeros(32, 64, dtype=torch.bfloat16)
+    bad["model.layers.0.mlp.experts.2.down_proj.weight"] = torch.zeros(64, 31, dtype=torch.bfloat16)
+    write_safetensors(str(tmp_path / "model.safetensors"), bad.items())
+    with pytest.raises(WeightError) as e:
+        load_folder(str(tmp_path), _decl("A"), gguf_alias)
+    msg = str(e.value)
+    assert "model.layers.1.mlp.experts.up_proj.weight[5]" in msg and "missing" in msg
+    assert "model.layers.0.mlp.experts.8.gate_proj.weight" in msg and "unexpected" in msg
+    assert "model.layers.0.mlp.experts.2.down_proj.weight: shape [64, 31], expected [64, 32]" in msg
+
+
+def test_pieces_of_a_tensor_can_be_read(tmp_path):
+    """What the upload through staging buffers reads: byte ranges of a tensor, by both readers."""
+    t = torch.arange(1000, dtype=torch.float32).reshape(10, 100)
+    write_safetensors(str(tmp_path / "x.safetensors"), [("pad", torch.zeros(3, dtype=torch.bfloat16)), ("t", t)])
+    from quench6k_b200.weights import SafetensorsFile
+    raw = t.view(-1).view(torch.uint8)
+    for native in (True, False):
+        sf = SafetensorsFile(str(tmp_path / "x.safetensors"), native=native)
+        for off, n in ((0, 4000), (4, 8), (3996, 4), (1234, 1001), (50, 0)):
+            out = torch.full((n,), 255, dtype=torch.uint8)
+            sf.read_range("t", off, out)
+            assert torch.equal(out, raw[off:off + n])
+        with pytest.raises(SafetensorsError):
+            sf.read_range("t", 3999, torch.zeros(2, dtype=torch.uint8))

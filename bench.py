@@ -146,16 +146,26 @@ def expected_experts(E, k, B):
     return E * (1.0 - (1.0 - k / E) ** B)
 
 
-def decode_bytes(cfg, layers, B, ctx):
-    """Bytes one decode step has to read: every weight it uses once, and the cache of the live requests."""
+def decode_bytes(cfg, layers, B, ctx, experts_read=None):
+    """Bytes one decode step has to read: every weight it uses once, and the cache of the live requests.
+    experts_read: distinct experts per layer that the router really chose (measured); else the expectation."""
     D, Hq, Hkv, hd = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     E, k, I, V = cfg["n_routed_experts"], cfg["num_experts_per_tok"], cfg["moe_intermediate_size"], cfg["vocab_size"]
     attn = ((Hq + 2 * Hkv) * hd * D + D * Hq * hd) * 2
     router = E * D * 2
-    experts = expected_experts(E, k, B) * 3 * I * D * 2
+    experts = (experts_read if experts_read is not None else expected_experts(E, k, B)) * 3 * I * D * 2
     weights = layers * (attn + router + experts) + V * D * 2
     kv = B * ctx * layers * 2 * Hkv * hd * 2
     return weights + kv, weights, kv
+
+
+def prefill_bytes(cfg, layers, T):
+    """Bytes a prefill step of T tokens has to read at least: every weight once (with T * k pairs far above the number of
+    experts, all of them), the logits' row of the head aside."""
+    D, Hq, Hkv, hd = cfg["hidden_size"], cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    E, k, I, V = cfg["n_routed_experts"], cfg["num_experts_per_tok"], cfg["moe_intermediate_size"], cfg["vocab_size"]
+    per_layer = ((Hq + 2 * Hkv) * hd * D + D * Hq * hd + E * D + expected_experts(E, k, T) * 3 * I * D) * 2
+    return layers * per_layer + V * D * 2
 
 
 def prefill_flops(cfg, layers, T):
@@ -204,6 +214,46 @@ def kernel_attention_prefill(args):
     print(json.dumps({"kernel": "attention_tc (prompt portions)", "tokens": T, "context": n, "us": round(ms * 1e3, 1),
                       "tflops": round(flops / ms / 1e9, 1), "frac_of_bf16_peak": round(flops / ms / 1e9 / pk["bf16_tflops"], 3),
                       "peaks": pk["source"], "ctas": n_tiles * Hkv, "steps": args.steps}))
+    return 0
+
+
+def profile_ops(args, runner, cfg_d, layers, ctx, stand_at_context, rand_ids):
+    """Where the time of an eager decode step (batch --batch at the context) and of a prefill step goes, launcher by
+    launcher: CUDA events around every launch (quench6k_b200.ops.profile_begin/profile_end), no profiler involved.  Eager
+    launches leave gaps that a replayed graph does not have, so the sum is the step's kernel time, not its duration."""
+    import torch
+    from quench6k_b200 import ops
+    from quench6k_b200.engine import StepEntry
+    runner.cuda_graphs = False
+    B, T = args.batch, args.prefill_tokens
+    rids = [f"q{i}" for i in range(B)]
+    stand_at_context(rids)
+    toks = [rand_ids(args.steps + args.warmup) for _ in rids]
+    step = lambda i: runner.step([StepEntry(r, [toks[j][i]], [0]) for j, r in enumerate(rids)])
+    for i in range(args.warmup):
+        step(i)
+    torch.cuda.synchronize()
+    ops.profile_begin()
+    for i in range(args.warmup, args.warmup + args.steps):
+        step(i)
+    decode = ops.profile_end()
+    for r in rids:
+        runner.end_request(r)
+    prefill = {}
+    for it in range(2):
+        runner.add_request("p")
+        ids = rand_ids(T)
+        if it:
+            ops.profile_begin()
+        runner.step([StepEntry("p", ids, [T - 1])])
+        if it:
+            prefill = ops.profile_end()
+        runner.end_request("p")
+    table = lambda rec, n: [{"op": tag, "launcher": fn, "calls_per_step": calls / n, "us_per_step": round(ms * 1e3 / n, 1)}
+                            for (tag, fn), (calls, ms) in rec.items()]
+    print(json.dumps({"profile": "CUDA events around every launch of eager steps", "layers": layers, "batch": B, "context": ctx,
+                      "decode_step": table(decode, args.steps), "decode_us": round(sum(ms for _, ms in decode.values()) * 1e3 / args.steps, 1),
+                      "prefill_tokens": T, "prefill_step": table(prefill, 1), "prefill_us": round(sum(ms for _, ms in prefill.values()) * 1e3, 1)}))
     return 0
 
 
@@ -295,6 +345,9 @@ def main():
     ap.add_argument("--temperature", type=float, default=0.0, help="sampling temperature of the end-to-end part (0: greedy, the headline)")
     ap.add_argument("--dtype", default="bfloat16")
     ap.add_argument("--page-size", type=int, default=None, help="KV page size (default: the configuration's 16)")
+    ap.add_argument("--profile-ops", action="store_true",
+                    help="instead of the benchmark line: where an eager decode step and a prefill step spend their time, launcher by "
+                         "launcher (CUDA events around every launch; its own JSON line)")
     ap.add_argument("--kernel", default=None, choices=["attention_prefill"],
                     help="time one kernel alone at the configuration's head sizes instead of the model: attention_prefill runs "
                          "--prefill-tokens query tokens that end at position --context (one request, contiguous pages)")
@@ -336,7 +389,7 @@ def main():
     point_batches = [int(x) for x in args.points.split(",") if x.strip()]
     max_b = max([args.batch] + point_batches)
     ctx = args.context
-    headroom = max(64, args.steps + args.warmup + 16)            # every timed request decodes that many tokens past its context
+    headroom = max(96, args.steps + args.warmup + 16)            # every timed request decodes that many tokens past its context
     pages_per_req = (ctx + headroom + page - 1) // page + 1
     num_pages = max(max_b * pages_per_req, (args.prefill_tokens + page - 1) // page + 1)
     t0 = time.time()
@@ -355,16 +408,68 @@ def main():
     def rand_ids(n):
         return torch.randint(0, V, (n,), generator=gen).tolist()
 
-    def timed_decode(B, steps, warmup, sampler=None):
-        """Device-timed decode steps of B requests standing at `ctx` cached tokens."""
-        rids = [f"d{B}_{i}" for i in range(B)]
+    def stand_at_context(rids):
         for r in rids:
             runner.add_request(r)
         chunk = args.prefill_tokens              # pages are taken as a chunked prefill would take them:
         for at in range(0, ctx, chunk):          # one portion of each request in turn
             for r in rids:
                 runner.assume_cached(r, min(chunk, ctx - at))
-        toks = [rand_ids(steps + warmup) for _ in rids]
+
+    def graphs_equal_eager(B, n=64, prompt=4096):
+        """The reference times nothing before it has checked it (crates/cli/src/flint.rs:116-131: 64 graph-decoded
+        tokens must equal eager decoding): B prompts are prefilled in portions, then n greedy tokens are decoded by
+        replaying CUDA graphs; the same again with eager launches; the ids must be equal.  (Real prompts, not the
+        random cache contents of the timed part: those differ from page to page, and the two passes get other pages.)"""
+        prompt = min(prompt, ctx)
+        prompts = [rand_ids(prompt) for _ in range(B)]
+        seqs = []
+        for graphs in (True, False):
+            rids = [f"g{B}_{i}" for i in range(B)]
+            keep, runner.cuda_graphs = runner.cuda_graphs, runner.cuda_graphs and graphs
+            cur = []
+            for r, toks in zip(rids, prompts):
+                runner.add_request(r)
+                for at in range(0, prompt, args.prefill_tokens):
+                    part = toks[at:at + args.prefill_tokens]
+                    logits = runner.step([StepEntry(r, part, [len(part) - 1])])
+                cur.append(int(ops.argmax(logits)[0]))
+            ids = [cur]
+            for _ in range(n):
+                cur = ops.argmax(runner.step([StepEntry(r, [cur[j]], [0]) for j, r in enumerate(rids)])).tolist()
+                ids.append(cur)
+            runner.cuda_graphs = keep
+            for r in rids:
+                runner.end_request(r)
+            seqs.append(ids)
+        return seqs[0] == seqs[1], len({t for step in seqs[0] for t in step})
+
+    def experts_read(one, first, B, n=2):
+        """Distinct experts per routed layer that n further (eager) decode steps really chose, on average."""
+        from quench6k_b200.parts.base import Tap
+        tap = Tap(max(64, B))
+        routed = [b.ffn for b in runner.model.blocks if hasattr(b.ffn, "routing_tap")]
+        for f in routed:
+            f.routing_tap = tap
+        keep, runner.cuda_graphs = runner.cuda_graphs, False
+        total, count = 0, 0
+        for i in range(first, first + n):
+            one(i)
+            for (what, _), buf in tap.buffers.items():
+                if what == "experts":
+                    total += int(torch.unique(buf[:B]).numel())
+                    count += 1
+        runner.cuda_graphs = keep
+        for f in routed:
+            f.routing_tap = None
+        return total / count if count else None
+
+    def timed_decode(B, steps, warmup, sampler=None):
+        """Device-timed decode steps of B requests standing at `ctx` cached tokens: (ms per step, launches, distinct
+        experts per layer the router chose in two further steps)."""
+        rids = [f"d{B}_{i}" for i in range(B)]
+        stand_at_context(rids)
+        toks = [rand_ids(steps + warmup + 2) for _ in rids]
 
         def one(i):
             logits = runner.step([StepEntry(r, [toks[j][i]], [0]) for j, r in enumerate(rids)])
@@ -386,15 +491,22 @@ def main():
             sampler.result = sampler.stop()
         ms = a.elapsed_time(b) / steps
         launches = ops.launch_count - l0
+        chosen = experts_read(one, warmup + steps, B)
         for r in rids:
             runner.end_request(r)
-        return ms, launches
+        return ms, launches, chosen
 
+    if args.profile_ops:
+        return profile_ops(args, runner, cfg_d, layers, ctx, stand_at_context, rand_ids)
+    checked, distinct = graphs_equal_eager(args.batch)
+    if not checked:
+        print("bench.py: decoding by CUDA-graph replay and by eager launches gave different tokens; nothing is timed", file=sys.stderr)
+        return 1
     clocks = ClockSampler()
-    ms, launches = timed_decode(args.batch, args.steps, args.warmup, clocks)
+    ms, launches, chosen = timed_decode(args.batch, args.steps, args.warmup, clocks)
     clock_info = clocks.result
     value = args.batch * 1000.0 / ms
-    total_b, w_b, kv_b = decode_bytes(cfg_d, layers, args.batch, ctx)
+    total_b, w_b, kv_b = decode_bytes(cfg_d, layers, args.batch, ctx, chosen)
     achieved = total_b / (ms * 1e-3) / 1e9
 
     # prefill: one prompt of T tokens in one step, the logits of its last token wanted
@@ -413,13 +525,21 @@ def main():
         runner.end_request("p")
     pms = min(pre_ms[1:])
     pf = prefill_flops(cfg_d, layers, T)
+    pb = prefill_bytes(cfg_d, layers, T)
     prefill = {"value": round(T * 1000.0 / pms, 1), "tokens": T, "ms": round(pms, 3),
-               "frac": round(pf / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+               "frac": round(pf / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+               # a step of milliseconds runs under the power cap: the sustained product rate is its yardstick; and the step
+               # cannot be shorter than its weights take to stream, nor than that plus its products one after the other
+               "frac_sustained": round(pf / (pms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4),
+               "bytes_floor_ms": round(pb / pk["hbm_gbs"] / 1e6, 3),
+               "flops_floor_ms": round(pf / pk["bf16_tflops_sustained"] / 1e9, 3)}
 
-    points = {}
+    points, points_roofline, points_ms = {}, {}, {}
     for B in point_batches:
-        pms, _ = timed_decode(B, max(4, args.steps // 2), 3)
-        points[f"decode_b{B}"] = round(B * 1000.0 / pms, 1)
+        bms, _, bchosen = timed_decode(B, args.steps, 3)
+        points[f"decode_b{B}"] = round(B * 1000.0 / bms, 1)
+        points_ms[f"decode_b{B}"] = round(bms, 3)
+        points_roofline[f"decode_b{B}"] = round(decode_bytes(cfg_d, layers, B, ctx, bchosen)[0] / (bms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
 
     # end to end: Engine.step() with host ids in and sampled ids out each step
     for i in range(args.batch):
@@ -458,8 +578,11 @@ def main():
                    "kv_fill": "random values; pages taken in portions of prefill_tokens per request in turn", "peaks": pk["source"]},
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes": int(total_b), "weight_bytes": int(w_b), "kv_bytes": int(kv_b)},
-        "points": points, "e2e": e2e, "gpu_launches": launches, "clocks": clock_info, "impl": "ours",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes": int(total_b), "weight_bytes": int(w_b), "kv_bytes": int(kv_b),
+                     "experts_read_per_layer": None if chosen is None else round(chosen, 1)},
+        "points": points, "points_roofline": points_roofline, "points_ms": points_ms,
+        "checked": {"graph_replay_equals_eager": True, "tokens": 64, "distinct_ids": distinct},
+        "e2e": e2e, "gpu_launches": launches, "clocks": clock_info, "impl": "ours",
     }
     print(json.dumps(out))
     return 0

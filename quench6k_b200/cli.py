@@ -173,6 +173,7 @@ def _ppl(a) -> int:
     its second half (the logits of positions ctx/2 .. ctx-2 predict the next token)."""
     import math
     import torch
+    from . import ops
     from .engine import StepEntry
     ctx = a.ctx
     half = ctx // 2
@@ -195,9 +196,8 @@ def _ppl(a) -> int:
         while at < ctx - 1:
             rows = min(piece, ctx - 1 - at)
             logits = runner.step([StepEntry("p", toks[at:at + rows], list(range(rows)))])
-            target = torch.tensor(toks[at + 1:at + 1 + rows], device=logits.device)
-            lse = torch.logsumexp(logits, dim=-1)
-            tl = logits.gather(1, target[:, None])[:, 0]
+            target = torch.tensor(toks[at + 1:at + 1 + rows], dtype=torch.int32, device=logits.device)
+            lse, tl = ops.row_logsumexp(logits, target)
             nll += float((lse - tl).double().sum())
             count += rows
             at += rows

@@ -390,6 +390,46 @@ Q6K_API int q6k_argmax(const float* logits, int rows, int V, int* out, void* scr
     return q6k_check_launch("argmax");
 }
 
+namespace {
+// lse[row] = log(sum_i exp(logits[row, i])) and picked[row] = logits[row, target[row]]: what a perplexity needs of a row
+// of logits (reference: the row log-sum-exp of crates/cuda/kernels/topk.cu:181-198).  One block per row; the maximum
+// first, then the sum of the exponentials around it, the warps' sums added in warp order.
+__global__ void __launch_bounds__(1024) row_lse_kernel(const float* __restrict__ logits, int V, const int* __restrict__ target,
+                                                       float* __restrict__ lse, float* __restrict__ picked) {
+    pdl_enter();
+    __shared__ float red[32];
+    const float* row = logits + (size_t)blockIdx.x * V;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, row[i]);
+    mx = warp_max(mx);
+    if (lane == 0) red[warp] = mx;
+    __syncthreads();
+    mx = red[0];
+    for (int w = 1; w < warps; ++w) mx = fmaxf(mx, red[w]);
+    __syncthreads();
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) sum += expf(row[i] - mx);
+    sum = warp_sum(sum);
+    if (lane == 0) red[warp] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float total = 0.0f;
+        for (int w = 0; w < warps; ++w) total += red[w];
+        lse[blockIdx.x] = mx + logf(total);
+        if (target) picked[blockIdx.x] = row[target[blockIdx.x]];
+    }
+}
+}  // namespace
+
+// logits: FP32 [rows, V]; lse: FP32 [rows]; target (int32 [rows], ids in 0..V-1) and picked (FP32 [rows]) together or both null.
+Q6K_API int q6k_row_lse(const float* logits, int rows, int V, const int* target, float* lse, float* picked, cudaStream_t st) {
+    if (rows == 0) return 0;
+    Q6K_REQUIRE(rows > 0 && V > 0 && (!target == !picked), "row_lse: bad sizes rows=%d V=%d, or only one of target and picked", rows, V);
+    q6k_launch(row_lse_kernel, rows, V >= 8192 ? 1024 : 256, 0, st, logits, V, target, lse, picked);
+    return q6k_check_launch("row_lse");
+}
+
 // ids: int32 [rows, K], vals: FP32 [rows, K], sorted by (logit descending, id ascending).
 Q6K_API int q6k_topk_pool(const float* logits, int rows, int V, int K, int* ids, float* vals, cudaStream_t st) {
     if (rows == 0) return 0;

@@ -86,6 +86,7 @@ class DecoderModel:
     def forward(self, ctx, caches: List[Optional[LayerCache]], states: List[Optional[torch.Tensor]]) -> Optional[torch.Tensor]:
         """Runs the tokens of `ctx` through the executed layers; returns FP32 logits
         [len(ctx.logit_rows), vocab] or None when no row is wanted."""
+        ops.current_tag = "embedding"
         h = ops.embed(ctx.token_ids, self.embed, fed=ctx.fed)
         pending = None                      # an add into h that a block has left to the next norm
         for p, i in enumerate(self.order):
@@ -96,5 +97,7 @@ class DecoderModel:
         if pending is not None and not self.final_norm.fuses_weighted_rows:
             pending.apply(h)
             pending = None
+        ops.current_tag = "norm.final"
         xn = self.final_norm.forward(h, rows=ctx.logit_rows, add=pending)
+        ops.current_tag = "lm_head"
         return linear.matmul(xn, self.head, self.rt)

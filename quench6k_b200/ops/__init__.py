@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -61,6 +62,33 @@ launch_count = 0
 
 _functions = {}
 
+# Where a step's time goes, without a profiler (the reference times its forward pass op by op the same way and can
+# synchronise after every op: crates/engine/src/profile.rs:1-55, crates/engine/src/flint.rs:685-697).
+# profile_begin() makes every launcher call stand between two CUDA events; profile_end() adds them up per (tag, launcher).
+# Parts name what they are about to launch by setting ops.current_tag (a plain attribute: nothing is paid when no one
+# is profiling).  Steps replayed from a CUDA graph run no Python and are not seen: profile eager steps.
+# The environment variable Q6K_SYNC=op synchronises after every launcher call and raises where a kernel failed.
+current_tag = ""
+_profile = None
+_sync_each = os.environ.get("Q6K_SYNC", "") == "op"
+
+
+def profile_begin() -> None:
+    global _profile
+    _profile = []
+
+
+def profile_end():
+    """{(tag, launcher): (calls, milliseconds)} since profile_begin(), in the order of first use (synchronises)."""
+    global _profile
+    records, _profile = _profile or [], None
+    torch.cuda.synchronize()
+    out = {}
+    for key, e0, e1 in records:
+        calls, ms = out.get(key, (0, 0.0))
+        out[key] = (calls + 1, ms + e0.elapsed_time(e1))
+    return out
+
 
 def _call(fn_name: str, *args):
     global launch_count
@@ -69,11 +97,23 @@ def _call(fn_name: str, *args):
     if fn is None:
         fn = _functions[fn_name] = getattr(library(), fn_name)
         fn.restype = ctypes.c_int
-    rc = fn(*args)
+    if _profile is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        rc = fn(*args)
+        e1.record()
+        _profile.append(((current_tag, fn_name), e0, e1))
+    else:
+        rc = fn(*args)
     if rc != 0:
         lib = library()
         lib.q6k_last_error.restype = ctypes.c_char_p
         raise KernelError(lib.q6k_last_error().decode())
+    if _sync_each:
+        torch.cuda.synchronize()
+        status = tc_status()
+        if status:
+            raise KernelError(f"{fn_name} ({current_tag}): a bounded wait ran out inside a kernel (status {status})")
 
 
 _i = ctypes.c_int
@@ -719,6 +759,19 @@ def argmax(logits: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Te
     scratch = torch.empty(lib.q6k_argmax_scratch_ints(_i(rows), _i(V)), dtype=torch.int32, device=logits.device)
     _call("q6k_argmax", _ptr(logits), _i(rows), _i(V), _ptr(out), _ptr(scratch), _stream())
     return out
+
+
+def row_logsumexp(logits: torch.Tensor, target: Optional[torch.Tensor] = None):
+    """log(sum(exp(row))) of every row, FP32 [rows]; with target (int32 [rows]) also each row's logit at its target."""
+    _need(logits, "logits", torch.float32)
+    rows, V = logits.shape
+    lse = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    picked = None
+    if target is not None:
+        _need(target, "target", torch.int32, (rows,))
+        picked = torch.empty(rows, dtype=torch.float32, device=logits.device)
+    _call("q6k_row_lse", _ptr(logits), _i(rows), _i(V), _ptr(target), _ptr(lse), _ptr(picked), _stream())
+    return lse if target is None else (lse, picked)
 
 
 def sample_pool(ids: torch.Tensor, vals: torch.Tensor, rows: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:

@@ -69,8 +69,10 @@ class Attention(Mixer):
         rotary = self.pos.rotary_table()
         fused_pos = rotary is not None or self.pos.is_identity
         # FP32 [T, (Hq + 2 Hkv) hd] or [T, Hq hd]; for few rows possibly as split-K partials, which qk_prep sums
+        ops.current_tag = "attention.qkv"
         qkv = linear.matmul(xn, self.w_qkv if write else self.w_q, rt, partials_ok=fused_pos)
         table = ctx.block_tables[cache.group]
+        ops.current_tag = "attention.prepare"
         if not fused_pos:
             qkv = self._unfused_position(qkv, ctx, write)
             q = ops.qk_prep(qkv, self.Hq, self.Hkv, self.hd, None, None, self.eps, None, ctx.positions, ctx.req_of_token,
@@ -80,8 +82,10 @@ class Attention(Mixer):
             q = ops.qk_prep(qkv, self.Hq, self.Hkv, self.hd, self.q_norm, self.k_norm, self.eps, rotary, ctx.positions,
                             ctx.req_of_token, table if write else None, cache.page_size, cache.k if write else None,
                             cache.v if write else None, rt.dtype)
+        ops.current_tag = "attention.keys"
         a = self._attend(q, cache, table, ctx)
         # the block adds it into the stream inside its next norm (which also sums split-K partials)
+        ops.current_tag = "attention.o"
         return linear.matmul(a, self.w_o, rt, partials_ok=True)
 
     def _attend(self, q, cache, table, ctx):

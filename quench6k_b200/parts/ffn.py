@@ -33,7 +33,9 @@ class DenseSwiGLU(FeedForward):
         self.w_down = to_operand(get("down_proj.weight"), rt)
 
     def forward(self, xn, ctx, out):
+        ops.current_tag = "dense.gate_up"
         act = linear.swiglu_matmul(xn, self.w_gate, self.w_up, self.rt)
+        ops.current_tag = "dense.down"
         linear.matmul(act, self.w_down, self.rt, out=out, accumulate=True)
 
 
@@ -92,26 +94,35 @@ class RoutedExperts(FeedForward):
                 and ops.tc_supported(xn, self.w_gate) and self.I % 8 == 0):
             # a decode step: router and top-k in one launch, then one weight tile stream per
             # (token, slot) pair straight from the selection, no permutation and no gather
+            ops.current_tag = "experts.router"
             sel_e, sel_w, order, logits = ops.router_small(xn, self.w_router, self.k, self.scoring, self.renorm, with_logits=True)
             if self.routing_tap is not None:
                 self._tap(ctx, sel_e, logits)
+            ops.current_tag = "experts.gate_up"
             act = ops.gemm_tc_pairs(xn, self.w_gate, sel_e, self.k, w2=self.w_up, order=order)      # [pairs, I]
+            ops.current_tag = "experts.down"
             y = ops.gemm_tc_pairs(act, self.w_down, sel_e, 1, order=order)                           # FP32 [pairs, D]
             if defer:
                 return WeightedRows(y, sel_w)
+            ops.current_tag = "experts.combine"
             ops.combine(y, None, sel_w, out)
             if self.shared is not None:
                 self.shared.forward(xn, ctx, out)
             return None
+        ops.current_tag = "experts.router"
         logits = linear.matmul(xn, self.w_router, rt, partials_ok=True)    # FP32 [T, E], or split-K slices of it that route() sums
         sel_e, sel_w = ops.route(logits, self.k, self.scoring, self.renorm)
         if self.routing_tap is not None:
             self._tap(ctx, sel_e, logits)
+        ops.current_tag = "experts.permute"
         plan = linear.group_plan(xn, self.w_gate, sel_e, rt)             # permutation by expert, row tiles, gathered rows
+        ops.current_tag = "experts.gate_up"
         act = linear.grouped_swiglu(xn, plan, self.w_gate, self.w_up, rt)                         # [pairs, I]
+        ops.current_tag = "experts.down"
         y = linear.grouped_matmul(act, plan, self.w_down, rt)                                     # FP32 [pairs, D]
         if defer:
             return WeightedRows(y, sel_w, plan.pair_row)
+        ops.current_tag = "experts.combine"
         ops.combine(y, plan.pair_row, sel_w, out)
         if self.shared is not None:
             self.shared.forward(xn, ctx, out)

@@ -387,6 +387,46 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
     return out
 
 
+# --------------------------------------------------------------------------- matrix-vector products (a step of very few tokens)
+def gemv_preferred(tokens: int, N: int, K: int) -> bool:
+    """Whether a bfloat16 product of `tokens` rows with an [N, K] matrix should go to the matrix-vector kernel."""
+    lib = library()
+    lib.q6k_gemv_preferred.restype = ctypes.c_int
+    return bool(lib.q6k_gemv_preferred(_i(tokens), _i(N), _i(K)))
+
+
+def gemv(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, accumulate: bool = False,
+         pair_expert: Optional[torch.Tensor] = None, pair_div: int = 1) -> torch.Tensor:
+    """out[t] (+)= x[t] @ w^T for one to four rows of x (bfloat16, FP32 sums and output); with w2 the SwiGLU epilogue
+    silu(x w^T) * (x w2^T) in bfloat16.  With pair_expert (int32 [pairs]) and w [experts, N, K]: pair y multiplies row
+    y // pair_div of x with the matrix of expert pair_expert[y] and writes row y (any number of pairs)."""
+    if not tc_supported(x, w):
+        raise KernelError("gemv: operands must be bfloat16 with K a multiple of 8 and 16-byte aligned rows")
+    K = x.shape[1]
+    N = w.shape[-2]
+    if w.shape[-1] != K or (w.dim() == 3) != (pair_expert is not None):
+        raise KernelError(f"gemv: x has K={K}, w has shape {tuple(w.shape)} (three dimensions go with pair_expert)")
+    pairs = 0
+    if pair_expert is not None:
+        _need(pair_expert, "pair_expert", torch.int32)
+        pairs = pair_expert.numel()
+    rows = pairs if pair_expert is not None else x.shape[0]
+    epi = EPI_SWIGLU if w2 is not None else (EPI_ADD if accumulate else EPI_STORE)
+    out_dtype = torch.bfloat16 if w2 is not None else torch.float32
+    if w2 is not None:
+        _need(w2, "w2", torch.bfloat16, w.shape)
+    if out is None:
+        if accumulate:
+            raise KernelError("gemv: accumulate needs an output")
+        out = torch.empty((rows, N), dtype=out_dtype, device=x.device)
+    _need(out, "out", out_dtype)
+    if out.shape[0] < rows or out.shape[1] != N:
+        raise KernelError(f"gemv: out has shape {tuple(out.shape)}, needs [{rows}, {N}]")
+    _call("q6k_gemv", _ptr(x), _ll(x.stride(0)), _i(x.shape[0]), _ptr(w), _ptr(w2), _i(N), _i(K), _ptr(pair_expert), _i(pairs), _i(pair_div),
+          _ptr(out), _ll(out.stride(0)), _i(epi), _stream())
+    return out
+
+
 # --------------------------------------------------------------------------- attention
 def qk_prep(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, q_norm, k_norm, eps: float, rotary,
             positions: torch.Tensor, req_of_token: torch.Tensor, block_table: Optional[torch.Tensor], page_size: int,

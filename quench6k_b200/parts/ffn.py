@@ -99,9 +99,14 @@ class RoutedExperts(FeedForward):
             if self.routing_tap is not None:
                 self._tap(ctx, sel_e, logits)
             ops.current_tag = "experts.gate_up"
-            act = ops.gemm_tc_pairs(xn, self.w_gate, sel_e, self.k, w2=self.w_up, order=order)      # [pairs, I]
-            ops.current_tag = "experts.down"
-            y = ops.gemm_tc_pairs(act, self.w_down, sel_e, 1, order=order)                           # FP32 [pairs, D]
+            if ops.gemv_preferred(T, self.I, self.D):                     # a token or two: the matrix-vector kernel per pair
+                act = ops.gemv(xn, self.w_gate, w2=self.w_up, pair_expert=sel_e.view(-1), pair_div=self.k)
+                ops.current_tag = "experts.down"
+                y = ops.gemv(act, self.w_down, pair_expert=sel_e.view(-1), pair_div=1)
+            else:
+                act = ops.gemm_tc_pairs(xn, self.w_gate, sel_e, self.k, w2=self.w_up, order=order)  # [pairs, I]
+                ops.current_tag = "experts.down"
+                y = ops.gemm_tc_pairs(act, self.w_down, sel_e, 1, order=order)                       # FP32 [pairs, D]
             if defer:
                 return WeightedRows(y, sel_w)
             ops.current_tag = "experts.combine"

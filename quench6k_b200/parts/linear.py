@@ -2,7 +2,8 @@
 
 float32 operands always take the CUDA-core FP32 kernel (no reduced-precision matrix mode exists on
 that path).  bfloat16 operands take the tcgen05 tensor-core kernel where the shape allows (K a
-multiple of 8, rows starting on 16 bytes) and the CUDA-core kernel otherwise.
+multiple of 8, rows starting on 16 bytes), the matrix-vector kernel where the library prefers it (a
+step of a token or two), and the CUDA-core kernel otherwise.
 """
 from __future__ import annotations
 
@@ -23,6 +24,8 @@ def matmul(a: torch.Tensor, w: torch.Tensor, rt, out: Optional[torch.Tensor] = N
     can sum split-K partial products itself, so the result may come as [slices, M, N] (a view of
     the device's scratch buffer: consume it before the next kernel that uses scratch)."""
     if _tc(a, w, rt):
+        if ops.gemv_preferred(a.shape[0], w.shape[0], w.shape[1]):       # a token or two: the matrix-vector kernel
+            return ops.gemv(a, w, out=out, accumulate=accumulate)
         if partials_ok and out is None and not accumulate and w.shape[0] % 4 == 0:
             return ops.gemm_tc(a, w, keep_partials=True)
         return ops.gemm_tc(a, w, out=out, accumulate=accumulate)
@@ -32,6 +35,8 @@ def matmul(a: torch.Tensor, w: torch.Tensor, rt, out: Optional[torch.Tensor] = N
 def swiglu_matmul(a: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, rt) -> torch.Tensor:
     """act[r] = silu(a[r] @ w_gate^T) * (a[r] @ w_up^T) in a's dtype."""
     if _tc(a, w_gate, rt):
+        if ops.gemv_preferred(a.shape[0], w_gate.shape[0], w_gate.shape[1]):
+            return ops.gemv(a, w_gate, w2=w_up)
         return ops.gemm_tc(a, w_gate, w2=w_up)
     return ops.gemm_simt(a, w_gate, w2=w_up)
 

@@ -356,6 +356,50 @@ def test_gemm_tc_dense(M, N, K):
         assert torch.equal(again[-1], out[0])
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 5120, 2048), (2, 2048, 4096), (1, 100, 72), (3, 77, 264), (4, 384, 1032), (1, 5, 8), (2, 33, 520)])
+def test_gemv_dense(M, N, K):
+    """The matrix-vector kernel for steps of one to four tokens against float64: plain store,
+    accumulation, the SwiGLU epilogue; ragged row counts and widths that are no multiple of the
+    256-element stride of a warp."""
+    from quench6k_b200 import ops
+    a, w = _t(M, K, dtype=torch.bfloat16), _t(N, K, dtype=torch.bfloat16, seed=1)
+    ref = a.double().cpu() @ w.double().cpu().T
+    out = ops.gemv(a, w)
+    tol = 1e-5 * math.sqrt(K) * ref.abs().max()
+    assert out.dtype == torch.float32 and (out.double().cpu() - ref).abs().max() <= tol
+    base = _t(M, N, seed=2)
+    acc = base.clone()
+    ops.gemv(a, w, out=acc, accumulate=True)
+    assert (acc.double().cpu() - (base.double().cpu() + ref)).abs().max() <= tol
+    w2 = _t(N, K, dtype=torch.bfloat16, seed=3)
+    act = ops.gemv(a, w, w2=w2)
+    want = P.silu(ref) * (a.double().cpu() @ w2.double().cpu().T)
+    assert act.dtype == torch.bfloat16 and (act.double().cpu() - want).abs().max() <= 1e-2 * want.abs().max()
+    with pytest.raises(ops.KernelError, match="tokens"):
+        ops.gemv(_t(5, K, dtype=torch.bfloat16), w)
+    assert ops.gemv_preferred(1, 5120, 2048) and not ops.gemv_preferred(8, 5120, 2048) and not ops.gemv_preferred(1, 151936, 2048)
+
+
+@pytest.mark.parametrize("T,k,E,D,I", [(1, 8, 256, 2048, 512), (2, 3, 7, 264, 40), (9, 2, 5, 72, 136)])
+def test_gemv_per_pair(T, k, E, D, I):
+    """The same kernel with one (token, expert) pair per block row, as the decode path of the experts calls it."""
+    from quench6k_b200 import ops
+    x = _t(T, D, dtype=torch.bfloat16)
+    wg, wu, wd = _t(E, I, D, dtype=torch.bfloat16, seed=1), _t(E, I, D, dtype=torch.bfloat16, seed=2), _t(E, D, I, dtype=torch.bfloat16, seed=3)
+    g = torch.Generator().manual_seed(T)
+    sel = torch.stack([torch.randperm(E, generator=g)[:k] for _ in range(T)]).to(torch.int32).to(DEV)
+    act = ops.gemv(x, wg, w2=wu, pair_expert=sel.view(-1), pair_div=k)
+    y = ops.gemv(act, wd, pair_expert=sel.view(-1), pair_div=1)
+    assert act.shape == (T * k, I) and y.shape == (T * k, D) and y.dtype == torch.float32
+    xd = x.double().cpu()
+    for p in range(T * k):
+        e, t = int(sel.view(-1)[p]), p // k
+        a_ref = P.silu(xd[t] @ wg[e].double().cpu().T) * (xd[t] @ wu[e].double().cpu().T)
+        assert (act[p].double().cpu() - a_ref).abs().max() <= 1e-2 * a_ref.abs().max()
+        y_ref = act[p].double().cpu() @ wd[e].double().cpu().T
+        assert (y[p].double().cpu() - y_ref).abs().max() <= 1e-5 * math.sqrt(I) * y_ref.abs().max()
+
+
 def test_gemm_tc_refuses_unaligned():
     from quench6k_b200 import ops
     a, w = _t(4, 20, dtype=torch.bfloat16), _t(8, 20, dtype=torch.bfloat16)

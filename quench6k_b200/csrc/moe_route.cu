@@ -154,60 +154,102 @@ __global__ void route_kernel(const float* logits, int slices, size_t slice_strid
 }
 
 // Router of a decode step in one launch (reference: router_kernel, crates/cuda/kernels/flint.cu:1002-1055,
-// which also routes in its last block): a block per expert computes the logits of every token
-// (T <= 16) against bfloat16 activations with FP32 accumulation; the block that finishes last
-// (atomic ticket, no waiting) scores and picks the top-k of every token.
+// which also routes in its last block).  The logits are a matrix-vector product of at most 16 tokens with the
+// [E, D] router matrix: a block of eight warps takes four experts, its warps split D between them (16 bytes per
+// lane and row: with D = 2,048 every load of the kernel is in flight at once), each lane multiplies its eight
+// weights of four experts with its eight activations of every token, and the 4 x T sums of a warp are brought
+// together by a transposing reduction (the lanes halve the set of sums they carry while they double the set of
+// lanes summed over: 31 shuffles for 32 sums where one reduction per sum would take 160).  The warps' sums meet
+// in shared memory and are added in warp order.  The block that finishes last (atomic ticket, no waiting) scores
+// every token, picks its top-k and sorts the (token, slot) pairs by expert.
 constexpr int SMALL_T = 16;
-__global__ void __launch_bounds__(512) router_small_kernel(const __nv_bfloat16* xn, const __nv_bfloat16* w, int T_, int E, int D, int k,
-                                                           int sigmoid, int renorm, float* logits, int* sel_e, float* sel_w,
+constexpr int ROUTER_ROWS = 4;              // experts of a block
+
+// v[0..NV) of every lane -> lane L holds the warp's sum of v[index(L)]; NV a power of two <= 32.  index(L) takes
+// its bits from the lane's high bits: for NV = 32 it is L itself, for NV = 8 it is L >> 2 (lanes 0, 4, 8, ... hold sums 0..7).
+template <int NV>
+__device__ __forceinline__ float transpose_reduce(float (&v)[NV]) {
+    const int lane = threadIdx.x & 31;
+    int off = 16;
+#pragma unroll
+    for (int n = NV; n > 1; n >>= 1, off >>= 1) {
+        const bool upper = lane & off;
+#pragma unroll
+        for (int i = 0; i < n / 2; ++i) {
+            const float keep = upper ? v[i + n / 2] : v[i], give = upper ? v[i] : v[i + n / 2];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, give, off);
+        }
+    }
+    float r = v[0];
+    for (; off > 0; off >>= 1) r += __shfl_xor_sync(0xffffffffu, r, off);
+    return r;
+}
+
+// TP: the token count rounded up to a power of two (1, 2, 4, 8, 16).
+template <int TP>
+__global__ void __launch_bounds__(256) router_small_kernel(const __nv_bfloat16* __restrict__ xn, const __nv_bfloat16* __restrict__ w, int T_, int E,
+                                                           int D, int k, int sigmoid, int renorm, float* logits, int* sel_e, float* sel_w,
                                                            int* order, unsigned* ticket) {
     pdl_enter();
-    extern __shared__ float sc[];             // the last block: [16 warps][E] scores
-    __shared__ float red[16][SMALL_T];
+    constexpr int NV = ROUTER_ROWS * TP;                                  // sums of a warp: index = row * TP + token
+    constexpr int PASS = NV > 32 ? 32 : NV;                               // reduced 32 at a time
+    __shared__ float meet[8][NV];
+    __shared__ int pair_e[SMALL_T * 8 * 4];                               // the last block: the pairs' experts (up to 512 pairs)
     __shared__ int is_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int e = blockIdx.x;                 // one block per expert: every thread takes 16-byte pieces of the row
+    const int e0 = blockIdx.x * ROUTER_ROWS;
     {
-        float acc[SMALL_T];
+        float acc[NV];
 #pragma unroll
-        for (int t = 0; t < SMALL_T; ++t) acc[t] = 0.0f;
-        const __nv_bfloat16* wr = w + (size_t)e * D;
-        for (int d0 = threadIdx.x * 8; d0 < D; d0 += 512 * 8) {
-            const uint4 wv = *reinterpret_cast<const uint4*>(wr + d0);
-            const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
-            float wf[8];
+        for (int i = 0; i < NV; ++i) acc[i] = 0.0f;
+        for (int d0 = (warp * 32 + lane) * 8; d0 < D; d0 += 8 * 256) {
+            float wf[ROUTER_ROWS][8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float2 f = __bfloat1622float2(w2[i]);
-                wf[2 * i] = f.x, wf[2 * i + 1] = f.y;
+            for (int r = 0; r < ROUTER_ROWS; ++r) {
+                const int e = e0 + r < E ? e0 + r : E - 1;                // a ragged last block reads a valid row and drops the sum
+                const uint4 wv = *reinterpret_cast<const uint4*>(w + (size_t)e * D + d0);
+                const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __bfloat1622float2(w2[i]);
+                    wf[r][2 * i] = f.x, wf[r][2 * i + 1] = f.y;
+                }
             }
 #pragma unroll
-            for (int t = 0; t < SMALL_T; ++t) {
+            for (int t = 0; t < TP; ++t) {
                 if (t < T_) {
                     const uint4 xv = *reinterpret_cast<const uint4*>(xn + (size_t)t * D + d0);
                     const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const float2 f = __bfloat1622float2(x2[i]);
-                        acc[t] = fmaf(f.x, wf[2 * i], acc[t]);
-                        acc[t] = fmaf(f.y, wf[2 * i + 1], acc[t]);
+#pragma unroll
+                        for (int r = 0; r < ROUTER_ROWS; ++r) {
+                            acc[r * TP + t] = fmaf(f.x, wf[r][2 * i], acc[r * TP + t]);
+                            acc[r * TP + t] = fmaf(f.y, wf[r][2 * i + 1], acc[r * TP + t]);
+                        }
                     }
                 }
             }
         }
 #pragma unroll
-        for (int t = 0; t < SMALL_T; ++t) {
-            if (t < T_) {
-                const float z = warp_sum(acc[t]);
-                if (lane == 0) red[warp][t] = z;
-            }
+        for (int p0 = 0; p0 < NV; p0 += PASS) {
+            float part[PASS];
+#pragma unroll
+            for (int i = 0; i < PASS; ++i) part[i] = acc[p0 + i];
+            const float total = transpose_reduce<PASS>(part);
+            constexpr int STEP = 32 / PASS;                               // lanes 0, STEP, 2 STEP, ... hold sums 0, 1, 2, ...
+            if (lane % STEP == 0) meet[warp][p0 + lane / STEP] = total;
         }
         __syncthreads();
-        if (threadIdx.x < T_) {
-            float z = 0.0f;
+        if (threadIdx.x < NV) {
+            const int r = threadIdx.x / TP, t = threadIdx.x % TP;
+            if (t < T_ && e0 + r < E) {
+                float z = 0.0f;
 #pragma unroll
-            for (int wi = 0; wi < 16; ++wi) z += red[wi][threadIdx.x];       // warps in order: a fixed sum
-            logits[(size_t)threadIdx.x * E + e] = z;
+                for (int wi = 0; wi < 8; ++wi) z += meet[wi][threadIdx.x];       // warps in order: a fixed sum
+                logits[(size_t)t * E + e0 + r] = z;
+            }
         }
     }
     __threadfence();
@@ -216,25 +258,46 @@ __global__ void __launch_bounds__(512) router_small_kernel(const __nv_bfloat16* 
     __syncthreads();
     if (!is_last) return;
     __threadfence();
-    for (int t = warp; t < T_; t += 16) {        // a warp per token, its scores in registers
+    const int pairs = T_ * k;
+    const bool sort_here = pairs <= SMALL_T * 8 * 4;          // the pairs' experts fit the shared array: they are sorted from there
+    for (int t = warp; t < T_; t += 8) {         // a warp per token, its scores in registers
         const float* z = logits + (size_t)t * E;
         if (E <= 256) warp_route_regs<8>(z, E, k, sigmoid, renorm, sel_e + (size_t)t * k, sel_w + (size_t)t * k);
         else warp_route_regs<22>(z, E, k, sigmoid, renorm, sel_e + (size_t)t * k, sel_w + (size_t)t * k);
+        __syncwarp();
+        if (sort_here)
+            for (int r = lane; r < k; r += 32) pair_e[t * k + r] = sel_e[(size_t)t * k + r];      // this warp's own stores, read back
     }
-    // pairs sorted by expert (stable): tiles of one expert run side by side and share its weights in L2
+    // pairs sorted by expert (stable): tiles of one expert run side by side and share its weights in L2.  A pair's
+    // place is the number of pairs with a lower expert, or the same expert and a lower index.
     __syncthreads();
-    const int pairs = T_ * k;
-    int* sel_s = reinterpret_cast<int*>(sc);      // the scores are done with: T_ * k <= 16 * E ints fit
-    for (int p = threadIdx.x; p < pairs; p += blockDim.x) sel_s[p] = sel_e[p];
-    __syncthreads();
-    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
-        const int e = sel_s[p];
-        int rank = 0;
-        for (int q = 0; q < pairs; ++q) {
-            const int eq = sel_s[q];
-            rank += (eq < e) || (eq == e && q < p);
+    if (sort_here) {
+        // `share` lanes count for one pair, each over its part of the pairs
+        int share = 1;
+        while (share < 32 && pairs * share * 2 <= (int)blockDim.x) share *= 2;
+        for (int base = 0; base < pairs; base += blockDim.x / share) {
+            const int p = base + threadIdx.x / share, sub = threadIdx.x % share;
+            int rank = 0;
+            if (p < pairs) {
+                const int e = pair_e[p];
+                for (int q = sub; q < pairs; q += share) {
+                    const int eq = pair_e[q];
+                    rank += (eq < e) || (eq == e && q < p);
+                }
+            }
+            for (int o = share >> 1; o > 0; o >>= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);
+            if (p < pairs && sub == 0) order[rank] = p;
         }
-        order[rank] = p;
+    } else {
+        for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+            const int e = sel_e[p];
+            int rank = 0;
+            for (int q = 0; q < pairs; ++q) {
+                const int eq = sel_e[q];
+                rank += (eq < e) || (eq == e && q < p);
+            }
+            order[rank] = p;
+        }
     }
     if (threadIdx.x == 0) *ticket = 0;          // ready for the next launch
 }
@@ -465,8 +528,16 @@ Q6K_API int q6k_router_small(const void* xn, const void* w, int T_, int E, int D
     Q6K_REQUIRE(q6k_router_small_supported(T_, E, D, k), "router_small: %d tokens, %d experts of width %d, %d per token (at most %d tokens, 704 experts)",
                 T_, E, D, k, SMALL_T);
     Q6K_REQUIRE(((uintptr_t)xn & 15) == 0 && ((uintptr_t)w & 15) == 0, "router_small: D=%d must be a multiple of 8 and the operands 16-byte aligned", D);
-    q6k_launch(router_small_kernel, E, 512, 16 * E * sizeof(float), st, (const __nv_bfloat16*)xn, (const __nv_bfloat16*)w, T_, E, D, k,
-                                                                       sigmoid, renorm, logits, sel_e, sel_w, order, ticket);
+    const int blocks = (E + ROUTER_ROWS - 1) / ROUTER_ROWS;
+#define ROUTER_LAUNCH(TP)                                                                                                            \
+    q6k_launch(router_small_kernel<TP>, blocks, 256, 0, st, (const __nv_bfloat16*)xn, (const __nv_bfloat16*)w, T_, E, D, k, sigmoid, renorm, \
+               logits, sel_e, sel_w, order, ticket)
+    if (T_ == 1) ROUTER_LAUNCH(1);
+    else if (T_ == 2) ROUTER_LAUNCH(2);
+    else if (T_ <= 4) ROUTER_LAUNCH(4);
+    else if (T_ <= 8) ROUTER_LAUNCH(8);
+    else ROUTER_LAUNCH(16);
+#undef ROUTER_LAUNCH
     return q6k_check_launch("router_small");
 }
 

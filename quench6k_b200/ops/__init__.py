@@ -427,6 +427,38 @@ def gemv(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = None, ou
     return out
 
 
+def gemm_skinny_preferred(tokens: int, N: int, K: int) -> bool:
+    """Whether a bfloat16 product of `tokens` rows (3 to 16) with an [N, K] matrix should go to the mma.sync kernel for few tokens."""
+    lib = library()
+    lib.q6k_gemm_skinny_preferred.restype = ctypes.c_int
+    return bool(lib.q6k_gemm_skinny_preferred(_i(tokens), _i(N), _i(K)))
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+                accumulate: bool = False) -> torch.Tensor:
+    """out[t] (+)= x[t] @ w^T for at most 16 rows of x (bfloat16, FP32 sums and output) on mma.sync, no split of K over
+    blocks; with w2 the SwiGLU epilogue silu(x w^T) * (x w2^T) in bfloat16."""
+    if not tc_supported(x, w) or w.dim() != 2:
+        raise KernelError("gemm_skinny: operands must be bfloat16 matrices with K a multiple of 8 and 16-byte aligned rows")
+    T, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"gemm_skinny: x has K={K}, w has K={w.shape[1]}")
+    epi = EPI_SWIGLU if w2 is not None else (EPI_ADD if accumulate else EPI_STORE)
+    out_dtype = torch.bfloat16 if w2 is not None else torch.float32
+    if w2 is not None:
+        _need(w2, "w2", torch.bfloat16, w.shape)
+    if out is None:
+        if accumulate:
+            raise KernelError("gemm_skinny: accumulate needs an output")
+        out = torch.empty((T, N), dtype=out_dtype, device=x.device)
+    _need(out, "out", out_dtype)
+    if out.shape[0] < T or out.shape[1] != N:
+        raise KernelError(f"gemm_skinny: out has shape {tuple(out.shape)}, needs [{T}, {N}]")
+    _call("q6k_gemm_skinny", _ptr(x), _ll(x.stride(0)), _i(T), _ptr(w), _ptr(w2), _i(N), _i(K), _ptr(out), _ll(out.stride(0)), _i(epi), _stream())
+    return out
+
+
 # --------------------------------------------------------------------------- attention
 def qk_prep(qkv: torch.Tensor, Hq: int, Hkv: int, hd: int, q_norm, k_norm, eps: float, rotary,
             positions: torch.Tensor, req_of_token: torch.Tensor, block_table: Optional[torch.Tensor], page_size: int,

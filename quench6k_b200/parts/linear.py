@@ -2,8 +2,8 @@
 
 float32 operands always take the CUDA-core FP32 kernel (no reduced-precision matrix mode exists on
 that path).  bfloat16 operands take the tcgen05 tensor-core kernel where the shape allows (K a
-multiple of 8, rows starting on 16 bytes), the matrix-vector kernel where the library prefers it (a
-step of a token or two), and the CUDA-core kernel otherwise.
+multiple of 8, rows starting on 16 bytes), the matrix-vector kernel or the mma.sync kernel for few tokens where the
+library prefers them (steps of at most 16 tokens), and the CUDA-core kernel otherwise.
 """
 from __future__ import annotations
 
@@ -26,6 +26,8 @@ def matmul(a: torch.Tensor, w: torch.Tensor, rt, out: Optional[torch.Tensor] = N
     if _tc(a, w, rt):
         if ops.gemv_preferred(a.shape[0], w.shape[0], w.shape[1]):       # a token or two: the matrix-vector kernel
             return ops.gemv(a, w, out=out, accumulate=accumulate)
+        if ops.gemm_skinny_preferred(a.shape[0], w.shape[0], w.shape[1]):  # up to 16 tokens against many rows: mma.sync, K not split over blocks
+            return ops.gemm_skinny(a, w, out=out, accumulate=accumulate)
         if partials_ok and out is None and not accumulate and w.shape[0] % 4 == 0:
             return ops.gemm_tc(a, w, keep_partials=True)
         return ops.gemm_tc(a, w, out=out, accumulate=accumulate)
@@ -37,6 +39,8 @@ def swiglu_matmul(a: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, rt)
     if _tc(a, w_gate, rt):
         if ops.gemv_preferred(a.shape[0], w_gate.shape[0], w_gate.shape[1]):
             return ops.gemv(a, w_gate, w2=w_up)
+        if ops.gemm_skinny_preferred(a.shape[0], w_gate.shape[0], w_gate.shape[1]):
+            return ops.gemm_skinny(a, w_gate, w2=w_up)
         return ops.gemm_tc(a, w_gate, w2=w_up)
     return ops.gemm_simt(a, w_gate, w2=w_up)
 

@@ -380,6 +380,30 @@ def test_gemv_dense(M, N, K):
     assert ops.gemv_preferred(1, 5120, 2048) and not ops.gemv_preferred(8, 5120, 2048) and not ops.gemv_preferred(1, 151936, 2048)
 
 
+@pytest.mark.parametrize("M,N,K", [(8, 5120, 2048), (3, 4096, 512), (16, 4100, 4096), (11, 77, 520), (1, 16, 1032), (9, 40, 264), (5, 8200, 8)])
+def test_gemm_skinny(M, N, K):
+    """The mma.sync kernel for at most 16 tokens against float64 (its operands enter the instruction in a permuted
+    order of k, which both sides must agree on): store, accumulation, SwiGLU; ragged rows, tokens and widths."""
+    from quench6k_b200 import ops
+    a, w = _t(M, K, dtype=torch.bfloat16), _t(N, K, dtype=torch.bfloat16, seed=1)
+    ref = a.double().cpu() @ w.double().cpu().T
+    out = ops.gemm_skinny(a, w)
+    tol = 1e-5 * math.sqrt(K) * ref.abs().max()
+    assert out.dtype == torch.float32 and (out.double().cpu() - ref).abs().max() <= tol
+    base = _t(M, N, seed=2)
+    acc = base.clone()
+    ops.gemm_skinny(a, w, out=acc, accumulate=True)
+    assert (acc.double().cpu() - (base.double().cpu() + ref)).abs().max() <= tol
+    w2 = _t(N, K, dtype=torch.bfloat16, seed=3)
+    act = ops.gemm_skinny(a, w, w2=w2)
+    want = P.silu(ref) * (a.double().cpu() @ w2.double().cpu().T)
+    assert act.dtype == torch.bfloat16 and (act.double().cpu() - want).abs().max() <= 1e-2 * want.abs().max()
+    with pytest.raises(ops.KernelError, match="tokens"):
+        ops.gemm_skinny(_t(17, K, dtype=torch.bfloat16), w)
+    assert ops.gemm_skinny_preferred(8, 5120, 2048) and ops.gemm_skinny_preferred(1, 151936, 2048)
+    assert not ops.gemm_skinny_preferred(8, 2048, 4096) and not ops.gemm_skinny_preferred(1, 5120, 2048) and not ops.gemm_skinny_preferred(17, 5120, 2048)
+
+
 @pytest.mark.parametrize("T,k,E,D,I", [(1, 8, 256, 2048, 512), (2, 3, 7, 264, 40), (9, 2, 5, 72, 136)])
 def test_gemv_per_pair(T, k, E, D, I):
     """The same kernel with one (token, expert) pair per block row, as the decode path of the experts calls it."""

@@ -102,10 +102,10 @@ __device__ __forceinline__ int plan_block_sum(int v, int* red) {
     return t;
 }
 
-__global__ void __launch_bounds__(PLAN_THREADS) attention_plan_kernel(const int* __restrict__ positions, const int* __restrict__ req_of_token,
-                                                                       const int* __restrict__ tile_tok0, const int* __restrict__ tile_ntok,
-                                                                       int n_tiles, int window, int n_work, int min_per, int* __restrict__ work,
-                                                                       int* __restrict__ tile_plan) {
+__global__ void __launch_bounds__(PLAN_THREADS) attention_plan_kernel(const int* positions, const int* req_of_token,
+                                                                       const int* tile_tok0, const int* tile_ntok,
+                                                                       int n_tiles, int window, int n_work, int min_per, int* work,
+                                                                       int* tile_plan) {
     pdl_enter();
     __shared__ int red[PLAN_THREADS / 32];
     __shared__ int scan[PLAN_THREADS];

@@ -61,10 +61,17 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // every block of the kernel before it has executed pdl_launch() (or ended); it must execute
 // pdl_wait() before it touches anything an earlier kernel writes or reads, since pdl_wait() returns
 // only when the kernel before it has completed and its memory is visible.  Every kernel calls
-// pdl_enter() (both, in this order) first unless it has work that needs no earlier result: the
-// dense tensor-core GEMM sets itself up and fetches weights before it waits.  A kernel that
+// pdl_enter() first (the wait, then the signal) unless it has work that needs no earlier result: the
+// products set themselves up and fetch weights before they wait, and signal first.  Waiting before
+// signalling is what lets such a kernel also read, before its wait, what the kernel before its
+// predecessor wrote (a pair list two kernels old): its predecessor, if it is an ordinary kernel,
+// lets nobody start before it has itself seen everything older complete, whatever the launch mode.  A kernel that
 // allocates tensor memory calls pdl_launch() only after the allocation, so that a successor cannot
 // take the columns one of its own blocks still needs.  Without the attribute both are no-ops.
+// Pointers to anything an earlier kernel of the step writes carry no __restrict__: a load through a `const __restrict__`
+// pointer counts as read-only for the kernel's lifetime, and the compiler may move it ahead of pdl_wait() (it did, in
+// the matrix-vector kernel: a step replayed from a CUDA graph then read activations that were not written yet).
+// Only weights keep the qualifier.
 //
 // Measured on B200 under CUDA-graph replay, the attribute costs about 0.3 us per launch when the
 // kernel has nothing to overlap (a decode step with it on every launch: 4.93 vs 4.86 ms), so only
@@ -73,8 +80,16 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 __device__ __forceinline__ void pdl_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_enter() {
-    pdl_launch();
     pdl_wait();
+    pdl_launch();
+}
+// 16 bytes that the kernel before this one may have written, read after pdl_wait(): a volatile asm load, which the compiler
+// keeps behind the (volatile asm) wait.  A plain load through a `const __restrict__` pointer counts as read-only for the
+// kernel's lifetime and may be moved ahead of the wait, where the data is not there yet.
+__device__ __forceinline__ uint4 ld_after_wait(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
 }
 
 int q6k_pdl_mode();           // 0: never, 1: every launch, 2: launches marked as overlapping

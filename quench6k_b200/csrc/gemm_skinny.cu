@@ -36,10 +36,13 @@ enum { SK_STORE = 0, SK_ADD = 1, SK_SWIGLU = 2 };
 // block works on the same rows and takes every eighth stretch of K; LOADS: 16-byte loads per lane and row in flight at
 // once (a stretch is 32 LOADS elements of k: 4 for the usual widths, 8 for long rows, which then take fewer turns).
 template <int NB, int RB, int EPI, int LOADS>
-__global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, int T_,
+__global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx, int T_,
                                                                     const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ w2,
-                                                                    void* __restrict__ out, long long ldo, int N, int K) {
-    pdl_enter();
+                                                                    void* out, long long ldo, int N, int K) {
+    // The weights are a model's and older than any kernel of the step: their first stretch is asked for while the kernel
+    // launched before this one still runs (programmatic dependent launch); the activations and the output wait for it.
+    pdl_launch();
+    bool waited = false;
     constexpr bool DUAL = EPI == SK_SWIGLU;
     constexpr int MATS = DUAL ? 2 : 1;
     __shared__ float meet[SK_WARPS][MATS * RB * NB * 4 * 32];
@@ -82,9 +85,18 @@ __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(const __nv_b
                 for (int rb = 0; rb < RB; ++rb)
 #pragma unroll
                     for (int h = 0; h < 2; ++h) a[m][rb][h][j] = in ? sk_ld_stream(wrow[m][rb][h] + k) : make_uint4(0, 0, 0, 0);
+        }
+        if (!waited) {
+            pdl_wait();
+            waited = true;
+        }
+#pragma unroll
+        for (int j = 0; j < LOADS; ++j) {
+            const int k = k0 + j * 32;
+            const bool in = k + pair * 8 < K;
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb)
-                b[nb][j] = in && live[nb] ? *reinterpret_cast<const uint4*>(xrow[nb] + k) : make_uint4(0, 0, 0, 0);
+                b[nb][j] = in && live[nb] ? ld_after_wait(xrow[nb] + k) : make_uint4(0, 0, 0, 0);
         }
 #pragma unroll
         for (int j = 0; j < LOADS; ++j)
@@ -99,6 +111,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(const __nv_b
                         sk_mma(acc[m][rb][nb], lo.z, hi.z, lo.w, hi.w, t.z, t.w);
                     }
     }
+    if (!waited) pdl_wait();                  // a warp without a stretch of its own
     // the warps' sums, fragment by fragment: [matrix][row block][token block][4] per lane
     constexpr int PER_LANE = MATS * RB * NB * 4;
 #pragma unroll
@@ -133,9 +146,9 @@ template <int NB, int RB, int LOADS>
 int skinny_launch(int epi, cudaStream_t st, const __nv_bfloat16* x, long long ldx, int T_, const __nv_bfloat16* w, const __nv_bfloat16* w2, void* out,
                   long long ldo, int N, int K) {
     const int grid = (N + RB * 16 - 1) / (RB * 16);
-    if (epi == SK_SWIGLU) q6k_launch(gemm_skinny_kernel<NB, 1, SK_SWIGLU, 4>, (N + 15) / 16, SK_WARPS * 32, 0, st, x, ldx, T_, w, w2, out, ldo, N, K);
-    else if (epi == SK_ADD) q6k_launch(gemm_skinny_kernel<NB, RB, SK_ADD, LOADS>, grid, SK_WARPS * 32, 0, st, x, ldx, T_, w, w2, out, ldo, N, K);
-    else q6k_launch(gemm_skinny_kernel<NB, RB, SK_STORE, LOADS>, grid, SK_WARPS * 32, 0, st, x, ldx, T_, w, w2, out, ldo, N, K);
+    if (epi == SK_SWIGLU) q6k_launch_as(true, gemm_skinny_kernel<NB, 1, SK_SWIGLU, 4>, (N + 15) / 16, SK_WARPS * 32, 0, st, x, ldx, T_, w, w2, out, ldo, N, K);
+    else if (epi == SK_ADD) q6k_launch_as(true, gemm_skinny_kernel<NB, RB, SK_ADD, LOADS>, grid, SK_WARPS * 32, 0, st, x, ldx, T_, w, w2, out, ldo, N, K);
+    else q6k_launch_as(true, gemm_skinny_kernel<NB, RB, SK_STORE, LOADS>, grid, SK_WARPS * 32, 0, st, x, ldx, T_, w, w2, out, ldo, N, K);
     return q6k_check_launch("gemm_skinny");
 }
 

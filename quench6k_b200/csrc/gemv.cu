@@ -42,11 +42,14 @@ enum { GEMV_STORE = 0, GEMV_ADD = 1, GEMV_SWIGLU = 2 };
 // grid (ceil(N / ((GEMV_WARPS / KW) * ROWS)), pairs or 1).  TT: tokens handled together (dense calls; 1 for pair calls);
 // ROWS: output rows of a warp; KW: warps that share a row's K.
 template <int TT, int ROWS, int KW, int EPI>
-__global__ void __launch_bounds__(GEMV_WARPS * 32, 4) gemv_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const __nv_bfloat16* __restrict__ w,
+__global__ void __launch_bounds__(GEMV_WARPS * 32, 4) gemv_kernel(const __nv_bfloat16* x, long long ldx, const __nv_bfloat16* __restrict__ w,
                                                                const __nv_bfloat16* __restrict__ w2, long long expert_stride,
-                                                               const int* __restrict__ pair_expert, int pair_div, void* __restrict__ out,
-                                                               long long ldo, int N, int K) {
-    pdl_enter();
+                                                               const int* pair_expert, int pair_div, void* out,
+                                                               long long ldo, int N, int K, int early) {
+    // early: the weights (and the pair list) are older than the kernel before this one, so they may be asked for
+    // before that kernel has ended (programmatic dependent launch); the activations and the output wait for it
+    if (!early) pdl_wait();                   // an ordinary kernel: the wait first, then the signal (see common.cuh)
+    pdl_launch();
     constexpr bool DUAL = EPI == GEMV_SWIGLU;
     constexpr int RG = GEMV_WARPS / KW;                                   // groups of warps along the rows
     constexpr int SUMS = ROWS * TT * (DUAL ? 2 : 1);
@@ -77,8 +80,12 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, 4) gemv_kernel(const __nv_bfl
                 wv[r] = ld_stream(w + row * K + k0);
                 if (DUAL) w2v[r] = ld_stream(w2 + row * K + k0);
             }
+            if (early) {
+                pdl_wait();                                              // the weights are on their way; now the kernel before must be done
+                early = 0;
+            }
 #pragma unroll
-            for (int t = 0; t < TT; ++t) xv[t] = *reinterpret_cast<const uint4*>(x + (xrow + t) * ldx + k0);
+            for (int t = 0; t < TT; ++t) xv[t] = ld_after_wait(x + (xrow + t) * ldx + k0);
             float xf[TT][8];
 #pragma unroll
             for (int t = 0; t < TT; ++t) unpack8(xv[t], xf[t]);
@@ -110,6 +117,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, 4) gemv_kernel(const __nv_bfl
                 if (lane == 0) meet[warp][ROWS * TT + r * TT + t] = s2;
             }
         }
+    if (early) pdl_wait();                                                // a warp without a stride of its own
     __syncthreads();
     // one thread per (row group, row, token): the KW warps' sums in warp order
     const int idx = threadIdx.x;
@@ -130,23 +138,24 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, 4) gemv_kernel(const __nv_bfl
 }
 
 template <int TT, int ROWS, int KW>
-int gemv_launch(int epi, int blocks_y, cudaStream_t st, const __nv_bfloat16* x, long long ldx, const __nv_bfloat16* w, const __nv_bfloat16* w2,
+int gemv_launch(int early, int epi, int blocks_y, cudaStream_t st, const __nv_bfloat16* x, long long ldx, const __nv_bfloat16* w, const __nv_bfloat16* w2,
                 long long expert_stride, const int* pair_expert, int pair_div, void* out, long long ldo, int N, int K) {
     const int per_block = (GEMV_WARPS / KW) * ROWS;
     const dim3 grid((N + per_block - 1) / per_block, blocks_y);
-    if (epi == GEMV_SWIGLU) q6k_launch(gemv_kernel<TT, ROWS, KW, GEMV_SWIGLU>, grid, GEMV_WARPS * 32, 0, st, x, ldx, w, w2, expert_stride, pair_expert, pair_div, out, ldo, N, K);
-    else if (epi == GEMV_ADD) q6k_launch(gemv_kernel<TT, ROWS, KW, GEMV_ADD>, grid, GEMV_WARPS * 32, 0, st, x, ldx, w, w2, expert_stride, pair_expert, pair_div, out, ldo, N, K);
-    else q6k_launch(gemv_kernel<TT, ROWS, KW, GEMV_STORE>, grid, GEMV_WARPS * 32, 0, st, x, ldx, w, w2, expert_stride, pair_expert, pair_div, out, ldo, N, K);
+    const bool over = early != 0;
+    if (epi == GEMV_SWIGLU) q6k_launch_as(over, gemv_kernel<TT, ROWS, KW, GEMV_SWIGLU>, grid, GEMV_WARPS * 32, 0, st, x, ldx, w, w2, expert_stride, pair_expert, pair_div, out, ldo, N, K, early);
+    else if (epi == GEMV_ADD) q6k_launch_as(over, gemv_kernel<TT, ROWS, KW, GEMV_ADD>, grid, GEMV_WARPS * 32, 0, st, x, ldx, w, w2, expert_stride, pair_expert, pair_div, out, ldo, N, K, early);
+    else q6k_launch_as(over, gemv_kernel<TT, ROWS, KW, GEMV_STORE>, grid, GEMV_WARPS * 32, 0, st, x, ldx, w, w2, expert_stride, pair_expert, pair_div, out, ldo, N, K, early);
     return q6k_check_launch("gemv");
 }
 
 template <int TT, int ROWS>
-int gemv_launch_k(int kw, int epi, int blocks_y, cudaStream_t st, const __nv_bfloat16* x, long long ldx, const __nv_bfloat16* w, const __nv_bfloat16* w2,
+int gemv_launch_k(int early, int kw, int epi, int blocks_y, cudaStream_t st, const __nv_bfloat16* x, long long ldx, const __nv_bfloat16* w, const __nv_bfloat16* w2,
                   long long es, const int* pe, int pd, void* out, long long ldo, int N, int K) {
-    if (kw == 8) return gemv_launch<TT, ROWS, 8>(epi, blocks_y, st, x, ldx, w, w2, es, pe, pd, out, ldo, N, K);
-    if (kw == 4) return gemv_launch<TT, ROWS, 4>(epi, blocks_y, st, x, ldx, w, w2, es, pe, pd, out, ldo, N, K);
-    if (kw == 2) return gemv_launch<TT, ROWS, 2>(epi, blocks_y, st, x, ldx, w, w2, es, pe, pd, out, ldo, N, K);
-    return gemv_launch<TT, ROWS, 1>(epi, blocks_y, st, x, ldx, w, w2, es, pe, pd, out, ldo, N, K);
+    if (kw == 8) return gemv_launch<TT, ROWS, 8>(early, epi, blocks_y, st, x, ldx, w, w2, es, pe, pd, out, ldo, N, K);
+    if (kw == 4) return gemv_launch<TT, ROWS, 4>(early, epi, blocks_y, st, x, ldx, w, w2, es, pe, pd, out, ldo, N, K);
+    if (kw == 2) return gemv_launch<TT, ROWS, 2>(early, epi, blocks_y, st, x, ldx, w, w2, es, pe, pd, out, ldo, N, K);
+    return gemv_launch<TT, ROWS, 1>(early, epi, blocks_y, st, x, ldx, w, w2, es, pe, pd, out, ldo, N, K);
 }
 
 }  // namespace
@@ -161,8 +170,11 @@ Q6K_API int q6k_gemv_preferred(int tokens, int N, int K) {
 // x: bfloat16 [tokens, K] (row pitch ldx elements, rows on 16 bytes); w (and w2 for the SwiGLU epilogue): bfloat16 [N, K], or
 // [experts, N, K] with pair_expert (int32 [pairs]) naming each pair's expert, pair y using row y / pair_div of x and
 // writing row y of out.  out: FP32 [rows, N] (epi 0 store, 1 add) or bfloat16 [rows, N] (epi 2), row pitch ldo.
+// early != 0: the weights and the pair list were written before the kernel that precedes this one started (weights of a
+// model always; a pair list only when another kernel lies between its maker and this call): the launch then carries the
+// programmatic-launch attribute and streams its weights while that kernel ends; x and out are touched after it has ended.
 Q6K_API int q6k_gemv(const void* x, long long ldx, int tokens, const void* w, const void* w2, int N, int K, const int* pair_expert, int pairs,
-                     int pair_div, void* out, long long ldo, int epi, cudaStream_t st) {
+                     int pair_div, void* out, long long ldo, int epi, int early, cudaStream_t st) {
     if (tokens == 0 || (pair_expert && pairs == 0)) return 0;
     Q6K_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)w2 & 15) == 0,
                 "gemv: K=%d and the row pitch %lld must be multiples of 8 and the operands 16-byte aligned", K, ldx);
@@ -174,13 +186,13 @@ Q6K_API int q6k_gemv(const void* x, long long ldx, int tokens, const void* w, co
     const int strides = (K + 255) / 256;                                  // 256-element strides of a row
     const int kw = strides >= 8 ? 8 : strides >= 4 ? 4 : strides >= 2 ? 2 : 1;
     if (pair_expert) {
-        if (epi == GEMV_SWIGLU) return gemv_launch_k<1, 2>(kw, epi, pairs, st, xp, ldx, wp, w2p, es, pair_expert, pair_div, out, ldo, N, K);
-        return gemv_launch_k<1, 4>(kw, epi, pairs, st, xp, ldx, wp, w2p, es, pair_expert, pair_div, out, ldo, N, K);
+        if (epi == GEMV_SWIGLU) return gemv_launch_k<1, 2>(early, kw, epi, pairs, st, xp, ldx, wp, w2p, es, pair_expert, pair_div, out, ldo, N, K);
+        return gemv_launch_k<1, 4>(early, kw, epi, pairs, st, xp, ldx, wp, w2p, es, pair_expert, pair_div, out, ldo, N, K);
     }
 #define GEMV_CASE(TT)                                                                                                               \
     case TT:                                                                                                                        \
-        if (epi == GEMV_SWIGLU || TT > 2) return gemv_launch_k<TT, 2>(kw, epi, 1, st, xp, ldx, wp, w2p, es, nullptr, 1, out, ldo, N, K); \
-        return gemv_launch_k<TT, 4>(kw, epi, 1, st, xp, ldx, wp, w2p, es, nullptr, 1, out, ldo, N, K);
+        if (epi == GEMV_SWIGLU || TT > 2) return gemv_launch_k<TT, 2>(early, kw, epi, 1, st, xp, ldx, wp, w2p, es, nullptr, 1, out, ldo, N, K); \
+        return gemv_launch_k<TT, 4>(early, kw, epi, 1, st, xp, ldx, wp, w2p, es, nullptr, 1, out, ldo, N, K);
     switch (tokens) {
         GEMV_CASE(1)
         GEMV_CASE(2)

@@ -187,10 +187,13 @@ __device__ __forceinline__ float transpose_reduce(float (&v)[NV]) {
 
 // TP: the token count rounded up to a power of two (1, 2, 4, 8, 16).
 template <int TP>
-__global__ void __launch_bounds__(256) router_small_kernel(const __nv_bfloat16* __restrict__ xn, const __nv_bfloat16* __restrict__ w, int T_, int E,
+__global__ void __launch_bounds__(256) router_small_kernel(const __nv_bfloat16* xn, const __nv_bfloat16* __restrict__ w, int T_, int E,
                                                            int D, int k, int sigmoid, int renorm, float* logits, int* sel_e, float* sel_w,
                                                            int* order, unsigned* ticket) {
-    pdl_enter();
+    // the router matrix is older than any kernel of the step: its rows are asked for while the kernel launched before this
+    // one still runs (programmatic dependent launch); the activations wait for that kernel
+    pdl_launch();
+    bool waited = false;
     constexpr int NV = ROUTER_ROWS * TP;                                  // sums of a warp: index = row * TP + token
     constexpr int PASS = NV > 32 ? 32 : NV;                               // reduced 32 at a time
     __shared__ float meet[8][NV];
@@ -215,10 +218,14 @@ __global__ void __launch_bounds__(256) router_small_kernel(const __nv_bfloat16* 
                     wf[r][2 * i] = f.x, wf[r][2 * i + 1] = f.y;
                 }
             }
+            if (!waited) {
+                pdl_wait();
+                waited = true;
+            }
 #pragma unroll
             for (int t = 0; t < TP; ++t) {
                 if (t < T_) {
-                    const uint4 xv = *reinterpret_cast<const uint4*>(xn + (size_t)t * D + d0);
+                    const uint4 xv = ld_after_wait(xn + (size_t)t * D + d0);
                     const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
@@ -232,6 +239,7 @@ __global__ void __launch_bounds__(256) router_small_kernel(const __nv_bfloat16* 
                 }
             }
         }
+        if (!waited) pdl_wait();                                          // a warp without a stride of its own
 #pragma unroll
         for (int p0 = 0; p0 < NV; p0 += PASS) {
             float part[PASS];
@@ -324,8 +332,8 @@ __global__ void count_kernel(const int* sel_e, int pairs, int E, int* counts) {
 // deterministic one): lanes with the same expert find one another with match.any, the warps' counts per expert
 // stand in shared memory ([32][E] bytes, a warp has at most 32 pairs), a pair adds those of the warps before its own.
 constexpr int COUNT_RANK_MAX_E = 1024;
-__global__ void __launch_bounds__(PERM_CHUNK) count_rank_kernel(const int* __restrict__ sel_e, int pairs, int E, int* __restrict__ counts,
-                                                                int* __restrict__ local) {
+__global__ void __launch_bounds__(PERM_CHUNK) count_rank_kernel(const int* sel_e, int pairs, int E, int* counts,
+                                                                int* local) {
     pdl_enter();
     extern __shared__ unsigned char warp_cnt[];          // [32][E]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, c = blockIdx.x;
@@ -351,7 +359,7 @@ __global__ void __launch_bounds__(PERM_CHUNK) count_rank_kernel(const int* __res
 }
 
 // out[r, :] = x[idx[r], :] (rows of vec_per_row 16-byte words), for the path with more experts than count_rank_kernel takes.
-__global__ void gather_pairs_kernel(const uint4* __restrict__ x, const int* __restrict__ idx, uint4* __restrict__ out, int vec_per_row) {
+__global__ void gather_pairs_kernel(const uint4* x, const int* idx, uint4* out, int vec_per_row) {
     pdl_enter();
     const size_t src = (size_t)idx[blockIdx.x] * vec_per_row, dst = (size_t)blockIdx.x * vec_per_row;
     for (int i = threadIdx.x; i < vec_per_row; i += blockDim.x) out[dst + i] = x[src + i];
@@ -359,8 +367,8 @@ __global__ void gather_pairs_kernel(const uint4* __restrict__ x, const int* __re
 
 // After the offsets: a pair's row is its expert's offset plus its chunk's first row within the expert plus its
 // rank within the chunk (which stands in pair_row); row_token[row] = pair / k.
-__global__ void finish_rank_kernel(const int* __restrict__ sel_e, const int* __restrict__ chunk_base, const int* __restrict__ offsets,
-                                   int pairs, int k, int E, int* __restrict__ pair_row, int* __restrict__ row_token) {
+__global__ void finish_rank_kernel(const int* sel_e, const int* chunk_base, const int* offsets,
+                                   int pairs, int k, int E, int* pair_row, int* row_token) {
     pdl_enter();
     const int p = blockIdx.x * blockDim.x + threadIdx.x;
     if (p >= pairs) return;
@@ -372,9 +380,9 @@ __global__ void finish_rank_kernel(const int* __restrict__ sel_e, const int* __r
 
 // The same with the copy of the pair's input row: out[row, :] = x[pair / k, :] (rows of vec_per_row 16-byte words), a
 // block per pair.
-__global__ void finish_rank_gather_kernel(const int* __restrict__ sel_e, const int* __restrict__ chunk_base, const int* __restrict__ offsets,
-                                          int k, int E, int* __restrict__ pair_row, int* __restrict__ row_token, const uint4* __restrict__ x,
-                                          uint4* __restrict__ out, int vec_per_row) {
+__global__ void finish_rank_gather_kernel(const int* sel_e, const int* chunk_base, const int* offsets,
+                                          int k, int E, int* pair_row, int* row_token, const uint4* x,
+                                          uint4* out, int vec_per_row) {
     pdl_enter();
     const int p = blockIdx.x;
     const int e = sel_e[p];
@@ -530,7 +538,7 @@ Q6K_API int q6k_router_small(const void* xn, const void* w, int T_, int E, int D
     Q6K_REQUIRE(((uintptr_t)xn & 15) == 0 && ((uintptr_t)w & 15) == 0, "router_small: D=%d must be a multiple of 8 and the operands 16-byte aligned", D);
     const int blocks = (E + ROUTER_ROWS - 1) / ROUTER_ROWS;
 #define ROUTER_LAUNCH(TP)                                                                                                            \
-    q6k_launch(router_small_kernel<TP>, blocks, 256, 0, st, (const __nv_bfloat16*)xn, (const __nv_bfloat16*)w, T_, E, D, k, sigmoid, renorm, \
+    q6k_launch_as(true, router_small_kernel<TP>, blocks, 256, 0, st, (const __nv_bfloat16*)xn, (const __nv_bfloat16*)w, T_, E, D, k, sigmoid, renorm, \
                logits, sel_e, sel_w, order, ticket)
     if (T_ == 1) ROUTER_LAUNCH(1);
     else if (T_ == 2) ROUTER_LAUNCH(2);

@@ -267,7 +267,7 @@ constexpr int TOPK_CLUSTER_MIN_V = 8192;                 // shorter rows: one CT
 constexpr int TOPK_CLUSTER_MAX_SLICE = 48 * 1024;        // keys of a slice (192 KB of shared memory)
 
 __global__ void __cluster_dims__(TOPK_CLUSTER, 1, 1) __launch_bounds__(1024, 1)
-    topk_pool_cluster_kernel(const float* __restrict__ logits, int V, int K, int slice, int* out_ids, float* out_vals) {
+    topk_pool_cluster_kernel(const float* logits, int V, int K, int slice, int* out_ids, float* out_vals) {
     pdl_enter();
     namespace cg = cooperative_groups;
     extern __shared__ unsigned keys[];
@@ -394,8 +394,8 @@ namespace {
 // lse[row] = log(sum_i exp(logits[row, i])) and picked[row] = logits[row, target[row]]: what a perplexity needs of a row
 // of logits (reference: the row log-sum-exp of crates/cuda/kernels/topk.cu:181-198).  One block per row; the maximum
 // first, then the sum of the exponentials around it, the warps' sums added in warp order.
-__global__ void __launch_bounds__(1024) row_lse_kernel(const float* __restrict__ logits, int V, const int* __restrict__ target,
-                                                       float* __restrict__ lse, float* __restrict__ picked) {
+__global__ void __launch_bounds__(1024) row_lse_kernel(const float* logits, int V, const int* target,
+                                                       float* lse, float* picked) {
     pdl_enter();
     __shared__ float red[32];
     const float* row = logits + (size_t)blockIdx.x * V;
@@ -468,8 +468,8 @@ struct SampleRow {                  // 32 bytes per row, written by the host
     double u;                       // the request's next uniform in [0, 1)
 };
 
-__global__ void __launch_bounds__(POOL_MAX) sample_pool_kernel(const int* __restrict__ ids, const float* __restrict__ vals, int stride,
-                                                               const SampleRow* __restrict__ rows, int* __restrict__ out) {
+__global__ void __launch_bounds__(POOL_MAX) sample_pool_kernel(const int* ids, const float* vals, int stride,
+                                                               const SampleRow* rows, int* out) {
     pdl_enter();
     __shared__ double probs[POOL_MAX];
     const int row = blockIdx.x, tid = threadIdx.x;

@@ -396,10 +396,13 @@ def gemv_preferred(tokens: int, N: int, K: int) -> bool:
 
 
 def gemv(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, accumulate: bool = False,
-         pair_expert: Optional[torch.Tensor] = None, pair_div: int = 1) -> torch.Tensor:
+         pair_expert: Optional[torch.Tensor] = None, pair_div: int = 1, pairs_are_old: bool = False) -> torch.Tensor:
     """out[t] (+)= x[t] @ w^T for one to four rows of x (bfloat16, FP32 sums and output); with w2 the SwiGLU epilogue
     silu(x w^T) * (x w2^T) in bfloat16.  With pair_expert (int32 [pairs]) and w [experts, N, K]: pair y multiplies row
-    y // pair_div of x with the matrix of expert pair_expert[y] and writes row y (any number of pairs)."""
+    y // pair_div of x with the matrix of expert pair_expert[y] and writes row y (any number of pairs).
+    The kernel streams its weights while the kernel launched before it on the stream still runs (only x and out wait
+    for that kernel); with a pair list this needs the caller's word (pairs_are_old) that the list was not made by that
+    very kernel."""
     if not tc_supported(x, w):
         raise KernelError("gemv: operands must be bfloat16 with K a multiple of 8 and 16-byte aligned rows")
     K = x.shape[1]
@@ -422,8 +425,9 @@ def gemv(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = None, ou
     _need(out, "out", out_dtype)
     if out.shape[0] < rows or out.shape[1] != N:
         raise KernelError(f"gemv: out has shape {tuple(out.shape)}, needs [{rows}, {N}]")
+    early = pair_expert is None or pairs_are_old
     _call("q6k_gemv", _ptr(x), _ll(x.stride(0)), _i(x.shape[0]), _ptr(w), _ptr(w2), _i(N), _i(K), _ptr(pair_expert), _i(pairs), _i(pair_div),
-          _ptr(out), _ll(out.stride(0)), _i(epi), _stream())
+          _ptr(out), _ll(out.stride(0)), _i(epi), _i(1 if early else 0), _stream())
     return out
 
 

@@ -102,7 +102,7 @@ class RoutedExperts(FeedForward):
             if ops.gemv_preferred(T, self.I, self.D):                     # a token or two: the matrix-vector kernel per pair
                 act = ops.gemv(xn, self.w_gate, w2=self.w_up, pair_expert=sel_e.view(-1), pair_div=self.k)
                 ops.current_tag = "experts.down"
-                y = ops.gemv(act, self.w_down, pair_expert=sel_e.view(-1), pair_div=1)
+                y = ops.gemv(act, self.w_down, pair_expert=sel_e.view(-1), pair_div=1, pairs_are_old=True)   # the router made them, two kernels ago
             else:
                 act = ops.gemm_tc_pairs(xn, self.w_gate, sel_e, self.k, w2=self.w_up, order=order)  # [pairs, I]
                 ops.current_tag = "experts.down"

@@ -47,6 +47,8 @@ struct AttnParams {
     int n_work;
     int max_blocks, page_size, window, Hq, Hkv, G;
     float scale_log2;
+    int early;                               // the plan, the block tables and every key before a tile's first position are older than the
+                                             // kernel launched before this one: key tiles may be fetched before the wait for it
     int pool_rows;                           // rows of the [Hkv * pages * page_size, HD] view of a pool (TMA path)
     int num_pages;                           // pages of a pool (per KV head)
 };
@@ -197,7 +199,13 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + 32, WIDE ? 1 : 2) attent
                                                                                  const __grid_constant__ CUtensorMap tm_v,
                                                                                  const __grid_constant__ CUtensorMap tm_k_run,
                                                                                  const __grid_constant__ CUtensorMap tm_v_run, const AttnParams p) {
-    pdl_enter();
+    // Narrow tiles hold all the tokens a request brings to the step, so every key before the tile's first position was
+    // written by an earlier step: the producer fetches those key tiles while the kernel launched before this one (the
+    // one that writes this step's keys and q) still runs, and only then waits for it (programmatic dependent launch;
+    // the plan and the block tables are older than that kernel too).  Wide tiles wait first, like any other kernel.
+    const bool EARLY = !WIDE && p.early != 0;
+    if (EARLY) pdl_launch();
+    else pdl_enter();
     constexpr int CW = WIDE ? 8 : 4;         // consumer warps
     constexpr int ROWS = WIDE ? 128 : NQ;    // query rows of the CTA's tile
     constexpr int NB = NQ / 8;               // row blocks (n = 8) of a warp
@@ -243,8 +251,14 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + 32, WIDE ? 1 : 2) attent
     if (warp == CW) {
         const int ps = p.page_size;
         if (TMA && lane != 0) return;         // one elected lane issues the TMA loads; the copies of the other path take all 32
+        bool waited = !EARLY;
         for (int i = 0; i < n_mine; ++i) {
             const int st = i % STAGES;
+            // the first tiles of the ring need no free stage; of those, the ones that end before this step's first key need no wait
+            if (!waited && (i >= STAGES || (t_begin + i + 1) * KT > pos_first)) {
+                pdl_wait();
+                waited = true;
+            }
             if (i >= STAGES && !mbar_wait(empty0 + 8 * st, ((i / STAGES) & 1) ^ 1)) {
                 if (lane == 0) atomicExch(&g_attn_status, 1);
                 return;
@@ -305,6 +319,7 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + 32, WIDE ? 1 : 2) attent
     }
 
     // ------------------------------------------------------------------ the consumer warps
+    if (EARLY) pdl_wait();                    // q is the work of the kernel before this one
     // A thread of the fragment layout: quad = lane / 4 names a key (first product's rows) or a head
     // dimension (second product's rows), pair = lane % 4 names two neighbouring query rows.
     const int quad = lane >> 2, pair = lane & 3;
@@ -696,7 +711,7 @@ int launch(const AttnParams& p, const CUtensorMap* maps, int n_tiles, cudaStream
             return q6k_check_launch("attention_mma: shared memory attribute");
         configured = true;
     }
-    q6k_launch(attention_mma_kernel<HD, NQ, WIDE, TMA>, dim3(p.n_work, p.Hkv), (WIDE ? 8 : 4) * 32 + 32, smem, st, maps[0], maps[1], maps[2], maps[3], p);
+    q6k_launch_as(!WIDE && p.early != 0, attention_mma_kernel<HD, NQ, WIDE, TMA>, dim3(p.n_work, p.Hkv), (WIDE ? 8 : 4) * 32 + 32, smem, st, maps[0], maps[1], maps[2], maps[3], p);
     if (int rc = q6k_check_launch("attention_mma")) return rc;
     if (p.n_work > n_tiles) {                 // some tile may have more than one part
         q6k_launch(attention_merge_kernel<HD>, dim3(n_tiles, p.Hkv, ROWS), MERGE_THREADS, 0, st, p);
@@ -773,10 +788,13 @@ Q6K_API int q6k_attention_plan(const int* positions, const int* req_of_token, co
 // addresses a pool as one [Hkv * num_pages * page_size, hd] matrix); work / tile_plan: what q6k_attention_plan made for
 // these tiles (of at most rows / G tokens each; rows: 8, 16 or 128) and this window; part_o: FP32 [n_work * Hkv * rows * hd],
 // part_ml: FP32 [n_work * Hkv * rows * 2] (unused when n_work == n_tiles).
+// early != 0 (tiles of 8 or 16 rows only): the caller's word that the plan and the block table were made before the kernel
+// launched before this one started, and that this kernel writes this step's keys; key tiles older than a tile's first
+// position are then fetched while it still runs.
 Q6K_API int q6k_attention_mma(const void* q, const void* k_pages, const void* v_pages, long long num_pages, const int* block_table,
                               int max_blocks, int page_size, const int* work, const int* tile_plan, int n_work, int n_tiles, int rows,
                               int window, const float* sinks, float scale, void* out, float* part_o, float* part_ml, int Hq, int Hkv,
-                              int hd, cudaStream_t st) {
+                              int hd, int early, cudaStream_t st) {
     if (n_tiles == 0) return 0;
     Q6K_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention_mma: bad head counts Hq=%d Hkv=%d", Hq, Hkv);
     const int G = Hq / Hkv;
@@ -793,6 +811,7 @@ Q6K_API int q6k_attention_mma(const void* q, const void* k_pages, const void* v_
     p.part_o = part_o, p.part_ml = part_ml;
     p.max_blocks = max_blocks, p.page_size = page_size, p.window = window, p.Hq = Hq, p.Hkv = Hkv, p.G = G;
     p.scale_log2 = scale * LOG2E;
+    p.early = early;
     // pages of 8, 16, 32, 64 keys (or whole multiples of 64) are boxes TMA can place on the swizzle pattern
     p.num_pages = (int)num_pages;
     const long long pool_rows = num_pages * Hkv * page_size;

@@ -53,6 +53,7 @@ struct Params {
     int rows_total, N, K, ldo;
     int epilogue, stages, kb_per_split;
     int pair_div;                      // > 0: one tile per (token, slot) pair, see q6k_gemm_tc_pairs
+    int lists_old;                     // the pair list was written before the kernel launched before this one started: weights may be fetched before the wait
     int n_y, n_z;                      // row tiles (or pairs; an upper bound when num_tiles is given) and K slices
 };
 
@@ -140,8 +141,9 @@ template <int BT, bool DUAL>
 __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_w2,
                                                        const __grid_constant__ CUtensorMap tm_a, const Params p) {
     // Dense tiles follow from the launch alone, so their weights can be on the way before the kernel
-    // that makes the activations has ended; tile lists and pair lists come from earlier kernels.
-    const bool early = p.tile_group == nullptr;
+    // that makes the activations has ended; tile lists and pair lists come from earlier kernels, and
+    // only a caller who knows that another kernel lies between their maker and this one says so.
+    const bool early = p.tile_group == nullptr || p.lists_old != 0;
     if (!early) pdl_wait();
     const int n_x = (p.N + WM - 1) / WM;
     const int n_y = p.pair_div > 0 ? p.n_y : (p.tile_group ? *p.num_tiles : p.n_y);
@@ -637,7 +639,7 @@ int launch(const CUtensorMap& tw, const CUtensorMap& tw2, const CUtensorMap& ta,
     }
     const int slots = sm_count() * per_sm;
     const int grid = (int)(total < slots ? total : slots);
-    q6k_launch_as(p.tile_group == nullptr, gemm_tc_kernel<BT, DUAL>, grid, 192, smem, st, tw, tw2, ta, p);
+    q6k_launch_as(p.tile_group == nullptr || p.lists_old != 0, gemm_tc_kernel<BT, DUAL>, grid, 192, smem, st, tw, tw2, ta, p);
     return q6k_check_launch("gemm_tc");
 }
 
@@ -859,7 +861,7 @@ Q6K_API int q6k_gemm_tc_pairs_scratch(int pairs, int N, int K, int dual, long lo
 
 Q6K_API int q6k_gemm_tc_pairs(const void* A, long long lda, int a_rows, const void* W, const void* W2, int groups, int N, int K,
                               void* out, int ldo, int epilogue, const int* pair_expert, const int* pair_order, int pairs, int pair_div,
-                              float* partial, long long partial_floats, unsigned* tickets, int n_tickets, cudaStream_t st) {
+                              float* partial, long long partial_floats, unsigned* tickets, int n_tickets, int lists_old, cudaStream_t st) {
     if (pairs == 0 || N == 0) return 0;
     Q6K_REQUIRE(a_rows > 0 && N > 0 && K > 0 && groups > 0 && pairs > 0 && pair_div > 0, "gemm_tc_pairs: bad sizes rows=%d N=%d K=%d pairs=%d", a_rows, N, K, pairs);
     Q6K_REQUIRE(K % 8 == 0 && lda % 8 == 0, "gemm_tc_pairs: K=%d and the row pitch %lld must be multiples of 8", K, lda);
@@ -888,5 +890,6 @@ Q6K_API int q6k_gemm_tc_pairs(const void* A, long long lda, int a_rows, const vo
     p.partial = partial, p.tickets = tickets;
     p.pair_div = pair_div;
     p.pair_order = pair_order;
+    p.lists_old = lists_old;
     return dual ? launch<16, true>(tw, tw2, ta, p, pairs, splits, st) : launch<16, false>(tw, tw2, ta, p, pairs, splits, st);
 }

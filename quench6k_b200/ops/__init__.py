@@ -637,13 +637,15 @@ def attention_plan(positions: torch.Tensor, req_of_token: torch.Tensor, tile_tok
 def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                   req_of_token: torch.Tensor, positions: torch.Tensor, tile_tok0: torch.Tensor, tile_ntok: torch.Tensor,
                   rows: int, window: Optional[int], sinks: Optional[torch.Tensor], max_splits: int = 1, min_tiles: int = 2,
-                  scale: Optional[float] = None, out: Optional[torch.Tensor] = None, plan=None) -> torch.Tensor:
+                  scale: Optional[float] = None, out: Optional[torch.Tensor] = None, plan=None, plan_is_old: bool = False) -> torch.Tensor:
     """bfloat16 tensor-core attention over the pages.  Tiles: tile_tok0[i] is the first row and
     tile_ntok[i] the number of tokens (consecutive positions of one request, at most rows // G;
     rows: 8, 16 or 128, see attention_mma_tile_rows) of tile i.  plan: attention_plan(...) of these tiles and this
     window; without one it is made here for max_splits CTAs per tile on average, none with fewer
     than min_tiles key tiles.  Only the rows of the listed tiles are written (into `out`
-    [T, Hq*hd] when given)."""
+    [T, Hq*hd] when given).  plan_is_old: the caller's word that the plan and the block table were
+    made before the kernel launched just before this call (the one that writes this step's q and
+    keys); narrow tiles then fetch their older key tiles while that kernel still runs."""
     _need(q, "q", torch.bfloat16)
     T, Hq, hd = q.shape
     _need(k_pages, "k_pages", torch.bfloat16)
@@ -656,6 +658,7 @@ def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
         _need(sinks, "sinks", torch.float32, (Hq,))
     n_tiles = tile_tok0.numel()
     if plan is None:
+        plan_is_old = False
         plan = attention_plan(positions, req_of_token, tile_tok0, tile_ntok, window, n_tiles * max(1, max_splits), min_tiles)
     work, tile_plan = plan
     _need(work, "work", torch.int32)
@@ -674,7 +677,7 @@ def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
     _call("q6k_attention_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ll(num_pages), _ptr(block_table),
           _i(block_table.shape[1]), _i(page_size), _ptr(work), _ptr(tile_plan), _i(n_work), _i(n_tiles), _i(rows),
           _i(window or 0), _ptr(sinks), _f(scale if scale is not None else 1.0 / math.sqrt(hd)), _ptr(out), _ptr(part_o), _ptr(part_ml),
-          _i(Hq), _i(Hkv), _i(hd), _stream())
+          _i(Hq), _i(Hkv), _i(hd), _i(1 if plan_is_old else 0), _stream())
     return out
 
 
@@ -732,10 +735,12 @@ _pair_scratch = {}
 
 
 def gemm_tc_pairs(a: torch.Tensor, w: torch.Tensor, pair_expert: torch.Tensor, pair_div: int, w2: Optional[torch.Tensor] = None,
-                  order: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  order: Optional[torch.Tensor] = None, pairs_are_old: bool = False) -> torch.Tensor:
     """Expert products of a decode step without a permutation: pair y (= token * slots + slot)
     multiplies row y // pair_div of `a` with expert pair_expert[y]; output row y.  With w2 the
-    SwiGLU epilogue (bfloat16 output), else FP32."""
+    SwiGLU epilogue (bfloat16 output), else FP32.  pairs_are_old: the caller's word that
+    pair_expert and order were not made by the kernel launched just before this one; the kernel
+    then fetches its first weights while that kernel still runs."""
     if not tc_supported(a, w) or w.dim() != 3:
         raise KernelError("gemm_tc_pairs: operands must be bfloat16, K a multiple of 8, weights [experts, N, K]")
     _need(pair_expert, "pair_expert", torch.int32)
@@ -763,7 +768,7 @@ def gemm_tc_pairs(a: torch.Tensor, w: torch.Tensor, pair_expert: torch.Tensor, p
     _call("q6k_gemm_tc_pairs", _ptr(a), _ll(a.stride(0)), _i(a.shape[0]), _ptr(w), _ptr(w2), _i(G), _i(N), _i(K), _ptr(out),
           _i(out.stride(0)), _i(EPI_SWIGLU if w2 is not None else EPI_STORE), _ptr(pair_expert), _ptr(order), _i(pairs), _i(pair_div),
           _ptr(partial), _ll(partial.numel() if partial is not None else 0), _ptr(tickets),
-          _i(tickets.numel() if tickets is not None else 0), _stream())
+          _i(tickets.numel() if tickets is not None else 0), _i(1 if pairs_are_old else 0), _stream())
     return out
 
 

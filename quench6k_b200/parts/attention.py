@@ -66,6 +66,9 @@ class Attention(Mixer):
     def forward(self, xn, ctx, cache, state, out):
         rt = self.rt
         write = cache.write
+        # which attention kernels this step takes, and the plan of the key splits, before anything of the layer is
+        # launched: the kernel that splits the keys reads its plan while the kernel before it still runs
+        how = self._choose(cache, ctx)
         rotary = self.pos.rotary_table()
         fused_pos = rotary is not None or self.pos.is_identity
         # FP32 [T, (Hq + 2 Hkv) hd] or [T, Hq hd]; for few rows possibly as split-K partials, which qk_prep sums
@@ -83,17 +86,20 @@ class Attention(Mixer):
                             ctx.req_of_token, table if write else None, cache.page_size, cache.k if write else None,
                             cache.v if write else None, rt.dtype)
         ops.current_tag = "attention.keys"
-        a = self._attend(q, cache, table, ctx)
+        a = self._attend(q, cache, table, ctx, how)
         # the block adds it into the stream inside its next norm (which also sums split-K partials)
         ops.current_tag = "attention.o"
         return linear.matmul(a, self.w_o, rt, partials_ok=True)
 
-    def _attend(self, q, cache, table, ctx):
-        """The tensor-core kernels for bfloat16 where they cover the head and group size, else the generic one."""
+    tc_min_fill = 0.5             # the tcgen05 prompt kernel runs when its CTAs (two tiles each) cover at least this share of the SMs
+
+    def _choose(self, cache, ctx):
+        """("generic",) | ("split", plan args) | ("tc", tile pairs, plan args of the short requests or None): the tensor-core
+        kernels for bfloat16 where they cover the head and group size, else the generic one.  The plans are made here."""
         rt, G = self.rt, self.Hq // self.Hkv
         rows = 0 if rt.is_fp32 or not rt.tensor_cores else ops.attention_mma_tile_rows(self.hd, G, ctx.max_q_len)
         if not rows:
-            return ops.attention_generic(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, self.window, self.sinks, self.scale)
+            return ("generic",)
         if rows > 16 and ops.attention_tc_supported(self.hd, G, cache.page_size):
             tile = ops.attention_tc_tile_tokens(G)
             # beside prompt portions, requests with a few tokens (decoded tokens, the stub of a prompt) go to the kernel
@@ -102,31 +108,42 @@ class Attention(Mixer):
             tok0, ntok, n_pairs = ctx.query_tile_pairs(tile, zigzag=False, more_than=cut)
             if n_pairs * self.Hkv >= self.tc_min_fill * self._sm_count():
                 # prompt portions with enough tiles (two to a CTA) to fill that share of the SMs: both products on tcgen05, no key splits
-                out = ops.attention_tc(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, tok0, ntok, self.window,
-                                       self.sinks, scale=self.scale)
                 count, _, _, most, _ = ctx.short_requests(cut)
-                if count:
-                    self._split_keys(q, cache, table, ctx, ops.attention_mma_tile_rows(self.hd, G, most), at_most=cut, out=out)
-                return out
-        return self._split_keys(q, cache, table, ctx, rows)
+                short = self._plan(ctx, ops.attention_mma_tile_rows(self.hd, G, most), cut) if count else None
+                return ("tc", (tok0, ntok), short)
+        return ("split", self._plan(ctx, rows, None))
 
-    tc_min_fill = 0.5             # the tcgen05 prompt kernel runs when its CTAs (two tiles each) cover at least this share of the SMs
-
-    def _split_keys(self, q, cache, table, ctx, rows, at_most=None, out=None):
-        """The mma.sync kernel over all requests of the step, or over those with at most `at_most` tokens."""
-        G = self.Hq // self.Hkv
-        tokens = rows // G
+    def _plan(self, ctx, rows, at_most):
+        """The tiles and the plan of the key splits for the mma.sync kernel over all requests of the step, or over those
+        with at most `at_most` tokens.  The keys are split over one wave of resident CTAs, and no further (a second,
+        partly filled wave would cost as much as a full one); the plan is made on the device, once per step for all
+        layers with this window."""
+        tokens = rows // (self.Hq // self.Hkv)
         tok0, ntok, n_tiles = ctx.query_tiles(tokens, at_most)
-        # the keys are split over one wave of resident CTAs, and no further (a second, partly filled wave would cost as
-        # much as a full one); the plan is made on the device, once per step for all layers with this window
         key = ("attention_plan", tokens, at_most, self.window, self.Hkv)
         if key not in ctx.made:                     # the first layer of this pass with these tiles and this window
             ctx.plans[key] = ops.attention_plan(ctx.positions, ctx.req_of_token, tok0, ntok, self.window,
                                                 ops.attention_mma_resident_ctas(self.hd, rows) // self.Hkv, min_per=2,
                                                 into=ctx.plans.get(key))
             ctx.made.add(key)
+        return rows, tok0, ntok, ctx.plans[key]
+
+    def _attend(self, q, cache, table, ctx, how):
+        if how[0] == "generic":
+            return ops.attention_generic(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, self.window, self.sinks, self.scale)
+        if how[0] == "tc":
+            (tok0, ntok), short = how[1], how[2]
+            out = ops.attention_tc(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, tok0, ntok, self.window,
+                                   self.sinks, scale=self.scale)
+            return out if short is None else self._split_keys(q, cache, table, ctx, short, out)
+        return self._split_keys(q, cache, table, ctx, how[1])
+
+    def _split_keys(self, q, cache, table, ctx, planned, out=None):
+        rows, tok0, ntok, plan = planned
+        # the plan was made before this layer's first launch, and the kernel before this one is the one that wrote q and
+        # the new keys (or, beside prompt portions, the tcgen05 attention, which itself waited for that one)
         return ops.attention_mma(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, tok0, ntok, rows, self.window,
-                                 self.sinks, scale=self.scale, out=out, plan=ctx.plans[key])
+                                 self.sinks, scale=self.scale, out=out, plan=plan, plan_is_old=True)
 
     def _sm_count(self) -> int:
         if "_sms" not in self.__dict__:

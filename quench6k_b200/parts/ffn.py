@@ -106,7 +106,7 @@ class RoutedExperts(FeedForward):
             else:
                 act = ops.gemm_tc_pairs(xn, self.w_gate, sel_e, self.k, w2=self.w_up, order=order)  # [pairs, I]
                 ops.current_tag = "experts.down"
-                y = ops.gemm_tc_pairs(act, self.w_down, sel_e, 1, order=order)                       # FP32 [pairs, D]
+                y = ops.gemm_tc_pairs(act, self.w_down, sel_e, 1, order=order, pairs_are_old=True)   # FP32 [pairs, D]
             if defer:
                 return WeightedRows(y, sel_w)
             ops.current_tag = "experts.combine"

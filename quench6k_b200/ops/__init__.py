@@ -7,6 +7,7 @@ machine without the built extension or without a GPU these functions raise.
 from __future__ import annotations
 
 import ctypes
+import functools
 import math
 import os
 from typing import Optional, Tuple
@@ -183,6 +184,7 @@ def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype
     return out
 
 
+@functools.lru_cache(maxsize=None)          # a question about sizes: asked of the library once
 def rmsnorm_fuses_weighted(D: int) -> bool:
     lib = library()
     lib.q6k_rmsnorm_fuses_pairs.restype = ctypes.c_int
@@ -388,6 +390,7 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None
 
 
 # --------------------------------------------------------------------------- matrix-vector products (a step of very few tokens)
+@functools.lru_cache(maxsize=None)          # a question about sizes: asked of the library once
 def gemv_preferred(tokens: int, N: int, K: int) -> bool:
     """Whether a bfloat16 product of `tokens` rows with an [N, K] matrix should go to the matrix-vector kernel."""
     lib = library()
@@ -431,6 +434,7 @@ def gemv(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = None, ou
     return out
 
 
+@functools.lru_cache(maxsize=None)          # a question about sizes: asked of the library once
 def gemm_skinny_preferred(tokens: int, N: int, K: int) -> bool:
     """Whether a bfloat16 product of `tokens` rows (3 to 16) with an [N, K] matrix should go to the mma.sync kernel for few tokens."""
     lib = library()
@@ -530,12 +534,14 @@ def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
     return out
 
 
+@functools.lru_cache(maxsize=None)          # a question about sizes: asked of the library once
 def attention_tc_supported(hd: int, G: int, page_size: int) -> bool:
     lib = library()
     lib.q6k_attention_tc_supported.restype = ctypes.c_int
     return bool(lib.q6k_attention_tc_supported(_i(hd), _i(G), _i(page_size)))
 
 
+@functools.lru_cache(maxsize=None)          # a question about sizes: asked of the library once
 def attention_tc_tile_tokens(G: int) -> int:
     """Tokens one tile of attention_tc may hold (128 // G: 128 query rows)."""
     lib = library()
@@ -578,12 +584,14 @@ def attention_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, 
     return out
 
 
+@functools.lru_cache(maxsize=None)          # a question about sizes: asked of the library once
 def attention_mma_supported(hd: int, G: int, wide: bool) -> bool:
     lib = library()
     lib.q6k_attention_mma_supported.restype = ctypes.c_int
     return bool(lib.q6k_attention_mma_supported(_i(hd), _i(G), _i(1 if wide else 0)))
 
 
+@functools.lru_cache(maxsize=None)          # a question about sizes: asked of the library once
 def attention_mma_tile_rows(hd: int, G: int, max_tokens: int) -> int:
     """Query rows of the tiles attention_mma should be given when no request brings more than
     max_tokens tokens to the step: 8, 16 or 128 (a tile holds rows // G tokens); 0 if the kernel
@@ -700,6 +708,7 @@ def route(logits: torch.Tensor, k: int, scoring: str, renorm: bool):
 _tickets = {}
 
 
+@functools.lru_cache(maxsize=None)          # a question about sizes: asked of the library once
 def router_small_supported(T: int, E: int, D: int, k: int) -> bool:
     """Whether the one-launch decode router (router_small, and with it the per-pair expert products) takes this step."""
     lib = library()

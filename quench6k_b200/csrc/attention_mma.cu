@@ -31,6 +31,7 @@
 namespace {
 
 constexpr int KT = 64;                       // keys per tile
+constexpr int PREP_TOKENS = 8;               // tokens of a tile whose q and keys the kernel can make itself
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct AttnParams {
@@ -51,6 +52,18 @@ struct AttnParams {
                                              // kernel launched before this one: key tiles may be fetched before the wait for it
     int pool_rows;                           // rows of the [Hkv * pages * page_size, HD] view of a pool (TMA path)
     int num_pages;                           // pages of a pool (per KV head)
+    // Narrow tiles may prepare q and the new keys themselves (qkv != null; q is then unused): what the kernel in
+    // qk_prep.cu does, folded in.  qkv: FP32 [qkv_splits, T, qkv_ld], q heads | k heads | v heads in a row; the slices
+    // (split-K partial products, qkv_split_stride floats apart) are summed in order.
+    const float* qkv;
+    long long qkv_split_stride;
+    int qkv_splits;
+    const float* q_norm;                     // [HD] or null
+    const float* k_norm;
+    const float* inv_freq;                   // [rd / 2] or null: pairs by halves, rd a multiple of 64
+    float eps;
+    int qkv_ld, rd;
+    int write_kv;                            // the new keys and values are made here and written to the pages
 };
 
 __device__ int g_attn_status = 0;
@@ -252,10 +265,13 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + 32, WIDE ? 1 : 2) attent
         const int ps = p.page_size;
         if (TMA && lane != 0) return;         // one elected lane issues the TMA loads; the copies of the other path take all 32
         bool waited = !EARLY;
+        // a launch that makes the new keys itself finds only keys of earlier steps in the pages: nothing there is the
+        // work of the kernel before this one (the rows of this step's positions are replaced in shared memory)
+        const bool makes_kv = !WIDE && p.qkv != nullptr && p.write_kv;
         for (int i = 0; i < n_mine; ++i) {
             const int st = i % STAGES;
             // the first tiles of the ring need no free stage; of those, the ones that end before this step's first key need no wait
-            if (!waited && (i >= STAGES || (t_begin + i + 1) * KT > pos_first)) {
+            if (!waited && (i >= STAGES || (!makes_kv && (t_begin + i + 1) * KT > pos_first))) {
                 pdl_wait();
                 waited = true;
             }
@@ -319,11 +335,25 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + 32, WIDE ? 1 : 2) attent
     }
 
     // ------------------------------------------------------------------ the consumer warps
-    if (EARLY) pdl_wait();                    // q is the work of the kernel before this one
     // A thread of the fragment layout: quad = lane / 4 names a key (first product's rows) or a head
     // dimension (second product's rows), pair = lane % 4 names two neighbouring query rows.
     const int quad = lane >> 2, pair = lane & 3;
     const int row0 = WIDE ? warp * NQ : 0;                                   // first row of the CTA's tile this warp works on
+    const bool prepares = !WIDE && p.qkv != nullptr;                         // q and the new keys are made here
+    __nv_bfloat16* stash = reinterpret_cast<__nv_bfloat16*>(smem + 2 * STAGES * TILE_BYTES);      // [PREP_TOKENS][K, V][HD]
+    float2* turn = reinterpret_cast<float2*>(stash + PREP_TOKENS * 2 * HD);                       // [PREP_TOKENS][HD / 2]: cosine, sine
+    if (prepares && p.inv_freq) {
+        // the rotations of the tile's tokens depend on their positions only: made while the kernel before this one still runs
+        const int half = p.rd / 2;
+        for (int idx = tid; idx < ntok * half; idx += CW * 32) {
+            const int tt = idx / half, i = idx % half;
+            float sn, cs;
+            sincosf((float)(pos_first + tt) * p.inv_freq[i], &sn, &cs);
+            turn[tt * (HD / 2) + i] = make_float2(cs, sn);
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");
+    }
+    if (EARLY) pdl_wait();                    // q (or the q/k/v product) is the work of the kernel before this one
     // the rows this thread holds in the accumulator fragments: block nb, rows nb*8 + 2*pair + {0, 1}
     int see_to[NB][2], see_from[NB][2];
 #pragma unroll
@@ -334,18 +364,142 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + 32, WIDE ? 1 : 2) attent
             see_to[nb][c] = tt < ntok ? pos : -1;                            // a row past the tile's tokens sees nothing
             see_from[nb][c] = p.window > 0 ? pos - p.window + 1 : 0;
         }
-    // Q^T as the first product's B operand, straight from global memory: this thread's row is
-    // nb*8 + quad, its head dimensions 16 ks + 2 pair + {0, 1} and + 8
+    // Q^T as the first product's B operand: this thread's row is nb*8 + quad, its head dimensions
+    // 16 ks + 2 pair + {0, 1} and + 8
     uint32_t qf[DB][NB][2];
+    bool has_new = false;                      // some of the tile's new keys lie in this CTA's key tiles (the same for all its warps)
+    if (prepares) {
+        // ---- q, and the keys and values of the tile's tokens, from the FP32 product [q | k | v]: per-head RMSNorm,
+        // rotation by position * inv_freq (pairs d, d + rd/2), rounding to bfloat16: the arithmetic of qk_prep.cu.
+        // Everything a stretch needs is asked of memory at once: one round trip, then arithmetic.
+        const int t_end = t_begin + n_mine;
+        has_new = p.write_kv && n_mine > 0 && pos_last / KT >= t_begin && pos_first / KT < t_end;
+        if (has_new) {
+            // a warp per token: lane l holds head dimensions l + 32 i, so both members of a rotating pair sit in one lane
+            constexpr int EPL = HD / 32;
+            for (int tt = warp; tt < ntok; tt += CW) {
+                const int pos = pos_first + tt;
+                if (pos / KT < t_begin || pos / KT >= t_end) continue;       // another part's key tile: that CTA makes it
+                const int page = bt[pos / p.page_size];
+                const float* ksrc = p.qkv + (size_t)(tok0 + tt) * p.qkv_ld + (size_t)(p.Hq + kh) * HD;
+                const float* vsrc = ksrc + (size_t)p.Hkv * HD;
+                float x[EPL], v[EPL], w[EPL];
 #pragma unroll
-    for (int nb = 0; nb < NB; ++nb) {
-        const int r = row0 + nb * 8 + quad, tt = r / G, hg = r % G;
-        const bool live = tt < ntok;
-        const uint32_t* src = reinterpret_cast<const uint32_t*>(p.q + ((size_t)(tok0 + (live ? tt : 0)) * p.Hq + kh * G + hg) * HD) + pair;
+                for (int i = 0; i < EPL; ++i) x[i] = ksrc[lane + 32 * i], v[i] = vsrc[lane + 32 * i], w[i] = p.k_norm ? p.k_norm[lane + 32 * i] : 1.0f;
+                for (int sp = 1; sp < p.qkv_splits; ++sp)
 #pragma unroll
-        for (int ks = 0; ks < DB; ++ks) {
-            qf[ks][nb][0] = live ? src[ks * 8] : 0u;
-            qf[ks][nb][1] = live ? src[ks * 8 + 4] : 0u;
+                    for (int i = 0; i < EPL; ++i) x[i] += ksrc[sp * p.qkv_split_stride + lane + 32 * i], v[i] += vsrc[sp * p.qkv_split_stride + lane + 32 * i];
+                if (p.k_norm) {
+                    float ss = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < EPL; ++i) ss = fmaf(x[i], x[i], ss);
+                    const float inv = rsqrtf(warp_sum(ss) / (float)HD + p.eps);
+#pragma unroll
+                    for (int i = 0; i < EPL; ++i) x[i] = x[i] * inv * w[i];
+                }
+                if (p.inv_freq) {
+                    const int per = p.rd / 64;                               // elements of a lane in each half of the rotated part
+#pragma unroll
+                    for (int i = 0; i < EPL / 2; ++i)
+                        if (i < per) {
+                            const float2 cs = turn[tt * (HD / 2) + lane + 32 * i];
+                            float lo = x[i], hi = 0.0f;
+#pragma unroll
+                            for (int j = 1; j <= EPL / 2; ++j)               // x[i + per] without indexing registers by a variable
+                                if (j == per) hi = x[i + j];
+                            const float a = lo * cs.x - hi * cs.y, b = hi * cs.x + lo * cs.y;
+                            x[i] = a;
+#pragma unroll
+                            for (int j = 1; j <= EPL / 2; ++j)
+                                if (j == per) x[i + j] = b;
+                        }
+                }
+                __nv_bfloat16* sk = stash + (size_t)tt * 2 * HD;
+                __nv_bfloat16* kdst = const_cast<__nv_bfloat16*>(p.k_pages) + (((size_t)kh * p.num_pages + max(page, 0)) * p.page_size + pos % p.page_size) * HD;
+                __nv_bfloat16* vdst = const_cast<__nv_bfloat16*>(p.v_pages) + (kdst - p.k_pages);
+#pragma unroll
+                for (int i = 0; i < EPL; ++i) {
+                    // a position without a page has no key: zeros, as the pages' loader gives them
+                    const __nv_bfloat16 kb16 = __float2bfloat16(page >= 0 ? x[i] : 0.0f), vb16 = __float2bfloat16(page >= 0 ? v[i] : 0.0f);
+                    sk[lane + 32 * i] = kb16, sk[HD + lane + 32 * i] = vb16;
+                    if (page >= 0) kdst[lane + 32 * i] = kb16, vdst[lane + 32 * i] = vb16;
+                }
+            }
+        }
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            const int r = nb * 8 + quad, tt = r / G, hg = r % G;
+            const bool live = tt < ntok;
+            const float* src = p.qkv + (size_t)(tok0 + (live ? tt : 0)) * p.qkv_ld + (size_t)(kh * G + hg) * HD + 2 * pair;
+            float x[DB][4], w[DB][4];          // slot s of block ks: head dimension 16 ks + 2 pair + (s & 1) + 8 (s >> 1)
+#pragma unroll
+            for (int ks = 0; ks < DB; ++ks) {
+                const float2 a = *reinterpret_cast<const float2*>(src + ks * 16), b = *reinterpret_cast<const float2*>(src + ks * 16 + 8);
+                x[ks][0] = a.x, x[ks][1] = a.y, x[ks][2] = b.x, x[ks][3] = b.y;
+                if (p.q_norm) {
+                    const float2 c = *reinterpret_cast<const float2*>(p.q_norm + ks * 16 + 2 * pair), d = *reinterpret_cast<const float2*>(p.q_norm + ks * 16 + 8 + 2 * pair);
+                    w[ks][0] = c.x, w[ks][1] = c.y, w[ks][2] = d.x, w[ks][3] = d.y;
+                }
+            }
+            for (int sp = 1; sp < p.qkv_splits; ++sp)
+#pragma unroll
+                for (int ks = 0; ks < DB; ++ks) {
+                    const float2 a = *reinterpret_cast<const float2*>(src + sp * p.qkv_split_stride + ks * 16), b = *reinterpret_cast<const float2*>(src + sp * p.qkv_split_stride + ks * 16 + 8);
+                    x[ks][0] += a.x, x[ks][1] += a.y, x[ks][2] += b.x, x[ks][3] += b.y;
+                }
+            if (p.q_norm) {
+                float ss = 0.0f;
+#pragma unroll
+                for (int ks = 0; ks < DB; ++ks)
+#pragma unroll
+                    for (int s = 0; s < 4; ++s) ss = fmaf(x[ks][s], x[ks][s], ss);
+                ss += __shfl_xor_sync(0xffffffffu, ss, 1);                   // the four lanes of a quad hold the row's HD values between them
+                ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+                const float inv = rsqrtf(ss / (float)HD + p.eps);
+#pragma unroll
+                for (int ks = 0; ks < DB; ++ks)
+#pragma unroll
+                    for (int s = 0; s < 4; ++s) x[ks][s] = x[ks][s] * inv * w[ks][s];
+            }
+            if (p.inv_freq) {
+                const int per = p.rd / 32;                                   // blocks of 16 dimensions in each half of the rotated part
+                const float2* trow = turn + (live ? tt : 0) * (HD / 2) + 2 * pair;
+#pragma unroll
+                for (int ks = 0; ks < DB / 2; ++ks)
+                    if (ks < per) {
+#pragma unroll
+                        for (int s = 0; s < 4; ++s) {
+                            const float2 cs = trow[ks * 16 + (s & 1) + 8 * (s >> 1)];
+                            float lo = x[ks][s], hi = 0.0f;
+#pragma unroll
+                            for (int j = 1; j <= DB / 2; ++j)
+                                if (j == per) hi = x[ks + j][s];
+                            const float a = lo * cs.x - hi * cs.y, b = hi * cs.x + lo * cs.y;
+                            x[ks][s] = a;
+#pragma unroll
+                            for (int j = 1; j <= DB / 2; ++j)
+                                if (j == per) x[ks + j][s] = b;
+                        }
+                    }
+            }
+#pragma unroll
+            for (int ks = 0; ks < DB; ++ks) {
+                qf[ks][nb][0] = live ? pack_bf16(x[ks][0], x[ks][1]) : 0u;
+                qf[ks][nb][1] = live ? pack_bf16(x[ks][2], x[ks][3]) : 0u;
+            }
+        }
+        if (has_new) asm volatile("bar.sync 1, %0;" ::"n"(CW * 32) : "memory");          // the stash is whole before any warp copies from it
+    } else {
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) {
+            const int r = row0 + nb * 8 + quad, tt = r / G, hg = r % G;
+            const bool live = tt < ntok;
+            const uint32_t* src = reinterpret_cast<const uint32_t*>(p.q + ((size_t)(tok0 + (live ? tt : 0)) * p.Hq + kh * G + hg) * HD) + pair;
+#pragma unroll
+            for (int ks = 0; ks < DB; ++ks) {
+                qf[ks][nb][0] = live ? src[ks * 8] : 0u;
+                qf[ks][nb][1] = live ? src[ks * 8 + 4] : 0u;
+            }
         }
     }
     float top[NB][2], sum[NB][2];              // running maximum (base-2 logits) and sum of the probabilities of this thread's keys
@@ -371,6 +525,19 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + 32, WIDE ? 1 : 2) attent
             continue;
         }
         const uint32_t kb = k_s + st * TILE_BYTES, vb = v_s + st * TILE_BYTES;
+        if (!WIDE && has_new && kt >= pos_first / KT) {
+            // the rows of this step's positions: from the stash, in place of what the pages held there
+            for (int tt = 0; tt < ntok; ++tt) {
+                const int pos = pos_first + tt;
+                if (pos / KT != kt) continue;
+                for (int idx = lane; idx < 2 * CH; idx += 32) {
+                    const int which = idx / CH, c = idx % CH;
+                    const uint4 val = *reinterpret_cast<const uint4*>(stash + ((size_t)tt * 2 + which) * HD + c * 8);
+                    *reinterpret_cast<uint4*>(smem + (which ? v_s - k_s : 0) + st * TILE_BYTES + swk(pos - kt * KT, c)) = val;
+                }
+            }
+            __syncwarp();
+        }
         if (TMA && kt == end_tile - 1 && (pos_last + 1) % KT != 0) {
             // the last page came in whole: the keys past the last position hold whatever the page held
             // before.  Their scores are masked, but 0 * V must not meet a stale NaN: clear those V rows.
@@ -697,8 +864,11 @@ template <int HD, int NQ, bool WIDE, bool TMA>
 constexpr size_t attention_smem() {
     constexpr int STAGES = HD == 128 ? 3 : 4;
     constexpr size_t ring = 2 * STAGES * KT * HD * 2;
-    constexpr size_t meet = WIDE ? 0 : 4 * NQ * (HD + 4 + 2) * sizeof(float);       // the narrow tiles' slabs and statistics
-    return (ring > meet ? ring : meet) + 1024;
+    constexpr size_t meet = WIDE ? 0 : 4 * NQ * (HD + 4 + 2) * sizeof(float);       // the narrow tiles' slabs and statistics: in the ring, idle by then
+    static_assert(ring >= meet, "the slabs lie in the ring");
+    // behind the ring of a narrow tile: the new keys and values of its tokens (bfloat16) and their rotations (cosine, sine)
+    constexpr size_t stash = WIDE ? 0 : (size_t)PREP_TOKENS * (2 * HD * 2 + HD / 2 * 8);
+    return ring + stash + 1024;
 }
 
 template <int HD, int NQ, bool WIDE, bool TMA>
@@ -791,10 +961,22 @@ Q6K_API int q6k_attention_plan(const int* positions, const int* req_of_token, co
 // early != 0 (tiles of 8 or 16 rows only): the caller's word that the plan and the block table were made before the kernel
 // launched before this one started, and that this kernel writes this step's keys; key tiles older than a tile's first
 // position are then fetched while it still runs.
+// qkv != null (tiles of 8 or 16 rows only; q is then unused): FP32 [qkv_splits, T, qkv_ld] rows of q heads | k heads | v heads
+// (slices qkv_split_stride floats apart, summed in order: split-K partial products), which the
+// kernel itself normalises per head (q_norm, k_norm: FP32 [hd] or null; eps), rotates (inv_freq: FP32 [rotary_dim / 2] or
+// null; pairs d, d + rotary_dim / 2; rotary_dim a multiple of 64) and rounds; write_kv != 0: the tiles' keys and values
+// are made the same way and written to the pages (which nothing else may read or write meanwhile).  With early != 0 the
+// kernel launched before this one must then have been launched early itself or be the only writer of qkv.
+Q6K_API int q6k_attention_mma_prepares(int hd, int G, int rows, int rotary_dim, int neighbours) {
+    return (hd == 64 || hd == 128) && (rows == 8 || rows == 16) && G >= 1 && rows / G <= PREP_TOKENS &&
+           (rotary_dim == 0 || (!neighbours && rotary_dim % 64 == 0 && rotary_dim <= hd));
+}
+
 Q6K_API int q6k_attention_mma(const void* q, const void* k_pages, const void* v_pages, long long num_pages, const int* block_table,
                               int max_blocks, int page_size, const int* work, const int* tile_plan, int n_work, int n_tiles, int rows,
                               int window, const float* sinks, float scale, void* out, float* part_o, float* part_ml, int Hq, int Hkv,
-                              int hd, int early, cudaStream_t st) {
+                              int hd, int early, const float* qkv, int qkv_ld, int qkv_splits, long long qkv_split_stride, const float* q_norm, const float* k_norm, float eps,
+                              const float* inv_freq, int rotary_dim, int write_kv, cudaStream_t st) {
     if (n_tiles == 0) return 0;
     Q6K_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention_mma: bad head counts Hq=%d Hkv=%d", Hq, Hkv);
     const int G = Hq / Hkv;
@@ -812,6 +994,17 @@ Q6K_API int q6k_attention_mma(const void* q, const void* k_pages, const void* v_
     p.max_blocks = max_blocks, p.page_size = page_size, p.window = window, p.Hq = Hq, p.Hkv = Hkv, p.G = G;
     p.scale_log2 = scale * LOG2E;
     p.early = early;
+    if (qkv) {
+        Q6K_REQUIRE(q6k_attention_mma_prepares(hd, G, rows, inv_freq ? rotary_dim : 0, 0), "attention_mma: tiles of %d rows of heads of %d (groups of %d) do not prepare q and k with %d rotating dimensions",
+                    rows, hd, G, rotary_dim);
+        Q6K_REQUIRE(qkv_ld >= (write_kv ? Hq + 2 * Hkv : Hq) * hd && qkv_ld % 2 == 0 && ((uintptr_t)qkv & 7) == 0, "attention_mma: qkv rows of %d values for %d + 2 x %d heads of %d", qkv_ld, Hq, Hkv, hd);
+        Q6K_REQUIRE(qkv_splits >= 1 && qkv_split_stride % 2 == 0, "attention_mma: %d slices of qkv, %lld values apart", qkv_splits, qkv_split_stride);
+        p.qkv_splits = qkv_splits, p.qkv_split_stride = qkv_split_stride;
+        p.qkv = qkv, p.qkv_ld = qkv_ld, p.q_norm = q_norm, p.k_norm = k_norm, p.eps = eps, p.write_kv = write_kv;
+        p.inv_freq = inv_freq, p.rd = inv_freq ? rotary_dim : 0;
+    } else {
+        Q6K_REQUIRE(q != nullptr, "attention_mma: neither q nor qkv%s", "");
+    }
     // pages of 8, 16, 32, 64 keys (or whole multiples of 64) are boxes TMA can place on the swizzle pattern
     p.num_pages = (int)num_pages;
     const long long pool_rows = num_pages * Hkv * page_size;

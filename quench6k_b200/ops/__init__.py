@@ -317,8 +317,8 @@ _workspaces = {}
 _retired = []                             # outgrown scratch stays allocated: recorded CUDA graphs still point at it
 
 
-def _workspace(nbytes: int, device) -> torch.Tensor:
-    key = str(device)                     # one scratch buffer per device: the engine runs on one stream
+def _workspace(nbytes: int, device, which: str = "") -> torch.Tensor:
+    key = str(device) + which             # one scratch buffer per device and kind: the engine runs on one stream
     ws = _workspaces.get(key)
     if ws is None or ws.numel() * 4 < nbytes:
         if ws is not None:
@@ -642,10 +642,20 @@ def attention_plan(positions: torch.Tensor, req_of_token: torch.Tensor, tile_tok
     return work, tile_plan
 
 
-def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+@functools.lru_cache(maxsize=None)          # a question about sizes: asked of the library once
+def attention_mma_prepares(hd: int, G: int, rows: int, rotary_dim: int, neighbours: bool) -> bool:
+    """Whether attention_mma with tiles of `rows` rows can make q and the new keys itself (its `prepare` argument)
+    for heads of hd in groups of G with rotary_dim rotating dimensions (0: none)."""
+    lib = library()
+    lib.q6k_attention_mma_prepares.restype = ctypes.c_int
+    return bool(lib.q6k_attention_mma_prepares(_i(hd), _i(G), _i(rows), _i(rotary_dim), _i(1 if neighbours else 0)))
+
+
+def attention_mma(q: Optional[torch.Tensor], k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                   req_of_token: torch.Tensor, positions: torch.Tensor, tile_tok0: torch.Tensor, tile_ntok: torch.Tensor,
                   rows: int, window: Optional[int], sinks: Optional[torch.Tensor], max_splits: int = 1, min_tiles: int = 2,
-                  scale: Optional[float] = None, out: Optional[torch.Tensor] = None, plan=None, plan_is_old: bool = False) -> torch.Tensor:
+                  scale: Optional[float] = None, out: Optional[torch.Tensor] = None, plan=None, plan_is_old: bool = False,
+                  prepare=None) -> torch.Tensor:
     """bfloat16 tensor-core attention over the pages.  Tiles: tile_tok0[i] is the first row and
     tile_ntok[i] the number of tokens (consecutive positions of one request, at most rows // G;
     rows: 8, 16 or 128, see attention_mma_tile_rows) of tile i.  plan: attention_plan(...) of these tiles and this
@@ -653,14 +663,44 @@ def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
     than min_tiles key tiles.  Only the rows of the listed tiles are written (into `out`
     [T, Hq*hd] when given).  plan_is_old: the caller's word that the plan and the block table were
     made before the kernel launched just before this call (the one that writes this step's q and
-    keys); narrow tiles then fetch their older key tiles while that kernel still runs."""
-    _need(q, "q", torch.bfloat16)
-    T, Hq, hd = q.shape
+    keys); narrow tiles then fetch their older key tiles while that kernel still runs.
+
+    prepare (tiles of 8 or 16 rows, see attention_mma_prepares; q is then None): a dict with what
+    qk_prep takes: qkv float32 [T, >= (Hq + 2 Hkv) hd], heads (Hq), q_norm, k_norm, eps, rotary,
+    write (bool); qkv may be [slices, T, width] split-K partial products.  The kernel then normalises, rotates and rounds q itself, and with write=True
+    makes the tiles' keys and values and puts them into the pages (every token of the step must
+    then lie in a tile).  With plan_is_old the plan must be older than the kernel that made qkv
+    AND the one before it."""
     _need(k_pages, "k_pages", torch.bfloat16)
     _need(v_pages, "v_pages", torch.bfloat16, k_pages.shape)
-    Hkv, num_pages, page_size, hd2 = k_pages.shape
-    if hd2 != hd:
-        raise KernelError(f"attention: q has head_dim {hd}, the pages {hd2}")
+    Hkv, num_pages, page_size, hd = k_pages.shape
+    qkv = q_norm = k_norm = inv_freq = None
+    eps, rotary_dim, write, ld, splits, split_stride = 0.0, 0, False, 0, 1, 0
+    if prepare is not None:
+        qkv, Hq, write = prepare["qkv"], int(prepare["heads"]), bool(prepare.get("write", False))
+        if not qkv.is_cuda or qkv.dtype != torch.float32 or qkv.dim() not in (2, 3) or qkv.stride(-1) != 1:
+            raise KernelError("attention_mma: qkv must be float32 rows [T, width] or [slices, T, width] on the device (rows may have a pitch of their own)")
+        if qkv.dim() == 3:                   # split-K partial products: summed in order by the kernel
+            splits, split_stride = qkv.shape[0], qkv.stride(0)
+        T, ld = qkv.shape[-2], qkv.stride(-2)
+        if qkv.shape[-1] < (Hq + 2 * Hkv if write else Hq) * hd:
+            raise KernelError(f"attention_mma: qkv of shape {tuple(qkv.shape)} for {Hq} + 2 x {Hkv} heads of {hd}")
+        q_norm, k_norm, eps = prepare.get("q_norm"), prepare.get("k_norm"), float(prepare.get("eps", 0.0))
+        for nm, w in (("q_norm", q_norm), ("k_norm", k_norm)):
+            if w is not None:
+                _need(w, nm, torch.float32, (hd,))
+        if prepare.get("rotary") is not None:
+            inv_freq, rotary_dim, neighbours = prepare["rotary"]
+            _need(inv_freq, "inv_freq", torch.float32, (rotary_dim // 2,))
+            if neighbours:
+                raise KernelError("attention_mma: pairs of neighbours are rotated by qk_prep only")
+        dev = qkv.device
+    else:
+        _need(q, "q", torch.bfloat16)
+        T, Hq, hd2 = q.shape
+        if hd2 != hd:
+            raise KernelError(f"attention: q has head_dim {hd2}, the pages {hd}")
+        dev = q.device
     _need(block_table, "block_table", torch.int32)
     if sinks is not None:
         _need(sinks, "sinks", torch.float32, (Hq,))
@@ -673,19 +713,20 @@ def attention_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
     _need(tile_plan, "tile_plan", torch.int32, (n_tiles, 4))
     n_work = work.shape[0]
     if out is None:
-        out = torch.empty((T, Hq * hd), dtype=torch.bfloat16, device=q.device)
+        out = torch.empty((T, Hq * hd), dtype=torch.bfloat16, device=dev)
     else:
         _need(out, "out", torch.bfloat16, (T, Hq * hd))
     part_o = part_ml = None
     if n_work > n_tiles:
         part_rows = n_work * Hkv * rows
-        ws = _workspace(part_rows * (hd + 2) * 4, q.device)
+        ws = _workspace(part_rows * (hd + 2) * 4, dev, "attention")       # a buffer of its own: qkv may be a view of the common one
         part_o = ws[: part_rows * hd]
         part_ml = ws[part_rows * hd: part_rows * (hd + 2)]
     _call("q6k_attention_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ll(num_pages), _ptr(block_table),
           _i(block_table.shape[1]), _i(page_size), _ptr(work), _ptr(tile_plan), _i(n_work), _i(n_tiles), _i(rows),
           _i(window or 0), _ptr(sinks), _f(scale if scale is not None else 1.0 / math.sqrt(hd)), _ptr(out), _ptr(part_o), _ptr(part_ml),
-          _i(Hq), _i(Hkv), _i(hd), _i(1 if plan_is_old else 0), _stream())
+          _i(Hq), _i(Hkv), _i(hd), _i(1 if plan_is_old else 0), _ptr(qkv), _i(ld), _i(splits), _ll(split_stride), _ptr(q_norm), _ptr(k_norm), _f(eps),
+          _ptr(inv_freq), _i(rotary_dim), _i(1 if write else 0), _stream())
     return out
 
 

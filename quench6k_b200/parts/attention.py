@@ -71,10 +71,21 @@ class Attention(Mixer):
         how = self._choose(cache, ctx)
         rotary = self.pos.rotary_table()
         fused_pos = rotary is not None or self.pos.is_identity
-        # FP32 [T, (Hq + 2 Hkv) hd] or [T, Hq hd]; for few rows possibly as split-K partials, which qk_prep sums
+        # a step of a few tokens per request: the kernel that splits the keys normalises and rotates q itself and makes
+        # the new keys and values (one launch less)
+        in_attention = (self.prepare_in_attention and how[0] == "split" and fused_pos and
+                        ops.attention_mma_prepares(self.hd, self.Hq // self.Hkv, how[1][0], rotary[1] if rotary else 0, bool(rotary and rotary[2])))
+        # FP32 [T, (Hq + 2 Hkv) hd] or [T, Hq hd]; for few rows possibly as split-K partials, which the next kernel sums
         ops.current_tag = "attention.qkv"
         qkv = linear.matmul(xn, self.w_qkv if write else self.w_q, rt, partials_ok=fused_pos)
         table = ctx.block_tables[cache.group]
+        if in_attention:
+            ops.current_tag = "attention.keys"
+            a = self._split_keys(None, cache, table, ctx, how[1],
+                                 prepare={"qkv": qkv, "heads": self.Hq, "q_norm": self.q_norm, "k_norm": self.k_norm, "eps": self.eps,
+                                          "rotary": rotary, "write": write})
+            ops.current_tag = "attention.o"
+            return linear.matmul(a, self.w_o, rt, partials_ok=True)
         ops.current_tag = "attention.prepare"
         if not fused_pos:
             qkv = self._unfused_position(qkv, ctx, write)
@@ -91,6 +102,7 @@ class Attention(Mixer):
         ops.current_tag = "attention.o"
         return linear.matmul(a, self.w_o, rt, partials_ok=True)
 
+    prepare_in_attention = True   # the kernel that splits the keys makes q and the new keys itself where it can (else qk_prep does)
     tc_min_fill = 0.5             # the tcgen05 prompt kernel runs when its CTAs (two tiles each) cover at least this share of the SMs
 
     def _choose(self, cache, ctx):
@@ -121,12 +133,13 @@ class Attention(Mixer):
         tokens = rows // (self.Hq // self.Hkv)
         tok0, ntok, n_tiles = ctx.query_tiles(tokens, at_most)
         key = ("attention_plan", tokens, at_most, self.window, self.Hkv)
-        if key not in ctx.made:                     # the first layer of this pass with these tiles and this window
+        fresh = key not in ctx.made
+        if fresh:                                   # the first layer of this pass with these tiles and this window
             ctx.plans[key] = ops.attention_plan(ctx.positions, ctx.req_of_token, tok0, ntok, self.window,
                                                 ops.attention_mma_resident_ctas(self.hd, rows) // self.Hkv, min_per=2,
                                                 into=ctx.plans.get(key))
             ctx.made.add(key)
-        return rows, tok0, ntok, ctx.plans[key]
+        return rows, tok0, ntok, ctx.plans[key], fresh
 
     def _attend(self, q, cache, table, ctx, how):
         if how[0] == "generic":
@@ -138,12 +151,16 @@ class Attention(Mixer):
             return out if short is None else self._split_keys(q, cache, table, ctx, short, out)
         return self._split_keys(q, cache, table, ctx, how[1])
 
-    def _split_keys(self, q, cache, table, ctx, planned, out=None):
-        rows, tok0, ntok, plan = planned
-        # the plan was made before this layer's first launch, and the kernel before this one is the one that wrote q and
-        # the new keys (or, beside prompt portions, the tcgen05 attention, which itself waited for that one)
+    def _split_keys(self, q, cache, table, ctx, planned, out=None, prepare=None):
+        rows, tok0, ntok, plan, fresh = planned
+        # The plan was made before this layer's first launch.  With q from qk_prep, the kernel before this one is that
+        # one (or, beside prompt portions, the tcgen05 attention), which itself waited for everything before it: the plan
+        # is complete when this kernel starts.  When this kernel prepares q itself, the kernel before it is the q/k/v
+        # product, which may itself have started before the one before it ended: then only a plan of an earlier layer
+        # is surely complete.
         return ops.attention_mma(q, cache.k, cache.v, table, ctx.req_of_token, ctx.positions, tok0, ntok, rows, self.window,
-                                 self.sinks, scale=self.scale, out=out, plan=plan, plan_is_old=True)
+                                 self.sinks, scale=self.scale, out=out, plan=plan, plan_is_old=prepare is None or not fresh,
+                                 prepare=prepare)
 
     def _sm_count(self) -> int:
         if "_sms" not in self.__dict__:

@@ -528,6 +528,74 @@ def test_attention_mma(Hq, Hkv, hd, ps, window, sinks, mode):
     assert err <= 1.5e-2, ("plan", err)
 
 
+@pytest.mark.parametrize("Hq,Hkv,hd,ps,window,sinks,qk_norm,rd", [(32, 4, 128, 16, None, False, True, 128), (8, 2, 64, 8, None, True, True, 64),
+                                                                   (6, 2, 128, 16, 100, True, False, 64), (16, 1, 64, 32, 37, False, True, 0),
+                                                                   (5, 5, 128, 4, None, False, True, 128), (12, 3, 128, 64, None, False, True, 128)])
+@pytest.mark.parametrize("few", [False, True])
+def test_attention_mma_prepares_q_and_keys(Hq, Hkv, hd, ps, window, sinks, qk_norm, rd, few):
+    """The narrow tiles making q and the new keys themselves, from the FP32 q/k/v product: the
+    pages afterwards hold the bits qk_prep writes, and the output is that of qk_prep followed by
+    the kernel.  The new positions' rows of the pages hold NaN before; with two tokens a request,
+    one request's tokens lie on both sides of a key tile's edge (positions 63 and 64), which with
+    many splits are different CTAs' key tiles; the product then comes as three split-K slices."""
+    from quench6k_b200 import ops
+    G = Hq // Hkv
+    g = torch.Generator().manual_seed(Hq * 1000 + hd + (window or 0) + rd)
+    lens = [700, 150, 333, 64, 65]
+    per = min(2, max(1, 16 // G)) if few else 1
+    q_lens = [per] * len(lens)
+    q_lens[1] = 1
+    starts = [n - ql for n, ql in zip(lens, q_lens)]
+    num_pages = sum(-(-n // ps) for n in lens) + 5
+    perm = torch.randperm(num_pages, generator=g).tolist()
+    kp = torch.full((Hkv, num_pages, ps, hd), float("nan"), dtype=torch.bfloat16)
+    vp = torch.full((Hkv, num_pages, ps, hd), float("nan"), dtype=torch.bfloat16)
+    tables = []
+    for n, start in zip(lens, starts):
+        table = [perm.pop() for _ in range(-(-n // ps))]
+        for t in range(start):                               # the keys of earlier steps; this step's rows stay NaN
+            kp[:, table[t // ps], t % ps] = torch.randn(Hkv, hd, generator=g).to(torch.bfloat16)
+            vp[:, table[t // ps], t % ps] = torch.randn(Hkv, hd, generator=g).to(torch.bfloat16)
+        tables.append(table)
+    width = max(len(t) for t in tables)
+    bt = torch.tensor([t + [-1] * (width - len(t)) for t in tables], dtype=torch.int32, device=DEV)
+    ctx = helpers.make_context(q_lens, starts, [tables])
+    T = sum(q_lens)
+    if few:                                                  # split-K partial products, which both kernels sum in order
+        qkv = (torch.randn(3, T, (Hq + 2 * Hkv) * hd, generator=g) * 0.9).to(DEV)
+    else:                                                    # rows with a pitch of their own
+        qkv = (torch.randn(T, (Hq + 2 * Hkv) * hd + 6, generator=g) * 1.5).to(DEV)[:, :(Hq + 2 * Hkv) * hd]
+    qn = (1 + 0.1 * torch.randn(hd, generator=g)).to(DEV) if qk_norm else None
+    kn = (1 + 0.1 * torch.randn(hd, generator=g)).to(DEV) if qk_norm else None
+    rotary = None
+    if rd:
+        inv = (10000.0 ** (-torch.arange(0, rd, 2, dtype=torch.float64) / rd)).to(torch.float32).to(DEV)
+        rotary = (inv, rd, False)
+    sk = torch.randn(Hq, generator=g).to(DEV) if sinks else None
+    rows = ops.attention_mma_tile_rows(hd, G, max(q_lens))
+    assert rows in (8, 16) and ops.attention_mma_prepares(hd, G, rows, rd, False)
+    assert not ops.attention_mma_prepares(hd, G, 128, rd, False) and not ops.attention_mma_prepares(hd, G, rows, 32, False)
+    assert not ops.attention_mma_prepares(hd, 1, 16, rd, False)             # sixteen tokens to a tile: qk_prep's work
+    tok0, ntok, n_tiles = ctx.query_tiles(rows // G)
+    k1, v1 = kp.to(DEV), vp.to(DEV)
+    q = ops.qk_prep(qkv.contiguous(), Hq, Hkv, hd, qn, kn, 1e-5, rotary, ctx.positions, ctx.req_of_token, bt, ps, k1, v1, torch.bfloat16)
+    prepare = {"qkv": qkv, "heads": Hq, "q_norm": qn, "k_norm": kn, "eps": 1e-5, "rotary": rotary, "write": True}
+    for max_splits in (1, 4, 64):
+        want = ops.attention_mma(q, k1, v1, bt, ctx.req_of_token, ctx.positions, tok0, ntok, rows, window, sk, max_splits=max_splits, min_tiles=1)
+        k2, v2 = kp.to(DEV), vp.to(DEV)
+        got = ops.attention_mma(None, k2, v2, bt, ctx.req_of_token, ctx.positions, tok0, ntok, rows, window, sk, max_splits=max_splits,
+                                min_tiles=1, prepare=prepare)
+        assert ops.tc_status() == 0
+        assert torch.equal(k2.view(torch.int16), k1.view(torch.int16)) and torch.equal(v2.view(torch.int16), v1.view(torch.int16)), max_splits
+        assert not torch.isnan(got.float()).any()
+        assert (got.float() - want.float()).abs().max() <= 1e-2 * want.float().abs().max(), max_splits
+    # a layer that reads another layer's cache: q alone is made; the pages stay as they are
+    got = ops.attention_mma(None, k1, v1, bt, ctx.req_of_token, ctx.positions, tok0, ntok, rows, window, sk, max_splits=4, min_tiles=1,
+                            prepare=dict(prepare, qkv=qkv[..., :Hq * hd], write=False))
+    assert (got.float() - want.float()).abs().max() <= 1e-2 * want.float().abs().max()
+    assert torch.equal(k2.view(torch.int16), k1.view(torch.int16))
+
+
 @pytest.mark.parametrize("window", [None, 300])
 @pytest.mark.parametrize("n_work,min_per", [(7, 2), (8, 1), (40, 2), (296, 2), (1000, 3)])
 def test_attention_plan_shares_the_key_tiles(window, n_work, min_per):

@@ -268,6 +268,35 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + 32, WIDE ? 1 : 2) attent
         // a launch that makes the new keys itself finds only keys of earlier steps in the pages: nothing there is the
         // work of the kernel before this one (the rows of this step's positions are replaced in shared memory)
         const bool makes_kv = !WIDE && p.qkv != nullptr && p.write_kv;
+        // The boxes of the key tile that starts at key j0: emit(K map, V map, x, y, byte offset in a stage) for each.
+        // Pages with consecutive numbers are contiguous for one head: when the tile's pages form such a run, each
+        // half comes in as one box of 64 keys instead of one box per page.
+        auto boxes = [&](int j0, auto&& emit) {
+            const int box = ps < KT ? ps : KT;                                   // keys per box of the per-page maps
+            bool run = ps < KT && j0 >= k_lo && j0 / ps + KT / ps <= p.max_blocks;
+            int first = -1;
+            if (run) {
+                first = bt[j0 / ps];
+                run = first >= 0;
+                for (int b = 1; b < KT / ps && run; ++b) run = bt[j0 / ps + b] == first + b;
+            }
+            if (run) {
+                const int y = (kh * p.num_pages + first) * ps;
+#pragma unroll
+                for (int h = 0; h < HD / 64; ++h) emit(&tm_k_run, &tm_v_run, h * 64, y, (uint32_t)(h * (KT * 128)));
+                return;
+            }
+            for (int b = 0; b < KT / box; ++b) {
+                const int j = j0 + b * box;
+                int y = p.pool_rows;                                             // out of range: the box is filled with zeros
+                if (j + box > k_lo && j <= pos_last) {
+                    const int page = bt[j / ps];
+                    if (page >= 0) y = (kh * p.num_pages + page) * ps + j % ps;
+                }
+#pragma unroll
+                for (int h = 0; h < HD / 64; ++h) emit(&tm_k, &tm_v, h * 64, y, (uint32_t)(h * (KT * 128) + b * box * 128));
+            }
+        };
         for (int i = 0; i < n_mine; ++i) {
             const int st = i % STAGES;
             // the first tiles of the ring need no free stage; of those, the ones that end before this step's first key need no wait
@@ -282,41 +311,11 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + 32, WIDE ? 1 : 2) attent
             const uint32_t fb = full0 + 8 * st;
             const int j0 = (t_begin + i) * KT;
             if (TMA) {
-                const int box = ps < KT ? ps : KT;                               // keys per box of the per-page maps
                 mbar_expect_tx(fb, 2 * TILE_BYTES);
-                // pages with consecutive numbers are contiguous for one head: when the tile's pages form
-                // such a run, each half comes in as one box of 64 keys instead of one box per page
-                bool run = ps < KT && j0 >= k_lo && j0 / ps + KT / ps <= p.max_blocks;
-                int first = -1;
-                if (run) {
-                    first = bt[j0 / ps];
-                    run = first >= 0;
-                    for (int b = 1; b < KT / ps && run; ++b) run = bt[j0 / ps + b] == first + b;
-                }
-                if (run) {
-                    const int y = (kh * p.num_pages + first) * ps;
-#pragma unroll
-                    for (int h = 0; h < HD / 64; ++h) {
-                        const uint32_t off = st * TILE_BYTES + h * (KT * 128);
-                        tma_load_2d(k_s + off, &tm_k_run, h * 64, y, fb);
-                        tma_load_2d(v_s + off, &tm_v_run, h * 64, y, fb);
-                    }
-                    continue;
-                }
-                for (int b = 0; b < KT / box; ++b) {
-                    const int j = j0 + b * box;
-                    int y = p.pool_rows;                                         // out of range: the box is filled with zeros
-                    if (j + box > k_lo && j <= pos_last) {
-                        const int page = bt[j / ps];
-                        if (page >= 0) y = (kh * p.num_pages + page) * ps + j % ps;
-                    }
-#pragma unroll
-                    for (int h = 0; h < HD / 64; ++h) {
-                        const uint32_t off = st * TILE_BYTES + h * (KT * 128) + b * box * 128;
-                        tma_load_2d(k_s + off, &tm_k, h * 64, y, fb);
-                        tma_load_2d(v_s + off, &tm_v, h * 64, y, fb);
-                    }
-                }
+                boxes(j0, [&](const CUtensorMap* mk, const CUtensorMap* mv, int x, int y, uint32_t off) {
+                    tma_load_2d(k_s + st * TILE_BYTES + off, mk, x, y, fb);
+                    tma_load_2d(v_s + st * TILE_BYTES + off, mv, x, y, fb);
+                });
             } else {
                 // every lane copies its share of the tile's chunks; keys outside the tile's range or without a page become zeros
                 for (int idx = lane; idx < KT * CH; idx += 32) {
@@ -756,7 +755,10 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + 32, WIDE ? 1 : 2) attent
 // of a long context at a small batch are fetched side by side; the groups' sums meet in shared
 // memory and are added in group order (a fixed order for a given number of splits).
 constexpr int MERGE_THREADS = 256;
-template <int HD>
+// U: parts a thread has in flight at once.  Few tiles with many parts each (a batch of one or two deep in their
+// contexts): 10, so that a round of 80 parts (head size 128) is one trip to memory; many tiles: 4, which leaves
+// registers for three blocks per SM.
+template <int HD, int U>
 __global__ void __launch_bounds__(MERGE_THREADS) attention_merge_kernel(const AttnParams p) {
     pdl_enter();
     constexpr int LPR = HD / 4;                   // threads that cover one row of HD values
@@ -779,7 +781,6 @@ __global__ void __launch_bounds__(MERGE_THREADS) attention_merge_kernel(const At
     const float sk = p.sinks ? p.sinks[kh * G + hg] * LOG2E : -INFINITY;
     // every load of the first round goes out before the maximum is known: the values and the
     // (m, l) pairs do not depend on it
-    constexpr int U = 4;
     const int g = tid / LPR, c = tid % LPR;
     float2 v0[U];
     float4 o0[U];
@@ -884,7 +885,8 @@ int launch(const AttnParams& p, const CUtensorMap* maps, int n_tiles, cudaStream
     q6k_launch_as(!WIDE && p.early != 0, attention_mma_kernel<HD, NQ, WIDE, TMA>, dim3(p.n_work, p.Hkv), (WIDE ? 8 : 4) * 32 + 32, smem, st, maps[0], maps[1], maps[2], maps[3], p);
     if (int rc = q6k_check_launch("attention_mma")) return rc;
     if (p.n_work > n_tiles) {                 // some tile may have more than one part
-        q6k_launch(attention_merge_kernel<HD>, dim3(n_tiles, p.Hkv, ROWS), MERGE_THREADS, 0, st, p);
+        if (p.n_work >= 32 * n_tiles) q6k_launch(attention_merge_kernel<HD, 10>, dim3(n_tiles, p.Hkv, ROWS), MERGE_THREADS, 0, st, p);
+        else q6k_launch(attention_merge_kernel<HD, 4>, dim3(n_tiles, p.Hkv, ROWS), MERGE_THREADS, 0, st, p);
         return q6k_check_launch("attention_merge");
     }
     return 0;

@@ -9,7 +9,12 @@
 // Permutation (reference: count/plan/scatter, flint.cu:1163-1209, which ranks with atomics): here
 // the row of a (token, slot) pair inside its expert's group is its rank among the pairs of that
 // expert in pair order, so the whole permutation is a pure function of the selection.
+#include <cooperative_groups.h>
+
+#include <algorithm>
+
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace {
 
@@ -20,36 +25,97 @@ namespace {
 
 // Top-k of one token's scores by one warp, the scores in registers (lane l holds experts l, l + 32, ...; NL of
 // them, E <= 32 NL).  Writes the chosen experts and weights (renormalised if asked).  `total` divides softmax scores.
+// also_e (or null): a second place for the chosen experts (shared memory of the caller).
+//
+// One warp runs this alone, so what counts is the number of dependent instructions of a round.  With eight values
+// per lane each lane first sorts its own (a network of compare-exchanges: value descending, ties by index
+// ascending); a round then looks at the lanes' first entries only (two warp reductions), and the lane that held
+// the winner moves its entries up by one.  With more values per lane a round scans them.  Scores, their sum and
+// the stores wait until the rounds are over (lane r keeps round r's result).
 template <int NL>
-__device__ __forceinline__ void warp_topk_regs(float (&val)[NL], int E, int k, int sigmoid, int renorm, float total, int* sel_e, float* sel_w) {
+__device__ __forceinline__ void warp_topk_regs(float (&val)[NL], int E, int k, int sigmoid, int renorm, float total, int* sel_e, float* sel_w,
+                                               int* also_e = nullptr) {
     const int lane = threadIdx.x & 31;
     int bits[NL];
 #pragma unroll
     for (int i = 0; i < NL; ++i) bits[i] = lane + 32 * i < E ? __float_as_int(val[i]) : -1;      // -1: no expert / taken
-    float chosen_sum = 0.0f, mine = 0.0f;
-    for (int r = 0; r < k; ++r) {
-        int best = -1, best_i = 0;
+    constexpr bool SORTED = NL == 8;
+    [[maybe_unused]] int slot[NL];                       // sorted variant: which of the lane's experts an entry is
+    if constexpr (SORTED) {
 #pragma unroll
-        for (int i = 0; i < NL; ++i)
-            if (bits[i] > best) best = bits[i], best_i = i;
+        for (int i = 0; i < NL; ++i) slot[i] = i;
+        auto cx = [&](int a, int b) {                    // the greater value first; of equal ones the lower index
+            const bool swap = bits[b] > bits[a] || (bits[b] == bits[a] && slot[b] < slot[a]);
+            const int ba = bits[a], sa = slot[a];
+            bits[a] = swap ? bits[b] : ba, slot[a] = swap ? slot[b] : sa;
+            bits[b] = swap ? ba : bits[b], slot[b] = swap ? sa : slot[b];
+        };
+        cx(0, 1), cx(2, 3), cx(4, 5), cx(6, 7);
+        cx(0, 2), cx(1, 3), cx(4, 6), cx(5, 7);
+        cx(1, 2), cx(5, 6);
+        cx(0, 4), cx(1, 5), cx(2, 6), cx(3, 7);
+        cx(2, 4), cx(3, 5);
+        cx(1, 2), cx(3, 4), cx(5, 6);
+    }
+    int my_top = -1, my_e = 0;                           // lane r: the bits of the r-th score and its expert (r < 32)
+    for (int r = 0; r < k; ++r) {
+        int best, best_i = 0;
+        if constexpr (SORTED) {
+            best = bits[0], best_i = slot[0];
+        } else {
+            int m[NL];
+#pragma unroll
+            for (int i = 0; i < NL; ++i) m[i] = bits[i];
+#pragma unroll
+            for (int w = 1; w < NL; w *= 2)
+#pragma unroll
+                for (int i = 0; i + w < NL; i += 2 * w) m[i] = max(m[i], m[i + w]);
+            best = m[0];
+#pragma unroll
+            for (int i = NL - 1; i >= 0; --i)            // the first of equal ones: the lane's lowest expert
+                if (bits[i] == best) best_i = i;
+        }
         const int top = __reduce_max_sync(0xffffffffu, best);
         const int idx = __reduce_min_sync(0xffffffffu, best == top ? lane + 32 * best_i : 0x7fffffff);      // ties: the lower expert
-        if ((idx & 31) == lane) {
+        const bool won = (idx & 31) == lane;
+        if constexpr (SORTED) {
+#pragma unroll
+            for (int i = 0; i + 1 < NL; ++i) bits[i] = won ? bits[i + 1] : bits[i], slot[i] = won ? slot[i + 1] : slot[i];
+            bits[NL - 1] = won ? -1 : bits[NL - 1];
+        } else {
 #pragma unroll
             for (int i = 0; i < NL; ++i)
-                if (i == (idx >> 5)) bits[i] = -1;
+                if (won && i == (idx >> 5)) bits[i] = -1;
         }
-        const float best_f = __int_as_float(top);
-        const float score = sigmoid ? best_f : best_f / total;
-        chosen_sum += score;
-        if (lane == 0) sel_e[r] = idx;
-        if (lane == r) mine = score;                 // lane r keeps the r-th score (r < 32; later ones: below)
-        if (r >= 32 && lane == 0) sel_w[r] = score;
+        if (lane == (r & 31)) {
+            if (r >= 32) {                               // the lane's earlier result makes room (more than 32 per token: rare)
+                sel_e[r - 32] = my_e, sel_w[r - 32] = __int_as_float(my_top);
+                if (also_e) also_e[r - 32] = my_e;
+            }
+            my_top = top, my_e = idx;
+        }
     }
+    __syncwarp();
+    // the scores and their sum: rounds lane, lane + 32, ... of this lane, the earlier ones from memory
+    const int last = ((k - 1 - lane) >> 5) * 32 + lane;  // this lane's last round (negative: none)
+    float part = 0.0f, mine = 0.0f;
+    for (int r = lane; r < k; r += 32) {
+        const float raw = r == last ? __int_as_float(my_top) : sel_w[r];
+        const float score = sigmoid ? raw : raw / total;
+        part += score;
+        if (r == last) mine = score;
+        else sel_w[r] = score;
+    }
+    const float chosen_sum = warp_sum(part);
     const float den = !renorm ? 1.0f : (sigmoid ? chosen_sum + 1e-20f : chosen_sum);
-    if (lane < k && lane < 32) sel_w[lane] = mine / den;
-    if (k > 32 && renorm && lane == 0)
-        for (int r = 32; r < k; ++r) sel_w[r] /= den;
+    for (int r = lane; r < k; r += 32) {
+        if (r == last) {
+            sel_e[r] = my_e, sel_w[r] = mine / den;
+            if (also_e) also_e[r] = my_e;
+        } else {
+            sel_w[r] /= den;
+        }
+    }
 }
 
 // The same for any number of experts, the scores' bits in shared memory bits[0..E) (lane l looks after l, l + 32, ...).
@@ -82,7 +148,7 @@ __device__ __forceinline__ void warp_topk_shared(int* bits, int E, int k, int si
 // One token's scores from its logits (sigmoid, or the numerators of the softmax and their sum), then the top-k.
 // z: the logits in global memory (written by other blocks of this kernel: read past L1) or, SHARED, in shared memory.
 template <int NL, bool SHARED = false>
-__device__ __forceinline__ void warp_route_regs(const float* z, int E, int k, int sigmoid, int renorm, int* sel_e, float* sel_w) {
+__device__ __forceinline__ void warp_route_regs(const float* z, int E, int k, int sigmoid, int renorm, int* sel_e, float* sel_w, int* also_e = nullptr) {
     const int lane = threadIdx.x & 31;
     float val[NL];
 #pragma unroll
@@ -109,7 +175,7 @@ __device__ __forceinline__ void warp_route_regs(const float* z, int E, int k, in
         }
         total = warp_sum(sum);
     }
-    warp_topk_regs<NL>(val, E, k, sigmoid, renorm, total, sel_e, sel_w);
+    warp_topk_regs<NL>(val, E, k, sigmoid, renorm, total, sel_e, sel_w, also_e);
 }
 
 // logits: [slices, T, E]; the slices (split-K partial products of the router) are summed in order first.
@@ -154,160 +220,206 @@ __global__ void route_kernel(const float* logits, int slices, size_t slice_strid
 }
 
 // Router of a decode step in one launch (reference: router_kernel, crates/cuda/kernels/flint.cu:1002-1055,
-// which also routes in its last block).  The logits are a matrix-vector product of at most 16 tokens with the
-// [E, D] router matrix: a block of eight warps takes four experts, its warps split D between them (16 bytes per
-// lane and row: with D = 2,048 every load of the kernel is in flight at once), each lane multiplies its eight
-// weights of four experts with its eight activations of every token, and the 4 x T sums of a warp are brought
-// together by a transposing reduction (the lanes halve the set of sums they carry while they double the set of
-// lanes summed over: 31 shuffles for 32 sums where one reduction per sum would take 160).  The warps' sums meet
-// in shared memory and are added in warp order.  The block that finishes last (atomic ticket, no waiting) scores
-// every token, picks its top-k and sorts the (token, slot) pairs by expert.
+// which routes in the block that finishes last).  Here one cluster of eight CTAs does it all and nothing meets
+// through global memory:
+//
+//   1. every CTA owns an eighth of the experts.  It copies their rows of the router matrix into its shared memory
+//      (one bulk copy per row, rows padded so that a quarter warp's 16-byte reads fall into different banks) while
+//      the kernel launched before this one still runs: the matrix is older than any kernel of the step.
+//   2. after the wait its eight warps split D and multiply their stretches of the rows with the step's activations
+//      (at most 16 tokens) on mma.sync, experts as the M side, tokens as the N side, both operands read as 16
+//      contiguous bytes per lane (the sum over k may be taken in any order both operands agree on); the warps'
+//      sums meet in shared memory and are added in warp order.
+//   3. the logits go into CTA 0's shared memory (and to global memory for whoever wants them); after a cluster
+//      barrier the other CTAs are done, and in CTA 0 a warp per token scores it and picks its top-k.
+//   4. CTA 0 sorts the (token, slot) pairs by expert.
+// A model with more experts than fit at once (32 rows of D, or 16) walks them in chunks through a few buffers.
+namespace cg = cooperative_groups;
 constexpr int SMALL_T = 16;
-constexpr int ROUTER_ROWS = 4;              // experts of a block
+constexpr int RC_CL = 8;                     // CTAs of the cluster
+constexpr int RC_WARPS = 8;
+constexpr int RC_MAXBUF = 8;
+constexpr int RC_PAIRS = 512;                // pairs whose experts fit CTA 0's array
+constexpr size_t RC_SMEM = 200 * 1024;       // what a CTA may use of its shared memory
 
-// v[0..NV) of every lane -> lane L holds the warp's sum of v[index(L)]; NV a power of two <= 32.  index(L) takes
-// its bits from the lane's high bits: for NV = 32 it is L itself, for NV = 8 it is L >> 2 (lanes 0, 4, 8, ... hold sums 0..7).
-template <int NV>
-__device__ __forceinline__ float transpose_reduce(float (&v)[NV]) {
-    const int lane = threadIdx.x & 31;
-    int off = 16;
-#pragma unroll
-    for (int n = NV; n > 1; n >>= 1, off >>= 1) {
-        const bool upper = lane & off;
-#pragma unroll
-        for (int i = 0; i < n / 2; ++i) {
-            const float keep = upper ? v[i + n / 2] : v[i], give = upper ? v[i] : v[i + n / 2];
-            v[i] = keep + __shfl_xor_sync(0xffffffffu, give, off);
-        }
-    }
-    float r = v[0];
-    for (; off > 0; off >>= 1) r += __shfl_xor_sync(0xffffffffu, r, off);
-    return r;
+__device__ int g_router_status = 0;
+
+__host__ __device__ inline int rc_stride(int D) { return D * 2 + (64 + 128 - (D * 2) % 128) % 128; }      // bytes; 64 mod 128
+__host__ __device__ inline size_t rc_fixed_bytes(int RB, int NB, int E) {                                  // all but the weight buffers
+    return (size_t)RC_WARPS * RB * NB * 128 * sizeof(float) + (size_t)NB * 8 * E * sizeof(float) + RC_PAIRS * sizeof(int) + 128;
 }
 
-// TP: the token count rounded up to a power of two (1, 2, 4, 8, 16).
-template <int TP>
-__global__ void __launch_bounds__(256) router_small_kernel(const __nv_bfloat16* xn, const __nv_bfloat16* __restrict__ w, int T_, int E,
-                                                           int D, int k, int sigmoid, int renorm, float* logits, int* sel_e, float* sel_w,
-                                                           int* order, unsigned* ticket) {
-    // the router matrix is older than any kernel of the step: its rows are asked for while the kernel launched before this
-    // one still runs (programmatic dependent launch); the activations wait for that kernel
+__device__ __forceinline__ void rc_bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void rc_mma(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// NB: blocks of 8 tokens (1 or 2); RB: blocks of 16 experts per chunk (1 or 2); bufs: weight buffers of a chunk each.
+template <int NB, int RB>
+__global__ void __cluster_dims__(RC_CL, 1, 1) __launch_bounds__(RC_WARPS * 32, 1)
+    router_cluster_kernel(const __nv_bfloat16* xn, const __nv_bfloat16* w, int T_, int E, int D, int k, int sigmoid, int renorm, float* logits,
+                          int* sel_e, float* sel_w, int* order, int bufs) {
     pdl_launch();
-    bool waited = false;
-    constexpr int NV = ROUTER_ROWS * TP;                                  // sums of a warp: index = row * TP + token
-    constexpr int PASS = NV > 32 ? 32 : NV;                               // reduced 32 at a time
-    __shared__ float meet[8][NV];
-    __shared__ int pair_e[SMALL_T * 8 * 4];                               // the last block: the pairs' experts (up to 512 pairs)
-    __shared__ int is_last;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int e0 = blockIdx.x * ROUTER_ROWS;
-    {
-        float acc[NV];
-#pragma unroll
-        for (int i = 0; i < NV; ++i) acc[i] = 0.0f;
-        for (int d0 = (warp * 32 + lane) * 8; d0 < D; d0 += 8 * 256) {
-            float wf[ROUTER_ROWS][8];
-#pragma unroll
-            for (int r = 0; r < ROUTER_ROWS; ++r) {
-                const int e = e0 + r < E ? e0 + r : E - 1;                // a ragged last block reads a valid row and drops the sum
-                const uint4 wv = *reinterpret_cast<const uint4*>(w + (size_t)e * D + d0);
-                const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 f = __bfloat1622float2(w2[i]);
-                    wf[r][2 * i] = f.x, wf[r][2 * i + 1] = f.y;
-                }
-            }
-            if (!waited) {
-                pdl_wait();
-                waited = true;
-            }
-#pragma unroll
-            for (int t = 0; t < TP; ++t) {
-                if (t < T_) {
-                    const uint4 xv = ld_after_wait(xn + (size_t)t * D + d0);
-                    const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&xv);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const float2 f = __bfloat1622float2(x2[i]);
-#pragma unroll
-                        for (int r = 0; r < ROUTER_ROWS; ++r) {
-                            acc[r * TP + t] = fmaf(f.x, wf[r][2 * i], acc[r * TP + t]);
-                            acc[r * TP + t] = fmaf(f.y, wf[r][2 * i + 1], acc[r * TP + t]);
-                        }
-                    }
-                }
-            }
-        }
-        if (!waited) pdl_wait();                                          // a warp without a stride of its own
-#pragma unroll
-        for (int p0 = 0; p0 < NV; p0 += PASS) {
-            float part[PASS];
-#pragma unroll
-            for (int i = 0; i < PASS; ++i) part[i] = acc[p0 + i];
-            const float total = transpose_reduce<PASS>(part);
-            constexpr int STEP = 32 / PASS;                               // lanes 0, STEP, 2 STEP, ... hold sums 0, 1, 2, ...
-            if (lane % STEP == 0) meet[warp][p0 + lane / STEP] = total;
-        }
-        __syncthreads();
-        if (threadIdx.x < NV) {
-            const int r = threadIdx.x / TP, t = threadIdx.x % TP;
-            if (t < T_ && e0 + r < E) {
-                float z = 0.0f;
-#pragma unroll
-                for (int wi = 0; wi < 8; ++wi) z += meet[wi][threadIdx.x];       // warps in order: a fixed sum
-                logits[(size_t)t * E + e0 + r] = z;
-            }
-        }
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();
+    constexpr int CR = RB * 16;                                              // experts of a chunk
+    extern __shared__ __align__(128) uint8_t rc_smem[];
+    const int stride = rc_stride(D);
+    uint8_t* wbuf = rc_smem;                                                 // [bufs][CR][stride]
+    float* meet = reinterpret_cast<float*>(rc_smem + (size_t)bufs * CR * stride);      // [warps][RB * NB * 128]
+    float* lg_all = meet + RC_WARPS * RB * NB * 128;                         // [8 NB][E]: CTA 0's holds every token's logits
+    int* pair_e = reinterpret_cast<int*>(lg_all + NB * 8 * E);               // [RC_PAIRS]: the pairs' experts (CTA 0)
+    __shared__ __align__(8) uint64_t bars[RC_MAXBUF];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, quad = lane >> 2, pair = lane & 3;
+    const int per = (E + RC_CL - 1) / RC_CL, e_begin = min(E, rank * per), n_rows = min(E, e_begin + per) - e_begin;
+    const int chunks = (n_rows + CR - 1) / CR;
+    if (threadIdx.x == 0) {
+        for (int b = 0; b < bufs; ++b) mbar_init(smem_u32(&bars[b]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) is_last = atomicAdd(ticket, 1u) == gridDim.x - 1;
-    __syncthreads();
-    if (!is_last) return;
-    __threadfence();
-    const int pairs = T_ * k;
-    const bool sort_here = pairs <= SMALL_T * 8 * 4;          // the pairs' experts fit the shared array: they are sorted from there
-    for (int t = warp; t < T_; t += 8) {         // a warp per token, its scores in registers
-        const float* z = logits + (size_t)t * E;
-        if (E <= 256) warp_route_regs<8>(z, E, k, sigmoid, renorm, sel_e + (size_t)t * k, sel_w + (size_t)t * k);
-        else warp_route_regs<22>(z, E, k, sigmoid, renorm, sel_e + (size_t)t * k, sel_w + (size_t)t * k);
+    // chunk c into buffer c % bufs: warp 0, a row per lane
+    auto stage = [&](int c) {
+        const int rows_here = min(CR, n_rows - c * CR), b = c % bufs;
+        const uint32_t bar = smem_u32(&bars[b]);
+        if (lane == 0) mbar_expect_tx(bar, (uint32_t)rows_here * D * 2);
         __syncwarp();
-        if (sort_here)
-            for (int r = lane; r < k; r += 32) pair_e[t * k + r] = sel_e[(size_t)t * k + r];      // this warp's own stores, read back
+        for (int r = lane; r < rows_here; r += 32)
+            rc_bulk_copy(smem_u32(wbuf + ((size_t)b * CR + r) * stride), w + (size_t)(e_begin + c * CR + r) * D, (uint32_t)D * 2, bar);
+    };
+    if (warp == 0)
+        for (int c = 0; c < chunks && c < bufs; ++c) stage(c);
+    // another CTA's shared memory may be written once that CTA runs: every CTA says so here, and listens below
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    pdl_wait();                               // the activations, and the outputs' last readers
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    const __nv_bfloat16* xrow[NB];
+    bool live[NB];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+        live[nb] = nb * 8 + quad < T_;
+        xrow[nb] = xn + (size_t)(live[nb] ? nb * 8 + quad : 0) * D + pair * 8;
     }
-    // pairs sorted by expert (stable): tiles of one expert run side by side and share its weights in L2.  A pair's
-    // place is the number of pairs with a lower expert, or the same expert and a lower index.
-    __syncthreads();
-    if (sort_here) {
-        // `share` lanes count for one pair, each over its part of the pairs
-        int share = 1;
-        while (share < 32 && pairs * share * 2 <= (int)blockDim.x) share *= 2;
-        for (int base = 0; base < pairs; base += blockDim.x / share) {
-            const int p = base + threadIdx.x / share, sub = threadIdx.x % share;
-            int rank = 0;
-            if (p < pairs) {
-                const int e = pair_e[p];
-                for (int q = sub; q < pairs; q += share) {
-                    const int eq = pair_e[q];
-                    rank += (eq < e) || (eq == e && q < p);
+    float* lg_zero = cluster.map_shared_rank(lg_all, 0);
+    bool ok = true;
+    for (int c = 0; c < chunks; ++c) {
+        const int b = c % bufs, rows_here = min(CR, n_rows - c * CR);
+        if (ok && !mbar_wait(smem_u32(&bars[b]), (c / bufs) & 1)) {
+            if (threadIdx.x == 0) atomicExch(&g_router_status, 1);
+            ok = false;                       // nothing more is computed; the barriers below are still kept
+        }
+        float acc[RB][NB][4];
+#pragma unroll
+        for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) acc[rb][nb][0] = acc[rb][nb][1] = acc[rb][nb][2] = acc[rb][nb][3] = 0.0f;
+        const uint8_t* wb = wbuf + (size_t)b * CR * stride;
+        // a warp's stretches of 128 k, two at a time: all their activations are asked for before the first product
+        for (int k0 = warp * 128; ok && k0 < D; k0 += 2 * RC_WARPS * 128) {
+            uint4 bx[2][NB][4];
+#pragma unroll
+            for (int s2 = 0; s2 < 2; ++s2)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int kk = k0 + s2 * RC_WARPS * 128 + j * 32 + pair * 8;      // this lane's eight elements of k
+#pragma unroll
+                    for (int nb = 0; nb < NB; ++nb) bx[s2][nb][j] = kk < D && live[nb] ? ld_after_wait(xrow[nb] + kk - pair * 8) : make_uint4(0, 0, 0, 0);
                 }
+#pragma unroll
+            for (int s2 = 0; s2 < 2; ++s2) {
+                uint4 a[RB][2][4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const int kk = k0 + s2 * RC_WARPS * 128 + j * 32 + pair * 8;
+#pragma unroll
+                    for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+                        for (int h = 0; h < 2; ++h)   // rows past the chunk's last hold whatever the buffer held: their sums are dropped;
+                                                      // D is a multiple of 8: a lane's 16 bytes are inside or outside as a whole
+                            a[rb][h][j] = kk < D ? *reinterpret_cast<const uint4*>(wb + (size_t)(rb * 16 + quad + 8 * h) * stride + kk * 2) : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+#pragma unroll
+                    for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+                        for (int nb = 0; nb < NB; ++nb) {
+                            const uint4 lo = a[rb][0][j], hi = a[rb][1][j], t = bx[s2][nb][j];
+                            rc_mma(acc[rb][nb], lo.x, hi.x, lo.y, hi.y, t.x, t.y);
+                            rc_mma(acc[rb][nb], lo.z, hi.z, lo.w, hi.w, t.z, t.w);
+                        }
             }
-            for (int o = share >> 1; o > 0; o >>= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);
-            if (p < pairs && sub == 0) order[rank] = p;
         }
-    } else {
-        for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
-            const int e = sel_e[p];
-            int rank = 0;
-            for (int q = 0; q < pairs; ++q) {
-                const int eq = sel_e[q];
-                rank += (eq < e) || (eq == e && q < p);
-            }
-            order[rank] = p;
+#pragma unroll
+        for (int rb = 0; rb < RB; ++rb)
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) meet[(size_t)warp * (RB * NB * 128) + ((rb * NB + nb) * 4 + i) * 32 + lane] = acc[rb][nb][i];
+        __syncthreads();
+        // thread -> (row block, token block, element and lane of the fragment): experts quad (+8), tokens 2 pair (+1)
+        for (int idx = threadIdx.x; idx < RB * NB * 128; idx += RC_WARPS * 32) {
+            const int ln = idx & 31, i = (idx >> 5) & 3, nb = (idx >> 7) % NB, rb = (idx >> 7) / NB;
+            const int row = rb * 16 + (ln >> 2) + 8 * (i >> 1), t = nb * 8 + 2 * (ln & 3) + (i & 1);
+            if (row >= rows_here || t >= T_) continue;
+            float z = 0.0f;
+#pragma unroll
+            for (int q = 0; q < RC_WARPS; ++q) z += meet[(size_t)q * (RB * NB * 128) + idx];      // warps in order: a fixed sum
+            const int e = e_begin + c * CR + row;
+            logits[(size_t)t * E + e] = z;
+            lg_zero[t * E + e] = z;
+        }
+        __syncthreads();                      // meet and the buffer are free again
+        if (warp == 0 && c + bufs < chunks) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");          // the reads above, before the copy overwrites them
+            stage(c + bufs);
         }
     }
-    if (threadIdx.x == 0) *ticket = 0;          // ready for the next launch
+    cluster.sync();                           // every token's logits are in CTA 0; nothing is written into its memory after this
+    if (rank != 0) return;
+    for (int t = warp; t < T_; t += RC_WARPS) {
+        const float* z = lg_all + (size_t)t * E;
+        if (E <= 256) warp_route_regs<8, true>(z, E, k, sigmoid, renorm, sel_e + (size_t)t * k, sel_w + (size_t)t * k, pair_e + t * k);
+        else warp_route_regs<22, true>(z, E, k, sigmoid, renorm, sel_e + (size_t)t * k, sel_w + (size_t)t * k, pair_e + t * k);
+    }
+    if (T_ == 1 && k <= 32) {
+        // one token: its warp sorts the pairs by itself (a pair's place is the number of pairs with a lower expert)
+        if (warp != 0) return;
+        __syncwarp();
+        if (lane < k) {
+            const int e = pair_e[lane];
+            int rnk = 0;
+            for (int q = 0; q < k; ++q) rnk += pair_e[q] < e;                // a token's experts differ
+            order[rnk] = lane;
+        }
+        return;
+    }
+    __syncthreads();
+    // pairs sorted by expert (stable): tiles of one expert run side by side and share its weights in L2.  A pair's
+    // place is the number of pairs with a lower expert, or the same expert and a lower index.  `share` lanes count
+    // for one pair, each over its part of the pairs.
+    const int pairs = T_ * k;
+    int share = 1;
+    while (share < 32 && pairs * share * 2 <= (int)blockDim.x) share *= 2;
+    for (int base = 0; base < pairs; base += blockDim.x / share) {
+        const int p = base + threadIdx.x / share, sub = threadIdx.x % share;
+        int rnk = 0;
+        if (p < pairs) {
+            const int e = pair_e[p];
+            for (int q = sub; q < pairs; q += share) {
+                const int eq = pair_e[q];
+                rnk += (eq < e) || (eq == e && q < p);
+            }
+        }
+        for (int o = share >> 1; o > 0; o >>= 1) rnk += __shfl_xor_sync(0xffffffffu, rnk, o);
+        if (p < pairs && sub == 0) order[rnk] = p;
+    }
 }
 
 constexpr int PERM_CHUNK = 1024;           // pairs per chunk of the permutation kernels
@@ -522,29 +634,60 @@ Q6K_API int q6k_route(const float* logits, int slices, int T_, int E, int k, int
     return q6k_check_launch("route");
 }
 
-// Whether the one-launch decode router takes a step of T tokens with E experts of width D (k of them per token).
-Q6K_API int q6k_router_small_supported(int T_, int E, int D, int k) {
-    return T_ > 0 && T_ <= SMALL_T && E > 0 && E <= 704 && k > 0 && k <= E && D > 0 && D % 8 == 0;
+// How the cluster router lays out a step: blocks of 16 experts per chunk (2 where 32 rows of D fit a CTA's shared
+// memory beside the rest, else 1, else 0: not supported) and the number of chunk buffers.
+static int router_layout(int T_, int E, int D, int* bufs) {
+    const int NB = T_ <= 8 ? 1 : 2, per = (E + RC_CL - 1) / RC_CL;
+    for (int RB = 2; RB >= 1; --RB) {
+        const size_t chunk = (size_t)RB * 16 * rc_stride(D), fixed = rc_fixed_bytes(RB, NB, E);
+        if (fixed + chunk > RC_SMEM) continue;
+        if (RB == 2 && per <= 16) continue;                                  // an eighth of the experts fits one block of 16
+        const int chunks = (per + RB * 16 - 1) / (RB * 16);
+        *bufs = (int)std::min<size_t>(std::min(chunks, RC_MAXBUF), (RC_SMEM - fixed) / chunk);
+        return RB;
+    }
+    return 0;
 }
 
-// xn: bfloat16 [T, D], T <= 16, D a multiple of 8; w: bfloat16 [E, D]; logits: FP32 [T, E] scratch;
-// ticket: one zeroed 32-bit word that the kernel leaves zeroed.
-// order: int32 [T*k], the pairs (token * k + slot) sorted by expert, ties in pair order.
+// Whether the one-launch decode router takes a step of T tokens with E experts of width D (k of them per token).
+Q6K_API int q6k_router_small_supported(int T_, int E, int D, int k) {
+    int bufs = 0;
+    return T_ > 0 && T_ <= SMALL_T && E > 0 && E <= 704 && k > 0 && k <= E && T_ * k <= RC_PAIRS && D > 0 && D % 8 == 0 &&
+           router_layout(T_, E, D, &bufs) > 0;
+}
+
+Q6K_API int q6k_router_status() {
+    int v = -1;
+    if (cudaMemcpyFromSymbol(&v, g_router_status, sizeof v) != cudaSuccess) return -1;
+    return v;
+}
+
+// xn: bfloat16 [T, D], T <= 16, D a multiple of 8; w: bfloat16 [E, D]; logits: FP32 [T, E] (the router logits, for
+// whoever wants them); order: int32 [T*k], the pairs (token * k + slot) sorted by expert, ties in pair order.
 Q6K_API int q6k_router_small(const void* xn, const void* w, int T_, int E, int D, int k, int sigmoid, int renorm, float* logits,
-                             int* sel_e, float* sel_w, int* order, unsigned* ticket, cudaStream_t st) {
+                             int* sel_e, float* sel_w, int* order, cudaStream_t st) {
     if (T_ == 0) return 0;
-    Q6K_REQUIRE(q6k_router_small_supported(T_, E, D, k), "router_small: %d tokens, %d experts of width %d, %d per token (at most %d tokens, 704 experts)",
-                T_, E, D, k, SMALL_T);
+    Q6K_REQUIRE(q6k_router_small_supported(T_, E, D, k), "router_small: %d tokens, %d experts of width %d, %d per token (at most %d tokens, 704 experts, %d pairs)",
+                T_, E, D, k, SMALL_T, RC_PAIRS);
     Q6K_REQUIRE(((uintptr_t)xn & 15) == 0 && ((uintptr_t)w & 15) == 0, "router_small: D=%d must be a multiple of 8 and the operands 16-byte aligned", D);
-    const int blocks = (E + ROUTER_ROWS - 1) / ROUTER_ROWS;
-#define ROUTER_LAUNCH(TP)                                                                                                            \
-    q6k_launch_as(true, router_small_kernel<TP>, blocks, 256, 0, st, (const __nv_bfloat16*)xn, (const __nv_bfloat16*)w, T_, E, D, k, sigmoid, renorm, \
-               logits, sel_e, sel_w, order, ticket)
-    if (T_ == 1) ROUTER_LAUNCH(1);
-    else if (T_ == 2) ROUTER_LAUNCH(2);
-    else if (T_ <= 4) ROUTER_LAUNCH(4);
-    else if (T_ <= 8) ROUTER_LAUNCH(8);
-    else ROUTER_LAUNCH(16);
+    int bufs = 0;
+    const int RB = router_layout(T_, E, D, &bufs), NB = T_ <= 8 ? 1 : 2;
+    const size_t smem = (size_t)bufs * RB * 16 * rc_stride(D) + rc_fixed_bytes(RB, NB, E);
+#define ROUTER_LAUNCH(NB_, RB_)                                                                                                       \
+    do {                                                                                                                              \
+        static bool configured = false;                                                                                               \
+        if (!configured) {                                                                                                            \
+            if (cudaFuncSetAttribute(router_cluster_kernel<NB_, RB_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)RC_SMEM) != cudaSuccess) \
+                return q6k_check_launch("router_small: shared memory attribute");                                                     \
+            configured = true;                                                                                                        \
+        }                                                                                                                             \
+        q6k_launch_as(true, router_cluster_kernel<NB_, RB_>, RC_CL, RC_WARPS * 32, smem, st, (const __nv_bfloat16*)xn, (const __nv_bfloat16*)w, T_, E, D, k, \
+                      sigmoid, renorm, logits, sel_e, sel_w, order, bufs);                                                            \
+    } while (0)
+    if (NB == 1 && RB == 1) ROUTER_LAUNCH(1, 1);
+    else if (NB == 1) ROUTER_LAUNCH(1, 2);
+    else if (RB == 1) ROUTER_LAUNCH(2, 1);
+    else ROUTER_LAUNCH(2, 2);
 #undef ROUTER_LAUNCH
     return q6k_check_launch("router_small");
 }

@@ -310,7 +310,8 @@ def tc_status() -> int:
     lib.q6k_tc_status.restype = ctypes.c_int
     lib.q6k_attention_status.restype = ctypes.c_int
     lib.q6k_attention_tc_status.restype = ctypes.c_int
-    return lib.q6k_tc_status() or lib.q6k_attention_status() or lib.q6k_attention_tc_status()
+    lib.q6k_router_status.restype = ctypes.c_int
+    return lib.q6k_tc_status() or lib.q6k_attention_status() or lib.q6k_attention_tc_status() or lib.q6k_router_status()
 
 
 _workspaces = {}
@@ -746,9 +747,6 @@ def route(logits: torch.Tensor, k: int, scoring: str, renorm: bool):
     return sel_e, sel_w
 
 
-_tickets = {}
-
-
 @functools.lru_cache(maxsize=None)          # a question about sizes: asked of the library once
 def router_small_supported(T: int, E: int, D: int, k: int) -> bool:
     """Whether the one-launch decode router (router_small, and with it the per-pair expert products) takes this step."""
@@ -769,15 +767,12 @@ def router_small(xn: torch.Tensor, w: torch.Tensor, k: int, scoring: str, renorm
     if w.shape[1] != D:
         raise KernelError("router_small: widths disagree")
     dev = xn.device
-    ticket = _tickets.get(str(dev))
-    if ticket is None:
-        ticket = _tickets[str(dev)] = torch.zeros(1, dtype=torch.int32, device=dev)
     logits = torch.empty((T, E), dtype=torch.float32, device=dev)
     sel_e = torch.empty((T, k), dtype=torch.int32, device=dev)
     sel_w = torch.empty((T, k), dtype=torch.float32, device=dev)
     order = torch.empty(T * k, dtype=torch.int32, device=dev)
     _call("q6k_router_small", _ptr(xn), _ptr(w), _i(T), _i(E), _i(D), _i(k), _i(1 if scoring == "sigmoid" else 0),
-          _i(1 if renorm else 0), _ptr(logits), _ptr(sel_e), _ptr(sel_w), _ptr(order), _ptr(ticket), _stream())
+          _i(1 if renorm else 0), _ptr(logits), _ptr(sel_e), _ptr(sel_w), _ptr(order), _stream())
     return (sel_e, sel_w, order, logits) if with_logits else (sel_e, sel_w, order)
 
 

@@ -268,6 +268,7 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + 32, WIDE ? 1 : 2) attent
         // a launch that makes the new keys itself finds only keys of earlier steps in the pages: nothing there is the
         // work of the kernel before this one (the rows of this step's positions are replaced in shared memory)
         const bool makes_kv = !WIDE && p.qkv != nullptr && p.write_kv;
+        const uint64_t once = l2_evict_first_policy();                       // a step reads a key once
         // The boxes of the key tile that starts at key j0: emit(K map, V map, x, y, byte offset in a stage) for each.
         // Pages with consecutive numbers are contiguous for one head: when the tile's pages form such a run, each
         // half comes in as one box of 64 keys instead of one box per page.
@@ -313,8 +314,8 @@ __global__ void __launch_bounds__((WIDE ? 8 : 4) * 32 + 32, WIDE ? 1 : 2) attent
             if (TMA) {
                 mbar_expect_tx(fb, 2 * TILE_BYTES);
                 boxes(j0, [&](const CUtensorMap* mk, const CUtensorMap* mv, int x, int y, uint32_t off) {
-                    tma_load_2d(k_s + st * TILE_BYTES + off, mk, x, y, fb);
-                    tma_load_2d(v_s + st * TILE_BYTES + off, mv, x, y, fb);
+                    tma_load_2d_once(k_s + st * TILE_BYTES + off, mk, x, y, fb, once);
+                    tma_load_2d_once(v_s + st * TILE_BYTES + off, mv, x, y, fb, once);
                 });
             } else {
                 // every lane copies its share of the tile's chunks; keys outside the tile's range or without a page become zeros

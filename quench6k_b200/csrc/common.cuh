@@ -92,6 +92,21 @@ __device__ __forceinline__ uint4 ld_after_wait(const void* p) {
     return v;
 }
 
+// Data that a step reads once (weights, a request's keys and values) is fetched with this policy: its lines are the
+// first to leave the L2 cache again, so that what is read again soon (activations, partial sums, the kernels'
+// own code) stays there.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+// 16 bytes of such data (read-only for the kernel's lifetime), past L1.
+__device__ __forceinline__ uint4 ld_once(const void* p, uint64_t policy) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p), "l"(policy));
+    return v;
+}
+
 int q6k_pdl_mode();           // 0: never, 1: every launch, 2: launches marked as overlapping
 
 template <typename... KArgs, typename... Args>

@@ -18,11 +18,6 @@ namespace {
 
 constexpr int SK_WARPS = 8;
 
-__device__ __forceinline__ uint4 sk_ld_stream(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
 __device__ __forceinline__ void sk_mma(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
@@ -43,6 +38,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(const __nv_b
     // launched before this one still runs (programmatic dependent launch); the activations and the output wait for it.
     pdl_launch();
     bool waited = false;
+    const uint64_t once = l2_evict_first_policy();
     constexpr bool DUAL = EPI == SK_SWIGLU;
     constexpr int MATS = DUAL ? 2 : 1;
     __shared__ float meet[SK_WARPS][MATS * RB * NB * 4 * 32];
@@ -84,7 +80,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(const __nv_b
 #pragma unroll
                 for (int rb = 0; rb < RB; ++rb)
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) a[m][rb][h][j] = in ? sk_ld_stream(wrow[m][rb][h] + k) : make_uint4(0, 0, 0, 0);
+                    for (int h = 0; h < 2; ++h) a[m][rb][h][j] = in ? ld_once(wrow[m][rb][h] + k, once) : make_uint4(0, 0, 0, 0);
         }
         if (!waited) {
             pdl_wait();

@@ -55,6 +55,7 @@ struct Params {
     int pair_div;                      // > 0: one tile per (token, slot) pair, see q6k_gemm_tc_pairs
     int lists_old;                     // the pair list was written before the kernel launched before this one started: weights may be fetched before the wait
     int n_y, n_z;                      // row tiles (or pairs; an upper bound when num_tiles is given) and K slices
+    int w_once;                        // every weight tile is fetched by one CTA only (or by a few side by side): its lines may leave the L2 cache first
 };
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) with the
@@ -192,6 +193,11 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
     if (warp == 0) {
         if (lane == 0) {
             int pre = 0;                                   // k-blocks whose weights went out before the wait
+            const uint64_t once = l2_evict_first_policy();
+            auto load_w = [&](uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+                if (p.w_once) tma_load_2d_once(dst, map, x, y, bar, once);
+                else tma_load_2d(dst, map, x, y, bar);
+            };
             if (early) {
                 for (int t = blockIdx.x; t < total && pre < stages; t += gridDim.x) {
                     Tile tl;
@@ -202,8 +208,8 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
                         const uint32_t fb = full0 + 8 * pre;
                         mbar_expect_tx(fb, STAGE_BYTES);
                         const int kx = (tl.kb0 + i) * BK;
-                        tma_load_2d(st, &tm_w, kx, wy, fb);
-                        if (DUAL) tma_load_2d(st + W_BYTES, &tm_w2, kx, wy, fb);
+                        load_w(st, &tm_w, kx, wy, fb);
+                        if (DUAL) load_w(st + W_BYTES, &tm_w2, kx, wy, fb);
                     }
                 }
                 pdl_wait();
@@ -226,8 +232,8 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
                             break;
                         }
                         mbar_expect_tx(fb, STAGE_BYTES);
-                        tma_load_2d(st, &tm_w, kx, wy, fb);
-                        if (DUAL) tma_load_2d(st + W_BYTES, &tm_w2, kx, wy, fb);
+                        load_w(st, &tm_w, kx, wy, fb);
+                        if (DUAL) load_w(st + W_BYTES, &tm_w2, kx, wy, fb);
                     }
                     tma_load_2d(st + W_BYTES * (DUAL ? 2 : 1), &tm_a, kx, tl.row0, fb);
                 }
@@ -797,6 +803,9 @@ Q6K_API int q6k_gemm_tc(const void* A, long long lda, int rows_total, const void
     p.out = out;
     p.tile_group = tile_group, p.tile_row0 = tile_row0, p.group_offsets = group_offsets, p.num_tiles = num_tiles;
     p.rows_total = rows_total, p.N = N, p.K = K, p.ldo = ldo, p.epilogue = epilogue;
+    // one row tile (dense), or groups of about one row tile each (experts with a prompt portion's rows): every
+    // weight tile is fetched once, or by the few row tiles of its group, which lie side by side
+    p.w_once = grouped ? (long long)rows_total <= 2LL * groups * bt : rows_total <= 128;
     const int kb = (K + BK - 1) / BK;
     int splits = 1;
     if (!grouped && !dual) {
@@ -891,5 +900,6 @@ Q6K_API int q6k_gemm_tc_pairs(const void* A, long long lda, int a_rows, const vo
     p.pair_div = pair_div;
     p.pair_order = pair_order;
     p.lists_old = lists_old;
+    p.w_once = 1;                          // a pair's weight tile is shared with the few pairs of the same expert, which run side by side
     return dual ? launch<16, true>(tw, tw2, ta, p, pairs, splits, st) : launch<16, false>(tw, tw2, ta, p, pairs, splits, st);
 }

@@ -23,11 +23,6 @@ namespace {
 
 constexpr int GEMV_WARPS = 8;
 
-__device__ __forceinline__ uint4 ld_stream(const void* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
 __device__ __forceinline__ void unpack8(const uint4& v, float* f) {
     const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
 #pragma unroll
@@ -50,6 +45,7 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, 4) gemv_kernel(const __nv_bfl
     // before that kernel has ended (programmatic dependent launch); the activations and the output wait for it
     if (!early) pdl_wait();                   // an ordinary kernel: the wait first, then the signal (see common.cuh)
     pdl_launch();
+    const uint64_t once = l2_evict_first_policy();
     constexpr bool DUAL = EPI == GEMV_SWIGLU;
     constexpr int RG = GEMV_WARPS / KW;                                   // groups of warps along the rows
     constexpr int SUMS = ROWS * TT * (DUAL ? 2 : 1);
@@ -77,8 +73,8 @@ __global__ void __launch_bounds__(GEMV_WARPS * 32, 4) gemv_kernel(const __nv_bfl
 #pragma unroll
             for (int r = 0; r < ROWS; ++r) {
                 const long long row = n0 + r < N ? n0 + r : N - 1;      // a ragged last group reads a valid row and drops the sum
-                wv[r] = ld_stream(w + row * K + k0);
-                if (DUAL) w2v[r] = ld_stream(w2 + row * K + k0);
+                wv[r] = ld_once(w + row * K + k0, once);
+                if (DUAL) w2v[r] = ld_once(w2 + row * K + k0, once);
             }
             if (early) {
                 pdl_wait();                                              // the weights are on their way; now the kernel before must be done

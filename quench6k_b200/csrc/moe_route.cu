@@ -27,11 +27,9 @@ namespace {
 // them, E <= 32 NL).  Writes the chosen experts and weights (renormalised if asked).  `total` divides softmax scores.
 // also_e (or null): a second place for the chosen experts (shared memory of the caller).
 //
-// One warp runs this alone, so what counts is the number of dependent instructions of a round.  With eight values
-// per lane each lane first sorts its own (a network of compare-exchanges: value descending, ties by index
-// ascending); a round then looks at the lanes' first entries only (two warp reductions), and the lane that held
-// the winner moves its entries up by one.  With more values per lane a round scans them.  Scores, their sum and
-// the stores wait until the rounds are over (lane r keeps round r's result).
+// One warp runs this alone (and mostly with a cold instruction cache: the code is kept short).  A round: the lane's
+// largest entry by a tree of integer maxima, its index by independent compares, two warp reductions, the winner's
+// entry marked.  Scores, their sum and the stores wait until the rounds are over (lane r keeps round r's result).
 template <int NL>
 __device__ __forceinline__ void warp_topk_regs(float (&val)[NL], int E, int k, int sigmoid, int renorm, float total, int* sel_e, float* sel_w,
                                                int* also_e = nullptr) {
@@ -39,54 +37,26 @@ __device__ __forceinline__ void warp_topk_regs(float (&val)[NL], int E, int k, i
     int bits[NL];
 #pragma unroll
     for (int i = 0; i < NL; ++i) bits[i] = lane + 32 * i < E ? __float_as_int(val[i]) : -1;      // -1: no expert / taken
-    constexpr bool SORTED = NL == 8;
-    [[maybe_unused]] int slot[NL];                       // sorted variant: which of the lane's experts an entry is
-    if constexpr (SORTED) {
-#pragma unroll
-        for (int i = 0; i < NL; ++i) slot[i] = i;
-        auto cx = [&](int a, int b) {                    // the greater value first; of equal ones the lower index
-            const bool swap = bits[b] > bits[a] || (bits[b] == bits[a] && slot[b] < slot[a]);
-            const int ba = bits[a], sa = slot[a];
-            bits[a] = swap ? bits[b] : ba, slot[a] = swap ? slot[b] : sa;
-            bits[b] = swap ? ba : bits[b], slot[b] = swap ? sa : slot[b];
-        };
-        cx(0, 1), cx(2, 3), cx(4, 5), cx(6, 7);
-        cx(0, 2), cx(1, 3), cx(4, 6), cx(5, 7);
-        cx(1, 2), cx(5, 6);
-        cx(0, 4), cx(1, 5), cx(2, 6), cx(3, 7);
-        cx(2, 4), cx(3, 5);
-        cx(1, 2), cx(3, 4), cx(5, 6);
-    }
     int my_top = -1, my_e = 0;                           // lane r: the bits of the r-th score and its expert (r < 32)
     for (int r = 0; r < k; ++r) {
-        int best, best_i = 0;
-        if constexpr (SORTED) {
-            best = bits[0], best_i = slot[0];
-        } else {
-            int m[NL];
+        int m[NL];
 #pragma unroll
-            for (int i = 0; i < NL; ++i) m[i] = bits[i];
+        for (int i = 0; i < NL; ++i) m[i] = bits[i];
 #pragma unroll
-            for (int w = 1; w < NL; w *= 2)
+        for (int w = 1; w < NL; w *= 2)
 #pragma unroll
-                for (int i = 0; i + w < NL; i += 2 * w) m[i] = max(m[i], m[i + w]);
-            best = m[0];
+            for (int i = 0; i + w < NL; i += 2 * w) m[i] = max(m[i], m[i + w]);
+        const int best = m[0];
+        int best_i = 0;
 #pragma unroll
-            for (int i = NL - 1; i >= 0; --i)            // the first of equal ones: the lane's lowest expert
-                if (bits[i] == best) best_i = i;
-        }
+        for (int i = NL - 1; i >= 0; --i)                // the first of equal ones: the lane's lowest expert
+            if (bits[i] == best) best_i = i;
         const int top = __reduce_max_sync(0xffffffffu, best);
         const int idx = __reduce_min_sync(0xffffffffu, best == top ? lane + 32 * best_i : 0x7fffffff);      // ties: the lower expert
         const bool won = (idx & 31) == lane;
-        if constexpr (SORTED) {
 #pragma unroll
-            for (int i = 0; i + 1 < NL; ++i) bits[i] = won ? bits[i + 1] : bits[i], slot[i] = won ? slot[i + 1] : slot[i];
-            bits[NL - 1] = won ? -1 : bits[NL - 1];
-        } else {
-#pragma unroll
-            for (int i = 0; i < NL; ++i)
-                if (won && i == (idx >> 5)) bits[i] = -1;
-        }
+        for (int i = 0; i < NL; ++i)
+            if (won && i == (idx >> 5)) bits[i] = -1;
         if (lane == (r & 31)) {
             if (r >= 32) {                               // the lane's earlier result makes room (more than 32 per token: rare)
                 sel_e[r - 32] = my_e, sel_w[r - 32] = __int_as_float(my_top);
@@ -249,8 +219,9 @@ __host__ __device__ inline size_t rc_fixed_bytes(int RB, int NB, int E) {       
     return (size_t)RC_WARPS * RB * NB * 128 * sizeof(float) + (size_t)NB * 8 * E * sizeof(float) + RC_PAIRS * sizeof(int) + 128;
 }
 
-__device__ __forceinline__ void rc_bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+__device__ __forceinline__ void rc_bulk_copy(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(dst), "l"(src),
+                 "r"(bytes), "r"(bar), "l"(policy)
                  : "memory");
 }
 __device__ __forceinline__ void rc_mma(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -284,14 +255,15 @@ __global__ void __cluster_dims__(RC_CL, 1, 1) __launch_bounds__(RC_WARPS * 32, 1
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    // chunk c into buffer c % bufs: warp 0, a row per lane
+    // chunk c into buffer c % bufs: warp 0, a row per lane (the matrix is read once a step)
+    const uint64_t once = l2_evict_first_policy();
     auto stage = [&](int c) {
         const int rows_here = min(CR, n_rows - c * CR), b = c % bufs;
         const uint32_t bar = smem_u32(&bars[b]);
         if (lane == 0) mbar_expect_tx(bar, (uint32_t)rows_here * D * 2);
         __syncwarp();
         for (int r = lane; r < rows_here; r += 32)
-            rc_bulk_copy(smem_u32(wbuf + ((size_t)b * CR + r) * stride), w + (size_t)(e_begin + c * CR + r) * D, (uint32_t)D * 2, bar);
+            rc_bulk_copy(smem_u32(wbuf + ((size_t)b * CR + r) * stride), w + (size_t)(e_begin + c * CR + r) * D, (uint32_t)D * 2, bar, once);
     };
     if (warp == 0)
         for (int c = 0; c < chunks && c < bufs; ++c) stage(c);

@@ -68,6 +68,7 @@ class Attention(Mixer):
         write = cache.write
         # which attention kernels this step takes, and the plan of the key splits, before anything of the layer is
         # launched: the kernel that splits the keys reads its plan while the kernel before it still runs
+        ops.current_tag = "attention.plan"
         how = self._choose(cache, ctx)
         rotary = self.pos.rotary_table()
         fused_pos = rotary is not None or self.pos.is_identity

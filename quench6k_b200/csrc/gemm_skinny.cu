@@ -33,7 +33,7 @@ enum { SK_STORE = 0, SK_ADD = 1, SK_SWIGLU = 2 };
 template <int NB, int RB, int EPI, int LOADS>
 __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(const __nv_bfloat16* x, long long ldx, int T_,
                                                                     const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ w2,
-                                                                    void* out, long long ldo, int N, int K) {
+                                                                    void* out, long long ldo, int N, int K, int k_slice, long long slice_stride) {
     // The weights are a model's and older than any kernel of the step: their first stretch is asked for while the kernel
     // launched before this one still runs (programmatic dependent launch); the activations and the output wait for it.
     pdl_launch();
@@ -69,12 +69,14 @@ __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(const __nv_b
         xrow[nb] = x + (long long)(live[nb] ? nb * 8 + quad : 0) * ldx + pair * 8;
     }
     constexpr int STRETCH = 32 * LOADS;
-    for (int k0 = warp * STRETCH; k0 < K; k0 += SK_WARPS * STRETCH) {
+    // blockIdx.y: a slice of K of its own (k_slice elements), whose sums go to a slice of the output (plain stores only)
+    const int k_begin = blockIdx.y * k_slice, k_end = min(K, k_begin + k_slice);
+    for (int k0 = k_begin + warp * STRETCH; k0 < k_end; k0 += SK_WARPS * STRETCH) {
         uint4 a[MATS][RB][2][LOADS], b[NB][LOADS];
 #pragma unroll
         for (int j = 0; j < LOADS; ++j) {
             const int k = k0 + j * 32;                       // the lane's eight elements start at k + 8 pair
-            const bool in = k + pair * 8 < K;                // K is a multiple of 8: a lane's 16 bytes are inside or outside as a whole
+            const bool in = k + pair * 8 < k_end;            // K and the slices are multiples of 8: a lane's 16 bytes are inside or outside as a whole
 #pragma unroll
             for (int m = 0; m < MATS; ++m)
 #pragma unroll
@@ -89,7 +91,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(const __nv_b
 #pragma unroll
         for (int j = 0; j < LOADS; ++j) {
             const int k = k0 + j * 32;
-            const bool in = k + pair * 8 < K;
+            const bool in = k + pair * 8 < k_end;
 #pragma unroll
             for (int nb = 0; nb < NB; ++nb)
                 b[nb][j] = in && live[nb] ? ld_after_wait(xrow[nb] + k) : make_uint4(0, 0, 0, 0);
@@ -130,7 +132,7 @@ __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(const __nv_b
             if (DUAL) s2 += meet[q][RB * NB * 4 * 32 + idx];
         }
         if (n >= N || t >= T_) continue;
-        const long long at = (long long)t * ldo + n;
+        const long long at = (long long)blockIdx.y * slice_stride + (long long)t * ldo + n;
         if (EPI == SK_SWIGLU) reinterpret_cast<__nv_bfloat16*>(out)[at] = __float2bfloat16_rn(s / (1.0f + __expf(-s)) * s2);
         else if (EPI == SK_ADD) reinterpret_cast<float*>(out)[at] += s;
         else reinterpret_cast<float*>(out)[at] = s;
@@ -140,11 +142,11 @@ __global__ void __launch_bounds__(SK_WARPS * 32) gemm_skinny_kernel(const __nv_b
 
 template <int NB, int RB, int LOADS>
 int skinny_launch(int epi, cudaStream_t st, const __nv_bfloat16* x, long long ldx, int T_, const __nv_bfloat16* w, const __nv_bfloat16* w2, void* out,
-                  long long ldo, int N, int K) {
-    const int grid = (N + RB * 16 - 1) / (RB * 16);
-    if (epi == SK_SWIGLU) q6k_launch_as(true, gemm_skinny_kernel<NB, 1, SK_SWIGLU, 4>, (N + 15) / 16, SK_WARPS * 32, 0, st, x, ldx, T_, w, w2, out, ldo, N, K);
-    else if (epi == SK_ADD) q6k_launch_as(true, gemm_skinny_kernel<NB, RB, SK_ADD, LOADS>, grid, SK_WARPS * 32, 0, st, x, ldx, T_, w, w2, out, ldo, N, K);
-    else q6k_launch_as(true, gemm_skinny_kernel<NB, RB, SK_STORE, LOADS>, grid, SK_WARPS * 32, 0, st, x, ldx, T_, w, w2, out, ldo, N, K);
+                  long long ldo, int N, int K, int slices, int k_slice, long long slice_stride) {
+    const dim3 grid((N + RB * 16 - 1) / (RB * 16), slices);
+    if (epi == SK_SWIGLU) q6k_launch_as(true, gemm_skinny_kernel<NB, 1, SK_SWIGLU, 4>, (N + 15) / 16, SK_WARPS * 32, 0, st, x, ldx, T_, w, w2, out, ldo, N, K, K, 0LL);
+    else if (epi == SK_ADD) q6k_launch_as(true, gemm_skinny_kernel<NB, RB, SK_ADD, LOADS>, grid, SK_WARPS * 32, 0, st, x, ldx, T_, w, w2, out, ldo, N, K, K, 0LL);
+    else q6k_launch_as(true, gemm_skinny_kernel<NB, RB, SK_STORE, LOADS>, grid, SK_WARPS * 32, 0, st, x, ldx, T_, w, w2, out, ldo, N, K, k_slice, slice_stride);
     return q6k_check_launch("gemm_skinny");
 }
 
@@ -160,23 +162,41 @@ Q6K_API int q6k_gemm_skinny_preferred(int tokens, int N, int K) {
     return tokens >= 3 || (long long)N * K > (64LL << 20);
 }
 
+// Slices of K for a plain product whose caller can add partial sums itself, when the matrix has too few rows to give
+// every SM two blocks of 16 (the o projection of a decode step): as many as bring the blocks to two per SM, each slice a
+// multiple of 1,024 elements (eight warps' stretches) and at least that long.  0: not for this kernel.
+Q6K_API int q6k_gemm_skinny_slices(int tokens, int N, int K) {
+    if (tokens < 3 || tokens > 16 || K % 8 || N < 512 || N >= 4096 || K < 2048) return 0;
+    const int blocks = (N + 15) / 16;
+    int slices = (2 * 148 + blocks - 1) / blocks;
+    if (slices > K / 1024) slices = K / 1024;
+    if (slices < 2) return 0;
+    const int k_slice = ((K + slices - 1) / slices + 1023) / 1024 * 1024;    // as q6k_gemm_skinny cuts it
+    return (K + k_slice - 1) / k_slice;
+}
+
 // x: bfloat16 [tokens <= 16, K] (row pitch ldx elements); w (and w2 for the SwiGLU epilogue): bfloat16 [N, K]; out: FP32
 // [tokens, N] (epi 0 store, 1 add) or bfloat16 [tokens, N] (epi 2: silu(x w^T) * (x w2^T)), row pitch ldo.
+// slices > 1 (epi 0 only): K is cut into that many slices, slice z's sums go to out + z * slice_stride floats.
 Q6K_API int q6k_gemm_skinny(const void* x, long long ldx, int tokens, const void* w, const void* w2, int N, int K, void* out, long long ldo, int epi,
-                            cudaStream_t st) {
+                            int slices, long long slice_stride, cudaStream_t st) {
     if (tokens == 0) return 0;
     Q6K_REQUIRE(tokens >= 1 && tokens <= 16, "gemm_skinny: %d tokens (1 to 16)", tokens);
     Q6K_REQUIRE(N > 0 && K > 0 && K % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)w2 & 15) == 0,
                 "gemm_skinny: K=%d and the row pitch %lld must be multiples of 8 and the operands 16-byte aligned", K, ldx);
     Q6K_REQUIRE(epi >= 0 && epi <= 2 && (epi == SK_SWIGLU) == (w2 != nullptr), "gemm_skinny: epilogue %d with%s a second matrix", epi, w2 ? "" : "out");
+    Q6K_REQUIRE(slices >= 1 && (slices == 1 || epi == SK_STORE), "gemm_skinny: %d slices of K with epilogue %d", slices, epi);
+    const int k_slice = slices == 1 ? K : ((K + slices - 1) / slices + 1023) / 1024 * 1024;
     const __nv_bfloat16 *xp = (const __nv_bfloat16*)x, *wp = (const __nv_bfloat16*)w, *w2p = (const __nv_bfloat16*)w2;
     // 32 rows per block where that still gives every SM two blocks; 16 otherwise
-    const bool wide = N >= 148 * 2 * 32, deep = K >= 4096 && !wide;          // long rows and few of them: eight loads per row at once
+    const bool wide = N >= 148 * 2 * 32, deep = k_slice >= 4096 && !wide;          // long rows and few of them: eight loads per row at once
+#define SK_GO(NB_, RB_, LOADS_) skinny_launch<NB_, RB_, LOADS_>(epi, st, xp, ldx, tokens, wp, w2p, out, ldo, N, K, slices, k_slice, slice_stride)
     if (tokens <= 8) {
-        if (wide) return skinny_launch<1, 2, 4>(epi, st, xp, ldx, tokens, wp, w2p, out, ldo, N, K);
-        if (deep) return skinny_launch<1, 1, 8>(epi, st, xp, ldx, tokens, wp, w2p, out, ldo, N, K);
-        return skinny_launch<1, 1, 4>(epi, st, xp, ldx, tokens, wp, w2p, out, ldo, N, K);
+        if (wide) return SK_GO(1, 2, 4);
+        if (deep) return SK_GO(1, 1, 8);
+        return SK_GO(1, 1, 4);
     }
-    if (deep) return skinny_launch<2, 1, 8>(epi, st, xp, ldx, tokens, wp, w2p, out, ldo, N, K);
-    return skinny_launch<2, 1, 4>(epi, st, xp, ldx, tokens, wp, w2p, out, ldo, N, K);
+    if (deep) return SK_GO(2, 1, 8);
+    return SK_GO(2, 1, 4);
+#undef SK_GO
 }

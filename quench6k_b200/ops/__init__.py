@@ -443,10 +443,21 @@ def gemm_skinny_preferred(tokens: int, N: int, K: int) -> bool:
     return bool(lib.q6k_gemm_skinny_preferred(_i(tokens), _i(N), _i(K)))
 
 
+@functools.lru_cache(maxsize=None)          # a question about sizes: asked of the library once
+def gemm_skinny_slices(tokens: int, N: int, K: int) -> int:
+    """Slices of K the mma.sync kernel for few tokens would cut a plain product into when the caller can add partial
+    sums itself (a matrix with too few rows to fill the SMs otherwise); 0: the product is not for this kernel."""
+    lib = library()
+    lib.q6k_gemm_skinny_slices.restype = ctypes.c_int
+    return lib.q6k_gemm_skinny_slices(_i(tokens), _i(N), _i(K))
+
+
 def gemm_skinny(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
-                accumulate: bool = False) -> torch.Tensor:
-    """out[t] (+)= x[t] @ w^T for at most 16 rows of x (bfloat16, FP32 sums and output) on mma.sync, no split of K over
-    blocks; with w2 the SwiGLU epilogue silu(x w^T) * (x w2^T) in bfloat16."""
+                accumulate: bool = False, slices: int = 1) -> torch.Tensor:
+    """out[t] (+)= x[t] @ w^T for at most 16 rows of x (bfloat16, FP32 sums and output) on mma.sync; with w2 the SwiGLU
+    epilogue silu(x w^T) * (x w2^T) in bfloat16.  K is not split over blocks unless slices > 1 (plain products only):
+    the result is then [slices, T, N] partial sums, a view of the device's scratch buffer that stays valid until the
+    next kernel that uses scratch; the consumer adds the slices in order."""
     if not tc_supported(x, w) or w.dim() != 2:
         raise KernelError("gemm_skinny: operands must be bfloat16 matrices with K a multiple of 8 and 16-byte aligned rows")
     T, K = x.shape
@@ -457,6 +468,13 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = N
     out_dtype = torch.bfloat16 if w2 is not None else torch.float32
     if w2 is not None:
         _need(w2, "w2", torch.bfloat16, w.shape)
+    if slices > 1:
+        if out is not None or epi != EPI_STORE:
+            raise KernelError("gemm_skinny: slices of K are for plain products into scratch")
+        out = _workspace(slices * T * N * 4, x.device)[: slices * T * N].view(slices, T, N)
+        _call("q6k_gemm_skinny", _ptr(x), _ll(x.stride(0)), _i(T), _ptr(w), _ptr(w2), _i(N), _i(K), _ptr(out), _ll(N), _i(epi), _i(slices),
+              _ll(T * N), _stream())
+        return out
     if out is None:
         if accumulate:
             raise KernelError("gemm_skinny: accumulate needs an output")
@@ -464,7 +482,8 @@ def gemm_skinny(x: torch.Tensor, w: torch.Tensor, w2: Optional[torch.Tensor] = N
     _need(out, "out", out_dtype)
     if out.shape[0] < T or out.shape[1] != N:
         raise KernelError(f"gemm_skinny: out has shape {tuple(out.shape)}, needs [{T}, {N}]")
-    _call("q6k_gemm_skinny", _ptr(x), _ll(x.stride(0)), _i(T), _ptr(w), _ptr(w2), _i(N), _i(K), _ptr(out), _ll(out.stride(0)), _i(epi), _stream())
+    _call("q6k_gemm_skinny", _ptr(x), _ll(x.stride(0)), _i(T), _ptr(w), _ptr(w2), _i(N), _i(K), _ptr(out), _ll(out.stride(0)), _i(epi), _i(1),
+          _ll(0), _stream())
     return out
 
 

@@ -29,6 +29,9 @@ def matmul(a: torch.Tensor, w: torch.Tensor, rt, out: Optional[torch.Tensor] = N
         if ops.gemm_skinny_preferred(a.shape[0], w.shape[0], w.shape[1]):  # up to 16 tokens against many rows: mma.sync, K not split over blocks
             return ops.gemm_skinny(a, w, out=out, accumulate=accumulate)
         if partials_ok and out is None and not accumulate and w.shape[0] % 4 == 0:
+            slices = ops.gemm_skinny_slices(a.shape[0], w.shape[0], w.shape[1])
+            if slices:                                                   # a few tokens against few rows: the same kernel, K in slices
+                return ops.gemm_skinny(a, w, slices=slices)
             return ops.gemm_tc(a, w, keep_partials=True)
         return ops.gemm_tc(a, w, out=out, accumulate=accumulate)
     return ops.gemm_simt(a, w, out=out, accumulate=accumulate)

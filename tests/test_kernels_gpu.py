@@ -402,6 +402,13 @@ def test_gemm_skinny(M, N, K):
         ops.gemm_skinny(_t(17, K, dtype=torch.bfloat16), w)
     assert ops.gemm_skinny_preferred(8, 5120, 2048) and ops.gemm_skinny_preferred(1, 151936, 2048)
     assert not ops.gemm_skinny_preferred(8, 2048, 4096) and not ops.gemm_skinny_preferred(1, 5120, 2048) and not ops.gemm_skinny_preferred(17, 5120, 2048)
+    # K in slices whose partial sums the caller adds: any number of slices gives the product
+    for slices in (2, 3, 5):
+        parts = ops.gemm_skinny(a, w, slices=slices)
+        assert parts.shape == (slices, M, N)
+        assert (parts.double().sum(0).cpu() - ref).abs().max() <= tol, slices
+    assert ops.gemm_skinny_slices(8, 2048, 4096) == 2 and ops.gemm_skinny_slices(8, 1024, 4096) == 4
+    assert ops.gemm_skinny_slices(8, 5120, 2048) == 0 and ops.gemm_skinny_slices(2, 2048, 4096) == 0 and ops.gemm_skinny_slices(8, 2048, 1024) == 0
 
 
 @pytest.mark.parametrize("T,k,E,D,I", [(1, 8, 256, 2048, 512), (2, 3, 7, 264, 40), (9, 2, 5, 72, 136)])

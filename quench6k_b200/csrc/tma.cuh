@@ -18,8 +18,8 @@ __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
 __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
-// Bounded wait for the phase of the given parity to complete.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+// Bounded wait for the phase of the given parity to complete: false when `limit` cycles have passed without it.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, long long limit = WAIT_LIMIT_CYCLES) {
     long long t0 = 0;
     for (uint32_t spin = 0;; ++spin) {
         uint32_t ok;
@@ -34,7 +34,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
         if ((spin & 255u) == 255u) {
             const long long now = clock64();
             if (t0 == 0) t0 = now;
-            else if (now - t0 > WAIT_LIMIT_CYCLES) return false;
+            else if (now - t0 > limit) return false;
         }
     }
 }

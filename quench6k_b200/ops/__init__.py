@@ -314,6 +314,15 @@ def tc_status() -> int:
     return lib.q6k_tc_status() or lib.q6k_attention_status() or lib.q6k_attention_tc_status() or lib.q6k_router_status()
 
 
+def selftest_wait_runs_out(limit_cycles: int = 2_000_000):
+    """Runs a kernel whose bounded mbarrier wait must run out (nothing ever arrives on its barrier):
+    (status, cycles waited); status 1 is the run-out the kernel has to record.  The product kernels'
+    waits go through the same routine with a limit of about two seconds."""
+    status, waited = ctypes.c_int(-1), ctypes.c_longlong()
+    _call("q6k_selftest_wait_runs_out", _ll(limit_cycles), ctypes.byref(status), ctypes.byref(waited), _stream())
+    return status.value, waited.value
+
+
 _workspaces = {}
 _retired = []                             # outgrown scratch stays allocated: recorded CUDA graphs still point at it
 

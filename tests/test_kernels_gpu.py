@@ -743,3 +743,16 @@ def test_attention_tc(Hq, Hkv, ps, window, sinks):
         assert ops.tc_status() == 0
         err = (out.double().cpu() - want).abs().max() / want.abs().max()
         assert err <= 1.5e-2, ("two kernels", err)
+
+
+def test_a_bounded_wait_that_runs_out_is_recorded_and_the_device_stays_usable():
+    """Every spin of the kernels on an mbarrier has a limit.  A kernel that waits on a barrier nothing arrives on
+    (limit: two million cycles, about a millisecond) comes back with the run-out recorded, having waited at least
+    that long, and the next kernels run as before."""
+    from quench6k_b200 import ops
+    status, waited = ops.selftest_wait_runs_out(2_000_000)
+    assert status == 1 and 2_000_000 <= waited < 50_000_000
+    x = _t(3, 1000, seed=5)
+    assert torch.equal(ops.argmax(x).long().cpu(), x.argmax(-1).cpu())
+    assert ops.tc_status() == 0                                  # no product kernel's wait has run out in this process
+

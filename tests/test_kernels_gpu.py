@@ -645,10 +645,12 @@ def test_attention_plan_shares_the_key_tiles(window, n_work, min_per):
 
 @pytest.mark.parametrize("scoring,renorm", [("softmax", True), ("sigmoid", False)])
 @pytest.mark.parametrize("T,E,k,D,I", [(1, 256, 8, 2048, 512), (8, 256, 8, 2048, 512), (16, 256, 8, 2048, 512), (8, 64, 6, 256, 128), (16, 10, 3, 72, 40), (2, 32, 4, 1024, 256),
-                                       (3, 16, 2, 640, 1024), (5, 300, 7, 128, 64)])
+                                       (3, 16, 2, 640, 1024), (5, 300, 7, 128, 64), (4, 704, 6, 2048, 64), (12, 520, 5, 3072, 64)])
 def test_decode_moe_path(scoring, renorm, T, E, k, D, I):
-    """router_small + per-pair expert tiles against float64.  The first and the last two sizes have
-    so few pairs that the pair products slice K over CTAs (both epilogues)."""
+    """router_small + per-pair expert tiles against float64.  The first and two of the small sizes have
+    so few pairs that the pair products slice K over CTAs (both epilogues).  The last two have more
+    experts per CTA of the router's cluster than fit its shared memory at once: their rows go through
+    one buffer, chunk after chunk (32 rows of 2,048, 16 rows of 3,072)."""
     from quench6k_b200 import ops
     x = _t(T, D, dtype=torch.bfloat16)
     wr = _t(E, D, dtype=torch.bfloat16, seed=1, scale=0.02)      # small: a saturated sigmoid would tie in FP32

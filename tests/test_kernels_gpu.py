@@ -537,8 +537,9 @@ def test_attention_mma(Hq, Hkv, hd, ps, window, sinks, mode):
 
 @pytest.mark.parametrize("Hq,Hkv,hd,ps,window,sinks,qk_norm,rd", [(32, 4, 128, 16, None, False, True, 128), (8, 2, 64, 8, None, True, True, 64),
                                                                    (6, 2, 128, 16, 100, True, False, 64), (16, 1, 64, 32, 37, False, True, 0),
-                                                                   (5, 5, 128, 4, None, False, True, 128), (12, 3, 128, 64, None, False, True, 128)])
-@pytest.mark.parametrize("few", [False, True])
+                                                                   (5, 5, 128, 4, None, False, True, 128), (12, 3, 128, 64, None, False, True, 128),
+                                                                   (4, 2, 64, 16, 50, True, True, 64)])
+@pytest.mark.parametrize("few", [False, True, "eight"])
 def test_attention_mma_prepares_q_and_keys(Hq, Hkv, hd, ps, window, sinks, qk_norm, rd, few):
     """The narrow tiles making q and the new keys themselves, from the FP32 q/k/v product: the
     pages afterwards hold the bits qk_prep writes, and the output is that of qk_prep followed by
@@ -549,7 +550,9 @@ def test_attention_mma_prepares_q_and_keys(Hq, Hkv, hd, ps, window, sinks, qk_no
     G = Hq // Hkv
     g = torch.Generator().manual_seed(Hq * 1000 + hd + (window or 0) + rd)
     lens = [700, 150, 333, 64, 65]
-    per = min(2, max(1, 16 // G)) if few else 1
+    if few == "eight" and G > 2:
+        pytest.skip("eight tokens to a tile need groups of at most two heads")
+    per = 8 if few == "eight" else min(2, max(1, 16 // G)) if few else 1      # eight: as many as the kernel prepares
     q_lens = [per] * len(lens)
     q_lens[1] = 1
     starts = [n - ql for n, ql in zip(lens, q_lens)]

@@ -213,13 +213,18 @@ Q6K_API int q6k_rmsnorm(float* x, const float* add, int add_splits, long long ad
                      (add_stride % 4 == 0) && (!pair_y || ((uintptr_t)pair_y & 15) == 0);
     if (vec) {
         const int v4 = (D / 4 + 255) / 256;
-        // With one or two rows the kernels around a norm inside the layers are matrix-vector streams of a few microseconds:
-        // the norm lets the one after it start, and fetch its first weights, under the one before it (measured on B200
-        // at 32,768 cached tokens: 1.37 -> 1.31 ms a step at one row, 1.93 -> 1.88 at two).  With more rows the kernel
-        // before is a tensor-core kernel that fills the SMs, and blocks parked beside it only get in its way (2.65 ->
-        // 2.69 ms at four rows, 4.03 -> 4.09 at eight); and the LM head behind the last norm, parked that early, took
-        // twice as long.
-        const int early = rows == nullptr && R <= 2;
+        // A norm inside the layers may let the kernel after it start, and fetch its first weights, under the kernel before
+        // the norm (that kernel reads nothing but weights before its own wait).  Whether that pays depends on the kernel
+        // before (measured on B200 at 32,768 cached tokens):
+        //  - one or two rows: the kernels around every norm are matrix-vector streams of a few microseconds, and it pays
+        //    (1.37 -> 1.31 ms a step at one row, 1.93 -> 1.88 at two);
+        //  - up to 16 rows, a norm that adds a product's result (the one between mixer and feed-forward: the o product
+        //    before it is a few-token kernel of small blocks, the router's cluster after it finds room beside them):
+        //    3.99 -> 3.94 ms a step at eight rows, 2.57 -> 2.55 at four;
+        //  - a norm that adds the experts' weighted rows at more than two rows comes after a tensor-core kernel that
+        //    fills the SMs, and blocks parked beside it only get in its way (4.03 -> 4.09 ms at eight rows); and the LM
+        //    head behind the last norm, parked that early, took twice as long.
+        const int early = rows == nullptr && (R <= 2 || (R <= 16 && add != nullptr && pair_y == nullptr));
 #define Q6K_NORM_GO(V4_, NB_) q6k_launch_as(early != 0, rmsnorm_reg_kernel<T, V4_, NB_>, R, 256, 0, st, x, add, add_splits, (size_t)add_stride, rows, w, eps, (T*)out, D, pair_y, pair_row, pair_w, S, early)
         Q6K_DISPATCH(dtype, {
             if (R <= 64) {
